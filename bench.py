@@ -1,0 +1,295 @@
+"""Serving benchmark: output tokens/s per box at fixed concurrency (plus p50 TTFT / ITL).
+
+    python bench.py --gpus 1 --steps 2 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+
+Workload (the Llama-3-8B serving configuration): Llama-3-8B architecture, bf16, random-init
+weights, uniform-random token ids, fixed input 1024 / output 256 tokens, greedy, `--conc`
+(256) requests in flight, tensor parallel over the N GPUs.  One *step* is one wave: `conc`
+requests taken from arrival to their last token (16 chunked-prefill passes of 16384 tokens and
+255 decode passes at batch 256, CUDA-graph replayed, sampling included); 2 steps are the 512
+requests of the configuration.
+
+Two measurements of the same metric:
+  value : device-timed (CUDA events around K waves, max over ranks).  The wave is driven through
+          the model runner with the sampled tokens staying on the device, so it is the kernel
+          throughput of the whole serving step with no host round trip per token.
+  e2e   : K waves through the public offline API `LLM.generate` (admission queue, radix cache,
+          per-step H2D of the step's indices / prompt ids from pinned memory, per-step D2H of
+          the sampled tokens, stop checks), host clock, max over ranks.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+MODELS = {
+    "llama3-8b": dict(model_type="llama", hidden_size=4096, num_hidden_layers=32, num_attention_heads=32,
+                      num_key_value_heads=8, head_dim=128, intermediate_size=14336, vocab_size=128256,
+                      rms_norm_eps=1e-5, rope_theta=5e5, eos_token_id=128001, torch_dtype="bfloat16"),
+    "llama3-70b": dict(model_type="llama", hidden_size=8192, num_hidden_layers=80, num_attention_heads=64,
+                       num_key_value_heads=8, head_dim=128, intermediate_size=28672, vocab_size=128256,
+                       rms_norm_eps=1e-5, rope_theta=5e5, eos_token_id=128001, torch_dtype="bfloat16"),
+    "tiny": dict(model_type="llama", hidden_size=1024, num_hidden_layers=2, num_attention_heads=8,
+                 num_key_value_heads=2, head_dim=128, intermediate_size=2816, vocab_size=32000, rms_norm_eps=1e-5,
+                 rope_theta=5e5, eos_token_id=2, torch_dtype="bfloat16"),
+}
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="llama3-8b")
+    ap.add_argument("--conc", type=int, default=256)
+    ap.add_argument("--in-len", type=int, default=1024)
+    ap.add_argument("--out-len", type=int, default=256)
+    ap.add_argument("--batch-max-tokens", type=int, default=16384)
+    ap.add_argument("--skip-e2e", action="store_true")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.path = f"/tmp/llb_clocks_{os.getpid()}.csv"
+        self.proc = None
+        self.gpu_index = gpu_index
+
+    def start(self):
+        try:
+            self.f = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.gpu_index)], stdout=self.f,
+                                         stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.f.close()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        try:
+            for line in open(self.path):
+                p = [x.strip() for x in line.split(",")]
+                if len(p) < 9:
+                    continue
+                sm.append(float(p[1]))
+                mx.append(float(p[2]))
+                for n, v in zip(names, p[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(n)
+            os.remove(self.path)
+        except Exception:
+            pass
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        busy = [s for s in sm if s >= 0.5 * max(sm)] or sm
+        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def reference_arm(args):
+    """The unmodified reference engine (installed under baseline/_ref) on the same workload."""
+    try:
+        from baseline import reference_runner  # noqa: WPS433
+    except Exception as e:  # pragma: no cover
+        print(json.dumps({"impl": "reference", "unavailable": f"reference runner not importable: {e}"[:300]}))
+        return
+    reference_runner.main(args, MODELS)
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        reference_arm(args)
+        return
+    import torch
+
+    from lightllm_b200 import ops
+    from lightllm_b200.common.infer_state import ModelInput
+    from lightllm_b200.engine.llm import LLM
+    from lightllm_b200.parallel import dist as pdist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run"
+    ps = pdist.init_from_env()
+    dev = ps.device
+    rank = ps.global_rank
+    cfg = dict(MODELS[args.model])
+    conc, in_len, out_len = args.conc, args.in_len, args.out_len
+    total_len = in_len + out_len
+    pool_tokens = conc * (total_len + 8) + args.batch_max_tokens
+    llm = LLM(config=cfg, max_total_token_num=pool_tokens, running_max_req_size=conc, max_req_total_len=total_len + 8,
+              batch_max_tokens=args.batch_max_tokens, chunked_prefill_size=args.batch_max_tokens // 2,
+              disable_dynamic_prompt_cache=False, graph_max_batch_size=conc)
+    model = llm.model
+    llm.warmup([conc])
+    rng = np.random.default_rng(1234)
+
+    def new_prompts():
+        return rng.integers(1000, cfg["vocab_size"] - 1000, size=(conc, in_len), dtype=np.int64)
+
+    sp = {"max_new_tokens": out_len, "ignore_eos": True, "do_sample": False}
+
+    # ---------------- device-timed wave through the model runner ----------------
+    per_pass = max(1, args.batch_max_tokens // in_len)
+    req_ids = torch.arange(conc, dtype=torch.int32)
+
+    cuda = dev.type == "cuda"
+    pin = (lambda t: t.pin_memory()) if cuda else (lambda t: t)
+    seq_all = pin(torch.arange(in_len, total_len, dtype=torch.int32).view(-1, 1).repeat(1, conc).contiguous())
+    b_req = pin(req_ids.clone())
+    prefill_meta = []
+    for s in range(0, conc, per_pass):
+        e = min(conc, s + per_pass)
+        B = e - s
+        prefill_meta.append((s, e, pin(req_ids[s:e].clone()), pin(torch.full((B,), in_len, dtype=torch.int32)),
+                             pin(torch.zeros(B, dtype=torch.int32))))
+
+    def static_wave(prompts_np):
+        mm = model.mem_manager
+        mm.free_all()
+        slots = mm.alloc(conc * total_len).clone().view(conc, total_len)
+        slots_t = pin(slots.t().contiguous())           # [position, request]
+        ids_all = pin(torch.from_numpy(prompts_np))
+        nxt = model.req_manager.req_to_next_token_ids
+        tok = None
+        for s, e, reqs_p, len_p, zero_p in prefill_meta:
+            B = e - s
+            mi = ModelInput(batch_size=B, total_token_num=B * in_len, max_kv_len=in_len, is_prefill=True,
+                            b_req_idx=reqs_p, b_seq_len=len_p,
+                            mem_indexes=pin(slots[s:e, :in_len].reshape(-1).contiguous()),
+                            input_ids=ids_all[s:e].reshape(-1), b_ready_cache_len=zero_p, b_q_len=len_p,
+                            max_q_len=in_len)
+            out = model.forward(mi)
+            tok, _ = ops.sample(out.logits)
+            ops.scatter_next_token_(nxt, tok, dev_req[s:e])
+        for t in range(1, out_len):
+            L = in_len + t
+            mi = ModelInput(batch_size=conc, total_token_num=conc * L, max_kv_len=L, is_prefill=False, b_req_idx=b_req,
+                            b_seq_len=seq_all[t], mem_indexes=slots_t[L - 1])
+            out = model.forward(mi)
+            tok, _ = ops.sample(out.logits)
+            ops.scatter_next_token_(nxt, tok, dev_req)
+        return tok
+
+    dev_req = req_ids.to(dev)
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        if cuda:
+            torch.cuda.synchronize(dev)
+
+    class _HostEvent:  # CPU dry runs only
+        def record(self):
+            self.t = time.time()
+
+        def elapsed_time(self, other):
+            return (other.t - self.t) * 1e3
+
+    for _ in range(args.warmup):
+        static_wave(new_prompts())
+    barrier()
+    clocks = ClockSampler(dev.index or 0)
+    clocks.start()
+    n0 = ops.launch_count()
+    ev0, ev1 = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) if cuda else \
+        (_HostEvent(), _HostEvent())
+    ev0.record()
+    for _ in range(args.steps):
+        static_wave(new_prompts())
+    ev1.record()
+    barrier()
+    dev_ms = ev0.elapsed_time(ev1)
+    launches = ops.launch_count() - n0
+    clock_info = clocks.stop()
+    status = int(ops.gemm_status(dev).item()) if cuda else 0
+    model.mem_manager.free_all()
+
+    # ---------------- end to end through the public API ----------------
+    e2e = None
+    ttft_p50 = itl_p50 = None
+    if not args.skip_e2e:
+        h2d0 = d2h0 = 0
+        for _ in range(min(args.warmup, 1)):
+            llm.generate(new_prompts().tolist(), sp)
+        barrier()
+        st0 = dict(llm.backend.stats)
+        t0 = time.time()
+        ttfts, itls = [], []
+        for _ in range(args.steps):
+            outs, _ = llm.generate(new_prompts().tolist(), sp, return_stats=True)
+            for o in outs:
+                if o["ttft_s"] is not None:
+                    ttfts.append(o["ttft_s"])
+                tt = o["token_times"]
+                if len(tt) > 1:
+                    itls.append((tt[-1] - tt[0]) / (len(tt) - 1))
+        barrier()
+        e2e_s = time.time() - t0
+        st1 = llm.backend.stats
+        fwd = (st1["prefill_steps"] - st0["prefill_steps"]) + (st1["decode_steps"] - st0["decode_steps"])
+        e2e = {"seconds": e2e_s, "h2d": (st1["h2d_bytes"] - st0["h2d_bytes"]) / max(fwd, 1),
+               "d2h": (st1["d2h_bytes"] - st0["d2h_bytes"]) / max(fwd, 1)}
+        ttft_p50 = statistics.median(ttfts) * 1e3 if ttfts else None
+        itl_p50 = statistics.median(itls) * 1e3 if itls else None
+
+    # ---------------- max over ranks, print ----------------
+    vals = torch.tensor([dev_ms, e2e["seconds"] if e2e else 0.0], dtype=torch.float64, device=dev)
+    if world > 1:
+        torch.distributed.all_reduce(vals, op=torch.distributed.ReduceOp.MAX)
+    dev_ms, e2e_s = float(vals[0]), float(vals[1])
+    out_tokens = args.steps * conc * out_len
+    value = out_tokens / (dev_ms / 1e3)
+    if rank == 0:
+        line = {
+            "metric": "output tok/s per box at fixed concurrency", "value": round(value, 1), "unit": "tokens/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(dev_ms / args.steps, 2), "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform-random token ids, random-init weights",
+            "impl": "ours",
+            "config": {"model": args.model, "global_batch": conc, "seq_len": total_len, "input_len": in_len,
+                       "output_len": out_len, "parallelism": f"tp{args.gpus}", "step": "one wave of `global_batch` requests, prefill + all decode steps + sampling",
+                       "l2": "inputs larger than L2 (weights and KV pool are streamed every pass)",
+                       "gemm_wait_status": status},
+            "clocks": clock_info, "gpu_launches": launches,
+        }
+        if e2e:
+            line["e2e"] = {"value": round(out_tokens / e2e_s, 1), "unit": "tokens/s",
+                           "h2d_bytes_per_step": round(e2e["h2d"], 1), "d2h_bytes_per_step": round(e2e["d2h"], 1),
+                           "bytes_are_per": "forward pass (prefill chunk or decode step)",
+                           "p50_ttft_ms": round(ttft_p50, 2) if ttft_p50 else None,
+                           "p50_itl_ms": round(itl_p50, 3) if itl_p50 else None}
+        print(json.dumps(line), flush=True)
+    pdist.destroy()
+
+
+if __name__ == "__main__":
+    main()

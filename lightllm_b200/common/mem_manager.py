@@ -1,0 +1,172 @@
+"""Token-level KV pool ("TokenAttention"): page size = one token.
+
+``kv_buffer[layer, slot, 2*kv_heads_per_rank, head_dim]`` with K heads first, V heads second;
+slot ``size`` is the HOLD slot that padded (inactive) batch rows write to.  A stack allocator
+hands out slot indices; a request's slots need not be contiguous.  Sized for HBM3e: by default
+the pool takes ``mem_fraction`` of the memory left after weights (180 GB parts hold >1M tokens
+of an 8B model).
+
+Behavioural counterpart: lightllm/common/kv_cache_mem_manager/mem_manager.py:61-161 and
+allocator.py:11-80.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import numpy as np
+import torch
+
+
+class SlotAllocator:
+    """LIFO stack of free slot ids (host side, int32).  `alloc` returns a pinned int32 tensor taken
+    from a small ring so an async H2D copy of the previous step's result stays valid."""
+
+    RING = 4
+
+    def __init__(self, size: int, pin: bool = False):
+        self.size = size
+        self._stack = np.arange(size, dtype=np.int32)
+        self._top = 0  # _stack[_top:] are free
+        self._pin = pin and torch.cuda.is_available()
+        self._ring = [None] * self.RING
+        self._ring_i = 0
+        self._on_change = None
+
+    @property
+    def can_use_mem_size(self) -> int:
+        return self.size - self._top
+
+    def set_listener(self, fn):
+        self._on_change = fn
+
+    def _buf(self, n: int) -> torch.Tensor:
+        i = self._ring_i
+        self._ring_i = (i + 1) % self.RING
+        b = self._ring[i]
+        if b is None or b.numel() < n:
+            cap = max(n, 4096)
+            b = torch.empty(cap, dtype=torch.int32, pin_memory=self._pin)
+            self._ring[i] = b
+        return b[:n]
+
+    def alloc(self, n: int) -> torch.Tensor:
+        if n > self.can_use_mem_size:
+            raise MemoryError(f"KV pool exhausted: need {n}, free {self.can_use_mem_size}")
+        out = self._buf(n)
+        out.numpy()[:] = self._stack[self._top:self._top + n]
+        self._top += n
+        if self._on_change:
+            self._on_change(self.can_use_mem_size)
+        return out
+
+    def free(self, idx) -> None:
+        if isinstance(idx, torch.Tensor):
+            idx = idx.detach().cpu().numpy()
+        idx = np.asarray(idx, dtype=np.int32).reshape(-1)
+        n = idx.shape[0]
+        if n == 0:
+            return
+        assert self._top - n >= 0, "double free of KV slots"
+        self._top -= n
+        self._stack[self._top:self._top + n] = idx
+        if self._on_change:
+            self._on_change(self.can_use_mem_size)
+
+    def free_all(self) -> None:
+        self._stack = np.arange(self.size, dtype=np.int32)
+        self._top = 0
+        if self._on_change:
+            self._on_change(self.can_use_mem_size)
+
+
+class MemoryManager:
+    """GQA/MHA pool.  `head_num` is the number of KV heads held by this rank."""
+
+    def __init__(self, size: int, dtype: torch.dtype, head_num: int, head_dim: int, layer_num: int,
+                 device: torch.device, always_copy: bool = False):
+        self.size = int(size)
+        self.dtype = dtype
+        self.head_num = head_num
+        self.head_dim = head_dim
+        self.layer_num = layer_num
+        self.device = device
+        self.HOLD_TOKEN_MEMINDEX = self.size
+        self.allocator = SlotAllocator(self.size, pin=device.type == "cuda")
+        self._init_buffers()
+
+    # subclasses (MLA, quantised KV) override the next two
+    def kv_row_shape(self):
+        return (2 * self.head_num, self.head_dim)
+
+    def _init_buffers(self):
+        self.kv_buffer = torch.zeros((self.layer_num, self.size + 1, *self.kv_row_shape()), dtype=self.dtype,
+                                     device=self.device)
+
+    @staticmethod
+    def bytes_per_token(dtype, head_num, head_dim, layer_num) -> int:
+        return layer_num * 2 * head_num * head_dim * torch.empty((), dtype=dtype).element_size()
+
+    @property
+    def can_use_mem_size(self) -> int:
+        return self.allocator.can_use_mem_size
+
+    def alloc(self, n: int) -> torch.Tensor:
+        return self.allocator.alloc(n)
+
+    def free(self, idx) -> None:
+        self.allocator.free(idx)
+
+    def free_all(self) -> None:
+        self.allocator.free_all()
+
+    def layer(self, i: int) -> torch.Tensor:
+        return self.kv_buffer[i]
+
+    # ---- KV movement (prefix copies, PD staging pages, host offload) ----
+    def gather_pages(self, slots: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """[L, n, ...] staging copy of the given slots (device or pinned-host destination)."""
+        from .. import ops
+
+        n = slots.shape[0]
+        if out is None:
+            out = torch.empty((self.layer_num, n, *self.kv_row_shape()), dtype=self.dtype, device=self.device)
+        idx = slots.to(self.device, torch.int32)
+        for l in range(self.layer_num):
+            ops.copy_rows(out[l], self.kv_buffer[l], None, idx, n)
+        return out
+
+    def scatter_pages(self, slots: torch.Tensor, pages: torch.Tensor) -> None:
+        from .. import ops
+
+        n = slots.shape[0]
+        idx = slots.to(self.device, torch.int32)
+        for l in range(self.layer_num):
+            ops.copy_rows(self.kv_buffer[l], pages[l], idx, None, n)
+
+
+class MLAMemoryManager(MemoryManager):
+    """DeepSeek MLA latent cache: one row [kv_lora_rank + qk_rope_head_dim] per token and layer
+    (lightllm/common/kv_cache_mem_manager/deepseek2_mem_manager.py)."""
+
+    def __init__(self, size, dtype, kv_lora_rank, rope_dim, layer_num, device):
+        self.kv_lora_rank = kv_lora_rank
+        self.rope_dim = rope_dim
+        super().__init__(size, dtype, 1, kv_lora_rank + rope_dim, layer_num, device)
+
+    def kv_row_shape(self):
+        return (1, self.kv_lora_rank + self.rope_dim)
+
+    @staticmethod
+    def bytes_per_token(dtype, kv_lora_rank, rope_dim, layer_num) -> int:
+        return layer_num * (kv_lora_rank + rope_dim) * torch.empty((), dtype=dtype).element_size()
+
+
+def profile_max_tokens(device: torch.device, bytes_per_token: int, mem_fraction: float = 0.9,
+                       reserve_bytes: int = 6 << 30) -> int:
+    """Tokens that fit in `mem_fraction` of the currently free device memory, leaving `reserve_bytes`
+    for activations and CUDA graphs."""
+    if device.type != "cuda":
+        return 16384
+    free, total = torch.cuda.mem_get_info(device)
+    usable = int(free * mem_fraction) - reserve_bytes
+    return max(usable // bytes_per_token, 1024)

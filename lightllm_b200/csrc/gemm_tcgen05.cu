@@ -1,0 +1,426 @@
+// bf16 GEMM for sm_100a:  C[M, N] = A[M, K] . W[N, K]^T  (+ epilogue)
+//
+// Weights keep the checkpoint layout [out, in] (both operands K-major), which is exactly
+// what tcgen05.mma wants for A and B tiles in shared memory.
+//
+// Structure (one persistent CTA per SM, 192 threads):
+//   warp 0      TMA producer: 128 x 64 A tile + BN x 64 W tile per stage, 128-byte swizzle,
+//               completion counted on the stage's "full" mbarrier
+//   warp 1      MMA issuer: one thread issues tcgen05.mma (M=128, N=BN, K=16) x4 per stage into a
+//               TMEM accumulator; tcgen05.commit releases the stage / publishes the accumulator
+//   warps 2..5  epilogue: tcgen05.ld the fp32 accumulator (each warp its 32 TMEM lanes), apply the
+//               epilogue functor, store.  Two accumulators (2 x BN TMEM columns) so the epilogue
+//               of tile i overlaps the main loop of tile i+1.
+// Epilogues: plain store, + bias, + residual, SiLU/GELU-gated product of interleaved
+// gate/up column blocks (the SwiGLU FFN never materialises the [T, 2I] tensor), fp32 store
+// (lm_head logits).
+//
+// Behavioural counterpart in the reference: the cuBLAS calls behind
+// lightllm/common/quantization/no_quant.py (torch.mm / addmm), silu_and_mul_fwd and the
+// residual adds of the layer template.
+#include "sm100_ptx.cuh"
+
+using namespace llb;
+using namespace llb::sm100;
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;  // 64 bf16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int GEMM_THREADS = 192;
+constexpr int SMEM_BUDGET = 200 * 1024;
+
+enum Epi { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_GATED_SILU = 2, EPI_F32 = 3, EPI_GATED_GELU = 4 };
+
+struct GemmParams {
+  void* C;
+  const bf16* residual;  // [M, ldc] bf16 (EPI_RESIDUAL)
+  const bf16* bias;      // [N] or null
+  int* status;
+  int M, N, K;
+  int64_t ldc;  // elements
+  int num_m_blocks, num_n_blocks;
+};
+
+template <int BN>
+constexpr int stage_bytes() {
+  return BM * BK * 2 + BN * BK * 2;
+}
+template <int BN>
+constexpr int num_stages() {
+  return SMEM_BUDGET / stage_bytes<BN>() > 8 ? 8 : SMEM_BUDGET / stage_bytes<BN>();
+}
+template <int BN>
+constexpr int smem_bytes() {
+  return num_stages<BN>() * stage_bytes<BN>() + 1024 /*align slack*/ + 256 /*barriers*/;
+}
+
+__device__ __forceinline__ float silu_f(float v) { return v / (1.f + __expf(-v)); }
+__device__ __forceinline__ float gelu_tanh_f(float v) {
+  return 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+}
+
+// Tile order: groups of 8 M-blocks, M fastest inside a group, so CTAs running at the same time
+// share W tiles (decode: both M-blocks of one W tile) and re-read a bounded set of A tiles from L2.
+__device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int& mb, int& nb) {
+  constexpr int GROUP = 8;
+  int per_group = GROUP * num_n;
+  int grp = tile / per_group;
+  int first_m = grp * GROUP;
+  int gsz = min(GROUP, num_m - first_m);
+  int in = tile - grp * per_group;
+  mb = first_m + in % gsz;
+  nb = in / gsz;
+}
+
+template <int BN, int EPI>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const GemmParams p) {
+  constexpr int STAGES = num_stages<BN>();
+  constexpr int A_BYTES = BM * BK * 2;
+  constexpr int STAGE_BYTES = stage_bytes<BN>();
+  constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;  // power of two for BN in {32,64,128,256}
+  constexpr uint32_t IDESC = umma_idesc(BM, BN, 1);
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
+  auto full_bar = [&](int s) { return bar_base + 8 * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8 * (STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8 * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8 * (2 * STAGES + 2 + a); };
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_tiles = p.num_m_blocks * p.num_n_blocks;
+  const int k_blocks = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 4);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(smem_u32(&tmem_base_slot), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+        int mb, nb;
+        tile_coords(tile, p.num_m_blocks, p.num_n_blocks, mb, nb);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          mbar_wait(empty_bar(stage), phase ^ 1, &abort_flag, p.status, 1);
+          const uint32_t sa = smem_base + stage * STAGE_BYTES;
+          mbar_expect_tx(full_bar(stage), STAGE_BYTES);
+          tma_load_2d(sa, &tmA, full_bar(stage), kb * BK, mb * BM);
+          tma_load_2d(sa + A_BYTES, &tmB, full_bar(stage), kb * BK, nb * BN);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        mbar_wait(tempty_bar(acc), acc_phase ^ 1, &abort_flag, p.status, 2);
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          mbar_wait(full_bar(stage), phase, &abort_flag, p.status, 3);
+          tc_fence_after();
+          const uint32_t sa = smem_base + stage * STAGE_BYTES;
+          const uint64_t da = umma_smem_desc_sw128(sa);
+          const uint64_t db = umma_smem_desc_sw128(sa + A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // advancing K inside the 128-byte swizzle row: +32 bytes = +2 in 16-byte units
+            umma_bf16(d_tmem, da + 2 * k, db + 2 * k, IDESC, (kb | k) != 0);
+          }
+          umma_commit(empty_bar(stage));  // stage reusable once these MMAs have read it
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        umma_commit(tfull_bar(acc));  // accumulator complete
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ------------------------------
+    const int lane_grp = warp & 3;  // TMEM lanes 32*lane_grp .. +31 are the ones this warp may read
+    int it = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+      int mb, nb;
+      tile_coords(tile, p.num_m_blocks, p.num_n_blocks, mb, nb);
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      mbar_wait(tfull_bar(acc), acc_phase, &abort_flag, p.status, 4);
+      tc_fence_after();
+      const int row = mb * BM + lane_grp * 32 + lane;
+      const bool row_ok = row < p.M;
+      const uint32_t t_row = tmem_base + ((uint32_t)(lane_grp * 32) << 16) + acc * BN;
+
+      if (EPI == EPI_GATED_SILU || EPI == EPI_GATED_GELU) {
+        // columns come as [32 gate | 32 up] pairs; output has N/2 columns
+        bf16* crow = (bf16*)p.C + (int64_t)row * p.ldc;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 64) {
+          uint32_t gr[32], ur[32];
+          tmem_ld_32x32(t_row + c, gr);
+          tmem_ld_32x32(t_row + c + 32, ur);
+          tmem_wait_ld();
+          const int ocol = (nb * BN + c) / 2;
+          if (row_ok && nb * BN + c < p.N) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              float o[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                float gv = __uint_as_float(gr[j + e]);
+                float uv = __uint_as_float(ur[j + e]);
+                o[e] = (EPI == EPI_GATED_SILU ? silu_f(gv) : gelu_tanh_f(gv)) * uv;
+              }
+              *reinterpret_cast<bf16x8*>(crow + ocol + j) = pack8(o);
+            }
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_row + c, r);
+          tmem_wait_ld();
+          const int col0 = nb * BN + c;
+          if (row_ok && col0 < p.N) {
+            const int ncols = min(32, p.N - col0);
+            if (EPI == EPI_F32) {
+              float* crow = (float*)p.C + (int64_t)row * p.ldc + col0;
+              if (ncols == 32) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 4) {
+                  float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
+                                         __uint_as_float(r[j + 3]));
+                  if (p.bias) {
+                    v.x += __bfloat162float(p.bias[col0 + j]);
+                    v.y += __bfloat162float(p.bias[col0 + j + 1]);
+                    v.z += __bfloat162float(p.bias[col0 + j + 2]);
+                    v.w += __bfloat162float(p.bias[col0 + j + 3]);
+                  }
+                  *reinterpret_cast<float4*>(crow + j) = v;
+                }
+              } else {
+                for (int j = 0; j < ncols; ++j)
+                  crow[j] = __uint_as_float(r[j]) + (p.bias ? __bfloat162float(p.bias[col0 + j]) : 0.f);
+              }
+            } else {
+              bf16* crow = (bf16*)p.C + (int64_t)row * p.ldc + col0;
+              const bf16* rrow = EPI == EPI_RESIDUAL ? p.residual + (int64_t)row * p.ldc + col0 : nullptr;
+              if (ncols == 32) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                  float o[8];
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) o[e] = __uint_as_float(r[j + e]);
+                  if (p.bias) {
+                    float bv[8];
+                    unpack8(*reinterpret_cast<const bf16x8*>(p.bias + col0 + j), bv);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) o[e] += bv[e];
+                  }
+                  if (EPI == EPI_RESIDUAL) {
+                    float rv[8];
+                    unpack8(*reinterpret_cast<const bf16x8*>(rrow + j), rv);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) o[e] += rv[e];
+                  }
+                  *reinterpret_cast<bf16x8*>(crow + j) = pack8(o);
+                }
+              } else {
+                for (int j = 0; j < ncols; ++j) {
+                  float v = __uint_as_float(r[j]);
+                  if (p.bias) v += __bfloat162float(p.bias[col0 + j]);
+                  if (EPI == EPI_RESIDUAL) v += __bfloat162float(rrow[j]);
+                  crow[j] = __float2bfloat16(v);
+                }
+              }
+            }
+          }
+        }
+      }
+      // accumulator drained: hand it back to the MMA warp
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(acc));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---- host side ----
+struct MapKey {
+  const void* p;
+  uint64_t rows, cols, ld;
+  uint32_t box_rows;
+  bool operator==(const MapKey& o) const {
+    return p == o.p && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = (size_t)k.p;
+    h = h * 1000003u ^ k.rows;
+    h = h * 1000003u ^ k.cols;
+    h = h * 1000003u ^ k.ld;
+    h = h * 1000003u ^ k.box_rows;
+    return h;
+  }
+};
+std::mutex g_map_mu;
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
+
+int cached_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows) {
+  MapKey key{base, rows, cols, ld, box_rows};
+  std::lock_guard<std::mutex> lk(g_map_mu);
+  auto it = g_maps.find(key);
+  if (it != g_maps.end()) {
+    *out = it->second;
+    return LLB_OK;
+  }
+  int rc = make_tmap_2d(out, base, 2, rows, cols, ld, box_rows, BK);
+  if (rc) return rc;
+  if (g_maps.size() > 8192) g_maps.clear();
+  g_maps.emplace(key, *out);
+  return LLB_OK;
+}
+
+template <int BN, int EPI>
+int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, cudaStream_t st) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e =
+        cudaFuncSetAttribute(gemm_bf16_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<BN>());
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  p.num_m_blocks = cdiv(p.M, BM);
+  p.num_n_blocks = cdiv(p.N, BN);
+  int tiles = p.num_m_blocks * p.num_n_blocks;
+  int grid = tiles < sm_count() ? tiles : sm_count();
+  gemm_bf16_kernel<BN, EPI><<<grid, GEMM_THREADS, smem_bytes<BN>(), st>>>(ta, tb, p);
+  LLB_LAUNCH_CHECK();
+  return LLB_OK;
+}
+
+template <int BN>
+int dispatch_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, cudaStream_t st) {
+  switch (epi) {
+    case EPI_STORE:
+      return launch_gemm<BN, EPI_STORE>(ta, tb, p, st);
+    case EPI_RESIDUAL:
+      return launch_gemm<BN, EPI_RESIDUAL>(ta, tb, p, st);
+    case EPI_GATED_SILU:
+      return launch_gemm<BN, EPI_GATED_SILU>(ta, tb, p, st);
+    case EPI_F32:
+      return launch_gemm<BN, EPI_F32>(ta, tb, p, st);
+    case EPI_GATED_GELU:
+      return launch_gemm<BN, EPI_GATED_GELU>(ta, tb, p, st);
+  }
+  return LLB_ERR_UNSUPPORTED;
+}
+
+// Largest BN whose tile count wastes little of the last wave; small problems get small tiles so
+// that every SM streams a share of the weights.
+int pick_bn(int M, int N) {
+  const int sms = sm_count();
+  const int cands[3] = {256, 128, 64};
+  double best_eff = -1.0;
+  int best = 128;
+  for (int i = 0; i < 3; ++i) {
+    int bn = cands[i];
+    int64_t tiles = (int64_t)cdiv(M, BM) * cdiv(N, bn);
+    int64_t waves = (tiles + sms - 1) / sms;
+    double eff = (double)tiles / (double)(waves * sms);
+    if (eff > best_eff * 1.08) {  // prefer the larger tile unless the smaller one is clearly better
+      best_eff = eff;
+      best = bn;
+    }
+  }
+  return best;
+}
+
+}  // namespace
+
+// C[M,N] (ldc) = A[M,K] (lda) . W[N,K]^T (ldw)  with epilogue `epi`:
+//   0 store bf16 (+bias)          1 store bf16 of acc (+bias) + residual[M,N] (same ldc)
+//   2 SiLU-gated: W rows interleaved as [32 gate | 32 up] blocks; C is [M, N/2]
+//   3 store fp32 (+bias)          4 GELU(tanh)-gated, layout as 2
+// bn: 0 = choose, else 64/128/256.  status: optional device int receiving a wait-timeout code.
+LLB_EXPORT int llb_gemm_bf16(const void* A, int64_t lda, const void* W, int64_t ldw, void* C, int64_t ldc,
+                             const void* residual, const void* bias, int M, int N, int K, int epi, int bn,
+                             int* status, cudaStream_t st) {
+  if (M <= 0 || N <= 0) return LLB_OK;
+  if (K <= 0 || (K % 8) != 0) return LLB_ERR_UNSUPPORTED;
+  if ((epi == EPI_GATED_SILU || epi == EPI_GATED_GELU) && (N % 64) != 0) return LLB_ERR_UNSUPPORTED;
+  if (epi != EPI_F32 && (((uintptr_t)C & 15) || (ldc % 8))) return LLB_ERR_BAD_ARG;
+  if (epi == EPI_F32 && (((uintptr_t)C & 15) || (ldc % 4))) return LLB_ERR_BAD_ARG;
+  if (epi == EPI_RESIDUAL && (residual == nullptr || ((uintptr_t)residual & 15))) return LLB_ERR_BAD_ARG;
+  if (bn == 0) bn = pick_bn(M, N);
+  CUtensorMap ta, tb;
+  int rc = cached_tmap(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM);
+  if (rc) return rc;
+  rc = cached_tmap(&tb, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, (uint32_t)bn);
+  if (rc) return rc;
+  GemmParams p;
+  p.C = C;
+  p.residual = (const bf16*)residual;
+  p.bias = (const bf16*)bias;
+  p.status = status;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.ldc = ldc;
+  switch (bn) {
+    case 256:
+      return dispatch_epi<256>(epi, ta, tb, p, st);
+    case 128:
+      return dispatch_epi<128>(epi, ta, tb, p, st);
+    case 64:
+      return dispatch_epi<64>(epi, ta, tb, p, st);
+  }
+  return LLB_ERR_UNSUPPORTED;
+}

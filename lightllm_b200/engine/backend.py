@@ -1,0 +1,401 @@
+"""The per-GPU inference backend: turns the request table into prefill / decode forward passes,
+samples, and publishes results into the shared request objects.
+
+One backend per model-rank process.  All TP ranks of a replica run the same deterministic
+schedule on the same request list, so they stay in lock step without exchanging decisions;
+with data-parallel attention (`dp > 1`) replicas exchange only their (prefill, decode) counts
+per step and pad idle replicas with the HOLD request.
+
+Step anatomy (chunked prefill, the default mode):
+    classify -> [pause if the pool is short] -> prefill chunk(s) OR one decode step
+    -> sample on device -> token ids stay on device for the next decode (scatter into the request
+    table's next-token column) and are copied to pinned host memory for stop checks / detokenizer.
+
+Reference: lightllm/server/router/model_infer/mode_backend/base_backend.py (ModeBackend),
+chunked_prefill/impl.py (ChunkedPrefillBackend), generic_pre_process.py, generic_post_process.py.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass
+from typing import Callable, Dict, List, Optional
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..common.infer_state import ModelInput
+from ..server.core.objs.req import FinishStatus, Req
+from .infer_batch import InferenceContext, InferReq
+from .radix_cache import RadixCache
+
+
+@dataclass
+class BackendArgs:
+    batch_max_tokens: int = 16384
+    chunked_prefill_size: int = 8192
+    disable_chunked_prefill: bool = False
+    router_max_wait_tokens: int = 1
+    disable_aggressive_schedule: bool = False
+    disable_dynamic_prompt_cache: bool = False
+    eos_ids: tuple = ()
+    max_req_total_len: int = 8192
+    return_all_prompt_logprobs: bool = False
+    enable_prefill_decode_mixed: bool = False
+    pause_recover_interval: int = 100
+
+
+class PinnedRing:
+    """A few pinned host buffers per key used round-robin, so an async copy issued for step k is not
+    overwritten while step k+1 is prepared (reference: pin_mem_manager.py)."""
+
+    def __init__(self, depth: int = 4, pin: bool = True):
+        self.depth = depth
+        self.pin = pin and torch.cuda.is_available()
+        self._bufs: Dict[str, list] = {}
+        self._i: Dict[str, int] = {}
+
+    def get(self, key: str, n: int, dtype) -> torch.Tensor:
+        lst = self._bufs.setdefault(key, [None] * self.depth)
+        i = self._i.get(key, 0)
+        self._i[key] = (i + 1) % self.depth
+        b = lst[i]
+        if b is None or b.numel() < n or b.dtype != dtype:
+            b = torch.empty(max(n, 1024), dtype=dtype, pin_memory=self.pin)
+            lst[i] = b
+        return b[:n]
+
+    def from_numpy(self, key: str, arr: np.ndarray, dtype) -> torch.Tensor:
+        t = self.get(key, arr.shape[0], dtype)
+        t.numpy()[:] = arr
+        return t
+
+
+class ControlState:
+    """Prefill-vs-decode choice: aggressive = prefill whenever something waits; otherwise at most one
+    prefill per `router_max_wait_tokens` decode steps (reference: control_state.py)."""
+
+    def __init__(self, args: BackendArgs):
+        self.aggressive = not args.disable_aggressive_schedule
+        self.max_wait = args.router_max_wait_tokens
+        self.decode_since_prefill = 0
+        self.step = 0
+
+    def select(self, n_prefill: int, n_decode: int) -> str:
+        self.step += 1
+        if n_prefill == 0 and n_decode == 0:
+            return "idle"
+        if n_prefill == 0:
+            self.decode_since_prefill += 1
+            return "decode"
+        if n_decode == 0 or self.aggressive or self.decode_since_prefill >= self.max_wait:
+            self.decode_since_prefill = 0
+            return "prefill"
+        self.decode_since_prefill += 1
+        return "decode"
+
+
+class ModelBackend:
+    def __init__(self, model, args: Optional[BackendArgs] = None, is_master_in_dp: bool = True,
+                 on_token: Optional[Callable[[InferReq, int, float], None]] = None):
+        self.model = model
+        self.args = args or BackendArgs()
+        self.device = model.device
+        self.radix_cache = None if self.args.disable_dynamic_prompt_cache else \
+            RadixCache("radix", model.max_total_token_num, 0, model.mem_manager)
+        self.ctx = InferenceContext(model, self.radix_cache)
+        self.pins = PinnedRing(pin=self.device.type == "cuda")
+        self.control = ControlState(self.args)
+        self.is_master_in_dp = is_master_in_dp   # only one rank per replica writes into shm
+        self.on_token = on_token
+        self.eos_ids = set(self.args.eos_ids)
+        self.prefill_mask_func = None   # hooks for constrained decoding backends
+        self.decode_mask_func = None
+        self.extra_post_req_handle_func = None
+        self.stats = {"prefill_steps": 0, "decode_steps": 0, "prefill_tokens": 0, "decode_tokens": 0,
+                      "h2d_bytes": 0, "d2h_bytes": 0, "paused": 0}
+        self._steps = 0
+
+    # ------------------------------------------------------------------ requests
+    def add_reqs(self, shm_reqs: List[Req]) -> List[InferReq]:
+        out = []
+        for r in shm_reqs:
+            req = self.ctx.add_req(r)
+            if req is None:
+                raise RuntimeError("request table full: running_max_req_size must not exceed the model's max_req_num")
+            out.append(req)
+        return out
+
+    def abort(self, req_id: int):
+        req = self.ctx.requests.get(req_id)
+        if req is not None:
+            req.infer_aborted = True
+
+    def stop_str_matched(self, req_id: int):
+        req = self.ctx.requests.get(req_id)
+        if req is not None:
+            req.stop_str_matched = True
+
+    def has_work(self) -> bool:
+        return bool(self.ctx.requests)
+
+    # ------------------------------------------------------------------ classification
+    def _get_classed_reqs(self):
+        """Splits live requests into (prefill list with chunk sizes, decode list); finishes aborted ones;
+        pauses requests when the pool cannot serve the step."""
+        ctx, a = self.ctx, self.args
+        prefill, decode, finished = [], [], []
+        budget = a.batch_max_tokens
+        chunk_cap = a.batch_max_tokens if a.disable_chunked_prefill else a.chunked_prefill_size
+        can_alloc = ctx.get_can_alloc_token_num()
+        recover = (self._steps % a.pause_recover_interval == 0)
+        paused_now = 0
+        for rid in ctx.infer_req_ids:
+            req = ctx.requests[rid]
+            if req.finish_status.is_finished():
+                finished.append(req)
+                continue
+            if req.infer_aborted or req.stop_str_matched or req.shm_req.is_aborted:
+                if req.shm_req.is_aborted:
+                    req.infer_aborted = True
+                self._finish_without_token(req)
+                finished.append(req)
+                continue
+            if req.paused:
+                if recover and can_alloc > req.total_len() + 64:
+                    ctx.recover_req(req)
+                else:
+                    continue
+            if req.need_prefill():
+                remaining = req.total_len() - req.cur_kv_len
+                chunk = min(remaining, chunk_cap)
+                if chunk <= budget and chunk <= can_alloc:
+                    prefill.append((req, chunk))
+                    budget -= chunk
+                    can_alloc -= chunk
+            else:
+                if can_alloc >= 1:
+                    decode.append(req)
+                    can_alloc -= 1
+                elif paused_now < 2:  # pool exhausted: pause (at most two per step), re-prefill later
+                    ctx.pause_req(req)
+                    paused_now += 1
+                    self.stats["paused"] += 1
+                    can_alloc = ctx.get_can_alloc_token_num()
+        return prefill, decode, finished
+
+    def _finish_without_token(self, req: InferReq):
+        """Aborted / stop-string requests end with a synthetic final token so downstream stages drain."""
+        status = FinishStatus.FINISHED_ABORTED if req.infer_aborted else FinishStatus.FINISHED_STOP
+        if req.cur_output_len == 0 or req.infer_aborted:
+            eos = next(iter(self.eos_ids)) if self.eos_ids else 0
+            req.append_token(eos, 0.0)
+        req.finish_status.set_status(status)
+        if self.is_master_in_dp:
+            req.publish()
+
+    # ------------------------------------------------------------------ one step
+    @torch.no_grad()
+    def step(self) -> dict:
+        """Runs at most one forward pass.  Returns {"kind", "finished": [InferReq], "tokens": n}."""
+        self._steps += 1
+        prefill, decode, finished = self._get_classed_reqs()
+        kind = self.control.select(len(prefill), len(decode))
+        n_tok = 0
+        if kind == "prefill":
+            n_tok = self._run_prefill(prefill)
+        elif kind == "decode":
+            n_tok = self._run_decode(decode)
+        for req in list(self.ctx.requests.values()):
+            if req.finish_status.is_finished() and req not in finished:
+                finished.append(req)
+        for req in finished:
+            self.ctx.remove_req(req)
+        return {"kind": kind, "finished": finished, "tokens": n_tok}
+
+    # ---- prefill ----
+    def _run_prefill(self, items) -> int:
+        reqs = [r for r, _ in items]
+        B = len(reqs)
+        chunks = np.array([c for _, c in items], dtype=np.int32)
+        ready = np.array([r.cur_kv_len for r in reqs], dtype=np.int32)
+        total = int(chunks.sum())
+        ids = np.concatenate([r.get_chunked_input_token_ids(int(c)) for r, c in items])
+        slots = self.ctx.alloc_slots(total)
+        slots_np = slots.numpy()
+        off = 0
+        for r, c in items:
+            r.slots = np.concatenate([r.slots[: r.cur_kv_len], slots_np[off:off + c]])
+            off += int(c)
+        pin = self.pins
+        want_all = self.args.return_all_prompt_logprobs and any(r.sampling.prompt_logprobs >= 0 for r in reqs)
+        mi = ModelInput(batch_size=B, total_token_num=int((ready + chunks).sum()), max_kv_len=int((ready + chunks).max()),
+                        is_prefill=True,
+                        b_req_idx=pin.from_numpy("p_req", np.array([r.req_idx for r in reqs], dtype=np.int32), torch.int32),
+                        b_seq_len=pin.from_numpy("p_seq", ready + chunks, torch.int32),
+                        mem_indexes=slots,
+                        input_ids=pin.from_numpy("p_ids", ids.astype(np.int64), torch.int64),
+                        b_ready_cache_len=pin.from_numpy("p_ready", ready, torch.int32),
+                        b_q_len=pin.from_numpy("p_qlen", chunks, torch.int32), max_q_len=int(chunks.max()),
+                        return_all_logits=want_all)
+        self.stats["h2d_bytes"] += total * 8 + total * 4 + B * 16
+        out = self.model.forward(mi)
+        has_out = np.array([r.cur_kv_len + int(c) >= r.total_len() for r, c in items], dtype=bool)
+        for r, c in items:
+            r.cur_kv_len += int(c)
+        logits = out.logits
+        if want_all:
+            self._handle_prompt_logprobs(reqs, chunks, ids, logits)
+            last_rows = torch.from_numpy(np.cumsum(chunks) - 1).to(self.device)
+            logits = logits.index_select(0, last_rows)
+        if has_out.any():
+            self._sample_and_post(reqs, logits, has_out, is_prefill=True)
+        elif self.is_master_in_dp:
+            for r in reqs:
+                r.shm_req.shm_cur_kv_len = r.cur_kv_len
+        self.stats["prefill_steps"] += 1
+        self.stats["prefill_tokens"] += total
+        return int(has_out.sum())
+
+    def _handle_prompt_logprobs(self, reqs, chunks, ids, logits):
+        """logprob of every prompt token given its prefix, written beside the prompt ids."""
+        T = ids.shape[0]
+        nxt = np.empty(T, dtype=np.int64)
+        off = 0
+        for r, c in zip(reqs, chunks):
+            c = int(c)
+            start = r.cur_kv_len - c  # cur_kv_len already advanced
+            arr = r.shm_req.shm_prompt_ids.arr
+            nxt[off:off + c] = arr[start + 1:start + c + 1]
+            off += c
+        lp = ops.token_logprob(logits, torch.from_numpy(nxt).to(self.device)).cpu().numpy()
+        off = 0
+        for r, c in zip(reqs, chunks):
+            c = int(c)
+            start = r.cur_kv_len - c
+            n = min(c, r.shm_req.input_len - 1 - start)
+            if n > 0 and self.is_master_in_dp:
+                r.shm_req.shm_logprobs.arr[start + 1:start + 1 + n] = lp[off:off + n]
+            off += c
+
+    # ---- decode ----
+    def _run_decode(self, reqs: List[InferReq]) -> int:
+        B = len(reqs)
+        slots = self.ctx.alloc_slots(B)
+        slots_np = slots.numpy()
+        seq = np.empty(B, dtype=np.int32)
+        idx = np.empty(B, dtype=np.int32)
+        for i, r in enumerate(reqs):
+            r.slots = np.append(r.slots[: r.cur_kv_len], slots_np[i])
+            r.cur_kv_len += 1
+            seq[i] = r.cur_kv_len
+            idx[i] = r.req_idx
+        pin = self.pins
+        mi = ModelInput(batch_size=B, total_token_num=int(seq.sum()), max_kv_len=int(seq.max()), is_prefill=False,
+                        b_req_idx=pin.from_numpy("d_req", idx, torch.int32),
+                        b_seq_len=pin.from_numpy("d_seq", seq, torch.int32), mem_indexes=slots)
+        self.stats["h2d_bytes"] += B * 12
+        out = self.model.forward(mi)
+        self._sample_and_post(reqs, out.logits, np.ones(B, dtype=bool), is_prefill=False)
+        self.stats["decode_steps"] += 1
+        self.stats["decode_tokens"] += B
+        return B
+
+    # ---- sampling + post ----
+    def _sample_and_post(self, reqs: List[InferReq], logits: torch.Tensor, has_out: np.ndarray, is_prefill: bool):
+        dev = self.device
+        B = len(reqs)
+        sp = [r.sampling for r in reqs]
+        mask_func = self.prefill_mask_func if is_prefill else self.decode_mask_func
+        if mask_func is not None:
+            mask_func(reqs, logits)
+        self._apply_penalties(reqs, logits)
+        all_greedy = all(s.top_k == 1 for s in sp)
+        if all_greedy:
+            ids, lps = ops.sample(logits)
+        else:
+            temp = torch.tensor([s.temperature for s in sp], dtype=torch.float32).to(dev, non_blocking=True)
+            top_p = torch.tensor([s.top_p for s in sp], dtype=torch.float32).to(dev, non_blocking=True)
+            top_k = torch.tensor([s.top_k for s in sp], dtype=torch.int32).to(dev, non_blocking=True)
+            seeds = torch.tensor([r.seed for r in reqs], dtype=torch.int64).to(dev, non_blocking=True)
+            steps = torch.tensor([r.cur_output_len for r in reqs], dtype=torch.int64).to(dev, non_blocking=True)
+            ids, lps = ops.sample(logits, temp, top_p, top_k, seeds, steps)
+        # the next decode step reads its input ids on the device
+        b_req_idx = torch.tensor([r.req_idx for r in reqs], dtype=torch.int32).to(dev, non_blocking=True)
+        has_dev = None if has_out.all() else torch.from_numpy(has_out.astype(np.uint8)).to(dev, non_blocking=True)
+        ops.scatter_next_token_(self.model.req_manager.req_to_next_token_ids, ids, b_req_idx, has_dev)
+        if dev.type == "cuda":
+            ids_h = self.pins.get("s_ids", B, torch.int64)
+            lps_h = self.pins.get("s_lps", B, torch.float32)
+            ids_h.copy_(ids, non_blocking=True)
+            lps_h.copy_(lps, non_blocking=True)
+            torch.cuda.current_stream(dev).synchronize()
+        else:
+            ids_h, lps_h = ids, lps
+        self.stats["d2h_bytes"] += B * 12
+        ids_np, lps_np = ids_h.numpy(), lps_h.numpy()
+        now = time.time()
+        for i, r in enumerate(reqs):
+            if not has_out[i]:
+                if self.is_master_in_dp:
+                    r.shm_req.shm_cur_kv_len = r.cur_kv_len
+                continue
+            tok = int(ids_np[i])
+            r.append_token(tok, float(lps_np[i]))
+            r.update_finish_status(self.eos_ids, self.args.max_req_total_len)
+            if self.extra_post_req_handle_func is not None:
+                self.extra_post_req_handle_func(r, tok, float(lps_np[i]))
+            if self.is_master_in_dp:
+                if r.cur_output_len == 1:
+                    r.shm_req.first_token_time = now
+                r.publish()
+            if self.on_token is not None:
+                self.on_token(r, tok, float(lps_np[i]))
+
+    def _apply_penalties(self, reqs: List[InferReq], logits: torch.Tensor):
+        """Builds the CSR (token id, count) lists of the requests that use penalties, the masks of
+        invalid / not-yet-allowed tokens (eos before min_new_tokens), and applies them in one kernel."""
+        need_pen = any(r.sampling.has_penalty for r in reqs)
+        need_mask = any(r.sampling.invalid_token_ids or
+                        (self.eos_ids and not r.sampling.ignore_eos
+                         and r.cur_output_len + 1 < r.sampling.min_new_tokens)
+                        for r in reqs)
+        need_decay = any(r.sampling.exp_decay_factor > 1.0 for r in reqs)
+        if not (need_pen or need_mask or need_decay):
+            return
+        dev = self.device
+        B = len(reqs)
+        cu = mask_cu = tok_ids = tok_cnt = mask_ids = pres = freq = rep = None
+        if need_pen:
+            cu_l, ids_l, cnt_l = [0], [], []
+            for r in reqs:
+                if r.sampling.has_penalty:
+                    ids_l.extend(r.out_token_counter.keys())
+                    cnt_l.extend(r.out_token_counter.values())
+                cu_l.append(len(ids_l))
+            cu = torch.tensor(cu_l, dtype=torch.int32).to(dev)
+            tok_ids = torch.tensor(ids_l or [0], dtype=torch.int32).to(dev)
+            tok_cnt = torch.tensor(cnt_l or [0], dtype=torch.int32).to(dev)
+            pres = torch.tensor([r.sampling.presence_penalty for r in reqs], dtype=torch.float32).to(dev)
+            freq = torch.tensor([r.sampling.frequency_penalty for r in reqs], dtype=torch.float32).to(dev)
+            rep = torch.tensor([r.sampling.repetition_penalty for r in reqs], dtype=torch.float32).to(dev)
+        if need_mask:
+            mcu, mids = [0], []
+            for r in reqs:
+                mids.extend(r.sampling.invalid_token_ids)
+                if r.cur_output_len + 1 < r.sampling.min_new_tokens and not r.sampling.ignore_eos:
+                    mids.extend(self.eos_ids)
+                mcu.append(len(mids))
+            mask_cu = torch.tensor(mcu, dtype=torch.int32).to(dev)
+            mask_ids = torch.tensor(mids or [0], dtype=torch.int32).to(dev)
+        if need_decay and self.eos_ids:
+            # exponential_decay_length_penalty: eos logit scaled up as the output grows past `start`
+            eos = sorted(self.eos_ids)
+            for i, r in enumerate(reqs):
+                f, s = r.sampling.exp_decay_factor, r.sampling.exp_decay_start
+                if f > 1.0 and r.cur_output_len > s:
+                    scale = f ** (r.cur_output_len - s)
+                    row = logits[i, eos]
+                    logits[i, eos] = torch.where(row > 0, row * scale, row / scale)
+        if need_pen or need_mask:
+            ops.apply_penalty_(logits, pres, freq, rep, cu, tok_ids, tok_cnt, mask_cu, mask_ids)

@@ -1,0 +1,506 @@
+"""Per-rank causal LM runtime: weights, KV pool, request table, prefill / decode forward,
+decode CUDA graphs.
+
+One `TransformerLM` lives in each model-rank process (one process per GPU).  The forward pass
+is a flat sequence of this package's kernels on a [tokens, hidden] activation:
+
+    embedding -> N x [ rmsnorm -> qkv GEMM -> rope + KV scatter -> paged attention
+                       -> o_proj GEMM (+residual / +TP reduce) -> rmsnorm
+                       -> gate_up GEMM with gated-activation epilogue -> down GEMM (+residual / +TP reduce) ]
+              -> final rmsnorm -> lm_head GEMM (fp32 logits)
+
+Decode runs as one CUDA graph per batch-size bucket (1..split, then every `grow_step` up to the
+maximum, the reference's bucket rule: lightllm/common/basemodel/cuda_graph.py:24-51); prefill is
+launched eagerly (it is GPU-bound).  Subclasses override `_attention_block` / `_ffn_block` and the
+weight loaders (MoE, MLA).
+
+Reference: lightllm/common/basemodel/basemodel.py (TpPartBaseModel), layer_infer/template/
+transformer_layer_infer_template.py, models/llama/*.
+"""
+from __future__ import annotations
+
+import json
+import math
+import os
+from typing import Dict, List, Optional
+
+import torch
+
+from .. import ops
+from ..common.infer_state import InferState, ModelInput, ModelOutput
+from ..common.mem_manager import MemoryManager, profile_max_tokens
+from ..common.req_manager import ReqManager
+from ..ops import reference as ref
+from ..parallel import dist as pdist
+from ..parallel.tp import TPContext
+from .weights import RandomSource, SafetensorsSource, WeightSource, kv_head_range, tp_range
+
+
+def load_config(model_dir: str) -> dict:
+    with open(os.path.join(model_dir, "config.json")) as f:
+        cfg = json.load(f)
+    if "text_config" in cfg and "hidden_size" not in cfg:  # multimodal wrappers
+        base = dict(cfg["text_config"])
+        base.setdefault("model_type", cfg.get("model_type"))
+        cfg = {**cfg, **base}
+    return cfg
+
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float16": torch.float16, "fp16": torch.float16,
+           "float32": torch.float32, "fp32": torch.float32}
+
+
+class LayerWeights:
+    """Plain attribute bag for one transformer layer (tensors already fused / sliced / on device)."""
+
+    def __init__(self):
+        self.__dict__["_t"] = {}
+
+    def __getattr__(self, k):
+        try:
+            return self.__dict__["_t"][k]
+        except KeyError:
+            return None
+
+    def __setattr__(self, k, v):
+        self.__dict__["_t"][k] = v
+
+    def tensors(self):
+        return self.__dict__["_t"]
+
+
+class TransformerLM:
+    model_type = "llama"
+
+    # ------------------------------------------------------------------ init
+    def __init__(self, config: dict, *, weight_source: Optional[WeightSource] = None, model_dir: Optional[str] = None,
+                 pstate: Optional[pdist.ParallelState] = None, data_type: Optional[str] = None,
+                 max_total_token_num: Optional[int] = None, mem_fraction: float = 0.9, max_req_num: int = 256,
+                 max_seq_length: int = 8192, batch_max_tokens: int = 16384, graph_max_batch_size: int = 256,
+                 graph_split_batch_size: int = 32, graph_grow_step_size: int = 16, disable_cudagraph: bool = False,
+                 graph_max_len_in_batch: Optional[int] = None, tp_fused=None, random_seed: int = 0,
+                 vocab_parallel_embedding: bool = False, num_layers_override: Optional[int] = None, **extra):
+        self.config = config
+        self.ps = pstate or pdist.state()
+        self.device = self.ps.device
+        self.tp = TPContext(self.ps, fused=tp_fused)
+        dt = data_type or config.get("torch_dtype") or config.get("dtype") or "bfloat16"
+        self.dtype = _DTYPES[str(dt).replace("torch.", "")]
+        if self.device.type == "cuda" and self.dtype != torch.bfloat16:
+            self.dtype = torch.bfloat16  # the sm_100a kernels are bf16
+        self.extra = extra
+        self._read_config(config)
+        if num_layers_override:
+            self.num_layers = num_layers_override
+        self.max_req_num = max_req_num
+        self.max_seq_length = max_seq_length
+        self.batch_max_tokens = batch_max_tokens
+        self.vocab_parallel_embedding = vocab_parallel_embedding
+        self.disable_cudagraph = disable_cudagraph or self.device.type != "cuda"
+        self.graph_max_batch_size = graph_max_batch_size
+        self.graph_split_batch_size = graph_split_batch_size
+        self.graph_grow_step_size = graph_grow_step_size
+        self.graph_max_len_in_batch = graph_max_len_in_batch or max_seq_length
+
+        if weight_source is None:
+            weight_source = SafetensorsSource(model_dir) if model_dir and self._has_weights(model_dir) else \
+                RandomSource(self.weight_shapes(), dtype=self.dtype, seed=random_seed,
+                             device=str(self.device) if self.device.type == "cuda" else "cpu",
+                             fp8_names=self.fp8_weight_names())
+        self.weight_source = weight_source
+        self._load_weights(weight_source)
+        self._init_rope()
+        self._init_mem(max_total_token_num, mem_fraction)
+        self.req_manager = ReqManager(max_req_num, max_seq_length, self.mem_manager, self.device)
+        self._graphs: Dict[int, dict] = {}
+        self._graph_pool = None
+        self.weight_version = "default"
+
+    @staticmethod
+    def _has_weights(model_dir):
+        import glob
+
+        return bool(glob.glob(os.path.join(model_dir, "*.safetensors")) or glob.glob(os.path.join(model_dir, "*.bin")))
+
+    def _read_config(self, c: dict):
+        self.hidden = c["hidden_size"]
+        self.num_layers = c["num_hidden_layers"]
+        self.num_q_heads = c["num_attention_heads"]
+        self.num_kv_heads = c.get("num_key_value_heads", self.num_q_heads)
+        self.head_dim = c.get("head_dim") or self.hidden // self.num_q_heads
+        self.inter = c.get("intermediate_size")
+        self.vocab = c["vocab_size"]
+        self.eps = c.get("rms_norm_eps", c.get("layer_norm_epsilon", 1e-6))
+        self.rope_theta = c.get("rope_theta", 10000.0)
+        self.rope_scaling = c.get("rope_scaling")
+        self.partial_rotary = c.get("partial_rotary_factor", 1.0)
+        self.tie_embeddings = c.get("tie_word_embeddings", False)
+        self.attn_bias = c.get("attention_bias", False)
+        self.act = "gelu" if "gelu" in str(c.get("hidden_act", c.get("hidden_activation", "silu"))) else "silu"
+        self.norm_w_offset = 0.0
+        self.qk_norm = False
+        self.embed_scale = 1.0
+        tp = self.tp.size
+        assert self.num_q_heads % tp == 0, "q heads must divide by tp"
+        self.hq = self.num_q_heads // tp
+        k0, k1 = kv_head_range(self.num_kv_heads, self.tp.rank, tp)
+        self.hkv = k1 - k0
+        self._kv_range = (k0, k1)
+        self.rot_dim = int(self.head_dim * self.partial_rotary)
+        self.sm_scale = 1.0 / math.sqrt(self.head_dim)
+
+    # ------------------------------------------------------------------ weights
+    def fp8_weight_names(self):
+        return set()
+
+    def weight_shapes(self) -> Dict[str, tuple]:
+        """HF names -> full (unsharded) shapes; drives RandomSource and documents the checkpoint format."""
+        H, D = self.hidden, self.head_dim
+        s = {"model.embed_tokens.weight": (self.vocab, H), "model.norm.weight": (H,)}
+        if not self.tie_embeddings:
+            s["lm_head.weight"] = (self.vocab, H)
+        for i in range(self.num_layers):
+            p = f"model.layers.{i}."
+            s[p + "input_layernorm.weight"] = (H,)
+            s[p + "post_attention_layernorm.weight"] = (H,)
+            s.update(self._attn_weight_shapes(p))
+            s.update(self._ffn_weight_shapes(p, i))
+        return s
+
+    def _attn_weight_shapes(self, p):
+        H, D = self.hidden, self.head_dim
+        s = {p + "self_attn.q_proj.weight": (self.num_q_heads * D, H),
+             p + "self_attn.k_proj.weight": (self.num_kv_heads * D, H),
+             p + "self_attn.v_proj.weight": (self.num_kv_heads * D, H),
+             p + "self_attn.o_proj.weight": (H, self.num_q_heads * D)}
+        if self.attn_bias:
+            s[p + "self_attn.q_proj.bias"] = (self.num_q_heads * D,)
+            s[p + "self_attn.k_proj.bias"] = (self.num_kv_heads * D,)
+            s[p + "self_attn.v_proj.bias"] = (self.num_kv_heads * D,)
+        if self.qk_norm:
+            s[p + "self_attn.q_norm.weight"] = (D,)
+            s[p + "self_attn.k_norm.weight"] = (D,)
+        return s
+
+    def _ffn_weight_shapes(self, p, layer):
+        H, I = self.hidden, self.inter
+        return {p + "mlp.gate_proj.weight": (I, H), p + "mlp.up_proj.weight": (I, H),
+                p + "mlp.down_proj.weight": (H, I)}
+
+    def _dev(self, t: torch.Tensor, dtype=None) -> torch.Tensor:
+        return t.to(device=self.device, dtype=dtype or self.dtype).contiguous()
+
+    def _load_weights(self, src: WeightSource):
+        tp, r = self.tp.size, self.tp.rank
+        emb = src.get("model.embed_tokens.weight")
+        if self.vocab_parallel_embedding and tp > 1:
+            v0, v1 = tp_range(self.vocab, r, tp)
+            self.embed_w = self._dev(emb[v0:v1])
+            self.embed_range = (v0, v1)
+        else:
+            self.embed_w = self._dev(emb)
+            self.embed_range = (0, self.vocab)
+        self.final_norm_w = self._dev(src.get("model.norm.weight"))
+        v0, v1 = tp_range(self.vocab, r, tp)
+        if src.has("lm_head.weight") and not self.tie_embeddings:
+            self.lm_head_w = self._dev(src.get("lm_head.weight", 0, v0, v1))
+        else:
+            self.lm_head_w = self._dev(emb[v0:v1]) if tp > 1 or self.vocab_parallel_embedding else self.embed_w
+        self.layers: List[LayerWeights] = []
+        for i in range(self.num_layers):
+            lw = LayerWeights()
+            p = f"model.layers.{i}."
+            lw.in_norm = self._dev(src.get(p + "input_layernorm.weight"))
+            lw.post_norm = self._dev(src.get(p + "post_attention_layernorm.weight"))
+            self._load_attn(lw, src, p, i)
+            self._load_ffn(lw, src, p, i)
+            self.layers.append(lw)
+
+    def _load_attn(self, lw, src, p, layer):
+        D = self.head_dim
+        tp, r = self.tp.size, self.tp.rank
+        q0, q1 = tp_range(self.num_q_heads, r, tp)
+        k0, k1 = self._kv_range
+        q = src.get(p + "self_attn.q_proj.weight", 0, q0 * D, q1 * D)
+        k = src.get(p + "self_attn.k_proj.weight", 0, k0 * D, k1 * D)
+        v = src.get(p + "self_attn.v_proj.weight", 0, k0 * D, k1 * D)
+        lw.qkv_w = self._dev(torch.cat([q, k, v], dim=0))
+        if self.attn_bias and src.has(p + "self_attn.q_proj.bias"):
+            lw.qkv_b = self._dev(torch.cat([src.get(p + "self_attn.q_proj.bias", 0, q0 * D, q1 * D),
+                                            src.get(p + "self_attn.k_proj.bias", 0, k0 * D, k1 * D),
+                                            src.get(p + "self_attn.v_proj.bias", 0, k0 * D, k1 * D)], dim=0))
+        lw.o_w = self._dev(src.get(p + "self_attn.o_proj.weight", 1, q0 * D, q1 * D))
+        if src.has(p + "self_attn.o_proj.bias"):
+            ob = src.get(p + "self_attn.o_proj.bias")
+            lw.o_b = self._dev(ob / tp)  # every rank adds its share (reference: ColSliceMixin._slice_bias)
+        if self.qk_norm:
+            lw.q_norm = self._dev(src.get(p + "self_attn.q_norm.weight"))
+            lw.k_norm = self._dev(src.get(p + "self_attn.k_norm.weight"))
+
+    def _load_dense_ffn(self, lw, src, prefix, inter, tp=None, r=None):
+        tp = self.tp.size if tp is None else tp
+        r = self.tp.rank if r is None else r
+        i0, i1 = tp_range(inter, r, tp)
+        g = src.get(prefix + "gate_proj.weight", 0, i0, i1)
+        u = src.get(prefix + "up_proj.weight", 0, i0, i1)
+        il = i1 - i0
+        if il % ref.GATE_UP_BLOCK == 0:
+            lw.gate_up_w = self._dev(ref.interleave_gate_up(g, u))
+            lw.gate_up_fused = True
+        else:  # odd shard size: plain [gate; up] rows and a standalone gated activation
+            lw.gate_up_w = self._dev(torch.cat([g, u], dim=0))
+            lw.gate_up_fused = False
+        lw.down_w = self._dev(src.get(prefix + "down_proj.weight", 1, i0, i1))
+
+    def _load_ffn(self, lw, src, p, layer):
+        self._load_dense_ffn(lw, src, p + "mlp.", self.inter)
+
+    def _init_rope(self):
+        n = max(self.max_seq_length + 8, 16)
+        self.cos, self.sin = ref.build_rope_cache(n, self.rot_dim, self.rope_theta, self.rope_scaling,
+                                                  device=self.device)
+
+    # ------------------------------------------------------------------ memory
+    def kv_bytes_per_token(self) -> int:
+        return MemoryManager.bytes_per_token(self.dtype, self.hkv, self.head_dim, self.num_layers)
+
+    def _make_mem_manager(self, size):
+        return MemoryManager(size, self.dtype, self.hkv, self.head_dim, self.num_layers, self.device)
+
+    def _init_mem(self, max_total_token_num, mem_fraction):
+        if max_total_token_num is None:
+            max_total_token_num = profile_max_tokens(self.device, self.kv_bytes_per_token(), mem_fraction)
+            if self.ps.world_size > 1:
+                import torch.distributed as dist
+
+                t = torch.tensor([max_total_token_num], dtype=torch.int64, device=self.device)
+                dist.all_reduce(t, op=dist.ReduceOp.MIN)
+                max_total_token_num = int(t.item())
+        self.max_total_token_num = int(max_total_token_num)
+        self.mem_manager = self._make_mem_manager(self.max_total_token_num)
+
+    # ------------------------------------------------------------------ forward
+    @torch.no_grad()
+    def forward(self, mi: ModelInput) -> ModelOutput:
+        if mi.is_prefill:
+            return self._prefill(mi)
+        return self._decode(mi)
+
+    # ---- prefill ----
+    def _prefill(self, mi: ModelInput) -> ModelOutput:
+        dev = self.device
+        B = mi.batch_size
+        b_req_idx = mi.b_req_idx.to(dev, non_blocking=True)
+        b_seq_len = mi.b_seq_len.to(dev, non_blocking=True)
+        ready = mi.b_ready_cache_len.to(dev, non_blocking=True)
+        mem_index = mi.mem_indexes.to(dev, non_blocking=True)
+        input_ids = mi.input_ids.to(dev, non_blocking=True)
+        T = input_ids.shape[0]
+        q_len = mi.b_q_len if mi.b_q_len is not None else (mi.b_seq_len - mi.b_ready_cache_len)
+        cu_host = torch.zeros(B + 1, dtype=torch.int32)
+        cu_host[1:] = torch.cumsum(q_len.to(torch.int32), 0)
+        cu_q = cu_host.to(dev, non_blocking=True)
+        pos, batch_of = ops.prefill_prologue(self.req_manager.req_to_token_indexs, b_req_idx, ready, cu_q, mem_index, T)
+        st = InferState(is_prefill=True, batch_size=B, num_tokens=T, max_kv_len=mi.max_kv_len, max_q_len=mi.max_q_len,
+                        b_req_idx=b_req_idx, b_seq_len=b_seq_len, mem_index=mem_index, position_ids=pos, cu_q=cu_q,
+                        b_ready_cache_len=ready, batch_of_token=batch_of)
+        st.extra["multimodal_params"] = mi.multimodal_params
+        h = self._embed(input_ids, st)
+        h = self._layers_forward(h, st)
+        if mi.return_all_logits:
+            last = h
+        else:
+            last_idx = (cu_q[1:] - 1).to(torch.int32)
+            last = torch.empty((B, self.hidden), dtype=h.dtype, device=dev)
+            ops.copy_rows(last, h, None, last_idx, B)
+        logits = self._lm_head(last)
+        return ModelOutput(logits=logits)
+
+    # ---- decode ----
+    def graph_batch_sizes(self) -> List[int]:
+        sizes = list(range(1, min(self.graph_split_batch_size, self.graph_max_batch_size) + 1))
+        b = self.graph_split_batch_size + self.graph_grow_step_size
+        while b <= self.graph_max_batch_size:
+            sizes.append(b)
+            b += self.graph_grow_step_size
+        if sizes[-1] != self.graph_max_batch_size:
+            sizes.append(self.graph_max_batch_size)
+        return sizes
+
+    def _bucket(self, B: int) -> Optional[int]:
+        for s in self.graph_batch_sizes():
+            if s >= B:
+                return s
+        return None
+
+    def _decode(self, mi: ModelInput) -> ModelOutput:
+        B = mi.batch_size
+        use_graph = (not self.disable_cudagraph and B <= self.graph_max_batch_size
+                     and mi.max_kv_len <= self.graph_max_len_in_batch)
+        if not use_graph:
+            dev = self.device
+            st = self._make_decode_state(B, mi.b_req_idx.to(dev, non_blocking=True),
+                                         mi.b_seq_len.to(dev, non_blocking=True),
+                                         mi.mem_indexes.to(dev, non_blocking=True), mi.max_kv_len)
+            return ModelOutput(logits=self._decode_body(st))
+        bucket = self._bucket(B)
+        g = self._graphs.get(bucket)
+        if g is None:
+            g = self._capture_decode_graph(bucket)
+        # stage inputs (rows beyond B keep the HOLD request / HOLD slot)
+        g["b_req_idx"][:B].copy_(mi.b_req_idx, non_blocking=True)
+        g["b_seq_len"][:B].copy_(mi.b_seq_len, non_blocking=True)
+        g["mem_index"][:B].copy_(mi.mem_indexes, non_blocking=True)
+        if bucket > B:
+            g["b_req_idx"][B:].fill_(self.req_manager.HOLD_REQUEST_ID)
+            g["b_seq_len"][B:].fill_(1)
+            g["mem_index"][B:].fill_(self.mem_manager.HOLD_TOKEN_MEMINDEX)
+        g["graph"].replay()
+        ops._count(g["launches"])
+        return ModelOutput(logits=g["logits"][:B])
+
+    def _make_decode_state(self, B, b_req_idx, b_seq_len, mem_index, max_kv_len, num_splits=None) -> InferState:
+        st = InferState(is_prefill=False, batch_size=B, num_tokens=B, max_kv_len=max_kv_len, max_q_len=1,
+                        b_req_idx=b_req_idx, b_seq_len=b_seq_len, mem_index=mem_index)
+        if self.device.type == "cuda":
+            st.decode_num_splits = num_splits or ops.gqa_decode_num_splits(B, self.hq, max(self.hkv, 1), max_kv_len)
+        return st
+
+    def _decode_body(self, st: InferState) -> torch.Tensor:
+        ids, pos = ops.decode_prologue(self.req_manager.req_to_token_indexs, self.req_manager.req_to_next_token_ids,
+                                       st.b_req_idx, st.b_seq_len, st.mem_index)
+        st.position_ids = pos
+        h = self._embed(ids, st)
+        h = self._layers_forward(h, st)
+        return self._lm_head(h)
+
+    def _capture_decode_graph(self, bucket: int) -> dict:
+        dev = self.device
+        g = {
+            "b_req_idx": torch.full((bucket,), self.req_manager.HOLD_REQUEST_ID, dtype=torch.int32, device=dev),
+            "b_seq_len": torch.ones(bucket, dtype=torch.int32, device=dev),
+            "mem_index": torch.full((bucket,), self.mem_manager.HOLD_TOKEN_MEMINDEX, dtype=torch.int32, device=dev),
+        }
+        splits = ops.gqa_decode_num_splits(bucket, self.hq, max(self.hkv, 1), self.graph_max_len_in_batch)
+        st = self._make_decode_state(bucket, g["b_req_idx"], g["b_seq_len"], g["mem_index"],
+                                     self.graph_max_len_in_batch, num_splits=splits)
+        if splits > 1:
+            st.decode_scratch = (torch.empty(bucket * self.hq * splits * self.head_dim, dtype=torch.float32, device=dev),
+                                 torch.empty(bucket * self.hq * splits, dtype=torch.float32, device=dev))
+        # warm-up on a side stream (allocations, lazy kernel attribute set-up), then capture
+        s = torch.cuda.Stream(device=dev)
+        s.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(s):
+            for _ in range(2):
+                self._decode_body(st)
+        torch.cuda.current_stream(dev).wait_stream(s)
+        graph = torch.cuda.CUDAGraph()
+        if self._graph_pool is None:
+            self._graph_pool = torch.cuda.graph_pool_handle()
+        n0 = ops.launch_count()
+        with torch.cuda.graph(graph, pool=self._graph_pool):
+            logits = self._decode_body(st)
+        g["launches"] = ops.launch_count() - n0
+        g["graph"] = graph
+        g["logits"] = logits
+        g["state"] = st
+        self._graphs[bucket] = g
+        return g
+
+    def warmup_graphs(self, sizes: Optional[List[int]] = None):
+        """Capture decode graphs up front, largest first (shares the memory pool)."""
+        if self.disable_cudagraph:
+            return
+        for b in sorted(sizes or self.graph_batch_sizes(), reverse=True):
+            if b not in self._graphs:
+                self._capture_decode_graph(b)
+
+    # ---- pieces ----
+    def _embed(self, ids, st):
+        h = ops.embedding(ids, self.embed_w, self.embed_range[0], self.embed_range[1])
+        if self.vocab_parallel_embedding and self.tp.size > 1:
+            self.tp.all_reduce_(h)
+        if self.embed_scale != 1.0:
+            h = h * self.embed_scale
+        return h
+
+    def _lm_head(self, h):
+        hn = ops.rmsnorm(h, self.final_norm_w, self.eps, self.norm_w_offset)
+        logits = ops.gemm(hn, self.lm_head_w, epi="f32")
+        return self.tp.gather_logits(logits)
+
+    def _layers_forward(self, x, st: InferState):
+        """x: embeddings [T, H]; returns the final residual stream (pre final-norm)."""
+        residual = x
+        h = ops.rmsnorm(residual, self.layers[0].in_norm, self.eps, self.norm_w_offset)
+        n = self.num_layers
+        for i, lw in enumerate(self.layers):
+            a = self._attention_block(i, lw, h, st)                      # [T, hq*D] (pre o_proj)
+            h = self._row_parallel(a, lw.o_w, lw.o_b, residual, lw.post_norm)
+            f = self._ffn_block(i, lw, h, st)                            # FFN output handler below
+            if isinstance(f, tuple):  # (activation, down weight): dense row-parallel tail
+                act, down_w = f
+                nxt = self.layers[i + 1].in_norm if i + 1 < n else None
+                h = self._row_parallel(act, down_w, None, residual, nxt)
+            else:  # an already complete (reduced) FFN output, e.g. expert-parallel MoE
+                nxt = self.layers[i + 1].in_norm if i + 1 < n else None
+                if nxt is not None:
+                    h = ops.add_rmsnorm_(residual, f, nxt, self.eps, self.norm_w_offset)
+                else:
+                    residual.add_(f)
+        return residual
+
+    def _row_parallel(self, a, w, bias, residual, next_norm_w):
+        """residual += a . w^T (summed over TP ranks); returns rmsnorm(residual) * next_norm_w (or None)."""
+        if self.tp.size == 1:
+            ops.gemm(a, w, epi="residual", residual=residual, bias=bias, out=residual)
+            if next_norm_w is None:
+                return None
+            return ops.rmsnorm(residual, next_norm_w, self.eps, self.norm_w_offset)
+        partial = ops.gemm(a, w, epi="store", bias=bias)
+        if next_norm_w is None:
+            self.tp.all_reduce_(partial)
+            residual.add_(partial)
+            return None
+        return self.tp.reduce_residual_norm(partial, residual, next_norm_w, self.eps, self.norm_w_offset)
+
+    def _attention_block(self, i, lw, h, st: InferState):
+        D, hq, hkv = self.head_dim, self.hq, self.hkv
+        qkv = ops.gemm(h, lw.qkv_w, bias=lw.qkv_b)
+        kv_layer = self.mem_manager.layer(i)
+        ops.rope_kv_scatter_(qkv, kv_layer, self.cos, self.sin, st.position_ids, st.mem_index, hq, hkv, D,
+                             self.rot_dim, lw.q_norm, lw.k_norm, self.eps, self.norm_w_offset)
+        q = qkv[:, : hq * D]
+        r2t = self.req_manager.req_to_token_indexs
+        if st.is_prefill:
+            o = ops.gqa_prefill(q, kv_layer, r2t, st.b_req_idx, st.cu_q, st.b_ready_cache_len, hq, hkv, D,
+                                st.max_q_len, self.sm_scale)
+        else:
+            o = ops.gqa_decode(q, kv_layer, r2t, st.b_req_idx, st.b_seq_len, hq, hkv, D, st.max_kv_len,
+                               self.sm_scale, num_splits=st.decode_num_splits, scratch=st.decode_scratch)
+        return o.view(-1, hq * D)
+
+    def _dense_ffn(self, lw, h):
+        if lw.gate_up_fused:
+            act = ops.gemm(h, lw.gate_up_w, epi="gated_" + self.act)
+        else:
+            act = ops.gated_act(ops.gemm(h, lw.gate_up_w), self.act)
+        return act, lw.down_w
+
+    def _ffn_block(self, i, lw, h, st):
+        return self._dense_ffn(lw, h)
+
+    # ------------------------------------------------------------------ misc
+    def flush_graphs(self):
+        self._graphs.clear()
+
+    def param_bytes(self) -> int:
+        seen, n = set(), 0
+        tensors = [self.embed_w, self.lm_head_w, self.final_norm_w]
+        for lw in self.layers:
+            tensors += [t for t in lw.tensors().values() if isinstance(t, torch.Tensor)]
+        for t in tensors:
+            if t.data_ptr() not in seen:
+                seen.add(t.data_ptr())
+                n += t.numel() * t.element_size()
+        return n

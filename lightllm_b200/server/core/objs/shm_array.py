@@ -1,0 +1,82 @@
+"""Numpy arrays over POSIX shared memory (or process-local memory when `name` is None).
+
+The HTTP worker creates the arrays of a request (token ids, logprobs); router, model ranks and
+the detokenizer link to them by name.  Reference: lightllm/server/core/objs/shm_array.py and
+lightllm/utils/shm_utils.py.
+"""
+from __future__ import annotations
+
+from multiprocessing import shared_memory
+from typing import Optional
+
+import numpy as np
+
+
+def create_or_link_shm(name: str, size: int, force_create: bool = False):
+    """Returns (SharedMemory, created)."""
+    try:
+        shm = shared_memory.SharedMemory(name=name, create=True, size=size)
+        return shm, True
+    except FileExistsError:
+        shm = shared_memory.SharedMemory(name=name, create=False)
+        if shm.size < size or force_create:
+            shm.close()
+            try:
+                shm.unlink()
+            except FileNotFoundError:
+                pass
+            shm = shared_memory.SharedMemory(name=name, create=True, size=size)
+            return shm, True
+        return shm, False
+
+
+def _untrack(shm):
+    """Stop Python's resource tracker from unlinking a segment this process only linked to."""
+    try:
+        from multiprocessing import resource_tracker
+
+        resource_tracker.unregister(shm._name, "shared_memory")
+    except Exception:
+        pass
+
+
+class ShmArray:
+    def __init__(self, name: Optional[str], shape, dtype):
+        self.name = name
+        self.shape = tuple(shape)
+        self.dtype = np.dtype(dtype)
+        self.shm = None
+        self.arr = None
+        self._owner = False
+
+    @property
+    def nbytes(self) -> int:
+        return int(np.prod(self.shape)) * self.dtype.itemsize
+
+    def create_shm(self):
+        if self.name is None:
+            self.arr = np.zeros(self.shape, dtype=self.dtype)
+            return self
+        self.shm, created = create_or_link_shm(self.name, max(self.nbytes, 1), force_create=True)
+        self._owner = True
+        self.arr = np.ndarray(self.shape, dtype=self.dtype, buffer=self.shm.buf)
+        return self
+
+    def link_shm(self):
+        if self.name is None:
+            raise ValueError("a process-local array cannot be linked")
+        self.shm = shared_memory.SharedMemory(name=self.name, create=False)
+        _untrack(self.shm)
+        self.arr = np.ndarray(self.shape, dtype=self.dtype, buffer=self.shm.buf)
+        return self
+
+    def close_shm(self, unlink: Optional[bool] = None):
+        self.arr = None
+        if self.shm is not None:
+            self.shm.close()
+            if unlink if unlink is not None else self._owner:
+                try:
+                    self.shm.unlink()
+                except FileNotFoundError:
+                    pass
+            self.shm = None

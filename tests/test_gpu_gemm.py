@@ -1,0 +1,64 @@
+"""tcgen05 bf16 GEMM and its epilogues against fp32 matmul."""
+import pytest
+import torch
+
+from lightllm_b200 import ops
+from lightllm_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+BF = torch.bfloat16
+
+
+def _check(got, want, K):
+    err = (got.float() - want.float()).abs().max().item()
+    tol = 0.02 * (K ** 0.5) * 0.05 + 2e-2  # bf16 output rounding on values of magnitude ~sqrt(K)*0.05
+    assert err < tol, f"max abs err {err} (tol {tol})"
+    assert int(ops.gemm_status(got.device).item()) == 0, "a bounded wait inside the GEMM timed out"
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 512), (1, 256, 128), (77, 512, 4096), (256, 6144, 4096),
+                                   (300, 1024, 1000), (2048, 4096, 14336), (129, 16032, 512), (4096, 1280, 8192)])
+@pytest.mark.parametrize("bn", [0, 64, 128, 256])
+def test_gemm_store(dev, M, N, K, bn):
+    torch.manual_seed(0)
+    a = (torch.randn(M, K, device=dev) * 0.5).to(BF)
+    w = (torch.randn(N, K, device=dev) * 0.1).to(BF)
+    got = ops.gemm(a, w, bn=bn)
+    _check(got, a.float() @ w.float().t(), K)
+
+
+def test_gemm_epilogues(dev):
+    torch.manual_seed(1)
+    M, N, K = 200, 1024, 768
+    a = (torch.randn(M, K, device=dev) * 0.5).to(BF)
+    w = (torch.randn(N, K, device=dev) * 0.1).to(BF)
+    bias = torch.randn(N, device=dev).to(BF)
+    res = torch.randn(M, N, device=dev).to(BF)
+    acc = a.float() @ w.float().t()
+    _check(ops.gemm(a, w, bias=bias), acc + bias.float(), K)
+    _check(ops.gemm(a, w, epi="residual", residual=res), acc + res.float(), K)
+    r2 = res.clone()
+    ops.gemm(a, w, epi="residual", residual=r2, out=r2)  # in place on the residual stream
+    _check(r2, acc + res.float(), K)
+    f = ops.gemm(a, w, epi="f32")
+    assert f.dtype == torch.float32
+    assert (f - acc).abs().max().item() < 1e-2
+    # gated (SwiGLU): interleaved weights
+    I = 512
+    g = (torch.randn(I, K, device=dev) * 0.1).to(BF)
+    u = (torch.randn(I, K, device=dev) * 0.1).to(BF)
+    wi = ref.interleave_gate_up(g, u)
+    want = torch.nn.functional.silu(a.float() @ g.float().t()) * (a.float() @ u.float().t())
+    for bn in (64, 128, 256):
+        _check(ops.gemm(a, wi, epi="gated_silu", bn=bn), want, K)
+    want_g = torch.nn.functional.gelu(a.float() @ g.float().t(), approximate="tanh") * (a.float() @ u.float().t())
+    _check(ops.gemm(a, wi, epi="gated_gelu"), want_g, K)
+
+
+def test_gemm_strided_a_and_tail_n(dev):
+    torch.manual_seed(2)
+    M, K, N = 150, 512, 264  # N not a multiple of 32
+    big = (torch.randn(M, K + 256, device=dev) * 0.5).to(BF)
+    a = big[:, :K]  # row stride K+256
+    w = (torch.randn(N, K, device=dev) * 0.1).to(BF)
+    _check(ops.gemm(a, w), a.float() @ w.float().t(), K)
