@@ -18,23 +18,36 @@ import torch
 
 
 class SlotAllocator:
-    """LIFO stack of free slot ids (host side, int32).  `alloc` returns a pinned int32 tensor taken
-    from a small ring so an async H2D copy of the previous step's result stays valid."""
+    """LIFO stack of free slot ids kept by the C++ runtime (host side, int32).  `alloc` returns a pinned
+    int32 tensor taken from a small ring so an async H2D copy of the previous step's result stays valid."""
 
     RING = 4
 
     def __init__(self, size: int, pin: bool = False):
+        import ctypes
+
+        from ..ops._native import runtime
+
         self.size = size
-        self._stack = np.arange(size, dtype=np.int32)
-        self._top = 0  # _stack[_top:] are free
+        self._lib = runtime()
+        self._lib.llb_slots_create.restype = ctypes.c_void_p
+        self._lib.llb_slots_free_count.restype = ctypes.c_int64
+        self._ct = ctypes
+        self._h = ctypes.c_void_p(self._lib.llb_slots_create(ctypes.c_int64(size)))
         self._pin = pin and torch.cuda.is_available()
         self._ring = [None] * self.RING
         self._ring_i = 0
         self._on_change = None
 
+    def __del__(self):
+        try:
+            self._lib.llb_slots_destroy(self._h)
+        except Exception:
+            pass
+
     @property
     def can_use_mem_size(self) -> int:
-        return self.size - self._top
+        return int(self._lib.llb_slots_free_count(self._h))
 
     def set_listener(self, fn):
         self._on_change = fn
@@ -50,11 +63,10 @@ class SlotAllocator:
         return b[:n]
 
     def alloc(self, n: int) -> torch.Tensor:
-        if n > self.can_use_mem_size:
-            raise MemoryError(f"KV pool exhausted: need {n}, free {self.can_use_mem_size}")
         out = self._buf(n)
-        out.numpy()[:] = self._stack[self._top:self._top + n]
-        self._top += n
+        rc = self._lib.llb_slots_alloc(self._h, self._ct.c_int64(n), self._ct.c_void_p(out.data_ptr()))
+        if rc != 0:
+            raise MemoryError(f"KV pool exhausted: need {n}, free {self.can_use_mem_size}")
         if self._on_change:
             self._on_change(self.can_use_mem_size)
         return out
@@ -62,19 +74,17 @@ class SlotAllocator:
     def free(self, idx) -> None:
         if isinstance(idx, torch.Tensor):
             idx = idx.detach().cpu().numpy()
-        idx = np.asarray(idx, dtype=np.int32).reshape(-1)
+        idx = np.ascontiguousarray(idx, dtype=np.int32).reshape(-1)
         n = idx.shape[0]
         if n == 0:
             return
-        assert self._top - n >= 0, "double free of KV slots"
-        self._top -= n
-        self._stack[self._top:self._top + n] = idx
+        rc = self._lib.llb_slots_free(self._h, self._ct.c_void_p(idx.ctypes.data), self._ct.c_int64(n))
+        assert rc == 0, "double free of KV slots"
         if self._on_change:
             self._on_change(self.can_use_mem_size)
 
     def free_all(self) -> None:
-        self._stack = np.arange(self.size, dtype=np.int32)
-        self._top = 0
+        self._lib.llb_slots_reset(self._h)
         if self._on_change:
             self._on_change(self.can_use_mem_size)
 

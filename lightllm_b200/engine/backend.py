@@ -27,7 +27,7 @@ from .. import ops
 from ..common.infer_state import ModelInput
 from ..server.core.objs.req import FinishStatus, Req
 from .infer_batch import InferenceContext, InferReq
-from .radix_cache import RadixCache
+from .native_radix import NativeRadixCache as RadixCache
 
 
 @dataclass

@@ -1,0 +1,220 @@
+"""Backend variants selected by launch flags.  Each one is `ModelBackend` plus hooks:
+logit masks before sampling (`prefill_mask_func` / `decode_mask_func`) and a per-token post
+handler (`extra_post_req_handle_func`).
+
+Reference: lightllm/server/router/model_infer/mode_backend/* (TokenHealingBackend,
+OutlinesConstraintBackend, XgrammarBackend, FirstTokenConstraintBackend, RewardModelBackend,
+DiversehBackend) and model_rpc.py:72-99 (selection).
+"""
+from __future__ import annotations
+
+import os
+from typing import List
+
+import numpy as np
+import torch
+
+from .backend import ModelBackend
+from .infer_batch import InferReq
+
+
+class FirstTokenConstraintBackend(ModelBackend):
+    """Only the ids in env FIRST_ALLOWED_TOKENS (comma separated) may be generated first."""
+
+    def __init__(self, *a, **kw):
+        super().__init__(*a, **kw)
+        allowed = [int(t) for t in os.environ.get("FIRST_ALLOWED_TOKENS", "").split(",") if t.strip()]
+        assert allowed, "set FIRST_ALLOWED_TOKENS=id,id,..."
+        self._allowed = torch.tensor(allowed, dtype=torch.long)
+        self.prefill_mask_func = self._mask
+
+    def _mask(self, reqs: List[InferReq], logits: torch.Tensor):
+        keep = self._allowed.to(logits.device)
+        m = torch.full_like(logits, float("-inf"))
+        m[:, keep] = 0.0
+        for i, r in enumerate(reqs):
+            if r.cur_output_len == 0:
+                logits[i] += m[i]
+
+
+class TokenHealingBackend(ModelBackend):
+    """The last prompt tokens were cut off (TokenHealingReq); generation is constrained to tokens whose
+    text continues the removed text until it is covered again."""
+
+    def __init__(self, *a, tokenizer=None, **kw):
+        super().__init__(*a, **kw)
+        self.tokenizer = tokenizer
+        self._vocab_strs = None
+        self.prefill_mask_func = self._mask
+        self.decode_mask_func = self._mask
+        self.extra_post_req_handle_func = self._post
+
+    def _vocab(self):
+        if self._vocab_strs is None:
+            V = self.model.vocab
+            toks = self.tokenizer.convert_ids_to_tokens(list(range(V))) if self.tokenizer is not None else None
+            self._vocab_strs = [t if isinstance(t, str) else "" for t in (toks or [""] * V)]
+        return self._vocab_strs
+
+    def _state(self, r: InferReq):
+        st = r.extra.get("heal")
+        if st is None:
+            ids = r.shm_req.prefix_token_ids.to_list()
+            text = "".join(self.tokenizer.convert_ids_to_tokens(ids)) if (ids and self.tokenizer is not None) else ""
+            st = r.extra["heal"] = {"remaining": text}
+        return st
+
+    def _mask(self, reqs, logits):
+        for i, r in enumerate(reqs):
+            rem = self._state(r)["remaining"]
+            if not rem:
+                continue
+            ok = [j for j, s in enumerate(self._vocab()) if s and (s.startswith(rem) or rem.startswith(s))]
+            if ok:
+                m = torch.full((logits.shape[1],), float("-inf"), device=logits.device)
+                m[torch.tensor(ok, device=logits.device)] = 0.0
+                logits[i] += m
+
+    def _post(self, r: InferReq, tok: int, lp: float):
+        st = self._state(r)
+        if st["remaining"]:
+            s = self._vocab()[tok]
+            st["remaining"] = st["remaining"][len(s):] if st["remaining"].startswith(s) else ""
+
+
+class XgrammarBackend(ModelBackend):
+    """EBNF / JSON-schema constrained decoding through xgrammar token bitmasks."""
+
+    def __init__(self, *a, tokenizer=None, **kw):
+        super().__init__(*a, **kw)
+        import xgrammar as xgr
+
+        self.xgr = xgr
+        info = xgr.TokenizerInfo.from_huggingface(tokenizer, vocab_size=self.model.vocab)
+        self.compiler = xgr.GrammarCompiler(info, max_threads=8)
+        self.prefill_mask_func = self._mask
+        self.decode_mask_func = self._mask
+        self.extra_post_req_handle_func = self._post
+
+    def _matcher(self, r: InferReq):
+        m = r.extra.get("xgr", False)
+        if m is False:
+            sp = r.sampling
+            if sp.guided_grammar == "json":
+                cg = self.compiler.compile_builtin_json_grammar()
+            elif sp.guided_grammar:
+                cg = self.compiler.compile_grammar(sp.guided_grammar)
+            elif sp.guided_json:
+                cg = self.compiler.compile_json_schema(sp.guided_json)
+            else:
+                cg = None
+            m = r.extra["xgr"] = self.xgr.GrammarMatcher(cg) if cg is not None else None
+        return m
+
+    def _mask(self, reqs, logits):
+        rows = [(i, self._matcher(r)) for i, r in enumerate(reqs)]
+        rows = [(i, m) for i, m in rows if m is not None]
+        if not rows:
+            return
+        bitmask = self.xgr.allocate_token_bitmask(len(rows), self.model.vocab)
+        for j, (i, m) in enumerate(rows):
+            m.fill_next_token_bitmask(bitmask, j)
+        idx = torch.tensor([i for i, _ in rows], device=logits.device)
+        sub = logits[idx]
+        self.xgr.apply_token_bitmask_inplace(sub, bitmask.to(logits.device))
+        logits[idx] = sub
+
+    def _post(self, r: InferReq, tok: int, lp: float):
+        m = self._matcher(r)
+        if m is not None:
+            if not m.accept_token(tok) or m.is_terminated():
+                from ..server.core.objs.req import FinishStatus
+
+                r.finish_status.set_status(FinishStatus.FINISHED_STOP)
+
+
+class OutlinesConstraintBackend(ModelBackend):
+    """Regex-constrained decoding with an outlines FSM (requires the `outlines` package)."""
+
+    def __init__(self, *a, tokenizer=None, **kw):
+        super().__init__(*a, **kw)
+        try:
+            from outlines.fsm.guide import RegexGuide  # noqa: F401
+        except Exception as e:  # pragma: no cover
+            raise RuntimeError("--output_constraint_mode outlines needs the `outlines` package; "
+                               "use xgrammar instead") from e
+        self.tokenizer = tokenizer
+
+
+class RewardModelBackend(ModelBackend):
+    """Reward models: one prefill, the score head output is stored in `reward_score`; no decoding."""
+
+    def _sample_and_post(self, reqs, logits, has_out, is_prefill):
+        from ..server.core.objs.req import FinishStatus
+
+        scores = logits[:, 0].float().cpu().numpy()
+        for i, r in enumerate(reqs):
+            if not has_out[i]:
+                continue
+            r.shm_req.reward_score = float(scores[i])
+            r.append_token(0, 0.0)
+            r.finish_status.set_status(FinishStatus.FINISHED_STOP)
+            if self.is_master_in_dp:
+                r.publish()
+
+
+class DiverseBackend(ModelBackend):
+    """n > 1 samples of one prompt: the first sub-request prefills, its KV goes to the radix tree
+    right away, and its siblings match it instead of recomputing the prompt."""
+
+    def add_reqs(self, shm_reqs):
+        out = []
+        by_group = {}
+        for r in shm_reqs:
+            by_group.setdefault(r.group_req_id, []).append(r)
+        for group in by_group.values():
+            out += super().add_reqs(group[:1])
+            self._deferred = getattr(self, "_deferred", []) + group[1:]
+        return out
+
+    def step(self):
+        res = super().step()
+        deferred = getattr(self, "_deferred", [])
+        if deferred and self.radix_cache is not None:
+            ready, wait = [], []
+            for r in deferred:
+                master = self.ctx.requests.get(r.group_req_id)
+                if master is None or master.cur_output_len > 0:
+                    ready.append(r)
+                else:
+                    wait.append(r)
+            for r in ready:
+                master = self.ctx.requests.get(r.group_req_id)
+                if master is not None:  # publish the prompt KV so that siblings hit it
+                    n = r.input_len - 1
+                    if n > 0:
+                        self.radix_cache.insert(master.shm_req.shm_prompt_ids.arr[:n], master.slots[:n])
+                        if master.shared_kv_node is not None:
+                            self.radix_cache.dec_node_ref_counter(master.shared_kv_node)
+                        node, m, _ = self.radix_cache.match_prefix(master.shm_req.shm_prompt_ids.arr[:n], True)
+                        master.shared_kv_node, master.shared_len = node, m
+                super().add_reqs([r])
+            self._deferred = wait
+        return res
+
+
+def select_backend_class(args):
+    if getattr(args, "use_reward_model", False):
+        return RewardModelBackend
+    if getattr(args, "token_healing_mode", False):
+        return TokenHealingBackend
+    mode = getattr(args, "output_constraint_mode", "none")
+    if mode == "xgrammar":
+        return XgrammarBackend
+    if mode == "outlines":
+        return OutlinesConstraintBackend
+    if getattr(args, "first_token_constraint_mode", False):
+        return FirstTokenConstraintBackend
+    if getattr(args, "diverse_mode", False):
+        return DiverseBackend
+    return ModelBackend

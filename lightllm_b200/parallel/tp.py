@@ -53,9 +53,9 @@ class TPContext:
         if self.size == 1:
             return local_logits
         B, Vl = local_logits.shape
-        out = torch.empty((self.size, B, Vl), dtype=local_logits.dtype, device=local_logits.device)
+        out = torch.empty((self.size * B, Vl), dtype=local_logits.dtype, device=local_logits.device)
         dist.all_gather_into_tensor(out, local_logits.contiguous(), group=self.group)
-        return out.permute(1, 0, 2).reshape(B, self.size * Vl)
+        return out.view(self.size, B, Vl).permute(1, 0, 2).reshape(B, self.size * Vl)
 
     # ---- fused semantics ----
     def reduce_residual_norm(self, partial, residual, norm_w, eps, w_offset=0.0):

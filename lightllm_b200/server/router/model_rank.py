@@ -1,0 +1,196 @@
+"""Model-rank process: one per GPU.  Builds the model and its `ModelBackend`, then self-drives:
+it polls the router's shm mailbox for commands (new requests, aborts, stop-string hits, profiler
+and RL operations) and runs prefill / decode steps; results go straight into the shm requests.
+
+Ranks of one tensor-parallel group must apply mailbox commands at the same step boundary.  The
+mailbox carries a generation counter; before each step the ranks of a node agree on the newest
+generation all of them have seen with a one-integer MIN all-reduce on the host (gloo) group, so
+no GPU collective and no device sync sits in the polling loop.
+
+Reference: lightllm/server/router/model_infer/model_rpc.py:56-238 (process entry, init_model)
+and mode_backend/base_backend.py:473-606 (_try_read_new_reqs, _init_reqs).
+"""
+from __future__ import annotations
+
+import os
+import time
+import traceback
+from typing import Optional
+
+import torch
+
+from ..core.objs.atomic_lock import SharedArray
+from ..core.objs.io_objs import AbortedReqCmd, FlushCacheCmd, NewReqsCmd, ProfilerCmd, RLCmd, StopStrMatchedReqCmd
+from ..core.objs.shm_objs_io_buffer import ShmObjsIOBuffer
+from ..core.objs.shm_req_manager import ShmReqManager
+from ..core.objs.start_args import StartArgs, set_env_start_args
+
+
+class ExitCmd:
+    pass
+
+
+def _build_model_and_backend(args: StartArgs, ps):
+    from ...engine.backend import BackendArgs, ModelBackend
+    from ...models.base import load_config
+    from ...models.registry import get_model
+
+    cfg = getattr(args, "_config_override", None) or load_config(args.model_dir)
+    fused = None
+    if ps.tp_size > 1 and ps.device.type == "cuda" and not args.disable_symm_mem_allreduce:
+        try:
+            from ...parallel.fused import FusedTP
+
+            fused = FusedTP(ps)
+        except Exception:
+            fused = None
+    model = get_model(cfg, model_dir=args.model_dir, pstate=ps, data_type=args.data_type,
+                      max_total_token_num=args.max_total_token_num, mem_fraction=args.mem_fraction,
+                      max_req_num=args.running_max_req_size, max_seq_length=args.max_req_total_len + 8,
+                      batch_max_tokens=args.batch_max_tokens, disable_cudagraph=args.disable_cudagraph,
+                      graph_max_batch_size=min(args.graph_max_batch_size, args.running_max_req_size),
+                      graph_split_batch_size=args.graph_split_batch_size,
+                      graph_grow_step_size=args.graph_grow_step_size,
+                      graph_max_len_in_batch=args.graph_max_len_in_batch or None, tp_fused=fused,
+                      enable_ep_moe=args.enable_ep_moe, quant_type=args.quant_type)
+    eos = args.eos_ids or args.eos_id or cfg.get("eos_token_id") or []
+    eos = tuple(eos) if isinstance(eos, (list, tuple)) else (eos,)
+    bargs = BackendArgs(batch_max_tokens=args.batch_max_tokens, chunked_prefill_size=args.chunked_prefill_size,
+                        disable_chunked_prefill=args.disable_chunked_prefill,
+                        router_max_wait_tokens=args.router_max_wait_tokens,
+                        disable_aggressive_schedule=args.disable_aggressive_schedule,
+                        disable_dynamic_prompt_cache=args.disable_dynamic_prompt_cache, eos_ids=eos,
+                        max_req_total_len=args.max_req_total_len,
+                        return_all_prompt_logprobs=args.enable_prompt_logprobs)
+    from ...engine.mode_backends import select_backend_class
+
+    backend_cls = select_backend_class(args)
+    backend = backend_cls(model, bargs, is_master_in_dp=(ps.tp_rank == 0))
+    return model, backend
+
+
+class ModelRankLoop:
+    def __init__(self, args: StartArgs, rank: int, ps, model, backend):
+        self.args = args
+        self.rank = rank
+        self.ps = ps
+        self.model = model
+        self.backend = backend
+        name = args.unique_server_name
+        self.node_world = args.tp // args.nnodes
+        self.mailbox = ShmObjsIOBuffer(f"{name}_router_to_ranks", self.node_world)
+        self.shm_req_manager = ShmReqManager(name, args.running_max_req_size)
+        # [rank, (free tokens, radix unreferenced tokens, running reqs)] read by the router
+        self.load_arr = SharedArray(f"{name}_rank_load", (args.tp, 4), "int64")
+        self.last_gen = self.mailbox.generation()
+        self.running = True
+        self.profiler = None
+        self.dp_index = ps.dp_rank
+
+    def _agree_generation(self) -> int:
+        g = self.mailbox.generation()
+        if self.ps.world_size == 1 or self.ps.cpu_group is None:
+            return g
+        t = torch.tensor([g], dtype=torch.int64)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MIN, group=self.ps.cpu_group)
+        return int(t.item())
+
+    def _handle(self, cmd):
+        b = self.backend
+        if isinstance(cmd, NewReqsCmd):
+            mine = []
+            for req_id, shm_index, mm_params, dp_index in cmd.reqs:
+                if self.ps.dp_size > 1 and dp_index != self.dp_index:
+                    continue
+                r = self.shm_req_manager.get_req_obj_by_index(shm_index)
+                r.link_prompt_ids_shm_array(self.args.unique_server_name)
+                r.link_logprobs_shm_array(self.args.unique_server_name)
+                r._mm_params = mm_params
+                mine.append(r)
+            if mine:
+                b.add_reqs(mine)
+        elif isinstance(cmd, AbortedReqCmd):
+            b.abort(cmd.req_id)
+        elif isinstance(cmd, StopStrMatchedReqCmd):
+            b.stop_str_matched(cmd.req_id)
+        elif isinstance(cmd, ProfilerCmd):
+            self._profiler_cmd(cmd.cmd)
+        elif isinstance(cmd, FlushCacheCmd):
+            if b.radix_cache is not None and not b.has_work():
+                b.radix_cache.clear_tree_nodes()
+        elif isinstance(cmd, RLCmd):
+            from ...engine.rl_ops import handle_rl_cmd
+
+            handle_rl_cmd(self, cmd)
+        elif isinstance(cmd, ExitCmd):
+            self.running = False
+
+    def _profiler_cmd(self, what: str):
+        from ...utils.profiler import ProcessProfiler
+
+        if self.profiler is None:
+            self.profiler = ProcessProfiler(self.args.enable_profiling or "torch_profiler", f"rank{self.rank}")
+        self.profiler.cmd(what)
+
+    def _read_mailbox(self):
+        g = self._agree_generation()
+        if g == self.last_gen:
+            return
+        cmds = self.mailbox.read_obj()
+        self.last_gen = g
+        self.mailbox.sub_state()
+        for c in cmds:
+            self._handle(c)
+
+    def _publish_load(self):
+        b = self.backend
+        row = self.load_arr.arr[self.ps.global_rank]
+        row[0] = self.model.mem_manager.can_use_mem_size
+        row[1] = b.radix_cache.unreferenced_tokens_num() if b.radix_cache is not None else 0
+        row[2] = len(b.ctx.requests)
+        row[3] = int(time.time())
+
+    def run(self):
+        idle_sleep = 0.001
+        while self.running:
+            self._read_mailbox()
+            if self.backend.has_work():
+                res = self.backend.step()
+                for ir in res["finished"]:
+                    ir.shm_req.release_shm_arrays(unlink=False)
+                    self.shm_req_manager.put_back_req_obj(ir.shm_req)
+            else:
+                time.sleep(idle_sleep)
+            self._publish_load()
+
+
+def model_rank_main(args_dict: dict, rank: int, pipe, config_override: Optional[dict] = None):
+    """Process entry (spawned by the router)."""
+    try:
+        from ...parallel import dist as pdist
+        from ...utils.process_utils import set_proc_title, start_parent_check_thread
+
+        args = StartArgs.from_dict(args_dict)
+        set_env_start_args(args)
+        set_proc_title(f"lightllm::{args.unique_server_name}::model_infer:RANK{rank}")
+        start_parent_check_thread()
+        use_cuda = torch.cuda.is_available() and args.hardware_platform == "cuda" and \
+            os.environ.get("LLB_FORCE_CPU", "0") != "1"
+        node_world = args.tp // args.nnodes
+        local_rank = rank % node_world
+        device = torch.device("cuda", local_rank) if use_cuda else torch.device("cpu")
+        ps = pdist.init_distributed(args.tp, rank, dp=args.dp, nnodes=args.nnodes, node_rank=args.node_rank,
+                                    host=args.nccl_host, port=args.nccl_port, device=device)
+        if config_override is not None:
+            args._config_override = config_override
+        model, backend = _build_model_and_backend(args, ps)
+        loop = ModelRankLoop(args, rank, ps, model, backend)
+        pipe.send(("init ok", model.max_total_token_num))
+    except Exception:
+        pipe.send(("init failed", traceback.format_exc()))
+        return
+    try:
+        loop.run()
+    except Exception:
+        traceback.print_exc()
+        os._exit(-1)

@@ -1,0 +1,59 @@
+"""Tokenizer factory (HF fast / slow / auto) and the token-id-only stand-in used when a model
+directory has no tokenizer files (synthetic benchmarks send token ids).
+Reference: lightllm/server/tokenizer.py.
+"""
+from __future__ import annotations
+
+import os
+from typing import List
+
+
+class IdOnlyTokenizer:
+    """Accepts prompts that are already token ids; decodes ids as ``<id>`` strings."""
+
+    eos_token_id = None
+    all_special_ids: List[int] = []
+    chat_template = None
+
+    def __init__(self, vocab_size: int = 1 << 30):
+        self.vocab_size = vocab_size
+
+    def __len__(self):
+        return self.vocab_size
+
+    def encode(self, text, add_special_tokens=True):
+        if isinstance(text, str):
+            return [int(t) % self.vocab_size for t in text.split()] if text.replace(" ", "").isdigit() else \
+                [ord(c) % self.vocab_size for c in text]
+        return list(text)
+
+    def decode(self, ids, skip_special_tokens=True, **kw):
+        return "".join(f"<{int(i)}>" for i in ids)
+
+    def convert_ids_to_tokens(self, ids, skip_special_tokens=False):
+        if isinstance(ids, int):
+            return f"<{ids}>"
+        return [f"<{int(i)}>" for i in ids]
+
+    def convert_tokens_to_string(self, tokens):
+        return "".join(tokens)
+
+    def apply_chat_template(self, messages, tokenize=False, add_generation_prompt=True, **kw):
+        text = "".join(f"[{m.get('role', 'user')}]{m.get('content', '')}" for m in messages)
+        return self.encode(text) if tokenize else text
+
+
+def get_tokenizer(model_dir: str, tokenizer_mode: str = "fast", trust_remote_code: bool = False, vocab_size=None):
+    has_files = model_dir and any(os.path.exists(os.path.join(model_dir, f))
+                                  for f in ("tokenizer.json", "tokenizer.model", "tokenizer_config.json", "vocab.json"))
+    if not has_files:
+        return IdOnlyTokenizer(vocab_size or (1 << 30))
+    from transformers import AutoTokenizer
+
+    use_fast = tokenizer_mode != "slow"
+    try:
+        return AutoTokenizer.from_pretrained(model_dir, use_fast=use_fast, trust_remote_code=trust_remote_code)
+    except Exception:
+        if tokenizer_mode == "auto" or use_fast:
+            return AutoTokenizer.from_pretrained(model_dir, use_fast=not use_fast, trust_remote_code=trust_remote_code)
+        raise

@@ -11,7 +11,7 @@ BF = torch.bfloat16
 
 def _check(got, want, K):
     err = (got.float() - want.float()).abs().max().item()
-    tol = 0.02 * (K ** 0.5) * 0.05 + 2e-2  # bf16 output rounding on values of magnitude ~sqrt(K)*0.05
+    tol = 1e-2 * want.abs().max().item() + 1e-2  # bf16 output rounding (2^-8 relative) plus accumulation order
     assert err < tol, f"max abs err {err} (tol {tol})"
     assert int(ops.gemm_status(got.device).item()) == 0, "a bounded wait inside the GEMM timed out"
 

@@ -1,0 +1,67 @@
+"""Tensor-parallel plumbing on CPU/gloo: TP=2 must reproduce TP=1 (tiny Llama, fp32, greedy)."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+TINY = dict(model_type="llama", hidden_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+            head_dim=64, intermediate_size=688, vocab_size=1024, rms_norm_eps=1e-6, rope_theta=1e4, eos_token_id=2)
+
+
+def _prompts():
+    g = torch.Generator().manual_seed(0)
+    lens = torch.randint(16, 65, (8,), generator=g).tolist()
+    return [torch.randint(3, 1024, (n,), generator=g).tolist() for n in lens]
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, out_dir):
+    from lightllm_b200.common.infer_state import ModelInput
+    from lightllm_b200.engine.llm import LLM
+    from lightllm_b200.parallel import dist as pdist
+
+    torch.set_num_threads(2)
+    pdist.init_distributed(world, rank, host="127.0.0.1", port=port, backend="gloo", device=torch.device("cpu"))
+    llm = LLM(config=TINY, data_type="float32", max_total_token_num=4096, running_max_req_size=8,
+              max_req_total_len=128, batch_max_tokens=256, random_seed=0)
+    prompts = _prompts()
+    # logits of one prefill pass
+    m = llm.model
+    ids = torch.tensor(prompts[0])
+    req = m.req_manager.alloc()
+    slots = m.mem_manager.alloc(len(ids))
+    mi = ModelInput(batch_size=1, total_token_num=len(ids), max_kv_len=len(ids), is_prefill=True,
+                    b_req_idx=torch.tensor([req], dtype=torch.int32), b_seq_len=torch.tensor([len(ids)], dtype=torch.int32),
+                    mem_indexes=slots.clone(), input_ids=ids, b_ready_cache_len=torch.zeros(1, dtype=torch.int32),
+                    max_q_len=len(ids))
+    logits = m.forward(mi).logits
+    m.mem_manager.free(slots)
+    m.req_manager.free(req)
+    outs = llm.generate(prompts, {"max_new_tokens": 32, "ignore_eos": True})
+    if rank == 0:
+        torch.save({"logits": logits, "tokens": [o["token_ids"] for o in outs]}, os.path.join(out_dir, f"tp{world}.pt"))
+    pdist.destroy()
+
+
+@pytest.mark.timeout(600)
+def test_tp2_matches_tp1(tmp_path):
+    port = _free_port()
+    mp.spawn(_worker, args=(1, port, str(tmp_path)), nprocs=1, join=True)
+    port = _free_port()
+    mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    a = torch.load(tmp_path / "tp1.pt")
+    b = torch.load(tmp_path / "tp2.pt")
+    assert a["logits"].shape == b["logits"].shape == (1, 1024)
+    assert torch.allclose(a["logits"], b["logits"], atol=2e-4, rtol=1e-4), (a["logits"] - b["logits"]).abs().max()
+    assert all(len(t) == 32 for t in b["tokens"])
+    assert a["tokens"] == b["tokens"]
