@@ -270,6 +270,7 @@ decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ 
   float num = 0.f, den = 0.f;
   if (M != -INFINITY) {
     for (int s = 0; s < num_splits; ++s) {
+      if (lse[s] == -INFINITY) continue;  // empty split: its partial row was never written
       float w = __expf(lse[s] - M);
       num += w * part_o[((int64_t)bh * num_splits + s) * D + d];
       den += w;
