@@ -557,3 +557,58 @@ LLB_EXPORT int llb_gqa_prefill(const void* q, int64_t q_stride, const void* kv_l
 #undef LAUNCH_PREFILL
   return LLB_OK;
 }
+
+// ---------------------------------------------------------------------------------------
+// Split-KV decode attention for callers that must not allocate device memory
+// (declaration and contract: attention_no_alloc.h).
+// ---------------------------------------------------------------------------------------
+#include "attention_no_alloc.h"
+#include <mutex>
+
+namespace {
+// Partial outputs [rows, 128] fp32 followed by partial log-sum-exps [rows] fp32.  Lives in the
+// library image: every GPU that loads the library holds these bytes until the process exits.
+static __device__ __align__(256) float g_no_alloc_scratch[LLB_NO_ALLOC_MAX_ROWS * 128 + LLB_NO_ALLOC_MAX_ROWS];
+
+constexpr int kMaxDevices = 64;
+float* g_no_alloc_ptr[kMaxDevices] = {nullptr};
+std::mutex g_no_alloc_mu;
+
+// Device address of the scratch array on the current device.  In host code the array's name is only a
+// stand-in for the symbol, not an address a kernel may use, so the address is asked for once per
+// device (with that device current) and cached.
+int no_alloc_scratch(float** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDevices) return LLB_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> lk(g_no_alloc_mu);
+  if (g_no_alloc_ptr[dev] == nullptr) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_no_alloc_scratch);
+    if (e != cudaSuccess) return (int)e;
+    g_no_alloc_ptr[dev] = p;
+  }
+  *out = g_no_alloc_ptr[dev];
+  return LLB_OK;
+}
+}  // namespace
+
+LLB_EXPORT int llb_gqa_decode_no_alloc(const void* q, int64_t q_stride, const void* kv_layer, const int* req_to_token,
+                                       int64_t r2t_stride, const int* b_req_idx, const int* b_seq_len, void* out,
+                                       int64_t out_stride, int B, int Hq, int Hkv, int D, int num_splits,
+                                       float sm_scale, cudaStream_t st) {
+  if (B <= 0) return LLB_OK;
+  if (num_splits < 1 || Hq <= 0) return LLB_ERR_BAD_ARG;
+  if (D > 128) return LLB_ERR_TOO_LARGE;
+  const int64_t rows = (int64_t)B * Hq * num_splits;
+  if (num_splits > 1 && rows > LLB_NO_ALLOC_MAX_ROWS) return LLB_ERR_TOO_LARGE;
+  float* scratch = nullptr;
+  int rc = no_alloc_scratch(&scratch);
+  if (rc) return rc;
+  // Nothing in the scratch has to start at zero: every (row, split) either gets its partial output and
+  // log-sum-exp written by this call, or is marked empty (lse = -inf) and skipped by the merge.
+  return llb_gqa_decode(q, q_stride, kv_layer, req_to_token, r2t_stride, b_req_idx, b_seq_len, out, out_stride,
+                        scratch, scratch + (int64_t)LLB_NO_ALLOC_MAX_ROWS * 128, B, Hq, Hkv, D, num_splits, sm_scale,
+                        st);
+}

@@ -41,6 +41,10 @@ struct GemmParams {
   int M, N, K;
   int64_t ldc;  // elements
   int num_m_blocks, num_n_blocks;
+  int group_m;         // M-blocks per raster group (sized so the group's A panel stays in L2)
+  int stream_k;        // 1: every CTA gets an equal share of (tile, k-block) units; split tiles are fixed up
+  float* sk_partials;  // [grid][2][BM * BN] fp32 partial tiles of split tiles (stream_k only)
+  int* sk_counters;    // [tiles] arrived k-blocks per tile, self-resetting (stream_k only)
 };
 
 template <int BN>
@@ -61,10 +65,42 @@ __device__ __forceinline__ float gelu_tanh_f(float v) {
   return 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
 }
 
-// Tile order: groups of 8 M-blocks, M fastest inside a group, so CTAs running at the same time
-// share W tiles (decode: both M-blocks of one W tile) and re-read a bounded set of A tiles from L2.
-__device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int& mb, int& nb) {
-  constexpr int GROUP = 8;
+// Tile order: groups of `GROUP` M-blocks, M fastest inside a group, so CTAs running at the same time
+// share W tiles (decode: both M-blocks of one W tile) and the group's A panel is re-read from L2
+// while W streams past it once per group.
+
+// Work of one CTA as a sequence of segments (tile, k-block range).  Data-parallel mode: whole tiles,
+// round-robin.  Stream-K mode: CTA c owns units [c*U/G, (c+1)*U/G) of the U = tiles * k_blocks
+// (tile, k-block) units, so a tile may be shared by neighbouring CTAs.
+struct SegIter {
+  int64_t u, u_end;
+  int tile_rr, num_tiles, kb, G;
+  bool stream_k;
+  __device__ SegIter(bool sk, int cta, int grid, int tiles, int k_blocks)
+      : tile_rr(cta), num_tiles(tiles), kb(k_blocks), G(grid), stream_k(sk) {
+    int64_t U = (int64_t)tiles * k_blocks;
+    u = (int64_t)cta * U / grid;
+    u_end = (int64_t)(cta + 1) * U / grid;
+  }
+  __device__ bool next(int& tile, int& k0, int& k1) {
+    if (stream_k) {
+      if (u >= u_end) return false;
+      tile = (int)(u / kb);
+      k0 = (int)(u - (int64_t)tile * kb);
+      int64_t left = u_end - u;
+      k1 = (int)(left < (int64_t)(kb - k0) ? k0 + left : kb);
+      u += k1 - k0;
+      return true;
+    }
+    if (tile_rr >= num_tiles) return false;
+    tile = tile_rr;
+    tile_rr += G;
+    k0 = 0;
+    k1 = kb;
+    return true;
+  }
+};
+__device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int GROUP, int& mb, int& nb) {
   int per_group = GROUP * num_n;
   int grp = tile / per_group;
   int first_m = grp * GROUP;
@@ -126,10 +162,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tma_prefetch_desc(&tmB);
       int stage = 0;
       uint32_t phase = 0;
-      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      SegIter segs(p.stream_k != 0, blockIdx.x, gridDim.x, num_tiles, k_blocks);
+      int tile, k0, k1;
+      while (segs.next(tile, k0, k1)) {
         int mb, nb;
-        tile_coords(tile, p.num_m_blocks, p.num_n_blocks, mb, nb);
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        tile_coords(tile, p.num_m_blocks, p.num_n_blocks, p.group_m, mb, nb);
+        for (int kb = k0; kb < k1; ++kb) {
           mbar_wait(empty_bar(stage), phase ^ 1, &abort_flag, p.status, 1);
           const uint32_t sa = smem_base + stage * STAGE_BYTES;
           mbar_expect_tx(full_bar(stage), STAGE_BYTES);
@@ -148,13 +186,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
-      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+      SegIter segs(p.stream_k != 0, blockIdx.x, gridDim.x, num_tiles, k_blocks);
+      int tile, k0, k1;
+      for (; segs.next(tile, k0, k1); ++it) {
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         mbar_wait(tempty_bar(acc), acc_phase ^ 1, &abort_flag, p.status, 2);
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb = k0; kb < k1; ++kb) {
           mbar_wait(full_bar(stage), phase, &abort_flag, p.status, 3);
           tc_fence_after();
           const uint32_t sa = smem_base + stage * STAGE_BYTES;
@@ -163,7 +203,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             // advancing K inside the 128-byte swizzle row: +32 bytes = +2 in 16-byte units
-            umma_bf16(d_tmem, da + 2 * k, db + 2 * k, IDESC, (kb | k) != 0);
+            umma_bf16(d_tmem, da + 2 * k, db + 2 * k, IDESC, ((kb - k0) | k) != 0);
           }
           umma_commit(empty_bar(stage));  // stage reusable once these MMAs have read it
           if (++stage == STAGES) {
@@ -177,19 +217,83 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else {
     // ------------------------------ epilogue ------------------------------
     const int lane_grp = warp & 3;  // TMEM lanes 32*lane_grp .. +31 are the ones this warp may read
+    const int erow = lane_grp * 32 + lane;  // row inside the tile owned by this thread
+    const int etid = threadIdx.x - 64;      // 0..127 among the epilogue threads
+    __shared__ int sk_last_flag;
     int it = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+    SegIter segs(p.stream_k != 0, blockIdx.x, gridDim.x, num_tiles, k_blocks);
+    int tile, k0, k1;
+    for (; segs.next(tile, k0, k1); ++it) {
       int mb, nb;
-      tile_coords(tile, p.num_m_blocks, p.num_n_blocks, mb, nb);
+      tile_coords(tile, p.num_m_blocks, p.num_n_blocks, p.group_m, mb, nb);
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       mbar_wait(tfull_bar(acc), acc_phase, &abort_flag, p.status, 4);
       tc_fence_after();
-      const int row = mb * BM + lane_grp * 32 + lane;
+      const int row = mb * BM + erow;
       const bool row_ok = row < p.M;
       const uint32_t t_row = tmem_base + ((uint32_t)(lane_grp * 32) << 16) + acc * BN;
 
-      if (EPI == EPI_GATED_SILU || EPI == EPI_GATED_GELU) {
+      // ---- stream-K: a tile split over several CTAs is summed by whichever CTA arrives last ----
+      int n_other = 0;        // partial tiles of other CTAs to add (only the last arriver has any)
+      int other_first = 0;    // first contributing CTA of this tile
+      bool do_epilogue = true;
+      const bool full_tile = (k0 == 0 && k1 == k_blocks);
+      if (!full_tile) {
+        const int slot = k0 > 0 ? 0 : 1;
+        float* mine = p.sk_partials + ((int64_t)blockIdx.x * 2 + slot) * (BM * BN) + (int64_t)erow * BN;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_row + c, r);
+          tmem_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; j += 4)
+            *reinterpret_cast<uint4*>(mine + c + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+        }
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (etid == 0) {
+          int prev = atomicAdd(p.sk_counters + tile, k1 - k0);
+          sk_last_flag = (prev + (k1 - k0) == k_blocks) ? 1 : 0;
+          if (sk_last_flag) p.sk_counters[tile] = 0;  // every contributor has arrived: ready for the next launch
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        do_epilogue = sk_last_flag != 0;
+        if (do_epilogue) {
+          __threadfence();
+          const int64_t U = (int64_t)num_tiles * k_blocks;
+          const int64_t ts = (int64_t)tile * k_blocks;
+          other_first = (int)(((ts + 1) * gridDim.x - 1) / U);
+          const int other_last = (int)(((ts + k_blocks) * gridDim.x - 1) / U);
+          n_other = other_last - other_first + 1;
+        }
+      }
+
+      // adds the partial tiles of the other contributors to 32 accumulator columns starting at `c`
+      auto add_partials = [&](uint32_t* r, int c) {
+        const int64_t U = (int64_t)num_tiles * k_blocks;
+        const int64_t ts = (int64_t)tile * k_blocks;
+        for (int q = 0; q < n_other; ++q) {
+          const int cta = other_first + q;
+          if (cta == (int)blockIdx.x) continue;
+          const int64_t cta_start = (int64_t)cta * U / gridDim.x;
+          const int oslot = cta_start > ts ? 0 : 1;
+          const float* src = p.sk_partials + ((int64_t)cta * 2 + oslot) * (BM * BN) + (int64_t)erow * BN + c;
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            float4 v = __ldcg(reinterpret_cast<const float4*>(src + j));
+            r[j] = __float_as_uint(__uint_as_float(r[j]) + v.x);
+            r[j + 1] = __float_as_uint(__uint_as_float(r[j + 1]) + v.y);
+            r[j + 2] = __float_as_uint(__uint_as_float(r[j + 2]) + v.z);
+            r[j + 3] = __float_as_uint(__uint_as_float(r[j + 3]) + v.w);
+          }
+        }
+      };
+
+      if (!do_epilogue) {
+        // partial handed over; nothing else to do for this segment
+      } else if (EPI == EPI_GATED_SILU || EPI == EPI_GATED_GELU) {
         // columns come as [32 gate | 32 up] pairs; output has N/2 columns
         bf16* crow = (bf16*)p.C + (int64_t)row * p.ldc;
 #pragma unroll 1
@@ -198,6 +302,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           tmem_ld_32x32(t_row + c, gr);
           tmem_ld_32x32(t_row + c + 32, ur);
           tmem_wait_ld();
+          if (n_other) {
+            add_partials(gr, c);
+            add_partials(ur, c + 32);
+          }
           const int ocol = (nb * BN + c) / 2;
           if (row_ok && nb * BN + c < p.N) {
 #pragma unroll
@@ -219,6 +327,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           uint32_t r[32];
           tmem_ld_32x32(t_row + c, r);
           tmem_wait_ld();
+          if (n_other) add_partials(r, c);
           const int col0 = nb * BN + c;
           if (row_ok && col0 < p.N) {
             const int ncols = min(32, p.N - col0);
@@ -238,8 +347,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                   *reinterpret_cast<float4*>(crow + j) = v;
                 }
               } else {
-                for (int j = 0; j < ncols; ++j)
-                  crow[j] = __uint_as_float(r[j]) + (p.bias ? __bfloat162float(p.bias[col0 + j]) : 0.f);
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (j < ncols) crow[j] = __uint_as_float(r[j]) + (p.bias ? __bfloat162float(p.bias[col0 + j]) : 0.f);
               }
             } else {
               bf16* crow = (bf16*)p.C + (int64_t)row * p.ldc + col0;
@@ -265,11 +375,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                   *reinterpret_cast<bf16x8*>(crow + j) = pack8(o);
                 }
               } else {
-                for (int j = 0; j < ncols; ++j) {
-                  float v = __uint_as_float(r[j]);
-                  if (p.bias) v += __bfloat162float(p.bias[col0 + j]);
-                  if (EPI == EPI_RESIDUAL) v += __bfloat162float(rrow[j]);
-                  crow[j] = __float2bfloat16(v);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                  if (j < ncols) {
+                    float v = __uint_as_float(r[j]);
+                    if (p.bias) v += __bfloat162float(p.bias[col0 + j]);
+                    if (EPI == EPI_RESIDUAL) v += __bfloat162float(rrow[j]);
+                    crow[j] = __float2bfloat16(v);
+                  }
                 }
               }
             }
@@ -328,6 +441,8 @@ int cached_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols
   return LLB_OK;
 }
 
+constexpr int64_t kPanelBytes = 24ll << 20;  // A panel kept hot in L2 while W streams past it
+
 template <int BN, int EPI>
 int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, cudaStream_t st) {
   static bool configured = false;
@@ -340,7 +455,14 @@ int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, cud
   p.num_m_blocks = cdiv(p.M, BM);
   p.num_n_blocks = cdiv(p.N, BN);
   int tiles = p.num_m_blocks * p.num_n_blocks;
+  int64_t panel_rows = kPanelBytes / ((int64_t)BM * p.K * 2);
+  p.group_m = (int)(panel_rows < 4 ? 4 : (panel_rows > 64 ? 64 : panel_rows));
   int grid = tiles < sm_count() ? tiles : sm_count();
+  if (p.stream_k) {
+    int64_t units = (int64_t)tiles * cdiv(p.K, BK);
+    grid = units < sm_count() ? (int)units : sm_count();
+    p.group_m = p.num_m_blocks;  // M fastest: neighbouring CTAs share a W tile
+  }
   gemm_bf16_kernel<BN, EPI><<<grid, GEMM_THREADS, smem_bytes<BN>(), st>>>(ta, tb, p);
   LLB_LAUNCH_CHECK();
   return LLB_OK;
@@ -363,20 +485,22 @@ int dispatch_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tb, GemmPara
   return LLB_ERR_UNSUPPORTED;
 }
 
-// Largest BN whose tile count wastes little of the last wave; small problems get small tiles so
-// that every SM streams a share of the weights.
+// Tile width for the data-parallel schedule: modelled time = waves x measured per-k-block cost of a
+// full wave of that tile width (L2-bound figures from B200 runs: 0.27 / 0.34 / 0.56 us).
 int pick_bn(int M, int N) {
   const int sms = sm_count();
   const int cands[3] = {256, 128, 64};
-  double best_eff = -1.0;
-  int best = 128;
+  const double cost[3] = {0.556, 0.343, 0.27};
+  double best_t = 1e30;
+  int best = 256;
   for (int i = 0; i < 3; ++i) {
     int bn = cands[i];
+    if (bn > 64 && N < bn) continue;
     int64_t tiles = (int64_t)cdiv(M, BM) * cdiv(N, bn);
     int64_t waves = (tiles + sms - 1) / sms;
-    double eff = (double)tiles / (double)(waves * sms);
-    if (eff > best_eff * 1.08) {  // prefer the larger tile unless the smaller one is clearly better
-      best_eff = eff;
+    double t = (double)waves * cost[i];
+    if (t < best_t * 0.97) {
+      best_t = t;
       best = bn;
     }
   }
@@ -390,15 +514,35 @@ int pick_bn(int M, int N) {
 //   2 SiLU-gated: W rows interleaved as [32 gate | 32 up] blocks; C is [M, N/2]
 //   3 store fp32 (+bias)          4 GELU(tanh)-gated, layout as 2
 // bn: 0 = choose, else 64/128/256.  status: optional device int receiving a wait-timeout code.
+// stream_k: 0 = whole tiles per CTA, 1 = equal (tile, k-block) shares with fix-up of split tiles,
+// -1 = choose (stream-K when the tiles would fill fewer than three waves).  Stream-K needs
+// sk_partials (>= SMs * 2 * 128 * bn floats) and sk_counters (>= tiles ints, zero before first use;
+// the kernel leaves them zero); launches that share them must not overlap on the GPU.
 LLB_EXPORT int llb_gemm_bf16(const void* A, int64_t lda, const void* W, int64_t ldw, void* C, int64_t ldc,
                              const void* residual, const void* bias, int M, int N, int K, int epi, int bn,
-                             int* status, cudaStream_t st) {
+                             int stream_k, float* sk_partials, int64_t sk_partials_floats, int* sk_counters,
+                             int sk_counters_len, int* status, cudaStream_t st) {
   if (M <= 0 || N <= 0) return LLB_OK;
   if (K <= 0 || (K % 8) != 0) return LLB_ERR_UNSUPPORTED;
   if ((epi == EPI_GATED_SILU || epi == EPI_GATED_GELU) && (N % 64) != 0) return LLB_ERR_UNSUPPORTED;
   if (epi != EPI_F32 && (((uintptr_t)C & 15) || (ldc % 8))) return LLB_ERR_BAD_ARG;
   if (epi == EPI_F32 && (((uintptr_t)C & 15) || (ldc % 4))) return LLB_ERR_BAD_ARG;
   if (epi == EPI_RESIDUAL && (residual == nullptr || ((uintptr_t)residual & 15))) return LLB_ERR_BAD_ARG;
+  const int kblocks = cdiv(K, BK);
+  if (stream_k != 0) {
+    int sk_bn = bn ? bn : (N >= 256 ? 256 : (N >= 128 ? 128 : 64));
+    int64_t tiles = (int64_t)cdiv(M, BM) * cdiv(N, sk_bn);
+    bool fits = sk_partials != nullptr && sk_counters != nullptr &&
+                sk_partials_floats >= (int64_t)sm_count() * 2 * BM * sk_bn && sk_counters_len >= tiles;
+    bool want = stream_k == 1 || (tiles < 3ll * sm_count() && tiles % sm_count() != 0 && kblocks >= 4);
+    if (fits && want) {
+      stream_k = 1;
+      bn = sk_bn;
+    } else {
+      if (stream_k == 1 && !fits) return LLB_ERR_BAD_ARG;
+      stream_k = 0;
+    }
+  }
   if (bn == 0) bn = pick_bn(M, N);
   CUtensorMap ta, tb;
   int rc = cached_tmap(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM);
@@ -414,6 +558,9 @@ LLB_EXPORT int llb_gemm_bf16(const void* A, int64_t lda, const void* W, int64_t 
   p.N = N;
   p.K = K;
   p.ldc = ldc;
+  p.stream_k = stream_k;
+  p.sk_partials = sk_partials;
+  p.sk_counters = sk_counters;
   switch (bn) {
     case 256:
       return dispatch_epi<256>(epi, ta, tb, p, st);

@@ -71,7 +71,9 @@ class InferReq:
         self.filter_mark = False
         self.out_token_counter: Dict[int, int] = {}
         self.cumlogprob = 0.0
-        self.seed = self.sampling.seed if self.sampling.seed >= 0 else (hash((self.req_id, time.time_ns())) & 0x7FFFFFFF)
+        # sub-requests of one group (n > 1) share the user's seed: offset it by the index inside the group
+        self.seed = (self.sampling.seed + (self.req_id - shm_req.group_req_id)) if self.sampling.seed >= 0 \
+            else (hash((self.req_id, time.time_ns())) & 0x7FFFFFFF)
         self.extra = {}
         if self.sampling.input_penalty and self.sampling.has_penalty:
             for t in shm_req.get_prompt_ids():

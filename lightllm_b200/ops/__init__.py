@@ -135,7 +135,23 @@ def gemm_status(device) -> torch.Tensor:
     return _status_words[key]
 
 
-def gemm(a, w, epi: str = "store", residual=None, bias=None, out=None, bn: int = 0):
+_sk_scratch = {}
+
+
+def _stream_k_scratch(device):
+    """fp32 partial-tile buffer and per-tile arrival counters for the stream-K schedule (per device;
+    all GEMMs of a stream share them, which is safe because they run back to back on that stream)."""
+    key = torch.device(device).index or 0
+    cur = _sk_scratch.get(key)
+    if cur is None:
+        sms = torch.cuda.get_device_properties(device).multi_processor_count
+        cur = (torch.empty(sms * 2 * 128 * 256, dtype=torch.float32, device=device),
+               torch.zeros(8192, dtype=torch.int32, device=device))
+        _sk_scratch[key] = cur
+    return cur
+
+
+def gemm(a, w, epi: str = "store", residual=None, bias=None, out=None, bn: int = 0, stream_k: int = -1):
     """C = A . W^T on the tcgen05 tensor cores.  a [M, K], w [N, K] (checkpoint layout).
 
     epi: "store" | "residual" (C += residual) | "gated_silu"/"gated_gelu" (w rows interleaved with
@@ -162,9 +178,12 @@ def gemm(a, w, epi: str = "store", residual=None, bias=None, out=None, bn: int =
         out = torch.empty((M, n_out), dtype=torch.float32 if epi == "f32" else a.dtype, device=a.device)
     if epi == "residual":
         assert residual.shape == out.shape and residual.stride(0) == out.stride(0)
+    skp, skc = (None, None) if stream_k == 0 else _stream_k_scratch(a.device)
     check(kernels().llb_gemm_bf16(ptr(a), i64(a.stride(0)), ptr(w), i64(w.stride(0)), ptr(out), i64(out.stride(0)),
                                   ptr(residual), ptr(bias), c_int(M), c_int(N), c_int(K), c_int(EPI_CODES[epi]),
-                                  c_int(bn), ptr(gemm_status(a.device)), stream()), "gemm_bf16")
+                                  c_int(bn), c_int(stream_k), ptr(skp), i64(skp.numel() if skp is not None else 0),
+                                  ptr(skc), c_int(skc.numel() if skc is not None else 0),
+                                  ptr(gemm_status(a.device)), stream()), "gemm_bf16")
     _count()
     return out
 

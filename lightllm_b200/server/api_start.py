@@ -1,0 +1,162 @@
+"""Argument normalisation and process start-up.
+
+`normalize_args` fills the derived values the same way the reference launcher does
+(lightllm/server/api_start.py:36-399): max_req_total_len from the model config, router_token_ratio
+0.85 (0.0 on prefill/decode nodes), batch_max_tokens = 16384 / dp, chunked_prefill_size = half of
+it, eos ids and dtype from config.json, a unique name that namespaces every shm segment and ipc
+socket so several servers can share a host, and the mode compatibility checks.  Start order:
+metric manager -> detokenizer -> router (which spawns one model process per GPU) -> HTTP workers.
+"""
+from __future__ import annotations
+
+import os
+import sys
+import time
+import uuid
+
+from ..utils import config_utils
+from ..utils.net_utils import alloc_can_use_network_port
+from ..utils.process_utils import process_manager, set_proc_title
+from .core.objs.start_args import StartArgs, set_env_start_args
+
+
+def normalize_args(args: StartArgs, config_override: dict = None) -> StartArgs:
+    a = args
+    assert a.tp >= 1 and a.dp >= 1 and a.tp % a.dp == 0, "--dp must divide --tp"
+    assert a.tp % a.nnodes == 0, "--tp must be a multiple of --nnodes"
+    if a.run_mode in ("normal", "prefill", "decode", "visual_only"):
+        assert a.model_dir is not None or config_override is not None, "--model_dir is required"
+    cfg = config_override
+    # ---- model-derived ----
+    if a.max_req_total_len is None:
+        a.max_req_total_len = config_utils.get_model_max_len(a.model_dir) if cfg is None else \
+            cfg.get("max_position_embeddings", 16384)
+    if a.eos_id is None:
+        a.eos_ids = (config_utils.get_eos_token_ids(a.model_dir) if cfg is None else
+                     ([cfg["eos_token_id"]] if isinstance(cfg.get("eos_token_id"), int) else list(cfg.get("eos_token_id") or [])))
+    else:
+        a.eos_ids = list(a.eos_id)
+    if a.vocab_size is None:
+        a.vocab_size = config_utils.get_vocab_size(a.model_dir) if cfg is None else cfg.get("vocab_size")
+    if a.data_type is None:
+        a.data_type = config_utils.get_dtype(a.model_dir) if cfg is None else cfg.get("torch_dtype", "bfloat16")
+    # ---- scheduler defaults ----
+    if a.router_token_ratio is None:
+        a.router_token_ratio = 0.0 if a.run_mode in ("prefill", "decode") else 0.85
+    if a.performance_mode == "personal":
+        a.graph_max_batch_size = min(a.graph_max_batch_size, 16)
+        a.running_max_req_size = min(a.running_max_req_size, 16)
+        a.disable_chunked_prefill = True
+    if a.batch_max_tokens is None:
+        a.batch_max_tokens = max(16384 // a.dp, 1024) if not a.disable_chunked_prefill else \
+            max(a.max_req_total_len, 16384 // a.dp)
+    if a.chunked_prefill_size is None:
+        a.chunked_prefill_size = a.batch_max_tokens if a.disable_chunked_prefill else max(a.batch_max_tokens // 2, 256)
+    if not a.disable_chunked_prefill:
+        assert a.batch_max_tokens >= a.chunked_prefill_size, "batch_max_tokens must cover chunked_prefill_size"
+    else:
+        assert a.batch_max_tokens >= a.max_req_total_len, "without chunked prefill batch_max_tokens must cover max_req_total_len"
+    if a.graph_max_len_in_batch == 0:
+        a.graph_max_len_in_batch = a.max_req_total_len
+    # ---- mode compatibility ----
+    if a.enable_prefill_microbatch_overlap or a.enable_decode_microbatch_overlap:
+        a.enable_tpsp_mix_mode = True
+    if a.use_dynamic_prompt_cache:
+        a.disable_dynamic_prompt_cache = False
+    if a.diverse_mode:
+        assert not a.disable_dynamic_prompt_cache, "diverse_mode needs the prompt cache"
+    if a.token_healing_mode:
+        assert a.output_constraint_mode == "none", "token healing and output constraints are exclusive"
+    assert not (a.first_token_constraint_mode and a.output_constraint_mode != "none")
+    if a.enable_ep_moe:
+        assert a.dp == a.tp or a.dp == 1, "--enable_ep_moe expects --dp 1 or --dp equal to --tp"
+    if a.mtp_mode is not None:
+        assert a.mtp_step > 0 and a.mtp_draft_model_dir, "mtp needs --mtp_step and --mtp_draft_model_dir"
+    if a.run_mode in ("prefill", "decode"):
+        assert a.pd_master_ip and a.pd_master_port, "PD nodes need --pd_master_ip/--pd_master_port"
+    # ---- names and ports ----
+    if a.unique_server_name is None:
+        a.unique_server_name = f"llb{os.getpid()}x{uuid.uuid4().hex[:6]}"
+    os.environ["LIGHTLLM_UNIQUE_SERVICE_NAME_ID"] = a.unique_server_name
+    need = ["router_port", "detokenization_port", "http_server_port", "metric_port", "visual_port", "audio_port",
+            "cache_port", "multi_level_kv_cache_port"]
+    missing = [n for n in need if getattr(a, n) is None]
+    extra = 1 if a.nccl_port is None else 0
+    ports = alloc_can_use_network_port(len(missing) + extra, used_ports=[a.port], start=20000 + (os.getpid() % 2000) * 10)
+    for n, p in zip(missing, ports):
+        setattr(a, n, p)
+    if a.nccl_port is None:
+        a.nccl_port = ports[-1]
+    if a.disable_vision is None:
+        a.disable_vision = True if cfg is not None else not config_utils.is_multimodal(a.model_dir)
+    if a.disable_audio is None:
+        a.disable_audio = True
+    a.enable_multimodal = not a.disable_vision
+    return a
+
+
+def start_core_processes(args: StartArgs, config_override: dict = None):
+    """Everything except the HTTP workers; returns when all of them reported "init ok"."""
+    from .detokenization.manager import start_detokenization_process
+    from .metrics.manager import start_metric_manager
+    from .router.manager import start_router_process
+
+    d = args.to_dict()
+    d = {k: v for k, v in d.items() if not k.startswith("_")}
+    process_manager.start_submodule_processes([start_metric_manager], [(d,)])
+    process_manager.start_submodule_processes([start_detokenization_process], [(d,)])
+    process_manager.start_submodule_processes([start_router_process], [(d, config_override)])
+
+
+def run_http_server(args: StartArgs):
+    import uvicorn
+
+    set_env_start_args(args)
+    uvicorn.run("lightllm_b200.server.api_http:app", host=args.host, port=args.port, workers=args.httpserver_workers,
+                log_level="warning", loop="uvloop", timeout_keep_alive=5)
+
+
+def normal_or_p_d_start(args: StartArgs, config_override: dict = None):
+    set_proc_title(f"lightllm::{args.model_name}::api_server")
+    args = normalize_args(args, config_override)
+    set_env_start_args(args)
+    start_core_processes(args, config_override)
+    if args.health_monitor:
+        from .health_monitor.manager import start_health_check_process
+
+        process_manager.start_submodule_processes([start_health_check_process], [(args.to_dict(),)])
+    try:
+        run_http_server(args)
+    finally:
+        process_manager.terminate_all()
+
+
+def pd_master_start(args: StartArgs):
+    args = normalize_args(args, {"vocab_size": None})
+    set_env_start_args(args)
+    from .metrics.manager import start_metric_manager
+
+    process_manager.start_submodule_processes([start_metric_manager], [(args.to_dict(),)])
+    try:
+        run_http_server(args)
+    finally:
+        process_manager.terminate_all()
+
+
+def config_server_start(args: StartArgs):
+    import uvicorn
+
+    from .config_server.api_http import app as cfg_app
+
+    set_env_start_args(args)
+    uvicorn.run(cfg_app, host=args.config_server_host or args.host, port=args.config_server_port or args.port,
+                log_level="warning")
+
+
+def visual_only_start(args: StartArgs):
+    from .visualserver.manager import start_visual_process
+
+    args = normalize_args(args)
+    set_env_start_args(args)
+    process_manager.start_submodule_processes([start_visual_process], [(args.to_dict(),)])
+    process_manager.supervise()

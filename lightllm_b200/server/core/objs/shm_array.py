@@ -66,7 +66,6 @@ class ShmArray:
         if self.name is None:
             raise ValueError("a process-local array cannot be linked")
         self.shm = shared_memory.SharedMemory(name=self.name, create=False)
-        _untrack(self.shm)
         self.arr = np.ndarray(self.shape, dtype=self.dtype, buffer=self.shm.buf)
         return self
 

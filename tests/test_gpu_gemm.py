@@ -62,3 +62,31 @@ def test_gemm_strided_a_and_tail_n(dev):
     a = big[:, :K]  # row stride K+256
     w = (torch.randn(N, K, device=dev) * 0.1).to(BF)
     _check(ops.gemm(a, w), a.float() @ w.float().t(), K)
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 4096, 4096), (256, 6144, 4096), (256, 28672, 4096), (256, 4096, 14336),
+                                   (1, 4096, 4096), (17, 1024, 512), (300, 768, 8192), (2000, 2048, 1024)])
+@pytest.mark.parametrize("bn", [0, 128, 256])
+def test_gemm_stream_k(dev, M, N, K, bn):
+    """Tiles split across CTAs along K and fixed up by the last arriver; run twice to check that the
+    arrival counters are left clean."""
+    torch.manual_seed(3)
+    a = (torch.randn(M, K, device=dev) * 0.5).to(BF)
+    w = (torch.randn(N, K, device=dev) * 0.1).to(BF)
+    want = a.float() @ w.float().t()
+    for _ in range(2):
+        _check(ops.gemm(a, w, bn=bn, stream_k=1), want, K)
+    res = torch.randn(M, N, device=dev).to(BF)
+    _check(ops.gemm(a, w, epi="residual", residual=res, bn=bn, stream_k=1), want + res.float(), K)
+
+
+def test_gemm_stream_k_gated(dev):
+    torch.manual_seed(4)
+    M, I, K = 256, 1792, 4096
+    a = (torch.randn(M, K, device=dev) * 0.5).to(BF)
+    g = (torch.randn(I, K, device=dev) * 0.1).to(BF)
+    u = (torch.randn(I, K, device=dev) * 0.1).to(BF)
+    wi = ref.interleave_gate_up(g, u)
+    want = torch.nn.functional.silu(a.float() @ g.float().t()) * (a.float() @ u.float().t())
+    _check(ops.gemm(a, wi, epi="gated_silu", stream_k=1), want, K)
+    _check(ops.gemm(a, wi, epi="gated_silu", stream_k=-1), want, K)
