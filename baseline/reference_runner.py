@@ -2,7 +2,7 @@
 
 The reference package is installed under ``baseline/_ref`` (pip, --no-deps, from a copy of the
 read-only source tree).  Its third-party pure-Python dependencies that are absent from the offline
-image (easydict, frozendict, orjson, ujson, rpyc, atomics, librosa, soxr) are satisfied by small
+image (easydict, frozendict, orjson, ujson, rpyc, atomics, librosa, soxr, cupy) are satisfied by small
 stand-ins in ``baseline/shims``; none of this repository's models, kernels or engine is on the path.
 
 The run goes through the reference's own engine API, the way its static benchmark does

@@ -1,0 +1,299 @@
+// Tensor-parallel reduction over NVLink peer memory, fused with the residual add and the RMSNorm
+// that follow every row-parallel GEMM (o_proj, down_proj).
+//
+//   residual += sum_over_ranks(partial_r)        h = rmsnorm(residual) * w
+//
+// Every rank owns one "symmetric" region with the same layout, mapped into all peers (CUDA IPC):
+//   partial[2][maxT, H]   the rank's GEMM output (the GEMM writes straight into it), double-buffered
+//   sums   [2][maxT, H]   reduced rows pushed by their owner ranks (two-shot mode), double-buffered
+//   ready  [world]        ready[q] = epoch of the last call for which rank q's partial is complete
+//   rowflag[maxT]         rowflag[i] = epoch of the last call for which row i of `sums` is complete
+//
+// One kernel per rank and call, no NCCL, no host round trip:
+//   one-shot  (small T): wait ready[*] -> every rank pulls all peers' rows with P2P loads, sums in
+//             fp32, adds the residual, normalises.  (tp-1) * T * H * 2 bytes in per rank, one hop.
+//   two-shot  (larger T): rank r reduces the rows it owns (row % world == r) from the peers' partials
+//             and pushes the bf16 sums into every rank's `sums` with P2P stores + a per-row flag;
+//             then every rank adds the residual and normalises all rows from its own memory.
+//             2 * (tp-1)/tp * T * H * 2 bytes per rank (the all-reduce minimum), rows stream through
+//             as they complete, no global barrier.
+// Flags carry a call epoch that only grows, so nothing is ever reset; the epoch lives in device memory
+// and is advanced by the last CTA to finish, which keeps CUDA-graph replays correct.  A rank can run at
+// most one call ahead of its slowest peer (it needs that peer's rows of the current call to finish), so
+// two buffers per kind are enough.  Every wait is bounded: on expiry the kernel records a code in the
+// status word and carries on, so it always terminates.
+//
+// The same kernel can be launched cooperatively with gridDim.y = world on ONE GPU (all "ranks" are
+// slices of that GPU's memory): that is how the protocol is tested where only one GPU is available.
+//
+// Reference behaviour: lightllm/distributed/communication_op.py (all_reduce dispatch: FlashInfer one-shot,
+// torch symmetric memory, NCCL) followed by separate add and rmsnorm kernels
+// (lightllm/common/basemodel/layer_infer/base_layer_infer.py:63-84).
+#include "common.cuh"
+#include <cooperative_groups.h>
+
+using namespace llb;
+
+namespace {
+
+constexpr int MAX_WORLD = 8;
+constexpr uint64_t kCommWaitNs = 2000000000ull;
+
+struct RankView {
+  // pointers as seen from THIS rank; index = peer rank
+  const bf16* partial[MAX_WORLD];  // peers' partial buffers (current parity)
+  bf16* sums[MAX_WORLD];           // peers' sums buffers (current parity)
+  uint32_t* ready[MAX_WORLD];      // peers' ready arrays
+  uint32_t* rowflag[MAX_WORLD];    // peers' row flag arrays
+  bf16* residual;                  // local [T, H]
+  bf16* out;                       // local [T, H] normed output
+  const bf16* norm_w;              // local [H]
+  uint32_t* epoch;                 // local device counter (value of the previous call)
+  uint32_t* arrive;                // local CTA arrival counter
+  int* status;                     // local status word
+  int rank;
+};
+
+struct CommParams {
+  RankView v[MAX_WORLD];  // v[0] in a real multi-GPU launch; v[blockIdx.y] in the one-GPU emulation
+  int world, T, H;
+  float eps, w_offset;
+  int one_shot;
+  int do_norm;  // 0: plain all-reduce (out = sum over ranks, residual untouched)
+};
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint4 ld_cg_16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
+// Wait until *flag >= want (wrap-safe).  Called by one thread; returns false on timeout.
+__device__ bool wait_flag(const uint32_t* flag, uint32_t want, int* status, int code) {
+  uint64_t t0 = 0;
+  for (uint32_t spin = 0;; ++spin) {
+    if ((int32_t)(ld_acquire_sys(flag) - want) >= 0) return true;
+    if ((spin & 0x3f) == 0x3f) {
+      uint64_t now = global_timer_ns();
+      if (t0 == 0)
+        t0 = now;
+      else if (now - t0 > kCommWaitNs) {
+        if (status) atomicCAS(status, 0, code);
+        return false;
+      }
+      __nanosleep(64);
+    }
+  }
+}
+
+__device__ __forceinline__ void add8(float* acc, const uint4& raw) {
+  const bf16x8* p = reinterpret_cast<const bf16x8*>(&raw);
+  float f[8];
+  unpack8(*p, f);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) acc[k] += f[k];
+}
+
+// sum over ranks of row `row` (vector v) read from the peers' partial buffers
+__device__ __forceinline__ void reduce_vec(const RankView& me, int world, int64_t off, float* acc) {
+#pragma unroll
+  for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+  uint4 raw[MAX_WORLD];
+#pragma unroll
+  for (int q = 0; q < MAX_WORLD; ++q)
+    if (q < world) raw[q] = ld_cg_16(me.partial[q] + off);
+#pragma unroll
+  for (int q = 0; q < MAX_WORLD; ++q)
+    if (q < world) add8(acc, raw[q]);
+}
+
+template <int MAX_VEC>
+__global__ void __launch_bounds__(256) tp_reduce_norm_kernel(const CommParams p) {
+  __shared__ float red[33];
+  __shared__ int s_ok;
+  const RankView& me = p.v[blockIdx.y];
+  const int world = p.world, T = p.T, H = p.H;
+  const int nvec = H >> 3;
+  const uint32_t epoch = *me.epoch + 1;  // this call
+  const int G = gridDim.x;
+
+  // ---- announce: my partial (written by the GEMM that ran before this kernel) is complete ----
+  if (blockIdx.x == 0 && threadIdx.x < world) {
+    __threadfence_system();
+    st_release_sys(me.ready[threadIdx.x] + me.rank, epoch);
+  }
+  // ---- wait for every peer's partial ----
+  if (threadIdx.x < world) wait_flag(me.ready[me.rank] + threadIdx.x, epoch, me.status, 100 + threadIdx.x);
+  __syncthreads();
+
+  if (!p.one_shot) {
+    // ---- phase 1: reduce the rows I own and push the sums to everyone ----
+    for (int row = me.rank + blockIdx.x * world; row < T; row += G * world) {
+      for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+        float acc[8];
+        const int64_t off = (int64_t)row * H + v * 8;
+        reduce_vec(me, world, off, acc);
+        bf16x8 packed = pack8(acc);
+        const uint4 out = *reinterpret_cast<uint4*>(&packed);
+#pragma unroll
+        for (int q = 0; q < MAX_WORLD; ++q)
+          if (q < world) *reinterpret_cast<uint4*>(me.sums[q] + off) = out;
+      }
+      __threadfence_system();
+      __syncthreads();
+      if (threadIdx.x < world) st_release_sys(me.rowflag[threadIdx.x] + row, epoch);
+    }
+  }
+
+  // ---- phase 2: residual add + RMSNorm over all rows (one-shot: reduce here from the peers) ----
+  for (int row = blockIdx.x; row < T; row += G) {
+    if (!p.one_shot) {
+      if (threadIdx.x == 0) s_ok = wait_flag(me.rowflag[me.rank] + row, epoch, me.status, 200) ? 1 : 0;
+      __syncthreads();
+    }
+    float vals[MAX_VEC][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAX_VEC; ++i) {
+      const int v = threadIdx.x + i * 256;
+      if (v < nvec) {
+        const int64_t off = (int64_t)row * H + v * 8;
+        if (p.one_shot) {
+          reduce_vec(me, world, off, vals[i]);
+        } else {
+          uint4 raw = ld_cg_16(me.sums[me.rank] + off);
+          unpack8(*reinterpret_cast<bf16x8*>(&raw), vals[i]);
+        }
+        if (p.do_norm) {
+          float r[8];
+          unpack8(*reinterpret_cast<const bf16x8*>(me.residual + off), r);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) vals[i][k] += r[k];
+          bf16x8 s = pack8(vals[i]);
+          *reinterpret_cast<bf16x8*>(me.residual + off) = s;
+          unpack8(s, vals[i]);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) ss += vals[i][k] * vals[i][k];
+        } else {
+          *reinterpret_cast<bf16x8*>(me.out + off) = pack8(vals[i]);
+        }
+      }
+    }
+    if (p.do_norm) {
+      ss = block_sum(ss, red);
+      const float inv = rsqrtf(ss / (float)H + p.eps);
+#pragma unroll
+      for (int i = 0; i < MAX_VEC; ++i) {
+        const int v = threadIdx.x + i * 256;
+        if (v < nvec) {
+          float wf[8], o[8];
+          unpack8(reinterpret_cast<const bf16x8*>(me.norm_w)[v], wf);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) o[k] = vals[i][k] * inv * (wf[k] + p.w_offset);
+          *reinterpret_cast<bf16x8*>(me.out + (int64_t)row * H + v * 8) = pack8(o);
+        }
+      }
+    }
+    __syncthreads();
+  }
+
+  // ---- the last CTA of this rank advances the epoch ----
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    unsigned prev = atomicAdd(me.arrive, 1u);
+    if (prev == (unsigned)G - 1) {
+      *me.arrive = 0;
+      __threadfence();
+      *me.epoch = epoch;
+    }
+  }
+}
+
+int launch(const CommParams& p, int ranks_in_grid, int ctas, cudaStream_t st) {
+  if (p.H % 8 != 0 || p.H > 8 * 256 * 8 || p.world > MAX_WORLD || p.world < 1) return LLB_ERR_UNSUPPORTED;
+  int per = cdiv(p.H / 8, 256);
+  dim3 grid(ctas, ranks_in_grid);
+  void* args[] = {(void*)&p};
+  const void* fn = per <= 1   ? (const void*)tp_reduce_norm_kernel<1>
+                   : per <= 2 ? (const void*)tp_reduce_norm_kernel<2>
+                   : per <= 4 ? (const void*)tp_reduce_norm_kernel<4>
+                              : (const void*)tp_reduce_norm_kernel<8>;
+  cudaError_t e;
+  if (ranks_in_grid > 1) {
+    // one-GPU emulation: CTAs of different "ranks" wait on one another, so they must be co-resident
+    e = cudaLaunchCooperativeKernel(fn, grid, dim3(256), args, 0, st);
+  } else {
+    e = cudaLaunchKernel(fn, grid, dim3(256), args, 0, st);
+  }
+  return e == cudaSuccess ? LLB_OK : (int)e;
+}
+
+}  // namespace
+
+// ---- symmetric memory helpers (plain cudaMalloc + legacy IPC handles; one process per GPU) ----
+LLB_EXPORT int llb_symm_alloc(void** out, int64_t bytes) {
+  cudaError_t e = cudaMalloc(out, (size_t)bytes);
+  if (e != cudaSuccess) return (int)e;
+  e = cudaMemset(*out, 0, (size_t)bytes);
+  return e == cudaSuccess ? LLB_OK : (int)e;
+}
+LLB_EXPORT int llb_symm_free(void* p) { return (int)cudaFree(p); }
+LLB_EXPORT int llb_ipc_get_handle(void* p, void* handle64) {
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) return (int)e;
+  memcpy(handle64, &h, sizeof(h));
+  return LLB_OK;
+}
+LLB_EXPORT int llb_ipc_open_handle(const void* handle64, void** out) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  cudaError_t e = cudaIpcOpenMemHandle(out, h, cudaIpcMemLazyEnablePeerAccess);
+  return e == cudaSuccess ? LLB_OK : (int)e;
+}
+LLB_EXPORT int llb_ipc_close_handle(void* p) { return (int)cudaIpcCloseMemHandle(p); }
+
+// Pointer tables (arrays of `world` device pointers as seen from the calling rank).  In the one-GPU
+// emulation (`emulate_ranks` = world) the tables hold world x world entries, rank-major.
+LLB_EXPORT int llb_tp_reduce_norm(const void** partial, void** sums, void** ready, void** rowflag, void** residual,
+                                  void** out, const void* norm_w, void** epoch, void** arrive, int* status, int rank,
+                                  int world, int emulate_ranks, int T, int H, float eps, float w_offset, int one_shot,
+                                  int do_norm, int ctas, cudaStream_t st) {
+  if (T <= 0) return LLB_OK;
+  CommParams p;
+  memset(&p, 0, sizeof(p));
+  p.world = world;
+  p.T = T;
+  p.H = H;
+  p.eps = eps;
+  p.w_offset = w_offset;
+  p.one_shot = one_shot;
+  p.do_norm = do_norm;
+  const int nr = emulate_ranks > 1 ? emulate_ranks : 1;
+  for (int r = 0; r < nr; ++r) {
+    RankView& v = p.v[r];
+    for (int q = 0; q < world; ++q) {
+      v.partial[q] = (const bf16*)partial[r * world + q];
+      v.sums[q] = (bf16*)sums[r * world + q];
+      v.ready[q] = (uint32_t*)ready[r * world + q];
+      v.rowflag[q] = (uint32_t*)rowflag[r * world + q];
+    }
+    v.residual = (bf16*)residual[r];
+    v.out = (bf16*)out[r];
+    v.norm_w = (const bf16*)norm_w;
+    v.epoch = (uint32_t*)epoch[r];
+    v.arrive = (uint32_t*)arrive[r];
+    v.status = status;
+    v.rank = emulate_ranks > 1 ? r : rank;
+  }
+  return launch(p, nr, ctas, st);
+}

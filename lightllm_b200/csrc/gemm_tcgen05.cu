@@ -30,6 +30,7 @@ constexpr int BK = 64;  // 64 bf16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int GEMM_THREADS = 192;
 constexpr int SMEM_BUDGET = 200 * 1024;
+constexpr int64_t kPanelBytes = 24ll << 20;  // A panel kept hot in L2 while W streams past it
 
 enum Epi { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_GATED_SILU = 2, EPI_F32 = 3, EPI_GATED_GELU = 4 };
 
@@ -45,6 +46,9 @@ struct GemmParams {
   int stream_k;        // 1: every CTA gets an equal share of (tile, k-block) units; split tiles are fixed up
   float* sk_partials;  // [grid][2][BM * BN] fp32 partial tiles of split tiles (stream_k only)
   int* sk_counters;    // [tiles] arrived k-blocks per tile, self-resetting (stream_k only)
+  // grouped (MoE) mode: A is the expert-sorted activation, W stacks the experts along its rows
+  // ([E * N, K]); M-block i multiplies with expert mblock_expert[i] (-1: padding block, skipped)
+  const int* mblock_expert;
 };
 
 template <int BN>
@@ -110,6 +114,110 @@ __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int 
   nb = in / gsz;
 }
 
+// Drains one accumulator tile (this thread's row, BN columns starting at TMEM address t_row) through the
+// epilogue functor EPI into C.  `add_partials(regs, col)` adds other CTAs' partial sums (stream-K) when
+// `has_add` is set.
+template <int BN, int EPI, typename AddFn>
+__device__ __forceinline__ void epilogue_store(const GemmParams& p, uint32_t t_row, int row, bool row_ok, int col_tile0,
+                                               bool has_add, AddFn add_partials) {
+  if (EPI == EPI_GATED_SILU || EPI == EPI_GATED_GELU) {
+    // columns come as [32 gate | 32 up] pairs; output has N/2 columns
+    bf16* crow = (bf16*)p.C + (int64_t)row * p.ldc;
+#pragma unroll 1
+    for (int c = 0; c < BN; c += 64) {
+      uint32_t gr[32], ur[32];
+      tmem_ld_32x32(t_row + c, gr);
+      tmem_ld_32x32(t_row + c + 32, ur);
+      tmem_wait_ld();
+      if (has_add) {
+        add_partials(gr, c);
+        add_partials(ur, c + 32);
+      }
+      const int ocol = (col_tile0 + c) / 2;
+      if (row_ok && col_tile0 + c < p.N) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+          float o[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            float gv = __uint_as_float(gr[j + e]);
+            float uv = __uint_as_float(ur[j + e]);
+            o[e] = (EPI == EPI_GATED_SILU ? silu_f(gv) : gelu_tanh_f(gv)) * uv;
+          }
+          *reinterpret_cast<bf16x8*>(crow + ocol + j) = pack8(o);
+        }
+      }
+    }
+  } else {
+#pragma unroll 1
+    for (int c = 0; c < BN; c += 32) {
+      uint32_t r[32];
+      tmem_ld_32x32(t_row + c, r);
+      tmem_wait_ld();
+      if (has_add) add_partials(r, c);
+      const int col0 = col_tile0 + c;
+      if (row_ok && col0 < p.N) {
+        const int ncols = min(32, p.N - col0);
+        if (EPI == EPI_F32) {
+          float* crow = (float*)p.C + (int64_t)row * p.ldc + col0;
+          if (ncols == 32) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
+                                     __uint_as_float(r[j + 3]));
+              if (p.bias) {
+                v.x += __bfloat162float(p.bias[col0 + j]);
+                v.y += __bfloat162float(p.bias[col0 + j + 1]);
+                v.z += __bfloat162float(p.bias[col0 + j + 2]);
+                v.w += __bfloat162float(p.bias[col0 + j + 3]);
+              }
+              *reinterpret_cast<float4*>(crow + j) = v;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (j < ncols) crow[j] = __uint_as_float(r[j]) + (p.bias ? __bfloat162float(p.bias[col0 + j]) : 0.f);
+          }
+        } else {
+          bf16* crow = (bf16*)p.C + (int64_t)row * p.ldc + col0;
+          const bf16* rrow = EPI == EPI_RESIDUAL ? p.residual + (int64_t)row * p.ldc + col0 : nullptr;
+          if (ncols == 32) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              float o[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) o[e] = __uint_as_float(r[j + e]);
+              if (p.bias) {
+                float bv[8];
+                unpack8(*reinterpret_cast<const bf16x8*>(p.bias + col0 + j), bv);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) o[e] += bv[e];
+              }
+              if (EPI == EPI_RESIDUAL) {
+                float rv[8];
+                unpack8(*reinterpret_cast<const bf16x8*>(rrow + j), rv);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) o[e] += rv[e];
+              }
+              *reinterpret_cast<bf16x8*>(crow + j) = pack8(o);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (j < ncols) {
+                float v = __uint_as_float(r[j]);
+                if (p.bias) v += __bfloat162float(p.bias[col0 + j]);
+                if (EPI == EPI_RESIDUAL) v += __bfloat162float(rrow[j]);
+                crow[j] = __float2bfloat16(v);
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+}
+
 template <int BN, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -167,12 +275,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       while (segs.next(tile, k0, k1)) {
         int mb, nb;
         tile_coords(tile, p.num_m_blocks, p.num_n_blocks, p.group_m, mb, nb);
+        int w_row0 = nb * BN;
+        if (p.mblock_expert != nullptr) {
+          const int e = p.mblock_expert[mb];
+          if (e < 0) continue;
+          w_row0 += e * p.N;
+        }
         for (int kb = k0; kb < k1; ++kb) {
           mbar_wait(empty_bar(stage), phase ^ 1, &abort_flag, p.status, 1);
           const uint32_t sa = smem_base + stage * STAGE_BYTES;
           mbar_expect_tx(full_bar(stage), STAGE_BYTES);
           tma_load_2d(sa, &tmA, full_bar(stage), kb * BK, mb * BM);
-          tma_load_2d(sa + A_BYTES, &tmB, full_bar(stage), kb * BK, nb * BN);
+          tma_load_2d(sa + A_BYTES, &tmB, full_bar(stage), kb * BK, w_row0);
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1;
@@ -188,9 +302,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int it = 0;
       SegIter segs(p.stream_k != 0, blockIdx.x, gridDim.x, num_tiles, k_blocks);
       int tile, k0, k1;
-      for (; segs.next(tile, k0, k1); ++it) {
+      while (segs.next(tile, k0, k1)) {
+        if (p.mblock_expert != nullptr) {
+          int mb, nb;
+          tile_coords(tile, p.num_m_blocks, p.num_n_blocks, p.group_m, mb, nb);
+          if (p.mblock_expert[mb] < 0) continue;
+        }
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
+        ++it;
         mbar_wait(tempty_bar(acc), acc_phase ^ 1, &abort_flag, p.status, 2);
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
@@ -223,11 +343,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     int it = 0;
     SegIter segs(p.stream_k != 0, blockIdx.x, gridDim.x, num_tiles, k_blocks);
     int tile, k0, k1;
-    for (; segs.next(tile, k0, k1); ++it) {
+    while (segs.next(tile, k0, k1)) {
       int mb, nb;
       tile_coords(tile, p.num_m_blocks, p.num_n_blocks, p.group_m, mb, nb);
+      if (p.mblock_expert != nullptr && p.mblock_expert[mb] < 0) continue;
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
+      ++it;
       mbar_wait(tfull_bar(acc), acc_phase, &abort_flag, p.status, 4);
       tc_fence_after();
       const int row = mb * BM + erow;
@@ -291,104 +413,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
       };
 
-      if (!do_epilogue) {
-        // partial handed over; nothing else to do for this segment
-      } else if (EPI == EPI_GATED_SILU || EPI == EPI_GATED_GELU) {
-        // columns come as [32 gate | 32 up] pairs; output has N/2 columns
-        bf16* crow = (bf16*)p.C + (int64_t)row * p.ldc;
-#pragma unroll 1
-        for (int c = 0; c < BN; c += 64) {
-          uint32_t gr[32], ur[32];
-          tmem_ld_32x32(t_row + c, gr);
-          tmem_ld_32x32(t_row + c + 32, ur);
-          tmem_wait_ld();
-          if (n_other) {
-            add_partials(gr, c);
-            add_partials(ur, c + 32);
-          }
-          const int ocol = (nb * BN + c) / 2;
-          if (row_ok && nb * BN + c < p.N) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              float o[8];
-#pragma unroll
-              for (int e = 0; e < 8; ++e) {
-                float gv = __uint_as_float(gr[j + e]);
-                float uv = __uint_as_float(ur[j + e]);
-                o[e] = (EPI == EPI_GATED_SILU ? silu_f(gv) : gelu_tanh_f(gv)) * uv;
-              }
-              *reinterpret_cast<bf16x8*>(crow + ocol + j) = pack8(o);
-            }
-          }
-        }
-      } else {
-#pragma unroll 1
-        for (int c = 0; c < BN; c += 32) {
-          uint32_t r[32];
-          tmem_ld_32x32(t_row + c, r);
-          tmem_wait_ld();
-          if (n_other) add_partials(r, c);
-          const int col0 = nb * BN + c;
-          if (row_ok && col0 < p.N) {
-            const int ncols = min(32, p.N - col0);
-            if (EPI == EPI_F32) {
-              float* crow = (float*)p.C + (int64_t)row * p.ldc + col0;
-              if (ncols == 32) {
-#pragma unroll
-                for (int j = 0; j < 32; j += 4) {
-                  float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
-                                         __uint_as_float(r[j + 3]));
-                  if (p.bias) {
-                    v.x += __bfloat162float(p.bias[col0 + j]);
-                    v.y += __bfloat162float(p.bias[col0 + j + 1]);
-                    v.z += __bfloat162float(p.bias[col0 + j + 2]);
-                    v.w += __bfloat162float(p.bias[col0 + j + 3]);
-                  }
-                  *reinterpret_cast<float4*>(crow + j) = v;
-                }
-              } else {
-#pragma unroll
-                for (int j = 0; j < 32; ++j)
-                  if (j < ncols) crow[j] = __uint_as_float(r[j]) + (p.bias ? __bfloat162float(p.bias[col0 + j]) : 0.f);
-              }
-            } else {
-              bf16* crow = (bf16*)p.C + (int64_t)row * p.ldc + col0;
-              const bf16* rrow = EPI == EPI_RESIDUAL ? p.residual + (int64_t)row * p.ldc + col0 : nullptr;
-              if (ncols == 32) {
-#pragma unroll
-                for (int j = 0; j < 32; j += 8) {
-                  float o[8];
-#pragma unroll
-                  for (int e = 0; e < 8; ++e) o[e] = __uint_as_float(r[j + e]);
-                  if (p.bias) {
-                    float bv[8];
-                    unpack8(*reinterpret_cast<const bf16x8*>(p.bias + col0 + j), bv);
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) o[e] += bv[e];
-                  }
-                  if (EPI == EPI_RESIDUAL) {
-                    float rv[8];
-                    unpack8(*reinterpret_cast<const bf16x8*>(rrow + j), rv);
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) o[e] += rv[e];
-                  }
-                  *reinterpret_cast<bf16x8*>(crow + j) = pack8(o);
-                }
-              } else {
-#pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                  if (j < ncols) {
-                    float v = __uint_as_float(r[j]);
-                    if (p.bias) v += __bfloat162float(p.bias[col0 + j]);
-                    if (EPI == EPI_RESIDUAL) v += __bfloat162float(rrow[j]);
-                    crow[j] = __float2bfloat16(v);
-                  }
-                }
-              }
-            }
-          }
-        }
-      }
+      if (do_epilogue) epilogue_store<BN, EPI>(p, t_row, row, row_ok, nb * BN, n_other != 0, add_partials);
       // accumulator drained: hand it back to the MMA warp
       tc_fence_before();
       __syncwarp();
@@ -441,8 +466,6 @@ int cached_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols
   return LLB_OK;
 }
 
-constexpr int64_t kPanelBytes = 24ll << 20;  // A panel kept hot in L2 while W streams past it
-
 template <int BN, int EPI>
 int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, cudaStream_t st) {
   static bool configured = false;
@@ -485,6 +508,202 @@ int dispatch_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tb, GemmPara
   return LLB_ERR_UNSUPPORTED;
 }
 
+// ---------------------------------------------------------------------------------------
+// CTA-pair variant (cta_group::2) for large M: the two CTAs of a cluster compute one 256 x 256 tile.
+// Each CTA loads its own 128 rows of A and 128 of the 256 W rows per stage (32 KB instead of 48 KB for
+// the same 128 x 256 x 64 of math per CTA, which is what the SM's L2 port can feed at full tensor
+// rate); the leader CTA's MMA thread issues tcgen05.mma.cta_group::2 (M = 256), the accumulator rows
+// 0-127 land in the leader's TMEM and 128-255 in the peer's.  All loads are plain per-CTA TMA loads.
+//   full[s]      (leader)    TMA bytes of stage s of BOTH CTAs landed (the peer's loads name the leader's
+//                            barrier through its cluster address)
+//   empty[s]     (each CTA)  leader's tcgen05.commit, issued once per CTA (local + mapped address)
+//   tfull[a]     (each CTA)  accumulator a complete (same two commits)
+//   tempty[a]    (leader)    8 arrivals: the 4 epilogue warps of both CTAs
+// ---------------------------------------------------------------------------------------
+constexpr int PAIR_BN = 256;       // tile width (W rows per pair tile)
+constexpr int PAIR_HALF = 128;     // W rows loaded by each CTA
+constexpr int PAIR_STAGE_BYTES = BM * BK * 2 + PAIR_HALF * BK * 2;  // 32 KB
+constexpr int PAIR_STAGES = 6;
+constexpr int pair_smem_bytes() { return PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 512; }
+
+template <int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                      const GemmParams p) {
+  constexpr int STAGES = PAIR_STAGES;
+  constexpr int A_BYTES = BM * BK * 2;
+  constexpr int STAGE_BYTES = PAIR_STAGE_BYTES;
+  constexpr uint32_t TMEM_COLS = 512;
+  constexpr uint32_t IDESC = umma_idesc(256, PAIR_BN, 1);
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
+  auto full_bar = [&](int s) { return bar_base + 8 * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8 * (STAGES + s); };
+  auto pfull_bar = [&](int s) { return bar_base + 8 * (2 * STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8 * (3 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8 * (3 * STAGES + 2 + a); };
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t cta = cluster_ctarank();  // 0 = leader
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  const int num_m = (p.M + 255) / 256, num_n = (p.N + PAIR_BN - 1) / PAIR_BN;
+  const int num_tiles = num_m * num_n;
+  const int k_blocks = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+      mbar_init(pfull_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull_bar(a), 1);
+      mbar_init(tempty_bar(a), 8);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 0) {
+    tmem_alloc_pair(smem_u32(&tmem_base_slot), TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers exist before anyone signals across the pair
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  if (warp == 0) {
+    // ---- TMA producer (both CTAs) ----
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int tile = pair; tile < num_tiles; tile += num_pairs) {
+        int mb, nb;
+        tile_coords(tile, num_m, num_n, p.group_m, mb, nb);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          mbar_wait(empty_bar(stage), phase ^ 1, &abort_flag, p.status, 11);
+          const uint32_t sa = smem_base + stage * STAGE_BYTES;
+          // both CTAs' bytes are counted on the leader's barrier (the only one the MMA thread waits on)
+          const uint32_t lead_full = map_to_cta(full_bar(stage), 0);
+          if (cta == 0) mbar_expect_tx(full_bar(stage), 2 * STAGE_BYTES);
+          tma_load_2d_pair(sa, &tmA, lead_full, kb * BK, mb * 256 + (int)cta * BM);
+          tma_load_2d_pair(sa + A_BYTES, &tmB, lead_full, kb * BK, nb * PAIR_BN + (int)cta * PAIR_HALF);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      if (cta == 0) {
+        // ---- leader: MMA issuer for the pair ----
+        int it = 0;
+        for (int tile = pair; tile < num_tiles; tile += num_pairs, ++it) {
+          const int acc = it & 1;
+          const uint32_t acc_phase = (it >> 1) & 1;
+          mbar_wait(tempty_bar(acc), acc_phase ^ 1, &abort_flag, p.status, 13);
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + acc * PAIR_BN;
+          for (int kb = 0; kb < k_blocks; ++kb) {
+            mbar_wait(full_bar(stage), phase, &abort_flag, p.status, 14);
+            tc_fence_after();
+            const uint32_t sa = smem_base + stage * STAGE_BYTES;
+            const uint64_t da = umma_smem_desc_sw128(sa);
+            const uint64_t db = umma_smem_desc_sw128(sa + A_BYTES);
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k) umma_bf16_pair(d_tmem, da + 2 * k, db + 2 * k, IDESC, (kb | k) != 0);
+            umma_commit_pair(empty_bar(stage));                 // my stage is free ...
+            umma_commit_pair(map_to_cta(empty_bar(stage), 1));  // ... and the peer's
+            if (++stage == STAGES) {
+              stage = 0;
+              phase ^= 1;
+            }
+          }
+          umma_commit_pair(tfull_bar(acc));
+          umma_commit_pair(map_to_cta(tfull_bar(acc), 1));
+        }
+      }
+    }
+  } else {
+    // ---- epilogue (both CTAs): this CTA's 128 rows of the pair tile ----
+    const int lane_grp = warp & 3;
+    const int erow = lane_grp * 32 + lane;
+    const uint32_t tempty_leader = map_to_cta(tempty_bar(0), 0);
+    int it = 0;
+    for (int tile = pair; tile < num_tiles; tile += num_pairs, ++it) {
+      int mb, nb;
+      tile_coords(tile, num_m, num_n, p.group_m, mb, nb);
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      mbar_wait(tfull_bar(acc), acc_phase, &abort_flag, p.status, 16);
+      tc_fence_after();
+      const int row = mb * 256 + (int)cta * BM + erow;
+      const uint32_t t_row = tmem_base + ((uint32_t)(lane_grp * 32) << 16) + acc * PAIR_BN;
+      epilogue_store<PAIR_BN, EPI>(p, t_row, row, row < p.M, nb * PAIR_BN, false, [](uint32_t*, int) {});
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(tempty_leader + 8 * acc);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // nobody leaves while the peer may still signal into this CTA
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int EPI>
+int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, cudaStream_t st) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_pair_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         pair_smem_bytes());
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  const int num_m = cdiv(p.M, 256), num_n = cdiv(p.N, PAIR_BN);
+  p.num_m_blocks = num_m;
+  p.num_n_blocks = num_n;
+  int64_t panel_rows = kPanelBytes / ((int64_t)256 * p.K * 2);
+  p.group_m = (int)(panel_rows < 2 ? 2 : (panel_rows > 32 ? 32 : panel_rows));
+  int pairs = num_m * num_n;
+  int max_pairs = sm_count() / 2;
+  if (pairs > max_pairs) pairs = max_pairs;
+  gemm_bf16_pair_kernel<EPI><<<pairs * 2, GEMM_THREADS, pair_smem_bytes(), st>>>(ta, tb, p);
+  LLB_LAUNCH_CHECK();
+  return LLB_OK;
+}
+
+int dispatch_pair(int epi, const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, cudaStream_t st) {
+  switch (epi) {
+    case EPI_STORE:
+      return launch_pair<EPI_STORE>(ta, tb, p, st);
+    case EPI_RESIDUAL:
+      return launch_pair<EPI_RESIDUAL>(ta, tb, p, st);
+    case EPI_GATED_SILU:
+      return launch_pair<EPI_GATED_SILU>(ta, tb, p, st);
+    case EPI_F32:
+      return launch_pair<EPI_F32>(ta, tb, p, st);
+    case EPI_GATED_GELU:
+      return launch_pair<EPI_GATED_GELU>(ta, tb, p, st);
+  }
+  return LLB_ERR_UNSUPPORTED;
+}
+
 // Tile width for the data-parallel schedule: modelled time = waves x measured per-k-block cost of a
 // full wave of that tile width (L2-bound figures from B200 runs: 0.27 / 0.34 / 0.56 us).
 int pick_bn(int M, int N) {
@@ -507,13 +726,17 @@ int pick_bn(int M, int N) {
   return best;
 }
 
+bool g_pair_auto = true;  // measured faster than one-CTA tiles for M >= 1024, K <= 8192 on B200
+
 }  // namespace
+
+LLB_EXPORT void llb_gemm_set_pair_auto(int on) { g_pair_auto = on != 0; }
 
 // C[M,N] (ldc) = A[M,K] (lda) . W[N,K]^T (ldw)  with epilogue `epi`:
 //   0 store bf16 (+bias)          1 store bf16 of acc (+bias) + residual[M,N] (same ldc)
 //   2 SiLU-gated: W rows interleaved as [32 gate | 32 up] blocks; C is [M, N/2]
 //   3 store fp32 (+bias)          4 GELU(tanh)-gated, layout as 2
-// bn: 0 = choose, else 64/128/256.  status: optional device int receiving a wait-timeout code.
+// bn: 0 = choose, else 64/128/256, or 512 = the CTA-pair (cta_group::2) kernel with 256x256 tiles.  status: optional device int receiving a wait-timeout code.
 // stream_k: 0 = whole tiles per CTA, 1 = equal (tile, k-block) shares with fix-up of split tiles,
 // -1 = choose (stream-K when the tiles would fill fewer than three waves).  Stream-K needs
 // sk_partials (>= SMs * 2 * 128 * bn floats) and sk_counters (>= tiles ints, zero before first use;
@@ -543,7 +766,12 @@ LLB_EXPORT int llb_gemm_bf16(const void* A, int64_t lda, const void* W, int64_t 
       stream_k = 0;
     }
   }
-  if (bn == 0) bn = pick_bn(M, N);
+  // CTA-pair kernel: explicit (bn == 512) or chosen for big problems (at least two waves of pair tiles)
+  bool use_pair = bn == 512;
+  if (bn == 0 && stream_k == 0 && g_pair_auto && M >= 1024 && N >= 512 && K <= 8192 &&
+      (int64_t)cdiv(M, 256) * cdiv(N, 256) >= 2ll * (sm_count() / 2))
+    use_pair = true;
+  if (bn == 0 || bn == 512) bn = use_pair ? PAIR_HALF : pick_bn(M, N);
   CUtensorMap ta, tb;
   int rc = cached_tmap(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM);
   if (rc) return rc;
@@ -561,6 +789,53 @@ LLB_EXPORT int llb_gemm_bf16(const void* A, int64_t lda, const void* W, int64_t 
   p.stream_k = stream_k;
   p.sk_partials = sk_partials;
   p.sk_counters = sk_counters;
+  p.mblock_expert = nullptr;
+  if (use_pair) {
+    p.stream_k = 0;
+    return dispatch_pair(epi, ta, tb, p, st);
+  }
+  switch (bn) {
+    case 256:
+      return dispatch_epi<256>(epi, ta, tb, p, st);
+    case 128:
+      return dispatch_epi<128>(epi, ta, tb, p, st);
+    case 64:
+      return dispatch_epi<64>(epi, ta, tb, p, st);
+  }
+  return LLB_ERR_UNSUPPORTED;
+}
+
+// Grouped GEMM for MoE experts.  A [M_pad, K] holds the routed tokens sorted by expert, every expert's
+// rows padded to a multiple of 128; W [E * N, K] stacks the expert weights; mblock_expert[M_pad / 128]
+// (device) names the expert of each 128-row block, -1 for blocks beyond the routed rows (skipped).
+// C [M_pad, N] (or [M_pad, N/2] for the gated epilogues).  N must be a multiple of the tile width.
+LLB_EXPORT int llb_gemm_bf16_grouped(const void* A, int64_t lda, const void* W, int64_t ldw, void* C, int64_t ldc,
+                                     const int* mblock_expert, int M_pad, int N, int K, int E, int epi, int bn,
+                                     int* status, cudaStream_t st) {
+  if (M_pad <= 0 || N <= 0 || E <= 0) return LLB_OK;
+  if (K <= 0 || (K % 8) != 0 || (M_pad % BM) != 0) return LLB_ERR_UNSUPPORTED;
+  if (epi == EPI_RESIDUAL) return LLB_ERR_UNSUPPORTED;
+  if (bn == 0) bn = (N % 256 == 0) ? 256 : ((N % 128 == 0) ? 128 : 64);
+  if (N % bn != 0) return LLB_ERR_UNSUPPORTED;
+  if (((uintptr_t)C & 15) || (ldc % 8)) return LLB_ERR_BAD_ARG;
+  CUtensorMap ta, tb;
+  int rc = cached_tmap(&ta, A, (uint64_t)M_pad, (uint64_t)K, (uint64_t)lda, BM);
+  if (rc) return rc;
+  rc = cached_tmap(&tb, W, (uint64_t)E * (uint64_t)N, (uint64_t)K, (uint64_t)ldw, (uint32_t)bn);
+  if (rc) return rc;
+  GemmParams p;
+  p.C = C;
+  p.residual = nullptr;
+  p.bias = nullptr;
+  p.status = status;
+  p.M = M_pad;
+  p.N = N;
+  p.K = K;
+  p.ldc = ldc;
+  p.stream_k = 0;
+  p.sk_partials = nullptr;
+  p.sk_counters = nullptr;
+  p.mblock_expert = mblock_expert;
   switch (bn) {
     case 256:
       return dispatch_epi<256>(epi, ta, tb, p, st);

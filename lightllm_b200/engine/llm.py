@@ -40,7 +40,14 @@ class LLM:
         if not eos_ids:
             e = config.get("eos_token_id")
             eos_ids = tuple(e) if isinstance(e, (list, tuple)) else ((e,) if e is not None else ())
-        self.model = get_model(config, model_dir=model_dir, pstate=self.ps, data_type=data_type,
+        tp_fused = model_kw.pop("tp_fused", None)
+        if tp_fused is None and self.ps.tp_size > 1 and self.ps.device.type == "cuda" \
+                and not model_kw.pop("disable_fused_tp", False):
+            from ..parallel.fused import FusedTP
+
+            hidden = config.get("hidden_size") or config.get("text_config", {}).get("hidden_size")
+            tp_fused = FusedTP(self.ps, max_tokens=batch_max_tokens, hidden=hidden)
+        self.model = get_model(config, model_dir=model_dir, pstate=self.ps, data_type=data_type, tp_fused=tp_fused,
                                max_total_token_num=max_total_token_num, mem_fraction=mem_fraction,
                                max_req_num=running_max_req_size, max_seq_length=max_req_total_len + 8,
                                batch_max_tokens=batch_max_tokens, disable_cudagraph=disable_cudagraph,

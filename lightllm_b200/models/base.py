@@ -437,18 +437,34 @@ class TransformerLM:
         for i, lw in enumerate(self.layers):
             a = self._attention_block(i, lw, h, st)                      # [T, hq*D] (pre o_proj)
             h = self._row_parallel(a, lw.o_w, lw.o_b, residual, lw.post_norm)
-            f = self._ffn_block(i, lw, h, st)                            # FFN output handler below
-            if isinstance(f, tuple):  # (activation, down weight): dense row-parallel tail
-                act, down_w = f
-                nxt = self.layers[i + 1].in_norm if i + 1 < n else None
-                h = self._row_parallel(act, down_w, None, residual, nxt)
-            else:  # an already complete (reduced) FFN output, e.g. expert-parallel MoE
-                nxt = self.layers[i + 1].in_norm if i + 1 < n else None
-                if nxt is not None:
-                    h = ops.add_rmsnorm_(residual, f, nxt, self.eps, self.norm_w_offset)
-                else:
-                    residual.add_(f)
+            nxt = self.layers[i + 1].in_norm if i + 1 < n else None
+            f = self._ffn_block(i, lw, h, st)
+            if f[0] == "rowpar":    # (activation, down weight): dense row-parallel tail
+                h = self._row_parallel(f[1], f[2], None, residual, nxt)
+            else:                   # ("partial", tensor): per-rank partial sum of the FFN output (MoE)
+                h = self._reduce_partial(f[1], residual, nxt)
         return residual
+
+    def _partial_out(self, T: int):
+        """Buffer a layer should write a to-be-reduced [T, hidden] partial sum into (the symmetric
+        buffer of the fused reduction when it is active, else a fresh tensor)."""
+        fused = self.tp.fused
+        if fused is not None and self.tp.size > 1 and T <= fused.max_tokens and self.hidden == fused.hidden:
+            return fused.partial_out(T, self.hidden)
+        return torch.empty((T, self.hidden), dtype=self.dtype, device=self.device)
+
+    def _reduce_partial(self, partial, residual, next_norm_w):
+        """residual += sum over TP ranks of `partial`; returns rmsnorm(residual) * next_norm_w (or None)."""
+        if self.tp.size == 1:
+            if next_norm_w is None:
+                residual.add_(partial)
+                return None
+            return ops.add_rmsnorm_(residual, partial, next_norm_w, self.eps, self.norm_w_offset)
+        if next_norm_w is None:
+            self.tp.all_reduce_(partial)
+            residual.add_(partial)
+            return None
+        return self.tp.reduce_residual_norm(partial, residual, next_norm_w, self.eps, self.norm_w_offset)
 
     def _row_parallel(self, a, w, bias, residual, next_norm_w):
         """residual += a . w^T (summed over TP ranks); returns rmsnorm(residual) * next_norm_w (or None)."""
@@ -457,7 +473,11 @@ class TransformerLM:
             if next_norm_w is None:
                 return None
             return ops.rmsnorm(residual, next_norm_w, self.eps, self.norm_w_offset)
-        partial = ops.gemm(a, w, epi="store", bias=bias)
+        fused = self.tp.fused
+        use_fused = (fused is not None and next_norm_w is not None and a.is_cuda
+                     and a.shape[0] <= fused.max_tokens and w.shape[0] == fused.hidden)
+        partial = ops.gemm(a, w, epi="store", bias=bias,
+                           out=fused.partial_out(a.shape[0], w.shape[0]) if use_fused else None)
         if next_norm_w is None:
             self.tp.all_reduce_(partial)
             residual.add_(partial)
@@ -485,7 +505,7 @@ class TransformerLM:
             act = ops.gemm(h, lw.gate_up_w, epi="gated_" + self.act)
         else:
             act = ops.gated_act(ops.gemm(h, lw.gate_up_w), self.act)
-        return act, lw.down_w
+        return "rowpar", act, lw.down_w
 
     def _ffn_block(self, i, lw, h, st):
         return self._dense_ffn(lw, h)

@@ -1,0 +1,108 @@
+"""Mixture-of-experts FFN shared by the MoE model families.
+
+Expert weights of a layer are two stacked tensors: `w13 [E_local, 2*I_local, H]` (gate and up rows
+interleaved in 32-row blocks, so the grouped GEMM's epilogue applies the gated activation) and
+`w2 [E_local, H, I_local]`.  Two sharding modes:
+
+  * tensor parallel (default): every rank holds all experts, each sliced along the intermediate
+    dimension (I_local = I / tp)
+  * expert parallel (`enable_ep_moe`): every rank holds E / tp whole experts.  With tensor-parallel
+    attention the hidden states are replicated, so a rank simply evaluates its own experts for all
+    tokens (pairs routed elsewhere are dropped by the alignment kernel) -- no all-to-all needed.
+
+Either way the layer produces a per-rank partial sum that goes through the same fused
+reduce + residual + RMSNorm as a dense row-parallel GEMM.  With data-parallel attention (`dp == tp`)
+tokens differ per rank and `parallel.ep` moves them (dispatch / combine).
+
+Reference: lightllm/common/basemodel/layer_weights/meta_weights/fused_moe/fused_moe_weight.py,
+lightllm/common/basemodel/triton_kernel/fused_moe/*, models/qwen3_moe, models/deepseek2 (_moe_ffn*).
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..ops import moe as moe_ops
+from ..ops import reference as ref
+from .weights import tp_range
+
+
+class MoEConfig:
+    def __init__(self, num_experts, top_k, inter, renorm=True, scoring="softmax", n_group=1, topk_group=1,
+                 routed_scale=1.0, has_bias=False, n_shared=0, shared_inter=0, act="silu"):
+        self.num_experts, self.top_k, self.inter = num_experts, top_k, inter
+        self.renorm, self.scoring = renorm, scoring
+        self.n_group, self.topk_group = n_group, topk_group
+        self.routed_scale, self.has_bias = routed_scale, has_bias
+        self.n_shared, self.shared_inter = n_shared, shared_inter
+        self.act = act
+
+
+def expert_weight_shapes(prefix: str, mc: MoEConfig, hidden: int, gate_name="gate", experts_name="experts"):
+    s = {prefix + f"{gate_name}.weight": (mc.num_experts, hidden)}
+    if mc.has_bias:
+        s[prefix + f"{gate_name}.e_score_correction_bias"] = (mc.num_experts,)
+    for e in range(mc.num_experts):
+        q = prefix + f"{experts_name}.{e}."
+        s[q + "gate_proj.weight"] = (mc.inter, hidden)
+        s[q + "up_proj.weight"] = (mc.inter, hidden)
+        s[q + "down_proj.weight"] = (hidden, mc.inter)
+    if mc.n_shared:
+        q = prefix + "shared_experts."
+        s[q + "gate_proj.weight"] = (mc.shared_inter, hidden)
+        s[q + "up_proj.weight"] = (mc.shared_inter, hidden)
+        s[q + "down_proj.weight"] = (hidden, mc.shared_inter)
+    return s
+
+
+def load_experts(model, lw, src, prefix: str, mc: MoEConfig, ep: bool, gate_name="gate", experts_name="experts"):
+    """Fills lw.router_w (fp32 logits GEMM runs in bf16 weights), lw.w13, lw.w2, lw.e0, lw.e_local (+ shared expert)."""
+    tp, r = model.tp.size, model.tp.rank
+    dev = model._dev
+    lw.router_w = dev(src.get(prefix + f"{gate_name}.weight"))
+    if mc.has_bias and src.has(prefix + f"{gate_name}.e_score_correction_bias"):
+        lw.router_bias = src.get(prefix + f"{gate_name}.e_score_correction_bias").to(model.device, torch.float32)
+    if ep and tp > 1:
+        e0, e1 = tp_range(mc.num_experts, r, tp)
+        i0, i1 = 0, mc.inter
+    else:
+        e0, e1 = 0, mc.num_experts
+        i0, i1 = tp_range(mc.inter, r, tp)
+    w13, w2 = [], []
+    for e in range(e0, e1):
+        q = prefix + f"{experts_name}.{e}."
+        g = src.get(q + "gate_proj.weight", 0, i0, i1)
+        u = src.get(q + "up_proj.weight", 0, i0, i1)
+        w13.append(ref.interleave_gate_up(g, u))
+        w2.append(src.get(q + "down_proj.weight", 1, i0, i1))
+    lw.w13 = dev(torch.stack(w13))
+    lw.w2 = dev(torch.stack(w2))
+    lw.e0 = e0 if (ep and tp > 1) else 0
+    lw.is_moe = True
+    if mc.n_shared:
+        model._load_dense_ffn(lw, src, prefix + "shared_experts.", mc.shared_inter)
+        lw.shared_gate_up_w, lw.shared_down_w, lw.shared_fused = lw.gate_up_w, lw.down_w, lw.gate_up_fused
+        lw.gate_up_w = lw.down_w = None
+
+
+def moe_ffn(model, lw, h, mc: MoEConfig):
+    """Returns the per-rank partial sum [T, H] of routed (+ shared) experts, written where the TP reduction
+    wants it."""
+    T = h.shape[0]
+    logits = ops.gemm(h, lw.router_w, epi="f32")
+    if mc.scoring == "softmax" and mc.n_group <= 1:
+        ids, w = moe_ops.topk_softmax(logits, mc.top_k, mc.renorm, mc.routed_scale)
+    else:
+        ids, w = moe_ops.grouped_topk(logits, lw.router_bias, mc.top_k, mc.n_group, mc.topk_group,
+                                      mc.scoring == "sigmoid", mc.renorm, mc.routed_scale)
+    out = model._partial_out(T)
+    accumulate = False
+    if mc.n_shared:
+        if lw.shared_fused:
+            act = ops.gemm(h, lw.shared_gate_up_w, epi="gated_" + mc.act)
+        else:
+            act = ops.gated_act(ops.gemm(h, lw.shared_gate_up_w), mc.act)
+        ops.gemm(act, lw.shared_down_w, out=out)
+        accumulate = True
+    moe_ops.fused_experts(h, lw.w13, lw.w2, ids, w, mc.act, lw.e0, out=out, accumulate=accumulate)
+    return out

@@ -151,11 +151,12 @@ def _stream_k_scratch(device):
     return cur
 
 
-def gemm(a, w, epi: str = "store", residual=None, bias=None, out=None, bn: int = 0, stream_k: int = -1):
+def gemm(a, w, epi: str = "store", residual=None, bias=None, out=None, bn: int = 0, stream_k: int = 0):
     """C = A . W^T on the tcgen05 tensor cores.  a [M, K], w [N, K] (checkpoint layout).
 
     epi: "store" | "residual" (C += residual) | "gated_silu"/"gated_gelu" (w rows interleaved with
     `reference.interleave_gate_up`, C is [M, N/2]) | "f32" (fp32 output, e.g. logits).
+    stream_k: 0 whole tiles per CTA (default: fastest on every measured shape), 1 stream-K, -1 heuristic.
     """
     if not _is_cuda(a):
         res = ref.gemm(a, w, epi, residual, bias)

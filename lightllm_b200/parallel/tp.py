@@ -61,7 +61,7 @@ class TPContext:
     def reduce_residual_norm(self, partial, residual, norm_w, eps, w_offset=0.0):
         """residual += sum_over_ranks(partial); returns rmsnorm(residual) * norm_w."""
         if self.size > 1:
-            if self.fused is not None and self.fused.can_reduce_residual_norm(partial):
+            if self.fused is not None and self.fused.owns(partial):
                 return self.fused.reduce_residual_norm(partial, residual, norm_w, eps, w_offset)
             self.all_reduce_(partial)
         return ops.add_rmsnorm_(residual, partial, norm_w, eps, w_offset)

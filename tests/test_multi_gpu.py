@@ -1,0 +1,67 @@
+"""Tensor parallelism on real GPUs (needs >= 2): the fused NVLink all-reduce + residual + RMSNorm path
+must agree with the NCCL baseline path and with a single GPU."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+CFG = dict(model_type="llama", hidden_size=1024, num_hidden_layers=4, num_attention_heads=8, num_key_value_heads=2,
+           head_dim=128, intermediate_size=2816, vocab_size=32000, rms_norm_eps=1e-5, rope_theta=5e5, eos_token_id=2)
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, out_dir, fused):
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    from lightllm_b200.common.infer_state import ModelInput
+    from lightllm_b200.engine.llm import LLM
+    from lightllm_b200.parallel import dist as pdist
+
+    pdist.init_distributed(world, rank, host="127.0.0.1", port=port, device=torch.device("cuda", rank))
+    llm = LLM(config=CFG, max_total_token_num=8192, running_max_req_size=8, max_req_total_len=512,
+              batch_max_tokens=2048, disable_fused_tp=not fused)
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(3, 32000, (700,), generator=g)
+    m = llm.model
+    req = m.req_manager.alloc()
+    slots = m.mem_manager.alloc(len(ids))
+    mi = ModelInput(batch_size=1, total_token_num=len(ids), max_kv_len=len(ids), is_prefill=True,
+                    b_req_idx=torch.tensor([req], dtype=torch.int32),
+                    b_seq_len=torch.tensor([len(ids)], dtype=torch.int32), mem_indexes=slots.clone(), input_ids=ids,
+                    b_ready_cache_len=torch.zeros(1, dtype=torch.int32), max_q_len=len(ids), return_all_logits=True)
+    logits = m.forward(mi).logits.float().cpu()
+    m.mem_manager.free(slots)
+    m.req_manager.free(req)
+    prompts = [torch.randint(3, 32000, (n,), generator=g).tolist() for n in (17, 64, 129, 300)]
+    outs = llm.generate(prompts, {"max_new_tokens": 24, "ignore_eos": True})
+    status = m.tp.fused.status() if (fused and m.tp.fused is not None) else 0
+    if rank == 0:
+        torch.save({"logits": logits, "tokens": [o["token_ids"] for o in outs], "status": status},
+                   os.path.join(out_dir, f"tp{world}_f{int(fused)}.pt"))
+    pdist.destroy()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.timeout(900)
+def test_tp2_fused_matches_nccl_and_tp1(tmp_path):
+    for world, fused in ((1, False), (2, False), (2, True)):
+        mp.spawn(_worker, args=(world, _free_port(), str(tmp_path), fused), nprocs=world, join=True)
+    one = torch.load(tmp_path / "tp1_f0.pt")
+    nccl = torch.load(tmp_path / "tp2_f0.pt")
+    fus = torch.load(tmp_path / "tp2_f1.pt")
+    assert fus["status"] == 0, "a bounded wait in the fused all-reduce ran out"
+    scale = one["logits"].abs().max().item()
+    assert (nccl["logits"] - one["logits"]).abs().max().item() < 0.05 * scale + 0.05
+    assert (fus["logits"] - one["logits"]).abs().max().item() < 0.05 * scale + 0.05
+    assert (fus["logits"] - nccl["logits"]).abs().max().item() < 0.05 * scale + 0.05
+    assert all(len(t) == 24 for t in fus["tokens"])

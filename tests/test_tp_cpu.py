@@ -65,3 +65,31 @@ def test_tp2_matches_tp1(tmp_path):
     assert torch.allclose(a["logits"], b["logits"], atol=2e-4, rtol=1e-4), (a["logits"] - b["logits"]).abs().max()
     assert all(len(t) == 32 for t in b["tokens"])
     assert a["tokens"] == b["tokens"]
+
+
+MOE = dict(model_type="qwen3_moe", hidden_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+           head_dim=64, intermediate_size=688, moe_intermediate_size=128, num_experts=8, num_experts_per_tok=2,
+           norm_topk_prob=True, vocab_size=1024, rms_norm_eps=1e-6, rope_theta=1e4, eos_token_id=2)
+
+
+def _moe_worker(rank, world, port, out_dir, ep):
+    from lightllm_b200.engine.llm import LLM
+    from lightllm_b200.parallel import dist as pdist
+
+    torch.set_num_threads(2)
+    pdist.init_distributed(world, rank, host="127.0.0.1", port=port, backend="gloo", device=torch.device("cpu"))
+    llm = LLM(config=MOE, data_type="float32", max_total_token_num=2048, running_max_req_size=4,
+              max_req_total_len=128, batch_max_tokens=128, enable_ep_moe=ep)
+    outs = llm.generate(_prompts()[:4], {"max_new_tokens": 12, "ignore_eos": True})
+    if rank == 0:
+        torch.save([o["token_ids"] for o in outs], os.path.join(out_dir, f"moe_tp{world}_ep{int(ep)}.pt"))
+    pdist.destroy()
+
+
+@pytest.mark.timeout(600)
+def test_moe_tp2_and_ep2_match_tp1(tmp_path):
+    for world, ep in ((1, False), (2, False), (2, True)):
+        mp.spawn(_moe_worker, args=(world, _free_port(), str(tmp_path), ep), nprocs=world, join=True)
+    base = torch.load(tmp_path / "moe_tp1_ep0.pt")
+    assert torch.load(tmp_path / "moe_tp2_ep0.pt") == base   # experts sliced along the intermediate dim
+    assert torch.load(tmp_path / "moe_tp2_ep1.pt") == base   # whole experts per rank
