@@ -49,6 +49,9 @@ struct GemmParams {
   // grouped (MoE) mode: A is the expert-sorted activation, W stacks the experts along its rows
   // ([E * N, K]); M-block i multiplies with expert mblock_expert[i] (-1: padding block, skipped)
   const int* mblock_expert;
+  // batched mode (per-head GEMMs of MLA): rank-3 tensor maps, tile -> (batch, m, n); C += batch * c_batch_stride
+  int batch_count;
+  int64_t c_batch_stride;
 };
 
 template <int BN>
@@ -239,7 +242,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   __shared__ int abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int num_tiles = p.num_m_blocks * p.num_n_blocks;
+  const int num_tiles = p.num_m_blocks * p.num_n_blocks * (p.batch_count > 1 ? p.batch_count : 1);
   const int k_blocks = (p.K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -274,7 +277,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int tile, k0, k1;
       while (segs.next(tile, k0, k1)) {
         int mb, nb;
-        tile_coords(tile, p.num_m_blocks, p.num_n_blocks, p.group_m, mb, nb);
+        const int tpb = p.num_m_blocks * p.num_n_blocks;
+        const int batch = p.batch_count > 1 ? tile / tpb : 0;
+        tile_coords(p.batch_count > 1 ? tile - batch * tpb : tile, p.num_m_blocks, p.num_n_blocks, p.group_m, mb, nb);
         int w_row0 = nb * BN;
         if (p.mblock_expert != nullptr) {
           const int e = p.mblock_expert[mb];
@@ -285,8 +290,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           mbar_wait(empty_bar(stage), phase ^ 1, &abort_flag, p.status, 1);
           const uint32_t sa = smem_base + stage * STAGE_BYTES;
           mbar_expect_tx(full_bar(stage), STAGE_BYTES);
-          tma_load_2d(sa, &tmA, full_bar(stage), kb * BK, mb * BM);
-          tma_load_2d(sa + A_BYTES, &tmB, full_bar(stage), kb * BK, w_row0);
+          if (p.batch_count > 1) {
+            tma_load_3d(sa, &tmA, full_bar(stage), kb * BK, mb * BM, batch);
+            tma_load_3d(sa + A_BYTES, &tmB, full_bar(stage), kb * BK, w_row0, batch);
+          } else {
+            tma_load_2d(sa, &tmA, full_bar(stage), kb * BK, mb * BM);
+            tma_load_2d(sa + A_BYTES, &tmB, full_bar(stage), kb * BK, w_row0);
+          }
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1;
@@ -345,7 +355,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     int tile, k0, k1;
     while (segs.next(tile, k0, k1)) {
       int mb, nb;
-      tile_coords(tile, p.num_m_blocks, p.num_n_blocks, p.group_m, mb, nb);
+      const int tpb = p.num_m_blocks * p.num_n_blocks;
+      const int batch = p.batch_count > 1 ? tile / tpb : 0;
+      tile_coords(p.batch_count > 1 ? tile - batch * tpb : tile, p.num_m_blocks, p.num_n_blocks, p.group_m, mb, nb);
       if (p.mblock_expert != nullptr && p.mblock_expert[mb] < 0) continue;
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
@@ -413,7 +425,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
       };
 
-      if (do_epilogue) epilogue_store<BN, EPI>(p, t_row, row, row_ok, nb * BN, n_other != 0, add_partials);
+      if (do_epilogue) {
+        if (p.batch_count > 1) {
+          GemmParams pb = p;
+          pb.C = (bf16*)p.C + (int64_t)batch * p.c_batch_stride;
+          epilogue_store<BN, EPI>(pb, t_row, row, row_ok, nb * BN, false, add_partials);
+        } else {
+          epilogue_store<BN, EPI>(p, t_row, row, row_ok, nb * BN, n_other != 0, add_partials);
+        }
+      }
       // accumulator drained: hand it back to the MMA warp
       tc_fence_before();
       __syncwarp();
@@ -477,7 +497,7 @@ int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, cud
   }
   p.num_m_blocks = cdiv(p.M, BM);
   p.num_n_blocks = cdiv(p.N, BN);
-  int tiles = p.num_m_blocks * p.num_n_blocks;
+  int tiles = p.num_m_blocks * p.num_n_blocks * (p.batch_count > 1 ? p.batch_count : 1);
   int64_t panel_rows = kPanelBytes / ((int64_t)BM * p.K * 2);
   p.group_m = (int)(panel_rows < 4 ? 4 : (panel_rows > 64 ? 64 : panel_rows));
   int grid = tiles < sm_count() ? tiles : sm_count();
@@ -790,6 +810,8 @@ LLB_EXPORT int llb_gemm_bf16(const void* A, int64_t lda, const void* W, int64_t 
   p.sk_partials = sk_partials;
   p.sk_counters = sk_counters;
   p.mblock_expert = nullptr;
+  p.batch_count = 1;
+  p.c_batch_stride = 0;
   if (use_pair) {
     p.stream_k = 0;
     return dispatch_pair(epi, ta, tb, p, st);
@@ -836,6 +858,8 @@ LLB_EXPORT int llb_gemm_bf16_grouped(const void* A, int64_t lda, const void* W, 
   p.sk_partials = nullptr;
   p.sk_counters = nullptr;
   p.mblock_expert = mblock_expert;
+  p.batch_count = 1;
+  p.c_batch_stride = 0;
   switch (bn) {
     case 256:
       return dispatch_epi<256>(epi, ta, tb, p, st);
@@ -843,6 +867,50 @@ LLB_EXPORT int llb_gemm_bf16_grouped(const void* A, int64_t lda, const void* W, 
       return dispatch_epi<128>(epi, ta, tb, p, st);
     case 64:
       return dispatch_epi<64>(epi, ta, tb, p, st);
+  }
+  return LLB_ERR_UNSUPPORTED;
+}
+
+// Batched GEMM: for every batch index h:  C[:, h, :] = A[:, h, :] . W[h]^T
+//   A [M, batch, K] with element strides (a_row_stride, a_batch_stride), inner stride 1
+//   W [batch, N, K] contiguous;  C [M, batch, N] with element strides (c_row_stride, c_batch_stride)
+// Strides in bytes must be multiples of 16 (TMA).  Used for the W_UK / W_UV absorption steps of MLA.
+LLB_EXPORT int llb_gemm_bf16_batched(const void* A, int64_t a_row_stride, int64_t a_batch_stride, const void* W,
+                                     void* C, int64_t c_row_stride, int64_t c_batch_stride, int M, int N, int K,
+                                     int batch, int* status, cudaStream_t st) {
+  if (M <= 0 || N <= 0 || batch <= 0) return LLB_OK;
+  if (K % 8 != 0 || N % 8 != 0) return LLB_ERR_UNSUPPORTED;
+  if ((a_row_stride % 8) || (a_batch_stride % 8) || (c_row_stride % 8) || (c_batch_stride % 8)) return LLB_ERR_BAD_ARG;
+  int bn = N >= 256 && N % 256 == 0 ? 256 : (N % 128 == 0 ? 128 : 64);
+  if ((int64_t)cdiv(M, BM) * cdiv(N, bn) * batch < sm_count() && bn > 64) bn = bn / 2;
+  CUtensorMap ta, tb;
+  int rc = make_tmap_3d(&ta, A, 2, (uint64_t)batch, (uint64_t)M, (uint64_t)K, (uint64_t)a_row_stride,
+                        (uint64_t)a_batch_stride, BM, BK);
+  if (rc) return rc;
+  rc = make_tmap_3d(&tb, W, 2, (uint64_t)batch, (uint64_t)N, (uint64_t)K, (uint64_t)K, (uint64_t)N * K, (uint32_t)bn, BK);
+  if (rc) return rc;
+  GemmParams p;
+  p.C = C;
+  p.residual = nullptr;
+  p.bias = nullptr;
+  p.status = status;
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.ldc = c_row_stride;
+  p.stream_k = 0;
+  p.sk_partials = nullptr;
+  p.sk_counters = nullptr;
+  p.mblock_expert = nullptr;
+  p.batch_count = batch;
+  p.c_batch_stride = c_batch_stride;
+  switch (bn) {
+    case 256:
+      return launch_gemm<256, EPI_STORE>(ta, tb, p, st);
+    case 128:
+      return launch_gemm<128, EPI_STORE>(ta, tb, p, st);
+    case 64:
+      return launch_gemm<64, EPI_STORE>(ta, tb, p, st);
   }
   return LLB_ERR_UNSUPPORTED;
 }

@@ -203,7 +203,85 @@ class DiverseBackend(ModelBackend):
         return res
 
 
+class PDPrefillBackend(ModelBackend):
+    """Prefill node of a disaggregated deployment: when a request's first token is sampled, its prompt KV is
+    streamed to the paired decode rank (same tp rank) before the request is retired.
+    Reference: mode_backend/pd/prefill_node_impl/prefill_impl.py:50-92."""
+
+    def __init__(self, *a, tp_rank: int = 0, page_tokens: int = 1024, **kw):
+        super().__init__(*a, **kw)
+        from .pd import KVSender
+
+        self.tp_rank = tp_rank
+        self.sender = KVSender(self.model.mem_manager, page_tokens)
+        self.extra_post_req_handle_func = self._ship
+
+    def _ship(self, r: InferReq, tok: int, lp: float):
+        params = r.shm_req.sample_params.pd_kv_trans_params.to_dict()
+        if not params or r.cur_output_len != 1:
+            return
+        n = r.cur_kv_len
+        try:
+            ids = r.shm_req.shm_prompt_ids.arr[:n].tolist()
+            self.sender.send_request((params["peer_ip"], params["peer_port"] + self.tp_rank), params["master_req_id"],
+                                     ids, torch.from_numpy(np.ascontiguousarray(r.slots[:n])), (tok, lp))
+        except Exception:
+            import traceback
+
+            traceback.print_exc()
+            from ..server.core.objs.req import FinishStatus
+
+            r.finish_status.set_status(FinishStatus.FINISHED_ERROR)
+
+
+class PDDecodeBackend(ModelBackend):
+    """Decode node: lands KV pages from prefill ranks between steps and publishes complete prompts to the
+    prefix cache, so that the follow-up request (prompt + first token) starts decoding at once.
+    `on_kv_done(group_req_id, ok)` is called on the master rank for each completed transfer.
+    Reference: mode_backend/pd/decode_node_impl/decode_impl.py, up_status.py."""
+
+    def __init__(self, *a, tp_rank: int = 0, host: str = "0.0.0.0", kv_port: int = 0, page_tokens: int = 1024,
+                 page_num: int = 16, cpu_group=None, tp_size: int = 1, on_kv_done=None, **kw):
+        super().__init__(*a, **kw)
+        from .pd import KVReceiver
+
+        assert self.radix_cache is not None, "a decode node needs the prefix cache (it is how transferred KV is found)"
+        self.receiver = KVReceiver(self.model.mem_manager, host, kv_port + tp_rank if kv_port else 0, page_tokens, page_num)
+        self.cpu_group, self.tp_size, self.on_kv_done = cpu_group, tp_size, on_kv_done
+
+    MAX_KEYS = 64
+
+    def _agree(self, keys):
+        """Keys landed on every tp rank: one fixed-size all-gather on the host group."""
+        import torch.distributed as dist
+
+        mine = torch.full((self.MAX_KEYS,), -1, dtype=torch.int64)
+        k = keys[: self.MAX_KEYS]
+        mine[: len(k)] = torch.tensor(k, dtype=torch.int64)
+        allk = torch.empty((self.tp_size, self.MAX_KEYS), dtype=torch.int64)
+        dist.all_gather_into_tensor(allk, mine, group=self.cpu_group)
+        common = set(allk[0].tolist())
+        for i in range(1, self.tp_size):
+            common &= set(allk[i].tolist())
+        common.discard(-1)
+        return sorted(common)
+
+    def has_work(self) -> bool:
+        # with tp > 1 every rank must enter step() together: the agreement is a collective
+        return super().has_work() or (self.tp_size == 1 and self.receiver.has_landed())
+
+    def poll_kv(self):
+        agree = self._agree if (self.tp_size > 1 and self.cpu_group is not None) else None
+        for gid, ok, _first in self.receiver.drain(self.radix_cache, agree):
+            if self.on_kv_done is not None and self.is_master_in_dp:
+                self.on_kv_done(gid, ok)
+
+
 def select_backend_class(args):
+    if getattr(args, "run_mode", "normal") == "prefill":
+        return PDPrefillBackend
+    if getattr(args, "run_mode", "normal") == "decode":
+        return PDDecodeBackend
     if getattr(args, "use_reward_model", False):
         return RewardModelBackend
     if getattr(args, "token_healing_mode", False):

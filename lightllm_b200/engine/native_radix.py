@@ -126,6 +126,16 @@ class NativeRadixCache:
         if need_token_num > free:
             self.evict(need_token_num - free, lambda v: self.mem_manager.free(v))
 
+    def publish(self, key, slots) -> int:
+        """Hand externally filled slots (KV that arrived from another node or cache tier) to the tree under
+        `key`; copies of positions the tree already had are returned to the pool.  Returns that count."""
+        v = np.asarray(slots.cpu() if hasattr(slots, "cpu") else slots, dtype=np.int32)
+        k = np.asarray(key.cpu() if hasattr(key, "cpu") else key, dtype=np.int64)
+        present = self.insert(k, v)
+        if present and self.mem_manager is not None:
+            self.mem_manager.free(v[:present])
+        return present
+
     def clear_tree_nodes(self):
         self.evict(self.get_tree_total_tokens_num(), lambda v: self.mem_manager.free(v) if self.mem_manager else None)
 

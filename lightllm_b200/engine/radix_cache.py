@@ -206,6 +206,15 @@ class RadixCache:
             if chunks:
                 self.mem_manager.free(np.concatenate(chunks))
 
+    def publish(self, key, slots) -> int:
+        """Insert externally filled slots; spare copies of already present positions go back to the pool."""
+        v = np.asarray(slots.cpu() if hasattr(slots, "cpu") else slots, dtype=np.int32)
+        k = np.asarray(key.cpu() if hasattr(key, "cpu") else key, dtype=np.int64)
+        present = self.insert(k, v)
+        if present and self.mem_manager is not None:
+            self.mem_manager.free(v[:present])
+        return present
+
     def clear_tree_nodes(self):
         """Drop every unreferenced path (flush_cache)."""
         chunks = []

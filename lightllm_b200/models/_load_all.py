@@ -1,3 +1,4 @@
 """Imports every model module so their @register_model decorators run."""
 from . import llama  # noqa: F401
 from . import qwen3_moe  # noqa: F401
+from . import deepseek2  # noqa: F401

@@ -1,0 +1,85 @@
+"""Weight quantisation formats of checkpoints.
+
+fp8 block format (DeepSeek-V3 style): `X.weight` is float8_e4m3fn [out, in] and `X.weight_scale_inv` is
+fp32 [ceil(out/128), ceil(in/128)]; the real weight is weight * scale_inv broadcast over 128x128 blocks.
+TP slicing applies the same row/column rule to the scale tensor at 1/128 granularity, so sharded
+dimensions must be multiples of 128 (reference: mm_slicer.py Quantized*SliceMixin, deepgemm.py:46-56).
+
+`load_dequant` returns the bf16 weight of a slice (the block-dequantising load path);
+`load_fp8` returns (e4m3 payload, scales) for the block-scaled fp8 GEMM.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+BLOCK = 128
+
+
+def is_fp8_block_config(cfg: dict) -> bool:
+    q = cfg.get("quantization_config") or {}
+    return q.get("quant_method") == "fp8" and list(q.get("weight_block_size") or []) == [BLOCK, BLOCK]
+
+
+def _scale_slice(src, name, dim, start, end):
+    sname = name + "_scale_inv"
+    if dim is None:
+        return src.get(sname)
+    assert start % BLOCK == 0, f"fp8 block-quantised {name}: slice start {start} is not a multiple of {BLOCK}"
+    s0 = start // BLOCK
+    s1 = None if end is None else (end + BLOCK - 1) // BLOCK
+    return src.get(sname, dim, s0, s1)
+
+
+def dequant_block(w: torch.Tensor, scale_inv: torch.Tensor, dtype=torch.bfloat16) -> torch.Tensor:
+    out_f, in_f = w.shape
+    s = scale_inv.float().repeat_interleave(BLOCK, 0)[:out_f].repeat_interleave(BLOCK, 1)[:, :in_f]
+    return (w.float() * s).to(dtype)
+
+
+def quant_block(w: torch.Tensor):
+    """bf16/fp32 [out, in] -> (e4m3 payload, scale_inv) with one scale per 128x128 block (online quantisation)."""
+    out_f, in_f = w.shape
+    po, pi = (out_f + BLOCK - 1) // BLOCK, (in_f + BLOCK - 1) // BLOCK
+    wp = torch.zeros(po * BLOCK, pi * BLOCK, dtype=torch.float32, device=w.device)
+    wp[:out_f, :in_f] = w.float()
+    blocks = wp.view(po, BLOCK, pi, BLOCK)
+    amax = blocks.abs().amax(dim=(1, 3)).clamp_min(1e-12)
+    scale = amax / 448.0
+    q = (blocks / scale[:, None, :, None]).clamp(-448, 448).view(po * BLOCK, pi * BLOCK)[:out_f, :in_f]
+    return q.to(torch.float8_e4m3fn), scale
+
+
+def load_dequant(src, name: str, dim: Optional[int] = None, start: int = 0, end: Optional[int] = None,
+                 dtype=torch.bfloat16) -> torch.Tensor:
+    w = src.get(name, dim, start, end) if dim is not None else src.get(name)
+    if w.dtype == torch.float8_e4m3fn and src.has(name + "_scale_inv"):
+        return dequant_block(w, _scale_slice(src, name, dim, start, end), dtype)
+    return w
+
+
+def load_fp8(src, name: str, dim: Optional[int] = None, start: int = 0, end: Optional[int] = None):
+    w = src.get(name, dim, start, end) if dim is not None else src.get(name)
+    if w.dtype == torch.float8_e4m3fn:
+        return w, _scale_slice(src, name, dim, start, end).float()
+    return quant_block(w)
+
+
+class DequantSource:
+    """WeightSource view that hands out bf16 tensors for fp8 block-quantised entries."""
+
+    def __init__(self, base, dtype=torch.bfloat16):
+        self.base, self.dtype = base, dtype
+
+    def has(self, n):
+        return self.base.has(n)
+
+    def shape(self, n):
+        return self.base.shape(n)
+
+    def names(self):
+        return self.base.names()
+
+    def get(self, n, dim=None, start=0, end=None):
+        return load_dequant(self.base, n, dim, start, end, self.dtype)

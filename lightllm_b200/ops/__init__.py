@@ -109,6 +109,22 @@ def rope_kv_scatter_(qkv, kv_layer, cos, sin, pos, slot, Hq, Hkv, D, rot_dim=Non
     return qkv
 
 
+def mla_rope_kv_scatter_(q3, kv_a, kv_layer, kv_norm_w, cos, sin, pos, slot, nope, rope, kv_lora, eps):
+    """RoPE on the rope part of q (in place), RMSNorm of the kv latent, RoPE of k_pe, scatter of
+    [c_kv | k_pe] into the latent pool -- one launch."""
+    if not _is_cuda(q3):
+        return ref.mla_rope_kv_scatter_(q3, kv_a, kv_layer, kv_norm_w, cos, sin, pos, slot, nope, rope, kv_lora, eps)
+    _req_bf16(q3, kv_a, kv_layer, kv_norm_w)
+    T, hq, qd = q3.shape
+    assert q3.stride(2) == 1 and kv_a.stride(1) == 1 and kv_layer.is_contiguous()
+    check(kernels().llb_mla_rope_kv_scatter(ptr(q3), i64(q3.stride(0)), i64(q3.stride(1)), ptr(kv_a),
+                                            i64(kv_a.stride(0)), ptr(kv_layer), ptr(kv_norm_w), ptr(cos), ptr(sin),
+                                            ptr(pos), ptr(slot), c_int(T), c_int(hq), c_int(nope), c_int(rope),
+                                            c_int(kv_lora), f32(eps), stream()), "mla_rope_kv_scatter")
+    _count()
+    return q3
+
+
 def embedding(ids, table, vocab_start: int = 0, vocab_end: Optional[int] = None):
     vocab_end = vocab_start + table.shape[0] if vocab_end is None else vocab_end
     if not _is_cuda(table):

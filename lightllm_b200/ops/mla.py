@@ -48,7 +48,7 @@ def ref_mla_attention(q_lat, q_pe, kv_layer, req_to_token, b_req_idx, b_seq_len,
 
 
 def mla_attention(q_lat, q_pe, kv_layer, req_to_token, b_req_idx, b_seq_len, cu_q, b_ready_len, kv_lora, scale,
-                  is_prefill: bool, max_q_len: int = 1, max_kv_len: int = 0):
+                  is_prefill: bool, max_q_len: int = 1, max_kv_len: int = 0, batch_of=None):
     if not q_lat.is_cuda:
         return ref_mla_attention(q_lat, q_pe, kv_layer, req_to_token, b_req_idx, b_seq_len, cu_q, b_ready_len, kv_lora,
                                  scale)
@@ -60,7 +60,8 @@ def mla_attention(q_lat, q_pe, kv_layer, req_to_token, b_req_idx, b_seq_len, cu_
     B = b_req_idx.shape[0]
     check(kernels().llb_mla_attention(ptr(q_lat), ptr(q_pe), i64(q_pe.stride(0)), i64(q_pe.stride(1)), ptr(kv_layer),
                                       ptr(req_to_token), i64(req_to_token.stride(0)), ptr(b_req_idx), ptr(cu_q),
-                                      ptr(b_ready_len), ptr(out), c_int(B), c_int(T), c_int(h), c_int(max_q_len),
+                                      ptr(b_ready_len), ptr(batch_of), ptr(out), c_int(B), c_int(T), c_int(h),
+                                      c_int(max_q_len),
                                       f32(scale), stream()), "mla_attention")
     _count()
     return out

@@ -272,3 +272,22 @@ def filtered_support(x, top_p, top_k):
 
 def token_logprob(logits, ids):
     return torch.log_softmax(logits.float(), dim=-1).gather(1, ids.view(-1, 1).long()).squeeze(1)
+
+
+def mla_rope_kv_scatter_(q3, kv_a, kv_layer, kv_norm_w, cos, sin, pos, slot, nope, rope, kv_lora, eps):
+    """MLA counterpart of rope_kv_scatter_: rotates q3[:, :, nope:] in place (half-split layout), normalises
+    the latent kv_a[:, :kv_lora], rotates k_pe = kv_a[:, kv_lora:], and writes [c_kv | k_pe] to kv_layer[slot, 0]."""
+    half = rope // 2
+    c = cos[pos.long()].unsqueeze(1)
+    s = sin[pos.long()].unsqueeze(1)
+
+    def rot(x):
+        x1, x2 = x[..., :half], x[..., half:]
+        return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s], dim=-1)
+
+    q3[:, :, nope:] = rot(q3[:, :, nope:].float()).to(q3.dtype)
+    ckv = rmsnorm(kv_a[:, :kv_lora], kv_norm_w, eps)
+    kpe = rot(kv_a[:, kv_lora:].float().unsqueeze(1)).squeeze(1).to(kv_a.dtype)
+    kv_layer[slot.long(), 0, :kv_lora] = ckv.to(kv_layer.dtype)
+    kv_layer[slot.long(), 0, kv_lora:] = kpe.to(kv_layer.dtype)
+    return q3

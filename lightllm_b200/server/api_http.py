@@ -265,3 +265,7 @@ async def startup_event():
         add_pd_routes(app, g_objs)
     loop = asyncio.get_event_loop()
     loop.create_task(g_objs.httpserver_manager.handle_loop())
+    if args.run_mode in ("prefill", "decode"):
+        from .httpserver.pd_loop import start_pd_loops
+
+        g_objs.pd_tasks = start_pd_loops(g_objs)

@@ -87,6 +87,13 @@ def normalize_args(args: StartArgs, config_override: dict = None) -> StartArgs:
         setattr(a, n, p)
     if a.nccl_port is None:
         a.nccl_port = ports[-1]
+    if a.run_mode == "decode":
+        from ..utils.net_utils import alloc_consecutive_ports
+
+        if a.pd_kv_port is None:  # rank r of this node receives KV pages on pd_kv_port + r
+            a.pd_kv_port = alloc_consecutive_ports(a.tp, start=30000 + (os.getpid() % 2000) * 10, used_ports=ports)
+        if a.pd_kv_status_port is None:
+            a.pd_kv_status_port = alloc_can_use_network_port(1, used_ports=ports + [a.port], start=a.pd_kv_port + a.tp)[0]
     if a.disable_vision is None:
         a.disable_vision = True if cfg is not None else not config_utils.is_multimodal(a.model_dir)
     if a.disable_audio is None:

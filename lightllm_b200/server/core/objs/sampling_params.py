@@ -161,7 +161,8 @@ class PDKVTransParams(ctypes.Structure):
 
     _pack_ = 4
     _fields_ = [("prefill_node_id", NodeUUId), ("decode_node_id", NodeUUId), ("peer_ip", ctypes.c_ubyte * 64),
-                ("peer_ip_len", ctypes.c_int), ("peer_port", ctypes.c_int), ("valid", ctypes.c_bool)]
+                ("peer_ip_len", ctypes.c_int), ("peer_port", ctypes.c_int), ("master_req_id", ctypes.c_int64),
+                ("valid", ctypes.c_bool)]
 
     def set(self, d: Optional[dict]):
         self.valid = bool(d)
@@ -173,12 +174,14 @@ class PDKVTransParams(ctypes.Structure):
         ctypes.memmove(self.peer_ip, ip, len(ip))
         self.peer_ip_len = len(ip)
         self.peer_port = int(d.get("peer_port", 0))
+        self.master_req_id = int(d.get("master_req_id", 0))
 
     def to_dict(self):
         if not self.valid:
             return None
         return {"prefill_node_id": self.prefill_node_id.get(), "decode_node_id": self.decode_node_id.get(),
-                "peer_ip": bytes(self.peer_ip[: self.peer_ip_len]).decode(), "peer_port": self.peer_port}
+                "peer_ip": bytes(self.peer_ip[: self.peer_ip_len]).decode(), "peer_port": self.peer_port,
+                "master_req_id": self.master_req_id}
 
 
 class SamplingParams(ctypes.Structure):

@@ -19,7 +19,7 @@ ENV_KEY = "LIGHTLLM_START_ARGS"
 DERIVED_DEFAULTS: Dict[str, Any] = {
     "router_port": None, "detokenization_port": None, "http_server_port": None, "visual_port": None,
     "audio_port": None, "cache_port": None, "metric_port": None, "multi_level_kv_cache_port": None,
-    "pd_node_id": -1, "pd_p_allowed_port_min": 20000, "pd_p_allowed_port_max": 30000,
+    "pd_node_id": -1, "pd_kv_port": None, "pd_kv_status_port": None, "pd_p_allowed_port_min": 20000, "pd_p_allowed_port_max": 30000,
     "pd_decode_rpyc_port": None, "child_ips": None, "enable_multimodal": False, "enable_multimodal_audio": False,
     "unique_server_name": None, "cpu_kv_cache_shm_id": None, "weight_version": "default",
     "model_rpc_ports": None, "vocab_size": None, "eos_ids": None,

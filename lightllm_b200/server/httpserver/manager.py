@@ -68,6 +68,7 @@ class HttpServerManager:
         self.run_reqs_count_mark = SharedInt(f"{self.name}_run_reqs_count_mark")
         self.metric_client = metric_client
         self.paused = False  # RL: admission gate
+        self.master_id_to_local: Dict[int, int] = {}  # PD nodes: pd_master request id -> local group id
         self.eos_ids = set(args.eos_ids or [])
         self.all_special_ids = set(getattr(self.tokenizer, "all_special_ids", []) or [])
         self._recycle_event = asyncio.Event()
@@ -103,7 +104,8 @@ class HttpServerManager:
 
     # ------------------------------------------------------------------ generate
     async def generate(self, prompt: Union[str, List[int]], sampling_params: SamplingParams, multimodal_params=None,
-                       request=None, is_health_req: bool = False):
+                       request=None, is_health_req: bool = False, pd_info: Optional[dict] = None):
+        """`pd_info` (P/D nodes only) = {"group_req_id": the pd_master's id, "peer": the paired node}."""
         if self.paused and not is_health_req:
             raise ServerBusyError("generation is paused")
         start_time = time.time()
@@ -111,6 +113,13 @@ class HttpServerManager:
         sampling_params.group_request_id = group_req_id
         prompt_ids = await self._encode(prompt, sampling_params)
         prompt_ids = self._check_and_repair_length(prompt_ids, sampling_params)
+        if pd_info is not None:
+            self.master_id_to_local[pd_info["group_req_id"]] = group_req_id
+            if self.args.run_mode == "prefill" and pd_info.get("peer"):
+                ip, port = pd_info["peer"]["kv_endpoint"]
+                sampling_params.pd_kv_trans_params.set({"peer_ip": ip, "peer_port": port,
+                                                        "master_req_id": pd_info["group_req_id"],
+                                                        "decode_node_id": pd_info["peer"]["node_id"]})
         if self.metric_client is not None:
             self.metric_client.counter_inc("lightllm_request_count")
             self.metric_client.histogram_observe("lightllm_request_input_length", len(prompt_ids))
@@ -150,11 +159,17 @@ class HttpServerManager:
         await self.send_to_router.send_pyobj(GroupReqIndexes(group_req_id, multimodal_params, indexes, start_time),
                                              protocol=pickle.HIGHEST_PROTOCOL)
         try:
+            first = True
             async for item in self._wait_to_token_package(start_time, len(prompt_ids), group_req_id, sampling_params,
                                                           status, request):
+                if first and pd_info is not None and self.args.run_mode == "prefill":
+                    item[2]["prompt_ids"] = prompt_ids  # the pd_master hands them to the decode node
+                first = False
                 yield item
         finally:
             self.run_reqs_count_mark.add(-1)
+            if pd_info is not None:
+                self.master_id_to_local.pop(pd_info["group_req_id"], None)
 
     async def _wait_to_token_package(self, start_time, prompt_tokens, group_req_id, sampling_params, status: ReqStatus,
                                      request):
@@ -207,6 +222,10 @@ class HttpServerManager:
         for r in st.req_objs:
             r.is_aborted = True
         return True
+
+    async def abort_by_master_id(self, master_req_id: int) -> bool:
+        gid = self.master_id_to_local.get(master_req_id)
+        return False if gid is None else await self.abort(gid)
 
     async def abort_all(self):
         for gid in list(self.req_id_to_out_inf):

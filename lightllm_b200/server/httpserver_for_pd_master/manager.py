@@ -1,0 +1,220 @@
+"""pd_master front-end: keeps the registry of prefill (P) and decode (D) nodes, picks a pair per request,
+drives the request through the pair and relays the token stream to the client.  No GPU in this process.
+
+Per request:  master --PDRequest(peer=D)--> P;  P prefills, pushes the KV pages to D and uploads the tokenised
+prompt and the first token;  D reports on /kv_move_status when all pages arrived;  master then sends
+PDRequest(prompt ids + first token) to D, which decodes the rest and uploads tokens;  master yields them with the
+same `(sub_req_id, text, metadata, FinishStatus)` contract as the single-node manager.
+
+Topology (--pd_master_mode): `elastic` serves as soon as one P and one D are registered and nodes may come and
+go; `<x>p<y>d` refuses requests until exactly that many of each have registered.
+Reference: lightllm/server/httpserver_for_pd_master/manager.py, register_loop.py.
+"""
+from __future__ import annotations
+
+import asyncio
+import pickle
+import re
+import time
+from typing import Dict, List, Optional
+
+from ...utils.errors import ServerBusyError
+from ..core.objs.req import FinishStatus
+from ..core.objs.sampling_params import SamplingParams
+from ..pd_io_struct import PDClient, PDHeartbeat, PDPromptIds, PDRegister, PDRequest, PDToken, UpKVStatus
+from ..req_id_generator import MAX_BEST_OF
+from .selector import create_selector
+
+HEARTBEAT_TIMEOUT_S = 90.0
+FIRST_TOKEN_TIMEOUT_S = 600.0
+KV_MOVE_TIMEOUT_S = 182.0
+
+
+class _ReqState:
+    def __init__(self, group_req_id, p: PDClient, d: PDClient, prompt_chars: int):
+        self.group_req_id, self.p, self.d, self.prompt_chars = group_req_id, p, d, prompt_chars
+        self.tokens: asyncio.Queue = asyncio.Queue()
+        self.prompt_ids: Optional[List[int]] = None
+        self.kv_done = asyncio.Event()
+        self.kv_ok = False
+
+
+class HttpServerManagerForPDMaster:
+    def __init__(self, args, metric_client=None):
+        self.args = args
+        self.metric_client = metric_client
+        self.nodes: Dict[int, PDClient] = {}
+        self.selector = create_selector(args.select_p_d_node_strategy)
+        self.reqs: Dict[int, _ReqState] = {}
+        self._next_id = MAX_BEST_OF
+        self.paused = False
+        self.tokenizer = None
+        m = re.fullmatch(r"(\d+)p(\d+)d", args.pd_master_mode or "elastic")
+        self.fixed_topology = (int(m.group(1)), int(m.group(2))) if m else None
+        if not m and (args.pd_master_mode or "elastic") != "elastic":
+            raise ValueError("--pd_master_mode is 'elastic' or '<P>p<D>d'")
+
+    # ---------------------------------------------------------------- registry
+    def _refresh(self):
+        ps = [n for n in self.nodes.values() if n.mode == "prefill"]
+        ds = [n for n in self.nodes.values() if n.mode == "decode"]
+        self.selector.update_nodes(ps, ds)
+        return ps, ds
+
+    async def register_pd(self, reg: PDRegister, websocket) -> PDClient:
+        node = PDClient(reg.node_id, reg.client_ip_port, reg.mode, reg.start_args, websocket)
+        self.nodes[reg.node_id] = node
+        self._refresh()
+        return node
+
+    async def remove_pd(self, node_id: int):
+        node = self.nodes.pop(node_id, None)
+        if node is None:
+            return
+        self.selector.forget_node(node)
+        self._refresh()
+        for st in list(self.reqs.values()):  # requests on the lost node end with an error
+            if st.p is node or st.d is node:
+                st.kv_ok = False
+                st.kv_done.set()
+                await st.tokens.put(PDToken(st.group_req_id, st.group_req_id, "", {"error": "pd node lost"},
+                                            FinishStatus.FINISHED_ERROR))
+
+    def update_node_status(self, hb: PDHeartbeat):
+        node = self.nodes.get(hb.node_id)
+        if node is not None:
+            node.run_status, node.last_heartbeat = hb.run_status, time.time()
+
+    async def drop_silent_nodes(self, now=None):
+        now = now or time.time()
+        for nid, n in list(self.nodes.items()):
+            if now - n.last_heartbeat > HEARTBEAT_TIMEOUT_S:
+                await self.remove_pd(nid)
+
+    def topology_ready(self) -> bool:
+        ps, ds = self._refresh()
+        if self.fixed_topology:
+            return (len(ps), len(ds)) == self.fixed_topology
+        return bool(ps) and bool(ds)
+
+    # ---------------------------------------------------------------- node -> master
+    async def on_node_message(self, obj):
+        if isinstance(obj, PDHeartbeat):
+            self.update_node_status(obj)
+        elif isinstance(obj, PDPromptIds):
+            st = self.reqs.get(obj.group_req_id)
+            if st is not None:
+                st.prompt_ids = obj.prompt_ids
+        elif isinstance(obj, PDToken):
+            st = self.reqs.get(obj.group_req_id)
+            if st is not None:
+                await st.tokens.put(obj)
+        elif isinstance(obj, UpKVStatus):
+            await self.update_kv_move_status(obj)
+
+    async def update_kv_move_status(self, up: UpKVStatus):
+        st = self.reqs.get(up.group_req_id)
+        if st is not None:
+            st.kv_ok = up.ok
+            st.kv_done.set()
+
+    # ---------------------------------------------------------------- generate
+    @staticmethod
+    async def _send(node: PDClient, obj):
+        await node.websocket.send_bytes(pickle.dumps(obj))
+
+    def tokens(self, prompt, multimodal_params=None, samping_params=None, kwargs=None) -> int:
+        raise ValueError("the pd_master has no tokenizer; ask a prefill node")
+
+    async def generate(self, prompt, sampling_params: SamplingParams, multimodal_params=None, request=None,
+                       is_health_req: bool = False):
+        if self.paused and not is_health_req:
+            raise ServerBusyError("generation is paused")
+        if not self.topology_ready():
+            raise ServerBusyError("no complete prefill/decode topology is registered")
+        if sampling_params.n != 1:
+            raise ValueError("pd_master mode serves n == best_of == 1")
+        gid = self._next_id
+        self._next_id += MAX_BEST_OF
+        p, d = self.selector.select_p_d_node(prompt, sampling_params, multimodal_params)
+        chars = len(prompt)
+        st = self.reqs[gid] = _ReqState(gid, p, d, chars)
+        for n in (p, d):
+            n.dispatched_req_num += 1
+        p.dispatched_prompt_chars += chars
+        sp = sampling_params.to_dict()
+        sp["group_request_id"] = gid
+        start = time.time()
+        try:
+            await self._send(p, PDRequest(gid, prompt, sp, multimodal_params, peer=d.to_wire()))
+            first: PDToken = await asyncio.wait_for(st.tokens.get(), FIRST_TOKEN_TIMEOUT_S)
+            fs = FinishStatus(first.finish_status)
+            meta = dict(first.metadata)
+            meta["first_token_cost_ms"] = (time.time() - start) * 1e3
+            if "prompt_cache_len" in meta and meta.get("prompt_tokens"):
+                self.selector.record_prompt_cache_hit_rate(meta["prompt_cache_len"] / meta["prompt_tokens"])
+            yield first.sub_req_id, first.text, meta, fs
+            if fs.is_finished():
+                return
+            try:
+                await asyncio.wait_for(st.kv_done.wait(), KV_MOVE_TIMEOUT_S)
+            except asyncio.TimeoutError:
+                st.kv_ok = False
+            if not st.kv_ok or st.prompt_ids is None:
+                yield first.sub_req_id, "", {"error": "kv transfer failed"}, FinishStatus(FinishStatus.FINISHED_ERROR)
+                return
+            sp_d = dict(sp)
+            sp_d["max_new_tokens"] = max(1, int(sp["max_new_tokens"]) - 1)
+            sp_d["min_new_tokens"] = max(1, int(sp.get("min_new_tokens", 1)) - 1)
+            await self._send(d, PDRequest(gid, st.prompt_ids + [meta["id"]], sp_d, multimodal_params, peer=p.to_wire(),
+                                          first_token=(meta["id"], meta.get("logprob", 0.0))))
+            while True:
+                tok: PDToken = await asyncio.wait_for(st.tokens.get(), FIRST_TOKEN_TIMEOUT_S)
+                if request is not None and await request.is_disconnected():
+                    await self.abort(gid)
+                    raise asyncio.CancelledError(f"client disconnected, req {gid} aborted")
+                m = dict(tok.metadata)
+                m.setdefault("prompt_tokens", meta.get("prompt_tokens", len(st.prompt_ids)))
+                if "count_output_tokens" in m:
+                    m["count_output_tokens"] += 1  # D counts from its own first step
+                fs = FinishStatus(tok.finish_status)
+                yield tok.sub_req_id, tok.text, m, fs
+                if fs.is_finished():
+                    return
+        finally:
+            self.reqs.pop(gid, None)
+            for n in (p, d):
+                n.dispatched_req_num = max(0, n.dispatched_req_num - 1)
+            p.dispatched_prompt_chars = max(0, p.dispatched_prompt_chars - chars)
+
+    async def abort(self, group_req_id: int) -> bool:
+        st = self.reqs.get(group_req_id)
+        if st is None:
+            return False
+        for n in (st.p, st.d):
+            try:
+                await self._send(n, ("ABORT", group_req_id))
+            except Exception:
+                pass
+        return True
+
+    async def abort_all(self):
+        for gid in list(self.reqs):
+            await self.abort(gid)
+
+    async def handle_loop(self):
+        while True:
+            await asyncio.sleep(10)
+            await self.drop_silent_nodes()
+
+    async def flush_cache(self):
+        for n in self.nodes.values():
+            await self._send(n, ("FLUSH_CACHE", None))
+
+    async def rl_op(self, op, payload=None):
+        for n in self.nodes.values():
+            await self._send(n, ("RL", (op, payload)))
+
+    async def profiler_cmd(self, what):
+        for n in self.nodes.values():
+            await self._send(n, ("PROFILER", what))

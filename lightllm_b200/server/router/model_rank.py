@@ -65,7 +65,25 @@ def _build_model_and_backend(args: StartArgs, ps):
     from ...engine.mode_backends import select_backend_class
 
     backend_cls = select_backend_class(args)
-    backend = backend_cls(model, bargs, is_master_in_dp=(ps.tp_rank == 0))
+    kw = {}
+    if args.run_mode == "prefill":
+        kw = dict(tp_rank=ps.tp_rank, page_tokens=args.pd_kv_page_size)
+    elif args.run_mode == "decode":
+        on_done = None
+        if ps.tp_rank == 0 and args.pd_kv_status_port:
+            import zmq
+
+            sock = zmq.Context.instance().socket(zmq.PUSH)
+            sock.connect(f"tcp://127.0.0.1:{args.pd_kv_status_port}")
+            on_done = lambda gid, ok: sock.send_pyobj((gid, ok))  # noqa: E731
+        kw = dict(tp_rank=ps.tp_rank, host=args.host if args.host not in ("localhost",) else "127.0.0.1",
+                  kv_port=args.pd_kv_port, page_tokens=args.pd_kv_page_size, page_num=args.pd_kv_page_num,
+                  cpu_group=ps.cpu_group, tp_size=ps.tp_size, on_kv_done=on_done)
+    elif backend_cls.__name__ in ("TokenHealingBackend", "XgrammarBackend", "OutlinesConstraintBackend"):
+        from ..tokenizer import get_tokenizer
+
+        kw = dict(tokenizer=get_tokenizer(args.model_dir, args.tokenizer_mode, args.trust_remote_code, args.vocab_size))
+    backend = backend_cls(model, bargs, is_master_in_dp=(ps.tp_rank == 0), **kw)
     return model, backend
 
 
@@ -154,6 +172,8 @@ class ModelRankLoop:
         idle_sleep = 0.001
         while self.running:
             self._read_mailbox()
+            if hasattr(self.backend, "poll_kv"):
+                self.backend.poll_kv()
             if self.backend.has_work():
                 res = self.backend.step()
                 for ir in res["finished"]:
