@@ -149,7 +149,15 @@ def main():
               batch_max_tokens=args.batch_max_tokens, chunked_prefill_size=args.batch_max_tokens // 2,
               disable_dynamic_prompt_cache=False, graph_max_batch_size=conc)
     model = llm.model
+    t_start = time.time()
+
+    def stage(msg):  # progress on stderr (rank 0), so a slow stage shows up in the log of a cut-off run
+        if rank == 0:
+            print(f"[bench +{time.time() - t_start:6.1f}s] {msg}", file=sys.stderr, flush=True)
+
+    stage("model built")
     llm.warmup([conc])
+    stage("decode graph captured")
     rng = np.random.default_rng(1234)
 
     def new_prompts():
@@ -214,9 +222,13 @@ def main():
         def elapsed_time(self, other):
             return (other.t - self.t) * 1e3
 
-    for _ in range(args.warmup):
+    for i in range(args.warmup):
         static_wave(new_prompts())
+        if i == 0:
+            barrier()
+            stage("first warm-up wave done")
     barrier()
+    stage("warm-up done")
     clocks = ClockSampler(dev.index or 0)
     clocks.start()
     n0 = ops.launch_count()
@@ -228,6 +240,7 @@ def main():
     ev1.record()
     barrier()
     dev_ms = ev0.elapsed_time(ev1)
+    stage(f"timed waves done: {dev_ms / args.steps:.1f} ms/wave")
     launches = ops.launch_count() - n0
     clock_info = clocks.stop()
     status = int(ops.gemm_status(dev).item()) if cuda else 0
@@ -288,7 +301,8 @@ def main():
                            "p50_ttft_ms": round(ttft_p50, 2) if ttft_p50 else None,
                            "p50_itl_ms": round(itl_p50, 3) if itl_p50 else None}
         print(json.dumps(line), flush=True)
-    pdist.destroy()
+    llm.close()
+    pdist.destroy(hard_exit_on_hang=True)
 
 
 if __name__ == "__main__":

@@ -37,7 +37,7 @@ using namespace llb;
 namespace {
 
 constexpr int MAX_WORLD = 8;
-constexpr uint64_t kCommWaitNs = 2000000000ull;
+constexpr uint64_t kCommWaitNs = 1000000000ull;
 
 struct RankView {
   // pointers as seen from THIS rank; index = peer rank
@@ -60,6 +60,8 @@ struct CommParams {
   float eps, w_offset;
   int one_shot;
   int do_norm;  // 0: plain all-reduce (out = sum over ranks, residual untouched)
+  int rows_per_chunk;  // two-shot: owned rows reduced and flagged together (about 1024 vectors of 16 bytes)
+  int max_chunks;      // flag slots per owner rank in every rank's flag array
 };
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
@@ -77,11 +79,14 @@ __device__ __forceinline__ uint4 ld_cg_16(const void* p) {
 }
 
 // Wait until *flag >= want (wrap-safe).  Called by one thread; returns false on timeout.
+// Once any wait of this rank has expired (status != 0) the later ones give up at their first check, so a
+// broken link costs one timeout per launch, not one per row.
 __device__ bool wait_flag(const uint32_t* flag, uint32_t want, int* status, int code) {
   uint64_t t0 = 0;
   for (uint32_t spin = 0;; ++spin) {
     if ((int32_t)(ld_acquire_sys(flag) - want) >= 0) return true;
     if ((spin & 0x3f) == 0x3f) {
+      if (status && *(volatile int*)status != 0) return false;
       uint64_t now = global_timer_ns();
       if (t0 == 0)
         t0 = now;
@@ -115,6 +120,57 @@ __device__ __forceinline__ void reduce_vec(const RankView& me, int world, int64_
     if (q < world) add8(acc, raw[q]);
 }
 
+// Two-shot phase 1: reduce the rows this rank owns (row % world == rank), chunk by chunk, and push the sums to
+// every rank.  All of a thread's peer loads of an iteration are issued before the first use (8 x 16 bytes in
+// flight per thread); a chunk's flag is released to all ranks after its sums are globally visible.
+template <int W>
+__device__ __forceinline__ void two_shot_phase1(const CommParams& p, const RankView& me, uint32_t epoch) {
+  constexpr int U = 8 / W;
+  const int world = p.world, T = p.T, H = p.H, nvec = H >> 3, G = gridDim.x;
+  const int n_owned = (T - me.rank + world - 1) / world;
+  const int rpc = p.rows_per_chunk;
+  const int n_chunks = (n_owned + rpc - 1) / rpc;
+  for (int c = blockIdx.x; c < n_chunks; c += G) {
+    const int i0 = c * rpc;
+    const int nv = (min(n_owned, i0 + rpc) - i0) * nvec;
+    for (int base = 0; base < nv; base += 256 * U) {
+      uint4 raw[U][W];
+      int64_t offs[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int idx = base + u * 256 + threadIdx.x;
+        offs[u] = -1;
+        if (idx < nv) {
+          const int row = me.rank + (i0 + idx / nvec) * world;
+          offs[u] = (int64_t)row * H + (idx % nvec) * 8;
+#pragma unroll
+          for (int q = 0; q < W; ++q)
+            if (q < world) raw[u][q] = ld_cg_16(me.partial[q] + offs[u]);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (offs[u] >= 0) {
+          float acc[8];
+#pragma unroll
+          for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+#pragma unroll
+          for (int q = 0; q < W; ++q)
+            if (q < world) add8(acc, raw[u][q]);
+          bf16x8 packed = pack8(acc);
+          const uint4 o = *reinterpret_cast<uint4*>(&packed);
+#pragma unroll
+          for (int q = 0; q < W; ++q)
+            if (q < world) *reinterpret_cast<uint4*>(me.sums[q] + offs[u]) = o;
+        }
+      }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x < world) st_release_sys(me.rowflag[threadIdx.x] + me.rank * p.max_chunks + c, epoch);
+  }
+}
+
 template <int MAX_VEC>
 __global__ void __launch_bounds__(256) tp_reduce_norm_kernel(const CommParams p) {
   __shared__ float red[33];
@@ -135,28 +191,21 @@ __global__ void __launch_bounds__(256) tp_reduce_norm_kernel(const CommParams p)
   __syncthreads();
 
   if (!p.one_shot) {
-    // ---- phase 1: reduce the rows I own and push the sums to everyone ----
-    for (int row = me.rank + blockIdx.x * world; row < T; row += G * world) {
-      for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
-        float acc[8];
-        const int64_t off = (int64_t)row * H + v * 8;
-        reduce_vec(me, world, off, acc);
-        bf16x8 packed = pack8(acc);
-        const uint4 out = *reinterpret_cast<uint4*>(&packed);
-#pragma unroll
-        for (int q = 0; q < MAX_WORLD; ++q)
-          if (q < world) *reinterpret_cast<uint4*>(me.sums[q] + off) = out;
-      }
-      __threadfence_system();
-      __syncthreads();
-      if (threadIdx.x < world) st_release_sys(me.rowflag[threadIdx.x] + row, epoch);
-    }
+    if (world <= 2)
+      two_shot_phase1<2>(p, me, epoch);
+    else if (world <= 4)
+      two_shot_phase1<4>(p, me, epoch);
+    else
+      two_shot_phase1<8>(p, me, epoch);
   }
 
   // ---- phase 2: residual add + RMSNorm over all rows (one-shot: reduce here from the peers) ----
   for (int row = blockIdx.x; row < T; row += G) {
     if (!p.one_shot) {
-      if (threadIdx.x == 0) s_ok = wait_flag(me.rowflag[me.rank] + row, epoch, me.status, 200) ? 1 : 0;
+      if (threadIdx.x == 0) {
+        const int owner = row % world, chunk = (row / world) / p.rows_per_chunk;
+        s_ok = wait_flag(me.rowflag[me.rank] + owner * p.max_chunks + chunk, epoch, me.status, 200) ? 1 : 0;
+      }
       __syncthreads();
     }
     float vals[MAX_VEC][8];
@@ -227,6 +276,18 @@ int launch(const CommParams& p, int ranks_in_grid, int ctas, cudaStream_t st) {
                    : per <= 2 ? (const void*)tp_reduce_norm_kernel<2>
                    : per <= 4 ? (const void*)tp_reduce_norm_kernel<4>
                               : (const void*)tp_reduce_norm_kernel<8>;
+  // CTAs of one launch wait on CTAs of the peers' launches (two-shot), so all of them must be resident
+  static int max_resident[4] = {0, 0, 0, 0};
+  const int slot = per <= 1 ? 0 : per <= 2 ? 1 : per <= 4 ? 2 : 3;
+  if (max_resident[slot] == 0) {
+    int occ = 0, dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, fn, 256, 0) != cudaSuccess || occ < 1) occ = 1;
+    max_resident[slot] = sms * occ;
+  }
+  if ((int)grid.x * ranks_in_grid > max_resident[slot]) grid.x = max_resident[slot] / ranks_in_grid;
+  if (grid.x < 1) grid.x = 1;
   cudaError_t e;
   if (ranks_in_grid > 1) {
     // one-GPU emulation: CTAs of different "ranks" wait on one another, so they must be co-resident
@@ -267,7 +328,7 @@ LLB_EXPORT int llb_ipc_close_handle(void* p) { return (int)cudaIpcCloseMemHandle
 LLB_EXPORT int llb_tp_reduce_norm(const void** partial, void** sums, void** ready, void** rowflag, void** residual,
                                   void** out, const void* norm_w, void** epoch, void** arrive, int* status, int rank,
                                   int world, int emulate_ranks, int T, int H, float eps, float w_offset, int one_shot,
-                                  int do_norm, int ctas, cudaStream_t st) {
+                                  int do_norm, int ctas, int max_chunks, cudaStream_t st) {
   if (T <= 0) return LLB_OK;
   CommParams p;
   memset(&p, 0, sizeof(p));
@@ -278,6 +339,8 @@ LLB_EXPORT int llb_tp_reduce_norm(const void** partial, void** sums, void** read
   p.w_offset = w_offset;
   p.one_shot = one_shot;
   p.do_norm = do_norm;
+  p.rows_per_chunk = (H / 8) >= 1024 ? 1 : 1024 / (H / 8);
+  p.max_chunks = max_chunks;
   const int nr = emulate_ranks > 1 ? emulate_ranks : 1;
   for (int r = 0; r < nr; ++r) {
     RankView& v = p.v[r];

@@ -199,6 +199,9 @@ class ModelBackend:
     def step(self) -> dict:
         """Runs at most one forward pass.  Returns {"kind", "finished": [InferReq], "tokens": n}."""
         self._steps += 1
+        fused = getattr(self.model.tp, "fused", None)
+        if fused is not None and (self._steps & 127) == 1:
+            fused.check()
         prefill, decode, finished = self._get_classed_reqs()
         kind = self.control.select(len(prefill), len(decode))
         n_tok = 0

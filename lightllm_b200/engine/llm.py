@@ -77,6 +77,18 @@ class LLM:
     def warmup(self, batch_sizes: Optional[List[int]] = None):
         self.model.warmup_graphs(batch_sizes)
 
+    def close(self):
+        """Release captured graphs (they hold the process group's collectives) and the peer-mapped buffers; call
+        before tearing the process group down."""
+        if self.model.device.type == "cuda":
+            torch.cuda.synchronize(self.model.device)
+        self.model.flush_graphs()
+        fused = getattr(self.model.tp, "fused", None)
+        if fused is not None:
+            fused.check()
+            self.model.tp.fused = None
+            fused.close()
+
     @torch.no_grad()
     def generate(self, prompt_token_ids: List[List[int]], sampling_params: Union[dict, List[dict], None] = None,
                  return_stats: bool = False):

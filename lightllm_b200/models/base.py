@@ -461,6 +461,8 @@ class TransformerLM:
                 return None
             return ops.add_rmsnorm_(residual, partial, next_norm_w, self.eps, self.norm_w_offset)
         if next_norm_w is None:
+            if self.tp.fused is not None:
+                self.tp.fused.skip()
             self.tp.all_reduce_(partial)
             residual.add_(partial)
             return None
@@ -479,6 +481,8 @@ class TransformerLM:
         partial = ops.gemm(a, w, epi="store", bias=bias,
                            out=fused.partial_out(a.shape[0], w.shape[0]) if use_fused else None)
         if next_norm_w is None:
+            if fused is not None:
+                fused.skip()
             self.tp.all_reduce_(partial)
             residual.add_(partial)
             return None

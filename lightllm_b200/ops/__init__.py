@@ -390,3 +390,48 @@ def token_logprob(logits, ids):
                                       ptr(out), stream()), "token_logprob")
     _count()
     return out
+
+
+# --------------------------------------------------------------------------------------
+def layernorm(x, w, b, eps: float, residual=None):
+    """LayerNorm(x [+ residual]) * w + b; with `residual` the sum is written back into it (in place)."""
+    if not _is_cuda(x):
+        return ref.layernorm(x, w, b, eps, residual)
+    _req_bf16(x, w)
+    assert x.is_contiguous() and (residual is None or residual.is_contiguous())
+    T, H = x.shape
+    out = torch.empty_like(x)
+    check(kernels().llb_layernorm(ptr(out), ptr(residual), ptr(x), ptr(w), ptr(b), c_int(T), c_int(H), f32(eps),
+                                  stream()), "layernorm")
+    _count()
+    return out
+
+
+def act_(x, kind: str, alpha: float = 1.0):
+    """In-place activation (silu | gelu | gelu_tanh | relu) or scaling (kind "scale", factor alpha)."""
+    if not _is_cuda(x):
+        return ref.act_(x, kind, alpha)
+    _req_bf16(x)
+    assert x.is_contiguous()
+    check(kernels().llb_act_(ptr(x), i64(x.numel()), c_int(ref.ACT_KINDS[kind]), f32(alpha), stream()), "act")
+    _count()
+    return x
+
+
+def attention_generic(q, kv_layer, req_to_token, b_req_idx, pos, batch_of, Hq, Hkv, D, sm_scale, window: int = 0,
+                      softcap: float = 0.0, alibi=None, sinks=None):
+    """Causal paged attention for any head size <= 256 with sliding window / ALiBi / soft-cap / sinks.
+    q [T, Hq*D] or [T, Hq, D]; returns [T, Hq, D]."""
+    T = q.shape[0]
+    if not _is_cuda(q):
+        return ref.attention_generic(q.reshape(T, Hq, D), kv_layer, req_to_token, b_req_idx, pos, batch_of, Hq, Hkv, D,
+                                     sm_scale, window, softcap, alibi, sinks)
+    _req_bf16(q, kv_layer)
+    assert q.stride(-1) == 1 and kv_layer.is_contiguous() and pos.dtype == torch.int32
+    out = torch.empty((T, Hq, D), dtype=q.dtype, device=q.device)
+    check(kernels().llb_attn_generic(ptr(q), i64(q.stride(0)), ptr(kv_layer), ptr(req_to_token),
+                                     i64(req_to_token.stride(0)), ptr(b_req_idx), ptr(pos), ptr(batch_of), ptr(out),
+                                     i64(out.stride(0)), c_int(T), c_int(Hq), c_int(Hkv), c_int(D), f32(sm_scale),
+                                     c_int(window), f32(softcap), ptr(alibi), ptr(sinks), stream()), "attn_generic")
+    _count()
+    return out

@@ -291,3 +291,62 @@ def mla_rope_kv_scatter_(q3, kv_a, kv_layer, kv_norm_w, cos, sin, pos, slot, nop
     kv_layer[slot.long(), 0, :kv_lora] = ckv.to(kv_layer.dtype)
     kv_layer[slot.long(), 0, kv_lora:] = kpe.to(kv_layer.dtype)
     return q3
+
+
+def layernorm(x, w, b, eps, residual=None):
+    """LayerNorm over the last dim; with `residual` the sum x + residual is normalised and stored back."""
+    if residual is not None:
+        residual.copy_((residual.float() + x.float()).to(residual.dtype))
+        x = residual
+    y = torch.nn.functional.layer_norm(x.float(), (x.shape[-1],), w.float(), None if b is None else b.float(), eps)
+    return y.to(x.dtype)
+
+
+ACT_KINDS = {"silu": 0, "gelu_tanh": 1, "gelu_pytorch_tanh": 1, "gelu_new": 1, "gelu_fast": 1, "gelu": 2, "relu": 3,
+             "scale": 4}
+
+
+def act_(x, kind: str, alpha: float = 1.0):
+    f = x.float()
+    k = ACT_KINDS[kind]
+    if k == 0:
+        f = torch.nn.functional.silu(f)
+    elif k == 1:
+        f = torch.nn.functional.gelu(f, approximate="tanh")
+    elif k == 2:
+        f = torch.nn.functional.gelu(f)
+    elif k == 3:
+        f = torch.relu(f)
+    else:
+        f = f * alpha
+    x.copy_(f.to(x.dtype))
+    return x
+
+
+def attention_generic(q, kv_layer, req_to_token, b_req_idx, pos, batch_of, Hq, Hkv, D, sm_scale, window=0,
+                      softcap=0.0, alibi=None, sinks=None):
+    """q [T, Hq, D]; token t belongs to request row batch_of[t] (t itself when None) at position pos[t] and
+    attends keys max(0, pos - window + 1) .. pos of that request."""
+    T = q.shape[0]
+    out = torch.zeros(T, Hq, D, dtype=q.dtype, device=q.device)
+    G = Hq // Hkv
+    for t in range(T):
+        b = int(batch_of[t]) if batch_of is not None else t
+        p = int(pos[t])
+        j0 = max(0, p - window + 1) if window > 0 else 0
+        slots = req_to_token[int(b_req_idx[b]), j0:p + 1].long()
+        k = kv_layer[slots, :Hkv].float().repeat_interleave(G, dim=1)      # [L, Hq, D]
+        v = kv_layer[slots, Hkv:2 * Hkv].float().repeat_interleave(G, dim=1)
+        s = torch.einsum("hd,lhd->hl", q[t].float(), k) * sm_scale
+        if softcap > 0:
+            s = softcap * torch.tanh(s / softcap)
+        if alibi is not None:
+            rel = torch.arange(j0, p + 1, device=q.device, dtype=torch.float32) - p
+            s = s + alibi.float()[:, None] * rel[None, :]
+        if sinks is not None:
+            s = torch.cat([s, sinks.float()[:, None]], dim=1)
+            pr = torch.softmax(s, dim=-1)[:, :-1]
+        else:
+            pr = torch.softmax(s, dim=-1)
+        out[t] = torch.einsum("hl,lhd->hd", pr, v).to(q.dtype)
+    return out

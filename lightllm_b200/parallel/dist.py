@@ -112,10 +112,28 @@ def init_from_env(dp: int = 1) -> ParallelState:
     return init_distributed(world, rank, dp=dp, host=host, port=port)
 
 
-def destroy():
+def destroy(hard_exit_on_hang: bool = False, wait_s: float = 20.0):
+    """Tear the process groups down.  Objects that still hold captured collectives (CUDA graphs) should be
+    released first (`LLM.close()`); if the tear-down does not return within `wait_s` and `hard_exit_on_hang` is
+    set (benchmarks, tests: their work is done and printed), the process exits at once instead of hanging."""
     global _STATE
     if dist.is_initialized():
-        dist.destroy_process_group()
+        import gc
+        import threading
+
+        gc.collect()
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+        t = threading.Thread(target=dist.destroy_process_group, daemon=True)
+        t.start()
+        t.join(wait_s)
+        if t.is_alive():
+            import sys
+
+            print(f"[dist] destroy_process_group still running after {wait_s:.0f}s", file=sys.stderr, flush=True)
+            if hard_exit_on_hang:
+                sys.stdout.flush()
+                os._exit(0)
     _STATE = ParallelState()
 
 

@@ -30,7 +30,7 @@ class FusedTP:
     ONE_SHOT_BYTES = 512 * 1024  # per-rank message below which every rank pulls all rows itself
 
     def __init__(self, pstate: Optional[pdist.ParallelState] = None, max_tokens: int = 16384, hidden: int = 8192,
-                 ctas: int = 64):
+                 ctas: int = 592):
         ps = pstate or pdist.state()
         assert ps.device.type == "cuda" and 1 < ps.tp_size <= 8
         self.ps = ps
@@ -43,13 +43,20 @@ class FusedTP:
         self.off_sums = [2 * self.buf_bytes, 3 * self.buf_bytes]
         self.off_ready = 4 * self.buf_bytes
         self.off_rowflag = self.off_ready + 256
-        total = self.off_rowflag + ((max_tokens * 4 + 255) // 256) * 256
+        self.max_chunks = max_tokens // self.world + 2   # chunk flags per owner rank (a chunk is >= 1 row)
+        total = self.off_rowflag + ((self.world * self.max_chunks * 4 + 255) // 256) * 256
         group = ps.cpu_group if ps.cpu_group is not None else ps.tp_group
         self.region = SymmetricRegion(total, self.rank, self.world, group=ps.tp_group if ps.dp_size > 1 else group,
                                       device=ps.device)
         self.local = torch.zeros(4, dtype=torch.int32, device=ps.device)  # [epoch, arrive, status, pad]
         self.parity = 0
         self.calls = 0
+        self._tabs = {}
+        self.force_one_shot = None  # experiments: 0 / 1 overrides the size rule
+
+    def close(self):
+        self._tabs = {}
+        self.region.close()
 
     # ---- buffers ----
     def partial_out(self, T: int, H: int) -> torch.Tensor:
@@ -64,21 +71,36 @@ class FusedTP:
     def can_all_reduce(self, x) -> bool:
         return False  # plain all-reduces (embedding, final residual) stay on NCCL
 
+    def _tables(self, par):
+        t = self._tabs.get(par)
+        if t is None:
+            r = self.region
+            base = self.local.data_ptr()
+            t = self._tabs[par] = dict(
+                partial=_ptr_array([r.ptrs[q] + self.off_partial[par] for q in range(self.world)]),
+                sums=_ptr_array([r.ptrs[q] + self.off_sums[par] for q in range(self.world)]),
+                ready=_ptr_array([r.ptrs[q] + self.off_ready for q in range(self.world)]),
+                rowflag=_ptr_array([r.ptrs[q] + self.off_rowflag for q in range(self.world)]),
+                epoch=_ptr_array([base]), arrive=_ptr_array([base + 4]), status=ctypes.c_void_p(base + 8))
+        return t
+
+    def _one_shot(self, T, H) -> int:
+        # one-shot: every rank pulls all peers' rows, (world - 1) x the message inbound and no second phase;
+        # two-shot: 2 (world - 1) / world x inbound plus a flag round.  With two ranks one-shot never moves more.
+        if self.force_one_shot is not None:
+            return self.force_one_shot
+        return 1 if (self.world == 2 or T * H * 2 * (self.world - 1) <= 4 * self.ONE_SHOT_BYTES) else 0
+
     def _launch(self, T, H, residual, out, norm_w, eps, w_offset, do_norm):
-        r = self.region
-        par = self.parity
-        one_shot = 1 if T * H * 2 <= self.ONE_SHOT_BYTES else 0
-        partial = _ptr_array([r.ptrs[q] + self.off_partial[par] for q in range(self.world)])
-        sums = _ptr_array([r.ptrs[q] + self.off_sums[par] for q in range(self.world)])
-        ready = _ptr_array([r.ptrs[q] + self.off_ready for q in range(self.world)])
-        rowflag = _ptr_array([r.ptrs[q] + self.off_rowflag for q in range(self.world)])
-        base = self.local.data_ptr()
-        check(kernels().llb_tp_reduce_norm(partial, sums, ready, rowflag, _ptr_array([residual.data_ptr() if residual is not None else 0]),
-                                           _ptr_array([out.data_ptr()]), ptr(norm_w), _ptr_array([base]),
-                                           _ptr_array([base + 4]), ctypes.c_void_p(base + 8), ctypes.c_int(self.rank),
-                                           ctypes.c_int(self.world), ctypes.c_int(0), ctypes.c_int(T), ctypes.c_int(H),
-                                           f32(eps), f32(w_offset), ctypes.c_int(one_shot), ctypes.c_int(do_norm),
-                                           ctypes.c_int(min(self.ctas, max(T, 1))), stream()), "tp_reduce_norm")
+        t = self._tables(self.parity)
+        check(kernels().llb_tp_reduce_norm(t["partial"], t["sums"], t["ready"], t["rowflag"],
+                                           _ptr_array([residual.data_ptr() if residual is not None else 0]),
+                                           _ptr_array([out.data_ptr()]), ptr(norm_w), t["epoch"], t["arrive"],
+                                           t["status"], ctypes.c_int(self.rank), ctypes.c_int(self.world),
+                                           ctypes.c_int(0), ctypes.c_int(T), ctypes.c_int(H), f32(eps), f32(w_offset),
+                                           ctypes.c_int(self._one_shot(T, H)), ctypes.c_int(do_norm),
+                                           ctypes.c_int(min(self.ctas, max(T, 1))), ctypes.c_int(self.max_chunks),
+                                           stream()), "tp_reduce_norm")
         _count()
         self.parity ^= 1
         self.calls += 1
@@ -92,8 +114,21 @@ class FusedTP:
         self._launch(T, H, residual, out, norm_w, eps, w_offset, 1)
         return out
 
+    def skip(self):
+        """A reduction of this forward pass went another way (the last layer has no following norm): keep the
+        buffer alternation in step, so that every pass starts on the same buffer (CUDA-graph replays reuse the
+        captured addresses and two consecutive calls must never share a buffer)."""
+        self.parity ^= 1
+
     def all_reduce_(self, x):
         raise NotImplementedError
+
+    def check(self):
+        """Raise if a bounded wait of the kernel ran out (a peer did not show up within a second)."""
+        st = self.status()
+        if st != 0:
+            raise RuntimeError(f"fused tensor-parallel reduction timed out waiting for a peer (code {st}); "
+                               "restart with --disable_symm_mem_allreduce to fall back to NCCL")
 
     def status(self) -> int:
         return int(self.local[2].item())

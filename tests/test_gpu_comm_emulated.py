@@ -23,7 +23,8 @@ def test_tp_reduce_norm_emulated(dev, world, T, H, one_shot):
     partial = [torch.zeros(2, maxT, H, dtype=BF, device=dev) for _ in range(world)]
     sums = [torch.zeros(2, maxT, H, dtype=BF, device=dev) for _ in range(world)]
     ready = [torch.zeros(64, dtype=torch.int32, device=dev) for _ in range(world)]
-    rowflag = [torch.zeros(maxT, dtype=torch.int32, device=dev) for _ in range(world)]
+    max_chunks = maxT // world + 2
+    rowflag = [torch.zeros(world * max_chunks, dtype=torch.int32, device=dev) for _ in range(world)]
     local = [torch.zeros(4, dtype=torch.int32, device=dev) for _ in range(world)]
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     w = (torch.randn(H, device=dev) * 0.1 + 1).to(BF)
@@ -45,7 +46,7 @@ def test_tp_reduce_norm_emulated(dev, world, T, H, one_shot):
             ctypes.c_void_p(w.data_ptr()), _ptr_array([t.data_ptr() for t in local]),
             _ptr_array([t.data_ptr() + 4 for t in local]), ctypes.c_void_p(status.data_ptr()), ctypes.c_int(0),
             ctypes.c_int(world), ctypes.c_int(world), ctypes.c_int(T), ctypes.c_int(H), ctypes.c_float(1e-5),
-            ctypes.c_float(0.0), ctypes.c_int(one_shot), ctypes.c_int(1), ctypes.c_int(ctas),
+            ctypes.c_float(0.0), ctypes.c_int(one_shot), ctypes.c_int(1), ctypes.c_int(ctas), ctypes.c_int(max_chunks),
             ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
         assert rc == 0
         torch.cuda.synchronize()

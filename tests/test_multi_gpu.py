@@ -48,7 +48,8 @@ def _worker(rank, world, port, out_dir, fused):
     if rank == 0:
         torch.save({"logits": logits, "tokens": [o["token_ids"] for o in outs], "status": status},
                    os.path.join(out_dir, f"tp{world}_f{int(fused)}.pt"))
-    pdist.destroy()
+    llm.close()
+    pdist.destroy(hard_exit_on_hang=True)
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
