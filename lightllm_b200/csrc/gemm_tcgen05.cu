@@ -52,6 +52,9 @@ struct GemmParams {
   // batched mode (per-head GEMMs of MLA): rank-3 tensor maps, tile -> (batch, m, n); C += batch * c_batch_stride
   int batch_count;
   int64_t c_batch_stride;
+  // W stored as [N/128][K/64][128][64] (every 128-row x 64-column tile is 16 contiguous KB): number of
+  // k-blocks per tile row, 0 for the row-major checkpoint layout
+  int w_tiled_kb;
 };
 
 template <int BN>
@@ -746,11 +749,317 @@ int pick_bn(int M, int N) {
   return best;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Skinny GEMM for decode (M <= 256): the weight matrix is streamed once, tokens are the small operand.
+//
+// One cluster of 2*S CTAs computes one output tile of 256 x (NB*256): S CTA pairs split the K range, each pair
+// runs cta_group::2 MMAs of M = 256 (CTA h supplies token rows h*128.. and 128 of every 256 weight rows), so a
+// CTA stages 16 KB of activations per 16 KB * NB of weights and k-block.  With S > 1 the fp32 partial tiles
+// are summed through distributed shared memory: every CTA spills its 128 x 256 accumulator to its own
+// shared memory (the drained pipeline stages), and after a cluster barrier each CTA reduces the column slice
+// 256/S that it owns from all S peers and writes the final values.  NB = 2 (both halves of the tensor
+// memory) is for wide N without split; S > 1 requires NB = 1.
+// ---------------------------------------------------------------------------------------------
+constexpr int SK_RSTRIDE = 260;  // floats per spilled row: 16-byte stores of 8 consecutive rows hit distinct banks
+
+template <int NB>
+constexpr int sk_stage_bytes() { return BM * BK * 2 + NB * PAIR_HALF * BK * 2; }
+template <int NB>
+constexpr int sk_stages() { return NB == 1 ? 6 : 4; }
+template <int NB>
+constexpr int sk_smem_bytes() { return sk_stages<NB>() * sk_stage_bytes<NB>() + 1024 + 512; }
+
+// No memory clobber: the caller orders these loads after the cluster barrier (both are volatile asm), and
+// several of them must be allowed in flight at once.
+__device__ __forceinline__ float4 ld_dsmem_f4(uint32_t cluster_addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(cluster_addr));
+  return v;
+}
+
+template <int NB, int EPI>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                        const GemmParams p, const int splits) {
+  constexpr int STAGES = sk_stages<NB>();
+  constexpr int A_BYTES = BM * BK * 2;
+  constexpr int B_BYTES = PAIR_HALF * BK * 2;
+  constexpr int STAGE_BYTES = sk_stage_bytes<NB>();
+  constexpr uint32_t TMEM_COLS = 512;
+  constexpr uint32_t IDESC = umma_idesc(256, 256, 1);
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
+  auto full_bar = [&](int s) { return bar_base + 8 * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8 * (STAGES + s); };
+  const uint32_t tfull_bar = bar_base + 8 * (2 * STAGES);
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const uint32_t half = rank & 1u, split = rank >> 1;
+  const uint32_t leader_rank = rank & ~1u, peer_rank = rank | 1u;
+  const int n0 = blockIdx.y * 256 * NB;
+  const int kb_total = (p.K + BK - 1) / BK;
+  const int kb_per = (kb_total + splits - 1) / splits;
+  const int kb0 = (int)split * kb_per;
+  const int nk = max(min(kb_total, kb0 + kb_per) - kb0, 0);
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    mbar_init(tfull_bar, 1);
+    fence_barrier_init();
+  }
+  if (warp == 0) {
+    tmem_alloc_pair(smem_u32(&tmem_base_slot), TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {  // ---- TMA producer (every CTA) ----
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int i = 0; i < nk; ++i) {
+        const int kb = kb0 + i;
+        mbar_wait(empty_bar(stage), phase ^ 1, &abort_flag, p.status, 21);
+        const uint32_t sa = smem_base + stage * STAGE_BYTES;
+        const uint32_t lead_full = map_to_cta(full_bar(stage), leader_rank);
+        if (half == 0) mbar_expect_tx(full_bar(stage), 2 * STAGE_BYTES);
+        tma_load_2d_pair(sa, &tmA, lead_full, kb * BK, (int)half * BM);
+#pragma unroll
+        for (int j = 0; j < NB; ++j) {
+          const int wrow = n0 + j * 256 + (int)half * PAIR_HALF;
+          if (p.w_tiled_kb)
+            tma_load_2d_pair(sa + A_BYTES + j * B_BYTES, &tmB, lead_full, 0, ((wrow >> 7) * p.w_tiled_kb + kb) * 128);
+          else
+            tma_load_2d_pair(sa + A_BYTES + j * B_BYTES, &tmB, lead_full, kb * BK, wrow);
+        }
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && half == 0) {  // ---- MMA issuer of the pair ----
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int i = 0; i < nk; ++i) {
+        mbar_wait(full_bar(stage), phase, &abort_flag, p.status, 22);
+        tc_fence_after();
+        const uint32_t sa = smem_base + stage * STAGE_BYTES;
+        const uint64_t da = umma_smem_desc_sw128(sa);
+#pragma unroll
+        for (int j = 0; j < NB; ++j) {
+          const uint64_t db = umma_smem_desc_sw128(sa + A_BYTES + j * B_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma_bf16_pair(tmem_base + j * 256, da + 2 * k, db + 2 * k, IDESC, (i | k) != 0);
+        }
+        umma_commit_pair(empty_bar(stage));
+        umma_commit_pair(map_to_cta(empty_bar(stage), peer_rank));
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+      umma_commit_pair(tfull_bar);
+      umma_commit_pair(map_to_cta(tfull_bar, peer_rank));
+    }
+  } else {
+    // ---- accumulator drain (every CTA): its 128 token rows ----
+    const int lane_grp = warp & 3;
+    const int erow = lane_grp * 32 + lane;
+    mbar_wait(tfull_bar, 0, &abort_flag, p.status, 23);
+    tc_fence_after();
+    const int row = (int)half * BM + erow;
+    const uint32_t t_row = tmem_base + ((uint32_t)(lane_grp * 32) << 16);
+    if (splits == 1) {
+#pragma unroll
+      for (int j = 0; j < NB; ++j)
+        epilogue_store<256, EPI>(p, t_row + j * 256, row, row < p.M, n0 + j * 256, false, [](uint32_t*, int) {});
+    } else {
+      float* R = reinterpret_cast<float*>(smem_gen) + (size_t)erow * SK_RSTRIDE;
+#pragma unroll 1
+      for (int c = 0; c < 256; c += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_row + c, r);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+          *reinterpret_cast<float4*>(R + c + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                                              __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+      }
+    }
+    tc_fence_before();
+  }
+
+  __syncthreads();
+  cluster_sync_all();  // every CTA's partial tile is in its shared memory
+
+  if (splits > 1) {
+    // all six warps reduce: thread t owns float4 column groups of the slice, two rows per iteration, and
+    // issues every peer load of an iteration before the first add
+    const int W = 256 / splits, W4 = W / 4;
+    const uint32_t r_base = smem_base;
+    uint32_t peer_base[4];
+#pragma unroll
+    for (int s2 = 0; s2 < 4; ++s2) peer_base[s2] = map_to_cta(r_base, (uint32_t)(2 * (s2 < splits ? s2 : 0)) + half);
+    for (int i = threadIdx.x; i < BM * W4; i += GEMM_THREADS) {
+      const int r = i / W4, c4 = i - r * W4;
+      const int col_local = (int)split * W + c4 * 4;
+      const uint32_t off = (uint32_t)(r * SK_RSTRIDE + col_local) * 4u;
+      float4 v[4];
+#pragma unroll
+      for (int s2 = 0; s2 < 4; ++s2)
+        if (s2 < splits) v[s2] = ld_dsmem_f4(peer_base[s2] + off);
+      float4 acc = v[0];
+#pragma unroll
+      for (int s2 = 1; s2 < 4; ++s2) {
+        if (s2 < splits) {
+          acc.x += v[s2].x;
+          acc.y += v[s2].y;
+          acc.z += v[s2].z;
+          acc.w += v[s2].w;
+        }
+      }
+      const int grow = (int)half * BM + r, gcol = n0 + col_local;
+      if (grow < p.M && gcol < p.N) {
+        if (p.bias) {
+          acc.x += __bfloat162float(p.bias[gcol]);
+          acc.y += __bfloat162float(p.bias[gcol + 1]);
+          acc.z += __bfloat162float(p.bias[gcol + 2]);
+          acc.w += __bfloat162float(p.bias[gcol + 3]);
+        }
+        if (EPI == EPI_F32) {
+          *reinterpret_cast<float4*>((float*)p.C + (int64_t)grow * p.ldc + gcol) = acc;
+        } else {
+          if (EPI == EPI_RESIDUAL) {
+            const bf162* rr = reinterpret_cast<const bf162*>(p.residual + (int64_t)grow * p.ldc + gcol);
+            const float2 r0 = __bfloat1622float2(rr[0]), r1 = __bfloat1622float2(rr[1]);
+            acc.x += r0.x;
+            acc.y += r0.y;
+            acc.z += r1.x;
+            acc.w += r1.y;
+          }
+          bf162 o0 = __floats2bfloat162_rn(acc.x, acc.y), o1 = __floats2bfloat162_rn(acc.z, acc.w);
+          uint2 packed = make_uint2(*reinterpret_cast<uint32_t*>(&o0), *reinterpret_cast<uint32_t*>(&o1));
+          *reinterpret_cast<uint2*>((bf16*)p.C + (int64_t)grow * p.ldc + gcol) = packed;
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // nobody leaves while a peer may still read its shared memory or signal into it
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int NB, int EPI>
+int launch_skinny(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int splits, cudaStream_t st) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_skinny_kernel<NB, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         sk_smem_bytes<NB>());
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(2 * splits, cdiv(p.N, 256 * NB), 1);
+  cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = sk_smem_bytes<NB>();
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2 * splits;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_bf16_skinny_kernel<NB, EPI>, ta, tb, p, splits);
+  return e == cudaSuccess ? LLB_OK : (int)e;
+}
+
+// nb: 1 or 2 accumulators; splits: 1, 2 or 4 (nb must be 1 when splits > 1; gated epilogues need splits == 1)
+int dispatch_skinny(int epi, int nb, int splits, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
+                    cudaStream_t st) {
+  if (splits > 1 && (nb != 1 || epi == EPI_GATED_SILU || epi == EPI_GATED_GELU)) return LLB_ERR_UNSUPPORTED;
+  if (nb == 1) {
+    switch (epi) {
+      case EPI_STORE: return launch_skinny<1, EPI_STORE>(ta, tb, p, splits, st);
+      case EPI_RESIDUAL: return launch_skinny<1, EPI_RESIDUAL>(ta, tb, p, splits, st);
+      case EPI_GATED_SILU: return launch_skinny<1, EPI_GATED_SILU>(ta, tb, p, splits, st);
+      case EPI_GATED_GELU: return launch_skinny<1, EPI_GATED_GELU>(ta, tb, p, splits, st);
+      case EPI_F32: return launch_skinny<1, EPI_F32>(ta, tb, p, splits, st);
+    }
+  } else {
+    switch (epi) {
+      case EPI_STORE: return launch_skinny<2, EPI_STORE>(ta, tb, p, 1, st);
+      case EPI_RESIDUAL: return launch_skinny<2, EPI_RESIDUAL>(ta, tb, p, 1, st);
+      case EPI_GATED_SILU: return launch_skinny<2, EPI_GATED_SILU>(ta, tb, p, 1, st);
+      case EPI_GATED_GELU: return launch_skinny<2, EPI_GATED_GELU>(ta, tb, p, 1, st);
+      case EPI_F32: return launch_skinny<2, EPI_F32>(ta, tb, p, 1, st);
+    }
+  }
+  return LLB_ERR_UNSUPPORTED;
+}
+
+// Shape rule for M <= 256 (measured on B200, CUDA-graph replays): at M = 256 these GEMMs sit on the roofline ridge,
+// so what matters is how many SMs work.  Up to 74 tiles of 256 columns: one accumulator, K split over 2 pairs
+// (4 pairs = clusters of 8 only for very narrow outputs: few of those clusters are co-resident).  Wider, up to
+// one wave of 512-column tiles: both accumulators, no split.  Beyond that the persistent pair kernel
+// (returns nb = 0, use_pair = true) overlaps its epilogues with the next tile.
+void skinny_plan(int M, int N, int K, int epi, int* nb, int* splits, bool* use_pair) {
+  const bool gated = epi == EPI_GATED_SILU || epi == EPI_GATED_GELU;
+  const int sms = sm_count();
+  const int tiles = cdiv(N, 256), kb = cdiv(K, BK);
+  *nb = 0;
+  *splits = 1;
+  *use_pair = false;
+  if (tiles * 2 <= sms) {
+    *nb = 1;
+    if (gated) return;
+    if (tiles <= 8 && kb >= 32)
+      *splits = 4;
+    else if (tiles * 4 <= sms && kb >= 16)
+      *splits = 2;
+    return;
+  }
+  if (cdiv(N, 512) * 2 <= sms) {
+    *nb = 2;
+    return;
+  }
+  if (M > 128) *use_pair = true;
+}
+
+bool g_skinny_auto = true;
 bool g_pair_auto = true;  // measured faster than one-CTA tiles for M >= 1024, K <= 8192 on B200
 
 }  // namespace
 
 LLB_EXPORT void llb_gemm_set_pair_auto(int on) { g_pair_auto = on != 0; }
+LLB_EXPORT void llb_gemm_set_skinny_auto(int on) { g_skinny_auto = on != 0; }
 
 // C[M,N] (ldc) = A[M,K] (lda) . W[N,K]^T (ldw)  with epilogue `epi`:
 //   0 store bf16 (+bias)          1 store bf16 of acc (+bias) + residual[M,N] (same ldc)
@@ -785,6 +1094,44 @@ LLB_EXPORT int llb_gemm_bf16(const void* A, int64_t lda, const void* W, int64_t 
       if (stream_k == 1 && !fits) return LLB_ERR_BAD_ARG;
       stream_k = 0;
     }
+  }
+  // skinny (decode) kernel: explicit (bn = 1000 + 10 * nb + splits) or chosen for M <= 256
+  int sk_nb = 0, sk_splits = 0;
+  if (bn >= 1000) {
+    sk_nb = (bn - 1000) / 10;
+    sk_splits = (bn - 1000) % 10;
+    if (M > 256 || (sk_nb != 1 && sk_nb != 2) || (sk_splits != 1 && sk_splits != 2 && sk_splits != 4) || (N % 8) ||
+        (int64_t)cdiv(kblocks, sk_splits) * (sk_splits - 1) >= kblocks)
+      return LLB_ERR_UNSUPPORTED;
+  } else if (bn == 0 && stream_k == 0 && g_skinny_auto && M <= 256 && N >= 1024 && (N % 8) == 0 && K >= 1024) {
+    bool plan_pair = false;
+    skinny_plan(M, N, K, epi, &sk_nb, &sk_splits, &plan_pair);
+    if (plan_pair && ldw >= 0) bn = 512;
+  }
+  const bool w_tiled = ldw < 0;  // W is [N/128][K/64][128][64]
+  if (w_tiled && ((N % 128) || (K % 64) || !sk_nb)) return LLB_ERR_UNSUPPORTED;
+  if (sk_nb) {
+    CUtensorMap ta, tb;
+    int rc = cached_tmap(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM);
+    if (rc) return rc;
+    if (w_tiled)
+      rc = cached_tmap(&tb, W, (uint64_t)N * (K / 64), 64, 64, (uint32_t)PAIR_HALF);
+    else
+      rc = cached_tmap(&tb, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, (uint32_t)PAIR_HALF);
+    if (rc) return rc;
+    GemmParams p;
+    memset(&p, 0, sizeof(p));
+    p.w_tiled_kb = w_tiled ? K / 64 : 0;
+    p.C = C;
+    p.residual = (const bf16*)residual;
+    p.bias = (const bf16*)bias;
+    p.status = status;
+    p.M = M;
+    p.N = N;
+    p.K = K;
+    p.ldc = ldc;
+    p.batch_count = 1;
+    return dispatch_skinny(epi, sk_nb, sk_splits, ta, tb, p, st);
   }
   // CTA-pair kernel: explicit (bn == 512) or chosen for big problems (at least two waves of pair tiles)
   bool use_pair = bn == 512;

@@ -167,6 +167,24 @@ def _stream_k_scratch(device):
     return cur
 
 
+class TiledWeight:
+    """A [N, K] weight stored as [N/128][K/64][128][64]: every 128-row x 64-column tile (what one TMA box of
+    the GEMM kernels fetches) is 16 contiguous KB, so that weight streaming reads whole DRAM pages instead of
+    128-byte pieces 2K bytes apart."""
+
+    def __init__(self, w: torch.Tensor):
+        N, K = w.shape
+        assert N % 128 == 0 and K % 64 == 0, "tiled weights need N % 128 == 0 and K % 64 == 0"
+        self.N, self.K = N, K
+        self.data = w.view(N // 128, 128, K // 64, 64).permute(0, 2, 1, 3).contiguous().view(-1, 64)
+        self.shape = (N, K)
+        self.dtype, self.device = w.dtype, w.device
+
+    def dense(self) -> torch.Tensor:
+        N, K = self.N, self.K
+        return self.data.view(N // 128, K // 64, 128, 64).permute(0, 2, 1, 3).reshape(N, K)
+
+
 def gemm(a, w, epi: str = "store", residual=None, bias=None, out=None, bn: int = 0, stream_k: int = 0):
     """C = A . W^T on the tcgen05 tensor cores.  a [M, K], w [N, K] (checkpoint layout).
 
@@ -189,14 +207,20 @@ def gemm(a, w, epi: str = "store", residual=None, bias=None, out=None, bn: int =
         return res
     M, K = a.shape
     N = w.shape[0]
-    assert w.shape[1] == K and a.stride(1) == 1 and w.stride(1) == 1
+    tiled = isinstance(w, TiledWeight)
+    ldw = -1 if tiled else w.stride(0)
+    if tiled:
+        w = w.data
+    else:
+        assert w.shape[1] == K and w.stride(1) == 1
+    assert a.stride(1) == 1
     n_out = N // 2 if epi.startswith("gated") else N
     if out is None:
         out = torch.empty((M, n_out), dtype=torch.float32 if epi == "f32" else a.dtype, device=a.device)
     if epi == "residual":
         assert residual.shape == out.shape and residual.stride(0) == out.stride(0)
     skp, skc = (None, None) if stream_k == 0 else _stream_k_scratch(a.device)
-    check(kernels().llb_gemm_bf16(ptr(a), i64(a.stride(0)), ptr(w), i64(w.stride(0)), ptr(out), i64(out.stride(0)),
+    check(kernels().llb_gemm_bf16(ptr(a), i64(a.stride(0)), ptr(w), i64(ldw), ptr(out), i64(out.stride(0)),
                                   ptr(residual), ptr(bias), c_int(M), c_int(N), c_int(K), c_int(EPI_CODES[epi]),
                                   c_int(bn), c_int(stream_k), ptr(skp), i64(skp.numel() if skp is not None else 0),
                                   ptr(skc), c_int(skc.numel() if skc is not None else 0),

@@ -11,6 +11,33 @@ import json
 import torch
 
 
+def timeit_graph(fn, flush, n=10, reps=8):
+    """Like `timeit`, but the `reps` calls are captured in one CUDA graph and replayed, so that no host launch
+    cost is in the number (what a kernel costs inside the decode graph)."""
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        for i in range(reps):
+            fn(i)
+    torch.cuda.current_stream().wait_stream(s)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for i in range(reps):
+            fn(i)
+    ts = []
+    for _ in range(n):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1) / reps)
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
 def timeit(fn, flush, n=10, reps=8):
     """Median over n samples of (time of `reps` back-to-back calls fn(i)) / reps.  fn(i) should use the
     i-th copy of its operands so that consecutive calls do not hit each other's data in L2; the launches
@@ -39,14 +66,30 @@ def main():
     ap.add_argument("--quick", action="store_true")
     ap.add_argument("--stream-k", action="store_true", help="also time the stream-K schedule")
     ap.add_argument("--reps", type=int, default=8, help="back-to-back launches per timed sample")
+    ap.add_argument("--decode", action="store_true", help="only the M <= 256 shapes, with the skinny-kernel variants")
+    ap.add_argument("--graph", action="store_true", help="time CUDA-graph replays (no host launch cost)")
+    ap.add_argument("--only", default=None, help="M,N,K: run just this shape (3 plain launches of --bn, for profilers)")
+    ap.add_argument("--bn", type=int, default=0, help="kernel selector passed to ops.gemm with --only")
     a = ap.parse_args()
     dev = torch.device("cuda")
+    if a.only:
+        M, N, K = (int(v) for v in a.only.split(","))
+        x = (torch.randn(M, K, device=dev) * 0.5).bfloat16()
+        ws = [(torch.randn(N, K, device=dev) * 0.1).bfloat16() for _ in range(3)]
+        for w in ws:
+            ops.gemm(x, w, bn=a.bn)
+        torch.cuda.synchronize()
+        print("gemm wait status", int(ops.gemm_status(dev).item()))
+        return
+    timer = timeit_graph if a.graph else timeit
     shapes = [(16384, 6144, 4096), (16384, 4096, 4096), (16384, 28672, 4096), (16384, 4096, 14336),
               (256, 6144, 4096), (256, 4096, 4096), (256, 28672, 4096), (256, 4096, 14336), (256, 128256, 4096),
               (64, 6144, 4096), (64, 4096, 14336), (8192, 8192, 8192), (4096, 1280, 8192), (4096, 8192, 1024),
               (256, 1280, 8192), (256, 8192, 1024), (256, 7168, 8192), (256, 8192, 3584)]
     if a.quick:
         shapes = shapes[:9]
+    if a.decode:
+        shapes = [sh for sh in shapes if sh[0] <= 256] + [(32, 6144, 4096), (32, 28672, 4096), (8, 4096, 14336)]
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     for M, N, K in shapes:
         reps = a.reps
@@ -55,20 +98,32 @@ def main():
         ws = [(torch.randn(N, K, device=dev) * 0.1).bfloat16() for _ in range(copies)]
         out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
         row = {"M": M, "N": N, "K": K}
-        t = timeit(lambda i: torch.matmul(xs[i % copies], ws[i % copies].t(), out=out), flush, reps=reps)
+        t = timer(lambda i: torch.matmul(xs[i % copies], ws[i % copies].t(), out=out), flush, reps=reps)
         row["cublas_ms"] = round(t, 4)
         row["cublas_tflops"] = round(2 * M * N * K / t / 1e9, 1)
         variants = {"auto": dict(), "dp256": dict(bn=256, stream_k=0), "dp128": dict(bn=128, stream_k=0),
                     "dp64": dict(bn=64, stream_k=0), "pair": dict(bn=512, stream_k=0)}
+        if M <= 256:  # skinny kernel: 1000 + 10 * accumulators + K splits
+            variants.update({"sk_n1s1": dict(bn=1011), "sk_n1s2": dict(bn=1012), "sk_n1s4": dict(bn=1014),
+                             "sk_n2s1": dict(bn=1021)})
         if a.stream_k:
             variants.update({"sk256": dict(bn=256, stream_k=1), "sk128": dict(bn=128, stream_k=1)})
+        tiled = None
+        if M <= 256 and N % 128 == 0 and K % 64 == 0:  # the same kernels over the tiled weight layout
+            tiled = [ops.TiledWeight(w) for w in ws]
+            variants.update({"skt_n1s1": dict(bn=1011, tiled=1), "skt_n1s2": dict(bn=1012, tiled=1),
+                             "skt_n1s4": dict(bn=1014, tiled=1), "skt_n2s1": dict(bn=1021, tiled=1)})
         done = []
         for name, kw in variants.items():
+            kw = dict(kw)
+            wsel = tiled if kw.pop("tiled", 0) else ws
             if kw.get("stream_k") == 1 and ((M + 127) // 128) * ((N + kw["bn"] - 1) // kw["bn"]) > 8192:
                 continue  # more tiles than arrival counters
             if kw.get("bn") == 512 and (M < 256 or N < 256):
                 continue
-            t = timeit(lambda i: ops.gemm(xs[i % copies], ws[i % copies], out=out, **kw), flush, reps=reps)
+            if kw.get("bn", 0) >= 1000 and ((K + 63) // 64) < 4 * (kw["bn"] % 10):
+                continue
+            t = timer(lambda i: ops.gemm(xs[i % copies], wsel[i % copies], out=out, **kw), flush, reps=reps)
             row[f"{name}_ms"] = round(t, 4)
             done.append(name)
         best = min(row[f"{n}_ms"] for n in done)

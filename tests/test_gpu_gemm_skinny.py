@@ -1,0 +1,70 @@
+"""Decode GEMM (M <= 256): CTA-pair tiles, K split across a cluster with a distributed-shared-memory reduction."""
+import pytest
+import torch
+
+from lightllm_b200 import ops
+from lightllm_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+BF = torch.bfloat16
+
+
+def _check(got, want):
+    err = (got.float() - want.float()).abs().max().item()
+    tol = 1e-2 * want.abs().max().item() + 1e-2
+    assert err < tol, f"max abs err {err} (tol {tol})"
+    assert int(ops.gemm_status(got.device).item()) == 0, "a bounded wait inside the GEMM timed out"
+
+
+# bn = 1000 + 10 * accumulators + splits
+@pytest.mark.parametrize("M", [1, 7, 100, 128, 129, 256])
+@pytest.mark.parametrize("N,K", [(1024, 1024), (4096, 4096), (6144, 4096), (4096, 14336), (1032, 4160)])
+@pytest.mark.parametrize("bn", [1011, 1012, 1014, 1021])
+def test_skinny_store(dev, M, N, K, bn):
+    torch.manual_seed(M + N)
+    a = (torch.randn(M, K, device=dev) * 0.5).to(BF)
+    w = (torch.randn(N, K, device=dev) * 0.1).to(BF)
+    _check(ops.gemm(a, w, bn=bn), a.float() @ w.float().t())
+
+
+@pytest.mark.parametrize("bn", [1011, 1012, 1014, 1021, 0])
+def test_skinny_epilogues(dev, bn):
+    torch.manual_seed(3)
+    M, N, K = 200, 2048, 2048
+    a = (torch.randn(M, K, device=dev) * 0.5).to(BF)
+    w = (torch.randn(N, K, device=dev) * 0.1).to(BF)
+    bias = torch.randn(N, device=dev).to(BF)
+    res = torch.randn(M, N, device=dev).to(BF)
+    acc = a.float() @ w.float().t()
+    _check(ops.gemm(a, w, bias=bias, bn=bn), acc + bias.float())
+    _check(ops.gemm(a, w, epi="residual", residual=res, bn=bn), acc + res.float())
+    r2 = res.clone()
+    ops.gemm(a, w, epi="residual", residual=r2, out=r2, bn=bn)
+    _check(r2, acc + res.float())
+    f = ops.gemm(a, w, epi="f32", bias=bias, bn=bn)
+    assert f.dtype == torch.float32 and (f - acc - bias.float()).abs().max().item() < 2e-2
+    if bn in (1011, 1021, 0):
+        g = (torch.randn(N // 2, K, device=dev) * 0.1).to(BF)
+        u = (torch.randn(N // 2, K, device=dev) * 0.1).to(BF)
+        want = torch.nn.functional.silu(a.float() @ g.float().t()) * (a.float() @ u.float().t())
+        _check(ops.gemm(a, ref.interleave_gate_up(g, u), epi="gated_silu", bn=bn), want)
+
+
+def test_skinny_auto_llama_shapes(dev):
+    torch.manual_seed(4)
+    for M in (256, 64):
+        for N, K in ((6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336)):
+            a = (torch.randn(M, K, device=dev) * 0.5).to(BF)
+            w = (torch.randn(N, K, device=dev) * 0.05).to(BF)
+            _check(ops.gemm(a, w), a.float() @ w.float().t())
+
+
+@pytest.mark.parametrize("bn", [1011, 1012, 1014, 1021])
+@pytest.mark.parametrize("M,N,K", [(256, 4096, 4096), (33, 1024, 14336), (200, 6144, 1024)])
+def test_skinny_tiled_weight(dev, bn, M, N, K):
+    torch.manual_seed(5)
+    a = (torch.randn(M, K, device=dev) * 0.5).to(BF)
+    w = (torch.randn(N, K, device=dev) * 0.1).to(BF)
+    tw = ops.TiledWeight(w)
+    assert torch.equal(tw.dense(), w)
+    _check(ops.gemm(a, tw, bn=bn), a.float() @ w.float().t())
