@@ -36,14 +36,32 @@ from ..parallel.tp import TPContext
 from .weights import RandomSource, SafetensorsSource, WeightSource, kv_head_range, tp_range
 
 
-def load_config(model_dir: str) -> dict:
-    with open(os.path.join(model_dir, "config.json")) as f:
-        cfg = json.load(f)
+def normalize_config(cfg: dict) -> dict:
+    """One spelling for keys that differ between config generations: `rope_parameters` (new) is unfolded into
+    `rope_theta` / `rope_scaling`, `num_local_experts` doubles as `num_experts`, multimodal wrappers expose
+    their `text_config` at the top level."""
+    cfg = dict(cfg)
     if "text_config" in cfg and "hidden_size" not in cfg:  # multimodal wrappers
         base = dict(cfg["text_config"])
         base.setdefault("model_type", cfg.get("model_type"))
         cfg = {**cfg, **base}
+    rp = cfg.get("rope_parameters")
+    if isinstance(rp, dict):
+        if "rope_theta" in rp:
+            cfg.setdefault("rope_theta", rp["rope_theta"])
+        kind = rp.get("rope_type", rp.get("type", "default"))
+        if kind not in (None, "default") and not cfg.get("rope_scaling"):
+            cfg["rope_scaling"] = {k: v for k, v in rp.items() if k != "rope_theta"}
+        if "partial_rotary_factor" in rp:
+            cfg.setdefault("partial_rotary_factor", rp["partial_rotary_factor"])
+    if "num_local_experts" in cfg:
+        cfg.setdefault("num_experts", cfg["num_local_experts"])
     return cfg
+
+
+def load_config(model_dir: str) -> dict:
+    with open(os.path.join(model_dir, "config.json")) as f:
+        return normalize_config(json.load(f))
 
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float16": torch.float16, "fp16": torch.float16,
@@ -80,6 +98,7 @@ class TransformerLM:
                  graph_split_batch_size: int = 32, graph_grow_step_size: int = 16, disable_cudagraph: bool = False,
                  graph_max_len_in_batch: Optional[int] = None, tp_fused=None, random_seed: int = 0,
                  vocab_parallel_embedding: bool = False, num_layers_override: Optional[int] = None, **extra):
+        config = normalize_config(config)
         self.config = config
         self.ps = pstate or pdist.state()
         self.device = self.ps.device

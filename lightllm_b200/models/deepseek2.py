@@ -69,10 +69,13 @@ class DeepseekV2LM(TransformerLM):
         n_routed = c.get("n_routed_experts")
         self.moe = None
         if n_routed:
-            has_bias = c.get("topk_method", "") == "noaux_tc"
+            # V3-generation checkpoints route with sigmoid scores and a learned selection bias; configs written by
+            # newer tooling omit the two keys that say so
+            v3_like = c.get("model_type") in ("deepseek_v3", "kimi_k2", "glm4_moe_lite")
+            has_bias = c.get("topk_method", "noaux_tc" if v3_like else "greedy") == "noaux_tc"
             self.moe = moe.MoEConfig(n_routed, c["num_experts_per_tok"], c["moe_intermediate_size"],
                                      renorm=c.get("norm_topk_prob", True),
-                                     scoring=c.get("scoring_func", "softmax"), n_group=c.get("n_group") or 1,
+                                     scoring=c.get("scoring_func", "sigmoid" if v3_like else "softmax"), n_group=c.get("n_group") or 1,
                                      topk_group=c.get("topk_group") or 1,
                                      routed_scale=float(c.get("routed_scaling_factor", 1.0)), has_bias=has_bias,
                                      n_shared=c.get("n_shared_experts") or 0,

@@ -95,10 +95,12 @@ def test_deepseek_tiny_model_gpu_matches_cpu(dev):
                eos_token_id=2)
     ids = torch.randint(3, 2048, (150,), generator=torch.Generator().manual_seed(0))
     outs = {}
+    source = None  # both models read the same CPU-generated tensors (a CUDA generator draws other numbers)
     for name, device in (("cpu", torch.device("cpu")), ("gpu", dev)):
         ps = pdist.ParallelState(device=device)
         m = get_model(cfg, pstate=ps, data_type="bfloat16" if name == "gpu" else "float32", max_total_token_num=1024,
-                      max_req_num=4, max_seq_length=256, disable_cudagraph=True, random_seed=0)
+                      max_req_num=4, max_seq_length=256, disable_cudagraph=True, random_seed=0, weight_source=source)
+        source = m.weight_source
         req = m.req_manager.alloc()
         slots = m.mem_manager.alloc(len(ids))
         mi = ModelInput(batch_size=1, total_token_num=len(ids), max_kv_len=len(ids), is_prefill=True,
