@@ -106,3 +106,55 @@ LLB_EXPORT int llb_attn_generic(const void* q, int64_t q_stride, const void* kv_
   LLB_LAUNCH_CHECK();
   return LLB_OK;
 }
+
+// RoPE + KV scatter for head sizes / rotary widths the vectorised kernel does not take (head size not 64, 128
+// or 256, rotary width not a multiple of 16).  One CTA per token: the token's qkv row is staged in shared
+// memory so that rotation partners are read before anything is overwritten.  Same contract as
+// llb_rope_kv_scatter (half-split rotary layout, q rotated in place, K and V written to kv_layer[slot]).
+__global__ void __launch_bounds__(256) rope_kv_scatter_generic_kernel(bf16* __restrict__ qkv, bf16* __restrict__ kv_layer,
+                                                                      const float* __restrict__ cos_t,
+                                                                      const float* __restrict__ sin_t,
+                                                                      const int* __restrict__ pos,
+                                                                      const int* __restrict__ slot, int Hq, int Hkv,
+                                                                      int D, int rot_dim, int64_t qkv_stride) {
+  extern __shared__ float srow[];
+  const int t = blockIdx.x;
+  const int n = (Hq + 2 * Hkv) * D;
+  bf16* row = qkv + (int64_t)t * qkv_stride;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) srow[i] = __bfloat162float(row[i]);
+  __syncthreads();
+  const int half = rot_dim >> 1;
+  const int p = pos[t], s = slot[t];
+  const float* cr = cos_t + (int64_t)p * half;
+  const float* sr = sin_t + (int64_t)p * half;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int head = i / D, d = i - head * D;
+    const int kind = head < Hq ? 0 : (head < Hq + Hkv ? 1 : 2);
+    float x = srow[i];
+    if (kind != 2 && d < rot_dim) {
+      if (d < half)
+        x = x * cr[d] - srow[i + half] * sr[d];
+      else
+        x = x * cr[d - half] + srow[i - half] * sr[d - half];
+    }
+    const bf16 o = __float2bfloat16(x);
+    if (kind == 0)
+      row[i] = o;
+    else
+      kv_layer[((int64_t)s * (2 * Hkv) + (head - Hq)) * D + d] = o;
+  }
+}
+
+LLB_EXPORT int llb_rope_kv_scatter_generic(void* qkv, void* kv_layer, const float* cos_t, const float* sin_t,
+                                           const int* pos, const int* slot, int T, int Hq, int Hkv, int D, int rot_dim,
+                                           int64_t qkv_stride, cudaStream_t st) {
+  if (T <= 0) return LLB_OK;
+  const size_t smem = (size_t)(Hq + 2 * Hkv) * D * sizeof(float);
+  if ((rot_dim & 1) || rot_dim > D || smem > 200 * 1024) return LLB_ERR_UNSUPPORTED;
+  if (smem > 48 * 1024)
+    cudaFuncSetAttribute(rope_kv_scatter_generic_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  rope_kv_scatter_generic_kernel<<<T, 256, smem, st>>>((bf16*)qkv, (bf16*)kv_layer, cos_t, sin_t, pos, slot, Hq, Hkv, D,
+                                                      rot_dim, qkv_stride);
+  LLB_LAUNCH_CHECK();
+  return LLB_OK;
+}

@@ -2,3 +2,4 @@
 from . import llama  # noqa: F401
 from . import qwen3_moe  # noqa: F401
 from . import deepseek2  # noqa: F401
+from . import generic  # noqa: F401

@@ -122,8 +122,8 @@ class TransformerLM:
         self.graph_max_len_in_batch = graph_max_len_in_batch or max_seq_length
 
         if weight_source is None:
-            weight_source = SafetensorsSource(model_dir) if model_dir and self._has_weights(model_dir) else \
-                RandomSource(self.weight_shapes(), dtype=self.dtype, seed=random_seed,
+            weight_source = self._wrap_source(SafetensorsSource(model_dir)) \
+                if model_dir and self._has_weights(model_dir) else RandomSource(self.weight_shapes(), dtype=self.dtype, seed=random_seed,
                              device=str(self.device) if self.device.type == "cuda" else "cpu",
                              fp8_names=self.fp8_weight_names())
         self.weight_source = weight_source
@@ -134,6 +134,11 @@ class TransformerLM:
         self._graphs: Dict[int, dict] = {}
         self._graph_pool = None
         self.weight_version = "default"
+
+    def _wrap_source(self, src: WeightSource) -> WeightSource:
+        """Hook for families whose checkpoints use other tensor names or fused tensors: return a view of `src`
+        under this package's canonical (Llama-style) names."""
+        return src
 
     @staticmethod
     def _has_weights(model_dir):
@@ -446,7 +451,9 @@ class TransformerLM:
     def _lm_head(self, h):
         hn = ops.rmsnorm(h, self.final_norm_w, self.eps, self.norm_w_offset)
         logits = ops.gemm(hn, self.lm_head_w, epi="f32")
-        return self.tp.gather_logits(logits)
+        logits = self.tp.gather_logits(logits)
+        scale = getattr(self, "logit_scale", 1.0)
+        return logits * scale if scale != 1.0 else logits
 
     def _layers_forward(self, x, st: InferState):
         """x: embeddings [T, H]; returns the final residual stream (pre final-norm)."""
@@ -515,7 +522,10 @@ class TransformerLM:
                              self.rot_dim, lw.q_norm, lw.k_norm, self.eps, self.norm_w_offset)
         q = qkv[:, : hq * D]
         r2t = self.req_manager.req_to_token_indexs
-        if st.is_prefill:
+        if D not in (64, 128):  # no tensor-core attention kernel for this head size
+            o = ops.attention_generic(q, kv_layer, r2t, st.b_req_idx, st.position_ids,
+                                      st.batch_of_token if st.is_prefill else None, hq, hkv, D, self.sm_scale)
+        elif st.is_prefill:
             o = ops.gqa_prefill(q, kv_layer, r2t, st.b_req_idx, st.cu_q, st.b_ready_cache_len, hq, hkv, D,
                                 st.max_q_len, self.sm_scale)
         else:

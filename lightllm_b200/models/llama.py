@@ -3,8 +3,11 @@ internlm2-style and other checkpoints that share the layer (reference: lightllm/
 qwen2, qwen3, mistral, internlm, stablelm, minicpm, phi3)."""
 from __future__ import annotations
 
+import torch
+
 from .base import TransformerLM
 from .registry import register_model
+from .remap import RemapSource, grouped_qkv, split_rows
 
 
 @register_model("llama", "mistral", "internlm3")
@@ -29,3 +32,118 @@ class Qwen3LM(TransformerLM):
         super()._read_config(c)
         self.qk_norm = True
         self.attn_bias = c.get("attention_bias", False)
+
+
+@register_model("internlm")
+class InternLM(TransformerLM):
+    """Llama layer with biases on q/k/v/o (config key `bias`)."""
+
+    def _read_config(self, c):
+        super()._read_config(c)
+        self.attn_bias = bool(c.get("bias", True))
+
+    def _attn_weight_shapes(self, p):
+        s = super()._attn_weight_shapes(p)
+        if self.attn_bias:
+            s[p + "self_attn.o_proj.bias"] = (self.hidden,)
+        return s
+
+
+@register_model("internlm2")
+class InternLM2(TransformerLM):
+    """Llama layer; the checkpoint fuses q/k/v per kv group (`attention.wqkv`) and names the MLP w1/w3/w2."""
+
+    def _wrap_source(self, src):
+        t = {"model.embed_tokens.weight": "model.tok_embeddings.weight", "lm_head.weight": "output.weight"}
+        kv, g, D = self.num_kv_heads, self.num_q_heads // self.num_kv_heads, self.head_dim
+        for i in range(self.num_layers):
+            p = f"model.layers.{i}."
+            t[p + "input_layernorm.weight"] = p + "attention_norm.weight"
+            t[p + "post_attention_layernorm.weight"] = p + "ffn_norm.weight"
+            for which in ("q", "k", "v"):
+                t[f"{p}self_attn.{which}_proj.weight"] = grouped_qkv(p + "attention.wqkv.weight", kv, g, D, which)
+            t[p + "self_attn.o_proj.weight"] = p + "attention.wo.weight"
+            t[p + "mlp.gate_proj.weight"] = p + "feed_forward.w1.weight"
+            t[p + "mlp.up_proj.weight"] = p + "feed_forward.w3.weight"
+            t[p + "mlp.down_proj.weight"] = p + "feed_forward.w2.weight"
+        return RemapSource(src, t)
+
+
+@register_model("phi3")
+class Phi3LM(TransformerLM):
+    """Llama layer with fused `qkv_proj` and `gate_up_proj` tensors."""
+
+    def _wrap_source(self, src):
+        t = {}
+        qd, kd = self.num_q_heads * self.head_dim, self.num_kv_heads * self.head_dim
+        for i in range(self.num_layers):
+            p = f"model.layers.{i}."
+            t[p + "self_attn.q_proj.weight"] = split_rows(p + "self_attn.qkv_proj.weight", 0, qd)
+            t[p + "self_attn.k_proj.weight"] = split_rows(p + "self_attn.qkv_proj.weight", qd, qd + kd)
+            t[p + "self_attn.v_proj.weight"] = split_rows(p + "self_attn.qkv_proj.weight", qd + kd, qd + 2 * kd)
+            t[p + "mlp.gate_proj.weight"] = split_rows(p + "mlp.gate_up_proj.weight", 0, self.inter)
+            t[p + "mlp.up_proj.weight"] = split_rows(p + "mlp.gate_up_proj.weight", self.inter, 2 * self.inter)
+        return RemapSource(src, t)
+
+
+@register_model("minicpm")
+class MiniCPM(TransformerLM):
+    """Llama layer with muP-style scales: embeddings x scale_emb, every residual branch x scale_depth / sqrt(L)
+    (folded into o_proj / down_proj at load), logits / (hidden / dim_model_base)."""
+
+    def _read_config(self, c):
+        super()._read_config(c)
+        self.embed_scale = float(c.get("scale_emb", 1.0))
+        self.branch_scale = float(c.get("scale_depth", 1.0)) / (self.num_layers ** 0.5)
+        self.logit_scale = 1.0 / (self.hidden / float(c.get("dim_model_base", self.hidden)))
+
+    def _load_attn(self, lw, src, p, layer):
+        super()._load_attn(lw, src, p, layer)
+        lw.o_w = (lw.o_w.float() * self.branch_scale).to(lw.o_w.dtype)
+
+    def _load_ffn(self, lw, src, p, layer):
+        super()._load_ffn(lw, src, p, layer)
+        lw.down_w = (lw.down_w.float() * self.branch_scale).to(lw.down_w.dtype)
+
+
+@register_model("qwen")
+class QwenV1LM(TransformerLM):
+    """First-generation Qwen: fused c_attn with bias, MLP out = c_proj(w1(x) * silu(w2(x))), config
+    `intermediate_size` counts both halves."""
+
+    def _read_config(self, c):
+        c = dict(c)
+        c["intermediate_size"] = c["intermediate_size"] // 2
+        c.setdefault("rms_norm_eps", c.get("layer_norm_epsilon", 1e-6))
+        c.setdefault("rope_theta", c.get("rotary_emb_base", 10000.0))
+        c.setdefault("num_key_value_heads", c["num_attention_heads"])
+        super()._read_config(c)
+        self.attn_bias = True
+
+    def _wrap_source(self, src):
+        t = {"model.embed_tokens.weight": "transformer.wte.weight", "model.norm.weight": "transformer.ln_f.weight"}
+        H = self.hidden
+        for i in range(self.num_layers):
+            p, q = f"model.layers.{i}.", f"transformer.h.{i}."
+            t[p + "input_layernorm.weight"] = q + "ln_1.weight"
+            t[p + "post_attention_layernorm.weight"] = q + "ln_2.weight"
+            for k, name in enumerate(("q_proj", "k_proj", "v_proj")):
+                t[f"{p}self_attn.{name}.weight"] = split_rows(q + "attn.c_attn.weight", k * H, (k + 1) * H)
+                t[f"{p}self_attn.{name}.bias"] = split_rows(q + "attn.c_attn.bias", k * H, (k + 1) * H)
+            t[p + "self_attn.o_proj.weight"] = q + "attn.c_proj.weight"
+            t[p + "mlp.gate_proj.weight"] = q + "mlp.w2.weight"
+            t[p + "mlp.up_proj.weight"] = q + "mlp.w1.weight"
+            t[p + "mlp.down_proj.weight"] = q + "mlp.c_proj.weight"
+        return RemapSource(src, t)
+
+
+@register_model("gemma")
+class GemmaLM(TransformerLM):
+    """Gemma (2B / 7B): RMSNorm with (1 + w), GeGLU, embeddings x sqrt(hidden), head size 256, tied lm_head."""
+
+    def _read_config(self, c):
+        super()._read_config(c)
+        self.norm_w_offset = 1.0
+        self.act = "gelu"
+        self.embed_scale = float(torch.tensor(self.hidden ** 0.5, dtype=torch.bfloat16))
+        self.tie_embeddings = True

@@ -92,15 +92,24 @@ def gated_act(x, act: str = "silu", out=None):
 
 def rope_kv_scatter_(qkv, kv_layer, cos, sin, pos, slot, Hq, Hkv, D, rot_dim=None, q_norm_w=None, k_norm_w=None,
                      norm_eps=1e-6, norm_w_offset=0.0):
-    rot_dim = rot_dim or D
+    """rot_dim None = full head; 0 = no rotation (ALiBi / learned positions: K and V are only scattered)."""
+    rot_dim = D if rot_dim is None else rot_dim
     if not _is_cuda(qkv):
         return ref.rope_kv_scatter_(qkv, kv_layer, cos, sin, pos, slot, Hq, Hkv, D, rot_dim, q_norm_w, k_norm_w,
                                     norm_eps, norm_w_offset)
     _req_bf16(qkv, kv_layer, q_norm_w, k_norm_w)
     assert qkv.stride(-1) == 1 and kv_layer.is_contiguous()
     assert pos.dtype == torch.int32 and slot.dtype == torch.int32
-    assert cos.dtype == torch.float32 and cos.shape[-1] == rot_dim // 2
     T = qkv.shape[0]
+    if D not in (64, 128, 256) or rot_dim % 16 != 0:
+        assert q_norm_w is None and k_norm_w is None, "q/k norm needs a head size of 64, 128 or 256"
+        assert rot_dim == 0 or (cos.dtype == torch.float32 and cos.shape[-1] == rot_dim // 2)
+        check(kernels().llb_rope_kv_scatter_generic(ptr(qkv), ptr(kv_layer), ptr(cos), ptr(sin), ptr(pos), ptr(slot),
+                                                    c_int(T), c_int(Hq), c_int(Hkv), c_int(D), c_int(rot_dim),
+                                                    i64(qkv.stride(0)), stream()), "rope_kv_scatter_generic")
+        _count()
+        return qkv
+    assert rot_dim == 0 or (cos.dtype == torch.float32 and cos.shape[-1] == rot_dim // 2)
     check(kernels().llb_rope_kv_scatter(ptr(qkv), ptr(kv_layer), ptr(cos), ptr(sin), ptr(pos), ptr(slot),
                                         ptr(q_norm_w), ptr(k_norm_w), f32(norm_eps), f32(norm_w_offset), c_int(T),
                                         c_int(Hq), c_int(Hkv), c_int(D), c_int(rot_dim), i64(qkv.stride(0)),

@@ -150,6 +150,11 @@ def rope_kv_scatter_(qkv, kv_layer, cos, sin, pos, slot, Hq, Hkv, D, rot_dim, q_
     if k_norm_w is not None:
         k = rmsnorm(k.to(qkv.dtype), k_norm_w, norm_eps, norm_w_offset).float()
     half = rot_dim // 2
+    if rot_dim == 0:
+        v3[:, :Hq] = q.to(qkv.dtype)
+        kv_layer[slot.long(), :Hkv] = k.to(kv_layer.dtype)
+        kv_layer[slot.long(), Hkv:] = v.to(kv_layer.dtype)
+        return qkv
     c = cos[pos.long()].unsqueeze(1)
     s = sin[pos.long()].unsqueeze(1)
 

@@ -131,3 +131,183 @@ def test_deepseek_v3(tmp_path):
         for layer in m.model.layers[1:]:
             layer.mlp.gate.e_score_correction_bias.copy_(torch.randn(8) * 0.1)
     _check(tmp_path, m, _ids(200))
+
+
+def test_bloom(tmp_path):
+    from transformers import BloomConfig, BloomForCausalLM
+
+    torch.manual_seed(0)
+    cfg = BloomConfig(hidden_size=64, n_layer=2, n_head=4, vocab_size=200)
+    _check(tmp_path, BloomForCausalLM(cfg), _ids(200))
+
+
+def test_gpt_bigcode(tmp_path):
+    from transformers import GPTBigCodeConfig, GPTBigCodeForCausalLM
+
+    torch.manual_seed(0)
+    cfg = GPTBigCodeConfig(n_embd=64, n_layer=2, n_head=4, n_inner=128, vocab_size=200, n_positions=256,
+                           multi_query=True)
+    _check(tmp_path, GPTBigCodeForCausalLM(cfg), _ids(200))
+
+
+def test_starcoder2(tmp_path):
+    from transformers import Starcoder2Config, Starcoder2ForCausalLM
+
+    torch.manual_seed(0)
+    cfg = Starcoder2Config(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                           num_key_value_heads=2, vocab_size=200, max_position_embeddings=256, sliding_window=16)
+    _check(tmp_path, Starcoder2ForCausalLM(cfg), _ids(200, n=40))
+
+
+def test_stablelm(tmp_path):
+    from transformers import StableLmConfig, StableLmForCausalLM
+
+    torch.manual_seed(0)
+    cfg = StableLmConfig(hidden_size=96, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                         num_key_value_heads=4, vocab_size=200, max_position_embeddings=256, partial_rotary_factor=0.25,
+                         use_qkv_bias=True)
+    _check(tmp_path, StableLmForCausalLM(cfg), _ids(200))
+
+
+def test_phi3(tmp_path):
+    from transformers import Phi3Config, Phi3ForCausalLM
+
+    torch.manual_seed(0)
+    cfg = Phi3Config(hidden_size=96, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                     num_key_value_heads=2, vocab_size=200, max_position_embeddings=256, pad_token_id=0)
+    _check(tmp_path, Phi3ForCausalLM(cfg), _ids(200))
+
+
+def test_gemma(tmp_path):
+    from transformers import GemmaConfig, GemmaForCausalLM
+
+    torch.manual_seed(0)
+    cfg = GemmaConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=1, head_dim=32, vocab_size=200, max_position_embeddings=256)
+    _check(tmp_path, GemmaForCausalLM(cfg), _ids(200))
+
+
+def test_gemma3_text(tmp_path):
+    from transformers import Gemma3ForCausalLM, Gemma3TextConfig
+
+    torch.manual_seed(0)
+    cfg = Gemma3TextConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=6, num_attention_heads=4,
+                           num_key_value_heads=2, head_dim=32, vocab_size=200, max_position_embeddings=256,
+                           sliding_window=8, query_pre_attn_scalar=32)
+    _check(tmp_path, Gemma3ForCausalLM(cfg), _ids(200, n=30))
+
+
+# ---- families without a transformers class: the same math under another checkpoint layout ----
+def _save_custom(tmp_path, cfg: dict, tensors: dict):
+    import json
+
+    from safetensors.torch import save_file
+
+    d = tmp_path / "custom"
+    d.mkdir()
+    with open(d / "config.json", "w") as f:
+        json.dump(cfg, f)
+    save_file({k: v.contiguous() for k, v in tensors.items()}, str(d / "model.safetensors"))
+    return str(d)
+
+
+def _compare(model_dir, hf_model, ids, tol=2e-3):
+    ours, seq = _run_ours(model_dir, ids)
+    with torch.no_grad():
+        ref = hf_model(torch.tensor([seq])).logits[0].float()
+    n = len(ids)
+    assert (ours[0] - ref[:n]).abs().max().item() < tol * max(ref.abs().max().item(), 1.0)
+    for k, o in enumerate(ours[1:]):
+        assert (o[0] - ref[n + k]).abs().max().item() < tol * max(ref.abs().max().item(), 1.0)
+
+
+def test_internlm2_layout(tmp_path):
+    from transformers import LlamaConfig, LlamaForCausalLM
+
+    torch.manual_seed(0)
+    H, nh, nkv, L = 64, 4, 2, 2
+    D, g = H // nh, nh // nkv
+    hf = LlamaForCausalLM(LlamaConfig(hidden_size=H, intermediate_size=128, num_hidden_layers=L, num_attention_heads=nh,
+                                      num_key_value_heads=nkv, vocab_size=200, max_position_embeddings=256)).eval().float()
+    sd = hf.state_dict()
+    t = {"model.tok_embeddings.weight": sd["model.embed_tokens.weight"], "model.norm.weight": sd["model.norm.weight"],
+         "output.weight": sd["lm_head.weight"]}
+    for i in range(L):
+        p = f"model.layers.{i}."
+        q = sd[p + "self_attn.q_proj.weight"].view(nkv, g, D, H)
+        k = sd[p + "self_attn.k_proj.weight"].view(nkv, 1, D, H)
+        v = sd[p + "self_attn.v_proj.weight"].view(nkv, 1, D, H)
+        t[p + "attention.wqkv.weight"] = torch.cat([q, k, v], dim=1).reshape(-1, H)
+        t[p + "attention.wo.weight"] = sd[p + "self_attn.o_proj.weight"]
+        t[p + "feed_forward.w1.weight"] = sd[p + "mlp.gate_proj.weight"]
+        t[p + "feed_forward.w3.weight"] = sd[p + "mlp.up_proj.weight"]
+        t[p + "feed_forward.w2.weight"] = sd[p + "mlp.down_proj.weight"]
+        t[p + "attention_norm.weight"] = sd[p + "input_layernorm.weight"]
+        t[p + "ffn_norm.weight"] = sd[p + "post_attention_layernorm.weight"]
+    cfg = dict(model_type="internlm2", hidden_size=H, intermediate_size=128, num_hidden_layers=L, num_attention_heads=nh,
+               num_key_value_heads=nkv, vocab_size=200, rms_norm_eps=hf.config.rms_norm_eps, rope_theta=10000.0)
+    _compare(_save_custom(tmp_path, cfg, t), hf, _ids(200))
+
+
+def test_qwen_v1_layout(tmp_path):
+    from transformers import Qwen2Config, Qwen2ForCausalLM
+
+    torch.manual_seed(0)
+    H, nh, L, I = 64, 4, 2, 96
+    hf = Qwen2ForCausalLM(Qwen2Config(hidden_size=H, intermediate_size=I, num_hidden_layers=L, num_attention_heads=nh,
+                                      num_key_value_heads=nh, vocab_size=200, max_position_embeddings=256,
+                                      tie_word_embeddings=False)).eval().float()
+    sd = hf.state_dict()
+    t = {"transformer.wte.weight": sd["model.embed_tokens.weight"], "transformer.ln_f.weight": sd["model.norm.weight"],
+         "lm_head.weight": sd["lm_head.weight"]}
+    for i in range(L):
+        p, q = f"model.layers.{i}.", f"transformer.h.{i}."
+        t[q + "attn.c_attn.weight"] = torch.cat([sd[p + f"self_attn.{n}_proj.weight"] for n in "qkv"], dim=0)
+        t[q + "attn.c_attn.bias"] = torch.cat([sd[p + f"self_attn.{n}_proj.bias"] for n in "qkv"], dim=0)
+        t[q + "attn.c_proj.weight"] = sd[p + "self_attn.o_proj.weight"]
+        t[q + "mlp.w2.weight"] = sd[p + "mlp.gate_proj.weight"]
+        t[q + "mlp.w1.weight"] = sd[p + "mlp.up_proj.weight"]
+        t[q + "mlp.c_proj.weight"] = sd[p + "mlp.down_proj.weight"]
+        t[q + "ln_1.weight"] = sd[p + "input_layernorm.weight"]
+        t[q + "ln_2.weight"] = sd[p + "post_attention_layernorm.weight"]
+    cfg = dict(model_type="qwen", hidden_size=H, intermediate_size=2 * I, num_hidden_layers=L, num_attention_heads=nh,
+               vocab_size=200, layer_norm_epsilon=hf.config.rms_norm_eps, rotary_emb_base=10000.0)
+    _compare(_save_custom(tmp_path, cfg, t), hf, _ids(200))
+
+
+def test_minicpm_scales(tmp_path):
+    from transformers import LlamaConfig, LlamaForCausalLM
+
+    torch.manual_seed(0)
+    H, L = 64, 2
+    s_e, depth, base = 12.0, 1.4, 32
+    hf = LlamaForCausalLM(LlamaConfig(hidden_size=H, intermediate_size=128, num_hidden_layers=L, num_attention_heads=4,
+                                      num_key_value_heads=2, vocab_size=200, max_position_embeddings=256,
+                                      tie_word_embeddings=False)).eval().float()
+    raw = {k: v.clone() for k, v in hf.state_dict().items()}  # the MiniCPM checkpoint: unscaled tensors
+    with torch.no_grad():  # the reference: the same network with the scales folded into the weights
+        hf.model.embed_tokens.weight.mul_(s_e)
+        hf.lm_head.weight.mul_(1.0 / (H / base))
+        for layer in hf.model.layers:
+            layer.self_attn.o_proj.weight.mul_(depth / L ** 0.5)
+            layer.mlp.down_proj.weight.mul_(depth / L ** 0.5)
+    cfg = dict(model_type="minicpm", hidden_size=H, intermediate_size=128, num_hidden_layers=L, num_attention_heads=4,
+               num_key_value_heads=2, vocab_size=200, rms_norm_eps=hf.config.rms_norm_eps, rope_theta=10000.0,
+               scale_emb=s_e, scale_depth=depth, dim_model_base=base, tie_word_embeddings=False)
+    _compare(_save_custom(tmp_path, cfg, raw), hf, _ids(200))
+
+
+def test_internlm_bias(tmp_path):
+    from transformers import LlamaConfig, LlamaForCausalLM
+
+    torch.manual_seed(0)
+    hf = LlamaForCausalLM(LlamaConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                                      num_key_value_heads=4, vocab_size=200, max_position_embeddings=256,
+                                      attention_bias=True)).eval().float()
+    with torch.no_grad():
+        for layer in hf.model.layers:
+            for n in ("q_proj", "k_proj", "v_proj", "o_proj"):
+                getattr(layer.self_attn, n).bias.normal_(0, 0.1)
+    cfg = dict(model_type="internlm", hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+               vocab_size=200, rms_norm_eps=hf.config.rms_norm_eps, rope_theta=10000.0, bias=True)
+    _compare(_save_custom(tmp_path, cfg, dict(hf.state_dict())), hf, _ids(200))
