@@ -29,7 +29,7 @@ constexpr int BM = 128;
 constexpr int BK = 64;  // 64 bf16 = 128 bytes = one swizzle row
 constexpr int UMMA_K = 16;
 constexpr int GEMM_THREADS = 192;
-constexpr int SMEM_BUDGET = 200 * 1024;
+constexpr int SMEM_BUDGET = 224 * 1024;
 constexpr int64_t kPanelBytes = 24ll << 20;  // A panel kept hot in L2 while W streams past it
 
 enum Epi { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_GATED_SILU = 2, EPI_F32 = 3, EPI_GATED_GELU = 4 };
@@ -546,7 +546,7 @@ int dispatch_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tb, GemmPara
 constexpr int PAIR_BN = 256;       // tile width (W rows per pair tile)
 constexpr int PAIR_HALF = 128;     // W rows loaded by each CTA
 constexpr int PAIR_STAGE_BYTES = BM * BK * 2 + PAIR_HALF * BK * 2;  // 32 KB
-constexpr int PAIR_STAGES = 6;
+constexpr int PAIR_STAGES = 7;
 constexpr int pair_smem_bytes() { return PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 512; }
 
 template <int EPI>
@@ -804,7 +804,10 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
   const uint32_t rank = cluster_ctarank();
   const uint32_t half = rank & 1u, split = rank >> 1;
   const uint32_t leader_rank = rank & ~1u, peer_rank = rank | 1u;
-  const int n0 = blockIdx.y * 256 * NB;
+  int mb, nbk;
+  tile_coords(blockIdx.y, p.num_m_blocks, p.num_n_blocks, p.group_m, mb, nbk);
+  const int m0 = mb * 256;
+  const int n0 = nbk * 256 * NB;
   const int kb_total = (p.K + BK - 1) / BK;
   const int kb_per = (kb_total + splits - 1) / splits;
   const int kb0 = (int)split * kb_per;
@@ -841,7 +844,7 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         const uint32_t sa = smem_base + stage * STAGE_BYTES;
         const uint32_t lead_full = map_to_cta(full_bar(stage), leader_rank);
         if (half == 0) mbar_expect_tx(full_bar(stage), 2 * STAGE_BYTES);
-        tma_load_2d_pair(sa, &tmA, lead_full, kb * BK, (int)half * BM);
+        tma_load_2d_pair(sa, &tmA, lead_full, kb * BK, m0 + (int)half * BM);
 #pragma unroll
         for (int j = 0; j < NB; ++j) {
           const int wrow = n0 + j * 256 + (int)half * PAIR_HALF;
@@ -888,7 +891,7 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     const int erow = lane_grp * 32 + lane;
     mbar_wait(tfull_bar, 0, &abort_flag, p.status, 23);
     tc_fence_after();
-    const int row = (int)half * BM + erow;
+    const int row = m0 + (int)half * BM + erow;
     const uint32_t t_row = tmem_base + ((uint32_t)(lane_grp * 32) << 16);
     if (splits == 1) {
 #pragma unroll
@@ -939,7 +942,7 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
           acc.w += v[s2].w;
         }
       }
-      const int grow = (int)half * BM + r, gcol = n0 + col_local;
+      const int grow = m0 + (int)half * BM + r, gcol = n0 + col_local;
       if (grow < p.M && gcol < p.N) {
         if (p.bias) {
           acc.x += __bfloat162float(p.bias[gcol]);
@@ -976,7 +979,12 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
 }
 
 template <int NB, int EPI>
-int launch_skinny(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int splits, cudaStream_t st) {
+int launch_skinny(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p_in, int splits, cudaStream_t st) {
+  GemmParams p = p_in;
+  p.num_m_blocks = cdiv(p.M, 256);
+  p.num_n_blocks = cdiv(p.N, 256 * NB);
+  int64_t panel_rows = kPanelBytes / ((int64_t)256 * p.K * 2);
+  p.group_m = (int)(panel_rows < 2 ? 2 : (panel_rows > 32 ? 32 : panel_rows));
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_bf16_skinny_kernel<NB, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -986,7 +994,7 @@ int launch_skinny(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams
   }
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
-  cfg.gridDim = dim3(2 * splits, cdiv(p.N, 256 * NB), 1);
+  cfg.gridDim = dim3(2 * splits, p.num_m_blocks * p.num_n_blocks, 1);
   cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
   cfg.dynamicSmemBytes = sk_smem_bytes<NB>();
   cfg.stream = st;
@@ -1100,9 +1108,13 @@ LLB_EXPORT int llb_gemm_bf16(const void* A, int64_t lda, const void* W, int64_t 
   if (bn >= 1000) {
     sk_nb = (bn - 1000) / 10;
     sk_splits = (bn - 1000) % 10;
-    if (M > 256 || (sk_nb != 1 && sk_nb != 2) || (sk_splits != 1 && sk_splits != 2 && sk_splits != 4) || (N % 8) ||
+    if ((sk_nb != 1 && sk_nb != 2) || (sk_splits != 1 && sk_splits != 2 && sk_splits != 4) || (N % 8) ||
         (int64_t)cdiv(kblocks, sk_splits) * (sk_splits - 1) >= kblocks)
       return LLB_ERR_UNSUPPORTED;
+  } else if (bn == 0 && stream_k == 0 && g_skinny_auto && M >= 1024 && K >= 8192 && (N % 512) == 0 && ldw >= 0 &&
+             (int64_t)cdiv(M, 256) * (N / 512) >= 2ll * (sm_count() / 2)) {
+    sk_nb = 2;  // long K: one 256 x 512 tile per CTA pair measured faster than the persistent 256 x 256 schedule
+    sk_splits = 1;
   } else if (bn == 0 && stream_k == 0 && g_skinny_auto && M <= 256 && N >= 1024 && (N % 8) == 0 && K >= 1024) {
     bool plan_pair = false;
     skinny_plan(M, N, K, epi, &sk_nb, &sk_splits, &plan_pair);
@@ -1135,7 +1147,7 @@ LLB_EXPORT int llb_gemm_bf16(const void* A, int64_t lda, const void* W, int64_t 
   }
   // CTA-pair kernel: explicit (bn == 512) or chosen for big problems (at least two waves of pair tiles)
   bool use_pair = bn == 512;
-  if (bn == 0 && stream_k == 0 && g_pair_auto && M >= 1024 && N >= 512 && K <= 8192 &&
+  if (bn == 0 && stream_k == 0 && g_pair_auto && M >= 1024 && N >= 512 &&
       (int64_t)cdiv(M, 256) * cdiv(N, 256) >= 2ll * (sm_count() / 2))
     use_pair = true;
   if (bn == 0 || bn == 512) bn = use_pair ? PAIR_HALF : pick_bn(M, N);

@@ -103,6 +103,8 @@ def main():
         row["cublas_tflops"] = round(2 * M * N * K / t / 1e9, 1)
         variants = {"auto": dict(), "dp256": dict(bn=256, stream_k=0), "dp128": dict(bn=128, stream_k=0),
                     "dp64": dict(bn=64, stream_k=0), "pair": dict(bn=512, stream_k=0)}
+        if M > 256:  # the same cluster kernel, one 256 x 512 (or 256 x 256) tile per CTA pair
+            variants.update({"sk_n2s1": dict(bn=1021), "sk_n1s1": dict(bn=1011)})
         if M <= 256:  # skinny kernel: 1000 + 10 * accumulators + K splits
             variants.update({"sk_n1s1": dict(bn=1011), "sk_n1s2": dict(bn=1012), "sk_n1s4": dict(bn=1014),
                              "sk_n2s1": dict(bn=1021)})

@@ -68,3 +68,14 @@ def test_skinny_tiled_weight(dev, bn, M, N, K):
     tw = ops.TiledWeight(w)
     assert torch.equal(tw.dense(), w)
     _check(ops.gemm(a, tw, bn=bn), a.float() @ w.float().t())
+
+
+@pytest.mark.parametrize("bn", [1011, 1021, 1012])
+def test_cluster_kernel_many_m_tiles(dev, bn):
+    torch.manual_seed(6)
+    M, N, K = 1100, 1536, 2048
+    a = (torch.randn(M, K, device=dev) * 0.5).to(BF)
+    w = (torch.randn(N, K, device=dev) * 0.1).to(BF)
+    res = torch.randn(M, N, device=dev).to(BF)
+    _check(ops.gemm(a, w, bn=bn), a.float() @ w.float().t())
+    _check(ops.gemm(a, w, epi="residual", residual=res, bn=bn), a.float() @ w.float().t() + res.float())
