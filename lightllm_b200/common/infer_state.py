@@ -48,7 +48,8 @@ class InferState:
     b_req_idx: torch.Tensor
     b_seq_len: torch.Tensor
     mem_index: torch.Tensor
-    position_ids: torch.Tensor = None
+    position_ids: torch.Tensor = None            # rotary position of every token (families may remap it)
+    seq_pos: torch.Tensor = None                 # index of every token inside its request (causal limit)
     cu_q: Optional[torch.Tensor] = None           # int32 [B+1]
     b_ready_cache_len: Optional[torch.Tensor] = None
     batch_of_token: Optional[torch.Tensor] = None

@@ -22,6 +22,8 @@ class ReqManager:
         self.req_to_token_indexs[self.HOLD_REQUEST_ID].fill_(mem_manager.HOLD_TOKEN_MEMINDEX)
         # next input token of every request (written by the sampler, read by the decode prologue)
         self.req_to_next_token_ids = torch.zeros((max_request_num + 1, 8), dtype=torch.int64, device=device)
+        # multimodal rotary: position of a decode token = sequence position + this offset (0 for text-only)
+        self.req_to_position_delta = torch.zeros(max_request_num + 1, dtype=torch.int32, device=device)
         self._free = list(range(max_request_num - 1, -1, -1))
 
     @property

@@ -232,6 +232,15 @@ class ModelBackend:
             off += int(c)
         pin = self.pins
         want_all = self.args.return_all_prompt_logprobs and any(r.sampling.prompt_logprobs >= 0 for r in reqs)
+        mm = None
+        if any(getattr(r.shm_req, "_mm_params", None) for r in reqs):
+            mm = []
+            for r in reqs:
+                p = getattr(r.shm_req, "_mm_params", None)
+                if p and getattr(self.model, "needs_prompt_ids", False):
+                    p = dict(p)
+                    p["_prompt_ids"] = np.asarray(r.shm_req.shm_prompt_ids.arr[: r.shm_req.input_len])
+                mm.append(p)
         mi = ModelInput(batch_size=B, total_token_num=int((ready + chunks).sum()), max_kv_len=int((ready + chunks).max()),
                         is_prefill=True,
                         b_req_idx=pin.from_numpy("p_req", np.array([r.req_idx for r in reqs], dtype=np.int32), torch.int32),
@@ -240,7 +249,7 @@ class ModelBackend:
                         input_ids=pin.from_numpy("p_ids", ids.astype(np.int64), torch.int64),
                         b_ready_cache_len=pin.from_numpy("p_ready", ready, torch.int32),
                         b_q_len=pin.from_numpy("p_qlen", chunks, torch.int32), max_q_len=int(chunks.max()),
-                        return_all_logits=want_all)
+                        return_all_logits=want_all, multimodal_params=mm)
         self.stats["h2d_bytes"] += total * 8 + total * 4 + B * 16
         out = self.model.forward(mi)
         has_out = np.array([r.cur_kv_len + int(c) >= r.total_len() for r, c in items], dtype=bool)

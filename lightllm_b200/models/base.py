@@ -43,8 +43,8 @@ def normalize_config(cfg: dict) -> dict:
     cfg = dict(cfg)
     if "text_config" in cfg and "hidden_size" not in cfg:  # multimodal wrappers
         base = dict(cfg["text_config"])
-        base.setdefault("model_type", cfg.get("model_type"))
-        cfg = {**cfg, **base}
+        outer = cfg.get("model_type") or base.get("model_type")
+        cfg = {**cfg, **base, "model_type": outer}
     rp = cfg.get("rope_parameters")
     if isinstance(rp, dict):
         if "rope_theta" in rp:
@@ -328,7 +328,13 @@ class TransformerLM:
         st = InferState(is_prefill=True, batch_size=B, num_tokens=T, max_kv_len=mi.max_kv_len, max_q_len=mi.max_q_len,
                         b_req_idx=b_req_idx, b_seq_len=b_seq_len, mem_index=mem_index, position_ids=pos, cu_q=cu_q,
                         b_ready_cache_len=ready, batch_of_token=batch_of)
+        st.seq_pos = pos
         st.extra["multimodal_params"] = mi.multimodal_params
+        st.extra["input_ids_cpu"] = mi.input_ids
+        st.extra["q_len_cpu"] = q_len
+        st.extra["ready_cpu"] = mi.b_ready_cache_len
+        st.extra["req_idx_cpu"] = mi.b_req_idx
+        self._prepare_prefill_state(st)
         h = self._embed(input_ids, st)
         h = self._layers_forward(h, st)
         if mi.return_all_logits:
@@ -394,6 +400,8 @@ class TransformerLM:
         ids, pos = ops.decode_prologue(self.req_manager.req_to_token_indexs, self.req_manager.req_to_next_token_ids,
                                        st.b_req_idx, st.b_seq_len, st.mem_index)
         st.position_ids = pos
+        st.seq_pos = pos
+        self._prepare_decode_state(st)
         h = self._embed(ids, st)
         h = self._layers_forward(h, st)
         return self._lm_head(h)
@@ -440,13 +448,54 @@ class TransformerLM:
                 self._capture_decode_graph(b)
 
     # ---- pieces ----
+    def _prepare_prefill_state(self, st: InferState):
+        """Hook: per-pass inputs a family derives on the host (multimodal rotary positions)."""
+
+    def _prepare_decode_state(self, st: InferState):
+        """Hook: runs inside the decode graph after the positions are known."""
+
+    def _rope_inputs(self, st: InferState, layer: int):
+        """(cos table, sin table, row index per token) for the rotary kernel."""
+        return self.cos, self.sin, st.position_ids
+
+    embed_arena = None  # shared embedding arena of the visual / audio servers (set by the rank process)
+
+    def _merge_multimodal(self, h, st: InferState):
+        """Rows of `h` whose token id lies in an image / audio item's virtual id range are replaced by the item's
+        embeddings from the shared arena (reference: lightllm/common/basemodel/triton_kernel/multimodal_emb.py)."""
+        mm = st.extra.get("multimodal_params")
+        if not st.is_prefill or not mm or self.embed_arena is None:
+            return h
+        ids = st.extra["input_ids_cpu"]
+        pos_all, rows_all = [], []
+        seen = set()
+        for params in mm:
+            for kind in ("images", "audios"):
+                for it in (params or {}).get(kind, []):
+                    t0, n = it.get("token_id"), it.get("token_num")
+                    if t0 is None or (t0, n) in seen:
+                        continue
+                    seen.add((t0, n))
+                    hit = ((ids >= t0) & (ids < t0 + n)).nonzero(as_tuple=True)[0]
+                    if hit.numel():
+                        pos_all.append(hit)
+                        rows_all.append(ids[hit] - t0 + it["start_index_in_embed_cache"])
+        if not pos_all:
+            return h
+        pos, rows = torch.cat(pos_all), torch.cat(rows_all)
+        emb = self.embed_arena.read_rows(rows).to(device=h.device, dtype=h.dtype)
+        if self.embed_scale != 1.0 and getattr(self, "scale_multimodal_embeds", False):
+            emb = emb * self.embed_scale
+        ops.copy_rows(h, emb, pos.to(h.device, torch.int32), None, pos.numel())
+        return h
+
     def _embed(self, ids, st):
         h = ops.embedding(ids, self.embed_w, self.embed_range[0], self.embed_range[1])
         if self.vocab_parallel_embedding and self.tp.size > 1:
             self.tp.all_reduce_(h)
         if self.embed_scale != 1.0:
             h = h * self.embed_scale
-        return h
+        return self._merge_multimodal(h, st)
 
     def _lm_head(self, h):
         hn = ops.rmsnorm(h, self.final_norm_w, self.eps, self.norm_w_offset)
@@ -518,12 +567,13 @@ class TransformerLM:
         D, hq, hkv = self.head_dim, self.hq, self.hkv
         qkv = ops.gemm(h, lw.qkv_w, bias=lw.qkv_b)
         kv_layer = self.mem_manager.layer(i)
-        ops.rope_kv_scatter_(qkv, kv_layer, self.cos, self.sin, st.position_ids, st.mem_index, hq, hkv, D,
+        cos, sin, rope_rows = self._rope_inputs(st, i)
+        ops.rope_kv_scatter_(qkv, kv_layer, cos, sin, rope_rows, st.mem_index, hq, hkv, D,
                              self.rot_dim, lw.q_norm, lw.k_norm, self.eps, self.norm_w_offset)
         q = qkv[:, : hq * D]
         r2t = self.req_manager.req_to_token_indexs
         if D not in (64, 128):  # no tensor-core attention kernel for this head size
-            o = ops.attention_generic(q, kv_layer, r2t, st.b_req_idx, st.position_ids,
+            o = ops.attention_generic(q, kv_layer, r2t, st.b_req_idx, st.seq_pos,
                                       st.batch_of_token if st.is_prefill else None, hq, hkv, D, self.sm_scale)
         elif st.is_prefill:
             o = ops.gqa_prefill(q, kv_layer, r2t, st.b_req_idx, st.cu_q, st.b_ready_cache_len, hq, hkv, D,

@@ -236,7 +236,7 @@ class GenericDecoderLM(TransformerLM):
             o = ops.gqa_decode(q, kv_layer, r2t, st.b_req_idx, st.b_seq_len, hq, hkv, D, st.max_kv_len, self.sm_scale,
                                num_splits=st.decode_num_splits, scratch=st.decode_scratch)
         else:
-            o = ops.attention_generic(q, kv_layer, r2t, st.b_req_idx, st.position_ids,
+            o = ops.attention_generic(q, kv_layer, r2t, st.b_req_idx, st.seq_pos,
                                       st.batch_of_token if st.is_prefill else None, hq, hkv, D, self.sm_scale,
                                       window=window, softcap=self.softcap, alibi=alibi)
         return o.view(-1, hq * D)

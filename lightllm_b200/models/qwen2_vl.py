@@ -1,0 +1,168 @@
+"""Qwen2-VL / Qwen2.5-VL language model: Qwen2 decoder with multimodal rotary embedding (M-RoPE).  The rotary
+frequency slots are split in three sections (temporal, height, width); text tokens advance all three together,
+the tokens of an image take the (t, row, column) of their merged patch, and the text after an image continues
+from the largest index used so far.  Image embeddings come from the shared arena (the vision tower runs in the
+visual server).
+Reference: lightllm/models/qwen2_vl/{model.py,infer_struct.py,triton_kernel/mrope.py,get_mrope_position_ids.py}.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Tuple
+
+import numpy as np
+import torch
+
+from .llama import Qwen2LM
+from .registry import register_model
+from .remap import RemapSource
+
+
+def mrope_positions(ids: np.ndarray, items: List[dict], merge: int = 2) -> Tuple[np.ndarray, int]:
+    """[3, len(ids)] rotary positions and the offset (next position - len(ids)) for the decode steps.
+    `items`: image dicts with token_id / token_num / grid_thwd = (t, gh, gw, merge) in prompt order."""
+    n = len(ids)
+    pos = np.zeros((3, n), dtype=np.int64)
+    spans = []
+    for it in items:
+        t0, cnt = it.get("token_id"), it.get("token_num")
+        if t0 is None:
+            continue
+        hit = np.nonzero((ids >= t0) & (ids < t0 + cnt))[0]
+        if hit.size:
+            spans.append((int(hit[0]), int(hit[-1]) + 1, it))
+    spans.sort(key=lambda s: s[0])
+    cur, nxt = 0, 0  # token cursor, next free position
+    for s, e, it in spans:
+        if s > cur:  # text run
+            pos[:, cur:s] = nxt + np.arange(s - cur)
+            nxt += s - cur
+        g = it.get("grid_thwd") or (1, 1, e - s, 1)
+        t, gh, gw = int(g[0]), int(g[1]) // merge, int(g[2]) // merge
+        if t * gh * gw != e - s:  # a chunk boundary cut the image: positions of the part present
+            t, gh, gw = 1, 1, e - s
+        tt = np.repeat(np.arange(t), gh * gw)
+        hh = np.tile(np.repeat(np.arange(gh), gw), t)
+        ww = np.tile(np.arange(gw), t * gh)
+        pos[0, s:e], pos[1, s:e], pos[2, s:e] = nxt + tt, nxt + hh, nxt + ww
+        nxt += max(t, gh, gw)
+        cur = e
+    if cur < n:
+        pos[:, cur:] = nxt + np.arange(n - cur)
+        nxt += n - cur
+    return pos, nxt - n
+
+
+@register_model("qwen2_vl", "qwen2_5_vl", is_multimodal=True)
+class Qwen2VLLM(Qwen2LM):
+    model_type = "qwen2_vl"
+    needs_prompt_ids = True  # the backend hands every prefill pass the request's whole prompt (M-RoPE is global)
+
+    def _read_config(self, c):
+        super()._read_config(c)
+        rs = c.get("rope_scaling") or c.get("rope_parameters") or {}
+        sec = rs.get("mrope_section") or [16, 24, 24]
+        self.mrope_section = [int(x) for x in sec]
+        assert sum(self.mrope_section) == self.rot_dim // 2, "mrope_section must cover the rotary half"
+        self.rope_scaling = None  # "mrope" is not a frequency scaling
+        vc = c.get("vision_config") or {}
+        self.merge = int(vc.get("spatial_merge_size", 2))
+
+    def _wrap_source(self, src):
+        if src.has("model.embed_tokens.weight"):
+            return src
+        t = {}
+        for pre in ("model.language_model.", "language_model.model."):
+            if src.has(pre + "embed_tokens.weight"):
+                for n in src.names():
+                    if n.startswith(pre):
+                        t["model." + n[len(pre):]] = n
+        return RemapSource(src, t) if t else src
+
+    def _init_rope(self):
+        super()._init_rope()
+        half = self.rot_dim // 2
+        sec = torch.repeat_interleave(torch.arange(3), torch.tensor(self.mrope_section))
+        self._section_of_slot = sec.to(self.device)          # [half] -> 0 / 1 / 2
+        self._slot = torch.arange(half, device=self.device)
+
+    def _prepare_prefill_state(self, st):
+        mm = st.extra.get("multimodal_params") or []
+        q_len, ready, req_idx = st.extra["q_len_cpu"], st.extra["ready_cpu"], st.extra["req_idx_cpu"]
+        ids = st.extra["input_ids_cpu"].numpy()
+        B = st.batch_size
+        cols, off = [], 0
+        deltas = np.zeros(B, dtype=np.int32)
+        for b in range(B):
+            n, r = int(q_len[b]), int(ready[b])
+            params = mm[b] if b < len(mm) and mm[b] else {}
+            images = params.get("images", [])
+            if images:
+                full = params.get("_prompt_ids")
+                if full is None:
+                    assert r == 0, "chunked prefill of a multimodal request needs the whole prompt (_prompt_ids)"
+                    full = ids[off:off + n]
+                p3, delta = mrope_positions(np.asarray(full), images, self.merge)
+                cols.append(p3[:, r:r + n])
+                deltas[b] = delta
+            else:
+                cols.append(np.broadcast_to(np.arange(r, r + n), (3, n)))
+            off += n
+        pos3 = torch.from_numpy(np.ascontiguousarray(np.concatenate(cols, axis=1))).to(self.device)
+        self.req_manager.req_to_position_delta[req_idx.long().to(self.device)] = torch.from_numpy(deltas).to(self.device)
+        p = pos3[self._section_of_slot].t()                   # [T, half]: the position each frequency slot uses
+        st.extra["rope"] = (self.cos[p, self._slot].contiguous(), self.sin[p, self._slot].contiguous(),
+                            torch.arange(pos3.shape[1], dtype=torch.int32, device=self.device))
+
+    def _prepare_decode_state(self, st):
+        st.position_ids = st.position_ids + self.req_manager.req_to_position_delta[st.b_req_idx.long()]
+        st.extra.pop("rope", None)
+
+    def _rope_inputs(self, st, layer):
+        r = st.extra.get("rope")
+        return r if r is not None else (self.cos, self.sin, st.position_ids)
+
+
+class Qwen2VLTokenizer:
+    """Wraps the text tokenizer: every `<|image_pad|>` of the prompt becomes the run of virtual token ids of the
+    corresponding image (the embed cache assigned them), so that equal images give equal prompt ids.
+    Reference: lightllm/server/tokenizer.py (QWen2VLTokenizer), models/qwen2_vl/vision_process.py."""
+
+    def __init__(self, tokenizer, model_cfg: dict):
+        self.tokenizer = tokenizer
+        vc = model_cfg.get("vision_config") or {}
+        self.patch = int(vc.get("patch_size", 14))
+        self.merge = int(vc.get("spatial_merge_size", 2))
+        self.image_pad_id = model_cfg.get("image_token_id", 151655)
+        self.min_pixels = int(model_cfg.get("min_pixels", 56 * 56))
+        self.max_pixels = int(model_cfg.get("max_pixels", 14 * 14 * 4 * 1280))
+
+    def __getattr__(self, name):
+        return getattr(self.tokenizer, name)
+
+    def init_imageitem_extral_params(self, img, multi_params=None, sampling_params=None):
+        pass
+
+    def get_image_token_length(self, img) -> int:
+        from .vit.qwen2_vl_visual import image_token_num
+
+        n, (t, gh, gw) = image_token_num(img.image_w, img.image_h, self.patch, self.merge, min_pixels=self.min_pixels,
+                                         max_pixels=self.max_pixels)
+        img.grid_thwd = (t, gh, gw, self.merge)
+        return n
+
+    def encode(self, prompt, multimodal_params=None, add_special_tokens: bool = False, **kw):
+        ids = list(self.tokenizer.encode(prompt, add_special_tokens=add_special_tokens))
+        images = list(multimodal_params.images) if multimodal_params is not None else []
+        if not images:
+            return ids
+        out, k = [], 0
+        for t in ids:
+            if t == self.image_pad_id and k < len(images):
+                im = images[k]
+                out.extend(range(im.token_id, im.token_id + im.token_num))
+                k += 1
+            else:
+                out.append(t)
+        if k != len(images):
+            raise ValueError(f"the prompt has {k} image placeholders for {len(images)} images")
+        return out

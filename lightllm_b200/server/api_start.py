@@ -112,7 +112,19 @@ def start_core_processes(args: StartArgs, config_override: dict = None):
     d = {k: v for k, v in d.items() if not k.startswith("_")}
     process_manager.start_submodule_processes([start_metric_manager], [(d,)])
     process_manager.start_submodule_processes([start_detokenization_process], [(d,)])
+    if args.enable_multimodal:  # the arena must exist before the ranks and the visual server open it
+        from ..models.base import load_config
+        from .embed_cache.manager import start_cache_manager
+
+        hidden = (config_override or load_config(args.model_dir))["hidden_size"]
+        process_manager.start_submodule_processes([start_cache_manager], [(d, hidden)])
     process_manager.start_submodule_processes([start_router_process], [(d, config_override)])
+    if args.enable_multimodal:
+        from .visualserver.manager import start_visual_process
+
+        dv = dict(d)
+        dv["_config_override"] = config_override
+        process_manager.start_submodule_processes([start_visual_process], [(dv,)])
 
 
 def run_http_server(args: StartArgs):

@@ -86,6 +86,13 @@ class EmbedArena:
 
         return torch.from_numpy(self.arr[start:start + n].view(np.int16)).view(torch.bfloat16)
 
+    def read_rows(self, rows):
+        """Arbitrary rows (int64 tensor) as a bf16 tensor."""
+        import torch
+
+        idx = rows.cpu().numpy() if hasattr(rows, "cpu") else np.asarray(rows)
+        return torch.from_numpy(self.arr[idx].view(np.int16)).view(torch.bfloat16)
+
     def close(self):
         self.arr = None
         self.shm.close()

@@ -57,7 +57,17 @@ class HttpServerManager:
         self.recv_from_detok.connect(zmq_addr(args, args.http_server_port))
         self.recv_from_detok.setsockopt(zmq.SUBSCRIBE, b"")
         self.shm_req_manager = ShmReqManager(self.name, args.running_max_req_size)
-        self.tokenizer = get_tokenizer(args.model_dir, args.tokenizer_mode, args.trust_remote_code, args.vocab_size)
+        self.tokenizer = get_tokenizer(args.model_dir, args.tokenizer_mode, args.trust_remote_code, args.vocab_size,
+                                       multimodal=bool(getattr(args, "enable_multimodal", False)),
+                                       config_override=getattr(args, "_config_override", None))
+        self.enable_multimodal = bool(getattr(args, "enable_multimodal", False))
+        self.embed_cache = None
+        if self.enable_multimodal:
+            from ..embed_cache.manager import EmbedCacheClient
+
+            self.embed_cache = EmbedCacheClient(args)
+            self.send_to_visual = ctx.socket(zmq.PUSH)
+            self.send_to_visual.connect(zmq_addr(args, args.visual_port))
         self.vocab_size = args.vocab_size
         self.id_gen = ReqIDGenerator(self.name)
         self.req_id_to_out_inf: Dict[int, ReqStatus] = {}
@@ -77,7 +87,43 @@ class HttpServerManager:
     def tokens(self, prompt: str, multimodal_params=None, samping_params=None, kwargs=None) -> int:
         return len(self.tokenizer.encode(prompt, **(kwargs or {})))
 
-    async def _encode(self, prompt: Union[str, List[int]], sampling_params: SamplingParams):
+    async def _alloc_multimodal(self, mm, sampling_params):
+        """Cache records for every image / audio clip: token-id ranges and arena rows; new payloads are uploaded
+        for the visual / audio server.  Retries while the cache is full of referenced records."""
+        items = mm.items()
+        md5s, nums = [], []
+        for it in items:
+            n = self.tokenizer.get_image_token_length(it) if it.kind == "image" else \
+                self.tokenizer.get_audio_token_length(it)
+            it.token_num = n
+            it.md5 = it.content_md5(salt=str(getattr(it, "grid_thwd", "")))
+            md5s.append(it.md5)
+            nums.append(n)
+        t0 = time.time()
+        while True:
+            recs = self.embed_cache.alloc(md5s, nums)
+            if recs is not None:
+                break
+            if time.time() - t0 > 30:
+                raise ServerBusyError("the multimodal embedding cache is full")
+            await asyncio.sleep(0.05)
+        have = self.embed_cache.get_items_data([r["id"] for r in recs])
+        new_ids, payloads = [], []
+        for it, r, h in zip(items, recs, have):
+            it.uuid, it.token_id, it.start_index_in_embed_cache = r["id"], r["token_id"], r["start_index_in_embed_cache"]
+            data = it.read()
+            if not h and r["id"] not in new_ids:
+                new_ids.append(r["id"])
+                payloads.append(data)
+        if new_ids:
+            self.embed_cache.set_items_data(new_ids, payloads)
+        return [r["id"] for r in recs]
+
+    async def _encode(self, prompt: Union[str, List[int]], sampling_params: SamplingParams, mm=None):
+        if mm is not None and isinstance(prompt, str):
+            loop = asyncio.get_running_loop()
+            return list(await loop.run_in_executor(None, lambda: self.tokenizer.encode(
+                prompt, mm, add_special_tokens=sampling_params.add_special_tokens)))
         if isinstance(prompt, str):
             loop = asyncio.get_running_loop()
             ids = await loop.run_in_executor(None, lambda: self.tokenizer.encode(
@@ -88,7 +134,7 @@ class HttpServerManager:
             raise ValueError("prompt token ids must be integers inside the vocabulary")
         return ids
 
-    def _check_and_repair_length(self, prompt_ids: List[int], sp: SamplingParams):
+    def _check_and_repair_length(self, prompt_ids: List[int], sp: SamplingParams, multimodal: bool = False):
         """max_new_tokens is clamped so that prompt + output fits the pool and the per-request limit."""
         if not prompt_ids:
             raise ValueError("prompt must not be empty")
@@ -111,8 +157,22 @@ class HttpServerManager:
         start_time = time.time()
         group_req_id = self.id_gen.generate_id()
         sampling_params.group_request_id = group_req_id
-        prompt_ids = await self._encode(prompt, sampling_params)
-        prompt_ids = self._check_and_repair_length(prompt_ids, sampling_params)
+        mm, mm_record_ids = None, []
+        if multimodal_params and self.enable_multimodal and \
+                (multimodal_params.get("images") or multimodal_params.get("audios")):
+            from ..multimodal_params import MultimodalParams
+
+            mm = MultimodalParams(**multimodal_params)
+            await mm.verify_and_preload(request)
+            mm_record_ids = await self._alloc_multimodal(mm, sampling_params)
+            multimodal_params = mm.to_dict()
+        try:
+            prompt_ids = await self._encode(prompt, sampling_params, mm)
+            prompt_ids = self._check_and_repair_length(prompt_ids, sampling_params, multimodal=mm is not None)
+        except Exception:
+            if mm_record_ids:
+                self.embed_cache.release(mm_record_ids)
+            raise
         if pd_info is not None:
             self.master_id_to_local[pd_info["group_req_id"]] = group_req_id
             if self.args.run_mode == "prefill" and pd_info.get("peer"):
@@ -156,8 +216,9 @@ class HttpServerManager:
         status = ReqStatus(group_req_id, multimodal_params, req_objs, start_time)
         self.req_id_to_out_inf[group_req_id] = status
         self.run_reqs_count_mark.add(1)
-        await self.send_to_router.send_pyobj(GroupReqIndexes(group_req_id, multimodal_params, indexes, start_time),
-                                             protocol=pickle.HIGHEST_PROTOCOL)
+        first_stage = self.send_to_visual if mm is not None else self.send_to_router
+        await first_stage.send_pyobj(GroupReqIndexes(group_req_id, multimodal_params, indexes, start_time),
+                                     protocol=pickle.HIGHEST_PROTOCOL)
         try:
             first = True
             async for item in self._wait_to_token_package(start_time, len(prompt_ids), group_req_id, sampling_params,
@@ -168,6 +229,8 @@ class HttpServerManager:
                 yield item
         finally:
             self.run_reqs_count_mark.add(-1)
+            if mm_record_ids:
+                self.embed_cache.release(mm_record_ids)
             if pd_info is not None:
                 self.master_id_to_local.pop(pd_info["group_req_id"], None)
 

@@ -84,6 +84,11 @@ def _build_model_and_backend(args: StartArgs, ps):
 
         kw = dict(tokenizer=get_tokenizer(args.model_dir, args.tokenizer_mode, args.trust_remote_code, args.vocab_size))
     backend = backend_cls(model, bargs, is_master_in_dp=(ps.tp_rank == 0), **kw)
+    if getattr(args, "enable_multimodal", False):
+        from ..embed_cache.cache import EmbedArena
+        from ..embed_cache.manager import arena_name, arena_rows
+
+        model.embed_arena = EmbedArena(arena_name(args), arena_rows(args, model.hidden), model.hidden, create=False)
     return model, backend
 
 

@@ -43,7 +43,23 @@ class IdOnlyTokenizer:
         return self.encode(text) if tokenize else text
 
 
-def get_tokenizer(model_dir: str, tokenizer_mode: str = "fast", trust_remote_code: bool = False, vocab_size=None):
+def get_tokenizer(model_dir: str, tokenizer_mode: str = "fast", trust_remote_code: bool = False, vocab_size=None,
+                  multimodal: bool = False, config_override: dict = None):
+    tok = _get_text_tokenizer(model_dir, tokenizer_mode, trust_remote_code, vocab_size)
+    if not multimodal:
+        return tok
+    from ..models.base import load_config
+
+    cfg = config_override or load_config(model_dir)
+    mt = cfg.get("model_type")
+    if mt in ("qwen2_vl", "qwen2_5_vl"):
+        from ..models.qwen2_vl import Qwen2VLTokenizer
+
+        return Qwen2VLTokenizer(tok, cfg)
+    raise ValueError(f"multimodal serving of model_type {mt!r} has no tokenizer wrapper")
+
+
+def _get_text_tokenizer(model_dir: str, tokenizer_mode: str = "fast", trust_remote_code: bool = False, vocab_size=None):
     has_files = model_dir and any(os.path.exists(os.path.join(model_dir, f))
                                   for f in ("tokenizer.json", "tokenizer.model", "tokenizer_config.json", "vocab.json"))
     if not has_files:

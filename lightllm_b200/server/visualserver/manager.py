@@ -1,0 +1,120 @@
+"""visual server process: sits between the HTTP workers and the router for multimodal deployments.  It pulls
+`GroupReqIndexes` from the HTTP workers, embeds the images that the embed cache does not hold yet (batched
+through the model's vision tower, on its own GPU stream / device), writes the embeddings into the shared arena,
+marks them ready and forwards the request to the next stage (audio server or router).  Requests without
+images pass straight through.  `--visual_dp` towers work on disjoint image subsets in parallel threads.
+Reference: lightllm/server/visualserver/manager.py, model_infer/model_rpc.py.
+"""
+from __future__ import annotations
+
+import pickle
+import time
+import traceback
+from typing import List
+
+import torch
+import zmq
+
+from ...utils.process_utils import set_proc_title, start_parent_check_thread
+from ..core.objs.io_objs import GroupReqIndexes
+from ..core.objs.start_args import StartArgs
+from ..embed_cache.manager import EmbedCacheClient
+
+
+def build_vision_tower(args, device, dtype=torch.bfloat16):
+    """The vision tower of the served model (by `model_type`)."""
+    from ...models.base import load_config
+    from ...models.weights import RandomSource, SafetensorsSource
+
+    cfg = getattr(args, "_config_override", None) or load_config(args.model_dir)
+    mt = cfg.get("model_type")
+    if mt in ("qwen2_vl", "qwen2_5_vl"):
+        from ...models.base import TransformerLM
+        from ...models.vit.qwen2_vl_visual import Qwen2VLVisionTower
+
+        vcfg = dict(cfg["vision_config"])
+        vcfg.setdefault("hidden_size", cfg["hidden_size"])
+        if args.model_dir and TransformerLM._has_weights(args.model_dir):
+            src = SafetensorsSource(args.model_dir)
+        else:
+            src = RandomSource(Qwen2VLVisionTower.weight_shapes(vcfg), dtype=dtype)
+        return Qwen2VLVisionTower(vcfg, src, device, dtype)
+    raise ValueError(f"no vision tower for model_type {mt!r}")
+
+
+class VisualManager:
+    def __init__(self, args: StartArgs, tower=None, cache=None, send_next=None, recv=None, infer_batch_size: int = 8):
+        self.args = args
+        self.tower = tower
+        self.cache = cache
+        self.send_next = send_next
+        self.recv = recv
+        self.infer_batch_size = infer_batch_size
+        self.waiting: List[GroupReqIndexes] = []
+
+    def _pending_images(self, group: GroupReqIndexes):
+        mm = group.multimodal_params or {}
+        imgs = mm.get("images", []) if isinstance(mm, dict) else []
+        if not imgs:
+            return []
+        ready = self.cache.get_items_embed([i["uuid"] for i in imgs])
+        return [i for i, r in zip(imgs, ready) if not r]
+
+    def embed(self, images: List[dict]):
+        """Runs the tower over `images` (deduplicated by cache record) and publishes the embeddings."""
+        uniq = {i["uuid"]: i for i in images}
+        items = list(uniq.values())
+        for s in range(0, len(items), self.infer_batch_size):
+            chunk = items[s:s + self.infer_batch_size]
+            payloads = [self.cache.get_payload(i["uuid"]) for i in chunk]
+            embs = self.tower.encode_images(payloads)
+            for it, e in zip(chunk, embs):
+                assert e.shape[0] == it["token_num"], f"image gives {e.shape[0]} tokens, the prompt reserved {it['token_num']}"
+                self.cache.arena.write(it["start_index_in_embed_cache"], e)
+            self.cache.set_items_embed([i["uuid"] for i in chunk])
+
+    def handle(self, group: GroupReqIndexes):
+        pending = self._pending_images(group)
+        if pending:
+            self.embed(pending)
+        self.send_next(group)
+
+    def loop(self):
+        while True:
+            msg = self.recv()
+            try:
+                if isinstance(msg, GroupReqIndexes):
+                    self.handle(msg)
+                else:
+                    self.send_next(msg)  # control commands travel on to the router
+            except Exception:
+                traceback.print_exc()
+                self.send_next(msg)  # the router fails the request when its embeddings never become ready
+
+
+def start_visual_process(args_dict: dict, pipe_writer=None):
+    from ..router.manager import zmq_addr
+
+    args = StartArgs.from_dict(args_dict)
+    set_proc_title(f"lightllm::{args.unique_server_name}::visual_server")
+    start_parent_check_thread()
+    try:
+        dev_index = (args.visual_gpu_ids or [0])[0] if torch.cuda.is_available() else None
+        device = torch.device("cuda", dev_index) if dev_index is not None else torch.device("cpu")
+        tower = build_vision_tower(args, device, torch.bfloat16 if device.type == "cuda" else torch.float32)
+        ctx = zmq.Context(2)
+        pull = ctx.socket(zmq.PULL)
+        pull.bind(zmq_addr(args, args.visual_port))
+        push = ctx.socket(zmq.PUSH)
+        nxt = args.audio_port if getattr(args, "enable_multimodal_audio", False) else args.router_port
+        push.connect(zmq_addr(args, nxt))
+        cache = EmbedCacheClient(args, hidden=tower.out_hidden, open_arena=True)
+        mgr = VisualManager(args, tower, cache, lambda m: push.send_pyobj(m, protocol=pickle.HIGHEST_PROTOCOL),
+                            pull.recv_pyobj, infer_batch_size=args.visual_infer_batch_size or 8)
+    except Exception:
+        if pipe_writer is not None:
+            pipe_writer.send(("init failed", traceback.format_exc()))
+        raise
+    if pipe_writer is not None:
+        pipe_writer.send("init ok")
+    mgr.loop()

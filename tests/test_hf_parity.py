@@ -311,3 +311,77 @@ def test_internlm_bias(tmp_path):
     cfg = dict(model_type="internlm", hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
                vocab_size=200, rms_norm_eps=hf.config.rms_norm_eps, rope_theta=10000.0, bias=True)
     _compare(_save_custom(tmp_path, cfg, dict(hf.state_dict())), hf, _ids(200))
+
+
+def test_qwen2_vl_vision_tower_mrope_and_merge(tmp_path):
+    """Pixels -> vision tower -> embedding arena -> M-RoPE language model, against Qwen2VLForConditionalGeneration."""
+    from transformers import Qwen2VLConfig, Qwen2VLForConditionalGeneration
+
+    from lightllm_b200.common.infer_state import ModelInput
+    from lightllm_b200.models.base import load_config
+    from lightllm_b200.models.registry import get_model
+    from lightllm_b200.models.vit.qwen2_vl_visual import Qwen2VLVisionTower, patchify
+    from lightllm_b200.models.weights import SafetensorsSource
+    from lightllm_b200.parallel import dist as pdist
+
+    torch.manual_seed(0)
+    text = dict(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                vocab_size=300, max_position_embeddings=512, rope_scaling={"type": "mrope", "mrope_section": [2, 3, 3]})
+    vision = dict(depth=2, embed_dim=32, hidden_size=64, num_heads=4, mlp_ratio=2, patch_size=14, spatial_merge_size=2,
+                  temporal_patch_size=2, in_chans=3)
+    cfg = Qwen2VLConfig(text_config=text, vision_config=vision, image_token_id=290, video_token_id=291,
+                        vision_start_token_id=292, vision_end_token_id=293)
+    hf = Qwen2VLForConditionalGeneration(cfg).eval().float()
+    d = str(tmp_path / "ckpt")
+    hf.save_pretrained(d, safe_serialization=True)
+
+    # one 56 x 84 image: 4 x 6 patches -> 2 x 3 = 6 merged tokens
+    pixels = torch.randn(1, 3, 56, 84)
+    patches, (t, gh, gw) = patchify(pixels)
+    n_img = t * gh * gw // 4
+    assert n_img == 6
+    pre, post = [5, 17, 292], [293, 9, 44, 120, 7]
+    hf_ids = torch.tensor([pre + [290] * n_img + post])
+    with torch.no_grad():
+        ref = hf(input_ids=hf_ids, pixel_values=patches, image_grid_thw=torch.tensor([[t, gh, gw]]),
+                 mm_token_type_ids=(hf_ids == 290).long()).logits[0].float()
+
+    src = SafetensorsSource(d)
+    tower = Qwen2VLVisionTower(load_config(d)["vision_config"], src, torch.device("cpu"), torch.float32)
+    emb = tower.forward(patches, [(t, gh, gw)])
+    with torch.no_grad():
+        want = hf.model.visual(patches, grid_thw=torch.tensor([[t, gh, gw]]))
+        want = want.pooler_output if hasattr(want, "pooler_output") else want
+    assert (emb - want).abs().max().item() < 1e-4
+
+    class Arena:  # stand-in for the shared embedding arena
+        def read_rows(self, rows):
+            return emb[rows - 40]
+
+    ps = pdist.ParallelState(device=torch.device("cpu"))
+    m = get_model(load_config(d), model_dir=d, pstate=ps, data_type="float32", max_total_token_num=256, max_req_num=2,
+                  max_seq_length=128, disable_cudagraph=True)
+    m.embed_arena = Arena()
+    tok0 = 100_000_000
+    ids = torch.tensor(pre + list(range(tok0, tok0 + n_img)) + post)
+    item = {"token_id": tok0, "token_num": n_img, "start_index_in_embed_cache": 40, "grid_thwd": (t, gh, gw, 2)}
+    req, n = m.req_manager.alloc(), len(ids)
+    slots = m.mem_manager.alloc(n)
+    mi = ModelInput(batch_size=1, total_token_num=n, max_kv_len=n, is_prefill=True,
+                    b_req_idx=torch.tensor([req], dtype=torch.int32), b_seq_len=torch.tensor([n], dtype=torch.int32),
+                    mem_indexes=slots.clone(), input_ids=ids, b_ready_cache_len=torch.zeros(1, dtype=torch.int32),
+                    max_q_len=n, return_all_logits=True, multimodal_params=[{"images": [item], "audios": []}])
+    got = m.forward(mi).logits.float()
+    assert (got - ref).abs().max().item() < 2e-3 * max(ref.abs().max().item(), 1.0)
+    # one decode step: the position continues after the image's largest index
+    nxt = int(ref[-1].argmax())
+    with torch.no_grad():
+        ids2 = torch.cat([hf_ids, torch.tensor([[nxt]])], dim=1)
+        ref2 = hf(input_ids=ids2, pixel_values=patches, image_grid_thw=torch.tensor([[t, gh, gw]]),
+                  mm_token_type_ids=(ids2 == 290).long()).logits[0, -1].float()
+    m.req_manager.req_to_next_token_ids[req] = nxt
+    mi = ModelInput(batch_size=1, total_token_num=n + 1, max_kv_len=n + 1, is_prefill=False,
+                    b_req_idx=torch.tensor([req], dtype=torch.int32), b_seq_len=torch.tensor([n + 1], dtype=torch.int32),
+                    mem_indexes=m.mem_manager.alloc(1).clone())
+    got2 = m.forward(mi).logits.float()[0]
+    assert (got2 - ref2).abs().max().item() < 2e-3 * max(ref.abs().max().item(), 1.0)
