@@ -41,9 +41,12 @@ def _id_range_source(args):
     return take
 
 
-def serve(cache: EmbedCache, sock, max_calls=None):
+def serve(cache: EmbedCache, sock, max_calls=None, stop=None):
+    """Request loop; `stop` (threading.Event) ends it within 100 ms (the socket is only touched by this thread)."""
     n = 0
-    while max_calls is None or n < max_calls:
+    while (max_calls is None or n < max_calls) and not (stop is not None and stop.is_set()):
+        if not sock.poll(100):
+            continue
         method, a = pickle.loads(sock.recv())
         n += 1
         try:

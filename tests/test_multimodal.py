@@ -98,7 +98,8 @@ def test_visual_manager_embeds_and_forwards():
     cache = EmbedCache(8, rows)
     sock = zmq.Context.instance().socket(zmq.REP)
     sock.bind(f"tcp://127.0.0.1:{port}")
-    th = threading.Thread(target=cm.serve, args=(cache, sock, 12), daemon=True)
+    stop = threading.Event()
+    th = threading.Thread(target=cm.serve, args=(cache, sock, None, stop), daemon=True)
     th.start()
     try:
         client = cm.EmbedCacheClient(args, hidden=24, open_arena=True)
@@ -121,7 +122,10 @@ def test_visual_manager_embeds_and_forwards():
         vm.handle(g)  # already embedded: forwarded without another tower pass (no payload left to read)
         assert len(sent) == 2
         client.arena.close()
+        client.sock.close(0)
     finally:
+        stop.set()
+        th.join(timeout=5)
         arena.close()
         sock.close(0)
 
