@@ -55,6 +55,8 @@ struct GemmParams {
   // W stored as [N/128][K/64][128][64] (every 128-row x 64-column tile is 16 contiguous KB): number of
   // k-blocks per tile row, 0 for the row-major checkpoint layout
   int w_tiled_kb;
+  // same tiling, every tile stored as its 128B-swizzled shared-memory image: loaded with one untiled bulk copy
+  const bf16* w_swz;
 };
 
 template <int BN>
@@ -296,6 +298,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (p.batch_count > 1) {
             tma_load_3d(sa, &tmA, full_bar(stage), kb * BK, mb * BM, batch);
             tma_load_3d(sa + A_BYTES, &tmB, full_bar(stage), kb * BK, w_row0, batch);
+          } else if (p.w_swz != nullptr) {
+            tma_load_2d(sa, &tmA, full_bar(stage), kb * BK, mb * BM);
+#pragma unroll
+            for (int j = 0; j < BN / 128; ++j)
+              bulk_load(sa + A_BYTES + j * 16384,
+                        p.w_swz + ((int64_t)((w_row0 >> 7) + j) * p.w_tiled_kb + kb) * (128 * BK), 16384,
+                        full_bar(stage));
           } else {
             tma_load_2d(sa, &tmA, full_bar(stage), kb * BK, mb * BM);
             tma_load_2d(sa + A_BYTES, &tmB, full_bar(stage), kb * BK, w_row0);
@@ -1120,8 +1129,10 @@ LLB_EXPORT int llb_gemm_bf16(const void* A, int64_t lda, const void* W, int64_t 
     skinny_plan(M, N, K, epi, &sk_nb, &sk_splits, &plan_pair);
     if (plan_pair && ldw >= 0) bn = 512;
   }
-  const bool w_tiled = ldw < 0;  // W is [N/128][K/64][128][64]
+  const bool w_swz = ldw == -2;   // tiled and pre-swizzled (one-CTA kernels, bn 128 / 256)
+  const bool w_tiled = ldw == -1;  // W is [N/128][K/64][128][64]
   if (w_tiled && ((N % 128) || (K % 64) || !sk_nb)) return LLB_ERR_UNSUPPORTED;
+  if (w_swz && ((N % 256) || (K % 64) || sk_nb || (bn != 128 && bn != 256) || stream_k)) return LLB_ERR_UNSUPPORTED;
   if (sk_nb) {
     CUtensorMap ta, tb;
     int rc = cached_tmap(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM);
@@ -1154,9 +1165,14 @@ LLB_EXPORT int llb_gemm_bf16(const void* A, int64_t lda, const void* W, int64_t 
   CUtensorMap ta, tb;
   int rc = cached_tmap(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM);
   if (rc) return rc;
-  rc = cached_tmap(&tb, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, (uint32_t)bn);
+  if (w_swz)
+    tb = ta;  // unused: W comes by untiled bulk copies
+  else
+    rc = cached_tmap(&tb, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, (uint32_t)bn);
   if (rc) return rc;
   GemmParams p;
+  p.w_tiled_kb = w_swz ? K / 64 : 0;
+  p.w_swz = w_swz ? (const bf16*)W : nullptr;
   p.C = C;
   p.residual = (const bf16*)residual;
   p.bias = (const bf16*)bias;

@@ -69,6 +69,13 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap
       "l"(map), "r"(bar), "r"(x), "r"(y)
       : "memory");
 }
+// Untiled bulk copy global -> shared memory of this CTA (both addresses 16-byte aligned, size a multiple of 16),
+// completion counted on an mbarrier of this CTA.  No multicast.
+__device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
 __device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const CUtensorMap* map, uint32_t bar, int x, int y,
                                             int z) {
   asm volatile(

@@ -181,16 +181,24 @@ class TiledWeight:
     the GEMM kernels fetches) is 16 contiguous KB, so that weight streaming reads whole DRAM pages instead of
     128-byte pieces 2K bytes apart."""
 
-    def __init__(self, w: torch.Tensor):
+    def __init__(self, w: torch.Tensor, swizzle: bool = False):
         N, K = w.shape
         assert N % 128 == 0 and K % 64 == 0, "tiled weights need N % 128 == 0 and K % 64 == 0"
         self.N, self.K = N, K
-        self.data = w.view(N // 128, 128, K // 64, 64).permute(0, 2, 1, 3).contiguous().view(-1, 64)
+        self.swizzled = swizzle
+        t = w.view(N // 128, 128, K // 64, 64).permute(0, 2, 1, 3).contiguous()
+        if swizzle:  # the 128B-swizzle shared-memory image: 16-byte chunk c of row r sits at chunk c ^ (r % 8)
+            r = torch.arange(128, device=w.device).view(128, 1)
+            c = torch.arange(8, device=w.device).view(1, 8)
+            idx = (c ^ (r & 7)).view(1, 1, 128, 8, 1).expand(N // 128, K // 64, 128, 8, 8)
+            t = t.view(N // 128, K // 64, 128, 8, 8).gather(3, idx).contiguous()
+        self.data = t.view(-1, 64)
         self.shape = (N, K)
         self.dtype, self.device = w.dtype, w.device
 
     def dense(self) -> torch.Tensor:
         N, K = self.N, self.K
+        assert not self.swizzled
         return self.data.view(N // 128, K // 64, 128, 64).permute(0, 2, 1, 3).reshape(N, K)
 
 
@@ -217,7 +225,7 @@ def gemm(a, w, epi: str = "store", residual=None, bias=None, out=None, bn: int =
     M, K = a.shape
     N = w.shape[0]
     tiled = isinstance(w, TiledWeight)
-    ldw = -1 if tiled else w.stride(0)
+    ldw = (-2 if w.swizzled else -1) if tiled else w.stride(0)
     if tiled:
         w = w.data
     else:

@@ -115,10 +115,15 @@ def main():
             tiled = [ops.TiledWeight(w) for w in ws]
             variants.update({"skt_n1s1": dict(bn=1011, tiled=1), "skt_n1s2": dict(bn=1012, tiled=1),
                              "skt_n1s4": dict(bn=1014, tiled=1), "skt_n2s1": dict(bn=1021, tiled=1)})
+        swz = None
+        if N % 256 == 0 and K % 64 == 0:  # one-CTA kernels with W as pre-swizzled tiles fetched by untiled bulk copies
+            swz = [ops.TiledWeight(w, swizzle=True) for w in ws]
+            variants.update({"swz256": dict(bn=256, tiled=2), "swz128": dict(bn=128, tiled=2)})
         done = []
         for name, kw in variants.items():
             kw = dict(kw)
-            wsel = tiled if kw.pop("tiled", 0) else ws
+            sel = kw.pop("tiled", 0)
+            wsel = swz if sel == 2 else (tiled if sel else ws)
             if kw.get("stream_k") == 1 and ((M + 127) // 128) * ((N + kw["bn"] - 1) // kw["bn"]) > 8192:
                 continue  # more tiles than arrival counters
             if kw.get("bn") == 512 and (M < 256 or N < 256):

@@ -90,3 +90,13 @@ def test_gemm_stream_k_gated(dev):
     want = torch.nn.functional.silu(a.float() @ g.float().t()) * (a.float() @ u.float().t())
     _check(ops.gemm(a, wi, epi="gated_silu", stream_k=1), want, K)
     _check(ops.gemm(a, wi, epi="gated_silu", stream_k=-1), want, K)
+
+
+@pytest.mark.parametrize("bn", [128, 256])
+@pytest.mark.parametrize("M,N,K", [(256, 1024, 4096), (77, 512, 512), (1000, 2048, 1024)])
+def test_gemm_preswizzled_tiled_weight(dev, bn, M, N, K):
+    """W stored as 128B-swizzled 128 x 64 tiles and fetched with untiled bulk copies."""
+    torch.manual_seed(7)
+    a = (torch.randn(M, K, device=dev) * 0.5).to(BF)
+    w = (torch.randn(N, K, device=dev) * 0.1).to(BF)
+    _check(ops.gemm(a, ops.TiledWeight(w, swizzle=True), bn=bn), a.float() @ w.float().t(), K)
