@@ -43,6 +43,10 @@ class BackendArgs:
     return_all_prompt_logprobs: bool = False
     enable_prefill_decode_mixed: bool = False
     pause_recover_interval: int = 100
+    cpu_cache_bytes: int = 0          # > 0: second prefix-cache tier in pinned host memory
+    cpu_cache_page_tokens: int = 256
+    disk_cache_dir: Optional[str] = None
+    disk_cache_bytes: int = 0
 
 
 class PinnedRing:
@@ -104,6 +108,12 @@ class ModelBackend:
         self.radix_cache = None if self.args.disable_dynamic_prompt_cache else \
             RadixCache("radix", model.max_total_token_num, 0, model.mem_manager)
         self.ctx = InferenceContext(model, self.radix_cache)
+        if self.args.cpu_cache_bytes > 0 and self.radix_cache is not None:
+            from .host_kv_cache import HostKVCache
+
+            self.ctx.host_cache = HostKVCache(model.mem_manager, self.args.cpu_cache_bytes,
+                                              self.args.cpu_cache_page_tokens, self.args.disk_cache_dir,
+                                              self.args.disk_cache_bytes, name=f"rank{model.ps.global_rank}")
         self.pins = PinnedRing(pin=self.device.type == "cuda")
         self.control = ControlState(self.args)
         self.is_master_in_dp = is_master_in_dp   # only one rank per replica writes into shm

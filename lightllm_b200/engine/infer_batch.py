@@ -155,6 +155,7 @@ class InferenceContext:
         self.vocab_size = vocab_size or model.vocab
         self.requests: Dict[int, InferReq] = {}
         self.infer_req_ids: List[int] = []
+        self.host_cache = None  # HostKVCache (second prefix-cache tier) when --enable_cpu_cache
 
     # ---- capacity ----
     def get_can_alloc_token_num(self) -> int:
@@ -187,6 +188,7 @@ class InferenceContext:
         ids = req.shm_req.shm_prompt_ids.arr[: max(req.total_len() - 1, 0)]
         node, n, slots = self.radix_cache.match_prefix(ids, update_refs=True)
         if node is None:
+            self._match_host_cache(req, ids, 0)
             return
         req.shared_kv_node = node
         req.shared_len = n
@@ -196,11 +198,45 @@ class InferenceContext:
         self.req_manager.req_to_token_indexs[req.req_idx, :n] = row.to(self.req_manager.device)
         if req.shm_req.prompt_cache_len == 0:
             req.shm_req.prompt_cache_len = n
+        self._match_host_cache(req, ids, n)
+
+    def _match_host_cache(self, req: InferReq, ids, n_gpu: int):
+        """Extend the cached prefix with pages of the host tier: pages from the one containing token n_gpu on."""
+        hc = self.host_cache
+        if hc is None or len(ids) < hc.P:
+            return
+        from .host_kv_cache import page_keys
+
+        keys = page_keys(ids, hc.P)
+        p0 = n_gpu // hc.P
+        m = hc.match(keys, p0)
+        if m == 0 or (p0 + m) * hc.P <= n_gpu:
+            return
+        need = m * hc.P
+        if self.get_can_alloc_token_num() < need + 64:
+            return
+        new = self.alloc_slots(need)
+        hc.load(keys, p0, m, new)
+        new_np = new.numpy().astype(np.int32)
+        skip = n_gpu - p0 * hc.P          # tokens of the first page the GPU tree already covers
+        if skip:
+            self.mem_manager.free(new_np[:skip])
+        use = new_np[skip:]
+        end = (p0 + m) * hc.P
+        req.slots = np.concatenate([req.slots[:n_gpu], use]) if n_gpu else use
+        req.cur_kv_len = end
+        self.req_manager.req_to_token_indexs[req.req_idx, n_gpu:end] = torch.from_numpy(use).to(self.req_manager.device)
+        req.shm_req.cpu_prompt_cache_len = end - n_gpu
+        if req.shm_req.prompt_cache_len < end:
+            req.shm_req.prompt_cache_len = end
 
     # ---- release ----
     def free_a_req_mem(self, req: InferReq):
         """Donate the request's KV to the radix tree (or free it) and drop its tree reference."""
         n = req.cur_kv_len
+        if self.host_cache is not None and n >= self.host_cache.P and not req.paused and \
+                not req.shm_req.sample_params.disable_prompt_cache:
+            self.host_cache.offload(req.shm_req.shm_prompt_ids.arr[:n], req.slots[:n])
         if self.radix_cache is None or req.shm_req.sample_params.disable_prompt_cache:
             own = req.slots[req.shared_len:n]
             if own.size:

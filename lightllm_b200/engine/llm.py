@@ -40,6 +40,10 @@ class LLM:
         if not eos_ids:
             e = config.get("eos_token_id")
             eos_ids = tuple(e) if isinstance(e, (list, tuple)) else ((e,) if e is not None else ())
+        cache_kw = dict(cpu_cache_bytes=int(model_kw.pop("cpu_cache_bytes", 0)),
+                        cpu_cache_page_tokens=int(model_kw.pop("cpu_cache_page_tokens", 256)),
+                        disk_cache_dir=model_kw.pop("disk_cache_dir", None),
+                        disk_cache_bytes=int(model_kw.pop("disk_cache_bytes", 0)))
         tp_fused = model_kw.pop("tp_fused", None)
         if tp_fused is None and self.ps.tp_size > 1 and self.ps.device.type == "cuda" \
                 and not model_kw.pop("disable_fused_tp", False):
@@ -56,7 +60,8 @@ class LLM:
         self.args = BackendArgs(batch_max_tokens=batch_max_tokens,
                                 chunked_prefill_size=chunked_prefill_size or max(batch_max_tokens // 2, 1),
                                 eos_ids=tuple(eos_ids), max_req_total_len=max_req_total_len,
-                                disable_dynamic_prompt_cache=disable_dynamic_prompt_cache)
+                                disable_dynamic_prompt_cache=disable_dynamic_prompt_cache,
+                                **cache_kw)
         self.backend = ModelBackend(self.model, self.args, is_master_in_dp=True)
         self.statics = RouterStatics()
         self.queue = ChunkedPrefillQueue(max_total_tokens=self.model.max_total_token_num,

@@ -61,7 +61,11 @@ def _build_model_and_backend(args: StartArgs, ps):
                         disable_aggressive_schedule=args.disable_aggressive_schedule,
                         disable_dynamic_prompt_cache=args.disable_dynamic_prompt_cache, eos_ids=eos,
                         max_req_total_len=args.max_req_total_len,
-                        return_all_prompt_logprobs=args.enable_prompt_logprobs)
+                        return_all_prompt_logprobs=args.enable_prompt_logprobs,
+                        cpu_cache_bytes=int(args.cpu_cache_storage_size * (1 << 30)) if args.enable_cpu_cache else 0,
+                        cpu_cache_page_tokens=args.cpu_cache_token_page_size,
+                        disk_cache_dir=args.disk_cache_dir if args.enable_disk_cache else None,
+                        disk_cache_bytes=int(args.disk_cache_storage_size * (1 << 30)) if args.enable_disk_cache else 0)
     from ...engine.mode_backends import select_backend_class
 
     backend_cls = select_backend_class(args)
