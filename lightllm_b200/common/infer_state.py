@@ -30,6 +30,8 @@ class ModelInput:
     multimodal_params: Optional[list] = None
     return_all_logits: bool = False      # prompt_logprobs: logits for every prompt position
     b_mtp_index: Optional[torch.Tensor] = None
+    return_hidden: bool = False          # speculative decoding: also return the final residual stream [T, hidden]
+    draft_input_hidden: Optional[torch.Tensor] = None  # draft modules: hidden state of the target model per token
 
 
 @dataclass

@@ -97,7 +97,8 @@ class TransformerLM:
                  max_seq_length: int = 8192, batch_max_tokens: int = 16384, graph_max_batch_size: int = 256,
                  graph_split_batch_size: int = 32, graph_grow_step_size: int = 16, disable_cudagraph: bool = False,
                  graph_max_len_in_batch: Optional[int] = None, tp_fused=None, random_seed: int = 0,
-                 vocab_parallel_embedding: bool = False, num_layers_override: Optional[int] = None, **extra):
+                 vocab_parallel_embedding: bool = False, num_layers_override: Optional[int] = None,
+                 share_with: Optional["TransformerLM"] = None, extra_kv_layers: int = 0, **extra):
         config = normalize_config(config)
         self.config = config
         self.ps = pstate or pdist.state()
@@ -108,6 +109,9 @@ class TransformerLM:
         if self.device.type == "cuda" and self.dtype != torch.bfloat16:
             self.dtype = torch.bfloat16  # the sm_100a kernels are bf16
         self.extra = extra
+        self.share_with = share_with          # draft module: lives on the target model's KV pool / request table
+        self.extra_kv_layers = extra_kv_layers  # pool layers appended for draft modules
+        self.kv_layer_offset = 0
         self._read_config(config)
         if num_layers_override:
             self.num_layers = num_layers_override
@@ -129,8 +133,12 @@ class TransformerLM:
         self.weight_source = weight_source
         self._load_weights(weight_source)
         self._init_rope()
-        self._init_mem(max_total_token_num, mem_fraction)
-        self.req_manager = ReqManager(max_req_num, max_seq_length, self.mem_manager, self.device)
+        if share_with is not None:
+            self.mem_manager, self.req_manager = share_with.mem_manager, share_with.req_manager
+            self.max_total_token_num = share_with.max_total_token_num
+        else:
+            self._init_mem(max_total_token_num, mem_fraction)
+            self.req_manager = ReqManager(max_req_num, max_seq_length, self.mem_manager, self.device)
         self._graphs: Dict[int, dict] = {}
         self._graph_pool = None
         self.weight_version = "default"
@@ -286,10 +294,14 @@ class TransformerLM:
 
     # ------------------------------------------------------------------ memory
     def kv_bytes_per_token(self) -> int:
-        return MemoryManager.bytes_per_token(self.dtype, self.hkv, self.head_dim, self.num_layers)
+        return MemoryManager.bytes_per_token(self.dtype, self.hkv, self.head_dim, self.num_layers + self.extra_kv_layers)
 
     def _make_mem_manager(self, size):
-        return MemoryManager(size, self.dtype, self.hkv, self.head_dim, self.num_layers, self.device)
+        return MemoryManager(size, self.dtype, self.hkv, self.head_dim, self.num_layers + self.extra_kv_layers,
+                             self.device)
+
+    def _kv_layer(self, i: int):
+        return self.mem_manager.layer(self.kv_layer_offset + i)
 
     def _init_mem(self, max_total_token_num, mem_fraction):
         if max_total_token_num is None:
@@ -334,9 +346,11 @@ class TransformerLM:
         st.extra["q_len_cpu"] = q_len
         st.extra["ready_cpu"] = mi.b_ready_cache_len
         st.extra["req_idx_cpu"] = mi.b_req_idx
+        st.extra["draft_input_hidden"] = mi.draft_input_hidden
         self._prepare_prefill_state(st)
         h = self._embed(input_ids, st)
         h = self._layers_forward(h, st)
+        hidden = h if mi.return_hidden else None
         if mi.return_all_logits:
             last = h
         else:
@@ -344,7 +358,7 @@ class TransformerLM:
             last = torch.empty((B, self.hidden), dtype=h.dtype, device=dev)
             ops.copy_rows(last, h, None, last_idx, B)
         logits = self._lm_head(last)
-        return ModelOutput(logits=logits)
+        return ModelOutput(logits=logits, hidden=hidden)
 
     # ---- decode ----
     def graph_batch_sizes(self) -> List[int]:
@@ -566,7 +580,7 @@ class TransformerLM:
     def _attention_block(self, i, lw, h, st: InferState):
         D, hq, hkv = self.head_dim, self.hq, self.hkv
         qkv = ops.gemm(h, lw.qkv_w, bias=lw.qkv_b)
-        kv_layer = self.mem_manager.layer(i)
+        kv_layer = self._kv_layer(i)
         cos, sin, rope_rows = self._rope_inputs(st, i)
         ops.rope_kv_scatter_(qkv, kv_layer, cos, sin, rope_rows, st.mem_index, hq, hkv, D,
                              self.rot_dim, lw.q_norm, lw.k_norm, self.eps, self.norm_w_offset)

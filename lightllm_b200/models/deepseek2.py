@@ -174,10 +174,12 @@ class DeepseekV2LM(TransformerLM):
 
     # ------------------------------------------------------------------ memory
     def kv_bytes_per_token(self):
-        return MLAMemoryManager.bytes_per_token(self.dtype, self.kv_lora, self.rope_d, self.num_layers)
+        return MLAMemoryManager.bytes_per_token(self.dtype, self.kv_lora, self.rope_d,
+                                                self.num_layers + self.extra_kv_layers)
 
     def _make_mem_manager(self, size):
-        return MLAMemoryManager(size, self.dtype, self.kv_lora, self.rope_d, self.num_layers, self.device)
+        return MLAMemoryManager(size, self.dtype, self.kv_lora, self.rope_d, self.num_layers + self.extra_kv_layers,
+                                self.device)
 
     # ------------------------------------------------------------------ layers
     def _make_decode_state(self, B, b_req_idx, b_seq_len, mem_index, max_kv_len, num_splits=None):
@@ -199,7 +201,7 @@ class DeepseekV2LM(TransformerLM):
             q = ops.gemm(h, lw.q_b_w)
             kv_a = ops.gemm(h, lw.kv_a_w)
         q3 = q.view(T, hq, nope + rope)
-        kv_layer = self.mem_manager.layer(i)                      # [slots, 1, kvl + rope]
+        kv_layer = self._kv_layer(i)                      # [slots, 1, kvl + rope]
         ops.mla_rope_kv_scatter_(q3, kv_a, kv_layer, lw.kv_a_norm, self.cos, self.sin, st.position_ids, st.mem_index,
                                  nope, rope, kvl, self.eps)
         q_lat = mla_ops.gemm_batched(q3[:, :, :nope], lw.w_uk)    # [T, hq, kvl]

@@ -219,7 +219,7 @@ class GenericDecoderLM(TransformerLM):
     def _attention_block(self, i, lw, h, st):
         D, hq, hkv = self.head_dim, self.hq, self.hkv
         qkv = ops.gemm(h, lw.qkv_w, bias=lw.qkv_b)
-        kv_layer = self.mem_manager.layer(i)
+        kv_layer = self._kv_layer(i)
         cos, sin = self._rope_tables(i)
         ops.rope_kv_scatter_(qkv, kv_layer, cos, sin, st.position_ids, st.mem_index, hq, hkv, D,
                              self.rot_dim if self.pos_type == "rope" else 0, lw.q_norm, lw.k_norm, self.eps,

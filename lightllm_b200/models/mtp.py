@@ -1,0 +1,107 @@
+"""Multi-token-prediction draft modules (speculative decoding).
+
+A draft module is one extra transformer layer of the target model's family that predicts the token after next:
+its input at position i is `eh_proj([RMSNorm_e(embed(token i+1)) ; RMSNorm_h(target hidden i)])`, it runs one
+decoder layer over its own KV layer (appended to the target model's pool, same slots and request table), and
+`shared_head` (norm + the target's lm_head unless the checkpoint carries its own) gives the logits of token i+2.
+Checkpoints keep the module under `model.layers.{num_hidden_layers + j}.`.
+
+Reference: lightllm/models/deepseek_mtp, qwen3_moe_mtp, mistral_mtp, glm4_moe_lite_mtp (pre_layer_infer.py: the
+enorm / hnorm / eh_proj fusion; model.py: sharing of the memory and request managers).
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from .deepseek2 import DeepseekV2LM
+from .llama import LlamaLM
+from .qwen3_moe import Qwen3MoeLM
+from .remap import RemapSource
+
+
+class MTPMixin:
+    """Mixed into a family class; construct with share_with=<target model>, mtp_index=j."""
+
+    def _read_config(self, c):
+        super()._read_config(c)
+        self.mtp_index = int(self.extra.get("mtp_index", 0))
+        self.target_layers = self.num_layers
+        self.num_layers = 1
+        self.kv_layer_offset = self.target_layers + self.mtp_index
+
+    def _module_prefix(self):
+        return f"model.layers.{self.target_layers + self.mtp_index}."
+
+    def weight_shapes(self):
+        s = super().weight_shapes()
+        H = self.hidden
+        s.update({"model.layers.0.enorm.weight": (H,), "model.layers.0.hnorm.weight": (H,),
+                  "model.layers.0.eh_proj.weight": (H, 2 * H), "model.layers.0.shared_head.norm.weight": (H,)})
+        return s
+
+    def _wrap_source(self, src):
+        pre = self._module_prefix()
+        t = {}
+        for n in src.names():
+            if n.startswith(pre):
+                t["model.layers.0." + n[len(pre):]] = n
+        t["model.norm.weight"] = pre + "shared_head.norm.weight"
+        if src.has(pre + "embed_tokens.weight"):
+            t["model.embed_tokens.weight"] = pre + "embed_tokens.weight"
+        if src.has(pre + "shared_head.head.weight"):
+            t["lm_head.weight"] = pre + "shared_head.head.weight"
+        return RemapSource(src, t)
+
+    def _load_weights(self, src):
+        if not src.has("model.norm.weight"):      # random-init source: canonical names
+            src = RemapSource(src, {"model.norm.weight": "model.layers.0.shared_head.norm.weight"})
+        super()._load_weights(src)
+        main = self.share_with
+        if main is not None:                      # one copy of the big tables
+            if self.embed_w.shape == main.embed_w.shape:
+                self.embed_w, self.embed_range = main.embed_w, main.embed_range
+            if self.lm_head_w.shape == main.lm_head_w.shape:
+                self.lm_head_w = main.lm_head_w
+        p = "model.layers.0."
+        self.enorm_w = self._dev(src.get(p + "enorm.weight"))
+        self.hnorm_w = self._dev(src.get(p + "hnorm.weight"))
+        self.eh_proj_w = self._dev(src.get(p + "eh_proj.weight"))
+
+    def _embed(self, ids, st):
+        e = super()._embed(ids, st)
+        prev = st.extra.get("draft_input_hidden")
+        assert prev is not None and prev.shape[0] == e.shape[0], "a draft module needs the target's hidden states"
+        cat = torch.cat([ops.rmsnorm(e, self.enorm_w, self.eps), ops.rmsnorm(prev.to(e.dtype), self.hnorm_w, self.eps)],
+                        dim=-1)
+        return ops.gemm(cat, self.eh_proj_w)
+
+
+class DeepseekV3MTP(MTPMixin, DeepseekV2LM):
+    def _is_moe_layer(self, i):
+        return self.moe is not None   # the module's layer follows the target's last (MoE) layer
+
+
+class Qwen3MoeMTP(MTPMixin, Qwen3MoeLM):
+    pass
+
+
+class LlamaMTP(MTPMixin, LlamaLM):
+    pass
+
+
+MTP_CLASSES = {"deepseek_v3": DeepseekV3MTP, "deepseek_v2": DeepseekV3MTP, "glm4_moe_lite": DeepseekV3MTP,
+               "kimi_k2": DeepseekV3MTP, "qwen3_moe": Qwen3MoeMTP, "mistral": LlamaMTP, "llama": LlamaMTP}
+
+
+def build_mtp_modules(main, n_modules: int, model_dir=None, weight_source=None, **kw):
+    """Draft modules 0..n-1 of `main` (which must have been built with extra_kv_layers >= n)."""
+    cls = MTP_CLASSES.get(main.config.get("model_type"))
+    if cls is None:
+        raise ValueError(f"no multi-token-prediction module for model_type {main.config.get('model_type')!r}")
+    assert main.extra_kv_layers >= n_modules, "build the target model with extra_kv_layers = number of draft modules"
+    extra = {k: v for k, v in main.extra.items() if k != "mtp_index"}
+    return [cls(main.config, model_dir=model_dir, weight_source=weight_source, pstate=main.ps,
+                data_type=str(main.dtype).replace("torch.", ""), max_req_num=main.max_req_num,
+                max_seq_length=main.max_seq_length, batch_max_tokens=main.batch_max_tokens, disable_cudagraph=True,
+                share_with=main, mtp_index=j, random_seed=1000 + j, **{**extra, **kw}) for j in range(n_modules)]

@@ -30,6 +30,13 @@ class ExitCmd:
     pass
 
 
+def _mtp_modules(args) -> int:
+    """Draft modules to build: one per step for the vanilla modes, one reused module for the eagle modes."""
+    if not getattr(args, "mtp_mode", None):
+        return 0
+    return 1 if str(args.mtp_mode).startswith("eagle") else max(1, int(args.mtp_step))
+
+
 def _build_model_and_backend(args: StartArgs, ps):
     from ...engine.backend import BackendArgs, ModelBackend
     from ...models.base import load_config
@@ -52,7 +59,8 @@ def _build_model_and_backend(args: StartArgs, ps):
                       graph_split_batch_size=args.graph_split_batch_size,
                       graph_grow_step_size=args.graph_grow_step_size,
                       graph_max_len_in_batch=args.graph_max_len_in_batch or None, tp_fused=fused,
-                      enable_ep_moe=args.enable_ep_moe, quant_type=args.quant_type)
+                      enable_ep_moe=args.enable_ep_moe, quant_type=args.quant_type,
+                      extra_kv_layers=_mtp_modules(args))
     eos = args.eos_ids or args.eos_id or cfg.get("eos_token_id") or []
     eos = tuple(eos) if isinstance(eos, (list, tuple)) else (eos,)
     bargs = BackendArgs(batch_max_tokens=args.batch_max_tokens, chunked_prefill_size=args.chunked_prefill_size,
@@ -87,7 +95,14 @@ def _build_model_and_backend(args: StartArgs, ps):
         from ..tokenizer import get_tokenizer
 
         kw = dict(tokenizer=get_tokenizer(args.model_dir, args.tokenizer_mode, args.trust_remote_code, args.vocab_size))
-    backend = backend_cls(model, bargs, is_master_in_dp=(ps.tp_rank == 0), **kw)
+    if _mtp_modules(args):
+        from ...engine.mtp_backend import MTPBackend
+        from ...models.mtp import build_mtp_modules
+
+        drafts = build_mtp_modules(model, _mtp_modules(args), model_dir=args.mtp_draft_model_dir or args.model_dir)
+        backend = MTPBackend(model, bargs, draft_models=drafts, mtp_step=args.mtp_step, is_master_in_dp=(ps.tp_rank == 0))
+    else:
+        backend = backend_cls(model, bargs, is_master_in_dp=(ps.tp_rank == 0), **kw)
     if getattr(args, "enable_multimodal", False):
         from ..embed_cache.cache import EmbedArena
         from ..embed_cache.manager import arena_name, arena_rows
