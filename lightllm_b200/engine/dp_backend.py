@@ -1,0 +1,86 @@
+"""Data-parallel attention: every replica (a tensor-parallel group; a single rank when --dp equals the world
+size) serves its own requests with its own KV pool and prefix tree, but all ranks of the world step together,
+because the expert-parallel MoE layers exchange tokens between all of them.  Before each step the ranks
+all-gather (prefill tokens, decode requests) on the host group: if anyone prefills, everybody runs a prefill
+pass; else if anyone decodes, everybody decodes; a rank with nothing of that kind runs the pass on the HOLD
+request (one dummy token, HOLD KV slot) so that it still takes part in the exchanges.
+Reference: mode_backend/dp_backend/impl.py:97-152, base_backend.py:933-959.
+"""
+from __future__ import annotations
+
+import time
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from ..common.infer_state import ModelInput
+from .backend import ModelBackend
+
+
+class DPBackend(ModelBackend):
+    def __init__(self, *a, idle_sleep_s: float = 0.001, **kw):
+        super().__init__(*a, **kw)
+        self.ps = self.model.ps
+        self.idle_sleep_s = idle_sleep_s
+        self.stats.update({"hold_prefill": 0, "hold_decode": 0})
+
+    def has_work(self) -> bool:
+        return True  # the agreement inside step() decides; every rank must keep calling step()
+
+    def _agree(self, n_prefill_tokens: int, n_decode: int):
+        mine = torch.tensor([n_prefill_tokens, n_decode, len(self.ctx.requests)], dtype=torch.int64)
+        if self.ps.world_size == 1 or self.ps.cpu_group is None:
+            return mine.view(1, 3)
+        allv = torch.empty(self.ps.world_size * 3, dtype=torch.int64)
+        dist.all_gather_into_tensor(allv, mine, group=self.ps.cpu_group)
+        return allv.view(self.ps.world_size, 3)
+
+    def _hold_input(self, is_prefill: bool) -> ModelInput:
+        rm, mm = self.model.req_manager, self.model.mem_manager
+        one = torch.ones(1, dtype=torch.int32)
+        kw = dict(batch_size=1, total_token_num=1, max_kv_len=1, is_prefill=is_prefill,
+                  b_req_idx=torch.tensor([rm.HOLD_REQUEST_ID], dtype=torch.int32), b_seq_len=one,
+                  mem_indexes=torch.tensor([mm.HOLD_TOKEN_MEMINDEX], dtype=torch.int32))
+        if is_prefill:
+            kw.update(input_ids=torch.zeros(1, dtype=torch.int64), b_ready_cache_len=torch.zeros(1, dtype=torch.int32),
+                      b_q_len=one, max_q_len=1)
+        return ModelInput(**kw)
+
+    @torch.no_grad()
+    def step(self) -> dict:
+        self._steps += 1
+        prefill, decode, finished = self._get_classed_reqs()
+        local_kind = self.control.select(len(prefill), len(decode))
+        votes = self._agree(sum(c for _, c in prefill) if local_kind == "prefill" else 0,
+                            len(decode) if local_kind == "decode" else 0)
+        any_prefill, any_decode = bool((votes[:, 0] > 0).any()), bool((votes[:, 1] > 0).any())
+        n_tok, kind = 0, "idle"
+        if any_prefill:
+            kind = "prefill"
+            if local_kind == "prefill":
+                n_tok = self._run_prefill(prefill)
+            else:
+                self.model.forward(self._hold_input(True))
+                self.stats["hold_prefill"] += 1
+        elif any_decode:
+            kind = "decode"
+            if local_kind == "decode":
+                n_tok = self._run_decode(decode)
+            else:
+                self.model.forward(self._hold_input(False))
+                self.stats["hold_decode"] += 1
+        else:
+            time.sleep(self.idle_sleep_s)
+        for req in list(self.ctx.requests.values()):
+            if req.finish_status.is_finished() and req not in finished:
+                finished.append(req)
+        for req in finished:
+            self.ctx.remove_req(req)
+        return {"kind": kind, "finished": finished, "tokens": n_tok, "world_busy": bool((votes[:, 2] > 0).any())}
+
+    def drain(self):
+        """Keep stepping (holding) until no rank has a live request: a rank that finished early must stay in the
+        exchanges of the others.  Every rank sees the same votes, so all of them leave on the same step."""
+        while self.step()["world_busy"]:
+            pass

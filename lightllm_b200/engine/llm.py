@@ -62,7 +62,12 @@ class LLM:
                                 eos_ids=tuple(eos_ids), max_req_total_len=max_req_total_len,
                                 disable_dynamic_prompt_cache=disable_dynamic_prompt_cache,
                                 **cache_kw)
-        self.backend = ModelBackend(self.model, self.args, is_master_in_dp=True)
+        if self.ps.dp_size > 1:
+            from .dp_backend import DPBackend
+
+            self.backend = DPBackend(self.model, self.args, is_master_in_dp=self.ps.tp_rank == 0)
+        else:
+            self.backend = ModelBackend(self.model, self.args, is_master_in_dp=True)
         self.statics = RouterStatics()
         self.queue = ChunkedPrefillQueue(max_total_tokens=self.model.max_total_token_num,
                                          batch_max_tokens=batch_max_tokens, running_max_req_size=running_max_req_size,
@@ -151,6 +156,8 @@ class LLM:
                 o["token_times"] = token_times[r.request_id]
             outs.append(o)
             r.release_shm_arrays()
+        if hasattr(self.backend, "drain"):
+            self.backend.drain()
         if return_stats:
             return outs, {"steps": step_log, "backend": dict(self.backend.stats)}
         return outs

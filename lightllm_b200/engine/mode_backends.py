@@ -278,6 +278,10 @@ class PDDecodeBackend(ModelBackend):
 
 
 def select_backend_class(args):
+    if int(getattr(args, "dp", 1) or 1) > 1:
+        from .dp_backend import DPBackend
+
+        return DPBackend
     if getattr(args, "run_mode", "normal") == "prefill":
         return PDPrefillBackend
     if getattr(args, "run_mode", "normal") == "decode":

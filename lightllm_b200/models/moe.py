@@ -58,6 +58,9 @@ def expert_weight_shapes(prefix: str, mc: MoEConfig, hidden: int, gate_name="gat
 def load_experts(model, lw, src, prefix: str, mc: MoEConfig, ep: bool, gate_name="gate", experts_name="experts"):
     """Fills lw.router_w (fp32 logits GEMM runs in bf16 weights), lw.w13, lw.w2, lw.e0, lw.e_local (+ shared expert)."""
     tp, r = model.tp.size, model.tp.rank
+    if ep and model.ps.dp_size > 1:  # data-parallel attention: the experts are spread over every rank of the world
+        assert model.ps.tp_size == 1, "expert parallelism under --dp needs --dp equal to the world size"
+        tp, r = model.ps.world_size, model.ps.global_rank
     dev = model._dev
     lw.router_w = dev(src.get(prefix + f"{gate_name}.weight"))
     if mc.has_bias and src.has(prefix + f"{gate_name}.e_score_correction_bias"):
@@ -78,6 +81,7 @@ def load_experts(model, lw, src, prefix: str, mc: MoEConfig, ep: bool, gate_name
     lw.w13 = dev(torch.stack(w13))
     lw.w2 = dev(torch.stack(w2))
     lw.e0 = e0 if (ep and tp > 1) else 0
+    lw.ep_world = tp if ep else 1
     lw.is_moe = True
     if mc.n_shared:
         model._load_dense_ffn(lw, src, prefix + "shared_experts.", mc.shared_inter)
@@ -104,5 +108,22 @@ def moe_ffn(model, lw, h, mc: MoEConfig):
             act = ops.gated_act(ops.gemm(h, lw.shared_gate_up_w), mc.act)
         ops.gemm(act, lw.shared_down_w, out=out)
         accumulate = True
+    epg = ep_group_of(model, mc)
+    if epg is not None:
+        epg.moe(h, ids, w, lambda hr, ir, wr, o: moe_ops.fused_experts(hr, lw.w13, lw.w2, ir, wr, mc.act, lw.e0, out=o),
+                out=out, accumulate=accumulate)
+        return out
     moe_ops.fused_experts(h, lw.w13, lw.w2, ids, w, mc.act, lw.e0, out=out, accumulate=accumulate)
     return out
+
+
+def ep_group_of(model, mc: MoEConfig):
+    """The token exchange of a data-parallel + expert-parallel model (created on first use), else None."""
+    if not (getattr(model, "ep", False) and model.ps.dp_size > 1 and model.ps.world_size > 1):
+        return None
+    g = getattr(model, "_ep_group", None)
+    if g is None:
+        from ..parallel.ep import EPGroup
+
+        g = model._ep_group = EPGroup(model.ps, model.hidden, mc.top_k, mc.num_experts, model.batch_max_tokens)
+    return g

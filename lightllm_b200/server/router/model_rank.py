@@ -99,7 +99,10 @@ def _build_model_and_backend(args: StartArgs, ps):
         from ...engine.mtp_backend import MTPBackend
         from ...models.mtp import build_mtp_modules
 
-        drafts = build_mtp_modules(model, _mtp_modules(args), model_dir=args.mtp_draft_model_dir or args.model_dir)
+        draft_dir = args.mtp_draft_model_dir
+        if isinstance(draft_dir, (list, tuple)):
+            draft_dir = draft_dir[0] if draft_dir else None
+        drafts = build_mtp_modules(model, _mtp_modules(args), model_dir=draft_dir or args.model_dir)
         backend = MTPBackend(model, bargs, draft_models=drafts, mtp_step=args.mtp_step, is_master_in_dp=(ps.tp_rank == 0))
     else:
         backend = backend_cls(model, bargs, is_master_in_dp=(ps.tp_rank == 0), **kw)
