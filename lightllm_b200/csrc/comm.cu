@@ -62,6 +62,12 @@ struct CommParams {
   int do_norm;  // 0: plain all-reduce (out = sum over ranks, residual untouched)
   int rows_per_chunk;  // two-shot: owned rows reduced and flagged together (about 1024 vectors of 16 bytes)
   int max_chunks;      // flag slots per owner rank in every rank's flag array
+  // pushed mode (one_shot == 2): the producing GEMMs of all ranks stored their partial tiles into this rank's
+  // gather slots (partial[q] are LOCAL here) and advance push_cnt[q * push_max_mb + row / 128] by the columns
+  // stored; a 128-row block is complete when every rank's counter reached (*push_epoch + 1) * H.
+  const uint32_t* push_cnt[MAX_WORLD];  // per emulated rank: that rank's local counter array
+  uint32_t* push_epoch[MAX_WORLD];      // per emulated rank: rounds finished on this buffer
+  int push_max_mb;
 };
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
@@ -181,16 +187,20 @@ __global__ void __launch_bounds__(256) tp_reduce_norm_kernel(const CommParams p)
   const uint32_t epoch = *me.epoch + 1;  // this call
   const int G = gridDim.x;
 
-  // ---- announce: my partial (written by the GEMM that ran before this kernel) is complete ----
-  if (blockIdx.x == 0 && threadIdx.x < world) {
-    __threadfence_system();
-    st_release_sys(me.ready[threadIdx.x] + me.rank, epoch);
+  const bool pushed = p.one_shot == 2;
+  const uint32_t push_target = pushed ? (*(volatile uint32_t*)p.push_epoch[blockIdx.y] + 1u) * (uint32_t)H : 0u;
+  if (!pushed) {
+    // ---- announce: my partial (written by the GEMM that ran before this kernel) is complete ----
+    if (blockIdx.x == 0 && threadIdx.x < world) {
+      __threadfence_system();
+      st_release_sys(me.ready[threadIdx.x] + me.rank, epoch);
+    }
+    // ---- wait for every peer's partial ----
+    if (threadIdx.x < world) wait_flag(me.ready[me.rank] + threadIdx.x, epoch, me.status, 100 + threadIdx.x);
+    __syncthreads();
   }
-  // ---- wait for every peer's partial ----
-  if (threadIdx.x < world) wait_flag(me.ready[me.rank] + threadIdx.x, epoch, me.status, 100 + threadIdx.x);
-  __syncthreads();
 
-  if (!p.one_shot) {
+  if (p.one_shot == 0) {
     if (world <= 2)
       two_shot_phase1<2>(p, me, epoch);
     else if (world <= 4)
@@ -201,7 +211,13 @@ __global__ void __launch_bounds__(256) tp_reduce_norm_kernel(const CommParams p)
 
   // ---- phase 2: residual add + RMSNorm over all rows (one-shot: reduce here from the peers) ----
   for (int row = blockIdx.x; row < T; row += G) {
-    if (!p.one_shot) {
+    if (pushed) {
+      if (threadIdx.x < world)
+        wait_flag(p.push_cnt[blockIdx.y] + threadIdx.x * p.push_max_mb + (row >> 7), push_target, me.status,
+                  600 + threadIdx.x);
+      __syncthreads();
+    }
+    if (p.one_shot == 0) {
       if (threadIdx.x == 0) {
         const int owner = row % world, chunk = (row / world) / p.rows_per_chunk;
         s_ok = wait_flag(me.rowflag[me.rank] + owner * p.max_chunks + chunk, epoch, me.status, 200) ? 1 : 0;
@@ -263,6 +279,7 @@ __global__ void __launch_bounds__(256) tp_reduce_norm_kernel(const CommParams p)
       *me.arrive = 0;
       __threadfence();
       *me.epoch = epoch;
+      if (pushed) *p.push_epoch[blockIdx.y] = *p.push_epoch[blockIdx.y] + 1u;
     }
   }
 }
@@ -328,7 +345,8 @@ LLB_EXPORT int llb_ipc_close_handle(void* p) { return (int)cudaIpcCloseMemHandle
 LLB_EXPORT int llb_tp_reduce_norm(const void** partial, void** sums, void** ready, void** rowflag, void** residual,
                                   void** out, const void* norm_w, void** epoch, void** arrive, int* status, int rank,
                                   int world, int emulate_ranks, int T, int H, float eps, float w_offset, int one_shot,
-                                  int do_norm, int ctas, int max_chunks, cudaStream_t st) {
+                                  int do_norm, int ctas, int max_chunks, void** push_cnt, void** push_epoch,
+                                  int push_max_mb, cudaStream_t st) {
   if (T <= 0) return LLB_OK;
   CommParams p;
   memset(&p, 0, sizeof(p));
@@ -341,6 +359,8 @@ LLB_EXPORT int llb_tp_reduce_norm(const void** partial, void** sums, void** read
   p.do_norm = do_norm;
   p.rows_per_chunk = (H / 8) >= 1024 ? 1 : 1024 / (H / 8);
   p.max_chunks = max_chunks;
+  p.push_max_mb = push_max_mb;
+  if (one_shot == 2 && (push_cnt == nullptr || push_epoch == nullptr || push_max_mb < cdiv(T, 128))) return LLB_ERR_BAD_ARG;
   const int nr = emulate_ranks > 1 ? emulate_ranks : 1;
   for (int r = 0; r < nr; ++r) {
     RankView& v = p.v[r];
@@ -357,6 +377,8 @@ LLB_EXPORT int llb_tp_reduce_norm(const void** partial, void** sums, void** read
     v.arrive = (uint32_t*)arrive[r];
     v.status = status;
     v.rank = emulate_ranks > 1 ? r : rank;
+    p.push_cnt[r] = one_shot == 2 ? (const uint32_t*)push_cnt[r] : nullptr;
+    p.push_epoch[r] = one_shot == 2 ? (uint32_t*)push_epoch[r] : nullptr;
   }
   return launch(p, nr, ctas, st);
 }

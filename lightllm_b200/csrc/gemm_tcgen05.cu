@@ -57,6 +57,13 @@ struct GemmParams {
   int w_tiled_kb;
   // same tiling, every tile stored as its 128B-swizzled shared-memory image: loaded with one untiled bulk copy
   const bf16* w_swz;
+  // fused all-gather of the output over NVLink peer memory (tensor-parallel partial sums): with push_world > 0 the
+  // bf16 tile is stored into every rank's gather slot of this rank (push[q], same row pitch ldc) instead of C, and
+  // after a CTA has stored a tile it adds the tile's column count to counter [push_rank * push_max_mb + row / 128]
+  // on every rank (release, system scope): a consumer that sees N columns for a 128-row block may read it.
+  bf16* push[8];
+  uint32_t* push_cnt[8];
+  int push_world, push_rank, push_max_mb;
 };
 
 template <int BN>
@@ -120,6 +127,20 @@ __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int 
   int in = tile - grp * per_group;
   mb = first_m + in % gsz;
   nb = in / gsz;
+}
+
+// Called by the four epilogue warps (threads 64..191) after they stored a tile of `ncols` valid columns of the
+// 128-row block `row_block`: makes the peer stores visible and advances the block's column counter on every rank.
+__device__ __forceinline__ void push_signal(const GemmParams& p, int row_block, int ncols) {
+  if (p.push_world <= 0) return;
+  __threadfence_system();
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+  if (threadIdx.x == 64 && ncols > 0 && row_block < p.push_max_mb) {
+    for (int q = 0; q < p.push_world; ++q)
+      asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p.push_cnt[q] + p.push_rank * p.push_max_mb + row_block),
+                   "r"((uint32_t)ncols)
+                   : "memory");
+  }
 }
 
 // Drains one accumulator tile (this thread's row, BN columns starting at TMEM address t_row) through the
@@ -207,7 +228,15 @@ __device__ __forceinline__ void epilogue_store(const GemmParams& p, uint32_t t_r
 #pragma unroll
                 for (int e = 0; e < 8; ++e) o[e] += rv[e];
               }
-              *reinterpret_cast<bf16x8*>(crow + j) = pack8(o);
+              if (EPI == EPI_STORE && p.push_world > 0) {
+                const bf16x8 packed = pack8(o);
+                const int64_t off = (int64_t)row * p.ldc + col0 + j;
+#pragma unroll
+                for (int q = 0; q < 8; ++q)
+                  if (q < p.push_world) *reinterpret_cast<bf16x8*>(p.push[q] + off) = packed;
+              } else {
+                *reinterpret_cast<bf16x8*>(crow + j) = pack8(o);
+              }
             }
           } else {
 #pragma unroll
@@ -444,6 +473,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           epilogue_store<BN, EPI>(pb, t_row, row, row_ok, nb * BN, false, add_partials);
         } else {
           epilogue_store<BN, EPI>(p, t_row, row, row_ok, nb * BN, n_other != 0, add_partials);
+          if (EPI == EPI_STORE) push_signal(p, mb, min(BN, p.N - nb * BN));
         }
       }
       // accumulator drained: hand it back to the MMA warp
@@ -683,6 +713,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       const int row = mb * 256 + (int)cta * BM + erow;
       const uint32_t t_row = tmem_base + ((uint32_t)(lane_grp * 32) << 16) + acc * PAIR_BN;
       epilogue_store<PAIR_BN, EPI>(p, t_row, row, row < p.M, nb * PAIR_BN, false, [](uint32_t*, int) {});
+      if (EPI == EPI_STORE) push_signal(p, mb * 2 + (int)cta, min(PAIR_BN, p.N - nb * PAIR_BN));
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(tempty_leader + 8 * acc);
@@ -906,6 +937,7 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
 #pragma unroll
       for (int j = 0; j < NB; ++j)
         epilogue_store<256, EPI>(p, t_row + j * 256, row, row < p.M, n0 + j * 256, false, [](uint32_t*, int) {});
+      if (EPI == EPI_STORE) push_signal(p, mb * 2 + (int)half, max(0, min(256 * NB, p.N - n0)));
     } else {
       float* R = reinterpret_cast<float*>(smem_gen) + (size_t)erow * SK_RSTRIDE;
 #pragma unroll 1
@@ -972,8 +1004,29 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
           }
           bf162 o0 = __floats2bfloat162_rn(acc.x, acc.y), o1 = __floats2bfloat162_rn(acc.z, acc.w);
           uint2 packed = make_uint2(*reinterpret_cast<uint32_t*>(&o0), *reinterpret_cast<uint32_t*>(&o1));
-          *reinterpret_cast<uint2*>((bf16*)p.C + (int64_t)grow * p.ldc + gcol) = packed;
+          if (EPI == EPI_STORE && p.push_world > 0) {
+            const int64_t off = (int64_t)grow * p.ldc + gcol;
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              if (q < p.push_world) *reinterpret_cast<uint2*>(p.push[q] + off) = packed;
+          } else {
+            *reinterpret_cast<uint2*>((bf16*)p.C + (int64_t)grow * p.ldc + gcol) = packed;
+          }
         }
+      }
+    }
+    if (EPI == EPI_STORE && p.push_world > 0) {  // this CTA wrote its column slice of its 128 rows
+      __threadfence_system();
+      __syncthreads();
+      const int c0 = n0 + (int)split * W;
+      const int valid = max(0, min(W, p.N - c0));
+      const int row_block = mb * 2 + (int)half;
+      if (threadIdx.x == 0 && valid > 0 && row_block < p.push_max_mb) {
+        for (int q = 0; q < p.push_world; ++q)
+          asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p.push_cnt[q] + p.push_rank * p.push_max_mb +
+                                                                          row_block),
+                       "r"((uint32_t)valid)
+                       : "memory");
       }
     }
   }
@@ -1071,12 +1124,43 @@ void skinny_plan(int M, int N, int K, int epi, int* nb, int* splits, bool* use_p
 }
 
 bool g_skinny_auto = true;
+
+// one-shot configuration of the next llb_gemm_bf16 call (set by llb_gemm_set_push, cleared by the call)
+struct PushCfg {
+  bf16* push[8];
+  uint32_t* cnt[8];
+  int world, rank, max_mb;
+} g_push = {{nullptr}, {nullptr}, 0, 0, 0};
+
+void apply_push(GemmParams& p) {
+  p.push_world = g_push.world;
+  p.push_rank = g_push.rank;
+  p.push_max_mb = g_push.max_mb;
+  for (int q = 0; q < 8; ++q) {
+    p.push[q] = g_push.push[q];
+    p.push_cnt[q] = g_push.cnt[q];
+  }
+  g_push.world = 0;
+}
 bool g_pair_auto = true;  // measured faster than one-CTA tiles for M >= 1024, K <= 8192 on B200
 
 }  // namespace
 
 LLB_EXPORT void llb_gemm_set_pair_auto(int on) { g_pair_auto = on != 0; }
 LLB_EXPORT void llb_gemm_set_skinny_auto(int on) { g_skinny_auto = on != 0; }
+// The next llb_gemm_bf16 call (epilogue "store", N % 32 == 0, no stream-K) writes its output into the gather slots
+// `push[q]` of all `world` ranks and advances their per-row-block column counters `cnt[q]` (see GemmParams).
+LLB_EXPORT int llb_gemm_set_push(void** push, void** cnt, int rank, int world, int max_mb) {
+  if (world < 1 || world > 8) return LLB_ERR_BAD_ARG;
+  for (int q = 0; q < 8; ++q) {
+    g_push.push[q] = q < world ? (bf16*)push[q] : nullptr;
+    g_push.cnt[q] = q < world ? (uint32_t*)cnt[q] : nullptr;
+  }
+  g_push.world = world;
+  g_push.rank = rank;
+  g_push.max_mb = max_mb;
+  return LLB_OK;
+}
 
 // C[M,N] (ldc) = A[M,K] (lda) . W[N,K]^T (ldw)  with epilogue `epi`:
 //   0 store bf16 (+bias)          1 store bf16 of acc (+bias) + residual[M,N] (same ldc)
@@ -1145,6 +1229,8 @@ LLB_EXPORT int llb_gemm_bf16(const void* A, int64_t lda, const void* W, int64_t 
     GemmParams p;
     memset(&p, 0, sizeof(p));
     p.w_tiled_kb = w_tiled ? K / 64 : 0;
+    apply_push(p);
+    if (p.push_world > 0 && (epi != EPI_STORE || (N % 32))) return LLB_ERR_UNSUPPORTED;
     p.C = C;
     p.residual = (const bf16*)residual;
     p.bias = (const bf16*)bias;
@@ -1171,8 +1257,11 @@ LLB_EXPORT int llb_gemm_bf16(const void* A, int64_t lda, const void* W, int64_t 
     rc = cached_tmap(&tb, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, (uint32_t)bn);
   if (rc) return rc;
   GemmParams p;
+  memset(&p, 0, sizeof(p));
   p.w_tiled_kb = w_swz ? K / 64 : 0;
   p.w_swz = w_swz ? (const bf16*)W : nullptr;
+  apply_push(p);
+  if (p.push_world > 0 && (epi != EPI_STORE || (N % 32) || stream_k)) return LLB_ERR_UNSUPPORTED;
   p.C = C;
   p.residual = (const bf16*)residual;
   p.bias = (const bf16*)bias;
@@ -1221,6 +1310,7 @@ LLB_EXPORT int llb_gemm_bf16_grouped(const void* A, int64_t lda, const void* W, 
   rc = cached_tmap(&tb, W, (uint64_t)E * (uint64_t)N, (uint64_t)K, (uint64_t)ldw, (uint32_t)bn);
   if (rc) return rc;
   GemmParams p;
+  memset(&p, 0, sizeof(p));
   p.C = C;
   p.residual = nullptr;
   p.bias = nullptr;
@@ -1265,6 +1355,7 @@ LLB_EXPORT int llb_gemm_bf16_batched(const void* A, int64_t a_row_stride, int64_
   rc = make_tmap_3d(&tb, W, 2, (uint64_t)batch, (uint64_t)N, (uint64_t)K, (uint64_t)K, (uint64_t)N * K, (uint32_t)bn, BK);
   if (rc) return rc;
   GemmParams p;
+  memset(&p, 0, sizeof(p));
   p.C = C;
   p.residual = nullptr;
   p.bias = nullptr;

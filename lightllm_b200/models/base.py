@@ -565,6 +565,11 @@ class TransformerLM:
                 return None
             return ops.rmsnorm(residual, next_norm_w, self.eps, self.norm_w_offset)
         fused = self.tp.fused
+        if (fused is not None and next_norm_w is not None and a.is_cuda and not isinstance(w, ops.TiledWeight)
+                and fused.can_push(a.shape[0], w.shape[0])):
+            # GEMM epilogue pushes the partial tiles to every rank; the reduction + residual + norm reads locally
+            T, H = fused.gemm_push(a, w, bias)
+            return fused.reduce_pushed(T, H, residual, next_norm_w, self.eps, self.norm_w_offset)
         use_fused = (fused is not None and next_norm_w is not None and a.is_cuda
                      and a.shape[0] <= fused.max_tokens and w.shape[0] == fused.hidden)
         partial = ops.gemm(a, w, epi="store", bias=bias,

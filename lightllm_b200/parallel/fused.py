@@ -30,7 +30,7 @@ class FusedTP:
     ONE_SHOT_BYTES = 512 * 1024  # per-rank message below which every rank pulls all rows itself
 
     def __init__(self, pstate: Optional[pdist.ParallelState] = None, max_tokens: int = 16384, hidden: int = 8192,
-                 ctas: int = 592):
+                 ctas: int = 592, push: bool = True, push_tokens: Optional[int] = 1024):
         ps = pstate or pdist.state()
         assert ps.device.type == "cuda" and 1 < ps.tp_size <= 8
         self.ps = ps
@@ -44,11 +44,19 @@ class FusedTP:
         self.off_ready = 4 * self.buf_bytes
         self.off_rowflag = self.off_ready + 256
         self.max_chunks = max_tokens // self.world + 2   # chunk flags per owner rank (a chunk is >= 1 row)
-        total = self.off_rowflag + ((self.world * self.max_chunks * 4 + 255) // 256) * 256
+        end_flags = self.off_rowflag + ((self.world * self.max_chunks * 4 + 255) // 256) * 256
+        # pushed mode: gather slots [parity][source rank][max_tokens, hidden] + column counters [parity][source][blocks]
+        self.max_mb = (max_tokens + 127) // 128
+        self.push_tokens = min(max_tokens, push_tokens if push_tokens is not None else max_tokens)
+        self.off_gather = [end_flags, end_flags + self.world * self.buf_bytes] if push else None
+        cnt_bytes = ((self.world * self.max_mb * 4 + 255) // 256) * 256
+        self.off_cnt = [end_flags + 2 * self.world * self.buf_bytes + i * cnt_bytes for i in range(2)] if push else None
+        total = end_flags + (2 * self.world * self.buf_bytes + 2 * cnt_bytes if push else 0)
+        self.push = bool(push)
         group = ps.cpu_group if ps.cpu_group is not None else ps.tp_group
         self.region = SymmetricRegion(total, self.rank, self.world, group=ps.tp_group if ps.dp_size > 1 else group,
                                       device=ps.device)
-        self.local = torch.zeros(4, dtype=torch.int32, device=ps.device)  # [epoch, arrive, status, pad]
+        self.local = torch.zeros(8, dtype=torch.int32, device=ps.device)  # [epoch, arrive, status, pad, push_epoch0, push_epoch1]
         self.parity = 0
         self.calls = 0
         self._tabs = {}
@@ -91,6 +99,55 @@ class FusedTP:
             return self.force_one_shot
         return 1 if (self.world == 2 or T * H * 2 * (self.world - 1) <= 4 * self.ONE_SHOT_BYTES) else 0
 
+    # ---- pushed mode: the GEMM stores its tiles into every rank's gather slot and counts columns ----
+    def can_push(self, T: int, H: int) -> bool:
+        return self.push and H == self.hidden and T <= self.push_tokens and H % 32 == 0 and self._one_shot(T, H) == 1
+
+    def gemm_push(self, a, w, bias=None):
+        """Row-parallel GEMM whose epilogue writes the partial sums of this rank into all ranks' gather slots
+        (peer stores, tile by tile while the other tiles still compute).  Follow with reduce_pushed()."""
+        from .. import ops
+
+        par = self.parity
+        key = ("push", par)
+        t = self._tabs.get(key)
+        if t is None:
+            r = self.region
+            slot = self.rank * self.buf_bytes
+            t = self._tabs[key] = (_ptr_array([r.ptrs[q] + self.off_gather[par] + slot for q in range(self.world)]),
+                                   _ptr_array([r.ptrs[q] + self.off_cnt[par] for q in range(self.world)]))
+        check(kernels().llb_gemm_set_push(t[0], t[1], ctypes.c_int(self.rank), ctypes.c_int(self.world),
+                                          ctypes.c_int(self.max_mb)), "gemm_set_push")
+        T, N = a.shape[0], w.shape[0]
+        # `out` is only a shape / stride carrier: the kernel stores through the push pointers
+        dummy = self.region.tensor(self.off_gather[par] + self.rank * self.buf_bytes, (T, N), torch.bfloat16)
+        ops.gemm(a, w, bias=bias, out=dummy)
+        return T, N
+
+    def reduce_pushed(self, T, H, residual, norm_w, eps, w_offset=0.0):
+        out = torch.empty((T, H), dtype=torch.bfloat16, device=residual.device)
+        par = self.parity
+        key = ("pushed", par)
+        t = self._tabs.get(key)
+        base = self.local.data_ptr()
+        if t is None:
+            r = self.region
+            t = self._tabs[key] = dict(
+                partial=_ptr_array([r.local_ptr + self.off_gather[par] + q * self.buf_bytes for q in range(self.world)]),
+                cnt=_ptr_array([r.local_ptr + self.off_cnt[par]]), pepoch=_ptr_array([base + 16 + 4 * par]))
+        tb = self._tables(par)
+        check(kernels().llb_tp_reduce_norm(t["partial"], tb["sums"], tb["ready"], tb["rowflag"],
+                                           _ptr_array([residual.data_ptr()]), _ptr_array([out.data_ptr()]), ptr(norm_w),
+                                           tb["epoch"], tb["arrive"], tb["status"], ctypes.c_int(self.rank),
+                                           ctypes.c_int(self.world), ctypes.c_int(0), ctypes.c_int(T), ctypes.c_int(H),
+                                           f32(eps), f32(w_offset), ctypes.c_int(2), ctypes.c_int(1),
+                                           ctypes.c_int(min(self.ctas, max(T, 1))), ctypes.c_int(self.max_chunks),
+                                           t["cnt"], t["pepoch"], ctypes.c_int(self.max_mb), stream()), "tp_reduce_pushed")
+        _count()
+        self.parity ^= 1
+        self.calls += 1
+        return out
+
     def _launch(self, T, H, residual, out, norm_w, eps, w_offset, do_norm):
         t = self._tables(self.parity)
         check(kernels().llb_tp_reduce_norm(t["partial"], t["sums"], t["ready"], t["rowflag"],
@@ -100,7 +157,7 @@ class FusedTP:
                                            ctypes.c_int(0), ctypes.c_int(T), ctypes.c_int(H), f32(eps), f32(w_offset),
                                            ctypes.c_int(self._one_shot(T, H)), ctypes.c_int(do_norm),
                                            ctypes.c_int(min(self.ctas, max(T, 1))), ctypes.c_int(self.max_chunks),
-                                           stream()), "tp_reduce_norm")
+                                           None, None, ctypes.c_int(0), stream()), "tp_reduce_norm")
         _count()
         self.parity ^= 1
         self.calls += 1

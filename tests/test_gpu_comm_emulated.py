@@ -46,7 +46,8 @@ def test_tp_reduce_norm_emulated(dev, world, T, H, one_shot):
             ctypes.c_void_p(w.data_ptr()), _ptr_array([t.data_ptr() for t in local]),
             _ptr_array([t.data_ptr() + 4 for t in local]), ctypes.c_void_p(status.data_ptr()), ctypes.c_int(0),
             ctypes.c_int(world), ctypes.c_int(world), ctypes.c_int(T), ctypes.c_int(H), ctypes.c_float(1e-5),
-            ctypes.c_float(0.0), ctypes.c_int(one_shot), ctypes.c_int(1), ctypes.c_int(ctas), ctypes.c_int(max_chunks),
+            ctypes.c_float(0.0), ctypes.c_int(one_shot), ctypes.c_int(1), ctypes.c_int(ctas), ctypes.c_int(max_chunks), None, None,
+            ctypes.c_int(0),
             ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
         assert rc == 0
         torch.cuda.synchronize()
@@ -60,3 +61,53 @@ def test_tp_reduce_norm_emulated(dev, world, T, H, one_shot):
             assert (residual[r].float() - want_res).abs().max().item() < 6e-2
             assert (out[r].float() - want_out.float()).abs().max().item() < 6e-2
             assert int(local[r][0].item()) == call + 1  # epoch advanced exactly once
+
+
+@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("T,N,K", [(200, 1024, 512), (256, 4096, 2048), (37, 2048, 4096), (700, 1024, 1024)])
+def test_gemm_push_then_pushed_reduce_emulated(dev, world, T, N, K):
+    """GEMM epilogue in push mode (tiles stored into every rank's gather slot + column counters) followed by the
+    reduce kernel in pushed mode; the ranks are slices of one GPU, run over three rounds without resetting."""
+    from lightllm_b200 import ops
+
+    torch.manual_seed(1)
+    max_mb = (T + 127) // 128 + 1
+    gather = [torch.zeros(world, T, N, dtype=BF, device=dev) for _ in range(world)]     # [dst rank][src rank]
+    cnt = [torch.zeros(world * max_mb, dtype=torch.int32, device=dev) for _ in range(world)]
+    local = [torch.zeros(8, dtype=torch.int32, device=dev) for _ in range(world)]
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    dummy_tab = _ptr_array([0] * (world * world))
+    norm_w = (torch.randn(N, device=dev) * 0.1 + 1).to(BF)
+    residual = [torch.zeros(T, N, dtype=BF, device=dev) for _ in range(world)]
+    want_res = torch.zeros(T, N, device=dev)
+    for rnd in range(3):
+        acts = [(torch.randn(T, K, device=dev) * 0.5).to(BF) for _ in range(world)]
+        ws = [(torch.randn(N, K, device=dev) * 0.05).to(BF) for _ in range(world)]
+        for r in range(world):   # rank r's GEMM pushes into slot r of every rank
+            rc = kernels().llb_gemm_set_push(_ptr_array([gather[q][r].data_ptr() for q in range(world)]),
+                                             _ptr_array([cnt[q].data_ptr() for q in range(world)]), ctypes.c_int(r),
+                                             ctypes.c_int(world), ctypes.c_int(max_mb))
+            assert rc == 0
+            ops.gemm(acts[r], ws[r], out=gather[r][r])
+        out = [torch.empty(T, N, dtype=BF, device=dev) for _ in range(world)]
+        rc = kernels().llb_tp_reduce_norm(
+            _ptr_array([gather[r][q].data_ptr() for r in range(world) for q in range(world)]), dummy_tab, dummy_tab,
+            dummy_tab, _ptr_array([t.data_ptr() for t in residual]), _ptr_array([t.data_ptr() for t in out]),
+            ctypes.c_void_p(norm_w.data_ptr()), _ptr_array([t.data_ptr() for t in local]),
+            _ptr_array([t.data_ptr() + 4 for t in local]), ctypes.c_void_p(status.data_ptr()), ctypes.c_int(0),
+            ctypes.c_int(world), ctypes.c_int(world), ctypes.c_int(T), ctypes.c_int(N), ctypes.c_float(1e-5),
+            ctypes.c_float(0.0), ctypes.c_int(2), ctypes.c_int(1), ctypes.c_int(min(16, T)), ctypes.c_int(4),
+            _ptr_array([t.data_ptr() for t in cnt]), _ptr_array([t.data_ptr() + 16 for t in local]),
+            ctypes.c_int(max_mb), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+        assert rc == 0
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0, "a bounded wait ran out"
+        assert int(ops.gemm_status(dev).item()) == 0
+        total = sum((a.float() @ w.float().t()).to(BF).float() for a, w in zip(acts, ws))
+        want_res = (want_res + total).to(BF).float()
+        want_out = ref.rmsnorm(want_res.to(BF), norm_w, 1e-5).float()
+        scale = want_res.abs().max().item()
+        for r in range(world):
+            assert (residual[r].float() - want_res).abs().max().item() < 2e-2 * scale + 5e-2
+            assert (out[r].float() - want_out).abs().max().item() < 8e-2
+            assert int(cnt[r][0].item()) == (rnd + 1) * N
