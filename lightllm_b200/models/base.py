@@ -538,7 +538,8 @@ class TransformerLM:
         """Buffer a layer should write a to-be-reduced [T, hidden] partial sum into (the symmetric
         buffer of the fused reduction when it is active, else a fresh tensor)."""
         fused = self.tp.fused
-        if fused is not None and self.tp.size > 1 and T <= fused.max_tokens and self.hidden == fused.hidden:
+        if fused is not None and self.tp.size > 1 and T <= fused.max_tokens and self.hidden == fused.hidden \
+                and fused.prefers(T, self.hidden):
             return fused.partial_out(T, self.hidden)
         return torch.empty((T, self.hidden), dtype=self.dtype, device=self.device)
 
@@ -571,7 +572,8 @@ class TransformerLM:
             T, H = fused.gemm_push(a, w, bias)
             return fused.reduce_pushed(T, H, residual, next_norm_w, self.eps, self.norm_w_offset)
         use_fused = (fused is not None and next_norm_w is not None and a.is_cuda
-                     and a.shape[0] <= fused.max_tokens and w.shape[0] == fused.hidden)
+                     and a.shape[0] <= fused.max_tokens and w.shape[0] == fused.hidden
+                     and fused.prefers(a.shape[0], w.shape[0]))
         partial = ops.gemm(a, w, epi="store", bias=bias,
                            out=fused.partial_out(a.shape[0], w.shape[0]) if use_fused else None)
         if next_norm_w is None:

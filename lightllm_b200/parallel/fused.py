@@ -72,6 +72,11 @@ class FusedTP:
         assert T <= self.max_tokens and H == self.hidden
         return self.region.tensor(self.off_partial[self.parity], (T, H), torch.bfloat16)
 
+    def prefers(self, T: int, H: int) -> bool:
+        """Measured: with 4 or more ranks NCCL + the norm kernel wins above about 64 MB per rank (455 vs 534 us at
+        134 MB on 4 GPUs); below that, and always with 2 ranks, the fused kernel is faster."""
+        return self.world == 2 or T * H * 2 <= (64 << 20)
+
     def owns(self, partial) -> bool:
         """True if `partial` is the buffer handed out by `partial_out` for the coming call."""
         return partial.is_cuda and partial.data_ptr() == self.region.local_ptr + self.off_partial[self.parity]
