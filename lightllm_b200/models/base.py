@@ -624,7 +624,7 @@ class TransformerLM:
         for lw in self.layers:
             tensors += [t for t in lw.tensors().values() if isinstance(t, torch.Tensor)]
         for t in tensors:
-            if t.data_ptr() not in seen:
+            if t is not None and t.data_ptr() not in seen:
                 seen.add(t.data_ptr())
                 n += t.numel() * t.element_size()
         return n

@@ -147,3 +147,60 @@ class GemmaLM(TransformerLM):
         self.act = "gelu"
         self.embed_scale = float(torch.tensor(self.hidden ** 0.5, dtype=torch.bfloat16))
         self.tie_embeddings = True
+
+
+class _RewardHead:
+    """Reward models replace the vocabulary projection by a scalar score head on the last token; the forward
+    pass returns it as a [B, 1] "logits" tensor that the reward backend stores in the request."""
+
+    def _load_weights(self, src):
+        super()._load_weights(src)
+        self.lm_head_w = None
+        self._load_score_head(src)
+
+    def weight_shapes(self):
+        s = super().weight_shapes()
+        s.pop("lm_head.weight", None)
+        s.update(self._score_shapes())
+        return s
+
+    def _lm_head(self, h):
+        from .. import ops
+
+        hn = ops.rmsnorm(h, self.final_norm_w, self.eps, self.norm_w_offset)
+        return self._score(hn)
+
+
+@register_model("qwen2", condition=lambda c: "Qwen2ForRewardModel" in (c.get("architectures") or []))
+class Qwen2RewardLM(_RewardHead, Qwen2LM):
+    """Qwen2.5-Math-RM style: score = Linear(H, 1)(ReLU(Linear(H, H)(h))), both with bias
+    (reference: lightllm/models/qwen2_reward)."""
+
+    def _score_shapes(self):
+        H = self.hidden
+        return {"score.0.weight": (H, H), "score.0.bias": (H,), "score.2.weight": (1, H), "score.2.bias": (1,)}
+
+    def _load_score_head(self, src):
+        self.s0_w, self.s0_b = self._dev(src.get("score.0.weight")), self._dev(src.get("score.0.bias"))
+        self.s2_w, self.s2_b = self._dev(src.get("score.2.weight")).float(), self._dev(src.get("score.2.bias")).float()
+
+    def _score(self, hn):
+        from .. import ops
+
+        x = ops.gemm(hn, self.s0_w, bias=self.s0_b)
+        ops.act_(x, "relu")
+        return x.float() @ self.s2_w.t() + self.s2_b
+
+
+@register_model("internlm2", condition=lambda c: "InternLM2ForRewardModel" in (c.get("architectures") or []))
+class InternLM2RewardLM(_RewardHead, InternLM2):
+    """InternLM2-reward: score = v_head(h), one Linear(H, 1) without bias (reference: lightllm/models/internlm2_reward)."""
+
+    def _score_shapes(self):
+        return {"v_head.weight": (1, self.hidden)}
+
+    def _load_score_head(self, src):
+        self.v_head_w = self._dev(src.get("v_head.weight")).float()
+
+    def _score(self, hn):
+        return hn.float() @ self.v_head_w.t()
