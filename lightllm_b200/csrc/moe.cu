@@ -341,3 +341,70 @@ LLB_EXPORT int llb_moe_combine(void* out, const void* y, const int* pair_row, co
   LLB_LAUNCH_CHECK();
   return LLB_OK;
 }
+
+// ---------------------------------------------------------------------------------------
+// Experts with biases (GPT-OSS): the grouped GEMMs run with the plain store epilogue and these two kernels add
+// the per-expert bias rows.  Rows live in 128-row blocks of one expert each (mblock_expert, -1 = padding block).
+//   moe_bias_act: h [M_pad, 2I] with gate / up interleaved in 32-column blocks -> out [M_pad, I]
+//     kind 0 / 1: SiLU / GELU(tanh) gate;  kind 2: clamped "swiglu_oai":
+//       g = min(g, limit); u = clamp(u, -limit, limit); out = (u + 1) * g * sigmoid(alpha * g)
+//   moe_add_bias: y [M_pad, H] += b2[expert of the row's block]
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) moe_bias_act_kernel(const bf16* __restrict__ h, const bf16* __restrict__ b13,
+                                                           const int* __restrict__ mblock_expert,
+                                                           bf16* __restrict__ out, int I, int kind, float alpha,
+                                                           float limit) {
+  const int row = blockIdx.x;
+  const int e = mblock_expert[row >> 7];
+  if (e < 0) return;
+  const bf16* hr = h + (int64_t)row * 2 * I;
+  const bf16* br = b13 ? b13 + (int64_t)e * 2 * I : nullptr;
+  for (int i = threadIdx.x; i < I; i += blockDim.x) {
+    const int blk = i >> 5, j = i & 31;
+    const int gi = blk * 64 + j, ui = gi + 32;
+    float g = __bfloat162float(hr[gi]), u = __bfloat162float(hr[ui]);
+    if (br) {
+      g += __bfloat162float(br[gi]);
+      u += __bfloat162float(br[ui]);
+    }
+    float o;
+    if (kind == 2) {
+      g = fminf(g, limit);
+      u = fminf(fmaxf(u, -limit), limit);
+      o = (u + 1.f) * g / (1.f + __expf(-alpha * g));
+    } else if (kind == 1) {
+      const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+      o = 0.5f * g * (1.f + tanhf(k0 * (g + k1 * g * g * g))) * u;
+    } else {
+      o = g / (1.f + __expf(-g)) * u;
+    }
+    out[(int64_t)row * I + i] = __float2bfloat16(o);
+  }
+}
+
+__global__ void __launch_bounds__(256) moe_add_bias_kernel(bf16* __restrict__ y, const bf16* __restrict__ b2,
+                                                           const int* __restrict__ mblock_expert, int H) {
+  const int row = blockIdx.x;
+  const int e = mblock_expert[row >> 7];
+  if (e < 0) return;
+  for (int i = threadIdx.x; i < H; i += blockDim.x)
+    y[(int64_t)row * H + i] = __float2bfloat16(__bfloat162float(y[(int64_t)row * H + i]) +
+                                                __bfloat162float(b2[(int64_t)e * H + i]));
+}
+
+LLB_EXPORT int llb_moe_bias_act(const void* h, const void* b13, const int* mblock_expert, void* out, int M_pad, int I,
+                                int kind, float alpha, float limit, cudaStream_t st) {
+  if (M_pad <= 0) return LLB_OK;
+  if ((I % 32) || kind < 0 || kind > 2) return LLB_ERR_UNSUPPORTED;
+  moe_bias_act_kernel<<<M_pad, 256, 0, st>>>((const bf16*)h, (const bf16*)b13, mblock_expert, (bf16*)out, I, kind, alpha,
+                                             limit);
+  LLB_LAUNCH_CHECK();
+  return LLB_OK;
+}
+
+LLB_EXPORT int llb_moe_add_bias(void* y, const void* b2, const int* mblock_expert, int M_pad, int H, cudaStream_t st) {
+  if (M_pad <= 0) return LLB_OK;
+  moe_add_bias_kernel<<<M_pad, 256, 0, st>>>((bf16*)y, (const bf16*)b2, mblock_expert, H);
+  LLB_LAUNCH_CHECK();
+  return LLB_OK;
+}

@@ -4,3 +4,4 @@ from . import qwen3_moe  # noqa: F401
 from . import deepseek2  # noqa: F401
 from . import generic  # noqa: F401
 from . import qwen2_vl  # noqa: F401
+from . import gpt_oss  # noqa: F401

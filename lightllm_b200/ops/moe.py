@@ -40,7 +40,15 @@ def ref_grouped_topk(logits, bias, k, n_group, topk_group, use_sigmoid=True, ren
     return ids.to(torch.int32), (w * scale).float()
 
 
-def ref_fused_experts(x, w13, w2, ids, weights, act="silu", e0=0, interleaved=True):
+def _swiglu_oai(h, alpha=1.702, limit=7.0):
+    """h [.., 2I] with gate / up interleaved in 32-column blocks (GPT-OSS clamped SwiGLU)."""
+    n = h.shape[-1] // 64
+    hv = h.reshape(*h.shape[:-1], n, 2, 32)
+    g, u = hv[..., 0, :].clamp(max=limit), hv[..., 1, :].clamp(min=-limit, max=limit)
+    return ((u + 1) * g * torch.sigmoid(alpha * g)).reshape(*h.shape[:-1], n * 32)
+
+
+def ref_fused_experts(x, w13, w2, ids, weights, act="silu", e0=0, interleaved=True, b13=None, b2=None):
     """x [T,H]; w13 [E_local, 2I, H] (gate/up interleaved in 32-row blocks when `interleaved`), w2 [E_local, H, I];
     experts outside [e0, e0+E_local) contribute nothing (expert parallel shard)."""
     T, H = x.shape
@@ -53,12 +61,18 @@ def ref_fused_experts(x, w13, w2, ids, weights, act="silu", e0=0, interleaved=Tr
             continue
         tok, slot = sel.nonzero(as_tuple=True)
         h = xf[tok] @ w13[e].float().t()
-        if interleaved:
+        if b13 is not None:
+            h = h.to(x.dtype).float() + b13[e].float()
+        if act == "swiglu_oai":
+            a = _swiglu_oai(h)
+        elif interleaved:
             a = ref.gated_act_interleaved(h, act).float()
         else:
             a = ref.gated_act(h, act).float()
         a = a.to(x.dtype).float()
         y = (a @ w2[e].float().t()).to(x.dtype).float()
+        if b2 is not None:
+            y = (y + b2[e].float()).to(x.dtype).float()
         out.index_add_(0, tok, y * weights[tok, slot].unsqueeze(-1))
     return out.to(x.dtype)
 
@@ -142,13 +156,14 @@ def gemm_grouped(a_sorted, w_stacked, mblock_expert, n_per_expert: int, epi: str
     return out
 
 
-def fused_experts(x, w13, w2, ids, weights, act="silu", e0: int = 0, out=None, accumulate: bool = False):
+def fused_experts(x, w13, w2, ids, weights, act="silu", e0: int = 0, out=None, accumulate: bool = False,
+                  b13=None, b2=None):
     """Routed expert FFN:  out[t] (+)= sum_k w[t,k] * down_e( act(gate_e(x_t)) * up_e(x_t) ),  e = ids[t,k].
 
     w13 [E_local, 2I, H] with gate/up rows interleaved in 32-row blocks, w2 [E_local, H, I].  On CUDA: align
     -> gather -> grouped GEMM with gated epilogue -> grouped GEMM -> weighted combine (5 launches)."""
     if not x.is_cuda:
-        r = ref_fused_experts(x, w13, w2, ids, weights, act, e0)
+        r = ref_fused_experts(x, w13, w2, ids, weights, act, e0, b13=b13, b2=b2)
         if out is not None:
             if accumulate:
                 out.add_(r)
@@ -165,8 +180,20 @@ def fused_experts(x, w13, w2, ids, weights, act="silu", e0: int = 0, out=None, a
     check(kernels().llb_moe_gather(ptr(a), ptr(x), ptr(lay.sorted_pair), ptr(lay.total_rows), c_int(k), c_int(H),
                                    i64(x.stride(0)), c_int(lay.m_pad), stream()), "moe_gather")
     _count()
-    h = gemm_grouped(a, w13, lay.mblock_expert, N13, epi="gated_" + act)
+    if b13 is None and act in ("silu", "gelu"):
+        h = gemm_grouped(a, w13, lay.mblock_expert, N13, epi="gated_" + act)
+    else:  # biased experts / clamped SwiGLU: plain grouped GEMM, then bias + activation in one pass
+        h13 = gemm_grouped(a, w13, lay.mblock_expert, N13, epi="store")
+        h = torch.empty((lay.m_pad, I), dtype=x.dtype, device=x.device)
+        kind = {"silu": 0, "gelu": 1, "swiglu_oai": 2}[act]
+        check(kernels().llb_moe_bias_act(ptr(h13), ptr(b13), ptr(lay.mblock_expert), ptr(h), c_int(lay.m_pad), c_int(I),
+                                         c_int(kind), f32(1.702), f32(7.0), stream()), "moe_bias_act")
+        _count()
     y = gemm_grouped(h, w2, lay.mblock_expert, H, epi="store")
+    if b2 is not None:
+        check(kernels().llb_moe_add_bias(ptr(y), ptr(b2), ptr(lay.mblock_expert), c_int(lay.m_pad), c_int(H), stream()),
+              "moe_add_bias")
+        _count()
     if out is None:
         out = torch.empty((T, H), dtype=x.dtype, device=x.device)
         accumulate = False

@@ -26,6 +26,12 @@ FAMILIES = {
                         query_pre_attn_scalar=256),
     "minicpm": dict(model_type="minicpm", hidden_size=256, intermediate_size=512, num_hidden_layers=2,
                     num_attention_heads=4, num_key_value_heads=2, scale_emb=12.0, scale_depth=1.4, dim_model_base=64),
+    "gpt_oss": dict(model_type="gpt_oss", hidden_size=256, intermediate_size=256, num_hidden_layers=2,
+                    num_attention_heads=4, num_key_value_heads=2, head_dim=64, num_local_experts=8,
+                    num_experts_per_tok=2, sliding_window=32, layer_types=["sliding_attention", "full_attention"]),
+    "qwen3_moe": dict(model_type="qwen3_moe", hidden_size=256, intermediate_size=512, moe_intermediate_size=128,
+                      num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=64, num_experts=8,
+                      num_experts_per_tok=2, norm_topk_prob=True, decoder_sparse_step=1, mlp_only_layers=[]),
     "internlm": dict(model_type="internlm", hidden_size=256, intermediate_size=512, num_hidden_layers=2,
                      num_attention_heads=4, bias=True),
 }

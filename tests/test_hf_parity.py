@@ -385,3 +385,23 @@ def test_qwen2_vl_vision_tower_mrope_and_merge(tmp_path):
                     mem_indexes=m.mem_manager.alloc(1).clone())
     got2 = m.forward(mi).logits.float()[0]
     assert (got2 - ref2).abs().max().item() < 2e-3 * max(ref.abs().max().item(), 1.0)
+
+
+def test_gpt_oss(tmp_path):
+    from transformers import GptOssConfig, GptOssForCausalLM
+
+    torch.manual_seed(0)
+    cfg = GptOssConfig(hidden_size=64, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
+                       num_key_value_heads=2, head_dim=16, num_local_experts=4, num_experts_per_tok=2, vocab_size=200,
+                       max_position_embeddings=256, sliding_window=8, rope_scaling=None,
+                       layer_types=["sliding_attention", "full_attention"])
+    m = GptOssForCausalLM(cfg)
+    with torch.no_grad():
+        for layer in m.model.layers:
+            layer.self_attn.sinks.normal_(0, 1)
+            layer.mlp.router.bias.normal_(0, 0.5)
+            layer.mlp.experts.gate_up_proj_bias.normal_(0, 0.5)
+            layer.mlp.experts.down_proj_bias.normal_(0, 0.5)
+            layer.mlp.experts.gate_up_proj.normal_(0, 0.3)
+            layer.mlp.experts.down_proj.normal_(0, 0.3)
+    _check(tmp_path, m, _ids(200, n=30))
