@@ -5,3 +5,4 @@ from . import deepseek2  # noqa: F401
 from . import generic  # noqa: F401
 from . import qwen2_vl  # noqa: F401
 from . import gpt_oss  # noqa: F401
+from . import llava  # noqa: F401

@@ -56,6 +56,10 @@ def get_tokenizer(model_dir: str, tokenizer_mode: str = "fast", trust_remote_cod
         from ..models.qwen2_vl import Qwen2VLTokenizer
 
         return Qwen2VLTokenizer(tok, cfg)
+    if mt == "llava":
+        from ..models.llava import LlavaTokenizer
+
+        return LlavaTokenizer(tok, cfg)
     raise ValueError(f"multimodal serving of model_type {mt!r} has no tokenizer wrapper")
 
 

@@ -39,6 +39,10 @@ def build_vision_tower(args, device, dtype=torch.bfloat16):
         else:
             src = RandomSource(Qwen2VLVisionTower.weight_shapes(vcfg), dtype=dtype)
         return Qwen2VLVisionTower(vcfg, src, device, dtype)
+    if mt == "llava":
+        from ...models.vit.clip_visual import ClipLlavaTower
+
+        return ClipLlavaTower(cfg, SafetensorsSource(args.model_dir), device, dtype)
     raise ValueError(f"no vision tower for model_type {mt!r}")
 
 

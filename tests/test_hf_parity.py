@@ -405,3 +405,56 @@ def test_gpt_oss(tmp_path):
             layer.mlp.experts.gate_up_proj.normal_(0, 0.3)
             layer.mlp.experts.down_proj.normal_(0, 0.3)
     _check(tmp_path, m, _ids(200, n=30))
+
+
+def test_llava_clip_tower_and_merge(tmp_path):
+    from transformers import CLIPVisionConfig, LlamaConfig, LlavaConfig, LlavaForConditionalGeneration
+
+    from lightllm_b200.common.infer_state import ModelInput
+    from lightllm_b200.models.base import load_config
+    from lightllm_b200.models.registry import get_model
+    from lightllm_b200.models.vit.clip_visual import ClipLlavaTower
+    from lightllm_b200.models.weights import SafetensorsSource
+    from lightllm_b200.parallel import dist as pdist
+    import json
+    import os
+
+    torch.manual_seed(0)
+    vc = CLIPVisionConfig(hidden_size=32, intermediate_size=64, num_hidden_layers=3, num_attention_heads=4,
+                          image_size=28, patch_size=14)
+    tc = LlamaConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                     num_key_value_heads=2, vocab_size=300, max_position_embeddings=256)
+    cfg = LlavaConfig(vision_config=vc, text_config=tc, image_token_index=290)
+    hf = LlavaForConditionalGeneration(cfg).eval().float()
+    d = str(tmp_path / "ckpt")
+    hf.save_pretrained(d, safe_serialization=True)
+    pixels = torch.randn(1, 3, 28, 28)
+    n_img = 4
+    pre, post = [5, 17], [9, 44, 120]
+    hf_ids = torch.tensor([pre + [290] * n_img + post])
+    with torch.no_grad():
+        ref = hf(input_ids=hf_ids, pixel_values=pixels).logits[0].float()
+    raw_cfg = json.load(open(os.path.join(d, "config.json")))
+    tower = ClipLlavaTower(raw_cfg, SafetensorsSource(d), torch.device("cpu"), torch.float32)
+    emb = tower.forward(pixels)[0]
+    assert emb.shape == (n_img, 64) and tower.tokens_per_image == n_img
+
+    class Arena:
+        def read_rows(self, rows):
+            return emb[rows - 7]
+
+    ps = pdist.ParallelState(device=torch.device("cpu"))
+    m = get_model(load_config(d), model_dir=d, pstate=ps, data_type="float32", max_total_token_num=256, max_req_num=2,
+                  max_seq_length=128, disable_cudagraph=True)
+    m.embed_arena = Arena()
+    tok0 = 100_000_000
+    ids = torch.tensor(pre + list(range(tok0, tok0 + n_img)) + post)
+    item = {"token_id": tok0, "token_num": n_img, "start_index_in_embed_cache": 7}
+    req, n = m.req_manager.alloc(), len(ids)
+    mi = ModelInput(batch_size=1, total_token_num=n, max_kv_len=n, is_prefill=True,
+                    b_req_idx=torch.tensor([req], dtype=torch.int32), b_seq_len=torch.tensor([n], dtype=torch.int32),
+                    mem_indexes=m.mem_manager.alloc(n).clone(), input_ids=ids,
+                    b_ready_cache_len=torch.zeros(1, dtype=torch.int32), max_q_len=n, return_all_logits=True,
+                    multimodal_params=[{"images": [item], "audios": []}])
+    got = m.forward(mi).logits.float()
+    assert (got - ref).abs().max().item() < 2e-3 * max(ref.abs().max().item(), 1.0)
