@@ -78,6 +78,12 @@ def test_family_gpu_matches_cpu(dev, family):
     # random norm weights of 1 (+1 offset) and the sandwich norms make the Gemma-3 toy network amplify bf16
     # rounding: its bf16 CPU restatement is 0.19 x scale away from fp32 as well
     rel = 0.3 if family == "gemma3_text" else 0.06
+    if family in ("gpt_oss", "qwen3_moe"):
+        # a near-tie in the router flips a token's expert under bf16 rounding: isolated large deviations on an
+        # otherwise tight match (the expert FFN kernels themselves agree to 5e-4 on these shapes)
+        rel = 0.4
+        mean = (out_c[0] - out_g[0]).abs().mean().item()
+        assert mean < 0.01 * scale, f"prefill logits: mean err {mean}, scale {scale}"
     assert err < rel * scale + 0.05, f"prefill logits: err {err}, scale {scale}"
     tok, n = int(out_c[0][-1].argmax()), len(ids)
     for k in range(2):  # the same token is fed to both, so the sequences stay aligned
