@@ -236,6 +236,77 @@ LLB_EXPORT int llb_sample(const void* logits, int dtype, int64_t stride, int B, 
   return LLB_OK;
 }
 
+// ---- all-greedy batches: arg-max + log-probability in two small passes over many CTAs ----
+// pass 1: CTA (b, s) scans slice s of row b (coalesced loads) and keeps (max, arg-max, sum exp(x - max));
+// pass 2: one warp per row merges the S partials.  part: [B, S, 3] floats (max, index bits, sum).
+template <typename T>
+__global__ void __launch_bounds__(256) greedy_partial_kernel(const T* __restrict__ logits, int64_t stride, int V,
+                                                             int per, float* __restrict__ part) {
+  __shared__ float red[33];
+  __shared__ ArgMax am[33];
+  const int b = blockIdx.x, s = blockIdx.y, S = gridDim.y;
+  const T* row = logits + (int64_t)b * stride;
+  const int i0 = s * per, i1 = min(V, i0 + per);
+  ArgMax best{-INFINITY, 0x7fffffff};
+  for (int i = i0 + threadIdx.x; i < i1; i += blockDim.x) best = better(best, ArgMax{ld_logit(row, i), i});
+  best = block_argmax(best, am);
+  float z = 0.f;
+  for (int i = i0 + threadIdx.x; i < i1; i += blockDim.x) z += __expf(ld_logit(row, i) - best.v);
+  z = block_sum(z, red);
+  if (threadIdx.x == 0) {
+    float* o = part + ((int64_t)b * S + s) * 3;
+    o[0] = best.v;
+    o[1] = __int_as_float(best.i);
+    o[2] = i1 > i0 ? z : 0.f;
+  }
+}
+
+__global__ void greedy_final_kernel(const float* __restrict__ part, int S, int64_t* __restrict__ out_ids,
+                                    float* __restrict__ out_logprob) {
+  const int b = blockIdx.x, lane = threadIdx.x;
+  ArgMax best{-INFINITY, 0x7fffffff};
+  for (int s = lane; s < S; s += 32) {
+    const float* o = part + ((int64_t)b * S + s) * 3;
+    best = better(best, ArgMax{o[0], __float_as_int(o[1])});
+  }
+#pragma unroll
+  for (int k = 16; k > 0; k >>= 1) {
+    ArgMax t;
+    t.v = __shfl_xor_sync(0xffffffffu, best.v, k);
+    t.i = __shfl_xor_sync(0xffffffffu, best.i, k);
+    best = better(best, t);
+  }
+  float z = 0.f;
+  for (int s = lane; s < S; s += 32) {
+    const float* o = part + ((int64_t)b * S + s) * 3;
+    if (o[2] > 0.f) z += o[2] * __expf(o[0] - best.v);
+  }
+  z = warp_sum(z);
+  if (lane == 0) {
+    out_ids[b] = best.i;
+    if (out_logprob) out_logprob[b] = -__logf(z);
+  }
+}
+
+// scratch: B * splits * 3 floats.
+LLB_EXPORT int llb_sample_greedy(const void* logits, int dtype, int64_t stride, int B, int V, float* scratch, int splits,
+                                 int64_t* out_ids, float* out_logprob, cudaStream_t st) {
+  if (B <= 0) return LLB_OK;
+  if (splits < 1 || splits > 1024 || scratch == nullptr) return LLB_ERR_BAD_ARG;
+  const int per = ((V + splits - 1) / splits + 3) & ~3;
+  dim3 grid(B, splits);
+  if (dtype == 0)
+    greedy_partial_kernel<float><<<grid, 256, 0, st>>>((const float*)logits, stride, V, per, scratch);
+  else if (dtype == 1)
+    greedy_partial_kernel<bf16><<<grid, 256, 0, st>>>((const bf16*)logits, stride, V, per, scratch);
+  else
+    return LLB_ERR_UNSUPPORTED;
+  LLB_LAUNCH_CHECK();
+  greedy_final_kernel<<<B, 32, 0, st>>>(scratch, splits, out_ids, out_logprob);
+  LLB_LAUNCH_CHECK();
+  return LLB_OK;
+}
+
 LLB_EXPORT int llb_token_logprob(const void* logits, int dtype, int64_t stride, int B, int V, const int64_t* ids,
                                  float* out, cudaStream_t st) {
   if (B <= 0) return LLB_OK;

@@ -413,6 +413,13 @@ def sample(logits, temperature=None, top_p=None, top_k=None, seeds=None, steps=N
     dt = {torch.float32: 0, torch.bfloat16: 1}[logits.dtype]
     ids = torch.empty(B, dtype=torch.int64, device=logits.device)
     lp = torch.empty(B, dtype=torch.float32, device=logits.device) if want_logprob else None
+    if temperature is None and top_k is None and top_p is None:  # every row greedy: many CTAs per row
+        splits = max(1, min(64, 2368 // B, V // 2048))
+        scratch = torch.empty(B * splits * 3, dtype=torch.float32, device=logits.device)
+        check(kernels().llb_sample_greedy(ptr(logits), c_int(dt), i64(logits.stride(0)), c_int(B), c_int(V), ptr(scratch),
+                                          c_int(splits), ptr(ids), ptr(lp), stream()), "sample_greedy")
+        _count(2)
+        return ids, lp
     if seeds is not None:
         assert seeds.dtype == torch.int64
     check(kernels().llb_sample(ptr(logits), c_int(dt), i64(logits.stride(0)), c_int(B), c_int(V), ptr(temperature),

@@ -130,6 +130,18 @@ def test_sampler_greedy_and_logprob(dev):
     assert ids2.tolist() == lb.float().argmax(-1).tolist()
 
 
+@pytest.mark.parametrize("B,V", [(256, 128256), (1, 151936), (700, 2048), (3, 1000)])
+def test_sampler_greedy_many_ctas(dev, B, V):
+    torch.manual_seed(B)
+    logits = torch.randn(B, V, device=dev) * 4
+    logits[:, V // 3] = logits.max() + 1.0          # a tie between two columns: the lower index wins
+    logits[:, V // 3 + 7] = logits[:, V // 3]
+    ids, lp = ops.sample(logits)
+    assert ids.tolist() == [V // 3] * B
+    want = torch.log_softmax(logits.float(), dim=-1)[:, V // 3]
+    close(lp, want, 1e-3, 1e-3)
+
+
 def test_sampler_topk_topp_support_and_distribution(dev):
     torch.manual_seed(7)
     V = 5000
