@@ -42,6 +42,7 @@ gqa_decode_kernel(const bf16* __restrict__ q, int64_t q_stride, const bf16* __re
                   const int* __restrict__ b_seq_len, bf16* __restrict__ out, int64_t out_stride,
                   float* __restrict__ part_o, float* __restrict__ part_lse, int Hq, int Hkv, int num_splits,
                   float scale_log2) {
+  pdl_wait();
   constexpr int CH = D / 8;            // 16-byte chunks per row
   constexpr int ROW_BYTES = D * 2;
   constexpr int TILE_BYTES = 16 * ROW_BYTES;           // 16 tokens
@@ -261,6 +262,7 @@ template <int D>
 __global__ void __launch_bounds__(D)
 decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse, bf16* __restrict__ out,
                     int64_t out_stride, int Hq, int num_splits) {
+  pdl_wait();
   const int bh = blockIdx.x;
   const int b = bh / Hq, h = bh % Hq;
   const int d = threadIdx.x;
@@ -507,12 +509,13 @@ LLB_EXPORT int llb_gqa_decode(const void* q, int64_t q_stride, const void* kv_la
       if (rc) return rc;                                                                                          \
       configured = true;                                                                                          \
     }                                                                                                             \
-    gqa_decode_kernel<DD, kDecodeStages><<<grid, 128, decode_smem_bytes<DD>(), st>>>(                             \
-        (const bf16*)q, q_stride, (const bf16*)kv_layer, req_to_token, r2t_stride, b_req_idx, b_seq_len,          \
-        (bf16*)out, out_stride, part_o, part_lse, Hq, Hkv, num_splits, sl2);                                      \
+    launch_pdl(gqa_decode_kernel<DD, kDecodeStages>, grid, dim3(128), decode_smem_bytes<DD>(), st, (const bf16*)q, \
+               q_stride, (const bf16*)kv_layer, req_to_token, r2t_stride, b_req_idx, b_seq_len, (bf16*)out,       \
+               out_stride, part_o, part_lse, Hq, Hkv, num_splits, sl2);                                           \
     LLB_LAUNCH_CHECK();                                                                                           \
     if (num_splits > 1) {                                                                                         \
-      decode_merge_kernel<DD><<<B * Hq, DD, 0, st>>>(part_o, part_lse, (bf16*)out, out_stride, Hq, num_splits);   \
+      launch_pdl(decode_merge_kernel<DD>, dim3(B * Hq), dim3(DD), 0, st, (const float*)part_o,                    \
+                 (const float*)part_lse, (bf16*)out, out_stride, Hq, num_splits);                                 \
       LLB_LAUNCH_CHECK();                                                                                         \
     }                                                                                                             \
   }

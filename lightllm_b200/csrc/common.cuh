@@ -13,6 +13,8 @@
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
 #include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
 
 #define LLB_OK 0
 #define LLB_ERR_BAD_ARG (-1)
@@ -29,6 +31,36 @@
   } while (0)
 
 namespace llb {
+
+// Programmatic dependent launch: a kernel launched through launch_pdl() may be scheduled while the previous
+// kernel of the stream is still draining; it must call pdl_wait() before it touches global memory (the call
+// returns once the previous kernel has completed and flushed).  Its own prologue (barrier set-up, tensor
+// memory allocation, index arithmetic) overlaps the predecessor's tail.  LLB_PDL=0 turns the attribute off.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+inline bool pdl_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("LLB_PDL");
+    v = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return v != 0;
+}
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 typedef __nv_bfloat16 bf16;
 typedef __nv_bfloat162 bf162;

@@ -298,6 +298,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_wait();  // barrier set-up and tensor-memory allocation overlapped the previous kernel's tail
   const uint32_t tmem_base = tmem_base_slot;
 
   if (warp == 0) {
@@ -548,8 +549,8 @@ int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, cud
     grid = units < sm_count() ? (int)units : sm_count();
     p.group_m = p.num_m_blocks;  // M fastest: neighbouring CTAs share a W tile
   }
-  gemm_bf16_kernel<BN, EPI><<<grid, GEMM_THREADS, smem_bytes<BN>(), st>>>(ta, tb, p);
-  LLB_LAUNCH_CHECK();
+  cudaError_t le = launch_pdl(gemm_bf16_kernel<BN, EPI>, dim3(grid), dim3(GEMM_THREADS), smem_bytes<BN>(), st, ta, tb, p);
+  if (le != cudaSuccess) return (int)le;
   return LLB_OK;
 }
 
@@ -637,6 +638,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   __syncthreads();
   cluster_sync_all();  // both CTAs' barriers exist before anyone signals across the pair
   tc_fence_after();
+  pdl_wait();          // everything above overlapped the previous kernel's tail
   const uint32_t tmem_base = tmem_base_slot;
 
   if (warp == 0) {
@@ -746,8 +748,9 @@ int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, cud
   int pairs = num_m * num_n;
   int max_pairs = sm_count() / 2;
   if (pairs > max_pairs) pairs = max_pairs;
-  gemm_bf16_pair_kernel<EPI><<<pairs * 2, GEMM_THREADS, pair_smem_bytes(), st>>>(ta, tb, p);
-  LLB_LAUNCH_CHECK();
+  cudaError_t le = launch_pdl(gemm_bf16_pair_kernel<EPI>, dim3(pairs * 2), dim3(GEMM_THREADS), pair_smem_bytes(), st, ta,
+                              tb, p);
+  if (le != cudaSuccess) return (int)le;
   return LLB_OK;
 }
 
@@ -870,6 +873,7 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
   __syncthreads();
   cluster_sync_all();
   tc_fence_after();
+  pdl_wait();
   const uint32_t tmem_base = tmem_base_slot;
 
   if (warp == 0) {
@@ -1060,13 +1064,15 @@ int launch_skinny(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams
   cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
   cfg.dynamicSmemBytes = sk_smem_bytes<NB>();
   cfg.stream = st;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2 * splits;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
   cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_bf16_skinny_kernel<NB, EPI>, ta, tb, p, splits);
   return e == cudaSuccess ? LLB_OK : (int)e;
 }

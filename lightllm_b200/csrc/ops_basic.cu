@@ -21,6 +21,7 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(bf16* __restrict__ out, bf
   __shared__ float red[33];
   const int row = blockIdx.x;
   const int nvec = H >> 3;
+  pdl_wait();
   const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + (int64_t)row * x_stride);
   bf16x8* rr = ADD ? reinterpret_cast<bf16x8*>(residual + (int64_t)row * res_stride) : nullptr;
   float vals[MAX_VEC][8];
@@ -72,13 +73,13 @@ static int launch_rmsnorm(bf16* out, bf16* residual, const bf16* x, const bf16* 
   int nvec = H / 8;
   int per = cdiv(nvec, 256);
   if (per <= 1)
-    rmsnorm_kernel<1, ADD><<<T, 256, 0, st>>>(out, residual, x, w, H, eps, w_offset, xs, os, rs);
+    launch_pdl(rmsnorm_kernel<1, ADD>, dim3(T), dim3(256), 0, st, out, residual, x, w, H, eps, w_offset, xs, os, rs);
   else if (per <= 2)
-    rmsnorm_kernel<2, ADD><<<T, 256, 0, st>>>(out, residual, x, w, H, eps, w_offset, xs, os, rs);
+    launch_pdl(rmsnorm_kernel<2, ADD>, dim3(T), dim3(256), 0, st, out, residual, x, w, H, eps, w_offset, xs, os, rs);
   else if (per <= 4)
-    rmsnorm_kernel<4, ADD><<<T, 256, 0, st>>>(out, residual, x, w, H, eps, w_offset, xs, os, rs);
+    launch_pdl(rmsnorm_kernel<4, ADD>, dim3(T), dim3(256), 0, st, out, residual, x, w, H, eps, w_offset, xs, os, rs);
   else
-    rmsnorm_kernel<8, ADD><<<T, 256, 0, st>>>(out, residual, x, w, H, eps, w_offset, xs, os, rs);
+    launch_pdl(rmsnorm_kernel<8, ADD>, dim3(T), dim3(256), 0, st, out, residual, x, w, H, eps, w_offset, xs, os, rs);
   LLB_LAUNCH_CHECK();
   return LLB_OK;
 }
@@ -155,6 +156,7 @@ __global__ void __launch_bounds__(256) rope_kv_scatter_kernel(bf16* __restrict__
                                                               int64_t qkv_stride) {
   constexpr int D = LANES_PER_HEAD * 8;
   const int t = blockIdx.x;
+  pdl_wait();
   const int total = (Hq + 2 * Hkv) * LANES_PER_HEAD;
   const int half = rot_dim >> 1;
   const int half_lanes = half >> 3;
@@ -225,9 +227,8 @@ LLB_EXPORT int llb_rope_kv_scatter(void* qkv, void* kv_layer, const float* cos_t
   if (T <= 0) return LLB_OK;
   if (rot_dim % 16 != 0 || rot_dim > D) return LLB_ERR_UNSUPPORTED;
 #define LAUNCH_ROPE(L)                                                                                              \
-  rope_kv_scatter_kernel<L><<<T, 256, 0, st>>>((bf16*)qkv, (bf16*)kv_layer, cos_t, sin_t, pos, slot,                \
-                                               (const bf16*)q_norm_w, (const bf16*)k_norm_w, norm_eps, norm_w_offset, \
-                                               Hq, Hkv, rot_dim, qkv_stride)
+  launch_pdl(rope_kv_scatter_kernel<L>, dim3(T), dim3(256), 0, st, (bf16*)qkv, (bf16*)kv_layer, cos_t, sin_t, pos,  \
+             slot, (const bf16*)q_norm_w, (const bf16*)k_norm_w, norm_eps, norm_w_offset, Hq, Hkv, rot_dim, qkv_stride)
   if (D == 128)
     LAUNCH_ROPE(16);
   else if (D == 64)
