@@ -38,7 +38,7 @@ async def serve_request(g, req: PDRequest, send):
         sp_kw.pop("group_request_id", None)
         sp_kw.pop("suggested_dp_index", None)
         sp = SamplingParams().init(tokenizer=mgr.tokenizer, **sp_kw)
-        sp.pd_master_node_id = int(req.peer["node_id"]) if req.peer else 0
+        sp.pd_master_node_id.set(int(req.peer["node_id"]) if req.peer else 0)
         mode = g.args.run_mode
         if mode == "prefill":
             sp.max_new_tokens = 1  # P emits exactly the first token; the sequence continues on D
