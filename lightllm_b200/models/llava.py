@@ -47,7 +47,8 @@ class LlavaTokenizer:
         return self.image_length
 
     def encode(self, prompt, multimodal_params=None, add_special_tokens: bool = True, **kw):
-        ids = list(self.tokenizer.encode(prompt, add_special_tokens=add_special_tokens))
+        ids = list(prompt) if isinstance(prompt, (list, tuple)) else \
+            list(self.tokenizer.encode(prompt, add_special_tokens=add_special_tokens))
         images = list(multimodal_params.images) if multimodal_params is not None else []
         out, k = [], 0
         for t in ids:

@@ -151,7 +151,8 @@ class Qwen2VLTokenizer:
         return n
 
     def encode(self, prompt, multimodal_params=None, add_special_tokens: bool = False, **kw):
-        ids = list(self.tokenizer.encode(prompt, add_special_tokens=add_special_tokens))
+        ids = list(prompt) if isinstance(prompt, (list, tuple)) else \
+            list(self.tokenizer.encode(prompt, add_special_tokens=add_special_tokens))
         images = list(multimodal_params.images) if multimodal_params is not None else []
         if not images:
             return ids

@@ -120,7 +120,7 @@ class HttpServerManager:
         return [r["id"] for r in recs]
 
     async def _encode(self, prompt: Union[str, List[int]], sampling_params: SamplingParams, mm=None):
-        if mm is not None and isinstance(prompt, str):
+        if mm is not None:  # text or token ids with image placeholders: the wrapper expands the placeholders
             loop = asyncio.get_running_loop()
             return list(await loop.run_in_executor(None, lambda: self.tokenizer.encode(
                 prompt, mm, add_special_tokens=sampling_params.add_special_tokens)))
