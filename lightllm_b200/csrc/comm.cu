@@ -209,8 +209,15 @@ __global__ void __launch_bounds__(256) tp_reduce_norm_kernel(const CommParams p)
       two_shot_phase1<8>(p, me, epoch);
   }
 
+  // token-sharded mode (one_shot == 3: reduce-scatter + residual + RMSNorm on the rows this rank owns, then
+  // all-gather of the normalised rows): only rows with row % world == rank are reduced here, their residual
+  // rows are the only ones kept up to date, and the normalised rows are pushed into every rank's `sums` buffer.
+  const bool tpsp = p.one_shot == 3;
+  const int row0 = tpsp ? me.rank + (int)blockIdx.x * world : (int)blockIdx.x;
+  const int row_step = tpsp ? G * world : G;
+
   // ---- phase 2: residual add + RMSNorm over all rows (one-shot: reduce here from the peers) ----
-  for (int row = blockIdx.x; row < T; row += G) {
+  for (int row = row0; row < T; row += row_step) {
     if (pushed) {
       if (threadIdx.x < world)
         wait_flag(p.push_cnt[blockIdx.y] + threadIdx.x * p.push_max_mb + (row >> 7), push_target, me.status,
@@ -263,11 +270,30 @@ __global__ void __launch_bounds__(256) tp_reduce_norm_kernel(const CommParams p)
           unpack8(reinterpret_cast<const bf16x8*>(me.norm_w)[v], wf);
 #pragma unroll
           for (int k = 0; k < 8; ++k) o[k] = vals[i][k] * inv * (wf[k] + p.w_offset);
-          *reinterpret_cast<bf16x8*>(me.out + (int64_t)row * H + v * 8) = pack8(o);
+          if (tpsp) {
+            const bf16x8 packed = pack8(o);
+#pragma unroll
+            for (int q = 0; q < MAX_WORLD; ++q)
+              if (q < world) *reinterpret_cast<bf16x8*>(me.sums[q] + (int64_t)row * H + v * 8) = packed;
+          } else {
+            *reinterpret_cast<bf16x8*>(me.out + (int64_t)row * H + v * 8) = pack8(o);
+          }
         }
       }
     }
+    if (tpsp) {
+      __threadfence_system();
+      __syncthreads();
+      if (threadIdx.x < world) st_release_sys(me.rowflag[threadIdx.x] + me.rank * p.max_chunks + row / world, epoch);
+    }
     __syncthreads();
+  }
+  if (tpsp) {  // all-gather completion: every row of the other owners has landed in my buffer
+    for (int row = blockIdx.x; row < T; row += G) {
+      const int owner = row % world;
+      if (owner != me.rank && threadIdx.x == 0)
+        wait_flag(me.rowflag[me.rank] + owner * p.max_chunks + row / world, epoch, me.status, 700);
+    }
   }
 
   // ---- the last CTA of this rank advances the epoch ----

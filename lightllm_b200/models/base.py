@@ -109,6 +109,7 @@ class TransformerLM:
         if self.device.type == "cuda" and self.dtype != torch.bfloat16:
             self.dtype = torch.bfloat16  # the sm_100a kernels are bf16
         self.extra = extra
+        self.tpsp_mix_mode = bool(extra.get("tpsp_mix_mode", False))  # token-sharded residual stream between layers
         self.share_with = share_with          # draft module: lives on the target model's KV pool / request table
         self.extra_kv_layers = extra_kv_layers  # pool layers appended for draft modules
         self.kv_layer_offset = 0
@@ -347,6 +348,7 @@ class TransformerLM:
         st.extra["ready_cpu"] = mi.b_ready_cache_len
         st.extra["req_idx_cpu"] = mi.b_req_idx
         st.extra["draft_input_hidden"] = mi.draft_input_hidden
+        st.extra["want_hidden"] = bool(mi.return_hidden)
         self._prepare_prefill_state(st)
         h = self._embed(input_ids, st)
         h = self._layers_forward(h, st)
@@ -357,7 +359,7 @@ class TransformerLM:
             last_idx = (cu_q[1:] - 1).to(torch.int32)
             last = torch.empty((B, self.hidden), dtype=h.dtype, device=dev)
             ops.copy_rows(last, h, None, last_idx, B)
-        logits = self._lm_head(last)
+        logits = self._lm_head(last, normed=True) if st.extra.get("normed") else self._lm_head(last)
         return ModelOutput(logits=logits, hidden=hidden)
 
     # ---- decode ----
@@ -418,7 +420,7 @@ class TransformerLM:
         self._prepare_decode_state(st)
         h = self._embed(ids, st)
         h = self._layers_forward(h, st)
-        return self._lm_head(h)
+        return self._lm_head(h, normed=True) if st.extra.get("normed") else self._lm_head(h)
 
     def _capture_decode_graph(self, bucket: int) -> dict:
         dev = self.device
@@ -511,28 +513,43 @@ class TransformerLM:
             h = h * self.embed_scale
         return self._merge_multimodal(h, st)
 
-    def _lm_head(self, h):
-        hn = ops.rmsnorm(h, self.final_norm_w, self.eps, self.norm_w_offset)
+    def _lm_head(self, h, normed: bool = False):
+        hn = h if normed else ops.rmsnorm(h, self.final_norm_w, self.eps, self.norm_w_offset)
         logits = ops.gemm(hn, self.lm_head_w, epi="f32")
         logits = self.tp.gather_logits(logits)
         scale = getattr(self, "logit_scale", 1.0)
         return logits * scale if scale != 1.0 else logits
 
     def _layers_forward(self, x, st: InferState):
-        """x: embeddings [T, H]; returns the final residual stream (pre final-norm)."""
+        """x: embeddings [T, H]; returns the final residual stream (pre final-norm).  In the token-sharded mode
+        the residual stream is only complete on its owner ranks, so the last reduction applies the final norm and
+        the normalised activations are returned instead (st.extra["normed"] tells the caller)."""
         residual = x
         h = ops.rmsnorm(residual, self.layers[0].in_norm, self.eps, self.norm_w_offset)
         n = self.num_layers
+        self._tpsp_now = self._tpsp_active(x.shape[0], st)
         for i, lw in enumerate(self.layers):
             a = self._attention_block(i, lw, h, st)                      # [T, hq*D] (pre o_proj)
             h = self._row_parallel(a, lw.o_w, lw.o_b, residual, lw.post_norm)
-            nxt = self.layers[i + 1].in_norm if i + 1 < n else None
+            nxt = self.layers[i + 1].in_norm if i + 1 < n else (self.final_norm_w if self._tpsp_now else None)
             f = self._ffn_block(i, lw, h, st)
             if f[0] == "rowpar":    # (activation, down weight): dense row-parallel tail
                 h = self._row_parallel(f[1], f[2], None, residual, nxt)
             else:                   # ("partial", tensor): per-rank partial sum of the FFN output (MoE)
                 h = self._reduce_partial(f[1], residual, nxt)
+        if self._tpsp_now:
+            self._tpsp_now = False
+            st.extra["normed"] = True
+            return h
         return residual
+
+    def _tpsp_active(self, T: int, st) -> bool:
+        """Token-sharded residual stream (--enable_tpsp_mix_mode) for this pass: needs the fused peer-memory
+        kernel, and is skipped when the caller wants the un-normalised hidden states back (draft models)."""
+        fused = self.tp.fused
+        return bool(getattr(self, "tpsp_mix_mode", False) and fused is not None and self.tp.size > 1
+                    and T <= fused.max_tokens and self.hidden == fused.hidden and self.device.type == "cuda"
+                    and not st.extra.get("want_hidden"))
 
     def _partial_out(self, T: int):
         """Buffer a layer should write a to-be-reduced [T, hidden] partial sum into (the symmetric
@@ -550,6 +567,13 @@ class TransformerLM:
                 residual.add_(partial)
                 return None
             return ops.add_rmsnorm_(residual, partial, next_norm_w, self.eps, self.norm_w_offset)
+        if getattr(self, "_tpsp_now", False):
+            fused = self.tp.fused
+            if not fused.owns(partial):
+                buf = fused.partial_out(partial.shape[0], partial.shape[1])
+                buf.copy_(partial)
+                partial = buf
+            return fused.tpsp_reduce(partial, residual, next_norm_w, self.eps, self.norm_w_offset)
         if next_norm_w is None:
             if self.tp.fused is not None:
                 self.tp.fused.skip()
@@ -566,6 +590,9 @@ class TransformerLM:
                 return None
             return ops.rmsnorm(residual, next_norm_w, self.eps, self.norm_w_offset)
         fused = self.tp.fused
+        if getattr(self, "_tpsp_now", False):
+            partial = ops.gemm(a, w, epi="store", bias=bias, out=fused.partial_out(a.shape[0], w.shape[0]))
+            return fused.tpsp_reduce(partial, residual, next_norm_w, self.eps, self.norm_w_offset)
         if (fused is not None and next_norm_w is not None and a.is_cuda and not isinstance(w, ops.TiledWeight)
                 and fused.can_push(a.shape[0], w.shape[0])):
             # GEMM epilogue pushes the partial tiles to every rank; the reduction + residual + norm reads locally

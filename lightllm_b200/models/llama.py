@@ -164,10 +164,10 @@ class _RewardHead:
         s.update(self._score_shapes())
         return s
 
-    def _lm_head(self, h):
+    def _lm_head(self, h, normed: bool = False):
         from .. import ops
 
-        hn = ops.rmsnorm(h, self.final_norm_w, self.eps, self.norm_w_offset)
+        hn = h if normed else ops.rmsnorm(h, self.final_norm_w, self.eps, self.norm_w_offset)
         return self._score(hn)
 
 

@@ -176,6 +176,31 @@ class FusedTP:
         self._launch(T, H, residual, out, norm_w, eps, w_offset, 1)
         return out
 
+    def tpsp_reduce(self, partial, residual, norm_w, eps, w_offset=0.0):
+        """Token-sharded variant (the reference's tpsp mix mode, lightllm/common/basemodel/layer_infer/template/
+        transformer_layer_infer_template.py tpsp_* paths: reduce-scatter, norm on the shard, all-gather) as ONE
+        kernel: each rank reduces the rows it owns (row % world == rank) from the peers' partial buffers, adds
+        its shard of the residual stream, normalises, and stores the normalised rows into every rank's gather
+        buffer.  Only the owned rows of `residual` are kept up to date.  Returns the complete normalised [T, H]
+        activations as a view of a symmetric buffer that stays valid until the call after the next one."""
+        T, H = partial.shape
+        assert partial.data_ptr() == self.region.local_ptr + self.off_partial[self.parity]
+        par = self.parity
+        out = self.region.tensor(self.off_sums[par], (T, H), torch.bfloat16)
+        t = self._tables(par)
+        rows = (T + self.world - 1) // self.world
+        check(kernels().llb_tp_reduce_norm(t["partial"], t["sums"], t["ready"], t["rowflag"],
+                                           _ptr_array([residual.data_ptr()]), _ptr_array([out.data_ptr()]), ptr(norm_w),
+                                           t["epoch"], t["arrive"], t["status"], ctypes.c_int(self.rank),
+                                           ctypes.c_int(self.world), ctypes.c_int(0), ctypes.c_int(T), ctypes.c_int(H),
+                                           f32(eps), f32(w_offset), ctypes.c_int(3), ctypes.c_int(1),
+                                           ctypes.c_int(min(self.ctas, max(rows, 1))), ctypes.c_int(self.max_chunks),
+                                           None, None, ctypes.c_int(0), stream()), "tp_tpsp_reduce")
+        _count()
+        self.parity ^= 1
+        self.calls += 1
+        return out
+
     def skip(self):
         """A reduction of this forward pass went another way (the last layer has no following norm): keep the
         buffer alternation in step, so that every pass starts on the same buffer (CUDA-graph replays reuse the

@@ -48,7 +48,8 @@ def _build_model_and_backend(args: StartArgs, ps):
         try:
             from ...parallel.fused import FusedTP
 
-            fused = FusedTP(ps)
+            hidden = cfg.get("hidden_size") or (cfg.get("text_config") or {}).get("hidden_size")
+            fused = FusedTP(ps, max_tokens=args.batch_max_tokens, hidden=int(hidden))
         except Exception:
             fused = None
     model = get_model(cfg, model_dir=args.model_dir, pstate=ps, data_type=args.data_type,
@@ -60,7 +61,8 @@ def _build_model_and_backend(args: StartArgs, ps):
                       graph_grow_step_size=args.graph_grow_step_size,
                       graph_max_len_in_batch=args.graph_max_len_in_batch or None, tp_fused=fused,
                       enable_ep_moe=args.enable_ep_moe, quant_type=args.quant_type,
-                      extra_kv_layers=_mtp_modules(args))
+                      extra_kv_layers=_mtp_modules(args),
+                      tpsp_mix_mode=bool(getattr(args, "enable_tpsp_mix_mode", False)))
     eos = args.eos_ids or args.eos_id or cfg.get("eos_token_id") or []
     eos = tuple(eos) if isinstance(eos, (list, tuple)) else (eos,)
     bargs = BackendArgs(batch_max_tokens=args.batch_max_tokens, chunked_prefill_size=args.chunked_prefill_size,

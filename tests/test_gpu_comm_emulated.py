@@ -111,3 +111,50 @@ def test_gemm_push_then_pushed_reduce_emulated(dev, world, T, N, K):
             assert (residual[r].float() - want_res).abs().max().item() < 2e-2 * scale + 5e-2
             assert (out[r].float() - want_out).abs().max().item() < 8e-2
             assert int(cnt[r][0].item()) == (rnd + 1) * N
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("T,H", [(5, 4096), (48, 4096), (33, 8192), (256, 2048), (1, 4096)])
+def test_tpsp_reduce_emulated(dev, world, T, H):
+    """Token-sharded mode: each rank reduces + normalises the rows it owns and pushes them to every rank's
+    gather buffer; only the owned rows of each rank's residual are kept up to date."""
+    torch.manual_seed(2)
+    maxT = 512
+    partial = [torch.zeros(2, maxT, H, dtype=BF, device=dev) for _ in range(world)]
+    sums = [torch.zeros(2, maxT, H, dtype=BF, device=dev) for _ in range(world)]
+    ready = [torch.zeros(64, dtype=torch.int32, device=dev) for _ in range(world)]
+    max_chunks = maxT // world + 2
+    rowflag = [torch.zeros(world * max_chunks, dtype=torch.int32, device=dev) for _ in range(world)]
+    local = [torch.zeros(4, dtype=torch.int32, device=dev) for _ in range(world)]
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    w = (torch.randn(H, device=dev) * 0.1 + 1).to(BF)
+    res0 = torch.randn(T, H, device=dev).to(BF)
+    residual = [res0.clone() for _ in range(world)]
+    want_res = res0.float().clone()
+    ctas = min(16, max((T + world - 1) // world, 1))
+    for call in range(4):
+        par = call & 1
+        parts = [(torch.randn(T, H, device=dev) * 0.5).to(BF) for _ in range(world)]
+        for r in range(world):
+            partial[r][par, :T] = parts[r]
+        tab = lambda ts, sel: _ptr_array([sel(ts[q]) for _ in range(world) for q in range(world)])
+        rc = kernels().llb_tp_reduce_norm(
+            tab(partial, lambda t: t[par].data_ptr()), tab(sums, lambda t: t[par].data_ptr()),
+            tab(ready, lambda t: t.data_ptr()), tab(rowflag, lambda t: t.data_ptr()),
+            _ptr_array([t.data_ptr() for t in residual]), _ptr_array([s[par].data_ptr() for s in sums]),
+            ctypes.c_void_p(w.data_ptr()), _ptr_array([t.data_ptr() for t in local]),
+            _ptr_array([t.data_ptr() + 4 for t in local]), ctypes.c_void_p(status.data_ptr()), ctypes.c_int(0),
+            ctypes.c_int(world), ctypes.c_int(world), ctypes.c_int(T), ctypes.c_int(H), ctypes.c_float(1e-5),
+            ctypes.c_float(0.0), ctypes.c_int(3), ctypes.c_int(1), ctypes.c_int(ctas), ctypes.c_int(max_chunks),
+            None, None, ctypes.c_int(0), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+        assert rc == 0
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0, "a bounded wait ran out"
+        want_res = (want_res + sum(p.float() for p in parts)).to(BF).float()
+        want_out = ref.rmsnorm(want_res.to(BF), w, 1e-5).float()
+        for r in range(world):
+            own = torch.arange(r, T, world, device=dev)
+            if own.numel():
+                assert (residual[r][own].float() - want_res[own]).abs().max().item() < 6e-2
+            assert (sums[r][par, :T].float() - want_out).abs().max().item() < 6e-2
+            assert int(local[r][0].item()) == call + 1

@@ -21,7 +21,7 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, out_dir, fused):
+def _worker(rank, world, port, out_dir, fused, tpsp=False):
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     from lightllm_b200.common.infer_state import ModelInput
     from lightllm_b200.engine.llm import LLM
@@ -29,7 +29,7 @@ def _worker(rank, world, port, out_dir, fused):
 
     pdist.init_distributed(world, rank, host="127.0.0.1", port=port, device=torch.device("cuda", rank))
     llm = LLM(config=CFG, max_total_token_num=8192, running_max_req_size=8, max_req_total_len=512,
-              batch_max_tokens=2048, disable_fused_tp=not fused)
+              batch_max_tokens=2048, disable_fused_tp=not fused, tpsp_mix_mode=tpsp)
     g = torch.Generator().manual_seed(0)
     ids = torch.randint(3, 32000, (700,), generator=g)
     m = llm.model
@@ -47,7 +47,7 @@ def _worker(rank, world, port, out_dir, fused):
     status = m.tp.fused.status() if (fused and m.tp.fused is not None) else 0
     if rank == 0:
         torch.save({"logits": logits, "tokens": [o["token_ids"] for o in outs], "status": status},
-                   os.path.join(out_dir, f"tp{world}_f{int(fused)}.pt"))
+                   os.path.join(out_dir, f"tp{world}_f{int(fused)}{'_sp' if tpsp else ''}.pt"))
     llm.close()
     pdist.destroy(hard_exit_on_hang=True)
 
@@ -66,6 +66,12 @@ def test_tp2_fused_matches_nccl_and_tp1(tmp_path):
     assert (fus["logits"] - one["logits"]).abs().max().item() < 0.05 * scale + 0.05
     assert (fus["logits"] - nccl["logits"]).abs().max().item() < 0.05 * scale + 0.05
     assert all(len(t) == 24 for t in fus["tokens"])
+    # token-sharded residual stream (reduce-scatter + norm on the shard + all-gather, one kernel)
+    mp.spawn(_worker, args=(2, _free_port(), str(tmp_path), True, True), nprocs=2, join=True)
+    sp = torch.load(tmp_path / "tp2_f1_sp.pt")
+    assert sp["status"] == 0
+    assert (sp["logits"] - one["logits"]).abs().max().item() < 0.05 * scale + 0.05
+    assert all(len(t) == 24 for t in sp["tokens"])
 
 
 MOE = dict(model_type="qwen3_moe", hidden_size=1024, intermediate_size=2048, moe_intermediate_size=512,
