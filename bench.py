@@ -59,6 +59,7 @@ def parse():
     ap.add_argument("--out-len", type=int, default=256)
     ap.add_argument("--batch-max-tokens", type=int, default=16384)
     ap.add_argument("--skip-e2e", action="store_true")
+    ap.add_argument("--tpsp", action="store_true", help="token-sharded residual stream between layers (N > 1)")
     return ap.parse_args()
 
 
@@ -147,7 +148,7 @@ def main():
     pool_tokens = conc * (total_len + 8) + args.batch_max_tokens
     llm = LLM(config=cfg, max_total_token_num=pool_tokens, running_max_req_size=conc, max_req_total_len=total_len + 8,
               batch_max_tokens=args.batch_max_tokens, chunked_prefill_size=args.batch_max_tokens // 2,
-              disable_dynamic_prompt_cache=False, graph_max_batch_size=conc)
+              disable_dynamic_prompt_cache=False, graph_max_batch_size=conc, tpsp_mix_mode=bool(args.tpsp))
     model = llm.model
     t_start = time.time()
 
@@ -289,7 +290,7 @@ def main():
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform-random token ids, random-init weights",
             "impl": "ours",
             "config": {"model": args.model, "global_batch": conc, "seq_len": total_len, "input_len": in_len,
-                       "output_len": out_len, "parallelism": f"tp{args.gpus}", "step": "one wave of `global_batch` requests, prefill + all decode steps + sampling",
+                       "output_len": out_len, "parallelism": f"tp{args.gpus}" + ("+tpsp" if args.tpsp else ""), "step": "one wave of `global_batch` requests, prefill + all decode steps + sampling",
                        "l2": "inputs larger than L2 (weights and KV pool are streamed every pass)",
                        "gemm_wait_status": status},
             "clocks": clock_info, "gpu_launches": launches,

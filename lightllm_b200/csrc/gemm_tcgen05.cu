@@ -805,12 +805,13 @@ int pick_bn(int M, int N) {
 // ---------------------------------------------------------------------------------------------
 constexpr int SK_RSTRIDE = 260;  // floats per spilled row: 16-byte stores of 8 consecutive rows hit distinct banks
 
-template <int NB>
-constexpr int sk_stage_bytes() { return BM * BK * 2 + NB * PAIR_HALF * BK * 2; }
-template <int NB>
-constexpr int sk_stages() { return NB == 1 ? 6 : 4; }
-template <int NB>
-constexpr int sk_smem_bytes() { return sk_stages<NB>() * sk_stage_bytes<NB>() + 1024 + 512; }
+// TW: tile width per accumulator (256, or 128 to spread a narrow output over twice as many SMs; NB = 1 only)
+template <int NB, int TW>
+constexpr int sk_stage_bytes() { return BM * BK * 2 + NB * (TW / 2) * BK * 2; }
+template <int NB, int TW>
+constexpr int sk_stages() { return NB == 1 ? (TW == 128 ? 8 : 6) : 4; }
+template <int NB, int TW>
+constexpr int sk_smem_bytes() { return sk_stages<NB, TW>() * sk_stage_bytes<NB, TW>() + 1024 + 512; }
 
 // No memory clobber: the caller orders these loads after the cluster barrier (both are volatile asm), and
 // several of them must be allowed in flight at once.
@@ -822,16 +823,18 @@ __device__ __forceinline__ float4 ld_dsmem_f4(uint32_t cluster_addr) {
   return v;
 }
 
-template <int NB, int EPI>
+template <int NB, int EPI, int TW>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                         const GemmParams p, const int splits) {
-  constexpr int STAGES = sk_stages<NB>();
+  static_assert(TW == 256 || (TW == 128 && NB == 1), "tile width");
+  constexpr int STAGES = sk_stages<NB, TW>();
+  constexpr int HALF = TW / 2;  // weight rows loaded by each CTA of a pair
   constexpr int A_BYTES = BM * BK * 2;
-  constexpr int B_BYTES = PAIR_HALF * BK * 2;
-  constexpr int STAGE_BYTES = sk_stage_bytes<NB>();
+  constexpr int B_BYTES = HALF * BK * 2;
+  constexpr int STAGE_BYTES = sk_stage_bytes<NB, TW>();
   constexpr uint32_t TMEM_COLS = 512;
-  constexpr uint32_t IDESC = umma_idesc(256, 256, 1);
+  constexpr uint32_t IDESC = umma_idesc(256, TW, 1);
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -850,7 +853,7 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
   int mb, nbk;
   tile_coords(blockIdx.y, p.num_m_blocks, p.num_n_blocks, p.group_m, mb, nbk);
   const int m0 = mb * 256;
-  const int n0 = nbk * 256 * NB;
+  const int n0 = nbk * TW * NB;
   const int kb_total = (p.K + BK - 1) / BK;
   const int kb_per = (kb_total + splits - 1) / splits;
   const int kb0 = (int)split * kb_per;
@@ -891,9 +894,10 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         tma_load_2d_pair(sa, &tmA, lead_full, kb * BK, m0 + (int)half * BM);
 #pragma unroll
         for (int j = 0; j < NB; ++j) {
-          const int wrow = n0 + j * 256 + (int)half * PAIR_HALF;
+          const int wrow = n0 + j * TW + (int)half * HALF;
           if (p.w_tiled_kb)
-            tma_load_2d_pair(sa + A_BYTES + j * B_BYTES, &tmB, lead_full, 0, ((wrow >> 7) * p.w_tiled_kb + kb) * 128);
+            tma_load_2d_pair(sa + A_BYTES + j * B_BYTES, &tmB, lead_full, 0,
+                             ((wrow >> 7) * p.w_tiled_kb + kb) * 128 + (wrow & 127));
           else
             tma_load_2d_pair(sa + A_BYTES + j * B_BYTES, &tmB, lead_full, kb * BK, wrow);
         }
@@ -917,7 +921,7 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
           const uint64_t db = umma_smem_desc_sw128(sa + A_BYTES + j * B_BYTES);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k)
-            umma_bf16_pair(tmem_base + j * 256, da + 2 * k, db + 2 * k, IDESC, (i | k) != 0);
+            umma_bf16_pair(tmem_base + j * TW, da + 2 * k, db + 2 * k, IDESC, (i | k) != 0);
         }
         umma_commit_pair(empty_bar(stage));
         umma_commit_pair(map_to_cta(empty_bar(stage), peer_rank));
@@ -940,12 +944,12 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     if (splits == 1) {
 #pragma unroll
       for (int j = 0; j < NB; ++j)
-        epilogue_store<256, EPI>(p, t_row + j * 256, row, row < p.M, n0 + j * 256, false, [](uint32_t*, int) {});
-      if (EPI == EPI_STORE) push_signal(p, mb * 2 + (int)half, max(0, min(256 * NB, p.N - n0)));
+        epilogue_store<TW, EPI>(p, t_row + j * TW, row, row < p.M, n0 + j * TW, false, [](uint32_t*, int) {});
+      if (EPI == EPI_STORE) push_signal(p, mb * 2 + (int)half, max(0, min(TW * NB, p.N - n0)));
     } else {
       float* R = reinterpret_cast<float*>(smem_gen) + (size_t)erow * SK_RSTRIDE;
 #pragma unroll 1
-      for (int c = 0; c < 256; c += 32) {
+      for (int c = 0; c < TW; c += 32) {
         uint32_t r[32];
         tmem_ld_32x32(t_row + c, r);
         tmem_wait_ld();
@@ -964,7 +968,7 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
   if (splits > 1) {
     // all six warps reduce: thread t owns float4 column groups of the slice, two rows per iteration, and
     // issues every peer load of an iteration before the first add
-    const int W = 256 / splits, W4 = W / 4;
+    const int W = TW / splits, W4 = W / 4;
     const uint32_t r_base = smem_base;
     uint32_t peer_base[4];
 #pragma unroll
@@ -1044,17 +1048,17 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
   }
 }
 
-template <int NB, int EPI>
+template <int NB, int EPI, int TW = 256>
 int launch_skinny(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p_in, int splits, cudaStream_t st) {
   GemmParams p = p_in;
   p.num_m_blocks = cdiv(p.M, 256);
-  p.num_n_blocks = cdiv(p.N, 256 * NB);
+  p.num_n_blocks = cdiv(p.N, TW * NB);
   int64_t panel_rows = kPanelBytes / ((int64_t)256 * p.K * 2);
   p.group_m = (int)(panel_rows < 2 ? 2 : (panel_rows > 32 ? 32 : panel_rows));
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_skinny_kernel<NB, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         sk_smem_bytes<NB>());
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_skinny_kernel<NB, EPI, TW>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, sk_smem_bytes<NB, TW>());
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
@@ -1062,7 +1066,7 @@ int launch_skinny(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams
   memset(&cfg, 0, sizeof(cfg));
   cfg.gridDim = dim3(2 * splits, p.num_m_blocks * p.num_n_blocks, 1);
   cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
-  cfg.dynamicSmemBytes = sk_smem_bytes<NB>();
+  cfg.dynamicSmemBytes = sk_smem_bytes<NB, TW>();
   cfg.stream = st;
   cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -1073,14 +1077,24 @@ int launch_skinny(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl_enabled() ? 2 : 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_bf16_skinny_kernel<NB, EPI>, ta, tb, p, splits);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_bf16_skinny_kernel<NB, EPI, TW>, ta, tb, p, splits);
   return e == cudaSuccess ? LLB_OK : (int)e;
 }
 
-// nb: 1 or 2 accumulators; splits: 1, 2 or 4 (nb must be 1 when splits > 1; gated epilogues need splits == 1)
-int dispatch_skinny(int epi, int nb, int splits, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p,
-                    cudaStream_t st) {
+// nb: 1 or 2 accumulators; splits: 1, 2 or 4 (nb must be 1 when splits > 1; gated epilogues need splits == 1);
+// tw: 256, or 128 (nb == 1, plain epilogues only)
+int dispatch_skinny(int epi, int nb, int splits, int tw, const CUtensorMap& ta, const CUtensorMap& tb,
+                    const GemmParams& p, cudaStream_t st) {
   if (splits > 1 && (nb != 1 || epi == EPI_GATED_SILU || epi == EPI_GATED_GELU)) return LLB_ERR_UNSUPPORTED;
+  if (tw == 128) {
+    if (nb != 1) return LLB_ERR_UNSUPPORTED;
+    switch (epi) {
+      case EPI_STORE: return launch_skinny<1, EPI_STORE, 128>(ta, tb, p, splits, st);
+      case EPI_RESIDUAL: return launch_skinny<1, EPI_RESIDUAL, 128>(ta, tb, p, splits, st);
+      case EPI_F32: return launch_skinny<1, EPI_F32, 128>(ta, tb, p, splits, st);
+    }
+    return LLB_ERR_UNSUPPORTED;
+  }
   if (nb == 1) {
     switch (epi) {
       case EPI_STORE: return launch_skinny<1, EPI_STORE>(ta, tb, p, splits, st);
@@ -1106,20 +1120,29 @@ int dispatch_skinny(int epi, int nb, int splits, const CUtensorMap& ta, const CU
 // (4 pairs = clusters of 8 only for very narrow outputs: few of those clusters are co-resident).  Wider, up to
 // one wave of 512-column tiles: both accumulators, no split.  Beyond that the persistent pair kernel
 // (returns nb = 0, use_pair = true) overlaps its epilogues with the next tile.
-void skinny_plan(int M, int N, int K, int epi, int* nb, int* splits, bool* use_pair) {
+bool g_skinny_auto = true;
+bool g_skinny_tw128 = true;
+
+void skinny_plan(int M, int N, int K, int epi, int* nb, int* splits, bool* use_pair, int* tw) {
   const bool gated = epi == EPI_GATED_SILU || epi == EPI_GATED_GELU;
   const int sms = sm_count();
   const int tiles = cdiv(N, 256), kb = cdiv(K, BK);
   *nb = 0;
   *splits = 1;
   *use_pair = false;
+  *tw = 256;
   if (tiles * 2 <= sms) {
     *nb = 1;
     if (gated) return;
-    if (tiles <= 8 && kb >= 32)
+    if (tiles <= 8 && kb >= 32) {
       *splits = 4;
-    else if (tiles * 4 <= sms && kb >= 16)
+    } else if (tiles * 4 <= sms && kb >= 16) {
       *splits = 2;
+      // clusters of 4: about sms / 4 of them are co-resident; half-width tiles double the SMs at work
+      if (g_skinny_tw128 && cdiv(N, 128) <= sms / 4 && (N % 128) == 0) *tw = 128;
+    } else if (g_skinny_tw128 && cdiv(N, 128) * 2 <= sms && tiles * 4 <= sms && (N % 128) == 0) {
+      *tw = 128;  // short K (no split): still twice the SMs
+    }
     return;
   }
   if (cdiv(N, 512) * 2 <= sms) {
@@ -1129,7 +1152,6 @@ void skinny_plan(int M, int N, int K, int epi, int* nb, int* splits, bool* use_p
   if (M > 128) *use_pair = true;
 }
 
-bool g_skinny_auto = true;
 
 // one-shot configuration of the next llb_gemm_bf16 call (set by llb_gemm_set_push, cleared by the call)
 struct PushCfg {
@@ -1154,6 +1176,7 @@ bool g_pair_auto = true;  // measured faster than one-CTA tiles for M >= 1024, K
 
 LLB_EXPORT void llb_gemm_set_pair_auto(int on) { g_pair_auto = on != 0; }
 LLB_EXPORT void llb_gemm_set_skinny_auto(int on) { g_skinny_auto = on != 0; }
+LLB_EXPORT void llb_gemm_set_skinny_tw128(int on) { g_skinny_tw128 = on != 0; }
 // The next llb_gemm_bf16 call (epilogue "store", N % 32 == 0, no stream-K) writes its output into the gather slots
 // `push[q]` of all `world` ranks and advances their per-row-block column counters `cnt[q]` (see GemmParams).
 LLB_EXPORT int llb_gemm_set_push(void** push, void** cnt, int rank, int world, int max_mb) {
@@ -1203,11 +1226,15 @@ LLB_EXPORT int llb_gemm_bf16(const void* A, int64_t lda, const void* W, int64_t 
     }
   }
   // skinny (decode) kernel: explicit (bn = 1000 + 10 * nb + splits) or chosen for M <= 256
-  int sk_nb = 0, sk_splits = 0;
+  int sk_nb = 0, sk_splits = 0, sk_tw = 256;
   if (bn >= 1000) {
+    if (bn >= 1100) {  // 1100 + 10 + splits: half-width tiles
+      sk_tw = 128;
+      bn -= 100;
+    }
     sk_nb = (bn - 1000) / 10;
     sk_splits = (bn - 1000) % 10;
-    if ((sk_nb != 1 && sk_nb != 2) || (sk_splits != 1 && sk_splits != 2 && sk_splits != 4) || (N % 8) ||
+    if ((sk_nb != 1 && sk_nb != 2) || (sk_tw == 128 && sk_nb != 1) || (sk_splits != 1 && sk_splits != 2 && sk_splits != 4) || (N % 8) ||
         (int64_t)cdiv(kblocks, sk_splits) * (sk_splits - 1) >= kblocks)
       return LLB_ERR_UNSUPPORTED;
   } else if (bn == 0 && stream_k == 0 && g_skinny_auto && M >= 1024 && K >= 8192 && (N % 512) == 0 && ldw >= 0 &&
@@ -1216,7 +1243,7 @@ LLB_EXPORT int llb_gemm_bf16(const void* A, int64_t lda, const void* W, int64_t 
     sk_splits = 1;
   } else if (bn == 0 && stream_k == 0 && g_skinny_auto && M <= 256 && N >= 1024 && (N % 8) == 0 && K >= 1024) {
     bool plan_pair = false;
-    skinny_plan(M, N, K, epi, &sk_nb, &sk_splits, &plan_pair);
+    skinny_plan(M, N, K, epi, &sk_nb, &sk_splits, &plan_pair, &sk_tw);
     if (plan_pair && ldw >= 0) bn = 512;
   }
   const bool w_swz = ldw == -2;   // tiled and pre-swizzled (one-CTA kernels, bn 128 / 256)
@@ -1228,9 +1255,9 @@ LLB_EXPORT int llb_gemm_bf16(const void* A, int64_t lda, const void* W, int64_t 
     int rc = cached_tmap(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM);
     if (rc) return rc;
     if (w_tiled)
-      rc = cached_tmap(&tb, W, (uint64_t)N * (K / 64), 64, 64, (uint32_t)PAIR_HALF);
+      rc = cached_tmap(&tb, W, (uint64_t)N * (K / 64), 64, 64, (uint32_t)(sk_tw / 2));
     else
-      rc = cached_tmap(&tb, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, (uint32_t)PAIR_HALF);
+      rc = cached_tmap(&tb, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, (uint32_t)(sk_tw / 2));
     if (rc) return rc;
     GemmParams p;
     memset(&p, 0, sizeof(p));
@@ -1246,7 +1273,7 @@ LLB_EXPORT int llb_gemm_bf16(const void* A, int64_t lda, const void* W, int64_t 
     p.K = K;
     p.ldc = ldc;
     p.batch_count = 1;
-    return dispatch_skinny(epi, sk_nb, sk_splits, ta, tb, p, st);
+    return dispatch_skinny(epi, sk_nb, sk_splits, sk_tw, ta, tb, p, st);
   }
   // CTA-pair kernel: explicit (bn == 512) or chosen for big problems (at least two waves of pair tiles)
   bool use_pair = bn == 512;

@@ -107,7 +107,7 @@ def main():
             variants.update({"sk_n2s1": dict(bn=1021), "sk_n1s1": dict(bn=1011)})
         if M <= 256:  # skinny kernel: 1000 + 10 * accumulators + K splits
             variants.update({"sk_n1s1": dict(bn=1011), "sk_n1s2": dict(bn=1012), "sk_n1s4": dict(bn=1014),
-                             "sk_n2s1": dict(bn=1021)})
+                             "sk_n2s1": dict(bn=1021), "sk_w128s1": dict(bn=1111), "sk_w128s2": dict(bn=1112)})
         if a.stream_k:
             variants.update({"sk256": dict(bn=256, stream_k=1), "sk128": dict(bn=128, stream_k=1)})
         tiled = None

@@ -100,3 +100,25 @@ def test_gemm_preswizzled_tiled_weight(dev, bn, M, N, K):
     a = (torch.randn(M, K, device=dev) * 0.5).to(BF)
     w = (torch.randn(N, K, device=dev) * 0.1).to(BF)
     _check(ops.gemm(a, ops.TiledWeight(w, swizzle=True), bn=bn), a.float() @ w.float().t(), K)
+
+
+# Per-rank shapes of Llama-3-8B and Llama-3-70B under 8-way tensor parallelism (qkv, o_proj, gate_up, down, lm_head):
+# narrow K and N that are not multiples of the widest tile, at decode and prefill row counts, automatic tile plan.
+@pytest.mark.parametrize("M", [32, 256, 3000])
+@pytest.mark.parametrize("N,K,epi", [(768, 4096, "store"), (4096, 512, "store"), (3584, 4096, "gated_silu"),
+                                     (4096, 1792, "store"), (16032, 4096, "f32"), (1280, 8192, "store"),
+                                     (8192, 1024, "store"), (7168, 8192, "gated_silu"), (8192, 3584, "store")])
+def test_gemm_tp8_shard_shapes(dev, M, N, K, epi):
+    torch.manual_seed(4)
+    a = (torch.randn(M, K, device=dev) * 0.5).to(BF)
+    w = (torch.randn(N, K, device=dev) * 0.05).to(BF)
+    acc = a.float() @ w.float().t()
+    if epi == "gated_silu":
+        wg, wu = w[: N // 2], w[N // 2:]
+        want = torch.nn.functional.silu(a.float() @ wg.float().t()) * (a.float() @ wu.float().t())
+        _check(ops.gemm(a, ref.interleave_gate_up(wg, wu), epi=epi), want, K)
+    elif epi == "f32":
+        got = ops.gemm(a, w, epi="f32")
+        assert (got - acc).abs().max().item() < 1e-2 * acc.abs().max().item() + 1e-2
+    else:
+        _check(ops.gemm(a, w), acc, K)

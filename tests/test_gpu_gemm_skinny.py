@@ -16,10 +16,10 @@ def _check(got, want):
     assert int(ops.gemm_status(got.device).item()) == 0, "a bounded wait inside the GEMM timed out"
 
 
-# bn = 1000 + 10 * accumulators + splits
+# bn = 1000 + 10 * accumulators + splits (+ 100: half-width tiles, 128 columns per cluster)
 @pytest.mark.parametrize("M", [1, 7, 100, 128, 129, 256])
 @pytest.mark.parametrize("N,K", [(1024, 1024), (4096, 4096), (6144, 4096), (4096, 14336), (1032, 4160)])
-@pytest.mark.parametrize("bn", [1011, 1012, 1014, 1021])
+@pytest.mark.parametrize("bn", [1011, 1012, 1014, 1021, 1111, 1112, 1114])
 def test_skinny_store(dev, M, N, K, bn):
     torch.manual_seed(M + N)
     a = (torch.randn(M, K, device=dev) * 0.5).to(BF)
@@ -27,7 +27,7 @@ def test_skinny_store(dev, M, N, K, bn):
     _check(ops.gemm(a, w, bn=bn), a.float() @ w.float().t())
 
 
-@pytest.mark.parametrize("bn", [1011, 1012, 1014, 1021, 0])
+@pytest.mark.parametrize("bn", [1011, 1012, 1014, 1021, 1111, 1112, 0])
 def test_skinny_epilogues(dev, bn):
     torch.manual_seed(3)
     M, N, K = 200, 2048, 2048
