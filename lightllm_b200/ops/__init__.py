@@ -209,6 +209,10 @@ def gemm(a, w, epi: str = "store", residual=None, bias=None, out=None, bn: int =
     `reference.interleave_gate_up`, C is [M, N/2]) | "f32" (fp32 output, e.g. logits).
     stream_k: 0 whole tiles per CTA (default: fastest on every measured shape), 1 stream-K, -1 heuristic.
     """
+    if type(w).__name__ == "Fp8Weight":  # block-scaled e4m3 weight: quantise the activations, fp8 tensor cores
+        from . import fp8
+
+        return fp8.gemm_fp8(a, w, epi, residual, bias, out)
     if not _is_cuda(a):
         res = ref.gemm(a, w, epi, residual, bias)
         if out is not None:

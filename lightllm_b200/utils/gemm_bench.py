@@ -59,6 +59,36 @@ def timeit(fn, flush, n=10, reps=8):
     return ts[len(ts) // 2]
 
 
+def fp8_main(a, dev):
+    """fp8 block-scaled GEMM (activations already quantised) and the activation quantiser, against cuBLAS bf16 and
+    the bf16 tcgen05 kernel on the same shapes (DeepSeek-V3 dense projections and one expert's matrices)."""
+    from lightllm_b200 import ops
+    from lightllm_b200.ops import fp8
+
+    timer = timeit_graph if a.graph else timeit
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    shapes = [(4096, 7168, 16384), (4096, 24576, 1536), (4096, 4096, 7168), (4096, 7168, 2048), (256, 7168, 16384),
+              (256, 24576, 1536), (256, 4096, 7168), (256, 7168, 2048), (8192, 8192, 8192)]
+    for M, N, K in shapes:
+        copies = max(1, min(a.reps, int((2 << 30) // max((M * K + N * K) * 2, 1))))
+        xs = [(torch.randn(M, K, device=dev) * 0.5).bfloat16() for _ in range(copies)]
+        ws = [(torch.randn(N, K, device=dev) * 0.05).bfloat16() for _ in range(copies)]
+        fws = [fp8.Fp8Weight.from_float(w) for w in ws]
+        qs = [fp8.quant_act(x) for x in xs]
+        out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        t_cublas = timer(lambda i: torch.matmul(xs[i % copies], ws[i % copies].t(), out=out), flush, reps=a.reps)
+        t_bf16 = timer(lambda i: ops.gemm(xs[i % copies], ws[i % copies], out=out), flush, reps=a.reps)
+        t_fp8 = timer(lambda i: fp8.gemm_fp8_quantized(qs[i % copies][0], qs[i % copies][1], fws[i % copies], out=out),
+                      flush, reps=a.reps)
+        t_q = timer(lambda i: fp8.quant_act(xs[i % copies]), flush, reps=a.reps)
+        fl = 2 * M * N * K / 1e9
+        print(json.dumps({"M": M, "N": N, "K": K, "cublas_bf16_ms": round(t_cublas, 4), "bf16_ms": round(t_bf16, 4),
+                          "fp8_ms": round(t_fp8, 4), "quant_ms": round(t_q, 4), "fp8_tflops": round(fl / t_fp8, 1),
+                          "cublas_bf16_tflops": round(fl / t_cublas, 1),
+                          "fp8_weight_gbs": round(N * K / t_fp8 / 1e6, 1)}), flush=True)
+    print("gemm wait status", int(ops.gemm_status(dev).item()))
+
+
 def main():
     from lightllm_b200 import ops
 
@@ -70,8 +100,11 @@ def main():
     ap.add_argument("--graph", action="store_true", help="time CUDA-graph replays (no host launch cost)")
     ap.add_argument("--only", default=None, help="M,N,K: run just this shape (3 plain launches of --bn, for profilers)")
     ap.add_argument("--bn", type=int, default=0, help="kernel selector passed to ops.gemm with --only")
+    ap.add_argument("--fp8", action="store_true", help="block-scaled e4m3 GEMM on DeepSeek-V3 shapes vs the bf16 kernels")
     a = ap.parse_args()
     dev = torch.device("cuda")
+    if a.fp8:
+        return fp8_main(a, dev)
     if a.only:
         M, N, K = (int(v) for v in a.only.split(","))
         x = (torch.randn(M, K, device=dev) * 0.5).bfloat16()
