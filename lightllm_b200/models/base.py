@@ -110,6 +110,9 @@ class TransformerLM:
             self.dtype = torch.bfloat16  # the sm_100a kernels are bf16
         self.extra = extra
         self.tpsp_mix_mode = bool(extra.get("tpsp_mix_mode", False))  # token-sharded residual stream between layers
+        from ..common.quantization import QuantConfig
+
+        self.quant_cfg = QuantConfig(config, extra.get("quant_type"), extra.get("quant_cfg"), extra.get("expert_dtype"))
         self.share_with = share_with          # draft module: lives on the target model's KV pool / request table
         self.extra_kv_layers = extra_kv_layers  # pool layers appended for draft modules
         self.kv_layer_offset = 0
@@ -247,7 +250,43 @@ class TransformerLM:
             lw.post_norm = self._dev(src.get(p + "post_attention_layernorm.weight"))
             self._load_attn(lw, src, p, i)
             self._load_ffn(lw, src, p, i)
+            if self.quant_cfg.any_fp8 and not self.extra.get("dequant_fp8", False):
+                self._quantize_layer_online(lw, i)
             self.layers.append(lw)
+
+    def _quantize_layer_online(self, lw, layer: int):
+        """`--quant_type fp8w8a8*` (or a `--quant_cfg` entry for this layer) on weights that are still bf16 after
+        loading: quantise them to e4m3 with block scales so the layer runs on the fp8 GEMM.  Weights a model
+        already loaded as fp8 (block-quantised checkpoints) are left alone."""
+        from ..common.quantization import FP8_BLOCK
+        from ..ops.fp8 import Fp8Experts, Fp8Weight, stack_experts
+
+        t = lw.tensors()
+        silu = getattr(self, "act", "silu") == "silu"
+
+        def want(name):
+            return self.quant_cfg.method_for(layer, name) == FP8_BLOCK
+
+        def q2(name, rows=128):
+            w = t.get(name)
+            if isinstance(w, torch.Tensor) and w.dim() == 2 and w.shape[1] % 16 == 0 and w.is_floating_point() \
+                    and want(name):
+                t[name] = Fp8Weight.from_float(w, rows)
+
+        for name in ("qkv_w", "o_w", "down_w", "shared_down_w", "q_b_w"):
+            q2(name)
+        for name, flag in (("gate_up_w", "gate_up_fused"), ("shared_gate_up_w", "shared_fused")):
+            if not t.get(flag):
+                q2(name)            # plain GEMM followed by a standalone gated activation
+            elif silu:
+                q2(name, 32)        # interleaved in 32-row blocks: one scale row per block
+        w13, w2 = t.get("w13"), t.get("w2")
+        if (isinstance(w13, torch.Tensor) and w13.dim() == 3 and silu and t.get("b13") is None and want("experts")
+                and w13.shape[2] % 16 == 0 and w2.shape[2] % 16 == 0 and w13.shape[1] % 128 == 0
+                and w2.shape[1] % 128 == 0):
+            E = w13.shape[0]
+            t["w13"] = Fp8Experts(stack_experts([Fp8Weight.from_float(w13[e], 32) for e in range(E)]), E)
+            t["w2"] = Fp8Experts(stack_experts([Fp8Weight.from_float(w2[e], 128) for e in range(E)]), E)
 
     def _load_attn(self, lw, src, p, layer):
         D = self.head_dim
@@ -593,7 +632,7 @@ class TransformerLM:
         if getattr(self, "_tpsp_now", False):
             partial = ops.gemm(a, w, epi="store", bias=bias, out=fused.partial_out(a.shape[0], w.shape[0]))
             return fused.tpsp_reduce(partial, residual, next_norm_w, self.eps, self.norm_w_offset)
-        if (fused is not None and next_norm_w is not None and a.is_cuda and not isinstance(w, ops.TiledWeight)
+        if (fused is not None and next_norm_w is not None and a.is_cuda and isinstance(w, torch.Tensor)
                 and fused.can_push(a.shape[0], w.shape[0])):
             # GEMM epilogue pushes the partial tiles to every rank; the reduction + residual + norm reads locally
             T, H = fused.gemm_push(a, w, bias)
@@ -649,7 +688,9 @@ class TransformerLM:
         seen, n = set(), 0
         tensors = [self.embed_w, self.lm_head_w, self.final_norm_w]
         for lw in self.layers:
-            tensors += [t for t in lw.tensors().values() if isinstance(t, torch.Tensor)]
+            vals = list(lw.tensors().values())
+            tensors += [t for t in vals if isinstance(t, torch.Tensor)]
+            n += sum(t.nbytes() for t in vals if type(t).__name__ in ("Fp8Weight", "Fp8Experts"))
         for t in tensors:
             if t is not None and t.data_ptr() not in seen:
                 seen.add(t.data_ptr())

@@ -26,6 +26,7 @@ from .. import ops
 from ..common.mem_manager import MLAMemoryManager
 from ..ops import mla as mla_ops
 from ..ops import reference as ref
+from ..ops.fp8 import Fp8Weight, interleave_gate_up_fp8
 from . import moe, quant
 from .base import TransformerLM
 from .registry import register_model
@@ -83,6 +84,9 @@ class DeepseekV2LM(TransformerLM):
                                      act=self.act)
         self.ep = bool(self.extra.get("enable_ep_moe", False))
         self.fp8 = quant.is_fp8_block_config(c) or str(self.extra.get("quant_type", "none")).startswith("fp8w8a8-b128")
+        # fp8 checkpoints run their big matrices (experts, dense FFN, q_b, o_proj) on the block-scaled fp8 GEMM;
+        # dequant_fp8=True keeps the older load path that expands everything to bf16
+        self.fp8_compute = self.fp8 and not self.extra.get("dequant_fp8", False)
 
     def _is_moe_layer(self, i):
         return self.moe is not None and i >= self.first_dense and i % self.moe_freq == 0
@@ -141,12 +145,21 @@ class DeepseekV2LM(TransformerLM):
                 -1, self.rope_d, w.shape[-1])
             return w.view(-1, w.shape[-1])
 
+        def load_q(name):
+            # the rope rows of a head are 64 rows starting at a multiple of 64, so they stay inside one 128-row
+            # scale block and the fp8 payload can be permuted without touching the scales
+            if self.fp8_compute and (h0 * qd) % 128 == 0 and self.nope % 64 == 0 and self.rope_d == 64:
+                fw = quant.load_fp8_weight(src, name, 0, h0 * qd, h1 * qd)
+                q8 = fix_q(fw.q.view(torch.uint8)).view(torch.float8_e4m3fn)
+                return Fp8Weight(q8, fw.scale, 128).to(self.device)
+            return self._dev(fix_q(self._w(src, name, 0, h0 * qd, h1 * qd)))
+
         if self.q_lora:
             lw.q_a_w = self._dev(self._w(src, a + "q_a_proj.weight"))
             lw.q_a_norm = self._dev(src.get(a + "q_a_layernorm.weight"))
-            lw.q_b_w = self._dev(fix_q(self._w(src, a + "q_b_proj.weight", 0, h0 * qd, h1 * qd)))
+            lw.q_b_w = load_q(a + "q_b_proj.weight")
         else:
-            lw.q_b_w = self._dev(fix_q(self._w(src, a + "q_proj.weight", 0, h0 * qd, h1 * qd)))
+            lw.q_b_w = load_q(a + "q_proj.weight")
         kva = self._w(src, a + "kv_a_proj_with_mqa.weight").clone()
         kva[self.kv_lora:] = _deinterleave_rows(kva[self.kv_lora:], self.rope_d)
         if self.q_lora:  # one GEMM produces the q latent and the kv latent
@@ -160,10 +173,24 @@ class DeepseekV2LM(TransformerLM):
         # W_UK as [h, kv_lora, nope] (q_lat = q_nope . W_UK: contraction over nope), W_UV as [h, v, kv_lora]
         lw.w_uk = self._dev(kvb[:, : self.nope].transpose(1, 2))
         lw.w_uv = self._dev(kvb[:, self.nope:])
-        lw.o_w = self._dev(self._w(src, a + "o_proj.weight", 1, h0 * self.v_dim, h1 * self.v_dim))
+        if self.fp8_compute and (h0 * self.v_dim) % 128 == 0:
+            lw.o_w = quant.load_fp8_weight(src, a + "o_proj.weight", 1, h0 * self.v_dim, h1 * self.v_dim).to(self.device)
+        else:
+            lw.o_w = self._dev(self._w(src, a + "o_proj.weight", 1, h0 * self.v_dim, h1 * self.v_dim))
 
     def _load_dense_ffn(self, lw, src, prefix, inter, tp=None, r=None):
-        super()._load_dense_ffn(lw, quant.DequantSource(src, self.dtype) if self.fp8 else src, prefix, inter, tp, r)
+        raw = getattr(src, "base", src)
+        tp_ = self.tp.size if tp is None else tp
+        r_ = self.tp.rank if r is None else r
+        i0, i1 = tp_range(inter, r_, tp_)
+        if self.fp8_compute and i0 % 128 == 0 and (i1 - i0) % 128 == 0 and self.act == "silu":
+            g = quant.load_fp8_weight(raw, prefix + "gate_proj.weight", 0, i0, i1)
+            u = quant.load_fp8_weight(raw, prefix + "up_proj.weight", 0, i0, i1)
+            lw.gate_up_w = interleave_gate_up_fp8(g, u).to(self.device)
+            lw.gate_up_fused = True
+            lw.down_w = quant.load_fp8_weight(raw, prefix + "down_proj.weight", 1, i0, i1).to(self.device)
+            return
+        super()._load_dense_ffn(lw, quant.DequantSource(raw, self.dtype) if self.fp8 else raw, prefix, inter, tp, r)
 
     def _load_ffn(self, lw, src, p, layer):
         if self._is_moe_layer(layer):

@@ -71,15 +71,33 @@ def load_experts(model, lw, src, prefix: str, mc: MoEConfig, ep: bool, gate_name
     else:
         e0, e1 = 0, mc.num_experts
         i0, i1 = tp_range(mc.inter, r, tp)
-    w13, w2 = [], []
-    for e in range(e0, e1):
+    raw = getattr(src, "base", src)  # the fp8 payload lives under a de-quantising view
+    if getattr(model, "fp8_compute", False) and i0 % 128 == 0 and (i1 - i0) % 128 == 0 and mc.act == "silu":
+        # keep the experts in e4m3 with their block scales: grouped fp8 GEMMs, half the weight bytes
+        from ..models import quant
+        from ..ops import fp8
+
+        w13, w2 = [], []
+        for e in range(e0, e1):
+            q = prefix + f"{experts_name}.{e}."
+            g = quant.load_fp8_weight(raw, q + "gate_proj.weight", 0, i0, i1)
+            u = quant.load_fp8_weight(raw, q + "up_proj.weight", 0, i0, i1)
+            w13.append(fp8.interleave_gate_up_fp8(g, u))
+            w2.append(quant.load_fp8_weight(raw, q + "down_proj.weight", 1, i0, i1))
+        lw.w13 = fp8.Fp8Experts(fp8.stack_experts(w13), e1 - e0).to(model.device)
+        lw.w2 = fp8.Fp8Experts(fp8.stack_experts(w2), e1 - e0).to(model.device)
+        w13 = w2 = None
+    else:
+        w13, w2 = [], []
+    for e in range(e0, e1) if w13 is not None else ():
         q = prefix + f"{experts_name}.{e}."
         g = src.get(q + "gate_proj.weight", 0, i0, i1)
         u = src.get(q + "up_proj.weight", 0, i0, i1)
         w13.append(ref.interleave_gate_up(g, u))
         w2.append(src.get(q + "down_proj.weight", 1, i0, i1))
-    lw.w13 = dev(torch.stack(w13))
-    lw.w2 = dev(torch.stack(w2))
+    if w13 is not None:
+        lw.w13 = dev(torch.stack(w13))
+        lw.w2 = dev(torch.stack(w2))
     lw.e0 = e0 if (ep and tp > 1) else 0
     lw.ep_world = tp if ep else 1
     lw.is_moe = True

@@ -66,6 +66,15 @@ def load_fp8(src, name: str, dim: Optional[int] = None, start: int = 0, end: Opt
     return quant_block(w)
 
 
+def load_fp8_weight(src, name: str, dim: Optional[int] = None, start: int = 0, end: Optional[int] = None):
+    """Fp8Weight (e4m3 payload + 128 x 128 block scales) of a checkpoint tensor slice; bf16 checkpoints are
+    quantised on the fly (`--quant_type fp8w8a8-b128` on an unquantised model)."""
+    from ..ops.fp8 import Fp8Weight
+
+    q, s = load_fp8(src, name, dim, start, end)
+    return Fp8Weight(q.contiguous(), s.contiguous().float(), BLOCK)
+
+
 class DequantSource:
     """WeightSource view that hands out bf16 tensors for fp8 block-quantised entries."""
 

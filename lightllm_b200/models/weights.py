@@ -94,7 +94,7 @@ class SafetensorsSource(WeightSource):
 class RandomSource(WeightSource):
     """Deterministic N(0, std) tensors keyed by name: every rank that asks for a name sees the same
     full tensor, so TP=n output can be checked against TP=1.  Norm weights are ones.  fp8 weights
-    are generated as e4m3 payload plus `*_scale_inv` ~ U(0.5, 2)/448 block scales."""
+    are generated as e4m3 payload ~ N(0, 96) plus `*_scale_inv` ~ U(0.5, 2) * std / 96 block scales."""
 
     def __init__(self, shapes: Dict[str, tuple], dtype=torch.bfloat16, std: float = 0.02, seed: int = 0,
                  device: str = "cpu", fp8_names: Optional[set] = None):
@@ -125,7 +125,7 @@ class RandomSource(WeightSource):
         if name.endswith("norm.weight") or name.endswith("layernorm.weight") or name.endswith("_norm.weight"):
             t = torch.ones(shape, dtype=self.dtype, device=self.device)
         elif name.endswith("_scale_inv"):
-            t = (torch.rand(shape, generator=self._gen(name), device=self.device, dtype=torch.float32) * 1.5 + 0.5) / 448.0
+            t = (torch.rand(shape, generator=self._gen(name), device=self.device, dtype=torch.float32) * 1.5 + 0.5) * (self.std / 96.0)
         elif name in self.fp8_names:
             t = (torch.randn(shape, generator=self._gen(name), device=self.device, dtype=torch.float32) * 96.0)
             t = t.clamp(-448, 448).to(torch.float8_e4m3fn)

@@ -112,6 +112,25 @@ def stack_experts(ws) -> Fp8Weight:
     return Fp8Weight(torch.cat([w.q.view(torch.uint8) for w in ws], 0).view(FP8), torch.cat([w.scale for w in ws], 0), g)
 
 
+class Fp8Experts:
+    """E expert matrices [N, K] stacked along the rows of one Fp8Weight (the grouped GEMM's weight operand)."""
+
+    def __init__(self, stacked: Fp8Weight, E: int):
+        assert stacked.shape[0] % E == 0
+        self.w, self.E = stacked, E
+        self.shape = (E, stacked.shape[0] // E, stacked.shape[1])
+        self.device, self.dtype = stacked.device, torch.bfloat16
+
+    def to(self, device) -> "Fp8Experts":
+        return Fp8Experts(self.w.to(device), self.E)
+
+    def dequant(self) -> torch.Tensor:
+        return self.w.dequant().view(*self.shape)
+
+    def nbytes(self) -> int:
+        return self.w.nbytes()
+
+
 def quant_act(x: torch.Tensor):
     """bf16 [M, K] -> (e4m3 [M, K], scale [ceil(K/128), M]).  CUDA: one warp per (token, group)."""
     if not x.is_cuda:

@@ -162,7 +162,10 @@ def fused_experts(x, w13, w2, ids, weights, act="silu", e0: int = 0, out=None, a
 
     w13 [E_local, 2I, H] with gate/up rows interleaved in 32-row blocks, w2 [E_local, H, I].  On CUDA: align
     -> gather -> grouped GEMM with gated epilogue -> grouped GEMM -> weighted combine (5 launches)."""
+    fp8_w = type(w13).__name__ == "Fp8Experts"
     if not x.is_cuda:
+        if fp8_w:  # CPU: same arithmetic with the de-quantised weights
+            w13, w2 = w13.dequant().to(x.dtype), w2.dequant().to(x.dtype)
         r = ref_fused_experts(x, w13, w2, ids, weights, act, e0, b13=b13, b2=b2)
         if out is not None:
             if accumulate:
@@ -180,7 +183,18 @@ def fused_experts(x, w13, w2, ids, weights, act="silu", e0: int = 0, out=None, a
     check(kernels().llb_moe_gather(ptr(a), ptr(x), ptr(lay.sorted_pair), ptr(lay.total_rows), c_int(k), c_int(H),
                                    i64(x.stride(0)), c_int(lay.m_pad), stream()), "moe_gather")
     _count()
-    if b13 is None and act in ("silu", "gelu"):
+    if fp8_w:
+        # block-scaled e4m3 experts: quantise the gathered rows per token group, grouped fp8 GEMM with the SwiGLU
+        # epilogue, quantise again, grouped fp8 GEMM (reference: lightllm/common/basemodel/layer_weights/
+        # meta_weights/fused_moe/impl/deepgemm_impl.py, the masked / contiguous m_grouped_fp8_gemm_nt path)
+        from . import fp8
+
+        assert act == "silu" and b13 is None and b2 is None, "fp8 experts: SwiGLU without bias"
+        aq, asc = fp8.quant_act(a)
+        h = fp8.gemm_fp8_quantized(aq, asc, w13.w, "gated_silu", mblock_expert=lay.mblock_expert, n_per_expert=N13)
+        hq, hsc = fp8.quant_act(h)
+        y = fp8.gemm_fp8_quantized(hq, hsc, w2.w, "store", mblock_expert=lay.mblock_expert, n_per_expert=H)
+    elif b13 is None and act in ("silu", "gelu"):
         h = gemm_grouped(a, w13, lay.mblock_expert, N13, epi="gated_" + act)
     else:  # biased experts / clamped SwiGLU: plain grouped GEMM, then bias + activation in one pass
         h13 = gemm_grouped(a, w13, lay.mblock_expert, N13, epi="store")
@@ -189,7 +203,8 @@ def fused_experts(x, w13, w2, ids, weights, act="silu", e0: int = 0, out=None, a
         check(kernels().llb_moe_bias_act(ptr(h13), ptr(b13), ptr(lay.mblock_expert), ptr(h), c_int(lay.m_pad), c_int(I),
                                          c_int(kind), f32(1.702), f32(7.0), stream()), "moe_bias_act")
         _count()
-    y = gemm_grouped(h, w2, lay.mblock_expert, H, epi="store")
+    if not fp8_w:
+        y = gemm_grouped(h, w2, lay.mblock_expert, H, epi="store")
     if b2 is not None:
         check(kernels().llb_moe_add_bias(ptr(y), ptr(b2), ptr(lay.mblock_expert), c_int(lay.m_pad), c_int(H), stream()),
               "moe_add_bias")

@@ -61,6 +61,7 @@ def _build_model_and_backend(args: StartArgs, ps):
                       graph_grow_step_size=args.graph_grow_step_size,
                       graph_max_len_in_batch=args.graph_max_len_in_batch or None, tp_fused=fused,
                       enable_ep_moe=args.enable_ep_moe, quant_type=args.quant_type,
+                      quant_cfg=getattr(args, "quant_cfg", None), expert_dtype=getattr(args, "expert_dtype", None),
                       extra_kv_layers=_mtp_modules(args),
                       tpsp_mix_mode=bool(getattr(args, "enable_tpsp_mix_mode", False)))
     eos = args.eos_ids or args.eos_id or cfg.get("eos_token_id") or []

@@ -93,3 +93,99 @@ def test_gpu_fp8_gated_and_grouped(dev):
     assert _rel(got_d[:128], hd[:128] @ wd[3 * K:4 * K].t()) < 6e-3
     assert _rel(got_d[128:], hd[128:] @ wd[K:2 * K].t()) < 6e-3
     assert int(ops.gemm_status(dev).item()) == 0
+
+
+DSV3_FP8 = dict(model_type="deepseek_v3", hidden_size=512, intermediate_size=1024, moe_intermediate_size=256,
+                num_hidden_layers=3, num_attention_heads=4, q_lora_rank=256, kv_lora_rank=512, qk_nope_head_dim=128,
+                qk_rope_head_dim=64, v_head_dim=128, n_routed_experts=8, num_experts_per_tok=2, n_shared_experts=1,
+                first_k_dense_replace=1, moe_layer_freq=1, n_group=2, topk_group=1, vocab_size=1024,
+                rms_norm_eps=1e-6, rope_theta=10000.0, routed_scaling_factor=2.5, norm_topk_prob=True, eos_token_id=2,
+                quantization_config=dict(quant_method="fp8", weight_block_size=[128, 128]))
+
+
+def _prefill_logits(device, source=None, **kw):
+    from lightllm_b200.common.infer_state import ModelInput
+    from lightllm_b200.models.registry import get_model
+    from lightllm_b200.parallel import dist as pdist
+
+    m = get_model(DSV3_FP8, pstate=pdist.ParallelState(device=device), max_total_token_num=512, max_req_num=4,
+                  max_seq_length=128, random_seed=3, disable_cudagraph=True, weight_source=source, **kw)
+    ids = torch.randint(3, 1000, (40,), generator=torch.Generator().manual_seed(0))
+    req = m.req_manager.alloc()
+    slots = m.mem_manager.alloc(len(ids))
+    mi = ModelInput(batch_size=1, total_token_num=len(ids), max_kv_len=len(ids), is_prefill=True,
+                    b_req_idx=torch.tensor([req], dtype=torch.int32),
+                    b_seq_len=torch.tensor([len(ids)], dtype=torch.int32), mem_indexes=slots.clone(), input_ids=ids,
+                    b_ready_cache_len=torch.zeros(1, dtype=torch.int32), max_q_len=len(ids), return_all_logits=True)
+    return m, m.forward(mi).logits.float().cpu()
+
+
+def test_deepseek_fp8_checkpoint_runs_on_fp8_weights_cpu():
+    """An fp8 block-quantised checkpoint keeps its experts, dense FFN, q_b and o_proj in e4m3 (half the bytes) and
+    stays close to the path that expands everything to bf16 (the difference is the activation quantisation)."""
+    m8, a = _prefill_logits(torch.device("cpu"))
+    m16, b = _prefill_logits(torch.device("cpu"), source=m8.weight_source, dequant_fp8=True)
+    assert type(m8.layers[1].w13).__name__ == "Fp8Experts" and type(m8.layers[0].gate_up_w).__name__ == "Fp8Weight"
+    assert type(m8.layers[0].o_w).__name__ == "Fp8Weight" and type(m8.layers[0].q_b_w).__name__ == "Fp8Weight"
+    assert isinstance(m16.layers[1].w13, torch.Tensor)
+    assert m8.param_bytes() < 0.7 * m16.param_bytes()
+    assert ((a - b).norm() / b.norm()).item() < 0.25
+
+
+@pytest.mark.gpu
+def test_deepseek_fp8_gpu_matches_cpu(dev):
+    mc, c = _prefill_logits(torch.device("cpu"))
+    mg, g = _prefill_logits(dev, source=mc.weight_source)
+    assert type(mg.layers[1].w13).__name__ == "Fp8Experts"
+    # same quantised operands on both sides; a router near-tie can still flip an expert for a token
+    assert ((g - c).norm() / c.norm()).item() < 0.1
+    assert int(ops.gemm_status(dev).item()) == 0
+
+
+@pytest.mark.parametrize("family", ["llama", "qwen3_moe"])
+def test_online_fp8_quantisation_of_bf16_checkpoints_cpu(family, tmp_path):
+    """`--quant_type fp8w8a8*` on an unquantised model: the big matrices become block-scaled e4m3 at load and the
+    logits stay close to the unquantised network; a `--quant_cfg` YAML can keep single layers in bf16."""
+    from lightllm_b200.common.infer_state import ModelInput
+    from lightllm_b200.common.quantization import QuantConfig, canonical
+    from lightllm_b200.models.registry import get_model
+    from lightllm_b200.parallel import dist as pdist
+
+    cfgs = {
+        "llama": dict(model_type="llama", hidden_size=256, intermediate_size=512, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=2, rms_norm_eps=1e-5, vocab_size=1024),
+        "qwen3_moe": dict(model_type="qwen3_moe", hidden_size=256, intermediate_size=512, moe_intermediate_size=128,
+                          num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+                          num_experts=8, num_experts_per_tok=2, norm_topk_prob=True, decoder_sparse_step=1,
+                          mlp_only_layers=[], vocab_size=1024),
+    }
+    ids = torch.randint(3, 1000, (33,), generator=torch.Generator().manual_seed(0))
+
+    def run(source=None, **kw):
+        m = get_model(cfgs[family], pstate=pdist.ParallelState(device=torch.device("cpu")), max_total_token_num=256,
+                      max_req_num=2, max_seq_length=64, random_seed=1, weight_source=source, **kw)
+        req, slots = m.req_manager.alloc(), m.mem_manager.alloc(len(ids))
+        mi = ModelInput(batch_size=1, total_token_num=len(ids), max_kv_len=len(ids), is_prefill=True,
+                        b_req_idx=torch.tensor([req], dtype=torch.int32),
+                        b_seq_len=torch.tensor([len(ids)], dtype=torch.int32), mem_indexes=slots.clone(),
+                        input_ids=ids, b_ready_cache_len=torch.zeros(1, dtype=torch.int32), max_q_len=len(ids),
+                        return_all_logits=True)
+        return m, m.forward(mi).logits.float()
+
+    m16, want = run()
+    m8, got = run(source=m16.weight_source, quant_type="fp8w8a8")
+    assert type(m8.layers[0].qkv_w).__name__ == "Fp8Weight" and type(m8.layers[1].o_w).__name__ == "Fp8Weight"
+    if family == "qwen3_moe":
+        assert type(m8.layers[0].w13).__name__ == "Fp8Experts"
+    else:
+        assert m8.layers[0].gate_up_w.ws_rows == 32
+    assert ((got - want).norm() / want.norm()).item() < 0.2
+    y = tmp_path / "q.yaml"
+    y.write_text("quant_type: fp8w8a8-b128\nmix_bits:\n  - layer_nums: [1]\n    quant_type: none\n")
+    mm, _ = run(source=m16.weight_source, quant_cfg=str(y))
+    assert type(mm.layers[0].qkv_w).__name__ == "Fp8Weight" and isinstance(mm.layers[1].qkv_w, torch.Tensor)
+    assert canonical("fp8w8a8-b128-deepgemm") == "fp8w8a8-b128"
+    with pytest.raises(NotImplementedError):
+        canonical("awq_marlin")
+    assert QuantConfig({"quantization_config": {"quant_method": "fp8", "weight_block_size": [128, 128]}}).default == \
+        "fp8w8a8-b128"
