@@ -68,23 +68,30 @@ typedef __nv_bfloat162 bf162;
 __host__ __device__ __forceinline__ int cdiv(int a, int b) { return (a + b - 1) / b; }
 __host__ __device__ __forceinline__ int64_t cdiv64(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
-// 16-byte vector of 8 bf16 values.
+// 16-byte vector of 8 bf16 values.  Plain words, so that the type is trivially copyable and a load or store of
+// it is one 128-bit access (a member of type bf162 has user-provided copy operations, which made every struct
+// assignment four separate 32-bit stores).
 struct alignas(16) bf16x8 {
-  bf162 v[4];
+  uint32_t w[4];
 };
 
 __device__ __forceinline__ void unpack8(const bf16x8& p, float* f) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(&p);
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    float2 t = __bfloat1622float2(p.v[i]);
-    f[2 * i] = t.x;
-    f[2 * i + 1] = t.y;
+    // a bf16 is the upper half of an fp32
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
   }
 }
 __device__ __forceinline__ bf16x8 pack8(const float* f) {
   bf16x8 p;
 #pragma unroll
-  for (int i = 0; i < 4; ++i) p.v[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  for (int i = 0; i < 4; ++i) {
+    const bf162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    p.w[i] = *reinterpret_cast<const uint32_t*>(&h);
+  }
   return p;
 }
 

@@ -66,17 +66,26 @@ struct GemmParams {
   int push_world, push_rank, push_max_mb;
 };
 
+// Output staging of the epilogue warps: a thread owns one accumulator row, so storing straight from registers
+// makes every store instruction touch 32 different rows (16 bytes each).  Instead each warp parks 32 rows x 128
+// bytes of finished output in shared memory and writes them back four whole 128-byte lines per instruction
+// (residual rows are fetched the same way).  Rows are 144 bytes apart so that the 16-byte accesses of eight
+// consecutive rows fall into distinct banks.
+constexpr int EPI_ROW_PITCH = 144;
+constexpr int EPI_WARP_BYTES = 32 * EPI_ROW_PITCH;
+constexpr int EPI_STAGE_BYTES = 4 * EPI_WARP_BYTES;
+
 template <int BN>
 constexpr int stage_bytes() {
   return BM * BK * 2 + BN * BK * 2;
 }
 template <int BN>
 constexpr int num_stages() {
-  return SMEM_BUDGET / stage_bytes<BN>() > 8 ? 8 : SMEM_BUDGET / stage_bytes<BN>();
+  return (SMEM_BUDGET - EPI_STAGE_BYTES) / stage_bytes<BN>() > 8 ? 8 : (SMEM_BUDGET - EPI_STAGE_BYTES) / stage_bytes<BN>();
 }
 template <int BN>
 constexpr int smem_bytes() {
-  return num_stages<BN>() * stage_bytes<BN>() + 1024 /*align slack*/ + 256 /*barriers*/;
+  return num_stages<BN>() * stage_bytes<BN>() + 1024 /*align slack*/ + 256 /*barriers*/ + EPI_STAGE_BYTES;
 }
 
 __device__ __forceinline__ float silu_f(float v) { return v / (1.f + __expf(-v)); }
@@ -143,41 +152,153 @@ __device__ __forceinline__ void push_signal(const GemmParams& p, int row_block, 
   }
 }
 
-// Drains one accumulator tile (this thread's row, BN columns starting at TMEM address t_row) through the
-// epilogue functor EPI into C.  `add_partials(regs, col)` adds other CTAs' partial sums (stream-K) when
-// `has_add` is set.
-template <int BN, int EPI, typename AddFn>
-__device__ __forceinline__ void epilogue_store(const GemmParams& p, uint32_t t_row, int row, bool row_ok, int col_tile0,
-                                               bool has_add, AddFn add_partials) {
-  if (EPI == EPI_GATED_SILU || EPI == EPI_GATED_GELU) {
-    // columns come as [32 gate | 32 up] pairs; output has N/2 columns
-    bf16* crow = (bf16*)p.C + (int64_t)row * p.ldc;
-#pragma unroll 1
-    for (int c = 0; c < BN; c += 64) {
-      uint32_t gr[32], ur[32];
-      tmem_ld_32x32(t_row + c, gr);
-      tmem_ld_32x32(t_row + c + 32, ur);
-      tmem_wait_ld();
-      if (has_add) {
-        add_partials(gr, c);
-        add_partials(ur, c + 32);
+// Copies the warp's staged 32 x 128-byte block to global memory: `elem_bytes`-wide elements, block origin
+// (row_base, col0) of a matrix with row pitch ldc elements.
+template <int ELEM_BYTES>
+__device__ __forceinline__ void epi_flush(const GemmParams& p, const uint8_t* stage, int lane, int row_base, int col0,
+                                          bool push) {
+  constexpr int EPS = 16 / ELEM_BYTES;  // elements per 16-byte segment
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int id = i * 32 + lane, r = id >> 3, seg = id & 7;
+    const int grow = row_base + r;
+    if (grow < p.M) {
+      const uint4 v = *reinterpret_cast<const uint4*>(stage + r * EPI_ROW_PITCH + seg * 16);
+      const int64_t off = (int64_t)grow * p.ldc + col0 + seg * EPS;
+      if (push) {
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          if (q < p.push_world) *reinterpret_cast<uint4*>(p.push[q] + off) = v;
+      } else {
+        *reinterpret_cast<uint4*>((uint8_t*)p.C + off * ELEM_BYTES) = v;
       }
-      const int ocol = (col_tile0 + c) / 2;
-      if (row_ok && col_tile0 + c < p.N) {
+    }
+  }
+}
+
+// 32 accumulator columns (registers r, first column col0 of the output) of this thread's row, straight from
+// registers: used for ragged right edges and by kernels without a staging buffer.
+template <int EPI>
+__device__ __forceinline__ void epi_direct32(const GemmParams& p, const uint32_t* r, int row, bool row_ok, int col0) {
+  if (!(row_ok && col0 < p.N)) return;
+  const int ncols = min(32, p.N - col0);
+  if (EPI == EPI_F32) {
+    float* crow = (float*)p.C + (int64_t)row * p.ldc + col0;
+    if (ncols == 32) {
 #pragma unroll
-        for (int j = 0; j < 32; j += 8) {
-          float o[8];
+      for (int j = 0; j < 32; j += 4) {
+        float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
+                               __uint_as_float(r[j + 3]));
+        if (p.bias) {
+          v.x += __bfloat162float(p.bias[col0 + j]);
+          v.y += __bfloat162float(p.bias[col0 + j + 1]);
+          v.z += __bfloat162float(p.bias[col0 + j + 2]);
+          v.w += __bfloat162float(p.bias[col0 + j + 3]);
+        }
+        *reinterpret_cast<float4*>(crow + j) = v;
+      }
+    } else {
 #pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            float gv = __uint_as_float(gr[j + e]);
-            float uv = __uint_as_float(ur[j + e]);
-            o[e] = (EPI == EPI_GATED_SILU ? silu_f(gv) : gelu_tanh_f(gv)) * uv;
-          }
-          *reinterpret_cast<bf16x8*>(crow + ocol + j) = pack8(o);
+      for (int j = 0; j < 32; ++j)
+        if (j < ncols) crow[j] = __uint_as_float(r[j]) + (p.bias ? __bfloat162float(p.bias[col0 + j]) : 0.f);
+    }
+  } else {
+    bf16* crow = (bf16*)p.C + (int64_t)row * p.ldc + col0;
+    const bf16* rrow = EPI == EPI_RESIDUAL ? p.residual + (int64_t)row * p.ldc + col0 : nullptr;
+    if (ncols == 32) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        float o[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = __uint_as_float(r[j + e]);
+        if (p.bias) {
+          float bv[8];
+          unpack8(*reinterpret_cast<const bf16x8*>(p.bias + col0 + j), bv);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) o[e] += bv[e];
+        }
+        if (EPI == EPI_RESIDUAL) {
+          float rv[8];
+          unpack8(*reinterpret_cast<const bf16x8*>(rrow + j), rv);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) o[e] += rv[e];
+        }
+        if (EPI == EPI_STORE && p.push_world > 0) {
+          const bf16x8 packed = pack8(o);
+          const int64_t off = (int64_t)row * p.ldc + col0 + j;
+#pragma unroll
+          for (int q = 0; q < 8; ++q)
+            if (q < p.push_world) *reinterpret_cast<bf16x8*>(p.push[q] + off) = packed;
+        } else {
+          *reinterpret_cast<bf16x8*>(crow + j) = pack8(o);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        if (j < ncols) {
+          float v = __uint_as_float(r[j]);
+          if (p.bias) v += __bfloat162float(p.bias[col0 + j]);
+          if (EPI == EPI_RESIDUAL) v += __bfloat162float(rrow[j]);
+          crow[j] = __float2bfloat16(v);
         }
       }
     }
-  } else {
+  }
+}
+
+// Drains one accumulator tile (this thread's row, BN columns starting at TMEM address t_row) through the
+// epilogue functor EPI into C.  `add_partials(regs, col)` adds other CTAs' partial sums (stream-K) when
+// `has_add` is set.  `stage`: this warp's EPI_WARP_BYTES of shared memory (null: store from registers).
+template <int BN, int EPI, typename AddFn>
+__device__ __forceinline__ void epilogue_store(const GemmParams& p, uint32_t t_row, int row, bool row_ok, int col_tile0,
+                                               bool has_add, AddFn add_partials, uint8_t* stage = nullptr) {
+  const int lane = threadIdx.x & 31;
+  const int row_base = row - lane;
+  uint8_t* my = stage + lane * EPI_ROW_PITCH;
+  if (EPI == EPI_GATED_SILU || EPI == EPI_GATED_GELU) {
+    // columns come as [32 gate | 32 up] pairs; output has N/2 columns
+    bf16* crow = (bf16*)p.C + (int64_t)row * p.ldc;
+    constexpr int STEP = (BN % 128 == 0) ? 128 : 64;
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN; c0 += STEP) {
+      const bool staged = stage != nullptr && STEP == 128 && col_tile0 + c0 + 128 <= p.N;
+#pragma unroll
+      for (int sub = 0; sub < STEP / 64; ++sub) {
+        const int c = c0 + sub * 64;
+        uint32_t gr[32], ur[32];
+        tmem_ld_32x32(t_row + c, gr);
+        tmem_ld_32x32(t_row + c + 32, ur);
+        tmem_wait_ld();
+        if (has_add) {
+          add_partials(gr, c);
+          add_partials(ur, c + 32);
+        }
+        const int ocol = (col_tile0 + c) / 2;
+        if (staged || (row_ok && col_tile0 + c < p.N)) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            float o[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              float gv = __uint_as_float(gr[j + e]);
+              float uv = __uint_as_float(ur[j + e]);
+              o[e] = (EPI == EPI_GATED_SILU ? silu_f(gv) : gelu_tanh_f(gv)) * uv;
+            }
+            if (staged)
+              *reinterpret_cast<bf16x8*>(my + sub * 64 + j * 2) = pack8(o);
+            else
+              *reinterpret_cast<bf16x8*>(crow + ocol + j) = pack8(o);
+          }
+        }
+      }
+      if (staged) {
+        __syncwarp();
+        epi_flush<2>(p, stage, lane, row_base, (col_tile0 + c0) / 2, false);
+        __syncwarp();
+      }
+    }
+  } else if (EPI == EPI_F32) {
 #pragma unroll 1
     for (int c = 0; c < BN; c += 32) {
       uint32_t r[32];
@@ -185,71 +306,77 @@ __device__ __forceinline__ void epilogue_store(const GemmParams& p, uint32_t t_r
       tmem_wait_ld();
       if (has_add) add_partials(r, c);
       const int col0 = col_tile0 + c;
-      if (row_ok && col0 < p.N) {
-        const int ncols = min(32, p.N - col0);
-        if (EPI == EPI_F32) {
-          float* crow = (float*)p.C + (int64_t)row * p.ldc + col0;
-          if (ncols == 32) {
+      if (stage != nullptr && col0 + 32 <= p.N) {
 #pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
-                                     __uint_as_float(r[j + 3]));
-              if (p.bias) {
-                v.x += __bfloat162float(p.bias[col0 + j]);
-                v.y += __bfloat162float(p.bias[col0 + j + 1]);
-                v.z += __bfloat162float(p.bias[col0 + j + 2]);
-                v.w += __bfloat162float(p.bias[col0 + j + 3]);
-              }
-              *reinterpret_cast<float4*>(crow + j) = v;
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (j < ncols) crow[j] = __uint_as_float(r[j]) + (p.bias ? __bfloat162float(p.bias[col0 + j]) : 0.f);
+        for (int j = 0; j < 32; j += 4) {
+          float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
+                                 __uint_as_float(r[j + 3]));
+          if (p.bias) {
+            v.x += __bfloat162float(p.bias[col0 + j]);
+            v.y += __bfloat162float(p.bias[col0 + j + 1]);
+            v.z += __bfloat162float(p.bias[col0 + j + 2]);
+            v.w += __bfloat162float(p.bias[col0 + j + 3]);
           }
-        } else {
-          bf16* crow = (bf16*)p.C + (int64_t)row * p.ldc + col0;
-          const bf16* rrow = EPI == EPI_RESIDUAL ? p.residual + (int64_t)row * p.ldc + col0 : nullptr;
-          if (ncols == 32) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 8) {
-              float o[8];
-#pragma unroll
-              for (int e = 0; e < 8; ++e) o[e] = __uint_as_float(r[j + e]);
-              if (p.bias) {
-                float bv[8];
-                unpack8(*reinterpret_cast<const bf16x8*>(p.bias + col0 + j), bv);
-#pragma unroll
-                for (int e = 0; e < 8; ++e) o[e] += bv[e];
-              }
-              if (EPI == EPI_RESIDUAL) {
-                float rv[8];
-                unpack8(*reinterpret_cast<const bf16x8*>(rrow + j), rv);
-#pragma unroll
-                for (int e = 0; e < 8; ++e) o[e] += rv[e];
-              }
-              if (EPI == EPI_STORE && p.push_world > 0) {
-                const bf16x8 packed = pack8(o);
-                const int64_t off = (int64_t)row * p.ldc + col0 + j;
-#pragma unroll
-                for (int q = 0; q < 8; ++q)
-                  if (q < p.push_world) *reinterpret_cast<bf16x8*>(p.push[q] + off) = packed;
-              } else {
-                *reinterpret_cast<bf16x8*>(crow + j) = pack8(o);
-              }
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              if (j < ncols) {
-                float v = __uint_as_float(r[j]);
-                if (p.bias) v += __bfloat162float(p.bias[col0 + j]);
-                if (EPI == EPI_RESIDUAL) v += __bfloat162float(rrow[j]);
-                crow[j] = __float2bfloat16(v);
-              }
-            }
-          }
+          *reinterpret_cast<float4*>(my + j * 4) = v;
         }
+        __syncwarp();
+        epi_flush<4>(p, stage, lane, row_base, col0, false);
+        __syncwarp();
+      } else {
+        epi_direct32<EPI>(p, r, row, row_ok, col0);
+      }
+    }
+  } else {
+#pragma unroll 1
+    for (int c = 0; c < BN; c += 64) {
+      const int col0 = col_tile0 + c;
+      const bool staged = stage != nullptr && col0 + 64 <= p.N;
+      if (staged && EPI == EPI_RESIDUAL) {  // residual rows: whole lines into the staging block
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int id = i * 32 + lane, r = id >> 3, seg = id & 7;
+          const int grow = row_base + r;
+          uint4 v = make_uint4(0u, 0u, 0u, 0u);
+          if (grow < p.M) v = *reinterpret_cast<const uint4*>(p.residual + (int64_t)grow * p.ldc + col0 + seg * 8);
+          *reinterpret_cast<uint4*>(stage + r * EPI_ROW_PITCH + seg * 16) = v;
+        }
+        __syncwarp();
+      }
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_row + c + half * 32, r);
+        tmem_wait_ld();
+        if (has_add) add_partials(r, c + half * 32);
+        if (!staged) {
+          epi_direct32<EPI>(p, r, row, row_ok, col0 + half * 32);
+          continue;
+        }
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+          float o[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) o[e] = __uint_as_float(r[j + e]);
+          if (p.bias) {
+            float bv[8];
+            unpack8(*reinterpret_cast<const bf16x8*>(p.bias + col0 + half * 32 + j), bv);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) o[e] += bv[e];
+          }
+          bf16x8* slot = reinterpret_cast<bf16x8*>(my + half * 64 + j * 2);
+          if (EPI == EPI_RESIDUAL) {
+            float rv[8];
+            unpack8(*slot, rv);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) o[e] += rv[e];
+          }
+          *slot = pack8(o);
+        }
+      }
+      if (staged) {
+        __syncwarp();
+        epi_flush<2>(p, stage, lane, row_base, col0, EPI == EPI_STORE && p.push_world > 0);
+        __syncwarp();
       }
     }
   }
@@ -391,6 +518,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int lane_grp = warp & 3;  // TMEM lanes 32*lane_grp .. +31 are the ones this warp may read
     const int erow = lane_grp * 32 + lane;  // row inside the tile owned by this thread
     const int etid = threadIdx.x - 64;      // 0..127 among the epilogue threads
+    uint8_t* epi_stage = smem_raw + (bar_base + 256 - smem_u32(smem_raw)) + lane_grp * EPI_WARP_BYTES;
     __shared__ int sk_last_flag;
     int it = 0;
     SegIter segs(p.stream_k != 0, blockIdx.x, gridDim.x, num_tiles, k_blocks);
@@ -471,9 +599,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (p.batch_count > 1) {
           GemmParams pb = p;
           pb.C = (bf16*)p.C + (int64_t)batch * p.c_batch_stride;
-          epilogue_store<BN, EPI>(pb, t_row, row, row_ok, nb * BN, false, add_partials);
+          epilogue_store<BN, EPI>(pb, t_row, row, row_ok, nb * BN, false, add_partials, epi_stage);
         } else {
-          epilogue_store<BN, EPI>(p, t_row, row, row_ok, nb * BN, n_other != 0, add_partials);
+          epilogue_store<BN, EPI>(p, t_row, row, row_ok, nb * BN, n_other != 0, add_partials, epi_stage);
           if (EPI == EPI_STORE) push_signal(p, mb, min(BN, p.N - nb * BN));
         }
       }
@@ -586,8 +714,8 @@ int dispatch_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tb, GemmPara
 constexpr int PAIR_BN = 256;       // tile width (W rows per pair tile)
 constexpr int PAIR_HALF = 128;     // W rows loaded by each CTA
 constexpr int PAIR_STAGE_BYTES = BM * BK * 2 + PAIR_HALF * BK * 2;  // 32 KB
-constexpr int PAIR_STAGES = 7;
-constexpr int pair_smem_bytes() { return PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 512; }
+constexpr int PAIR_STAGES = 6;
+constexpr int pair_smem_bytes() { return PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 512 + EPI_STAGE_BYTES; }
 
 template <int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
@@ -704,6 +832,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     const int lane_grp = warp & 3;
     const int erow = lane_grp * 32 + lane;
     const uint32_t tempty_leader = map_to_cta(tempty_bar(0), 0);
+    uint8_t* epi_stage = smem_raw + (bar_base + 256 - smem_u32(smem_raw)) + lane_grp * EPI_WARP_BYTES;
     int it = 0;
     for (int tile = pair; tile < num_tiles; tile += num_pairs, ++it) {
       int mb, nb;
@@ -714,7 +843,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       tc_fence_after();
       const int row = mb * 256 + (int)cta * BM + erow;
       const uint32_t t_row = tmem_base + ((uint32_t)(lane_grp * 32) << 16) + acc * PAIR_BN;
-      epilogue_store<PAIR_BN, EPI>(p, t_row, row, row < p.M, nb * PAIR_BN, false, [](uint32_t*, int) {});
+      epilogue_store<PAIR_BN, EPI>(p, t_row, row, row < p.M, nb * PAIR_BN, false, [](uint32_t*, int) {}, epi_stage);
       if (EPI == EPI_STORE) push_signal(p, mb * 2 + (int)cta, min(PAIR_BN, p.N - nb * PAIR_BN));
       tc_fence_before();
       __syncwarp();
@@ -811,7 +940,7 @@ constexpr int sk_stage_bytes() { return BM * BK * 2 + NB * (TW / 2) * BK * 2; }
 template <int NB, int TW>
 constexpr int sk_stages() { return NB == 1 ? (TW == 128 ? 8 : 6) : 4; }
 template <int NB, int TW>
-constexpr int sk_smem_bytes() { return sk_stages<NB, TW>() * sk_stage_bytes<NB, TW>() + 1024 + 512; }
+constexpr int sk_smem_bytes() { return sk_stages<NB, TW>() * sk_stage_bytes<NB, TW>() + 1024 + 512 + EPI_STAGE_BYTES; }
 
 // No memory clobber: the caller orders these loads after the cluster barrier (both are volatile asm), and
 // several of them must be allowed in flight at once.
@@ -942,9 +1071,11 @@ gemm_bf16_skinny_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     const int row = m0 + (int)half * BM + erow;
     const uint32_t t_row = tmem_base + ((uint32_t)(lane_grp * 32) << 16);
     if (splits == 1) {
+      uint8_t* epi_stage = smem_raw + (bar_base + 256 - smem_u32(smem_raw)) + lane_grp * EPI_WARP_BYTES;
 #pragma unroll
       for (int j = 0; j < NB; ++j)
-        epilogue_store<TW, EPI>(p, t_row + j * TW, row, row < p.M, n0 + j * TW, false, [](uint32_t*, int) {});
+        epilogue_store<TW, EPI>(p, t_row + j * TW, row, row < p.M, n0 + j * TW, false, [](uint32_t*, int) {},
+                                epi_stage);
       if (EPI == EPI_STORE) push_signal(p, mb * 2 + (int)half, max(0, min(TW * NB, p.N - n0)));
     } else {
       float* R = reinterpret_cast<float*>(smem_gen) + (size_t)erow * SK_RSTRIDE;

@@ -255,7 +255,7 @@ __global__ void __launch_bounds__(256) embedding_kernel(bf16* __restrict__ out, 
   bf16x8* dst = reinterpret_cast<bf16x8*>(out) + (int64_t)t * H_vec;
   bf16x8 z;
 #pragma unroll
-  for (int i = 0; i < 4; ++i) z.v[i] = __floats2bfloat162_rn(0.f, 0.f);
+  for (int i = 0; i < 4; ++i) z.w[i] = 0u;
   for (int v = threadIdx.x; v < H_vec; v += blockDim.x) dst[v] = in ? src[v] : z;
 }
 
