@@ -529,6 +529,20 @@ LLB_EXPORT int llb_gqa_decode(const void* q, int64_t q_stride, const void* kv_la
   return LLB_OK;
 }
 
+// tcgen05 kernel for head size 128 (attention_tc.cu); LLB_ATTN_TC=0 keeps the mma.sync kernel below
+LLB_EXPORT int llb_gqa_prefill_tc(const void* q, int64_t q_stride, const void* kv_layer, const int* req_to_token,
+                                  int64_t r2t_stride, const int* b_req_idx, const int* cu_q, const int* b_ready_len,
+                                  void* out, int64_t out_stride, int B, int max_q_len, int Hq, int Hkv, float sm_scale,
+                                  cudaStream_t st);
+static bool attn_tc_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("LLB_ATTN_TC");
+    on = (e == nullptr || e[0] != '0') ? 1 : 0;
+  }
+  return on == 1;
+}
+
 // q [T, Hq, D] new tokens of all requests back to back (cu_q [B+1]); out same layout.
 LLB_EXPORT int llb_gqa_prefill(const void* q, int64_t q_stride, const void* kv_layer, const int* req_to_token,
                                int64_t r2t_stride, const int* b_req_idx, const int* cu_q, const int* b_ready_len,
@@ -536,6 +550,10 @@ LLB_EXPORT int llb_gqa_prefill(const void* q, int64_t q_stride, const void* kv_l
                                float sm_scale, cudaStream_t st) {
   if (B <= 0 || max_q_len <= 0) return LLB_OK;
   if (Hkv <= 0 || Hq % Hkv != 0) return LLB_ERR_BAD_ARG;
+  if (D == 128 && attn_tc_enabled() && (q_stride % 8) == 0 && (out_stride % 8) == 0 && ((uintptr_t)q & 15) == 0 &&
+      ((uintptr_t)out & 15) == 0)
+    return llb_gqa_prefill_tc(q, q_stride, kv_layer, req_to_token, r2t_stride, b_req_idx, cu_q, b_ready_len, out,
+                              out_stride, B, max_q_len, Hq, Hkv, sm_scale, st);
   dim3 grid((max_q_len + 63) / 64, Hq, B);
   const float sl2 = sm_scale * kLog2e;
 #define LAUNCH_PREFILL(DD)                                                                                       \

@@ -1,0 +1,55 @@
+"""CUDA-event timing of the prefill attention kernels (tcgen05 kernel vs the mma.sync kernel selected with
+LLB_ATTN_TC=0) on Llama-3-8B head geometry, causal prompts of equal length.
+
+    python -m lightllm_b200.utils.attn_bench [--B 16 --len 1024 --reps 5]
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import torch
+
+
+def main():
+    from lightllm_b200 import ops
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--B", type=int, default=16)
+    ap.add_argument("--len", type=int, default=1024)
+    ap.add_argument("--ready", type=int, default=0, help="cached prefix length of every request")
+    ap.add_argument("--reps", type=int, default=5)
+    ap.add_argument("--hq", type=int, default=32)
+    ap.add_argument("--hkv", type=int, default=8)
+    a = ap.parse_args()
+    dev = torch.device("cuda")
+    Hq, Hkv, D, B, L, R = a.hq, a.hkv, 128, a.B, a.len, a.ready
+    T = B * L
+    total = B * (L + R)
+    kv = (torch.randn(total + 1, 2 * Hkv, D, device=dev) * 0.5).bfloat16()
+    r2t = torch.arange(total, dtype=torch.int32, device=dev).view(B, L + R)
+    b_req = torch.arange(B, dtype=torch.int32, device=dev)
+    cu = torch.arange(0, T + 1, L, dtype=torch.int32, device=dev)
+    ready = torch.full((B,), R, dtype=torch.int32, device=dev)
+    q = torch.randn(T, Hq * D, device=dev).bfloat16()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    for _ in range(3):
+        ops.gqa_prefill(q, kv, r2t, b_req, cu, ready, Hq, Hkv, D, L)
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(a.reps):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        ops.gqa_prefill(q, kv, r2t, b_req, cu, ready, Hq, Hkv, D, L)
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    ts.sort()
+    t = ts[len(ts) // 2]
+    flops = 4 * B * Hq * D * (L * L / 2 + L * R)
+    print(json.dumps({"B": B, "len": L, "ready": R, "ms": round(t, 4), "tflops": round(flops / t / 1e9, 1)}))
+
+
+if __name__ == "__main__":
+    main()

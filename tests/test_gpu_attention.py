@@ -70,3 +70,27 @@ def test_prefill(dev, Hq, Hkv, D):
     want = ref.gqa_prefill(q.reshape(T, Hq, D), kv, r2t, rows, cu, rdy, Hq, Hkv, D)
     err = (got.float() - want.float()).abs().max().item()
     assert err < 2e-2, f"max abs err {err}"
+
+
+@pytest.mark.parametrize("Hq,Hkv", [(8, 2), (4, 1)])
+def test_prefill_many_kv_tiles(dev, Hq, Hkv):
+    """Head size 128 on the tcgen05 kernel: several 128-key tiles per query tile (both K/V stages and both score
+    buffers wrap around), a long cached prefix, tile-unaligned lengths."""
+    from lightllm_b200.ops._native import kernels
+
+    D = 128
+    ready = [0, 300, 1000, 5]
+    new = [1024, 500, 130, 260]
+    lens = [r + n for r, n in zip(ready, new)]
+    kv, r2t, rows = _pool(dev, 6, lens, Hkv, D, 7)
+    T = sum(new)
+    torch.manual_seed(8)
+    q = torch.randn(T, Hq * D, device=dev, dtype=BF)
+    cu = torch.tensor([0] + list(torch.tensor(new).cumsum(0)), dtype=torch.int32, device=dev)
+    rdy = torch.tensor(ready, dtype=torch.int32, device=dev)
+    got = ops.gqa_prefill(q, kv, r2t, rows, cu, rdy, Hq, Hkv, D, max(new))
+    want = ref.gqa_prefill(q.reshape(T, Hq, D), kv, r2t, rows, cu, rdy, Hq, Hkv, D)
+    torch.cuda.synchronize()
+    assert int(kernels().llb_attn_tc_status()) == 0, "a bounded wait inside the attention kernel ran out"
+    err = (got.float() - want.float()).abs().max().item()
+    assert err < 2e-2, f"max abs err {err}"
