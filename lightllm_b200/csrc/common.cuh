@@ -36,7 +36,13 @@ namespace llb {
 // kernel of the stream is still draining; it must call pdl_wait() before it touches global memory (the call
 // returns once the previous kernel has completed and flushed).  Its own prologue (barrier set-up, tensor
 // memory allocation, index arithmetic) overlaps the predecessor's tail.  LLB_PDL=0 turns the attribute off.
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// After its own wait the kernel lets the next kernel of the stream be scheduled (launch_dependents): that kernel's
+// CTAs start on every SM as soon as this kernel's CTA there has exited and run their prologue up to their own
+// pdl_wait(), instead of waiting for the whole grid to drain plus a launch latency.
+__device__ __forceinline__ void pdl_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
 inline bool pdl_enabled() {
   static int v = -1;
   if (v < 0) {
