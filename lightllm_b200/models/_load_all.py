@@ -6,3 +6,4 @@ from . import generic  # noqa: F401
 from . import qwen2_vl  # noqa: F401
 from . import gpt_oss  # noqa: F401
 from . import llava  # noqa: F401
+from . import internvl  # noqa: F401

@@ -100,6 +100,6 @@ class ClipLlavaTower:
         x = F.gelu(F.linear(x, self.proj["linear_1.weight"], self.proj["linear_1.bias"]))
         return F.linear(x, self.proj["linear_2.weight"], self.proj["linear_2.bias"])
 
-    def encode_images(self, payloads: List[bytes]) -> List[torch.Tensor]:
+    def encode_images(self, payloads: List[bytes], items=None) -> List[torch.Tensor]:
         px = torch.stack([clip_preprocess(p, self.image_size) for p in payloads])
         return list(self.forward(px))

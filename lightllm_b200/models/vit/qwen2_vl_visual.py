@@ -175,7 +175,7 @@ class Qwen2VLVisionTower:
         x = F.gelu(F.linear(x, m["mlp.0.weight"], m["mlp.0.bias"]))
         return F.linear(x, m["mlp.2.weight"], m["mlp.2.bias"])
 
-    def encode_images(self, payloads: List[bytes]) -> List[torch.Tensor]:
+    def encode_images(self, payloads: List[bytes], items=None) -> List[torch.Tensor]:
         items = [preprocess_image(p, self.patch, self.merge, self.temporal) for p in payloads]
         out = self.forward(torch.cat([x for x, _ in items], dim=0), [g for _, g in items])
         res, s0 = [], 0

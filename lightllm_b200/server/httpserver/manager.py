@@ -93,10 +93,14 @@ class HttpServerManager:
         items = mm.items()
         md5s, nums = [], []
         for it in items:
+            init = getattr(self.tokenizer, "init_imageitem_extral_params" if it.kind == "image"
+                           else "init_audioitem_extral_params", None)
+            if init is not None:  # per-item settings that change the token count (e.g. the tile budget of an image)
+                init(it, mm, sampling_params)
             n = self.tokenizer.get_image_token_length(it) if it.kind == "image" else \
                 self.tokenizer.get_audio_token_length(it)
             it.token_num = n
-            it.md5 = it.content_md5(salt=str(getattr(it, "grid_thwd", "")))
+            it.md5 = it.content_md5(salt=str(getattr(it, "grid_thwd", "")) + str(sorted(it.extra_params.items())))
             md5s.append(it.md5)
             nums.append(n)
         t0 = time.time()

@@ -66,7 +66,8 @@ class _Item:
 
     def to_dict(self):
         return {"uuid": self.uuid, "token_id": self.token_id, "token_num": self.token_num,
-                "start_index_in_embed_cache": self.start_index_in_embed_cache, "md5": self.md5, **self._extra_dict()}
+                "start_index_in_embed_cache": self.start_index_in_embed_cache, "md5": self.md5,
+                "extra_params": dict(self.extra_params), **self._extra_dict()}
 
     def _extra_dict(self):
         return {}

@@ -60,6 +60,10 @@ def get_tokenizer(model_dir: str, tokenizer_mode: str = "fast", trust_remote_cod
         from ..models.llava import LlavaTokenizer
 
         return LlavaTokenizer(tok, cfg)
+    if mt == "internvl_chat":
+        from ..models.internvl import InternVLTokenizer
+
+        return InternVLTokenizer(tok, cfg)
     raise ValueError(f"multimodal serving of model_type {mt!r} has no tokenizer wrapper")
 
 

@@ -43,6 +43,15 @@ def build_vision_tower(args, device, dtype=torch.bfloat16):
         from ...models.vit.clip_visual import ClipLlavaTower
 
         return ClipLlavaTower(cfg, SafetensorsSource(args.model_dir), device, dtype)
+    if mt == "internvl_chat":
+        from ...models.base import TransformerLM
+        from ...models.vit.internvl_visual import InternVLVisionTower
+
+        if args.model_dir and TransformerLM._has_weights(args.model_dir):
+            src = SafetensorsSource(args.model_dir)
+        else:
+            src = RandomSource(InternVLVisionTower.weight_shapes(cfg), dtype=dtype)
+        return InternVLVisionTower(cfg, src, device, dtype)
     raise ValueError(f"no vision tower for model_type {mt!r}")
 
 
@@ -71,7 +80,7 @@ class VisualManager:
         for s in range(0, len(items), self.infer_batch_size):
             chunk = items[s:s + self.infer_batch_size]
             payloads = [self.cache.get_payload(i["uuid"]) for i in chunk]
-            embs = self.tower.encode_images(payloads)
+            embs = self.tower.encode_images(payloads, items=chunk)
             for it, e in zip(chunk, embs):
                 assert e.shape[0] == it["token_num"], f"image gives {e.shape[0]} tokens, the prompt reserved {it['token_num']}"
                 self.cache.arena.write(it["start_index_in_embed_cache"], e)
