@@ -59,6 +59,14 @@ def normalize_config(cfg: dict) -> dict:
     return cfg
 
 
+def embed_row_width(cfg: dict) -> int:
+    """Elements per row of the shared multimodal embedding arena: the language model's width, times (1 + number
+    of deep-stack feature sets) for towers that also feed early decoder layers (Qwen3-VL)."""
+    cfg = normalize_config(cfg)
+    k = len((cfg.get("vision_config") or {}).get("deepstack_visual_indexes") or [])
+    return int(cfg["hidden_size"]) * (1 + k)
+
+
 def load_config(model_dir: str) -> dict:
     with open(os.path.join(model_dir, "config.json")) as f:
         return normalize_config(json.load(f))
@@ -576,11 +584,17 @@ class TransformerLM:
                 h = self._row_parallel(f[1], f[2], None, residual, nxt)
             else:                   # ("partial", tensor): per-rank partial sum of the FFN output (MoE)
                 h = self._reduce_partial(f[1], residual, nxt)
+            h = self._after_layer(i, residual, h, st)
         if self._tpsp_now:
             self._tpsp_now = False
             st.extra["normed"] = True
             return h
         return residual
+
+    def _after_layer(self, i: int, residual, h, st):
+        """Hook run after decoder layer `i`: `residual` is the layer's output stream, `h` the normalised input of the
+        next layer (None after the last).  A family that edits the stream here returns the recomputed `h`."""
+        return h
 
     def _tpsp_active(self, T: int, st) -> bool:
         """Token-sharded residual stream (--enable_tpsp_mix_mode) for this pass: needs the fused peer-memory

@@ -12,7 +12,7 @@ from typing import List, Optional, Tuple
 import numpy as np
 import torch
 
-from .llama import Qwen2LM
+from .llama import Qwen2LM, Qwen3LM
 from .registry import register_model
 from .remap import RemapSource
 
@@ -52,10 +52,12 @@ def mrope_positions(ids: np.ndarray, items: List[dict], merge: int = 2) -> Tuple
     return pos, nxt - n
 
 
-@register_model("qwen2_vl", "qwen2_5_vl", is_multimodal=True)
-class Qwen2VLLM(Qwen2LM):
-    model_type = "qwen2_vl"
+class MRopeMixin:
+    """Multimodal rotary embedding on top of a decoder class: per-token (t, row, column) positions, one of which
+    drives every rotary frequency slot."""
+
     needs_prompt_ids = True  # the backend hands every prefill pass the request's whole prompt (M-RoPE is global)
+    mrope_interleaved = False  # False: slots in three contiguous sections; True: t / h / w slots alternate
 
     def _read_config(self, c):
         super()._read_config(c)
@@ -63,6 +65,7 @@ class Qwen2VLLM(Qwen2LM):
         sec = rs.get("mrope_section") or [16, 24, 24]
         self.mrope_section = [int(x) for x in sec]
         assert sum(self.mrope_section) == self.rot_dim // 2, "mrope_section must cover the rotary half"
+        self.mrope_interleaved = bool(rs.get("mrope_interleaved", self.mrope_interleaved))
         self.rope_scaling = None  # "mrope" is not a frequency scaling
         vc = c.get("vision_config") or {}
         self.merge = int(vc.get("spatial_merge_size", 2))
@@ -81,7 +84,13 @@ class Qwen2VLLM(Qwen2LM):
     def _init_rope(self):
         super()._init_rope()
         half = self.rot_dim // 2
-        sec = torch.repeat_interleave(torch.arange(3), torch.tensor(self.mrope_section))
+        if self.mrope_interleaved:  # slot i belongs to h (i % 3 == 1) or w (i % 3 == 2) while that axis has slots left
+            i = torch.arange(half)
+            sec = torch.zeros(half, dtype=torch.long)
+            sec[(i % 3 == 1) & (i < 3 * self.mrope_section[1])] = 1
+            sec[(i % 3 == 2) & (i < 3 * self.mrope_section[2])] = 2
+        else:
+            sec = torch.repeat_interleave(torch.arange(3), torch.tensor(self.mrope_section))
         self._section_of_slot = sec.to(self.device)          # [half] -> 0 / 1 / 2
         self._slot = torch.arange(half, device=self.device)
 
@@ -120,6 +129,11 @@ class Qwen2VLLM(Qwen2LM):
     def _rope_inputs(self, st, layer):
         r = st.extra.get("rope")
         return r if r is not None else (self.cos, self.sin, st.position_ids)
+
+
+@register_model("qwen2_vl", "qwen2_5_vl", is_multimodal=True)
+class Qwen2VLLM(MRopeMixin, Qwen2LM):
+    model_type = "qwen2_vl"
 
 
 class Qwen2VLTokenizer:
@@ -167,3 +181,69 @@ class Qwen2VLTokenizer:
         if k != len(images):
             raise ValueError(f"the prompt has {k} image placeholders for {len(images)} images")
         return out
+
+
+@register_model("qwen3_vl", is_multimodal=True)
+class Qwen3VLLM(MRopeMixin, Qwen3LM):
+    """Qwen3-VL language model: Qwen3 decoder (q/k RMSNorm), M-RoPE with interleaved t / h / w frequency slots, and
+    deep-stack: the vision tower's extra feature sets are added to the image positions of the residual stream after
+    the first decoder layers.  Reference: lightllm/models/qwen3_vl/."""
+
+    model_type = "qwen3_vl"
+    mrope_interleaved = True
+
+    def _read_config(self, c):
+        super()._read_config(c)
+        vc = c.get("vision_config") or {}
+        self.n_deepstack = len(vc.get("deepstack_visual_indexes") or [])
+        self.embed_row_width = self.hidden * (1 + self.n_deepstack)
+
+    def _merge_multimodal(self, h, st):
+        """Arena rows are [embedding | deep-stack sets]: the embedding replaces the placeholder rows, the rest is
+        kept for `_after_layer`."""
+        st.extra.pop("deepstack", None)
+        mm = st.extra.get("multimodal_params")
+        if not st.is_prefill or not mm or self.embed_arena is None or self.n_deepstack == 0:
+            return super()._merge_multimodal(h, st)
+        ids = st.extra["input_ids_cpu"]
+        pos_all, rows_all, seen = [], [], set()
+        for params in mm:
+            for it in (params or {}).get("images", []):
+                t0, n = it.get("token_id"), it.get("token_num")
+                if t0 is None or (t0, n) in seen:
+                    continue
+                seen.add((t0, n))
+                hit = ((ids >= t0) & (ids < t0 + n)).nonzero(as_tuple=True)[0]
+                if hit.numel():
+                    pos_all.append(hit)
+                    rows_all.append(ids[hit] - t0 + it["start_index_in_embed_cache"])
+        if not pos_all:
+            return h
+        pos, rows = torch.cat(pos_all).to(h.device), torch.cat(rows_all)
+        emb = self.embed_arena.read_rows(rows).to(device=h.device, dtype=h.dtype)
+        h[pos] = emb[:, : self.hidden]
+        st.extra["deepstack"] = (pos, emb[:, self.hidden:])
+        return h
+
+    def _after_layer(self, i, residual, h, st):
+        ds = st.extra.get("deepstack")
+        if ds is None or i >= self.n_deepstack:
+            return h
+        pos, feats = ds
+        residual[pos] += feats[:, i * self.hidden:(i + 1) * self.hidden]
+        if i + 1 < self.num_layers:
+            from .. import ops
+
+            return ops.rmsnorm(residual, self.layers[i + 1].in_norm, self.eps, self.norm_w_offset)
+        return h
+
+
+class Qwen3VLTokenizer(Qwen2VLTokenizer):
+    """Same placeholder expansion as Qwen2-VL with 16 x 16 patches (factor 32) and Qwen3-VL's pixel budget."""
+
+    def __init__(self, tokenizer, model_cfg: dict):
+        super().__init__(tokenizer, model_cfg)
+        vc = model_cfg.get("vision_config") or {}
+        self.patch = int(vc.get("patch_size", 16))
+        self.min_pixels = int(model_cfg.get("min_pixels", 64 * 32 * 32 // 16))
+        self.max_pixels = int(model_cfg.get("max_pixels", 16384 * 32 * 32 // 16))

@@ -116,7 +116,9 @@ def start_core_processes(args: StartArgs, config_override: dict = None):
         from ..models.base import load_config
         from .embed_cache.manager import start_cache_manager
 
-        hidden = (config_override or load_config(args.model_dir))["hidden_size"]
+        from ..models.base import embed_row_width
+
+        hidden = embed_row_width(config_override or load_config(args.model_dir))
         process_manager.start_submodule_processes([start_cache_manager], [(d, hidden)])
     process_manager.start_submodule_processes([start_router_process], [(d, config_override)])
     if args.enable_multimodal:

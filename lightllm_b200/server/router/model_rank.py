@@ -113,7 +113,8 @@ def _build_model_and_backend(args: StartArgs, ps):
         from ..embed_cache.cache import EmbedArena
         from ..embed_cache.manager import arena_name, arena_rows
 
-        model.embed_arena = EmbedArena(arena_name(args), arena_rows(args, model.hidden), model.hidden, create=False)
+        width = getattr(model, "embed_row_width", model.hidden)
+        model.embed_arena = EmbedArena(arena_name(args), arena_rows(args, width), width, create=False)
     return model, backend
 
 

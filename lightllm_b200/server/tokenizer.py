@@ -60,6 +60,10 @@ def get_tokenizer(model_dir: str, tokenizer_mode: str = "fast", trust_remote_cod
         from ..models.llava import LlavaTokenizer
 
         return LlavaTokenizer(tok, cfg)
+    if mt == "qwen3_vl":
+        from ..models.qwen2_vl import Qwen3VLTokenizer
+
+        return Qwen3VLTokenizer(tok, cfg)
     if mt == "internvl_chat":
         from ..models.internvl import InternVLTokenizer
 

@@ -39,6 +39,16 @@ def build_vision_tower(args, device, dtype=torch.bfloat16):
         else:
             src = RandomSource(Qwen2VLVisionTower.weight_shapes(vcfg), dtype=dtype)
         return Qwen2VLVisionTower(vcfg, src, device, dtype)
+    if mt == "qwen3_vl":
+        from ...models.base import TransformerLM
+        from ...models.vit.qwen3_vl_visual import Qwen3VLVisionTower
+
+        vcfg = dict(cfg["vision_config"])
+        if args.model_dir and TransformerLM._has_weights(args.model_dir):
+            src = SafetensorsSource(args.model_dir)
+        else:
+            src = RandomSource(Qwen3VLVisionTower.weight_shapes(vcfg), dtype=dtype)
+        return Qwen3VLVisionTower(vcfg, src, device, dtype)
     if mt == "llava":
         from ...models.vit.clip_visual import ClipLlavaTower
 
