@@ -44,7 +44,8 @@ def normalize_config(cfg: dict) -> dict:
     if "text_config" in cfg and "hidden_size" not in cfg:  # multimodal wrappers
         base = dict(cfg["text_config"])
         outer = cfg.get("model_type") or base.get("model_type")
-        cfg = {**cfg, **base, "model_type": outer}
+        keep = {k: cfg[k] for k in ("tie_word_embeddings",) if k in cfg}  # the wrapper decides about its own head
+        cfg = {**cfg, **base, **keep, "model_type": outer}
     rp = cfg.get("rope_parameters")
     if isinstance(rp, dict):
         if "rope_theta" in rp:

@@ -247,3 +247,42 @@ class Qwen3VLTokenizer(Qwen2VLTokenizer):
         self.patch = int(vc.get("patch_size", 16))
         self.min_pixels = int(model_cfg.get("min_pixels", 64 * 32 * 32 // 16))
         self.max_pixels = int(model_cfg.get("max_pixels", 16384 * 32 * 32 // 16))
+
+
+def _qwen3_vl_moe_class():
+    from .qwen3_moe import Qwen3MoeLM
+    from .remap import FusedExperts
+
+    class Qwen3VLMoeLM(Qwen3VLLM, Qwen3MoeLM):
+        """Qwen3-VL-MoE: the Qwen3-VL language path on the Qwen3-MoE decoder; the checkpoint stores every layer's
+        experts as two 3-D tensors (`experts.gate_up_proj`, `experts.down_proj`).  Reference: lightllm/models/
+        qwen3_vl_moe/."""
+
+        model_type = "qwen3_vl_moe"
+
+        def _wrap_source(self, src):
+            src = super()._wrap_source(src)
+            if not src.has("model.layers.0.mlp.experts.gate_up_proj") and not any(
+                    n.endswith("mlp.experts.gate_up_proj") for n in src.names()):
+                return src
+            t = {n: n for n in src.names()}
+            E, I, H = self.moe.num_experts, self.moe.inter, self.hidden
+            cache = FusedExperts()
+            for n in list(src.names()):
+                if n.endswith("mlp.experts.gate_up_proj"):
+                    p = n[: -len("gate_up_proj")]
+                    for e in range(E):
+                        t[f"{p}{e}.gate_proj.weight"] = cache.entry(n, e, 2 * I, 0, I)
+                        t[f"{p}{e}.up_proj.weight"] = cache.entry(n, e, 2 * I, I, 2 * I)
+                    t.pop(n)
+                elif n.endswith("mlp.experts.down_proj"):
+                    p = n[: -len("down_proj")]
+                    for e in range(E):
+                        t[f"{p}{e}.down_proj.weight"] = cache.entry(n, e, H)
+                    t.pop(n)
+            return RemapSource(src, t)
+
+    return Qwen3VLMoeLM
+
+
+Qwen3VLMoeLM = register_model("qwen3_vl_moe", is_multimodal=True)(_qwen3_vl_moe_class())

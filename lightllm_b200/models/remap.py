@@ -91,3 +91,26 @@ def grouped_qkv(fused_name: str, num_kv: int, group: int, head_dim: int, which: 
         return t[:, group + 1].reshape(num_kv * head_dim, -1)
 
     return f
+
+
+class FusedExperts:
+    """Per-expert views of expert weights stored as one 3-D tensor [E, out, in] (or [E, in, out] in older
+    checkpoints, recognised by `out_features`); the tensor is fetched once and kept while its experts are read."""
+
+    def __init__(self):
+        self._name, self._t = None, None
+
+    def _load(self, src, name, out_features):
+        if self._name != name:
+            t = src.get(name)
+            if t.shape[1] != out_features and t.shape[2] == out_features:
+                t = t.transpose(1, 2)
+            self._name, self._t = name, t
+        return self._t
+
+    def entry(self, name: str, expert: int, out_features: int, r0: int = 0, r1: Optional[int] = None):
+        def f(src):
+            t = self._load(src, name, out_features)[expert]
+            return t[r0:r1].contiguous()
+
+        return f

@@ -528,3 +528,39 @@ def test_qwen3_vl_tower_deepstack_and_interleaved_mrope(tmp_path):
                     multimodal_params=[{"images": [item], "audios": []}])
     got = m.forward(mi).logits.float()
     assert (got - ref).abs().max().item() < 2e-3 * max(ref.abs().max().item(), 1.0)
+
+
+def test_qwen3_vl_moe_fused_expert_tensors(tmp_path):
+    """Qwen3-VL-MoE text path (no image): experts stored as 3-D tensors are split per expert at load."""
+    from transformers import Qwen3VLMoeConfig, Qwen3VLMoeForConditionalGeneration
+
+    from lightllm_b200.common.infer_state import ModelInput
+    from lightllm_b200.models.base import load_config
+    from lightllm_b200.models.registry import get_model
+    from lightllm_b200.parallel import dist as pdist
+
+    torch.manual_seed(0)
+    text = dict(hidden_size=64, intermediate_size=128, moe_intermediate_size=64, num_experts=4, num_experts_per_tok=2,
+                num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=16, vocab_size=300,
+                decoder_sparse_step=1, mlp_only_layers=[], norm_topk_prob=True, max_position_embeddings=256,
+                rope_scaling={"rope_type": "default", "mrope_section": [2, 3, 3], "mrope_interleaved": True})
+    vision = dict(depth=1, hidden_size=32, num_heads=4, intermediate_size=64, out_hidden_size=64, patch_size=16,
+                  spatial_merge_size=2, temporal_patch_size=2, in_channels=3, num_position_embeddings=36,
+                  deepstack_visual_indexes=[0])
+    cfg = Qwen3VLMoeConfig(text_config=text, vision_config=vision, image_token_id=290, tie_word_embeddings=False)
+    hf = Qwen3VLMoeForConditionalGeneration(cfg).eval().float()
+    d = str(tmp_path / "ckpt")
+    hf.save_pretrained(d, safe_serialization=True)
+    ids = torch.randint(3, 280, (23,), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        ref = hf(input_ids=ids.unsqueeze(0)).logits[0].float()
+    m = get_model(load_config(d), model_dir=d, pstate=pdist.ParallelState(device=torch.device("cpu")),
+                  data_type="float32", max_total_token_num=128, max_req_num=2, max_seq_length=64, disable_cudagraph=True)
+    assert type(m).__name__ == "Qwen3VLMoeLM" and m.layers[0].w13.shape == (4, 128, 64)
+    req, n = m.req_manager.alloc(), len(ids)
+    mi = ModelInput(batch_size=1, total_token_num=n, max_kv_len=n, is_prefill=True,
+                    b_req_idx=torch.tensor([req], dtype=torch.int32), b_seq_len=torch.tensor([n], dtype=torch.int32),
+                    mem_indexes=m.mem_manager.alloc(n).clone(), input_ids=ids,
+                    b_ready_cache_len=torch.zeros(1, dtype=torch.int32), max_q_len=n, return_all_logits=True)
+    got = m.forward(mi).logits.float()
+    assert (got - ref).abs().max().item() < 2e-3 * max(ref.abs().max().item(), 1.0)
