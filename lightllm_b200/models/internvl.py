@@ -14,6 +14,7 @@ from .remap import RemapSource
 from .vit.internvl_visual import num_tiles
 
 IMG_START, IMG_END, IMG_TOKEN = "<img>", "</img>", "<image>"
+AUDIO_START, AUDIO_END = "<audio>", "</audio>"
 
 
 def _llm_type(cfg: dict) -> str:
@@ -65,6 +66,8 @@ class InternVLTokenizer:
         self.image_start_id = conv(IMG_START) if conv else model_cfg.get("img_start_token_id")
         self.image_end_id = conv(IMG_END) if conv else model_cfg.get("img_end_token_id")
         self.image_token_id = model_cfg.get("image_token_id")  # id-list prompts: placeholder id of a picture
+        self.audio_start_id = conv(AUDIO_START) if conv else model_cfg.get("audio_start_token_id")
+        self.audio_end_id = conv(AUDIO_END) if conv else model_cfg.get("audio_end_token_id")
 
     def __getattr__(self, name):
         return getattr(self.tokenizer, name)
@@ -80,6 +83,14 @@ class InternVLTokenizer:
         else:
             n = len(multi_params.images) if multi_params is not None else 1
             img.extra_params["image_patch_max_num"] = 12 if n == 1 else (6 if n <= 6 else 0)
+
+    def init_audioitem_extral_params(self, audio, multi_params=None, sampling_params=None):
+        pass
+
+    def get_audio_token_length(self, audio) -> int:
+        from .whisper_audio import audio_token_num
+
+        return audio_token_num(int(audio.audio_length))
 
     def get_image_token_length(self, img) -> int:
         cap = int(img.extra_params.get("image_patch_max_num", 12)) or 1
@@ -115,6 +126,22 @@ class InternVLTokenizer:
                     i += 1
         if k != len(images):
             raise ValueError(f"invalid image tag num: {len(images)} images vs {k} placeholders")
+        audios = list(multimodal_params.audios) if multimodal_params is not None else []
+        if audios:  # `<audio></audio>` pairs of the prompt take the clips' virtual ids, in order
+            ids, out, a, i = out, [], 0, 0
+            while i < len(ids):
+                if ids[i] == self.audio_start_id and i + 1 < len(ids) and ids[i + 1] == self.audio_end_id \
+                        and a < len(audios):
+                    out.append(ids[i])
+                    out.extend(range(audios[a].token_id, audios[a].token_id + audios[a].token_num))
+                    out.append(ids[i + 1])
+                    a += 1
+                    i += 2
+                else:
+                    out.append(ids[i])
+                    i += 1
+            if a != len(audios):
+                raise ValueError(f"invalid audio tag num: {len(audios)} clips vs {a} placeholders")
         return out
 
 

@@ -127,6 +127,10 @@ def start_core_processes(args: StartArgs, config_override: dict = None):
         dv = dict(d)
         dv["_config_override"] = config_override
         process_manager.start_submodule_processes([start_visual_process], [(dv,)])
+        if getattr(args, "enable_multimodal_audio", False):
+            from .audioserver.manager import start_audio_process
+
+            process_manager.start_submodule_processes([start_audio_process], [(dv,)])
 
 
 def run_http_server(args: StartArgs):
