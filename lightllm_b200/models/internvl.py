@@ -62,7 +62,15 @@ class InternVLTokenizer:
         self.image_length = int(os.environ.get("INTERNVL_IMAGE_LENGTH", 256))
         self.image_size = (model_cfg.get("vision_config") or {}).get("image_size", 448)
         self.use_thumbnail = bool(model_cfg.get("use_thumbnail", True))
-        conv = getattr(tokenizer, "convert_tokens_to_ids", None)
+        raw_conv = getattr(tokenizer, "convert_tokens_to_ids", None)
+
+        def conv(tok):  # a vocabulary without the tag (text-only build of the model) gives None
+            try:
+                return raw_conv(tok)
+            except (KeyError, ValueError):
+                return None
+
+        conv = conv if raw_conv else None
         self.image_start_id = conv(IMG_START) if conv else model_cfg.get("img_start_token_id")
         self.image_end_id = conv(IMG_END) if conv else model_cfg.get("img_end_token_id")
         self.image_token_id = model_cfg.get("image_token_id")  # id-list prompts: placeholder id of a picture
