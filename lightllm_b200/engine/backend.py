@@ -105,6 +105,9 @@ class ModelBackend:
         self.model = model
         self.args = args or BackendArgs()
         self.device = model.device
+        if not getattr(model, "supports_prefix_cache", True):
+            # hybrid models keep per-request recurrent state that a shared prefix cannot restore
+            self.args.disable_dynamic_prompt_cache = True
         self.radix_cache = None if self.args.disable_dynamic_prompt_cache else \
             RadixCache("radix", model.max_total_token_num, 0, model.mem_manager)
         self.ctx = InferenceContext(model, self.radix_cache)

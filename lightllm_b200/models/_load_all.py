@@ -7,3 +7,4 @@ from . import qwen2_vl  # noqa: F401
 from . import gpt_oss  # noqa: F401
 from . import llava  # noqa: F401
 from . import internvl  # noqa: F401
+from . import qwen3_next  # noqa: F401

@@ -29,13 +29,17 @@ from .weights import tp_range
 
 class MoEConfig:
     def __init__(self, num_experts, top_k, inter, renorm=True, scoring="softmax", n_group=1, topk_group=1,
-                 routed_scale=1.0, has_bias=False, n_shared=0, shared_inter=0, act="silu"):
+                 routed_scale=1.0, has_bias=False, n_shared=0, shared_inter=0, act="silu",
+                 shared_name="shared_experts", shared_gate=False):
         self.num_experts, self.top_k, self.inter = num_experts, top_k, inter
         self.renorm, self.scoring = renorm, scoring
         self.n_group, self.topk_group = n_group, topk_group
         self.routed_scale, self.has_bias = routed_scale, has_bias
         self.n_shared, self.shared_inter = n_shared, shared_inter
         self.act = act
+        # checkpoint prefix of the shared expert and whether its output is scaled by sigmoid(x . w_gate)
+        # (`shared_expert_gate`, Qwen2-MoE / Qwen3-Next)
+        self.shared_name, self.shared_gate = shared_name, shared_gate
 
 
 def expert_weight_shapes(prefix: str, mc: MoEConfig, hidden: int, gate_name="gate", experts_name="experts"):
@@ -48,10 +52,12 @@ def expert_weight_shapes(prefix: str, mc: MoEConfig, hidden: int, gate_name="gat
         s[q + "up_proj.weight"] = (mc.inter, hidden)
         s[q + "down_proj.weight"] = (hidden, mc.inter)
     if mc.n_shared:
-        q = prefix + "shared_experts."
+        q = prefix + mc.shared_name + "."
         s[q + "gate_proj.weight"] = (mc.shared_inter, hidden)
         s[q + "up_proj.weight"] = (mc.shared_inter, hidden)
         s[q + "down_proj.weight"] = (hidden, mc.shared_inter)
+        if mc.shared_gate:
+            s[prefix + mc.shared_name + "_gate.weight"] = (1, hidden)
     return s
 
 
@@ -102,7 +108,9 @@ def load_experts(model, lw, src, prefix: str, mc: MoEConfig, ep: bool, gate_name
     lw.ep_world = tp if ep else 1
     lw.is_moe = True
     if mc.n_shared:
-        model._load_dense_ffn(lw, src, prefix + "shared_experts.", mc.shared_inter)
+        model._load_dense_ffn(lw, src, prefix + mc.shared_name + ".", mc.shared_inter)
+        if mc.shared_gate:
+            lw.shared_gate_w = dev(src.get(prefix + mc.shared_name + "_gate.weight"))
         lw.shared_gate_up_w, lw.shared_down_w, lw.shared_fused = lw.gate_up_w, lw.down_w, lw.gate_up_fused
         lw.gate_up_w = lw.down_w = None
 
@@ -125,6 +133,8 @@ def moe_ffn(model, lw, h, mc: MoEConfig):
         else:
             act = ops.gated_act(ops.gemm(h, lw.shared_gate_up_w), mc.act)
         ops.gemm(act, lw.shared_down_w, out=out)
+        if mc.shared_gate:  # every rank scales its partial sum by the same (replicated) gate
+            out.mul_(torch.sigmoid(torch.nn.functional.linear(h.float(), lw.shared_gate_w.float())).to(out.dtype))
         accumulate = True
     epg = ep_group_of(model, mc)
     if epg is not None:

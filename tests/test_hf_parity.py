@@ -564,3 +564,64 @@ def test_qwen3_vl_moe_fused_expert_tensors(tmp_path):
                     b_ready_cache_len=torch.zeros(1, dtype=torch.int32), max_q_len=n, return_all_logits=True)
     got = m.forward(mi).logits.float()
     assert (got - ref).abs().max().item() < 2e-3 * max(ref.abs().max().item(), 1.0)
+
+
+def test_qwen3_next_hybrid_linear_attention(tmp_path):
+    """Qwen3-Next: Gated DeltaNet layers (convolution + matrix state carried over chunks and decode steps), gated
+    softmax attention with partial rotary embedding, shared expert with a sigmoid gate, against Hugging Face."""
+    from transformers import Qwen3NextConfig, Qwen3NextForCausalLM
+
+    from lightllm_b200.common.infer_state import ModelInput
+    from lightllm_b200.models.base import load_config
+    from lightllm_b200.models.registry import get_model
+    from lightllm_b200.parallel import dist as pdist
+
+    torch.manual_seed(0)
+    cfg = Qwen3NextConfig(hidden_size=64, intermediate_size=128, moe_intermediate_size=32,
+                          shared_expert_intermediate_size=32, num_experts=4, num_experts_per_tok=2,
+                          num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=32,
+                          vocab_size=300, linear_num_value_heads=4, linear_num_key_heads=2, linear_key_head_dim=16,
+                          linear_value_head_dim=16, linear_conv_kernel_dim=4, full_attention_interval=4,
+                          partial_rotary_factor=0.25, decoder_sparse_step=1, mlp_only_layers=[], norm_topk_prob=True,
+                          max_position_embeddings=256, tie_word_embeddings=False)
+    hf = Qwen3NextForCausalLM(cfg).eval().float()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if "norm" in n or "dt_bias" in n or "A_log" in n:
+                p.add_(torch.randn_like(p) * 0.1)
+    d = str(tmp_path / "ckpt")
+    hf.save_pretrained(d, safe_serialization=True)
+    ids = torch.randint(3, 280, (90,), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        ref = hf(input_ids=ids.unsqueeze(0)).logits[0].float()
+
+    m = get_model(load_config(d), model_dir=d, pstate=pdist.ParallelState(device=torch.device("cpu")),
+                  data_type="float32", max_total_token_num=256, max_req_num=3, max_seq_length=128, disable_cudagraph=True)
+    assert m.full_layers == [3] and m.mem_manager.layer(0) is not None and not m.supports_prefix_cache
+    scale = max(ref.abs().max().item(), 1.0)
+
+    def prefill(req, tokens, ready):
+        n = len(tokens)
+        mi = ModelInput(batch_size=1, total_token_num=ready + n, max_kv_len=ready + n, is_prefill=True,
+                        b_req_idx=torch.tensor([req], dtype=torch.int32),
+                        b_seq_len=torch.tensor([ready + n], dtype=torch.int32),
+                        mem_indexes=m.mem_manager.alloc(n).clone(), input_ids=tokens,
+                        b_ready_cache_len=torch.tensor([ready], dtype=torch.int32), max_q_len=n, return_all_logits=True)
+        return m.forward(mi).logits.float()
+
+    # whole prompt of 70 tokens in one pass, then 20 decode steps fed with the reference tokens
+    r0 = m.req_manager.alloc()
+    got = prefill(r0, ids[:70], 0)
+    assert (got - ref[:70]).abs().max().item() < 2e-3 * scale
+    for t in range(70, 74):
+        m.req_manager.req_to_next_token_ids[r0] = int(ids[t])
+        mi = ModelInput(batch_size=1, total_token_num=t + 1, max_kv_len=t + 1, is_prefill=False,
+                        b_req_idx=torch.tensor([r0], dtype=torch.int32),
+                        b_seq_len=torch.tensor([t + 1], dtype=torch.int32), mem_indexes=m.mem_manager.alloc(1).clone())
+        step = m.forward(mi).logits.float()
+        assert (step[0] - ref[t]).abs().max().item() < 2e-3 * scale, f"decode step at position {t}"
+    # chunked prefill of another request: 37 + 53 tokens, the state travels from the first chunk to the second
+    r1 = m.req_manager.alloc()
+    a = prefill(r1, ids[:37], 0)
+    b = prefill(r1, ids[37:], 37)
+    assert (torch.cat([a, b]) - ref).abs().max().item() < 2e-3 * scale
