@@ -232,3 +232,116 @@ class Qwen3NextLM(Qwen3MoeLM):
             core = torch.cat(outs, dim=0)
         out = la.rmsnorm_gated(core, z, lw.gnorm_w, self.eps)
         return out.reshape(T, self.nv * self.dv).to(h.dtype)
+
+
+class _SeparateProjections:
+    """Qwen3.5 stores the linear layers' input projections as four matrices (`in_proj_qkv` with all q heads, then
+    all k heads, then all v heads; `in_proj_z`, `in_proj_b`, `in_proj_a`): they are regrouped per key head at load
+    into the layout `_split_projection` reads."""
+
+    def _attn_weight_shapes(self, p):
+        s = super()._attn_weight_shapes(p)
+        a = p + "linear_attn."
+        if a + "in_proj_qkvz.weight" in s:
+            H = self.hidden
+            kd, vd = self.nk_all * self.dk, self.nv_all * self.dv
+            s.pop(a + "in_proj_qkvz.weight")
+            s.pop(a + "in_proj_ba.weight")
+            s.update({a + "in_proj_qkv.weight": (2 * kd + vd, H), a + "in_proj_z.weight": (vd, H),
+                      a + "in_proj_b.weight": (self.nv_all, H), a + "in_proj_a.weight": (self.nv_all, H)})
+        return s
+
+    def _load_attn(self, lw, src, p, layer):
+        if self.layer_types[layer] == "full_attention":
+            return super()._load_attn(lw, src, p, layer)
+        a = p + "linear_attn."
+        n0, n1 = self._nk_range
+        H, dk, dv, r = self.hidden, self.dk, self.dv, self.vrep
+        kd_all = self.nk_all * dk
+        qkv = src.get(a + "in_proj_qkv.weight")
+        q = qkv[n0 * dk:n1 * dk].view(self.nk, dk, H)
+        k = qkv[kd_all + n0 * dk:kd_all + n1 * dk].view(self.nk, dk, H)
+        v = qkv[2 * kd_all + n0 * r * dv:2 * kd_all + n1 * r * dv].view(self.nk, r * dv, H)
+        z = src.get(a + "in_proj_z.weight", 0, n0 * r * dv, n1 * r * dv).view(self.nk, r * dv, H)
+        b = src.get(a + "in_proj_b.weight", 0, n0 * r, n1 * r).view(self.nk, r, H)
+        aa = src.get(a + "in_proj_a.weight", 0, n0 * r, n1 * r).view(self.nk, r, H)
+        grouped = torch.cat([q, k, v, z], dim=1).reshape(-1, H)
+        ba = torch.cat([b, aa], dim=1).reshape(-1, H)
+
+        class _View:  # the grouped matrices under the names the parent loader asks for
+            def __init__(self, base):
+                self.base = base
+
+            def get(self, name, dim=None, start=0, end=None):
+                if name == a + "in_proj_qkvz.weight":
+                    return grouped
+                if name == a + "in_proj_ba.weight":
+                    return ba
+                return self.base.get(name, dim, start, end)
+
+            def has(self, name):
+                return self.base.has(name)
+
+        self._load_linear_from(lw, _View(src), p, (n0, n1))
+
+
+def _load_linear_from(self, lw, src, p, real_range):
+    """The linear layer's tensors with the input projections taken whole from `src` (already this rank's heads,
+    grouped per key head) and every other per-head tensor sliced by the rank's head range."""
+    a = p + "linear_attn."
+    n0, n1 = real_range
+    per_k = 2 * self.dk + 2 * self.vrep * self.dv
+    lw.in_w = self._dev(torch.cat([src.get(a + "in_proj_qkvz.weight")[: self.nk * per_k],
+                                   src.get(a + "in_proj_ba.weight")], dim=0))
+    conv = src.get(a + "conv1d.weight").reshape(-1, self.conv_k)
+    kd_all = self.nk_all * self.dk
+    parts = [conv[n0 * self.dk:n1 * self.dk], conv[kd_all + n0 * self.dk:kd_all + n1 * self.dk],
+             conv[2 * kd_all + n0 * self.vrep * self.dv:2 * kd_all + n1 * self.vrep * self.dv]]
+    lw.conv_w = torch.cat(parts, dim=0).to(self.device, torch.float32).contiguous()
+    v0, v1 = n0 * self.vrep, n1 * self.vrep
+    lw.neg_a = (-src.get(a + "A_log").float().exp())[v0:v1].to(self.device).contiguous()
+    lw.dt_bias = src.get(a + "dt_bias").float()[v0:v1].to(self.device).contiguous()
+    lw.gnorm_w = src.get(a + "norm.weight").to(self.device, torch.float32).contiguous()
+    lw.o_w = self._dev(src.get(a + "out_proj.weight", 1, v0 * self.dv, v1 * self.dv))
+    lw.is_linear = True
+
+
+_SeparateProjections._load_linear_from = _load_linear_from
+
+
+def _strip_language_model_prefix(src):
+    for pre in ("model.language_model.", "language_model.model."):
+        if src.has(pre + "embed_tokens.weight"):
+            return RemapSource(src, {"model." + n[len(pre):]: n for n in src.names() if n.startswith(pre)})
+    return src
+
+
+@register_model("qwen3_5_moe", "qwen3_5_moe_text")
+class Qwen3_5MoeLM(_SeparateProjections, Qwen3NextLM):
+    """Qwen3.5-MoE language model (text path): the Qwen3-Next layer stack with separately stored input projections.
+    Reference: lightllm/models/qwen3_5_moe/."""
+
+    model_type = "qwen3_5_moe"
+
+    def _wrap_source(self, src):
+        return super()._wrap_source(_strip_language_model_prefix(src))
+
+
+@register_model("qwen3_5", "qwen3_5_text")
+class Qwen3_5LM(_SeparateProjections, Qwen3NextLM):
+    """Qwen3.5 dense language model (text path): hybrid attention as Qwen3-Next, plain SwiGLU FFN in every layer.
+    Reference: lightllm/models/qwen3_5/."""
+
+    model_type = "qwen3_5"
+
+    def _read_config(self, c):
+        c = dict(c)
+        c.setdefault("num_experts", 1)
+        c.setdefault("num_experts_per_tok", 1)
+        c.setdefault("moe_intermediate_size", c.get("intermediate_size"))
+        super()._read_config(c)
+        self._moe_layers = set()  # every FFN is dense
+        self.moe = None
+
+    def _wrap_source(self, src):
+        return _strip_language_model_prefix(src)

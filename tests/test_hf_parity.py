@@ -625,3 +625,41 @@ def test_qwen3_next_hybrid_linear_attention(tmp_path):
     a = prefill(r1, ids[:37], 0)
     b = prefill(r1, ids[37:], 37)
     assert (torch.cat([a, b]) - ref).abs().max().item() < 2e-3 * scale
+
+
+def test_qwen3_5_text_model_separate_projections(tmp_path):
+    """Qwen3.5 dense text model: in_proj_qkv / z / b / a stored separately, regrouped per key head at load."""
+    from transformers.models.qwen3_5 import modeling_qwen3_5 as hfm
+    from transformers import Qwen3_5TextConfig
+
+    from lightllm_b200.common.infer_state import ModelInput
+    from lightllm_b200.models.base import load_config
+    from lightllm_b200.models.registry import get_model
+    from lightllm_b200.parallel import dist as pdist
+
+    torch.manual_seed(0)
+    tc = Qwen3_5TextConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=4, num_attention_heads=4,
+                           num_key_value_heads=2, head_dim=32, vocab_size=300, linear_num_value_heads=4,
+                           linear_num_key_heads=2, linear_key_head_dim=16, linear_value_head_dim=16,
+                           linear_conv_kernel_dim=4, full_attention_interval=4, max_position_embeddings=256,
+                           tie_word_embeddings=False)
+    hf = hfm.Qwen3_5ForCausalLM(tc).eval().float()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if "norm" in n or "dt_bias" in n or "A_log" in n:
+                p.add_(torch.randn_like(p) * 0.1)
+    d = str(tmp_path / "ckpt")
+    hf.save_pretrained(d, safe_serialization=True)
+    ids = torch.randint(3, 280, (50,), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        ref = hf(input_ids=ids.unsqueeze(0)).logits[0].float()
+    m = get_model(load_config(d), model_dir=d, pstate=pdist.ParallelState(device=torch.device("cpu")),
+                  data_type="float32", max_total_token_num=128, max_req_num=2, max_seq_length=64, disable_cudagraph=True)
+    assert type(m).__name__ == "Qwen3_5LM"
+    req, n = m.req_manager.alloc(), len(ids)
+    mi = ModelInput(batch_size=1, total_token_num=n, max_kv_len=n, is_prefill=True,
+                    b_req_idx=torch.tensor([req], dtype=torch.int32), b_seq_len=torch.tensor([n], dtype=torch.int32),
+                    mem_indexes=m.mem_manager.alloc(n).clone(), input_ids=ids,
+                    b_ready_cache_len=torch.zeros(1, dtype=torch.int32), max_q_len=n, return_all_logits=True)
+    got = m.forward(mi).logits.float()
+    assert (got - ref).abs().max().item() < 2e-3 * max(ref.abs().max().item(), 1.0)
