@@ -351,7 +351,7 @@ class StableLM(GenericDecoderLM):
         self.rot_dim = int(self.head_dim * self.partial_rotary)
 
 
-@register_model("gemma3_text", "gemma3")
+@register_model("gemma3_text")
 class Gemma3TextLM(GenericDecoderLM):
     """Gemma-3 language model: RMSNorm with (1 + w), q/k norm, sandwich norms, five sliding-window layers
     (local rotary base) per global layer, GeGLU, embeddings scaled by sqrt(hidden)."""
@@ -398,7 +398,7 @@ class Gemma3TextLM(GenericDecoderLM):
         if src.has("model.embed_tokens.weight"):
             return src
         # multimodal checkpoints keep the text tower under language_model
-        for pre in ("language_model.model.", "model.language_model."):
+        for pre in ("model.language_model.model.", "language_model.model.", "model.language_model."):
             if src.has(pre + "embed_tokens.weight"):
                 t = {}
                 for n in src.names() if hasattr(src, "names") else []:
@@ -406,3 +406,85 @@ class Gemma3TextLM(GenericDecoderLM):
                         t["model." + n[len(pre):]] = n
                 return RemapSource(src, t)
         return src
+
+
+@register_model("gemma3", is_multimodal=True)
+class Gemma3LM(Gemma3TextLM):
+    """Gemma-3 with pictures: the SigLIP tower's 256 soft tokens per picture replace the placeholder rows (not
+    scaled like word embeddings), and the tokens of one picture attend to each other in both directions: their
+    causal limit is the picture's last position.  Reference: lightllm/models/gemma3/model.py (which keeps the
+    picture tokens causal)."""
+
+    def _prepare_prefill_state(self, st):
+        super()._prepare_prefill_state(st)
+        mm = st.extra.get("multimodal_params")
+        if not mm:
+            return
+        ids = st.extra["input_ids_cpu"]
+        q_len = st.extra["q_len_cpu"].tolist()
+        pos = st.seq_pos.clone()
+        changed, off = False, 0
+        for b, n_tok in enumerate(q_len):  # per request: the same picture may appear in several requests of a batch
+            params = mm[b] if b < len(mm) and mm[b] else {}
+            seg = ids[off:off + n_tok]
+            for it in params.get("images", []):
+                t0, n = it.get("token_id"), it.get("token_num")
+                if t0 is None:
+                    continue
+                hit = ((seg >= t0) & (seg < t0 + n)).nonzero(as_tuple=True)[0]
+                if hit.numel() > 1:
+                    hit = (hit + off).to(pos.device)
+                    pos[hit] = pos[hit].max()
+                    changed = True
+            off += n_tok
+        if changed:
+            st.seq_pos = pos
+
+
+class Gemma3Tokenizer:
+    """`<start_of_image>` in the prompt becomes begin-of-image id + the picture's virtual ids + end-of-image id."""
+
+    def __init__(self, tokenizer, model_cfg: dict):
+        self.tokenizer = tokenizer
+        self.boi_token, self.eoi_token = "<start_of_image>", "<end_of_image>"
+        self.boi_id = model_cfg.get("boi_token_index", model_cfg.get("boi_token_id", 255_999))
+        self.eoi_id = model_cfg.get("eoi_token_index", model_cfg.get("eoi_token_id", 256_000))
+        self.image_token_id = model_cfg.get("image_token_index", model_cfg.get("image_token_id", 262_144))
+        self.image_length = int(model_cfg.get("mm_tokens_per_image", 256))
+
+    def __getattr__(self, name):
+        return getattr(self.tokenizer, name)
+
+    def init_imageitem_extral_params(self, img, multi_params=None, sampling_params=None):
+        pass
+
+    def get_image_token_length(self, img) -> int:
+        return self.image_length
+
+    def encode(self, prompt, multimodal_params=None, add_special_tokens: bool = False, **kw):
+        images = list(multimodal_params.images) if multimodal_params is not None else []
+
+        def run(im):
+            return [self.boi_id] + list(range(im.token_id, im.token_id + im.token_num)) + [self.eoi_id]
+
+        if isinstance(prompt, (list, tuple)):  # token ids: every image placeholder id stands for one picture
+            out, k = [], 0
+            for t in prompt:
+                if t == self.image_token_id and k < len(images):
+                    out += run(images[k])
+                    k += 1
+                else:
+                    out.append(t)
+        else:
+            chunks = prompt.split(self.boi_token)
+            out = list(self.tokenizer.encode(chunks[0], add_special_tokens=add_special_tokens))
+            k = 0
+            for c in chunks[1:]:
+                if k >= len(images):
+                    raise ValueError("more <start_of_image> tags than pictures")
+                out += run(images[k])
+                k += 1
+                out += list(self.tokenizer.encode(c, add_special_tokens=False))
+        if k != len(images):
+            raise ValueError(f"the prompt has {k} image placeholders for {len(images)} images")
+        return out

@@ -64,6 +64,10 @@ def get_tokenizer(model_dir: str, tokenizer_mode: str = "fast", trust_remote_cod
         from ..models.qwen2_vl import Qwen3VLTokenizer
 
         return Qwen3VLTokenizer(tok, cfg)
+    if mt == "gemma3":
+        from ..models.generic import Gemma3Tokenizer
+
+        return Gemma3Tokenizer(tok, cfg)
     if mt == "internvl_chat":
         from ..models.internvl import InternVLTokenizer
 

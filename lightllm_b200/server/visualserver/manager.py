@@ -53,6 +53,10 @@ def build_vision_tower(args, device, dtype=torch.bfloat16):
         from ...models.vit.clip_visual import ClipLlavaTower
 
         return ClipLlavaTower(cfg, SafetensorsSource(args.model_dir), device, dtype)
+    if mt == "gemma3":
+        from ...models.vit.siglip_visual import SiglipGemma3Tower
+
+        return SiglipGemma3Tower(cfg, SafetensorsSource(args.model_dir), device, dtype)
     if mt == "internvl_chat":
         from ...models.base import TransformerLM
         from ...models.vit.internvl_visual import InternVLVisionTower

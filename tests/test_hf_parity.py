@@ -663,3 +663,63 @@ def test_qwen3_5_text_model_separate_projections(tmp_path):
                     b_ready_cache_len=torch.zeros(1, dtype=torch.int32), max_q_len=n, return_all_logits=True)
     got = m.forward(mi).logits.float()
     assert (got - ref).abs().max().item() < 2e-3 * max(ref.abs().max().item(), 1.0)
+
+
+def test_gemma3_siglip_tower_and_bidirectional_picture_tokens(tmp_path):
+    from transformers import Gemma3Config, Gemma3ForConditionalGeneration
+
+    from lightllm_b200.common.infer_state import ModelInput
+    from lightllm_b200.models.base import load_config
+    from lightllm_b200.models.registry import get_model, is_multimodal
+    from lightllm_b200.models.vit.siglip_visual import SiglipGemma3Tower
+    from lightllm_b200.models.weights import SafetensorsSource
+    from lightllm_b200.parallel import dist as pdist
+    import json
+    import os
+
+    torch.manual_seed(0)
+    text = dict(hidden_size=64, intermediate_size=128, num_hidden_layers=3, num_attention_heads=2, num_key_value_heads=1,
+                head_dim=32, vocab_size=300, sliding_window=64, query_pre_attn_scalar=32, max_position_embeddings=256,
+                layer_types=["sliding_attention", "sliding_attention", "full_attention"])
+    vision = dict(hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4, image_size=56,
+                  patch_size=14, num_channels=3)
+    cfg = Gemma3Config(text_config=text, vision_config=vision, mm_tokens_per_image=4, image_token_index=290,
+                       boi_token_index=291, eoi_token_index=292)
+    hf = Gemma3ForConditionalGeneration(cfg).eval().float()
+    with torch.no_grad():
+        hf.model.multi_modal_projector.mm_input_projection_weight.normal_(0, 0.1)
+    d = str(tmp_path / "ckpt")
+    hf.save_pretrained(d, safe_serialization=True)
+    pixels = torch.randn(1, 3, 56, 56)
+    n_img = 4
+    pre, post = [5, 17, 291], [292, 9, 44, 120]
+    hf_ids = torch.tensor([pre + [290] * n_img + post])
+    with torch.no_grad():
+        ref = hf(input_ids=hf_ids, pixel_values=pixels, token_type_ids=(hf_ids == 290).long()).logits[0].float()
+        feats = hf.model.get_image_features(pixels)
+        want_emb = (feats.pooler_output if hasattr(feats, "pooler_output") else feats).reshape(n_img, -1)
+    raw_cfg = json.load(open(os.path.join(d, "config.json")))
+    assert is_multimodal(load_config(d))
+    tower = SiglipGemma3Tower(raw_cfg, SafetensorsSource(d), torch.device("cpu"), torch.float32)
+    emb = tower.forward(pixels)[0]
+    assert (emb - want_emb).abs().max().item() < 1e-4
+
+    class Arena:
+        def read_rows(self, rows):
+            return emb[rows - 3]
+
+    m = get_model(load_config(d), model_dir=d, pstate=pdist.ParallelState(device=torch.device("cpu")),
+                  data_type="float32", max_total_token_num=256, max_req_num=2, max_seq_length=128, disable_cudagraph=True)
+    assert type(m).__name__ == "Gemma3LM"
+    m.embed_arena = Arena()
+    tok0 = 100_000_000
+    ids = torch.tensor(pre + list(range(tok0, tok0 + n_img)) + post)
+    item = {"token_id": tok0, "token_num": n_img, "start_index_in_embed_cache": 3}
+    req, n = m.req_manager.alloc(), len(ids)
+    mi = ModelInput(batch_size=1, total_token_num=n, max_kv_len=n, is_prefill=True,
+                    b_req_idx=torch.tensor([req], dtype=torch.int32), b_seq_len=torch.tensor([n], dtype=torch.int32),
+                    mem_indexes=m.mem_manager.alloc(n).clone(), input_ids=ids,
+                    b_ready_cache_len=torch.zeros(1, dtype=torch.int32), max_q_len=n, return_all_logits=True,
+                    multimodal_params=[{"images": [item], "audios": []}])
+    got = m.forward(mi).logits.float()
+    assert (got - ref).abs().max().item() < 2e-3 * max(ref.abs().max().item(), 1.0)
