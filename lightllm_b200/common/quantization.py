@@ -12,14 +12,17 @@ Methods here:
                           spellings of this scheme are aliases: there is one kernel.
   fp8w8a8, fp8w8a8-pt,    per-channel / per-tensor / per-group fp8 schemes of the reference: run on the same block-scaled
   fp8w8a8g128, ...        kernel (weights are re-quantised at load with block scales, which are at least as fine)
-Methods that need a kernel that does not exist here (int8 `w8a8`, `awq`, `awq_marlin`, `fp4fp8-b32`) raise at
-start-up instead of silently running in another precision.
+  w8a8                    s8 weights with per-channel scales, s8 activations with per-token scales, s32 accumulation
+                          (tcgen05 kind::i8, `csrc/gemm_fp8.cu`); dense matrices only, experts stay bf16
+Methods that need a kernel that does not exist here (`awq`, `awq_marlin`, `fp4fp8-b32`) raise at start-up instead
+of silently running in another precision.
 """
 from __future__ import annotations
 
 from typing import Dict, Optional
 
 FP8_BLOCK = "fp8w8a8-b128"
+INT8 = "w8a8"
 NONE = "none"
 
 _ALIASES = {
@@ -29,10 +32,11 @@ _ALIASES = {
     "fp8w8a8": FP8_BLOCK, "fp8w8a8-vllm": FP8_BLOCK, "vllm-fp8w8a8": FP8_BLOCK, "fp8w8a8-pt-vllm": FP8_BLOCK,
     "fp8w8a8-pt-sgl": FP8_BLOCK, "fp8w8a8-pt-triton": FP8_BLOCK, "fp8w8a8g128": FP8_BLOCK, "fp8w8a8g64": FP8_BLOCK,
     "fp8w8a8g128-triton": FP8_BLOCK, "triton-fp8w8a8g128": FP8_BLOCK, "fp8": FP8_BLOCK,
+    "w8a8": INT8, "vllm-w8a8": INT8, "w8a8-vllm": INT8,
 }
-_UNBUILT = ("w8a8", "vllm-w8a8", "awq", "awq_marlin", "fp4fp8-b32-deepgemm", "fp4fp8-b32", "fp4")
+_UNBUILT = ("awq", "awq_marlin", "fp4fp8-b32-deepgemm", "fp4fp8-b32", "fp4")
 
-QUANTMETHODS = (NONE, FP8_BLOCK)
+QUANTMETHODS = (NONE, FP8_BLOCK, INT8)
 
 
 def canonical(name: Optional[str]) -> str:
@@ -89,5 +93,7 @@ class QuantConfig:
 
     @property
     def any_fp8(self) -> bool:
-        return self.default == FP8_BLOCK or self.expert_method == FP8_BLOCK or any(
-            m == FP8_BLOCK for d in self.per_layer.values() for m in d.values())
+        """True if some weight asks for online quantisation (fp8 or int8)."""
+        q = (FP8_BLOCK, INT8)
+        return self.default in q or self.expert_method in q or any(
+            m in q for d in self.per_layer.values() for m in d.values())

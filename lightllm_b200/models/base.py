@@ -267,8 +267,9 @@ class TransformerLM:
         """`--quant_type fp8w8a8*` (or a `--quant_cfg` entry for this layer) on weights that are still bf16 after
         loading: quantise them to e4m3 with block scales so the layer runs on the fp8 GEMM.  Weights a model
         already loaded as fp8 (block-quantised checkpoints) are left alone."""
-        from ..common.quantization import FP8_BLOCK
+        from ..common.quantization import FP8_BLOCK, INT8
         from ..ops.fp8 import Fp8Experts, Fp8Weight, stack_experts
+        from ..ops.int8 import Int8Weight
 
         t = lw.tensors()
         silu = getattr(self, "act", "silu") == "silu"
@@ -278,9 +279,13 @@ class TransformerLM:
 
         def q2(name, rows=128):
             w = t.get(name)
-            if isinstance(w, torch.Tensor) and w.dim() == 2 and w.shape[1] % 16 == 0 and w.is_floating_point() \
-                    and want(name):
+            if not (isinstance(w, torch.Tensor) and w.dim() == 2 and w.shape[1] % 16 == 0 and w.is_floating_point()):
+                return
+            method = self.quant_cfg.method_for(layer, name)
+            if method == FP8_BLOCK:
                 t[name] = Fp8Weight.from_float(w, rows)
+            elif method == INT8:
+                t[name] = Int8Weight.from_float(w)
 
         for name in ("qkv_w", "o_w", "down_w", "shared_down_w", "q_b_w"):
             q2(name)
@@ -705,7 +710,7 @@ class TransformerLM:
         for lw in self.layers:
             vals = list(lw.tensors().values())
             tensors += [t for t in vals if isinstance(t, torch.Tensor)]
-            n += sum(t.nbytes() for t in vals if type(t).__name__ in ("Fp8Weight", "Fp8Experts"))
+            n += sum(t.nbytes() for t in vals if type(t).__name__ in ("Fp8Weight", "Fp8Experts", "Int8Weight"))
         for t in tensors:
             if t is not None and t.data_ptr() not in seen:
                 seen.add(t.data_ptr())

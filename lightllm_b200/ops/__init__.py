@@ -213,6 +213,10 @@ def gemm(a, w, epi: str = "store", residual=None, bias=None, out=None, bn: int =
         from . import fp8
 
         return fp8.gemm_fp8(a, w, epi, residual, bias, out)
+    if type(w).__name__ == "Int8Weight":  # per-channel s8 weight, per-token s8 activations, s32 accumulation
+        from . import int8
+
+        return int8.gemm_int8(a, w, epi, residual, bias, out)
     if not _is_cuda(a):
         res = ref.gemm(a, w, epi, residual, bias)
         if out is not None:
