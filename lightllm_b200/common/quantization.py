@@ -58,8 +58,9 @@ class QuantConfig:
         self.from_checkpoint = NONE
         if hf.get("quant_method") == "fp8" and list(hf.get("weight_block_size") or []) == [128, 128]:
             self.from_checkpoint = FP8_BLOCK
-        elif hf.get("quant_method") in ("awq", "gptq", "compressed-tensors"):
+        elif hf.get("quant_method") in ("gptq", "compressed-tensors"):
             raise NotImplementedError(f"checkpoints quantised with {hf.get('quant_method')} are not supported")
+        # quant_method "awq": the loader expands the 4-bit weights to bf16 (models/quant.py), method stays "none"
         self.default = canonical(quant_type)
         self.per_layer: Dict[int, Dict[str, str]] = {}
         if quant_cfg_path:

@@ -139,7 +139,7 @@ class TransformerLM:
         self.graph_max_len_in_batch = graph_max_len_in_batch or max_seq_length
 
         if weight_source is None:
-            weight_source = self._wrap_source(SafetensorsSource(model_dir)) \
+            weight_source = self._wrap_source(self._open_checkpoint(model_dir)) \
                 if model_dir and self._has_weights(model_dir) else RandomSource(self.weight_shapes(), dtype=self.dtype, seed=random_seed,
                              device=str(self.device) if self.device.type == "cuda" else "cpu",
                              fp8_names=self.fp8_weight_names())
@@ -155,6 +155,16 @@ class TransformerLM:
         self._graphs: Dict[int, dict] = {}
         self._graph_pool = None
         self.weight_version = "default"
+
+    def _open_checkpoint(self, model_dir):
+        """The checkpoint as a WeightSource; AWQ checkpoints are presented de-quantised (no int4 GEMM here)."""
+        src = SafetensorsSource(model_dir)
+        q = self.config.get("quantization_config") or {}
+        if q.get("quant_method") == "awq":
+            from .quant import AwqDequantSource
+
+            src = AwqDequantSource(src, self.dtype)
+        return src
 
     def _wrap_source(self, src: WeightSource) -> WeightSource:
         """Hook for families whose checkpoints use other tensor names or fused tensors: return a view of `src`

@@ -92,3 +92,86 @@ class DequantSource:
 
     def get(self, n, dim=None, start=0, end=None):
         return load_dequant(self.base, n, dim, start, end, self.dtype)
+
+
+# ---- AWQ (4-bit weight-only, AutoAWQ "GEMM" packing) ----
+# `X.qweight` int32 [K, N/8] holds eight 4-bit values per word in the order 0, 2, 4, 6, 1, 3, 5, 7 (value j of a
+# word sits at bits 4 * AWQ_ORDER.index(j)), `X.qzeros` int32 [K/g, N/8] the zero points in the same packing,
+# `X.scales` fp16 [K/g, N]; the weight is W[n, k] = (q[k, n] - z[k / g, n]) * s[k / g, n].  There is no int4 GEMM in
+# this build: such checkpoints are expanded to bf16 at load (reference: lightllm/common/quantization/awq.py runs
+# them through vllm's awq / marlin kernels).
+_AWQ_REVERSE = (0, 4, 1, 5, 2, 6, 3, 7)
+
+
+def awq_unpack(packed: torch.Tensor) -> torch.Tensor:
+    """int32 [R, C/8] -> int32 [R, C] of 4-bit values in natural column order."""
+    shifts = torch.arange(0, 32, 4, device=packed.device, dtype=torch.int32)
+    v = (packed.unsqueeze(-1) >> shifts) & 0xF                      # [R, C/8, 8] in packed order
+    v = v[:, :, list(_AWQ_REVERSE)]
+    return v.reshape(packed.shape[0], -1)
+
+
+def awq_pack(values: torch.Tensor) -> torch.Tensor:
+    """Inverse of `awq_unpack` (used by tests and by tools that write checkpoints)."""
+    R, C = values.shape
+    v = values.to(torch.int32).view(R, C // 8, 8)
+    order = (0, 2, 4, 6, 1, 3, 5, 7)
+    out = torch.zeros(R, C // 8, dtype=torch.int32, device=values.device)
+    for pos, j in enumerate(order):
+        out |= (v[:, :, j] & 0xF) << (4 * pos)
+    return out
+
+
+def awq_dequant(qweight, qzeros, scales, dtype=torch.bfloat16) -> torch.Tensor:
+    """-> [N, K] weight in the checkpoint layout of an unquantised Linear."""
+    q = awq_unpack(qweight)                   # [K, N]
+    z = awq_unpack(qzeros)                    # [K/g, N]
+    g = q.shape[0] // z.shape[0]
+    w = (q - z.repeat_interleave(g, dim=0)).float() * scales.float().repeat_interleave(g, dim=0)
+    return w.t().contiguous().to(dtype)
+
+
+class AwqDequantSource:
+    """WeightSource view of an AWQ checkpoint: `X.weight` is built from `X.qweight / qzeros / scales`."""
+
+    def __init__(self, base, dtype=torch.bfloat16):
+        self.base, self.dtype = base, dtype
+        self._last = (None, None)
+
+    def _q(self, n):
+        return n.endswith(".weight") and not self.base.has(n) and self.base.has(n[:-len("weight")] + "qweight")
+
+    def has(self, n):
+        return self.base.has(n) or self._q(n)
+
+    def names(self):
+        out = []
+        for n in self.base.names():
+            if n.endswith(".qweight"):
+                out.append(n[:-len("qweight")] + "weight")
+            elif not (n.endswith(".qzeros") or n.endswith(".scales")):
+                out.append(n)
+        return out
+
+    def _full(self, n):
+        if self._last[0] != n:
+            p = n[:-len("weight")]
+            self._last = (n, awq_dequant(self.base.get(p + "qweight"), self.base.get(p + "qzeros"),
+                                         self.base.get(p + "scales"), self.dtype))
+        return self._last[1]
+
+    def shape(self, n):
+        if self._q(n):
+            p = n[:-len("weight")]
+            k, n8 = self.base.shape(p + "qweight")
+            return (n8 * 8, k)
+        return self.base.shape(n)
+
+    def get(self, n, dim=None, start=0, end=None):
+        if not self._q(n):
+            return self.base.get(n, dim, start, end)
+        t = self._full(n)
+        if dim is not None:
+            end = t.shape[dim] if end is None else end
+            t = t.narrow(dim, start, end - start)
+        return t
