@@ -16,6 +16,7 @@ chunked_prefill/impl.py (ChunkedPrefillBackend), generic_pre_process.py, generic
 """
 from __future__ import annotations
 
+import os
 import time
 from dataclasses import dataclass
 from typing import Callable, Dict, List, Optional
@@ -47,6 +48,9 @@ class BackendArgs:
     cpu_cache_page_tokens: int = 256
     disk_cache_dir: Optional[str] = None
     disk_cache_bytes: int = 0
+    # decode steps are launched before the previous step's tokens have been read back: the host-side bookkeeping
+    # of step k (token append, finish checks, publishing) runs while the GPU executes step k + 1
+    enable_decode_overlap: bool = True
 
 
 class PinnedRing:
@@ -128,6 +132,7 @@ class ModelBackend:
         self.stats = {"prefill_steps": 0, "decode_steps": 0, "prefill_tokens": 0, "decode_tokens": 0,
                       "h2d_bytes": 0, "d2h_bytes": 0, "paused": 0}
         self._steps = 0
+        self._pending = None  # a launched decode step whose tokens have not been read back yet
 
     # ------------------------------------------------------------------ requests
     def add_reqs(self, shm_reqs: List[Req]) -> List[InferReq]:
@@ -150,7 +155,7 @@ class ModelBackend:
             req.stop_str_matched = True
 
     def has_work(self) -> bool:
-        return bool(self.ctx.requests)
+        return bool(self.ctx.requests) or self._pending is not None
 
     # ------------------------------------------------------------------ classification
     def _get_classed_reqs(self):
@@ -179,7 +184,12 @@ class ModelBackend:
                     ctx.recover_req(req)
                 else:
                     continue
-            if req.need_prefill():
+            if req.inflight:
+                # its last token is still on the device: it decodes on unless that token must be its last
+                out = req.cur_output_len + req.inflight
+                if out >= req.sampling.max_new_tokens or req.shm_req.input_len + out >= a.max_req_total_len:
+                    continue
+            if not req.inflight and req.need_prefill():
                 remaining = req.total_len() - req.cur_kv_len
                 chunk = min(remaining, chunk_cap)
                 if chunk <= budget and chunk <= can_alloc:
@@ -218,10 +228,18 @@ class ModelBackend:
         prefill, decode, finished = self._get_classed_reqs()
         kind = self.control.select(len(prefill), len(decode))
         n_tok = 0
-        if kind == "prefill":
-            n_tok = self._run_prefill(prefill)
-        elif kind == "decode":
-            n_tok = self._run_decode(decode)
+        if kind == "decode" and self._can_defer(decode):
+            n_tok = self._run_decode(decode, defer=True)   # launches step k + 1, then settles step k
+        else:
+            if self._pending is not None:  # settle the step in flight, then look at the requests again
+                self._flush_pending()
+                prefill, decode, fin2 = self._get_classed_reqs()
+                finished += [r for r in fin2 if r not in finished]
+                kind = self.control.select(len(prefill), len(decode))
+            if kind == "prefill":
+                n_tok = self._run_prefill(prefill)
+            elif kind == "decode":
+                n_tok = self._run_decode(decode)
         for req in list(self.ctx.requests.values()):
             if req.finish_status.is_finished() and req not in finished:
                 finished.append(req)
@@ -304,7 +322,37 @@ class ModelBackend:
             off += c
 
     # ---- decode ----
-    def _run_decode(self, reqs: List[InferReq]) -> int:
+    def _can_defer(self, reqs: List[InferReq]) -> bool:
+        """A decode step may be launched ahead of the previous step's bookkeeping when nothing on the host shapes its
+        logits (penalties, token masks, constrained decoding) and this is the plain backend."""
+        on_gpu = self.device.type == "cuda" or os.environ.get("LLB_FORCE_DECODE_OVERLAP") == "1"  # CPU: tests only
+        if not (self.args.enable_decode_overlap and on_gpu and type(self) is ModelBackend):
+            return False
+        if self.decode_mask_func is not None or self.extra_post_req_handle_func is not None:
+            return False
+        for r in reqs:
+            sp = r.sampling
+            if sp.has_penalty or sp.invalid_token_ids or sp.exp_decay_factor > 1.0 or \
+                    (self.eos_ids and not sp.ignore_eos and r.cur_output_len + r.inflight + 1 < sp.min_new_tokens):
+                return False
+        return True
+
+    def _flush_pending(self):
+        """Reads back the tokens of the decode step in flight and does its host-side bookkeeping."""
+        pend, self._pending = self._pending, None
+        if pend is None:
+            return
+        reqs, ids_h, lps_h, event = pend
+        if event is not None:
+            event.synchronize()
+        live = []
+        for i, r in enumerate(reqs):
+            r.inflight = 0
+            # a request that ended in the meantime (its previous token was an end token) drops this extra token
+            live.append(not r.finish_status.is_finished())
+        self._post(reqs, ids_h.numpy(), lps_h.numpy(), np.array(live, dtype=bool))
+
+    def _run_decode(self, reqs: List[InferReq], defer: bool = False) -> int:
         B = len(reqs)
         slots = self.ctx.alloc_slots(B)
         slots_np = slots.numpy()
@@ -321,15 +369,35 @@ class ModelBackend:
                         b_seq_len=pin.from_numpy("d_seq", seq, torch.int32), mem_indexes=slots)
         self.stats["h2d_bytes"] += B * 12
         out = self.model.forward(mi)
-        self._sample_and_post(reqs, out.logits, np.ones(B, dtype=bool), is_prefill=False)
+        if defer:
+            ids, lps = self._sample(reqs, out.logits, np.ones(B, dtype=bool), is_prefill=False)
+            if self.device.type == "cuda":
+                ids_h = self.pins.get("s_ids", B, torch.int64)
+                lps_h = self.pins.get("s_lps", B, torch.float32)
+                ids_h.copy_(ids, non_blocking=True)
+                lps_h.copy_(lps, non_blocking=True)
+                event = torch.cuda.Event()
+                event.record(torch.cuda.current_stream(self.device))
+            else:
+                ids_h, lps_h, event = ids.clone(), lps.clone(), None
+            self.stats["d2h_bytes"] += B * 12
+            prev, self._pending = self._pending, None
+            if prev is not None:  # the previous step's bookkeeping overlaps this step's execution
+                self._pending = prev
+                self._flush_pending()
+            for r in reqs:
+                r.inflight = 1
+            self._pending = (reqs, ids_h, lps_h, event)
+        else:
+            self._sample_and_post(reqs, out.logits, np.ones(B, dtype=bool), is_prefill=False)
         self.stats["decode_steps"] += 1
         self.stats["decode_tokens"] += B
         return B
 
     # ---- sampling + post ----
-    def _sample_and_post(self, reqs: List[InferReq], logits: torch.Tensor, has_out: np.ndarray, is_prefill: bool):
+    def _sample(self, reqs: List[InferReq], logits: torch.Tensor, has_out: np.ndarray, is_prefill: bool):
+        """Masks / penalties, sampling and the device-side hand-over of the sampled ids to the next decode step."""
         dev = self.device
-        B = len(reqs)
         sp = [r.sampling for r in reqs]
         mask_func = self.prefill_mask_func if is_prefill else self.decode_mask_func
         if mask_func is not None:
@@ -343,12 +411,18 @@ class ModelBackend:
             top_p = torch.tensor([s.top_p for s in sp], dtype=torch.float32).to(dev, non_blocking=True)
             top_k = torch.tensor([s.top_k for s in sp], dtype=torch.int32).to(dev, non_blocking=True)
             seeds = torch.tensor([r.seed for r in reqs], dtype=torch.int64).to(dev, non_blocking=True)
-            steps = torch.tensor([r.cur_output_len for r in reqs], dtype=torch.int64).to(dev, non_blocking=True)
+            steps = torch.tensor([r.cur_output_len + r.inflight for r in reqs], dtype=torch.int64).to(dev, non_blocking=True)
             ids, lps = ops.sample(logits, temp, top_p, top_k, seeds, steps)
         # the next decode step reads its input ids on the device
         b_req_idx = torch.tensor([r.req_idx for r in reqs], dtype=torch.int32).to(dev, non_blocking=True)
         has_dev = None if has_out.all() else torch.from_numpy(has_out.astype(np.uint8)).to(dev, non_blocking=True)
         ops.scatter_next_token_(self.model.req_manager.req_to_next_token_ids, ids, b_req_idx, has_dev)
+        return ids, lps
+
+    def _sample_and_post(self, reqs: List[InferReq], logits: torch.Tensor, has_out: np.ndarray, is_prefill: bool):
+        dev = self.device
+        B = len(reqs)
+        ids, lps = self._sample(reqs, logits, has_out, is_prefill)
         if dev.type == "cuda":
             ids_h = self.pins.get("s_ids", B, torch.int64)
             lps_h = self.pins.get("s_lps", B, torch.float32)
@@ -358,11 +432,14 @@ class ModelBackend:
         else:
             ids_h, lps_h = ids, lps
         self.stats["d2h_bytes"] += B * 12
-        ids_np, lps_np = ids_h.numpy(), lps_h.numpy()
+        self._post(reqs, ids_h.numpy(), lps_h.numpy(), has_out)
+
+    def _post(self, reqs: List[InferReq], ids_np, lps_np, has_out):
+        """Host-side bookkeeping of sampled tokens: append, finish checks, publishing to the shared request."""
         now = time.time()
         for i, r in enumerate(reqs):
             if not has_out[i]:
-                if self.is_master_in_dp:
+                if self.is_master_in_dp and not r.finish_status.is_finished():
                     r.shm_req.shm_cur_kv_len = r.cur_kv_len
                 continue
             tok = int(ids_np[i])

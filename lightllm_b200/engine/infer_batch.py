@@ -68,6 +68,7 @@ class InferReq:
         self.infer_aborted = False
         self.stop_str_matched = False
         self.paused = False
+        self.inflight = 0                      # decode steps launched whose token has not been read back yet
         self.filter_mark = False
         self.out_token_counter: Dict[int, int] = {}
         self.cumlogprob = 0.0
