@@ -103,11 +103,22 @@ gqa_decode_kernel(const bf16* __restrict__ q, int64_t q_stride, const bf16* __re
   const int64_t r2t_base = (int64_t)req * r2t_stride;
   const uint32_t wbase = smem_u32(warp_smem);
 
-  auto issue = [&](int i) {  // i-th tile of this warp
+  // slot numbers of the tile that will be issued next: fetched one call ahead, so that the dependent load (slot
+  // number, then the row) does not sit between two issues
+  auto load_slots = [&](int i) {
+    int slot = -1;
     if (i < my_count) {
       const int p0 = s0 + (warp + 4 * i) * 16;
-      int slot = -1;
       if (lane < 16 && p0 + lane < e0) slot = req_to_token[r2t_base + p0 + lane];
+    }
+    return slot;
+  };
+  int slot_ahead = load_slots(0);
+
+  auto issue = [&](int i) {  // i-th tile of this warp
+    const int slot = slot_ahead;
+    slot_ahead = load_slots(i + 1);
+    if (i < my_count) {
       const uint32_t sb = wbase + (i % STAGES) * STAGE_BYTES;
 #pragma unroll
       for (int j = 0; j < (16 * CH) / 32; ++j) {
