@@ -85,6 +85,14 @@ class LLM:
         return r
 
     def warmup(self, batch_sizes: Optional[List[int]] = None):
+        from ..utils import autotuner
+
+        if autotuner.autotune_level() > 0 and self.model.device.type == "cuda" and self.config.get("intermediate_size"):
+            # tune the GEMM variants of this model's shapes before the decode graphs capture their choices
+            sizes = sorted(set(batch_sizes or self.model.graph_batch_sizes()))
+            pick = sorted({sizes[0], sizes[-1], *sizes[:: max(1, len(sizes) // 6)]})
+            autotuner.tune_model(self.config, self.ps.tp_size, Ms=pick, group=self.ps.cpu_group,
+                                 force=autotuner.autotune_level() >= 2, log=None)
         self.model.warmup_graphs(batch_sizes)
 
     def close(self):

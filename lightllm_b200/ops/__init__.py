@@ -202,6 +202,18 @@ class TiledWeight:
         return self.data.view(N // 128, K // 64, 128, 64).permute(0, 2, 1, 3).reshape(N, K)
 
 
+_autotuner = None
+
+
+def _tuned_bn(M: int, N: int, K: int, epi: str) -> int:
+    global _autotuner
+    if _autotuner is None:
+        from ..utils import autotuner as _autotuner_mod
+
+        _autotuner = _autotuner_mod
+    return _autotuner.gemm_lookup(M, N, K, epi)
+
+
 def gemm(a, w, epi: str = "store", residual=None, bias=None, out=None, bn: int = 0, stream_k: int = 0):
     """C = A . W^T on the tcgen05 tensor cores.  a [M, K], w [N, K] (checkpoint layout).
 
@@ -233,6 +245,8 @@ def gemm(a, w, epi: str = "store", residual=None, bias=None, out=None, bn: int =
     M, K = a.shape
     N = w.shape[0]
     tiled = isinstance(w, TiledWeight)
+    if bn == 0 and stream_k == 0 and M <= 256 and bias is None and not tiled:  # a tuned variant, if one is stored
+        bn = _tuned_bn(M, N, K, epi)
     ldw = (-2 if w.swizzled else -1) if tiled else w.stride(0)
     if tiled:
         w = w.data
