@@ -32,6 +32,7 @@ class ModelInput:
     b_mtp_index: Optional[torch.Tensor] = None
     return_hidden: bool = False          # speculative decoding: also return the final residual stream [T, hidden]
     draft_input_hidden: Optional[torch.Tensor] = None  # draft modules: hidden state of the target model per token
+    verify_pass: bool = False            # speculative decoding: a pass whose later positions may be rolled back
 
 
 @dataclass

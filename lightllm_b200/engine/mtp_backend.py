@@ -120,8 +120,9 @@ class MTPBackend(ModelBackend):
         slots_np = slots.numpy().reshape(B, q)
         for i, r in enumerate(reqs):
             r.slots = np.concatenate([r.slots[: r.cur_kv_len], slots_np[i]])
+        rollback = getattr(self.model, "needs_state_rollback", False)   # models with recurrent per-request state
         out = self.model.forward(self._mi(reqs, base, np.full(B, q, dtype=np.int32), slots, ids,
-                                          return_all_logits=True, return_hidden=True))
+                                          return_all_logits=True, return_hidden=True, verify_pass=rollback))
         logits = out.logits                                            # [B * q, V]
         first_rows = torch.arange(0, B * q, q, device=logits.device)
         if any(r.sampling.has_penalty for r in reqs):
@@ -172,6 +173,8 @@ class MTPBackend(ModelBackend):
             if self.on_token is not None:
                 for j in range(n_emit):
                     self.on_token(r, int(tok_np[i, j]), float(lps_np[i, j]))
+        if rollback:
+            self.model.commit_verify(emitted)
         # next proposals from the accepted positions (requests that just finished need none)
         live = [i for i, r in enumerate(reqs) if not r.finish_status.is_finished()]
         if live:

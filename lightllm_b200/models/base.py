@@ -411,6 +411,7 @@ class TransformerLM:
         st.extra["ready_cpu"] = mi.b_ready_cache_len
         st.extra["req_idx_cpu"] = mi.b_req_idx
         st.extra["draft_input_hidden"] = mi.draft_input_hidden
+        st.extra["verify_pass"] = bool(getattr(mi, "verify_pass", False))
         st.extra["want_hidden"] = bool(mi.return_hidden)
         self._prepare_prefill_state(st)
         h = self._embed(input_ids, st)

@@ -6,8 +6,13 @@ decoder layer over its own KV layer (appended to the target model's pool, same s
 `shared_head` (norm + the target's lm_head unless the checkpoint carries its own) gives the logits of token i+2.
 Checkpoints keep the module under `model.layers.{num_hidden_layers + j}.`.
 
-Reference: lightllm/models/deepseek_mtp, qwen3_moe_mtp, mistral_mtp, glm4_moe_lite_mtp (pre_layer_infer.py: the
-enorm / hnorm / eh_proj fusion; model.py: sharing of the memory and request managers).
+Qwen3.5 keeps its module under `mtp.` (`mtp.fc`, `mtp.pre_fc_norm_embedding`, `mtp.pre_fc_norm_hidden`,
+`mtp.norm`, `mtp.layers.{j}.`): one full-attention layer of the hybrid stack, fed with the target's hidden state
+after the target's final norm.
+
+Reference: lightllm/models/deepseek_mtp, qwen3_moe_mtp, mistral_mtp, glm4_moe_lite_mtp, qwen3_5_mtp,
+qwen3_5_moe_mtp (pre_layer_infer.py: the enorm / hnorm / eh_proj fusion; model.py: sharing of the memory and
+request managers).
 """
 from __future__ import annotations
 
@@ -17,6 +22,7 @@ from .. import ops
 from .deepseek2 import DeepseekV2LM
 from .llama import LlamaLM
 from .qwen3_moe import Qwen3MoeLM
+from .qwen3_next import Qwen3_5LM, Qwen3_5MoeLM, Qwen3NextLM
 from .remap import RemapSource
 
 
@@ -68,11 +74,16 @@ class MTPMixin:
         self.hnorm_w = self._dev(src.get(p + "hnorm.weight"))
         self.eh_proj_w = self._dev(src.get(p + "eh_proj.weight"))
 
+    def _target_hidden(self, prev):
+        return prev
+
     def _embed(self, ids, st):
         e = super()._embed(ids, st)
         prev = st.extra.get("draft_input_hidden")
         assert prev is not None and prev.shape[0] == e.shape[0], "a draft module needs the target's hidden states"
-        cat = torch.cat([ops.rmsnorm(e, self.enorm_w, self.eps), ops.rmsnorm(prev.to(e.dtype), self.hnorm_w, self.eps)],
+        prev = self._target_hidden(prev.to(e.dtype))
+        off = self.norm_w_offset
+        cat = torch.cat([ops.rmsnorm(e, self.enorm_w, self.eps, off), ops.rmsnorm(prev, self.hnorm_w, self.eps, off)],
                         dim=-1)
         return ops.gemm(cat, self.eh_proj_w)
 
@@ -90,8 +101,61 @@ class LlamaMTP(MTPMixin, LlamaLM):
     pass
 
 
+class _Qwen3_5MTPMixin(MTPMixin):
+    """The draft layer is a full-attention layer whatever the target's layer pattern; its KV layer follows the
+    target's full-attention layers in the pool."""
+
+    def _read_config(self, c):
+        c = dict(c)
+        n = c["num_hidden_layers"]
+        interval = int(c.get("full_attention_interval", 4))
+        types = c.get("layer_types") or ["full_attention" if (i + 1) % interval == 0 else "linear_attention"
+                                         for i in range(n)]
+        n_full = sum(t == "full_attention" for t in types)
+        c["layer_types"] = ["full_attention"] * n
+        super()._read_config(c)
+        self.layer_types, self.full_layers, self.lin_layers = ["full_attention"], [0], []
+        self._kv_slot, self._lin_slot = {0: 0}, {}
+        self.kv_layer_offset = n_full + self.mtp_index
+
+    def _wrap_source(self, src):
+        names = list(src.names())
+        t = {}
+        pre = f"mtp.layers.{self.mtp_index}."
+        for n in names:
+            if n.startswith(pre):
+                t["model.layers.0." + n[len(pre):]] = n
+        t.update({"model.layers.0.eh_proj.weight": "mtp.fc.weight",
+                  "model.layers.0.enorm.weight": "mtp.pre_fc_norm_embedding.weight",
+                  "model.layers.0.hnorm.weight": "mtp.pre_fc_norm_hidden.weight",
+                  "model.norm.weight": "mtp.norm.weight"})
+        for canon, tails in (("model.embed_tokens.weight", ("model.language_model.embed_tokens.weight",
+                                                            "language_model.model.embed_tokens.weight",
+                                                            "model.embed_tokens.weight")),
+                             ("lm_head.weight", ("lm_head.weight", "language_model.lm_head.weight"))):
+            for n in tails:
+                if src.has(n):
+                    t[canon] = n
+                    break
+        return Qwen3NextLM._wrap_source(self, RemapSource(src, t))
+
+    def _target_hidden(self, prev):
+        main = self.share_with
+        return ops.rmsnorm(prev, main.final_norm_w, main.eps, main.norm_w_offset)
+
+
+class Qwen3_5MTP(_Qwen3_5MTPMixin, Qwen3_5LM):
+    pass
+
+
+class Qwen3_5MoeMTP(_Qwen3_5MTPMixin, Qwen3_5MoeLM):
+    pass
+
+
 MTP_CLASSES = {"deepseek_v3": DeepseekV3MTP, "deepseek_v2": DeepseekV3MTP, "glm4_moe_lite": DeepseekV3MTP,
-               "kimi_k2": DeepseekV3MTP, "qwen3_moe": Qwen3MoeMTP, "mistral": LlamaMTP, "llama": LlamaMTP}
+               "kimi_k2": DeepseekV3MTP, "qwen3_moe": Qwen3MoeMTP, "mistral": LlamaMTP, "llama": LlamaMTP,
+               "qwen3_5": Qwen3_5MTP, "qwen3_5_text": Qwen3_5MTP, "qwen3_5_moe": Qwen3_5MoeMTP,
+               "qwen3_5_moe_text": Qwen3_5MoeMTP}
 
 
 def build_mtp_modules(main, n_modules: int, model_dir=None, weight_source=None, **kw):

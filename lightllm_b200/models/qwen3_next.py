@@ -151,7 +151,20 @@ class Qwen3NextLM(Qwen3MoeLM):
         n = len(self.lin_layers)
         self.conv_state = torch.zeros((n, rows, self.conv_dim, self.conv_k - 1), dtype=self.dtype, device=self.device)
         self.ssm_state = torch.zeros((n, rows, self.nv, self.dk, self.dv), dtype=torch.float32, device=self.device)
+        self._verify_snaps = {}
         super()._init_mem(max_total_token_num, mem_fraction)
+
+    needs_state_rollback = True   # a verification pass must be followed by `commit_verify`
+
+    def commit_verify(self, n_keep):
+        """After a verification pass (`verify_pass=True`) over the batch: request b keeps its first n_keep[b] >= 1
+        positions; the recurrent state of every linear layer is set to the state after that position."""
+        n_keep = torch.as_tensor(n_keep, dtype=torch.long, device=self.device)
+        for slot, (req, conv_snaps, ssm_snaps) in self._verify_snaps.items():
+            b = torch.arange(req.shape[0], device=self.device)
+            self.conv_state[slot].index_copy_(0, req, conv_snaps[b, n_keep - 1])
+            self.ssm_state[slot].index_copy_(0, req, ssm_snaps[b, n_keep - 1])
+        self._verify_snaps.clear()
 
     # ------------------------------------------------------------------ layers
     def _attention_block(self, i, lw, h, st):
@@ -214,6 +227,27 @@ class Qwen3NextLM(Qwen3MoeLM):
             qq, kk, vv = heads(y)
             core, new_s = la.gated_delta_step(qq, kk, vv, g, beta, ssm_state[req])
             ssm_state.index_copy_(0, req, new_s)
+        elif st.extra.get("verify_pass"):
+            # speculative verification: every request brings the same number of tokens; they go through the
+            # recurrence one position at a time and the state after every position is kept, so that
+            # `commit_verify` can restore the state at the last accepted position
+            req = st.b_req_idx.long()
+            B = req.shape[0]
+            qn = T // B
+            cs, ss = conv_state[req], ssm_state[req]
+            conv_snaps, ssm_snaps, cores = [], [], []
+            for t in range(qn):
+                y, cs = la.causal_conv_step(mixed[t::qn], cs, lw.conv_w)
+                cs = cs.to(conv_state.dtype)
+                qq, kk, vv = heads(y)
+                o, ss = la.gated_delta_step(qq, kk, vv, g[t::qn], beta[t::qn], ss)
+                conv_snaps.append(cs)
+                ssm_snaps.append(ss)
+                cores.append(o)
+            self._verify_snaps[slot] = (req, torch.stack(conv_snaps, dim=1), torch.stack(ssm_snaps, dim=1))
+            conv_state.index_copy_(0, req, cs)
+            ssm_state.index_copy_(0, req, ss)
+            core = torch.stack(cores, dim=1).reshape(T, self.nv, self.dv)
         else:
             q_len, ready, reqs = st.extra["q_len_cpu"].tolist(), st.extra["ready_cpu"].tolist(), \
                 st.extra["req_idx_cpu"].tolist()
