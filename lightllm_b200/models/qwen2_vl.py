@@ -286,3 +286,38 @@ def _qwen3_vl_moe_class():
 
 
 Qwen3VLMoeLM = register_model("qwen3_vl_moe", is_multimodal=True)(_qwen3_vl_moe_class())
+
+
+def _has_vision(cfg: dict) -> bool:
+    return bool(cfg.get("vision_config"))
+
+
+def _qwen3_5_vl_classes():
+    from .qwen3_next import Qwen3_5LM, Qwen3_5MoeLM
+
+    class Qwen3_5VLLM(MRopeMixin, Qwen3_5LM):
+        """Qwen3.5 with its vision tower: the hybrid decoder with interleaved M-RoPE over the rotary quarter of the
+        full-attention heads; the tower is Qwen3-VL's without deep-stack outputs.  Reference: lightllm/models/
+        qwen3_5/model.py."""
+
+        model_type = "qwen3_5"
+        mrope_interleaved = True
+
+        def _wrap_source(self, src):
+            return Qwen3_5LM._wrap_source(self, src)
+
+    class Qwen3_5MoeVLLM(MRopeMixin, Qwen3_5MoeLM):
+        """Qwen3.5-MoE with its vision tower.  Reference: lightllm/models/qwen3_5_moe/model.py."""
+
+        model_type = "qwen3_5_moe"
+        mrope_interleaved = True
+
+        def _wrap_source(self, src):
+            return Qwen3_5MoeLM._wrap_source(self, src)
+
+    return Qwen3_5VLLM, Qwen3_5MoeVLLM
+
+
+Qwen3_5VLLM, Qwen3_5MoeVLLM = _qwen3_5_vl_classes()
+register_model("qwen3_5", condition=_has_vision, is_multimodal=True)(Qwen3_5VLLM)
+register_model("qwen3_5_moe", condition=_has_vision, is_multimodal=True)(Qwen3_5MoeVLLM)

@@ -35,7 +35,11 @@ def get_model_class(config: dict):
 def is_multimodal(config: dict) -> bool:
     from . import _load_all  # noqa: F401
 
-    return any(mm for _, _, mm in _REGISTRY.get(config.get("model_type"), []))
+    cands = _REGISTRY.get(config.get("model_type"), [])
+    for cond, _, mm in cands:   # the variant that `get_model_class` would pick
+        if cond is not None and cond(config):
+            return bool(mm)
+    return any(mm for cond, _, mm in cands if cond is None)
 
 
 def supported_model_types():

@@ -60,7 +60,7 @@ def get_tokenizer(model_dir: str, tokenizer_mode: str = "fast", trust_remote_cod
         from ..models.llava import LlavaTokenizer
 
         return LlavaTokenizer(tok, cfg)
-    if mt in ("qwen3_vl", "qwen3_vl_moe"):
+    if mt in ("qwen3_vl", "qwen3_vl_moe", "qwen3_5", "qwen3_5_moe"):
         from ..models.qwen2_vl import Qwen3VLTokenizer
 
         return Qwen3VLTokenizer(tok, cfg)

@@ -39,7 +39,7 @@ def build_vision_tower(args, device, dtype=torch.bfloat16):
         else:
             src = RandomSource(Qwen2VLVisionTower.weight_shapes(vcfg), dtype=dtype)
         return Qwen2VLVisionTower(vcfg, src, device, dtype)
-    if mt in ("qwen3_vl", "qwen3_vl_moe"):
+    if mt in ("qwen3_vl", "qwen3_vl_moe", "qwen3_5", "qwen3_5_moe"):
         from ...models.base import TransformerLM
         from ...models.vit.qwen3_vl_visual import Qwen3VLVisionTower
 

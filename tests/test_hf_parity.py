@@ -723,3 +723,80 @@ def test_gemma3_siglip_tower_and_bidirectional_picture_tokens(tmp_path):
                     multimodal_params=[{"images": [item], "audios": []}])
     got = m.forward(mi).logits.float()
     assert (got - ref).abs().max().item() < 2e-3 * max(ref.abs().max().item(), 1.0)
+
+
+def test_qwen3_5_vision_tower_and_mrope_on_the_hybrid_decoder(tmp_path):
+    """Qwen3.5 with a picture: the Qwen3-VL style tower without deep-stack outputs, interleaved M-RoPE on the
+    rotary quarter of the full-attention heads, Gated DeltaNet layers in between, against
+    Qwen3_5ForConditionalGeneration."""
+    from transformers import Qwen3_5Config, Qwen3_5ForConditionalGeneration
+
+    from lightllm_b200.common.infer_state import ModelInput
+    from lightllm_b200.models.base import embed_row_width, load_config
+    from lightllm_b200.models.registry import get_model, is_multimodal
+    from lightllm_b200.models.vit.qwen2_vl_visual import patchify
+    from lightllm_b200.models.vit.qwen3_vl_visual import Qwen3VLVisionTower
+    from lightllm_b200.models.weights import SafetensorsSource
+    from lightllm_b200.parallel import dist as pdist
+
+    torch.manual_seed(0)
+    text = dict(hidden_size=64, intermediate_size=128, num_hidden_layers=4, num_attention_heads=4,
+                num_key_value_heads=2, head_dim=64, vocab_size=300, linear_num_value_heads=4, linear_num_key_heads=2,
+                linear_key_head_dim=16, linear_value_head_dim=16, linear_conv_kernel_dim=4, full_attention_interval=2,
+                max_position_embeddings=512,
+                rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "partial_rotary_factor": 0.25,
+                                 "mrope_section": [2, 3, 3], "mrope_interleaved": True})
+    vision = dict(depth=2, hidden_size=32, num_heads=4, intermediate_size=64, out_hidden_size=64, patch_size=16,
+                  spatial_merge_size=2, temporal_patch_size=2, in_channels=3, num_position_embeddings=36,
+                  hidden_act="gelu_pytorch_tanh")
+    cfg = Qwen3_5Config(text_config=text, vision_config=vision, image_token_id=290, video_token_id=291,
+                        vision_start_token_id=292, vision_end_token_id=293, tie_word_embeddings=False)
+    hf = Qwen3_5ForConditionalGeneration(cfg).eval().float()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if ("norm" in n and "visual" not in n) or "dt_bias" in n or "A_log" in n:
+                p.add_(torch.randn_like(p) * 0.1)
+    d = str(tmp_path / "ckpt")
+    hf.save_pretrained(d, safe_serialization=True)
+    # the tensors under the names the modules have (model.language_model.*, model.visual.*), as released checkpoints
+    from safetensors.torch import save_file
+    save_file({k: v.contiguous() for k, v in hf.state_dict().items()}, d + "/model.safetensors")
+
+    pixels = torch.randn(1, 3, 64, 96)
+    patches, (t, gh, gw) = patchify(pixels, patch=16)
+    n_img = t * gh * gw // 4
+    pre, post = [5, 17, 292], [293, 9, 44, 120, 7, 250, 31]
+    hf_ids = torch.tensor([pre + [290] * n_img + post])
+    with torch.no_grad():
+        ref = hf(input_ids=hf_ids, pixel_values=patches, image_grid_thw=torch.tensor([[t, gh, gw]]),
+                 mm_token_type_ids=(hf_ids == 290).long()).logits[0].float()
+        vis = hf.model.visual(patches, grid_thw=torch.tensor([[t, gh, gw]]))
+
+    conf = load_config(d)
+    assert is_multimodal(conf) and embed_row_width(conf) == 64
+    assert not is_multimodal({"model_type": "qwen3_5", "hidden_size": 64})       # a text-only checkpoint
+    src = SafetensorsSource(d)
+    tower = Qwen3VLVisionTower(conf["vision_config"], src, torch.device("cpu"), torch.float32)
+    emb = tower.forward(patches, [(t, gh, gw)])
+    assert emb.shape == (n_img, 64)
+    assert (emb - vis.pooler_output).abs().max().item() < 1e-4
+
+    class Arena:
+        def read_rows(self, rows):
+            return emb[rows - 40]
+
+    m = get_model(conf, model_dir=d, pstate=pdist.ParallelState(device=torch.device("cpu")), data_type="float32",
+                  max_total_token_num=256, max_req_num=2, max_seq_length=128, disable_cudagraph=True)
+    assert type(m).__name__ == "Qwen3_5VLLM" and m.full_layers == [1, 3]
+    m.embed_arena = Arena()
+    tok0 = 100_000_000
+    ids = torch.tensor(pre + list(range(tok0, tok0 + n_img)) + post)
+    item = {"token_id": tok0, "token_num": n_img, "start_index_in_embed_cache": 40, "grid_thwd": (t, gh, gw, 2)}
+    req, n = m.req_manager.alloc(), len(ids)
+    mi = ModelInput(batch_size=1, total_token_num=n, max_kv_len=n, is_prefill=True,
+                    b_req_idx=torch.tensor([req], dtype=torch.int32), b_seq_len=torch.tensor([n], dtype=torch.int32),
+                    mem_indexes=m.mem_manager.alloc(n).clone(), input_ids=ids,
+                    b_ready_cache_len=torch.zeros(1, dtype=torch.int32), max_q_len=n, return_all_logits=True,
+                    multimodal_params=[{"images": [item], "audios": []}])
+    got = m.forward(mi).logits.float()
+    assert (got - ref).abs().max().item() < 2e-3 * max(ref.abs().max().item(), 1.0)
