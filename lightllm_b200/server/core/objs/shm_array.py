@@ -11,6 +11,8 @@ from typing import Optional
 
 import numpy as np
 
+from ....utils.shm_cleanup import get_cleanup, register_posix_shm_for_cleanup
+
 
 def create_or_link_shm(name: str, size: int, force_create: bool = False):
     """Returns (SharedMemory, created)."""
@@ -59,6 +61,7 @@ class ShmArray:
             return self
         self.shm, created = create_or_link_shm(self.name, max(self.nbytes, 1), force_create=True)
         self._owner = True
+        register_posix_shm_for_cleanup(self.name)
         self.arr = np.ndarray(self.shape, dtype=self.dtype, buffer=self.shm.buf)
         return self
 
@@ -78,4 +81,5 @@ class ShmArray:
                     self.shm.unlink()
                 except FileNotFoundError:
                     pass
+                get_cleanup().unregister_posix(self.name)
             self.shm = None
