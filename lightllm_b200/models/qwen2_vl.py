@@ -321,3 +321,27 @@ def _qwen3_5_vl_classes():
 Qwen3_5VLLM, Qwen3_5MoeVLLM = _qwen3_5_vl_classes()
 register_model("qwen3_5", condition=_has_vision, is_multimodal=True)(Qwen3_5VLLM)
 register_model("qwen3_5_moe", condition=_has_vision, is_multimodal=True)(Qwen3_5MoeVLLM)
+
+
+def _text_type_is(kind: str):
+    return lambda cfg: (cfg.get("text_config") or {}).get("model_type") == kind
+
+
+@register_model("llava", condition=_text_type_is("qwen2_vl"), is_multimodal=True)
+class Tarsier2Qwen2VLLM(Qwen2VLLM):
+    """Tarsier2: a `llava` wrapper config whose `text_config` is a Qwen2-VL decoder and whose `vision_tower.*`
+    tensors are the Qwen2-VL tower; the language model sits under `language_model.`.
+    Reference: lightllm/models/tarsier2/model.py (Tarsier2Qwen2VLTpPartModel), tarsier2_visual.py."""
+
+    model_type = "llava"
+
+    def _wrap_source(self, src):
+        if src.has("model.embed_tokens.weight"):
+            return src
+        t = {}
+        for n in src.names():
+            if n.startswith("language_model.model."):
+                t["model." + n[len("language_model.model."):]] = n
+            elif n.startswith("language_model.lm_head."):
+                t["lm_head." + n[len("language_model.lm_head."):]] = n
+        return RemapSource(src, t) if t else src

@@ -28,7 +28,8 @@ def build_vision_tower(args, device, dtype=torch.bfloat16):
 
     cfg = getattr(args, "_config_override", None) or load_config(args.model_dir)
     mt = cfg.get("model_type")
-    if mt in ("qwen2_vl", "qwen2_5_vl"):
+    tarsier2 = mt == "llava" and (cfg.get("text_config") or {}).get("model_type") == "qwen2_vl"
+    if mt in ("qwen2_vl", "qwen2_5_vl") or tarsier2:
         from ...models.base import TransformerLM
         from ...models.vit.qwen2_vl_visual import Qwen2VLVisionTower
 
@@ -38,7 +39,9 @@ def build_vision_tower(args, device, dtype=torch.bfloat16):
             src = SafetensorsSource(args.model_dir)
         else:
             src = RandomSource(Qwen2VLVisionTower.weight_shapes(vcfg), dtype=dtype)
-        return Qwen2VLVisionTower(vcfg, src, device, dtype)
+        # Tarsier2 keeps the same tower under `vision_tower.`
+        prefix = "vision_tower." if tarsier2 and src.has("vision_tower.patch_embed.proj.weight") else None
+        return Qwen2VLVisionTower(vcfg, src, device, dtype, prefix=prefix)
     if mt in ("qwen3_vl", "qwen3_vl_moe", "qwen3_5", "qwen3_5_moe"):
         from ...models.base import TransformerLM
         from ...models.vit.qwen3_vl_visual import Qwen3VLVisionTower

@@ -800,3 +800,78 @@ def test_qwen3_5_vision_tower_and_mrope_on_the_hybrid_decoder(tmp_path):
                     multimodal_params=[{"images": [item], "audios": []}])
     got = m.forward(mi).logits.float()
     assert (got - ref).abs().max().item() < 2e-3 * max(ref.abs().max().item(), 1.0)
+
+
+def test_tarsier2_llava_wrapper_over_qwen2_vl(tmp_path):
+    """Tarsier2 checkpoints: `model_type: llava`, a Qwen2-VL decoder under `language_model.` and its tower under
+    `vision_tower.`; same numbers as Qwen2-VL with the tensors renamed."""
+    import json
+
+    from safetensors.torch import save_file
+    from transformers import Qwen2VLConfig, Qwen2VLForConditionalGeneration
+
+    from lightllm_b200.common.infer_state import ModelInput
+    from lightllm_b200.models.base import load_config
+    from lightllm_b200.models.registry import get_model, is_multimodal
+    from lightllm_b200.models.vit.qwen2_vl_visual import Qwen2VLVisionTower, patchify
+    from lightllm_b200.models.weights import SafetensorsSource
+    from lightllm_b200.parallel import dist as pdist
+
+    torch.manual_seed(0)
+    text = dict(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                vocab_size=300, max_position_embeddings=512, rope_scaling={"type": "mrope", "mrope_section": [2, 3, 3]})
+    vision = dict(depth=2, embed_dim=32, hidden_size=64, num_heads=4, mlp_ratio=2, patch_size=14, spatial_merge_size=2,
+                  temporal_patch_size=2, in_chans=3)
+    hf = Qwen2VLForConditionalGeneration(Qwen2VLConfig(
+        text_config=text, vision_config=vision, image_token_id=290, video_token_id=291, vision_start_token_id=292,
+        vision_end_token_id=293)).eval().float()
+    d = tmp_path / "ckpt"
+    d.mkdir()
+    renamed = {}
+    for k, v in hf.state_dict().items():
+        if k.startswith("model.language_model."):
+            renamed["language_model.model." + k[len("model.language_model."):]] = v.contiguous()
+        elif k.startswith("model.visual."):
+            renamed["vision_tower." + k[len("model.visual."):]] = v.contiguous()
+        elif k.startswith("lm_head."):
+            renamed["language_model." + k] = v.contiguous()
+    save_file(renamed, str(d / "model.safetensors"))
+    wrapper = {"model_type": "llava", "architectures": ["LlavaForConditionalGeneration"],
+               "text_config": dict(hf.config.text_config.to_dict(), model_type="qwen2_vl", image_token_id=290,
+                                   vision_start_token_id=292, vision_end_token_id=293, tie_word_embeddings=False),
+               "vision_config": dict(vision, model_type="qwen2_vl"), "image_token_index": 290}
+    (d / "config.json").write_text(json.dumps(wrapper))
+
+    pixels = torch.randn(1, 3, 56, 84)
+    patches, (t, gh, gw) = patchify(pixels)
+    n_img = t * gh * gw // 4
+    pre, post = [5, 17, 292], [293, 9, 44, 120, 7]
+    hf_ids = torch.tensor([pre + [290] * n_img + post])
+    with torch.no_grad():
+        ref = hf(input_ids=hf_ids, pixel_values=patches, image_grid_thw=torch.tensor([[t, gh, gw]]),
+                 mm_token_type_ids=(hf_ids == 290).long()).logits[0].float()
+    conf = load_config(str(d))
+    assert is_multimodal(conf)
+    tower = Qwen2VLVisionTower(conf["vision_config"], SafetensorsSource(str(d)), torch.device("cpu"), torch.float32,
+                               prefix="vision_tower.")
+    emb = tower.forward(patches, [(t, gh, gw)])
+
+    class Arena:
+        def read_rows(self, rows):
+            return emb[rows - 40]
+
+    m = get_model(conf, model_dir=str(d), pstate=pdist.ParallelState(device=torch.device("cpu")), data_type="float32",
+                  max_total_token_num=256, max_req_num=2, max_seq_length=128, disable_cudagraph=True)
+    assert type(m).__name__ == "Tarsier2Qwen2VLLM"
+    m.embed_arena = Arena()
+    tok0 = 100_000_000
+    ids = torch.tensor(pre + list(range(tok0, tok0 + n_img)) + post)
+    item = {"token_id": tok0, "token_num": n_img, "start_index_in_embed_cache": 40, "grid_thwd": (t, gh, gw, 2)}
+    req, n = m.req_manager.alloc(), len(ids)
+    mi = ModelInput(batch_size=1, total_token_num=n, max_kv_len=n, is_prefill=True,
+                    b_req_idx=torch.tensor([req], dtype=torch.int32), b_seq_len=torch.tensor([n], dtype=torch.int32),
+                    mem_indexes=m.mem_manager.alloc(n).clone(), input_ids=ids,
+                    b_ready_cache_len=torch.zeros(1, dtype=torch.int32), max_q_len=n, return_all_logits=True,
+                    multimodal_params=[{"images": [item], "audios": []}])
+    got = m.forward(mi).logits.float()
+    assert (got - ref).abs().max().item() < 2e-3 * max(ref.abs().max().item(), 1.0)
