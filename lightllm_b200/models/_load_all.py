@@ -8,3 +8,4 @@ from . import gpt_oss  # noqa: F401
 from . import llava  # noqa: F401
 from . import internvl  # noqa: F401
 from . import qwen3_next  # noqa: F401
+from . import qwen3_omni  # noqa: F401

@@ -41,6 +41,8 @@ def normalize_config(cfg: dict) -> dict:
     `rope_theta` / `rope_scaling`, `num_local_experts` doubles as `num_experts`, multimodal wrappers expose
     their `text_config` at the top level."""
     cfg = dict(cfg)
+    if isinstance(cfg.get("thinker_config"), dict) and "text_config" not in cfg:  # Qwen3-Omni: thinker / talker parts
+        cfg = {**cfg, **cfg["thinker_config"], "model_type": cfg.get("model_type")}
     if "text_config" in cfg and "hidden_size" not in cfg:  # multimodal wrappers
         base = dict(cfg["text_config"])
         outer = cfg.get("model_type") or base.get("model_type")

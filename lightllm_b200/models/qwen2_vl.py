@@ -208,7 +208,8 @@ class Qwen3VLLM(MRopeMixin, Qwen3LM):
         ids = st.extra["input_ids_cpu"]
         pos_all, rows_all, seen = [], [], set()
         for params in mm:
-            for it in (params or {}).get("images", []):
+            # audio rows carry zeros in the deep-stack columns
+            for it in list((params or {}).get("images", [])) + list((params or {}).get("audios", [])):
                 t0, n = it.get("token_id"), it.get("token_num")
                 if t0 is None or (t0, n) in seen:
                     continue

@@ -41,6 +41,8 @@ def interpolate_positions(table: torch.Tensor, grids, merge: int) -> torch.Tenso
 class Qwen3VLVisionTower:
     image_mean = (0.5, 0.5, 0.5)
     image_std = (0.5, 0.5, 0.5)
+    merger_keys: dict = {}                          # canonical merger tensor name -> name in the checkpoint
+    deepstack_prefix = "deepstack_merger_list."
 
     def __init__(self, vcfg: dict, source, device, dtype=torch.bfloat16, prefix: str = None):
         self.cfg = vcfg
@@ -70,8 +72,10 @@ class Qwen3VLVisionTower:
                 "norm2.weight", "norm2.bias", "mlp.linear_fc1.weight", "mlp.linear_fc1.bias", "mlp.linear_fc2.weight",
                 "mlp.linear_fc2.bias")})
         names = ("norm.weight", "norm.bias", "linear_fc1.weight", "linear_fc1.bias", "linear_fc2.weight", "linear_fc2.bias")
-        self.merger = {k: g("merger." + k) for k in names}
-        self.ds_mergers = [{k: g(f"deepstack_merger_list.{j}." + k) for k in names} for j in range(len(self.deepstack))]
+        ck = self.merger_keys
+        self.merger = {k: g("merger." + ck.get(k, k)) for k in names}
+        self.ds_mergers = [{k: g(f"{self.deepstack_prefix}{j}." + ck.get(k, k)) for k in names}
+                           for j in range(len(self.deepstack))]
 
     @staticmethod
     def weight_shapes(vcfg: dict, prefix: str = "model.visual.") -> dict:

@@ -27,6 +27,14 @@ def build_audio_tower(args, device, dtype=torch.bfloat16):
     cfg = getattr(args, "_config_override", None) or load_config(args.model_dir)
     if "audio_config" not in cfg:
         raise ValueError(f"model_type {cfg.get('model_type')!r} has no audio tower (no audio_config)")
+    if cfg.get("model_type") == "qwen3_omni_moe":
+        from ...models.qwen3_omni import Qwen3OmniAudioTower
+
+        if args.model_dir and TransformerLM._has_weights(args.model_dir):
+            src = SafetensorsSource(args.model_dir)
+        else:
+            src = RandomSource(Qwen3OmniAudioTower.weight_shapes(cfg), dtype=dtype)
+        return Qwen3OmniAudioTower(cfg, src, device, dtype)
     if args.model_dir and TransformerLM._has_weights(args.model_dir):
         src = SafetensorsSource(args.model_dir)
     else:
@@ -56,6 +64,10 @@ class AudioManager:
             embs = self.tower.encode_audios(clips, items=chunk)
             for it, e in zip(chunk, embs):
                 assert e.shape[0] == it["token_num"], f"clip gives {e.shape[0]} tokens, the prompt reserved {it['token_num']}"
+                arr = getattr(self.cache.arena, "arr", None)
+                width = arr.shape[1] if arr is not None else e.shape[1]
+                if e.shape[1] < width:  # arena rows also hold deep-stack image features: zeros for audio
+                    e = torch.nn.functional.pad(e, (0, width - e.shape[1]))
                 self.cache.arena.write(it["start_index_in_embed_cache"], e)
             self.cache.set_items_embed([a["uuid"] for a in chunk])
 

@@ -52,6 +52,16 @@ def build_vision_tower(args, device, dtype=torch.bfloat16):
         else:
             src = RandomSource(Qwen3VLVisionTower.weight_shapes(vcfg), dtype=dtype)
         return Qwen3VLVisionTower(vcfg, src, device, dtype)
+    if mt == "qwen3_omni_moe":
+        from ...models.base import TransformerLM
+        from ...models.qwen3_omni import Qwen3OmniVisionTower
+
+        vcfg = dict(cfg["vision_config"])
+        if args.model_dir and TransformerLM._has_weights(args.model_dir):
+            src = SafetensorsSource(args.model_dir)
+        else:
+            src = RandomSource(Qwen3OmniVisionTower.weight_shapes(vcfg), dtype=dtype)
+        return Qwen3OmniVisionTower(vcfg, src, device, dtype)
     if mt == "llava":
         from ...models.vit.clip_visual import ClipLlavaTower
 

@@ -104,3 +104,28 @@ def test_audio_manager_embeds_pending_clips():
     assert sent == [g] and 7 in cache.ready and cache.arena.rows[5].shape == (n, 48)
     mgr.handle(g)   # already embedded: passes straight through
     assert len(sent) == 2
+
+
+def test_qwen3_omni_tokenizer_expands_audio_and_image_placeholders():
+    from types import SimpleNamespace
+
+    from lightllm_b200.models.qwen3_omni import Qwen3OmniTokenizer, audio_token_num
+
+    class Tok:
+        def encode(self, text, add_special_tokens=False):
+            return [int(x) for x in text.split()]
+
+    cfg = {"image_token_id": 290, "audio_token_id": 288, "vision_config": {"patch_size": 16, "spatial_merge_size": 2},
+           "audio_config": {"n_window": 50}}
+    tk = Qwen3OmniTokenizer(Tok(), cfg)
+    clip = SimpleNamespace(audio_length=16000 * 3 + 700, token_id=5000, token_num=0)
+    clip.token_num = tk.get_audio_token_length(clip)
+    assert clip.token_num == audio_token_num(48700) == 3 * 13 + 1        # 304 frames: three windows and 4 frames
+    img = SimpleNamespace(token_id=7000, token_num=6)
+    mp = SimpleNamespace(images=[img], audios=[clip])
+    ids = tk.encode("1 292 290 293 2 294 288 295 3", mp)
+    assert ids == [1, 292] + list(range(7000, 7006)) + [293, 2, 294] + list(range(5000, 5000 + clip.token_num)) + [295, 3]
+    import pytest
+
+    with pytest.raises(ValueError):
+        tk.encode("1 294 295", mp)

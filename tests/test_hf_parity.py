@@ -875,3 +875,94 @@ def test_tarsier2_llava_wrapper_over_qwen2_vl(tmp_path):
                     multimodal_params=[{"images": [item], "audios": []}])
     got = m.forward(mi).logits.float()
     assert (got - ref).abs().max().item() < 2e-3 * max(ref.abs().max().item(), 1.0)
+
+
+def test_qwen3_omni_thinker_audio_and_vision_towers(tmp_path):
+    """Qwen3-Omni thinker with a picture and a sound clip in one prompt: audio tower (windowed convolutions, block
+    attention), vision tower under the thinker's tensor names with deep-stack outputs, MoE decoder with interleaved
+    M-RoPE, against Qwen3OmniMoeThinkerForConditionalGeneration."""
+    import json
+
+    from safetensors.torch import save_file
+    from transformers.models.qwen3_omni_moe import modeling_qwen3_omni_moe as hfm
+    from transformers.models.qwen3_omni_moe.configuration_qwen3_omni_moe import Qwen3OmniMoeThinkerConfig
+
+    from lightllm_b200.common.infer_state import ModelInput
+    from lightllm_b200.models.base import embed_row_width, load_config
+    from lightllm_b200.models.qwen3_omni import Qwen3OmniAudioTower, Qwen3OmniVisionTower, audio_token_num
+    from lightllm_b200.models.registry import get_model, is_multimodal
+    from lightllm_b200.models.vit.qwen2_vl_visual import patchify
+    from lightllm_b200.models.weights import SafetensorsSource
+    from lightllm_b200.parallel import dist as pdist
+
+    torch.manual_seed(0)
+    text = dict(hidden_size=64, intermediate_size=128, moe_intermediate_size=64, num_experts=4, num_experts_per_tok=2,
+                num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2, head_dim=16, vocab_size=300,
+                max_position_embeddings=512, norm_topk_prob=True, decoder_sparse_step=1, mlp_only_layers=[],
+                rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "mrope_section": [2, 3, 3],
+                                 "mrope_interleaved": True})
+    vision = dict(depth=3, hidden_size=32, num_heads=4, intermediate_size=64, out_hidden_size=64, patch_size=16,
+                  spatial_merge_size=2, temporal_patch_size=2, in_channels=3, num_position_embeddings=36,
+                  deepstack_visual_indexes=[0, 2], hidden_act="gelu_pytorch_tanh")
+    audio = dict(num_mel_bins=16, encoder_layers=2, encoder_attention_heads=2, encoder_ffn_dim=64, d_model=32,
+                 max_source_positions=64, n_window=50, n_window_infer=200, output_dim=64, downsample_hidden_size=8,
+                 conv_chunksize=500, activation_function="gelu")
+    cfg = Qwen3OmniMoeThinkerConfig(text_config=text, vision_config=vision, audio_config=audio, audio_token_id=288,
+                                    image_token_id=290, video_token_id=291, vision_start_token_id=292,
+                                    vision_end_token_id=293, audio_start_token_id=294, audio_end_token_id=295,
+                                    tie_word_embeddings=False)
+    hf = hfm.Qwen3OmniMoeThinkerForConditionalGeneration(cfg).eval().float()
+    d = tmp_path / "ckpt"
+    d.mkdir()
+    save_file({"thinker." + k: v.contiguous() for k, v in hf.state_dict().items()}, str(d / "model.safetensors"))
+    (d / "config.json").write_text(json.dumps({"model_type": "qwen3_omni_moe", "thinker_config": cfg.to_dict()}))
+
+    pixels = torch.randn(1, 3, 64, 96)
+    patches, (t, gh, gw) = patchify(pixels, patch=16)
+    n_img = t * gh * gw // 4
+    frames = 337                                      # three full windows of 100 mel frames and a tail of 37
+    mel = torch.randn(16, frames)
+    n_aud = 3 * 13 + 5
+    assert audio_token_num(frames * 160) == n_aud
+    pre, mid, post = [5, 17, 292], [293, 9, 294], [295, 44, 120, 7]
+    hf_ids = torch.tensor([pre + [290] * n_img + mid + [288] * n_aud + post])
+    with torch.no_grad():
+        ref = hf(input_ids=hf_ids, pixel_values=patches, image_grid_thw=torch.tensor([[t, gh, gw]]),
+                 input_features=mel.unsqueeze(0), feature_attention_mask=torch.ones(1, frames, dtype=torch.long),
+                 attention_mask=torch.ones_like(hf_ids)).logits[0].float()
+        want_aud = hf.audio_tower(mel, feature_lens=torch.tensor([frames])).last_hidden_state
+        vis = hf.visual(patches, grid_thw=torch.tensor([[t, gh, gw]]))
+
+    conf = load_config(str(d))
+    assert conf["model_type"] == "qwen3_omni_moe" and is_multimodal(conf) and embed_row_width(conf) == 192
+    src = SafetensorsSource(str(d))
+    atower = Qwen3OmniAudioTower(conf, src, torch.device("cpu"), torch.float32)
+    aud = atower.forward(mel)
+    assert aud.shape == (n_aud, 64) and (aud - want_aud).abs().max().item() < 1e-4
+    assert set(Qwen3OmniAudioTower.weight_shapes(conf)) <= set(src.names())
+    vtower = Qwen3OmniVisionTower(conf["vision_config"], src, torch.device("cpu"), torch.float32)
+    emb = vtower.forward(patches, [(t, gh, gw)])
+    assert (emb[:, :64] - vis.pooler_output).abs().max().item() < 1e-4
+    assert set(Qwen3OmniVisionTower.weight_shapes(conf["vision_config"])) <= set(src.names())
+    rows = torch.cat([emb, torch.nn.functional.pad(aud, (0, 128))], dim=0)   # arena: image rows, then audio rows
+
+    class Arena:
+        def read_rows(self, r):
+            return rows[r - 40]
+
+    m = get_model(conf, model_dir=str(d), pstate=pdist.ParallelState(device=torch.device("cpu")), data_type="float32",
+                  max_total_token_num=256, max_req_num=2, max_seq_length=128, disable_cudagraph=True)
+    assert type(m).__name__ == "Qwen3OmniThinkerLM"
+    m.embed_arena = Arena()
+    i0, a0 = 100_000_000, 100_001_000
+    ids = torch.tensor(pre + list(range(i0, i0 + n_img)) + mid + list(range(a0, a0 + n_aud)) + post)
+    image = {"token_id": i0, "token_num": n_img, "start_index_in_embed_cache": 40, "grid_thwd": (t, gh, gw, 2)}
+    clip = {"token_id": a0, "token_num": n_aud, "start_index_in_embed_cache": 40 + n_img}
+    req, n = m.req_manager.alloc(), len(ids)
+    mi = ModelInput(batch_size=1, total_token_num=n, max_kv_len=n, is_prefill=True,
+                    b_req_idx=torch.tensor([req], dtype=torch.int32), b_seq_len=torch.tensor([n], dtype=torch.int32),
+                    mem_indexes=m.mem_manager.alloc(n).clone(), input_ids=ids,
+                    b_ready_cache_len=torch.zeros(1, dtype=torch.int32), max_q_len=n, return_all_logits=True,
+                    multimodal_params=[{"images": [image], "audios": [clip]}])
+    got = m.forward(mi).logits.float()
+    assert (got - ref).abs().max().item() < 2e-3 * max(ref.abs().max().item(), 1.0)
