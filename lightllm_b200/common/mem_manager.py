@@ -154,6 +154,46 @@ class MemoryManager:
             ops.copy_rows(self.kv_buffer[l], pages[l], idx, None, n)
 
 
+class Int8KVMemoryManager(MemoryManager):
+    """GQA/MHA pool with int8 rows: every (slot, head) row is `head_dim` int8 values, an fp32 scale and padding to
+    a multiple of 16 bytes (`ops/kv_quant.py`).  `layer(i)` returns an `Int8KVLayer`, which the attention ops accept
+    in place of a bf16 slice; everything that moves rows (prefix copies, staging pages, host offload) sees opaque
+    int8 rows.  Reference: lightllm/common/kv_cache_mem_manager/ppl_int8kv_mem_manager.py (`--llm_kv_type int8kv`)."""
+
+    def __init__(self, size: int, dtype: torch.dtype, head_num: int, head_dim: int, layer_num: int,
+                 device: torch.device, always_copy: bool = False):
+        self.compute_dtype = dtype
+        super().__init__(size, torch.int8, head_num, head_dim, layer_num, device)
+
+    def kv_row_shape(self):
+        from ..ops.kv_quant import PAD
+
+        return (2 * self.head_num, self.head_dim + PAD)
+
+    @staticmethod
+    def bytes_per_token(dtype, head_num, head_dim, layer_num) -> int:
+        from ..ops.kv_quant import PAD
+
+        return layer_num * 2 * head_num * (head_dim + PAD)
+
+    def layer(self, i: int):
+        from ..ops.kv_quant import Int8KVLayer
+
+        return Int8KVLayer(self.kv_buffer[i], self.head_dim)
+
+
+KV_MANAGERS = {"none": MemoryManager, "int8kv": Int8KVMemoryManager}
+
+
+def select_mem_manager_class(kv_type: Optional[str]):
+    """Pool class for `--llm_kv_type` (reference: kv_cache_mem_manager/mem_utils.py select_mem_manager_class)."""
+    k = (kv_type or "none").lower()
+    if k not in KV_MANAGERS:
+        raise ValueError(f"--llm_kv_type {kv_type!r} is not available (have: {sorted(KV_MANAGERS)}); the int4 and "
+                         "calibrated fp8 pools of the reference are not built")
+    return KV_MANAGERS[k]
+
+
 class MLAMemoryManager(MemoryManager):
     """DeepSeek MLA latent cache: one row [kv_lora_rank + qk_rope_head_dim] per token and layer
     (lightllm/common/kv_cache_mem_manager/deepseek2_mem_manager.py)."""

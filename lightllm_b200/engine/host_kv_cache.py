@@ -38,7 +38,9 @@ class _DiskTier:
     def __init__(self, path: str, n_pages: int, page_shape, dtype):
         self.n_pages = n_pages
         self.page_numel = int(np.prod(page_shape))
-        self.np_dtype = np.uint16 if dtype in (torch.bfloat16, torch.float16) else np.float32
+        self.np_dtype = np.uint16 if dtype in (torch.bfloat16, torch.float16) else \
+            np.int8 if dtype == torch.int8 else np.float32
+        self.t_dtype = {np.uint16: torch.int16, np.int8: torch.int8, np.float32: torch.float32}[self.np_dtype]
         os.makedirs(os.path.dirname(path) or ".", exist_ok=True)
         self.mm = np.memmap(path, dtype=self.np_dtype, mode="w+", shape=(n_pages, self.page_numel))
         self.index: "OrderedDict[bytes, int]" = OrderedDict()
@@ -51,7 +53,7 @@ class _DiskTier:
             _, idx = self.index.popitem(last=False)
             self.free.append(idx)
         idx = self.free.pop()
-        raw = page.contiguous().view(torch.int16 if self.np_dtype == np.uint16 else torch.float32).reshape(-1).numpy()
+        raw = page.contiguous().view(self.t_dtype).reshape(-1).numpy()
         self.mm[idx] = raw.view(self.np_dtype)
         self.index[key] = idx
 
@@ -60,7 +62,7 @@ class _DiskTier:
         if idx is None:
             return False
         self.index.move_to_end(key)
-        src = torch.from_numpy(np.array(self.mm[idx])).view(torch.int16 if self.np_dtype == np.uint16 else torch.float32)
+        src = torch.from_numpy(np.array(self.mm[idx])).view(self.t_dtype)
         out.view(src.dtype).reshape(-1).copy_(src)
         return True
 

@@ -359,12 +359,18 @@ class TransformerLM:
                                                   device=self.device)
 
     # ------------------------------------------------------------------ memory
+    def _kv_manager_class(self):
+        from ..common.mem_manager import select_mem_manager_class
+
+        return select_mem_manager_class(self.extra.get("kv_type"))
+
     def kv_bytes_per_token(self) -> int:
-        return MemoryManager.bytes_per_token(self.dtype, self.hkv, self.head_dim, self.num_layers + self.extra_kv_layers)
+        return self._kv_manager_class().bytes_per_token(self.dtype, self.hkv, self.head_dim,
+                                                        self.num_layers + self.extra_kv_layers)
 
     def _make_mem_manager(self, size):
-        return MemoryManager(size, self.dtype, self.hkv, self.head_dim, self.num_layers + self.extra_kv_layers,
-                             self.device)
+        return self._kv_manager_class()(size, self.dtype, self.hkv, self.head_dim,
+                                        self.num_layers + self.extra_kv_layers, self.device)
 
     def _kv_layer(self, i: int):
         return self.mem_manager.layer(self.kv_layer_offset + i)

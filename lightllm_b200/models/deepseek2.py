@@ -205,6 +205,8 @@ class DeepseekV2LM(TransformerLM):
                                                 self.num_layers + self.extra_kv_layers)
 
     def _make_mem_manager(self, size):
+        if self.extra.get("kv_type") not in (None, "none", "None"):
+            raise ValueError("--llm_kv_type: the MLA latent cache has no quantised form here")
         return MLAMemoryManager(size, self.dtype, self.kv_lora, self.rope_d, self.num_layers + self.extra_kv_layers,
                                 self.device)
 

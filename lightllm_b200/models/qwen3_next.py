@@ -131,16 +131,12 @@ class Qwen3NextLM(Qwen3MoeLM):
 
     # ------------------------------------------------------------------ memory
     def kv_bytes_per_token(self):
-        from ..common.mem_manager import MemoryManager
-
-        return MemoryManager.bytes_per_token(self.dtype, self.hkv, self.head_dim,
-                                             len(self.full_layers) + self.extra_kv_layers)
+        return self._kv_manager_class().bytes_per_token(self.dtype, self.hkv, self.head_dim,
+                                                        len(self.full_layers) + self.extra_kv_layers)
 
     def _make_mem_manager(self, size):
-        from ..common.mem_manager import MemoryManager
-
-        return MemoryManager(size, self.dtype, self.hkv, self.head_dim, len(self.full_layers) + self.extra_kv_layers,
-                             self.device)
+        return self._kv_manager_class()(size, self.dtype, self.hkv, self.head_dim,
+                                        len(self.full_layers) + self.extra_kv_layers, self.device)
 
     def _kv_layer(self, i: int):
         return self.mem_manager.layer(self.kv_layer_offset + self._kv_slot[i])

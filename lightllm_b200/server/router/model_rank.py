@@ -30,6 +30,12 @@ class ExitCmd:
     pass
 
 
+def _kv_type(args):
+    """`--llm_kv_type`: None / "None" keep the model dtype; "int8kv" selects the quantised pool."""
+    k = getattr(args, "llm_kv_type", None)
+    return None if k in (None, "None", "none", "") else k
+
+
 def _mtp_modules(args) -> int:
     """Draft modules to build: one per step for the vanilla modes, one reused module for the eagle modes."""
     if not getattr(args, "mtp_mode", None):
@@ -62,7 +68,7 @@ def _build_model_and_backend(args: StartArgs, ps):
                       graph_max_len_in_batch=args.graph_max_len_in_batch or None, tp_fused=fused,
                       enable_ep_moe=args.enable_ep_moe, quant_type=args.quant_type,
                       quant_cfg=getattr(args, "quant_cfg", None), expert_dtype=getattr(args, "expert_dtype", None),
-                      extra_kv_layers=_mtp_modules(args),
+                      extra_kv_layers=_mtp_modules(args), kv_type=_kv_type(args),
                       tpsp_mix_mode=bool(getattr(args, "enable_tpsp_mix_mode", False)))
     eos = args.eos_ids or args.eos_id or cfg.get("eos_token_id") or []
     eos = tuple(eos) if isinstance(eos, (list, tuple)) else (eos,)

@@ -1,0 +1,140 @@
+"""int8 KV cache on CPU: row layout and quantisation error, attention over the quantised pool against the same
+attention over the dequantised rows, and a model served with `kv_type="int8kv"` (prefill, chunked prefill with a
+cached prefix, decode) staying close to the bf16-pool model."""
+import numpy as np
+import pytest
+import torch
+
+from lightllm_b200 import ops
+from lightllm_b200.common.mem_manager import Int8KVMemoryManager, MemoryManager, select_mem_manager_class
+from lightllm_b200.ops import kv_quant
+from lightllm_b200.ops import reference as ref
+
+
+def test_row_layout_and_quantisation_error():
+    torch.manual_seed(0)
+    mm = Int8KVMemoryManager(64, torch.float32, 2, 32, 3, torch.device("cpu"))
+    assert mm.kv_buffer.shape == (3, 65, 4, 48) and mm.kv_buffer.dtype == torch.int8
+    assert Int8KVMemoryManager.bytes_per_token(torch.bfloat16, 2, 32, 3) == 3 * 4 * 48
+    layer = mm.layer(1)
+    src = torch.randn(5, 4, 32) * torch.tensor([0.1, 1.0, 10.0, 0.0]).view(1, 4, 1)
+    slots = torch.tensor([7, 3, 60, 0, 9], dtype=torch.int32)
+    kv_quant.quant_store_(layer, src, slots)
+    back = layer.dequant_rows(slots, torch.float32)
+    amax = src.abs().amax(-1, keepdim=True)
+    assert ((back - src).abs() <= amax / 254 + 1e-7).all()            # half a quantisation step
+    assert (back[:, 3] == 0).all() and (layer.scales(layer.data[slots.long()])[:, 3] == 1).all()
+    assert (mm.layer(0).data == 0).all() and (mm.layer(2).data == 0).all()
+    assert select_mem_manager_class(None) is MemoryManager and select_mem_manager_class("int8kv") is Int8KVMemoryManager
+    with pytest.raises(ValueError):
+        select_mem_manager_class("int4kv")
+
+
+def test_pages_move_as_opaque_rows():
+    mm = Int8KVMemoryManager(32, torch.float32, 1, 16, 2, torch.device("cpu"))
+    for l in range(2):
+        kv_quant.quant_store_(mm.layer(l), torch.randn(4, 2, 16), torch.tensor([1, 2, 3, 4], dtype=torch.int32))
+    pages = mm.gather_pages(torch.tensor([2, 4], dtype=torch.int32))
+    assert pages.dtype == torch.int8 and pages.shape == (2, 2, 2, 32)
+    mm.scatter_pages(torch.tensor([10, 11], dtype=torch.int32), pages)
+    a = mm.layer(1).dequant_rows(torch.tensor([2, 4]), torch.float32)
+    b = mm.layer(1).dequant_rows(torch.tensor([10, 11]), torch.float32)
+    assert torch.equal(a, b)
+
+
+def _pool(slots_n, Hkv, D, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    mm = Int8KVMemoryManager(slots_n, torch.float32, Hkv, D, 1, torch.device("cpu"))
+    layer = mm.layer(0)
+    kv_quant.quant_store_(layer, torch.randn(slots_n, 2 * Hkv, D, generator=g),
+                          torch.arange(slots_n, dtype=torch.int32))
+    return layer
+
+
+def test_attention_ops_accept_the_quantised_layer():
+    Hq, Hkv, D = 4, 2, 32
+    layer = _pool(200, Hkv, D)
+    dense = layer.dequant_all(torch.float32)
+    g = torch.Generator().manual_seed(1)
+    perm = torch.randperm(199, generator=g).to(torch.int32)
+    r2t = torch.zeros((3, 96), dtype=torch.int32)
+    lens = [37, 80, 5]
+    off = 0
+    for b, n in enumerate(lens):
+        r2t[b, :n] = perm[off:off + n]
+        off += n
+    b_req = torch.tensor([2, 0, 1], dtype=torch.int32)
+    b_len = torch.tensor([lens[2], lens[0], lens[1]], dtype=torch.int32)
+    q = torch.randn(3, Hq, D, generator=g)
+    got = ops.gqa_decode(q, layer, r2t, b_req, b_len, Hq, Hkv, D, 96)
+    want = ref.gqa_decode(q, dense, r2t, b_req, b_len, Hq, Hkv, D, None)
+    assert torch.allclose(got, want, atol=1e-5)
+    # prefill: request 0 has 30 cached tokens and 7 new ones, request 1 starts from nothing with 80
+    b_req = torch.tensor([0, 1], dtype=torch.int32)
+    cu_q = torch.tensor([0, 7, 87], dtype=torch.int32)
+    ready = torch.tensor([30, 0], dtype=torch.int32)
+    q = torch.randn(87, Hq, D, generator=g)
+    got = ops.gqa_prefill(q, layer, r2t, b_req, cu_q, ready, Hq, Hkv, D, 80)
+    want = ref.gqa_prefill(q, dense, r2t, b_req, cu_q, ready, Hq, Hkv, D, None)
+    assert torch.allclose(got, want, atol=1e-5)
+    pos = torch.cat([torch.arange(30, 37), torch.arange(80)]).to(torch.int32)
+    batch_of = torch.cat([torch.zeros(7), torch.ones(80)]).to(torch.int32)
+    got = ops.attention_generic(q, layer, r2t, b_req, pos, batch_of, Hq, Hkv, D, D ** -0.5, window=16)
+    want = ref.attention_generic(q, dense, r2t, b_req, pos, batch_of, Hq, Hkv, D, D ** -0.5, 16, 0.0, None, None)
+    assert torch.allclose(got, want, atol=1e-5)
+
+
+CFG = dict(model_type="llama", hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+           num_key_value_heads=2, vocab_size=300, rms_norm_eps=1e-5, eos_token_id=2)
+KW = dict(max_total_token_num=2048, running_max_req_size=8, max_req_total_len=256, batch_max_tokens=64,
+          data_type="float32")
+
+
+def test_model_with_int8_pool_tracks_the_full_precision_model():
+    from lightllm_b200.common.infer_state import ModelInput
+    from lightllm_b200.engine.llm import LLM
+
+    a = LLM(config=CFG, **KW).model
+    b = LLM(config=CFG, kv_type="int8kv", **KW).model
+    assert isinstance(b.mem_manager, Int8KVMemoryManager) and b.mem_manager.kv_buffer.dtype == torch.int8
+    assert b.kv_bytes_per_token() == 2 * 2 * 2 * (16 + 16)
+    ids = torch.randint(3, 300, (50,), generator=torch.Generator().manual_seed(3))
+
+    def run(m):
+        outs = []
+        req = m.req_manager.alloc()
+        for s, e in ((0, 33), (33, 50)):       # second chunk attends to a quantised prefix
+            n = e - s
+            mi = ModelInput(batch_size=1, total_token_num=e, max_kv_len=e, is_prefill=True,
+                            b_req_idx=torch.tensor([req], dtype=torch.int32),
+                            b_seq_len=torch.tensor([e], dtype=torch.int32), mem_indexes=m.mem_manager.alloc(n).clone(),
+                            input_ids=ids[s:e], b_ready_cache_len=torch.tensor([s], dtype=torch.int32), max_q_len=n,
+                            return_all_logits=True)
+            outs.append(m.forward(mi).logits.float())
+        m.req_manager.req_to_next_token_ids[req] = 17
+        mi = ModelInput(batch_size=1, total_token_num=51, max_kv_len=51, is_prefill=False,
+                        b_req_idx=torch.tensor([req], dtype=torch.int32), b_seq_len=torch.tensor([51], dtype=torch.int32),
+                        mem_indexes=m.mem_manager.alloc(1).clone())
+        outs.append(m.forward(mi).logits.float())
+        return torch.cat(outs)
+
+    la, lb = run(a), run(b)
+    scale = la.abs().max().item()
+    assert (la - lb).abs().max().item() < 0.03 * scale          # int8 rows: about 0.4 % per element
+    assert (la.argmax(-1) == lb.argmax(-1)).float().mean() > 0.9
+
+
+def test_generation_through_the_engine_with_int8_pool():
+    from lightllm_b200.engine.llm import LLM
+
+    rng = np.random.default_rng(0)
+    prompts = [rng.integers(3, 300, n).tolist() for n in (9, 40, 70)]
+    sp = {"max_new_tokens": 8, "ignore_eos": True}
+    llm = LLM(config=CFG, kv_type="int8kv", **KW)
+    free0 = llm.model.mem_manager.can_use_mem_size
+    out = llm.generate(prompts, sp)
+    assert all(len(o["token_ids"]) == 8 for o in out)
+    again = llm.generate(prompts, sp)                               # prefix-cache hits read quantised rows
+    assert [o["token_ids"] for o in again] == [o["token_ids"] for o in out]
+    rc = llm.backend.radix_cache
+    assert llm.model.mem_manager.can_use_mem_size + rc.get_tree_total_tokens_num() == free0
