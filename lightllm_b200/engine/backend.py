@@ -51,6 +51,7 @@ class BackendArgs:
     # decode steps are launched before the previous step's tokens have been read back: the host-side bookkeeping
     # of step k (token append, finish checks, publishing) runs while the GPU executes step k + 1
     enable_decode_overlap: bool = True
+    linear_att_hash_page_size: int = 512   # hybrid models: token granularity of the recurrent-state snapshots
 
 
 class PinnedRing:
@@ -109,13 +110,20 @@ class ModelBackend:
         self.model = model
         self.args = args or BackendArgs()
         self.device = model.device
-        if not getattr(model, "supports_prefix_cache", True):
-            # hybrid models keep per-request recurrent state that a shared prefix cannot restore
+        state_slots = int(getattr(model, "state_snapshot_slots", 0) or 0)
+        if not getattr(model, "supports_prefix_cache", True) and state_slots <= 0:
+            # hybrid models keep per-request recurrent state: without state snapshots a shared prefix is useless
             self.args.disable_dynamic_prompt_cache = True
         self.radix_cache = None if self.args.disable_dynamic_prompt_cache else \
             RadixCache("radix", model.max_total_token_num, 0, model.mem_manager)
         self.ctx = InferenceContext(model, self.radix_cache)
-        if self.args.cpu_cache_bytes > 0 and self.radix_cache is not None:
+        self.state_cache = None
+        if self.radix_cache is not None and not getattr(model, "supports_prefix_cache", True):
+            from .state_cache import StateSnapshotCache
+
+            self.state_cache = StateSnapshotCache(model, self.args.linear_att_hash_page_size)
+            self.ctx.state_cache = self.state_cache
+        if self.args.cpu_cache_bytes > 0 and self.radix_cache is not None and self.state_cache is None:
             from .host_kv_cache import HostKVCache
 
             self.ctx.host_cache = HostKVCache(model.mem_manager, self.args.cpu_cache_bytes,
@@ -192,6 +200,12 @@ class ModelBackend:
             if not req.inflight and req.need_prefill():
                 remaining = req.total_len() - req.cur_kv_len
                 chunk = min(remaining, chunk_cap)
+                if self.state_cache is not None:
+                    # end a chunk at the last page boundary of the prompt: the state there is worth keeping
+                    page = self.state_cache.page
+                    last = (req.total_len() - 1) // page * page
+                    if req.cur_kv_len < last < req.cur_kv_len + chunk:
+                        chunk = last - req.cur_kv_len
                 if chunk <= budget and chunk <= can_alloc:
                     prefill.append((req, chunk))
                     budget -= chunk
@@ -286,6 +300,7 @@ class ModelBackend:
         has_out = np.array([r.cur_kv_len + int(c) >= r.total_len() for r, c in items], dtype=bool)
         for r, c in items:
             r.cur_kv_len += int(c)
+        self._snapshot_states(reqs)
         logits = out.logits
         if want_all:
             self._handle_prompt_logprobs(reqs, chunks, ids, logits)
@@ -322,11 +337,23 @@ class ModelBackend:
             off += c
 
     # ---- decode ----
+    def _snapshot_states(self, reqs: List[InferReq]):
+        """Hybrid models: keep the recurrent state of every request that now stands at a page boundary."""
+        sc = self.state_cache
+        if sc is None:
+            return
+        for r in reqs:
+            n = r.cur_kv_len
+            if n > 0 and n % sc.page == 0 and not r.shm_req.sample_params.disable_prompt_cache:
+                sc.save(r.req_idx, r.shm_req.shm_prompt_ids.arr[:n])
+
     def _can_defer(self, reqs: List[InferReq]) -> bool:
         """A decode step may be launched ahead of the previous step's bookkeeping when nothing on the host shapes its
         logits (penalties, token masks, constrained decoding) and this is the plain backend."""
         on_gpu = self.device.type == "cuda" or os.environ.get("LLB_FORCE_DECODE_OVERLAP") == "1"  # CPU: tests only
         if not (self.args.enable_decode_overlap and on_gpu and type(self) is ModelBackend):
+            return False
+        if self.state_cache is not None:   # snapshots are taken between steps
             return False
         if self.decode_mask_func is not None or self.extra_post_req_handle_func is not None:
             return False
@@ -389,6 +416,7 @@ class ModelBackend:
                 r.inflight = 1
             self._pending = (reqs, ids_h, lps_h, event)
         else:
+            self._snapshot_states(reqs)
             self._sample_and_post(reqs, out.logits, np.ones(B, dtype=bool), is_prefill=False)
         self.stats["decode_steps"] += 1
         self.stats["decode_tokens"] += B

@@ -157,6 +157,7 @@ class InferenceContext:
         self.requests: Dict[int, InferReq] = {}
         self.infer_req_ids: List[int] = []
         self.host_cache = None  # HostKVCache (second prefix-cache tier) when --enable_cpu_cache
+        self.state_cache = None  # StateSnapshotCache of hybrid linear-attention models
 
     # ---- capacity ----
     def get_can_alloc_token_num(self) -> int:
@@ -188,6 +189,15 @@ class InferenceContext:
             return
         ids = req.shm_req.shm_prompt_ids.arr[: max(req.total_len() - 1, 0)]
         node, n, slots = self.radix_cache.match_prefix(ids, update_refs=True)
+        if self.state_cache is not None:
+            # hybrid model: the match is only worth what the longest state snapshot inside it covers
+            L, snap = (0, None) if node is None else self.state_cache.lookup(ids, n)
+            if L == 0:
+                if node is not None:
+                    self.radix_cache.dec_node_ref_counter(node)
+                return
+            self.state_cache.restore(snap, req.req_idx, L)
+            n, slots = L, slots[:L]
         if node is None:
             self._match_host_cache(req, ids, 0)
             return
@@ -199,7 +209,8 @@ class InferenceContext:
         self.req_manager.req_to_token_indexs[req.req_idx, :n] = row.to(self.req_manager.device)
         if req.shm_req.prompt_cache_len == 0:
             req.shm_req.prompt_cache_len = n
-        self._match_host_cache(req, ids, n)
+        if self.state_cache is None:
+            self._match_host_cache(req, ids, n)
 
     def _match_host_cache(self, req: InferReq, ids, n_gpu: int):
         """Extend the cached prefix with pages of the host tier: pages from the one containing token n_gpu on."""

@@ -30,7 +30,9 @@ from .weights import kv_head_range, tp_range
 @register_model("qwen3_next")
 class Qwen3NextLM(Qwen3MoeLM):
     model_type = "qwen3_next"
-    supports_prefix_cache = False  # the linear layers' state at a prefix boundary is not kept
+    # a shared prefix is usable only with the linear layers' state at its end: `engine/state_cache.py` keeps
+    # snapshots at page boundaries when the model is built with state_snapshot_slots > 0
+    supports_prefix_cache = False
 
     # ------------------------------------------------------------------ config
     def _read_config(self, c):
@@ -148,9 +150,22 @@ class Qwen3NextLM(Qwen3MoeLM):
         self.conv_state = torch.zeros((n, rows, self.conv_dim, self.conv_k - 1), dtype=self.dtype, device=self.device)
         self.ssm_state = torch.zeros((n, rows, self.nv, self.dk, self.dv), dtype=torch.float32, device=self.device)
         self._verify_snaps = {}
+        self.state_snapshot_slots = int(self.extra.get("state_snapshot_slots") or 0)
+        if self.state_snapshot_slots > 0:
+            k = self.state_snapshot_slots
+            self.conv_snap = torch.zeros((k, n, self.conv_dim, self.conv_k - 1), dtype=self.dtype, device=self.device)
+            self.ssm_snap = torch.zeros((k, n, self.nv, self.dk, self.dv), dtype=torch.float32, device=self.device)
         super()._init_mem(max_total_token_num, mem_fraction)
 
     needs_state_rollback = True   # a verification pass must be followed by `commit_verify`
+
+    def save_state_snapshot(self, slot: int, req_idx: int):
+        self.conv_snap[slot].copy_(self.conv_state[:, req_idx])
+        self.ssm_snap[slot].copy_(self.ssm_state[:, req_idx])
+
+    def load_state_snapshot(self, slot: int, req_idx: int):
+        self.conv_state[:, req_idx] = self.conv_snap[slot]
+        self.ssm_state[:, req_idx] = self.ssm_snap[slot]
 
     def commit_verify(self, n_keep):
         """After a verification pass (`verify_pass=True`) over the batch: request b keeps its first n_keep[b] >= 1

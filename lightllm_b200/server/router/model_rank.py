@@ -30,6 +30,15 @@ class ExitCmd:
     pass
 
 
+def _state_slots(args) -> int:
+    """Recurrent-state snapshot slots of hybrid models (`--linear_att_cache_size`); none when the prefix cache is
+    off.  Models without linear-attention layers ignore the number."""
+    if getattr(args, "disable_dynamic_prompt_cache", False):
+        return 0
+    n = getattr(args, "linear_att_cache_size", None)
+    return int(n) if n else 32
+
+
 def _kv_type(args):
     """`--llm_kv_type`: None / "None" keep the model dtype; "int8kv" selects the quantised pool."""
     k = getattr(args, "llm_kv_type", None)
@@ -69,6 +78,7 @@ def _build_model_and_backend(args: StartArgs, ps):
                       enable_ep_moe=args.enable_ep_moe, quant_type=args.quant_type,
                       quant_cfg=getattr(args, "quant_cfg", None), expert_dtype=getattr(args, "expert_dtype", None),
                       extra_kv_layers=_mtp_modules(args), kv_type=_kv_type(args),
+                      state_snapshot_slots=_state_slots(args),
                       tpsp_mix_mode=bool(getattr(args, "enable_tpsp_mix_mode", False)))
     eos = args.eos_ids or args.eos_id or cfg.get("eos_token_id") or []
     eos = tuple(eos) if isinstance(eos, (list, tuple)) else (eos,)
@@ -82,7 +92,8 @@ def _build_model_and_backend(args: StartArgs, ps):
                         cpu_cache_bytes=int(args.cpu_cache_storage_size * (1 << 30)) if args.enable_cpu_cache else 0,
                         cpu_cache_page_tokens=args.cpu_cache_token_page_size,
                         disk_cache_dir=args.disk_cache_dir if args.enable_disk_cache else None,
-                        disk_cache_bytes=int(args.disk_cache_storage_size * (1 << 30)) if args.enable_disk_cache else 0)
+                        disk_cache_bytes=int(args.disk_cache_storage_size * (1 << 30)) if args.enable_disk_cache else 0,
+                        linear_att_hash_page_size=int(getattr(args, "linear_att_hash_page_size", 512) or 512))
     from ...engine.mode_backends import select_backend_class
 
     backend_cls = select_backend_class(args)
