@@ -72,7 +72,7 @@ class DeepseekV2LM(TransformerLM):
         if n_routed:
             # V3-generation checkpoints route with sigmoid scores and a learned selection bias; configs written by
             # newer tooling omit the two keys that say so
-            v3_like = c.get("model_type") in ("deepseek_v3", "kimi_k2", "glm4_moe_lite")
+            v3_like = c.get("model_type") in ("deepseek_v3", "deepseek_v32", "kimi_k2", "glm4_moe_lite")
             has_bias = c.get("topk_method", "noaux_tc" if v3_like else "greedy") == "noaux_tc"
             self.moe = moe.MoEConfig(n_routed, c["num_experts_per_tok"], c["moe_intermediate_size"],
                                      renorm=c.get("norm_topk_prob", True),
@@ -234,12 +234,16 @@ class DeepseekV2LM(TransformerLM):
         ops.mla_rope_kv_scatter_(q3, kv_a, kv_layer, lw.kv_a_norm, self.cos, self.sin, st.position_ids, st.mem_index,
                                  nope, rope, kvl, self.eps)
         q_lat = mla_ops.gemm_batched(q3[:, :, :nope], lw.w_uk)    # [T, hq, kvl]
-        o_lat = mla_ops.mla_attention(q_lat, q3[:, :, nope:], kv_layer, self.req_manager.req_to_token_indexs,
-                                      st.b_req_idx, st.b_seq_len, st.cu_q, st.b_ready_cache_len, kvl, self.sm_scale,
-                                      st.is_prefill, st.max_q_len, st.max_kv_len,
-                                      batch_of=st.batch_of_token if st.is_prefill else None)
+        o_lat = self._mla_attend(i, lw, h, q_a if self.q_lora else None, q_lat, q3[:, :, nope:], kv_layer, st)
         o = mla_ops.gemm_batched(o_lat, lw.w_uv)                  # [T, hq, v]
         return o.reshape(T, hq * self.v_dim)
+
+    def _mla_attend(self, i, lw, h, q_a, q_lat, q_pe, kv_layer, st):
+        """Absorbed attention over the latent cache: [T, hq, kv_lora].  Sparse variants override this."""
+        return mla_ops.mla_attention(q_lat, q_pe, kv_layer, self.req_manager.req_to_token_indexs,
+                                     st.b_req_idx, st.b_seq_len, st.cu_q, st.b_ready_cache_len, self.kv_lora,
+                                     self.sm_scale, st.is_prefill, st.max_q_len, st.max_kv_len,
+                                     batch_of=st.batch_of_token if st.is_prefill else None)
 
     def _ffn_block(self, i, lw, h, st):
         if lw.is_moe:

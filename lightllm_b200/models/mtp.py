@@ -20,6 +20,7 @@ import torch
 
 from .. import ops
 from .deepseek2 import DeepseekV2LM
+from .deepseek_v32 import DeepseekV32LM
 from .llama import LlamaLM
 from .qwen3_moe import Qwen3MoeLM
 from .qwen3_next import Qwen3_5LM, Qwen3_5MoeLM, Qwen3NextLM
@@ -93,6 +94,11 @@ class DeepseekV3MTP(MTPMixin, DeepseekV2LM):
         return self.moe is not None   # the module's layer follows the target's last (MoE) layer
 
 
+class DeepseekV32MTP(MTPMixin, DeepseekV32LM):
+    def _is_moe_layer(self, i):
+        return self.moe is not None
+
+
 class Qwen3MoeMTP(MTPMixin, Qwen3MoeLM):
     pass
 
@@ -153,7 +159,7 @@ class Qwen3_5MoeMTP(_Qwen3_5MTPMixin, Qwen3_5MoeLM):
 
 
 MTP_CLASSES = {"deepseek_v3": DeepseekV3MTP, "deepseek_v2": DeepseekV3MTP, "glm4_moe_lite": DeepseekV3MTP,
-               "kimi_k2": DeepseekV3MTP, "qwen3_moe": Qwen3MoeMTP, "mistral": LlamaMTP, "llama": LlamaMTP,
+               "kimi_k2": DeepseekV3MTP, "deepseek_v32": DeepseekV32MTP, "qwen3_moe": Qwen3MoeMTP, "mistral": LlamaMTP, "llama": LlamaMTP,
                "qwen3_5": Qwen3_5MTP, "qwen3_5_text": Qwen3_5MTP, "qwen3_5_moe": Qwen3_5MoeMTP,
                "qwen3_5_moe_text": Qwen3_5MoeMTP}
 
