@@ -219,3 +219,40 @@ class FusedTP:
 
     def status(self) -> int:
         return int(self.local[2].item())
+
+    def self_test(self, T: int = 24) -> bool:
+        """Start-up probe: two small reductions (both buffer parities) through the fused kernel against NCCL + torch
+        on the same numbers; every rank learns whether ALL ranks agreed, so they take the same decision about
+        falling back.  A peer that does not show up ends the kernel's bounded wait with an error status, which
+        counts as a failure.  Reference: lightllm/utils/dist_check_utils.py (2-GPU capability check before the
+        custom all-reduce paths are enabled)."""
+        import torch.distributed as dist
+
+        dev, H = self.ps.device, self.hidden
+        T = min(T, self.max_tokens)
+        ok = True
+        try:
+            for k in range(2):
+                g = torch.Generator(device=dev).manual_seed(4321 + 17 * k + self.rank)
+                mine = torch.randn(T, H, generator=g, device=dev).to(torch.bfloat16)
+                gs = torch.Generator(device=dev).manual_seed(99 + k)           # the same on every rank
+                residual = torch.randn(T, H, generator=gs, device=dev).to(torch.bfloat16)
+                norm_w = torch.ones(H, dtype=torch.bfloat16, device=dev)
+                total = mine.float()
+                dist.all_reduce(total, group=self.ps.tp_group)
+                want_res = residual.float() + total
+                want = want_res * torch.rsqrt(want_res.pow(2).mean(-1, keepdim=True) + 1e-6)
+                partial = self.partial_out(T, H)
+                partial.copy_(mine)
+                res = residual.clone()
+                got = self.reduce_residual_norm(partial, res, norm_w, 1e-6)
+                torch.cuda.synchronize(dev)
+                scale = max(want_res.abs().max().item(), 1.0)
+                ok = ok and self.status() == 0 and \
+                    (res.float() - want_res).abs().max().item() < 0.05 * scale and \
+                    (got.float() - want).abs().max().item() < 0.05 * max(want.abs().max().item(), 1.0)
+        except Exception:
+            ok = False
+        flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.ps.tp_group)
+        return bool(flag.item())

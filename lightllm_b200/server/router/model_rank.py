@@ -65,6 +65,11 @@ def _build_model_and_backend(args: StartArgs, ps):
 
             hidden = cfg.get("hidden_size") or (cfg.get("text_config") or {}).get("hidden_size")
             fused = FusedTP(ps, max_tokens=args.batch_max_tokens, hidden=int(hidden))
+            if not fused.self_test():   # all ranks see the same answer
+                print(f"[rank {ps.global_rank}] fused tensor-parallel reduction failed its start-up probe: "
+                      "falling back to NCCL", flush=True)
+                fused.close()
+                fused = None
         except Exception:
             fused = None
     model = get_model(cfg, model_dir=args.model_dir, pstate=ps, data_type=args.data_type,

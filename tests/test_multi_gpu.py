@@ -45,8 +45,9 @@ def _worker(rank, world, port, out_dir, fused, tpsp=False):
     prompts = [torch.randint(3, 32000, (n,), generator=g).tolist() for n in (17, 64, 129, 300)]
     outs = llm.generate(prompts, {"max_new_tokens": 24, "ignore_eos": True})
     status = m.tp.fused.status() if (fused and m.tp.fused is not None) else 0
+    probe = bool(m.tp.fused.self_test()) if (fused and m.tp.fused is not None) else True   # the start-up probe
     if rank == 0:
-        torch.save({"logits": logits, "tokens": [o["token_ids"] for o in outs], "status": status},
+        torch.save({"logits": logits, "tokens": [o["token_ids"] for o in outs], "status": status, "probe": probe},
                    os.path.join(out_dir, f"tp{world}_f{int(fused)}{'_sp' if tpsp else ''}.pt"))
     llm.close()
     pdist.destroy(hard_exit_on_hang=True)
@@ -61,6 +62,7 @@ def test_tp2_fused_matches_nccl_and_tp1(tmp_path):
     nccl = torch.load(tmp_path / "tp2_f0.pt")
     fus = torch.load(tmp_path / "tp2_f1.pt")
     assert fus["status"] == 0, "a bounded wait in the fused all-reduce ran out"
+    assert fus["probe"], "the start-up probe of the fused reduction disagreed with NCCL"
     scale = one["logits"].abs().max().item()
     assert (nccl["logits"] - one["logits"]).abs().max().item() < 0.05 * scale + 0.05
     assert (fus["logits"] - one["logits"]).abs().max().item() < 0.05 * scale + 0.05
