@@ -137,6 +137,83 @@ class QwenV1LM(TransformerLM):
         return RemapSource(src, t)
 
 
+@register_model("qwen", condition=lambda cfg: "visual" in cfg, is_multimodal=True)
+class QwenVLV1LM(QwenV1LM):
+    """Qwen-VL (first generation): the Qwen decoder; the rows of picture placeholders are replaced by the resampler's
+    256 embeddings per picture (`models/vit/qwen_vl_visual.py`).  Reference: lightllm/models/qwen_vl/model.py."""
+
+
+class QwenVLV1Tokenizer:
+    """`<img>anything</img>` in the prompt becomes `Picture k:<img>` + the k-th picture's id run + `</img>` + newline
+    (reference: QWenVLTokenizer).  The ids of the two tags come from the tokenizer (`img_start_id`, `img_end_id`)."""
+
+    def __init__(self, tokenizer, model_cfg: dict):
+        self.tokenizer = tokenizer
+        self.image_start_tag = getattr(tokenizer, "image_start_tag", "<img>")
+        self.image_end_tag = getattr(tokenizer, "image_end_tag", "</img>")
+        self.image_start_id = getattr(tokenizer, "img_start_id", model_cfg.get("img_start_id", 151857))
+        self.image_end_id = getattr(tokenizer, "img_end_id", model_cfg.get("img_end_id", 151858))
+        self.image_length = int((model_cfg.get("visual") or {}).get("n_queries", 256))
+
+    def __getattr__(self, name):
+        return getattr(self.tokenizer, name)
+
+    def init_imageitem_extral_params(self, img, multi_params=None, sampling_params=None):
+        pass
+
+    def get_image_token_length(self, img) -> int:
+        return self.image_length
+
+    def _format_prompt(self, prompt: str) -> str:
+        parts = prompt.split(self.image_start_tag)
+        out = parts[0]
+        for k, part in enumerate(parts[1:]):
+            out += f"Picture {k + 1}:" + self.image_start_tag + part
+        parts = out.split(self.image_end_tag)
+        return parts[0] + "".join(self.image_end_tag + "\n" + part for part in parts[1:])
+
+    def _encode_text(self, text: str):
+        inner = getattr(self.tokenizer, "tokenizer", None)
+        if inner is not None and hasattr(inner, "encode"):
+            try:
+                return list(inner.encode(text, allowed_special="all", disallowed_special=()))
+            except TypeError:
+                pass
+        return list(self.tokenizer.encode(text))
+
+    def encode(self, prompt, multimodal_params=None, **kw):
+        import unicodedata
+
+        if isinstance(prompt, (list, tuple)):
+            ids = list(prompt)
+        else:
+            ids = self._encode_text(self._format_prompt(unicodedata.normalize("NFC", prompt)))
+        images = list(multimodal_params.images) if multimodal_params is not None else []
+        out, k, pos = [], 0, 0
+        while True:
+            try:
+                s = ids.index(self.image_start_id, pos)
+            except ValueError:
+                break
+            try:
+                e = ids.index(self.image_end_id, s)
+            except ValueError:
+                raise ValueError("unclosed image tag") from None
+            if k >= len(images):
+                raise ValueError(f"the prompt has more image tags than the {len(images)} images sent")
+            im = images[k]
+            assert im.token_num == self.image_length, f"picture reserves {im.token_num} ids, the tower gives {self.image_length}"
+            out.extend(ids[pos:s])
+            out.append(self.image_start_id)
+            out.extend(range(im.token_id, im.token_id + im.token_num))
+            out.append(self.image_end_id)
+            pos, k = e + 1, k + 1
+        out.extend(ids[pos:])
+        if k != len(images):
+            raise ValueError(f"the prompt has {k} image tags for {len(images)} images")
+        return out
+
+
 @register_model("gemma")
 class GemmaLM(TransformerLM):
     """Gemma (2B / 7B): RMSNorm with (1 + w), GeGLU, embeddings x sqrt(hidden), head size 256, tied lm_head."""

@@ -65,6 +65,10 @@ def get_tokenizer(model_dir: str, tokenizer_mode: str = "fast", trust_remote_cod
         from ..models.qwen2_vl import Qwen3VLTokenizer
 
         return Qwen3VLTokenizer(tok, cfg)
+    if mt == "qwen" and "visual" in cfg:
+        from ..models.llama import QwenVLV1Tokenizer
+
+        return QwenVLV1Tokenizer(tok, cfg)
     if mt == "qwen3_omni_moe":
         from ..models.qwen3_omni import Qwen3OmniTokenizer
 

@@ -52,6 +52,16 @@ def build_vision_tower(args, device, dtype=torch.bfloat16):
         else:
             src = RandomSource(Qwen3VLVisionTower.weight_shapes(vcfg), dtype=dtype)
         return Qwen3VLVisionTower(vcfg, src, device, dtype)
+    if mt == "qwen" and "visual" in cfg:
+        from ...models.base import TransformerLM
+        from ...models.vit.qwen_vl_visual import QwenVLVisionTower
+
+        vcfg = dict(cfg["visual"])
+        if args.model_dir and TransformerLM._has_weights(args.model_dir):
+            src = SafetensorsSource(args.model_dir)
+        else:
+            src = RandomSource(QwenVLVisionTower.weight_shapes(vcfg), dtype=dtype)
+        return QwenVLVisionTower(vcfg, src, device, dtype)
     if mt == "qwen3_omni_moe":
         from ...models.base import TransformerLM
         from ...models.qwen3_omni import Qwen3OmniVisionTower

@@ -142,3 +142,63 @@ def test_config_server_ranges():
     m = c.get("/allocate_global_unique_multimodal_id_range").json()
     assert m["start_id"] >= 100_000_000 and m["end_id"] - m["start_id"] == MM_ID_RANGE
     assert c.get("/registered_objects").status_code == 200
+
+
+def test_qwen_vl_v1_tower_and_tokenizer():
+    """First-generation Qwen-VL: ViT with per-head packed qkv, resampler against torch's MultiheadAttention, prompt
+    formatting with picture numbers."""
+    import torch
+    import torch.nn.functional as F
+    from types import SimpleNamespace
+
+    from lightllm_b200.models.llama import QwenVLV1Tokenizer
+    from lightllm_b200.models.registry import get_model_class, is_multimodal
+    from lightllm_b200.models.vit.qwen_vl_visual import QwenVLVisionTower, resize_positions, sincos_2d
+    from lightllm_b200.models.weights import RandomSource
+
+    vcfg = dict(image_size=56, patch_size=14, width=32, layers=2, heads=4, mlp_ratio=2.0, output_dim=128, n_queries=16)
+    shapes = QwenVLVisionTower.weight_shapes(vcfg)
+    src = RandomSource(shapes, dtype=torch.float32, seed=0)
+    tower = QwenVLVisionTower(vcfg, src, torch.device("cpu"), torch.float32)
+    pixels = torch.randn(2, 3, 56, 56)
+    out = tower.forward(pixels)
+    assert out.shape == (2, 16, 128) and torch.isfinite(out).all()
+    # resampler == nn.MultiheadAttention with the same tensors
+    E, W = 128, 32
+    feats = torch.randn(2, 16, W)
+    mha = torch.nn.MultiheadAttention(E, tower.pool_heads)
+    with torch.no_grad():
+        mha.in_proj_weight.copy_(tower.pool["attn.in_proj_weight"])
+        mha.in_proj_bias.copy_(tower.pool["attn.in_proj_bias"])
+        mha.out_proj.weight.copy_(tower.pool["attn.out_proj.weight"])
+        mha.out_proj.bias.copy_(tower.pool["attn.out_proj.bias"])
+        x = F.linear(feats, tower.pool_kv_w)
+        kv = F.layer_norm(x, (E,), tower.pool["ln_kv.weight"], tower.pool["ln_kv.bias"], 1e-6).permute(1, 0, 2)
+        q = F.layer_norm(tower.pool["query"], (E,), tower.pool["ln_q.weight"], tower.pool["ln_q.bias"], 1e-6)
+        pe = tower.pool["pos_embed"]
+        want = mha(q.unsqueeze(1).repeat(1, 2, 1) + pe.unsqueeze(1), kv + resize_positions(pe, 16).unsqueeze(1), kv)[0]
+        got = tower._resample(feats)
+    assert (got - want.permute(1, 0, 2)).abs().max().item() < 1e-5
+    pe = sincos_2d(8, 2)      # 2 x 2 grid, 8 channels: [sin, cos] of the column index, then of the row index
+    assert pe.shape == (4, 8) and torch.allclose(pe[0], torch.tensor([0., 0., 1., 1., 0., 0., 1., 1.]))
+    assert torch.allclose(pe[1, :4], torch.tensor([0.8415, 0.0100, 0.5403, 0.99995]), atol=1e-4)
+    assert torch.allclose(pe[2, 4:], pe[1, :4]) and torch.allclose(pe[2, :4], pe[0, :4])
+
+    cfg = {"model_type": "qwen", "visual": vcfg, "hidden_size": 128}
+    assert is_multimodal(cfg) and not is_multimodal({"model_type": "qwen"})
+    assert get_model_class(cfg).__name__ == "QwenVLV1LM" and get_model_class({"model_type": "qwen"}).__name__ == "QwenV1LM"
+
+    class Tok:
+        img_start_id, img_end_id = 900, 901
+
+        def encode(self, text):
+            out = []
+            for w in text.replace("<img>", " <img> ").replace("</img>", " </img> ").replace("\n", " NL ").split():
+                out.append({"<img>": 900, "</img>": 901, "NL": 7}.get(w, 1 if w.startswith("Picture") else 5))
+            return out
+
+    tk = QwenVLV1Tokenizer(Tok(), cfg)
+    assert tk.get_image_token_length(None) == 16
+    mp = SimpleNamespace(images=[SimpleNamespace(token_id=5000, token_num=16), SimpleNamespace(token_id=6000, token_num=16)])
+    ids = tk.encode("look <img>a.jpg</img> and <img>b.jpg</img> ok", mp)
+    assert ids == [5, 1, 5, 900] + list(range(5000, 5016)) + [901, 7, 5, 1, 5, 900] + list(range(6000, 6016)) + [901, 7, 5]
