@@ -10,3 +10,4 @@ from . import internvl  # noqa: F401
 from . import qwen3_next  # noqa: F401
 from . import qwen3_omni  # noqa: F401
 from . import deepseek_v32  # noqa: F401
+from . import gemma4  # noqa: F401

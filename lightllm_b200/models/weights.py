@@ -122,7 +122,8 @@ class RandomSource(WeightSource):
 
     def get(self, name, dim=None, start=0, end=None):
         shape = self.shapes[name]
-        if name.endswith("norm.weight") or name.endswith("layernorm.weight") or name.endswith("_norm.weight"):
+        if name.endswith("norm.weight") or name.endswith("layernorm.weight") or name.endswith("_norm.weight") or \
+                name.endswith("layer_scalar") or name.endswith("router.scale") or name.endswith("per_expert_scale"):
             t = torch.ones(shape, dtype=self.dtype, device=self.device)
         elif name.endswith("_scale_inv"):
             t = (torch.rand(shape, generator=self._gen(name), device=self.device, dtype=torch.float32) * 1.5 + 0.5) * (self.std / 96.0)

@@ -38,6 +38,12 @@ FAMILIES = {
                        linear_num_key_heads=2, linear_key_head_dim=32, linear_value_head_dim=32,
                        linear_conv_kernel_dim=4, full_attention_interval=4, partial_rotary_factor=0.25,
                        norm_topk_prob=True),
+    "gemma4_text": dict(model_type="gemma4_text", hidden_size=256, intermediate_size=512, num_hidden_layers=4,
+                        num_attention_heads=2, num_key_value_heads=1, head_dim=128, global_head_dim=256,
+                        sliding_window=32, layer_types=["sliding_attention", "full_attention", "sliding_attention",
+                                                        "full_attention"],
+                        num_kv_shared_layers=2, hidden_size_per_layer_input=64, vocab_size_per_layer_input=1024,
+                        final_logit_softcapping=30.0, tie_word_embeddings=True),
     "internlm": dict(model_type="internlm", hidden_size=256, intermediate_size=512, num_hidden_layers=2,
                      num_attention_heads=4, bias=True),
 }
@@ -103,6 +109,12 @@ def test_family_gpu_matches_cpu(dev, family):
     # random norm weights of 1 (+1 offset) and the sandwich norms make the Gemma-3 toy network amplify bf16
     # rounding: its bf16 CPU restatement is 0.19 x scale away from fp32 as well
     rel = 0.3 if family == "gemma3_text" else 0.06
+    if family == "gemma4_text":
+        # the same amplification (the bf16 CPU restatement of this toy is 0.38 x scale away from fp32 at its worst
+        # element, 0.014 x scale on average): bound the worst element loosely and the average tightly
+        rel = 0.45
+        mean = (out_c[0] - out_g[0]).abs().mean().item()
+        assert mean < 0.03 * scale, f"prefill logits: mean err {mean}, scale {scale}"
     if family in ("gpt_oss", "qwen3_moe", "qwen3_next"):
         # a near-tie in the router flips a token's expert under bf16 rounding: isolated large deviations on an
         # otherwise tight match (the expert FFN kernels themselves agree to 5e-4 on these shapes)

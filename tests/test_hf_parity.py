@@ -966,3 +966,88 @@ def test_qwen3_omni_thinker_audio_and_vision_towers(tmp_path):
                     multimodal_params=[{"images": [image], "audios": [clip]}])
     got = m.forward(mi).logits.float()
     assert (got - ref).abs().max().item() < 2e-3 * max(ref.abs().max().item(), 1.0)
+
+
+def _gemma4_check(tmp_path, cfg_kw, force_torch_attention=False, n_tokens=60):
+    from transformers import Gemma4ForCausalLM, Gemma4TextConfig
+
+    from lightllm_b200.common.infer_state import ModelInput
+    from lightllm_b200.models.base import load_config
+    from lightllm_b200.models.registry import get_model
+    from lightllm_b200.parallel import dist as pdist
+
+    torch.manual_seed(0)
+    cfg = Gemma4TextConfig(**cfg_kw)
+    hf = Gemma4ForCausalLM(cfg).eval().float()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if "norm" in n or "router.scale" in n or "per_expert_scale" in n:
+                p.add_(torch.randn_like(p) * 0.1)
+        for i, layer in enumerate(hf.model.layers):
+            layer.layer_scalar.fill_(0.9 + 0.05 * i)
+    d = str(tmp_path / "ckpt")
+    hf.save_pretrained(d, safe_serialization=True)
+    from safetensors.torch import save_file
+
+    sd = {k: v.contiguous() for k, v in hf.state_dict().items()}
+    if cfg.tie_word_embeddings:
+        sd.pop("lm_head.weight", None)
+    save_file(sd, d + "/model.safetensors")
+    ids = torch.randint(3, cfg.vocab_size - 1, (n_tokens,), generator=torch.Generator().manual_seed(1))
+    with torch.no_grad():
+        ref = hf(input_ids=ids.unsqueeze(0)).logits[0].float()
+    m = get_model(load_config(d), model_dir=d, pstate=pdist.ParallelState(device=torch.device("cpu")),
+                  data_type="float32", max_total_token_num=512, max_req_num=3, max_seq_length=128, disable_cudagraph=True)
+    assert type(m).__name__ == "Gemma4TextLM"
+    if force_torch_attention:
+        m.big_head = 0
+    scale = max(ref.abs().max().item(), 1.0)
+
+    def prefill(req, tokens, ready):
+        n = len(tokens)
+        mi = ModelInput(batch_size=1, total_token_num=ready + n, max_kv_len=ready + n, is_prefill=True,
+                        b_req_idx=torch.tensor([req], dtype=torch.int32),
+                        b_seq_len=torch.tensor([ready + n], dtype=torch.int32),
+                        mem_indexes=m.mem_manager.alloc(n).clone(), input_ids=tokens,
+                        b_ready_cache_len=torch.tensor([ready], dtype=torch.int32), max_q_len=n, return_all_logits=True)
+        return m.forward(mi).logits.float()
+
+    r0 = m.req_manager.alloc()
+    cut = n_tokens - 6
+    got = torch.cat([prefill(r0, ids[:25], 0), prefill(r0, ids[25:cut], 25)])        # second chunk on a cached prefix
+    assert (got - ref[:cut]).abs().max().item() < 2e-3 * scale
+    for t in range(cut, n_tokens):
+        m.req_manager.req_to_next_token_ids[r0] = int(ids[t])
+        mi = ModelInput(batch_size=1, total_token_num=t + 1, max_kv_len=t + 1, is_prefill=False,
+                        b_req_idx=torch.tensor([r0], dtype=torch.int32),
+                        b_seq_len=torch.tensor([t + 1], dtype=torch.int32), mem_indexes=m.mem_manager.alloc(1).clone())
+        step = m.forward(mi).logits.float()
+        assert (step[0] - ref[t]).abs().max().item() < 2e-3 * scale, f"decode step at position {t}"
+    return m
+
+
+def test_gemma4_per_layer_inputs_shared_kv_and_k_eq_v(tmp_path):
+    """Gemma-4 small-model features: two head sizes, proportional rotary embedding on global layers, V = K on global
+    layers with fewer KV heads, the last layers reading earlier layers' caches with a double-wide MLP, per-layer
+    inputs, layer scalars, logit soft-cap; sliding window shorter than the prompt."""
+    kw = dict(vocab_size=300, hidden_size=64, intermediate_size=128, num_hidden_layers=6, num_attention_heads=4,
+              num_key_value_heads=2, head_dim=16, global_head_dim=32, num_global_key_value_heads=1,
+              attention_k_eq_v=True, num_kv_shared_layers=2, use_double_wide_mlp=True, sliding_window=16,
+              layer_types=["sliding_attention", "sliding_attention", "full_attention", "sliding_attention",
+                           "sliding_attention", "full_attention"],
+              hidden_size_per_layer_input=8, vocab_size_per_layer_input=300, final_logit_softcapping=30.0,
+              max_position_embeddings=256, tie_word_embeddings=True, pad_token_id=0)
+    m = _gemma4_check(tmp_path, kw)
+    assert m.kv_src == [0, 1, 2, 3, 3, 2] and (m.n_pool_s, m.n_pool_g) == (3, 1)
+    assert m.mem_manager.kv_sliding.shape[2:] == (4, 16) and m.mem_manager.kv_global.shape[2:] == (2, 32)
+
+
+def test_gemma4_moe_block_and_torch_attention(tmp_path):
+    """The mixture-of-experts block next to the dense MLP, and the torch attention used for head sizes above 256
+    (forced here on small heads)."""
+    kw = dict(vocab_size=300, hidden_size=64, intermediate_size=128, num_hidden_layers=3, num_attention_heads=4,
+              num_key_value_heads=2, head_dim=16, global_head_dim=32, sliding_window=12,
+              layer_types=["sliding_attention", "sliding_attention", "full_attention"], hidden_size_per_layer_input=0,
+              enable_moe_block=True, num_experts=4, top_k_experts=2, moe_intermediate_size=32,
+              max_position_embeddings=256, tie_word_embeddings=False, pad_token_id=0)
+    _gemma4_check(tmp_path, kw, force_torch_attention=True, n_tokens=40)
