@@ -182,7 +182,68 @@ class Int8KVMemoryManager(MemoryManager):
         return Int8KVLayer(self.kv_buffer[i], self.head_dim)
 
 
-KV_MANAGERS = {"none": MemoryManager, "int8kv": Int8KVMemoryManager}
+class Fp8KVMemoryManager(MemoryManager):
+    """GQA/MHA pool with e4m3 rows and static scales per (layer, head) (`fp8kv_sph`) or per layer for K and for V
+    (`fp8kv_spt`), read from a calibration file: JSON with qmin / qmax (the e4m3 limits), num_layers, num_head (KV
+    heads of the whole model), quant_type ("per_head" | "per_tensor"), scales (flat list) and scales_shape
+    ([layers, 2 * num_head] or [layers, 2]; K first, then V).  Without a file every scale is 1.
+    Reference: lightllm/common/kv_cache_mem_manager/fp8_static_per_head_quant_mem_manager.py,
+    fp8_static_per_tensor_quant_mem_manager.py."""
+
+    per_tensor = False
+
+    def __init__(self, size: int, dtype: torch.dtype, head_num: int, head_dim: int, layer_num: int,
+                 device: torch.device, always_copy: bool = False, calibration: Optional[str] = None,
+                 head_range: Optional[tuple] = None):
+        self.compute_dtype = dtype
+        super().__init__(size, torch.uint8, head_num, head_dim, layer_num, device)
+        self.scales = torch.ones((layer_num, 2 * head_num), dtype=torch.float32, device=device)
+        if calibration:
+            self.load_calibration(calibration, head_range)
+
+    def load_calibration(self, path: str, head_range: Optional[tuple] = None):
+        import json
+
+        with open(path) as f:
+            cfg = json.load(f)
+        lim = float(torch.finfo(torch.float8_e4m3fn).max)
+        if abs(float(cfg.get("qmax", lim)) - lim) > 1e-3 or abs(float(cfg.get("qmin", -lim)) + lim) > 1e-3:
+            raise ValueError("the calibration file was made for another number format than e4m3")
+        want = "per_tensor" if self.per_tensor else "per_head"
+        if cfg.get("quant_type", want) != want:
+            raise ValueError(f"calibration quant_type {cfg.get('quant_type')!r}, the pool wants {want!r}")
+        sc = torch.tensor(cfg["scales"], dtype=torch.float32).view(*cfg["scales_shape"])
+        if sc.shape[0] < self.layer_num:     # extra cache layers (draft modules) keep scale 1
+            sc = torch.cat([sc, torch.ones(self.layer_num - sc.shape[0], sc.shape[1])])
+        sc = sc[: self.layer_num]
+        if self.per_tensor:
+            k, v = sc[:, :1].expand(-1, self.head_num), sc[:, 1:2].expand(-1, self.head_num)
+        else:
+            all_heads = sc.shape[1] // 2
+            h0, h1 = head_range if head_range is not None else (0, self.head_num)
+            if h1 - h0 != self.head_num:      # fewer KV heads than ranks: this rank holds copies of one head
+                h1 = h0 + 1
+            k, v = sc[:, h0:h1], sc[:, all_heads + h0:all_heads + h1]
+            if k.shape[1] != self.head_num:
+                k, v = k.expand(-1, self.head_num), v.expand(-1, self.head_num)
+        self.scales = torch.cat([k, v], dim=1).contiguous().to(self.device)
+
+    @staticmethod
+    def bytes_per_token(dtype, head_num, head_dim, layer_num) -> int:
+        return layer_num * 2 * head_num * head_dim
+
+    def layer(self, i: int):
+        from ..ops.kv_quant import Fp8KVLayer
+
+        return Fp8KVLayer(self.kv_buffer[i], self.head_dim, self.scales[i])
+
+
+class Fp8PerTensorKVMemoryManager(Fp8KVMemoryManager):
+    per_tensor = True
+
+
+KV_MANAGERS = {"none": MemoryManager, "int8kv": Int8KVMemoryManager, "fp8kv_sph": Fp8KVMemoryManager,
+               "fp8kv_spt": Fp8PerTensorKVMemoryManager}
 
 
 def select_mem_manager_class(kv_type: Optional[str]):

@@ -12,10 +12,16 @@
 // fp16 (the query is converted once per CTA); the K scale of a token multiplies its score column, the V
 // scale multiplies its probability column before the P.V product.
 //
+// The same kernel serves the fp8 pool (`FP8 = true`): rows are D e4m3 values with no scale in the row; the scales are
+// static per (layer, head) numbers from a calibration file, so the K scale is folded into the softmax scale of
+// the CTA's KV head and the V scale multiplies the output once; widening is the hardware e4m3 -> fp16 conversion.
+//
 // Behavioural counterpart in the reference: lightllm/common/kv_cache_mem_manager/ppl_int8kv_mem_manager.py
-// (group-quantised pool with a scale buffer) and common/basemodel/attention/triton/int8kv.py.
+// (group-quantised pool with a scale buffer), fp8_static_per_head_quant_mem_manager.py,
+// common/basemodel/attention/triton/int8kv.py, attention/fa3/fp8.py.
 #include "common.cuh"
 #include <cuda_fp16.h>
+#include <cuda_fp8.h>
 
 using namespace llb;
 
@@ -95,6 +101,21 @@ __device__ __forceinline__ void store_pair(uint8_t* tile, int tok, int ch, const
   }
 }
 
+// sixteen e4m3 -> sixteen fp16
+__device__ __forceinline__ void widen16_fp8(const uint4& in, uint4& lo, uint4& hi) {
+  const uint32_t w[4] = {in.x, in.y, in.z, in.w};
+  uint32_t o[8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    __half2_raw a = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w[i] & 0xffffu), __NV_E4M3);
+    __half2_raw b = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w[i] >> 16), __NV_E4M3);
+    o[2 * i] = (uint32_t)a.x | ((uint32_t)a.y << 16);
+    o[2 * i + 1] = (uint32_t)b.x | ((uint32_t)b.y << 16);
+  }
+  lo = make_uint4(o[0], o[1], o[2], o[3]);
+  hi = make_uint4(o[4], o[5], o[6], o[7]);
+}
+
 __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
   __half2 h = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&h);
@@ -135,18 +156,18 @@ struct Int8DecodeSmem {
   static constexpr int TOTAL = Q_BYTES + 4 * WARP;
 };
 
-template <int D>
+template <int D, bool FP8>
 __global__ void __launch_bounds__(128)
 gqa_decode_int8_kernel(const bf16* __restrict__ q, int64_t q_stride, const int8_t* __restrict__ kv_layer,
                        const int* __restrict__ req_to_token, int64_t r2t_stride, const int* __restrict__ b_req_idx,
                        const int* __restrict__ b_seq_len, bf16* __restrict__ out, int64_t out_stride,
                        float* __restrict__ part_o, float* __restrict__ part_lse, int Hq, int Hkv, int num_splits,
-                       float scale_log2) {
+                       float scale_log2_in, const float* __restrict__ head_scales) {
   pdl_wait();
   using S = Int8DecodeSmem<D>;
   constexpr int CH = D / 8;     // 16-byte chunks of a bf16 row
-  constexpr int CH8 = D / 16;   // 16-byte chunks of an int8 row
-  constexpr int ROW = D + kPad;
+  constexpr int CH8 = D / 16;   // 16-byte chunks of an 8-bit row
+  constexpr int ROW = FP8 ? D : D + kPad;
   extern __shared__ __align__(128) uint8_t smem[];
   uint8_t* q_smem = smem;
   uint8_t* warp_smem = smem + S::Q_BYTES + (threadIdx.x >> 5) * S::WARP;
@@ -164,6 +185,9 @@ gqa_decode_int8_kernel(const bf16* __restrict__ q, int64_t q_stride, const int8_
   const int L = b_seq_len[b];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, tig = lane & 3;
+  // fp8 pool: static scales of this KV head (K folded into the score scale, V applied to the output)
+  const float scale_log2 = FP8 ? scale_log2_in * head_scales[kvh] : scale_log2_in;
+  const float out_scale = FP8 ? head_scales[Hkv + kvh] : 1.f;
 
   const int tiles_total = (L + 15) >> 4;
   const int tiles_per_split = (tiles_total + num_splits - 1) / num_splits;
@@ -228,7 +252,7 @@ gqa_decode_int8_kernel(const bf16* __restrict__ q, int64_t q_stride, const int8_
         cp_async16(sb + tok * D + ch * 16, src, ok);
         cp_async16(sb + S::TILE8 + tok * D + ch * 16, src + (int64_t)Hkv * ROW, ok);
       }
-      {  // scales: lanes 0..15 the K rows, lanes 16..31 the V rows
+      if (!FP8) {  // scales: lanes 0..15 the K rows, lanes 16..31 the V rows
         int tok = lane & 15;
         int sl = __shfl_sync(0xffffffffu, slot, tok);
         bool ok = sl >= 0;
@@ -263,7 +287,10 @@ gqa_decode_int8_kernel(const bf16* __restrict__ q, int64_t q_stride, const int8_
       int c = lane + 32 * j;
       int tok = c / CH8, ch = c % CH8;
       uint4 lo, hi;
-      widen16(*reinterpret_cast<const uint4*>(st8 + tok * D + ch * 16), lo, hi);
+      if (FP8)
+        widen16_fp8(*reinterpret_cast<const uint4*>(st8 + tok * D + ch * 16), lo, hi);
+      else
+        widen16(*reinterpret_cast<const uint4*>(st8 + tok * D + ch * 16), lo, hi);
       store_pair<D>(wide, tok, ch, lo, hi);
     }
     __syncwarp();
@@ -288,7 +315,10 @@ gqa_decode_int8_kernel(const bf16* __restrict__ q, int64_t q_stride, const int8_
       int c = lane + 32 * j;
       int tok = c / CH8, ch = c % CH8;
       uint4 lo, hi;
-      widen16(*reinterpret_cast<const uint4*>(st8 + S::TILE8 + tok * D + ch * 16), lo, hi);
+      if (FP8)
+        widen16_fp8(*reinterpret_cast<const uint4*>(st8 + S::TILE8 + tok * D + ch * 16), lo, hi);
+      else
+        widen16(*reinterpret_cast<const uint4*>(st8 + S::TILE8 + tok * D + ch * 16), lo, hi);
       store_pair<D>(wide, tok, ch, lo, hi);
     }
     __syncwarp();
@@ -299,8 +329,8 @@ gqa_decode_int8_kernel(const bf16* __restrict__ q, int64_t q_stride, const int8_
 #pragma unroll
       for (int c2 = 0; c2 < 2; ++c2) {
         const int col = j * 8 + tig * 2 + c2;
-        const float ks_ = sc[col * 4];
-        vs[j][c2] = sc[(16 + col) * 4];
+        const float ks_ = FP8 ? 1.f : sc[col * 4];
+        vs[j][c2] = FP8 ? 1.f : sc[(16 + col) * 4];
         const bool in = p0 + col < e0;
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
@@ -394,7 +424,7 @@ gqa_decode_int8_kernel(const bf16* __restrict__ q, int64_t q_stride, const int8_
         den += sc2 * pml[16 + r];
       }
     }
-    float val = den > 0.f ? num / den : 0.f;
+    float val = den > 0.f ? num / den * out_scale : 0.f;
     int head = head0 + r;
     if (num_splits == 1) {
       out[(int64_t)b * out_stride + (int64_t)head * D + d] = __float2bfloat16(val);
@@ -443,14 +473,16 @@ LLB_EXPORT int llb_kv_quant_store_int8(const void* src, int64_t src_stride, void
   return LLB_OK;
 }
 
-// Same contract as llb_gqa_decode with kv_layer the int8 pool slice described at the top of this file.
-LLB_EXPORT int llb_gqa_decode_int8kv(const void* q, int64_t q_stride, const void* kv_layer, const int* req_to_token,
-                                     int64_t r2t_stride, const int* b_req_idx, const int* b_seq_len, void* out,
-                                     int64_t out_stride, float* part_o, float* part_lse, int B, int Hq, int Hkv,
-                                     int D, int num_splits, float sm_scale, cudaStream_t st) {
+namespace {
+template <bool FP8>
+int launch_decode8(const void* q, int64_t q_stride, const void* kv_layer, const int* req_to_token, int64_t r2t_stride,
+                   const int* b_req_idx, const int* b_seq_len, void* out, int64_t out_stride, float* part_o,
+                   float* part_lse, int B, int Hq, int Hkv, int D, int num_splits, float sm_scale,
+                   const float* head_scales, cudaStream_t st) {
   if (B <= 0) return LLB_OK;
   if (Hkv <= 0 || Hq % Hkv != 0 || num_splits < 1) return LLB_ERR_BAD_ARG;
   if (num_splits > 1 && (part_o == nullptr || part_lse == nullptr)) return LLB_ERR_BAD_ARG;
+  if (FP8 && head_scales == nullptr) return LLB_ERR_BAD_ARG;
   const int G = Hq / Hkv;
   dim3 grid(num_splits, Hkv * ((G + 15) / 16), B);
   const float sl2 = sm_scale * kLog2e;
@@ -458,14 +490,14 @@ LLB_EXPORT int llb_gqa_decode_int8kv(const void* q, int64_t q_stride, const void
   {                                                                                                                 \
     static bool configured = false;                                                                                 \
     if (!configured) {                                                                                              \
-      cudaError_t e = cudaFuncSetAttribute(gqa_decode_int8_kernel<DD>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                           Int8DecodeSmem<DD>::TOTAL);                                              \
+      cudaError_t e = cudaFuncSetAttribute(gqa_decode_int8_kernel<DD, FP8>,                                         \
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, Int8DecodeSmem<DD>::TOTAL); \
       if (e != cudaSuccess) return (int)e;                                                                          \
       configured = true;                                                                                            \
     }                                                                                                               \
-    launch_pdl(gqa_decode_int8_kernel<DD>, grid, dim3(128), Int8DecodeSmem<DD>::TOTAL, st, (const bf16*)q, q_stride, \
-               (const int8_t*)kv_layer, req_to_token, r2t_stride, b_req_idx, b_seq_len, (bf16*)out, out_stride,     \
-               part_o, part_lse, Hq, Hkv, num_splits, sl2);                                                         \
+    launch_pdl(gqa_decode_int8_kernel<DD, FP8>, grid, dim3(128), Int8DecodeSmem<DD>::TOTAL, st, (const bf16*)q,     \
+               q_stride, (const int8_t*)kv_layer, req_to_token, r2t_stride, b_req_idx, b_seq_len, (bf16*)out,       \
+               out_stride, part_o, part_lse, Hq, Hkv, num_splits, sl2, head_scales);                                \
     LLB_LAUNCH_CHECK();                                                                                             \
     if (num_splits > 1) {                                                                                           \
       launch_pdl(decode_merge_int8_kernel<DD>, dim3(B * Hq), dim3(DD), 0, st, (const float*)part_o,                 \
@@ -481,4 +513,23 @@ LLB_EXPORT int llb_gqa_decode_int8kv(const void* q, int64_t q_stride, const void
     return LLB_ERR_UNSUPPORTED;
 #undef LAUNCH_DECODE8
   return LLB_OK;
+}
+}  // namespace
+
+// Same contract as llb_gqa_decode with kv_layer the int8 pool slice described at the top of this file.
+LLB_EXPORT int llb_gqa_decode_int8kv(const void* q, int64_t q_stride, const void* kv_layer, const int* req_to_token,
+                                     int64_t r2t_stride, const int* b_req_idx, const int* b_seq_len, void* out,
+                                     int64_t out_stride, float* part_o, float* part_lse, int B, int Hq, int Hkv,
+                                     int D, int num_splits, float sm_scale, cudaStream_t st) {
+  return launch_decode8<false>(q, q_stride, kv_layer, req_to_token, r2t_stride, b_req_idx, b_seq_len, out, out_stride,
+                               part_o, part_lse, B, Hq, Hkv, D, num_splits, sm_scale, nullptr, st);
+}
+
+// kv_layer: e4m3 rows [slot, 2*Hkv, D]; head_scales: fp32 [2*Hkv] of this layer (K heads, then V heads), x = q * scale.
+LLB_EXPORT int llb_gqa_decode_fp8kv(const void* q, int64_t q_stride, const void* kv_layer, const int* req_to_token,
+                                    int64_t r2t_stride, const int* b_req_idx, const int* b_seq_len, void* out,
+                                    int64_t out_stride, float* part_o, float* part_lse, int B, int Hq, int Hkv, int D,
+                                    int num_splits, float sm_scale, const float* head_scales, cudaStream_t st) {
+  return launch_decode8<true>(q, q_stride, kv_layer, req_to_token, r2t_stride, b_req_idx, b_seq_len, out, out_stride,
+                              part_o, part_lse, B, Hq, Hkv, D, num_splits, sm_scale, head_scales, st);
 }

@@ -368,9 +368,17 @@ class TransformerLM:
         return self._kv_manager_class().bytes_per_token(self.dtype, self.hkv, self.head_dim,
                                                         self.num_layers + self.extra_kv_layers)
 
+    def _kv_manager_kwargs(self) -> dict:
+        kw = {}
+        if str(self.extra.get("kv_type") or "").startswith("fp8kv"):
+            kw["calibration"] = self.extra.get("kv_quant_calibration_config_path")
+            kw["head_range"] = getattr(self, "_kv_range", None)
+        return kw
+
     def _make_mem_manager(self, size):
         return self._kv_manager_class()(size, self.dtype, self.hkv, self.head_dim,
-                                        self.num_layers + self.extra_kv_layers, self.device)
+                                        self.num_layers + self.extra_kv_layers, self.device,
+                                        **self._kv_manager_kwargs())
 
     def _kv_layer(self, i: int):
         return self.mem_manager.layer(self.kv_layer_offset + i)

@@ -138,7 +138,8 @@ class Qwen3NextLM(Qwen3MoeLM):
 
     def _make_mem_manager(self, size):
         return self._kv_manager_class()(size, self.dtype, self.hkv, self.head_dim,
-                                        len(self.full_layers) + self.extra_kv_layers, self.device)
+                                        len(self.full_layers) + self.extra_kv_layers, self.device,
+                                        **self._kv_manager_kwargs())
 
     def _kv_layer(self, i: int):
         return self.mem_manager.layer(self.kv_layer_offset + self._kv_slot[i])

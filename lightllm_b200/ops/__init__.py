@@ -95,7 +95,7 @@ def rope_kv_scatter_(qkv, kv_layer, cos, sin, pos, slot, Hq, Hkv, D, rot_dim=Non
                      norm_eps=1e-6, norm_w_offset=0.0):
     """rot_dim None = full head; 0 = no rotation (ALiBi / learned positions: K and V are only scattered)."""
     rot_dim = D if rot_dim is None else rot_dim
-    if isinstance(kv_layer, kv_quant.Int8KVLayer):
+    if isinstance(kv_layer, kv_quant.QuantKVLayer):
         return kv_quant.rope_kv_scatter_(qkv, kv_layer, cos, sin, pos, slot, Hq, Hkv, D, rot_dim, q_norm_w, k_norm_w,
                                          norm_eps, norm_w_offset)
     if not _is_cuda(qkv):
@@ -293,7 +293,7 @@ def gqa_decode_num_splits(B, Hq, Hkv, max_seq_len) -> int:
 def gqa_decode(q, kv_layer, req_to_token, b_req_idx, b_seq_len, Hq, Hkv, D, max_seq_len: int, sm_scale=None,
                out=None, num_splits: Optional[int] = None, scratch=None):
     """Paged GQA decode attention. q [B, Hq*D] or [B, Hq, D] (row stride arbitrary)."""
-    if isinstance(kv_layer, kv_quant.Int8KVLayer):
+    if isinstance(kv_layer, kv_quant.QuantKVLayer):
         return kv_quant.gqa_decode(q, kv_layer, req_to_token, b_req_idx, b_seq_len, Hq, Hkv, D, max_seq_len, sm_scale,
                                    out, num_splits, scratch)
     if not _is_cuda(q):
@@ -322,7 +322,7 @@ def gqa_decode(q, kv_layer, req_to_token, b_req_idx, b_seq_len, Hq, Hkv, D, max_
 def gqa_prefill(q, kv_layer, req_to_token, b_req_idx, cu_q, b_ready_len, Hq, Hkv, D, max_q_len: int, sm_scale=None,
                 out=None):
     """Causal varlen prefill attention over (cached prefix + new tokens). q [T, Hq*D] or [T, Hq, D]."""
-    if isinstance(kv_layer, kv_quant.Int8KVLayer):
+    if isinstance(kv_layer, kv_quant.QuantKVLayer):
         return kv_quant.gqa_prefill(q, kv_layer, req_to_token, b_req_idx, cu_q, b_ready_len, Hq, Hkv, D, max_q_len,
                                     sm_scale, out)
     if not _is_cuda(q):
@@ -503,7 +503,7 @@ def attention_generic(q, kv_layer, req_to_token, b_req_idx, pos, batch_of, Hq, H
     """Causal paged attention for any head size <= 256 with sliding window / ALiBi / soft-cap / sinks.
     q [T, Hq*D] or [T, Hq, D]; returns [T, Hq, D]."""
     T = q.shape[0]
-    if isinstance(kv_layer, kv_quant.Int8KVLayer):
+    if isinstance(kv_layer, kv_quant.QuantKVLayer):
         return kv_quant.attention_generic(q, kv_layer, req_to_token, b_req_idx, pos, batch_of, Hq, Hkv, D, sm_scale,
                                           window, softcap, alibi, sinks)
     if not _is_cuda(q):

@@ -9,8 +9,13 @@ scale = max|x| / 127 over the row), so a token's row is an opaque byte string fo
 * prefill (and the generic-head-size kernel) runs on a bf16 copy of the rows the batch refers to, gathered and
   widened once per layer, with a request table that points into that copy.
 
-Reference: lightllm/common/kv_cache_mem_manager/ppl_int8kv_mem_manager.py, common/basemodel/attention/triton/
-int8kv.py, `--llm_kv_type int8kv`.
+The fp8 pool (`Fp8KVLayer`, `--llm_kv_type fp8kv_sph | fp8kv_spt`) stores e4m3 rows without a scale in the row: the
+scales are static numbers per (layer, head) -- or one per layer for K and one for V -- read from a calibration file
+(`--kv_quant_calibration_config_path`; ones without a file).  The same three routes apply.
+
+Reference: lightllm/common/kv_cache_mem_manager/ppl_int8kv_mem_manager.py, fp8_static_per_head_quant_mem_manager.py,
+fp8_static_per_tensor_quant_mem_manager.py, common/basemodel/attention/triton/int8kv.py, attention/fa3/fp8.py,
+`--llm_kv_type`.
 """
 from __future__ import annotations
 
@@ -22,7 +27,44 @@ import torch
 PAD = 16  # bytes after the payload of a row: fp32 scale + padding
 
 
-class Int8KVLayer:
+class QuantKVLayer:
+    """A layer of a quantised pool; the attention ops accept it in place of a bf16 slice."""
+
+    __slots__ = ()
+
+
+class Fp8KVLayer(QuantKVLayer):
+    """`data` e4m3 (stored as uint8) [slots + 1, 2 * Hkv, D]; `scales` fp32 [2 * Hkv] (K heads, then V heads)."""
+
+    __slots__ = ("data", "head_dim", "scales")
+
+    def __init__(self, data: torch.Tensor, head_dim: int, scales: torch.Tensor):
+        assert data.dtype == torch.uint8 and data.shape[-1] == head_dim and scales.shape[0] == data.shape[1]
+        self.data, self.head_dim, self.scales = data, head_dim, scales
+
+    @property
+    def device(self):
+        return self.data.device
+
+    @property
+    def is_cuda(self):
+        return self.data.is_cuda
+
+    def _deq(self, rows, dtype):
+        return (rows.view(torch.float8_e4m3fn).float() * self.scales.view(1, -1, 1)).to(dtype)
+
+    def dequant_rows(self, slots: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+        return self._deq(self.data.index_select(0, slots.to(self.data.device, torch.long)), dtype)
+
+    def dequant_all(self, dtype: torch.dtype) -> torch.Tensor:
+        return self._deq(self.data, dtype)
+
+    def store_(self, src: torch.Tensor, slot: torch.Tensor) -> None:
+        q = (src.float() / self.scales.view(1, -1, 1)).clamp(-448.0, 448.0).to(torch.float8_e4m3fn)
+        self.data[slot.long()] = q.view(torch.uint8)
+
+
+class Int8KVLayer(QuantKVLayer):
     """One layer of the quantised pool: `data` int8 [slots + 1, 2 * Hkv, D + 16]."""
 
     __slots__ = ("data", "head_dim")
@@ -63,8 +105,10 @@ def quant_rows_reference(x: torch.Tensor):
     return q, scale
 
 
-def quant_store_(layer: Int8KVLayer, src: torch.Tensor, slot: torch.Tensor) -> None:
+def quant_store_(layer, src: torch.Tensor, slot: torch.Tensor) -> None:
     """layer[slot[t]] = quantised src[t];  src [T, 2 * Hkv, D] (bf16 on the GPU)."""
+    if isinstance(layer, Fp8KVLayer):
+        return layer.store_(src, slot)
     T, rows, D = src.shape
     assert D == layer.head_dim and rows == layer.data.shape[1]
     if not src.is_cuda:
@@ -82,7 +126,7 @@ def quant_store_(layer: Int8KVLayer, src: torch.Tensor, slot: torch.Tensor) -> N
     _count()
 
 
-def rope_kv_scatter_(qkv, layer: Int8KVLayer, cos, sin, pos, slot, Hq, Hkv, D, *rest, **kw):
+def rope_kv_scatter_(qkv, layer, cos, sin, pos, slot, Hq, Hkv, D, *rest, **kw):
     """The rotary / norm / scatter op with a quantised destination: K and V go through a scratch tensor."""
     from . import rope_kv_scatter_ as plain
 
@@ -94,7 +138,7 @@ def rope_kv_scatter_(qkv, layer: Int8KVLayer, cos, sin, pos, slot, Hq, Hkv, D, *
     return qkv
 
 
-def gqa_decode(q, layer: Int8KVLayer, req_to_token, b_req_idx, b_seq_len, Hq, Hkv, D, max_seq_len, sm_scale=None,
+def gqa_decode(q, layer, req_to_token, b_req_idx, b_seq_len, Hq, Hkv, D, max_seq_len, sm_scale=None,
                out=None, num_splits: Optional[int] = None, scratch=None):
     from . import _count, _scratch, c_int, check, f32, gqa_decode as plain, gqa_decode_num_splits, i64, kernels, ptr, \
         stream
@@ -116,6 +160,14 @@ def gqa_decode(q, layer: Int8KVLayer, req_to_token, b_req_idx, b_seq_len, Hq, Hk
     po = pl = None
     if num_splits > 1:
         po, pl = scratch if scratch is not None else _scratch(q.device, B * Hq * num_splits * D, B * Hq * num_splits)
+    if isinstance(layer, Fp8KVLayer):
+        check(kernels().llb_gqa_decode_fp8kv(ptr(q), i64(q.stride(0)), ptr(layer.data), ptr(req_to_token),
+                                             i64(req_to_token.stride(0)), ptr(b_req_idx), ptr(b_seq_len), ptr(out),
+                                             i64(out.stride(0)), ptr(po), ptr(pl), c_int(B), c_int(Hq), c_int(Hkv),
+                                             c_int(D), c_int(num_splits), f32(scale), ptr(layer.scales), stream()),
+              "gqa_decode_fp8kv")
+        _count(2 if num_splits > 1 else 1)
+        return out
     check(kernels().llb_gqa_decode_int8kv(ptr(q), i64(q.stride(0)), ptr(layer.data), ptr(req_to_token),
                                           i64(req_to_token.stride(0)), ptr(b_req_idx), ptr(b_seq_len), ptr(out),
                                           i64(out.stride(0)), ptr(po), ptr(pl), c_int(B), c_int(Hq), c_int(Hkv),
@@ -124,7 +176,7 @@ def gqa_decode(q, layer: Int8KVLayer, req_to_token, b_req_idx, b_seq_len, Hq, Hk
     return out
 
 
-def gather_dequant(layer: Int8KVLayer, req_to_token, b_req_idx, b_seq_len, dtype):
+def gather_dequant(layer, req_to_token, b_req_idx, b_seq_len, dtype):
     """A bf16 copy of the rows the batch refers to: (kv [n + 1, 2 * Hkv, D], request table [B, max_len] into it,
     request ids 0 .. B - 1).  Row n is a zero row for the positions past a request's length."""
     dev = layer.data.device
@@ -141,7 +193,7 @@ def gather_dequant(layer: Int8KVLayer, req_to_token, b_req_idx, b_seq_len, dtype
     return kv, new_table, torch.arange(B, dtype=torch.int32, device=dev)
 
 
-def gqa_prefill(q, layer: Int8KVLayer, req_to_token, b_req_idx, cu_q, b_ready_len, Hq, Hkv, D, max_q_len,
+def gqa_prefill(q, layer, req_to_token, b_req_idx, cu_q, b_ready_len, Hq, Hkv, D, max_q_len,
                 sm_scale=None, out=None):
     from . import gqa_prefill as plain
 
@@ -150,7 +202,7 @@ def gqa_prefill(q, layer: Int8KVLayer, req_to_token, b_req_idx, cu_q, b_ready_le
     return plain(q, kv, r2t, idx, cu_q, b_ready_len, Hq, Hkv, D, max_q_len, sm_scale, out)
 
 
-def attention_generic(q, layer: Int8KVLayer, req_to_token, b_req_idx, pos, batch_of, Hq, Hkv, D, sm_scale, *rest, **kw):
+def attention_generic(q, layer, req_to_token, b_req_idx, pos, batch_of, Hq, Hkv, D, sm_scale, *rest, **kw):
     from . import attention_generic as plain
 
     dev = layer.device

@@ -24,6 +24,14 @@ def bench_decode(a, dev, Hq, Hkv, D, B, L):
         kv = mm.layer(0)
         kv_quant.quant_store_(kv, vals, torch.arange(slots + 1, dtype=torch.int32, device=dev))
         row_bytes = 2 * Hkv * (D + kv_quant.PAD)
+    elif a.fp8kv:
+        from lightllm_b200.common.mem_manager import Fp8KVMemoryManager
+
+        mm = Fp8KVMemoryManager(slots, torch.bfloat16, Hkv, D, 1, dev)
+        mm.scales.fill_(0.01)
+        kv = mm.layer(0)
+        kv_quant.quant_store_(kv, vals, torch.arange(slots + 1, dtype=torch.int32, device=dev))
+        row_bytes = 2 * Hkv * D
     else:
         kv, row_bytes = vals, 2 * Hkv * D * 2
     r2t = torch.arange(slots, dtype=torch.int32, device=dev).view(B, L)
@@ -45,7 +53,7 @@ def bench_decode(a, dev, Hq, Hkv, D, B, L):
         ts.append(e0.elapsed_time(e1))
     ts.sort()
     t = ts[len(ts) // 2]
-    print(json.dumps({"decode": True, "int8kv": bool(a.int8kv), "B": B, "ctx": L, "ms": round(t, 4),
+    print(json.dumps({"decode": True, "int8kv": bool(a.int8kv), "fp8kv": bool(a.fp8kv), "B": B, "ctx": L, "ms": round(t, 4),
                       "kv_gb": round(slots * row_bytes / 1e9, 3), "gbs": round(slots * row_bytes / t / 1e6, 1)}))
 
 
@@ -61,6 +69,7 @@ def main():
     ap.add_argument("--hkv", type=int, default=8)
     ap.add_argument("--decode", action="store_true", help="time decode attention (one query token per request)")
     ap.add_argument("--int8kv", action="store_true", help="decode over the int8 pool")
+    ap.add_argument("--fp8kv", action="store_true", help="decode over the fp8 (e4m3, static per-head scales) pool")
     a = ap.parse_args()
     dev = torch.device("cuda")
     Hq, Hkv, D, B, L, R = a.hq, a.hkv, 128, a.B, a.len, a.ready

@@ -111,3 +111,52 @@ def test_llama_with_int8_pool_close_to_bf16_pool(dev):
     same = sum(x == y for oa, ob in zip(a, b) for x, y in zip(oa["token_ids"], ob["token_ids"]))
     assert same >= 0.7 * 4 * 12, f"{same} of 48 greedy tokens agree"    # random weights: near-ties may flip
     assert b == llm.generate(prompts, sp) or True
+
+
+@pytest.mark.parametrize("Hq,Hkv,D", [(32, 8, 128), (4, 1, 128), (8, 2, 64)])
+@pytest.mark.parametrize("splits", [1, 3])
+def test_decode_over_fp8_pool(dev, Hq, Hkv, D, splits):
+    from lightllm_b200.common.mem_manager import Fp8KVMemoryManager
+
+    lens = [1, 15, 16, 17, 130, 500, 64, 257]
+    g = torch.Generator(device="cpu").manual_seed(0)
+    total = sum(lens)
+    size = total + 17
+    mm = Fp8KVMemoryManager(size, BF, Hkv, D, 1, dev)
+    mm.scales.copy_((torch.rand(1, 2 * Hkv, generator=g) * 0.05 + 0.01).to(dev))
+    layer = mm.layer(0)
+    vals = torch.randn(size + 1, 2 * Hkv, D, generator=g) * 2
+    kv_quant.quant_store_(layer, vals.to(dev, BF), torch.arange(size + 1, dtype=torch.int32, device=dev))
+    perm = torch.randperm(size, generator=g)[:total].to(torch.int32)
+    r2t = torch.zeros(13, max(lens) + 3, dtype=torch.int32)
+    rows = torch.randperm(12, generator=g)[: len(lens)]
+    off = 0
+    for i, L in enumerate(lens):
+        r2t[rows[i], :L] = perm[off:off + L]
+        off += L
+    r2t, rows = r2t.to(dev), rows.to(torch.int32).to(dev)
+    B = len(lens)
+    torch.manual_seed(1)
+    q = torch.randn(B, Hq * D, device=dev, dtype=BF)
+    b_len = torch.tensor(lens, dtype=torch.int32, device=dev)
+    got = ops.gqa_decode(q, layer, r2t, rows, b_len, Hq, Hkv, D, max(lens), num_splits=splits)
+    want = ref.gqa_decode(q.reshape(B, Hq, D), layer.dequant_all(torch.float32), r2t, rows, b_len, Hq, Hkv, D)
+    scale = max(want.float().abs().max().item(), 1.0)
+    err = (got.float() - want.float()).abs().max().item()
+    assert err < 2e-2 * scale, f"max abs err {err} (scale {scale})"
+
+
+def test_llama_with_fp8_pool(dev):
+    from lightllm_b200.engine.llm import LLM
+
+    cfg = dict(model_type="llama", hidden_size=512, intermediate_size=1024, num_hidden_layers=2,
+               num_attention_heads=8, num_key_value_heads=2, head_dim=128, vocab_size=1000, rms_norm_eps=1e-5,
+               eos_token_id=2)
+    kw = dict(max_total_token_num=8192, running_max_req_size=16, max_req_total_len=1024, batch_max_tokens=1024)
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(3, 1000, (n,), generator=g).tolist() for n in (200, 37, 300, 64)]
+    sp = {"max_new_tokens": 12, "ignore_eos": True}
+    a = LLM(config=cfg, **kw).generate(prompts, sp)
+    b = LLM(config=cfg, kv_type="fp8kv_sph", **kw).generate(prompts, sp)
+    same = sum(x == y for oa, ob in zip(a, b) for x, y in zip(oa["token_ids"], ob["token_ids"]))
+    assert same >= 0.5 * 4 * 12, f"{same} of 48 greedy tokens agree"
