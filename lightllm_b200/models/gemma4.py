@@ -18,7 +18,8 @@ What differs from Gemma-3 and shapes this file:
 The projections, norms and expert GEMMs run on this package's kernels; the attention prologue (per-head norms,
 rotary embedding, cache write) is torch glue because head sizes differ per layer; attention runs on the generic
 kernel for head sizes up to 256 and on torch ops (per request, dense scores) above that, outside CUDA graphs.
-Vision and audio towers of the multimodal checkpoints are not built: picture / sound placeholders are not merged.
+`Gemma4LM` (bottom of the file) adds pictures: soft tokens of `models/vit/gemma4_visual.py` replace placeholder rows.
+The audio tower of the small multimodal checkpoints is not built.
 
 Reference: lightllm/models/gemma4/{model.py,layer_infer/transformer_layer_infer.py,layer_weights/*}.
 """
@@ -141,6 +142,8 @@ class Gemma4TextLM(TransformerLM):
         self.top_k = int(c.get("top_k_experts") or 0)
         self.moe_inter = int(c.get("moe_intermediate_size") or 0)
         self.logit_cap = float(c.get("final_logit_softcapping") or 0.0)
+        self.pad_id = int(c.get("pad_token_id") or 0)
+        self.bidirectional_pictures = c.get("use_bidirectional_attention") == "vision"
         rp = c.get("rope_parameters") or {}
         sl, fa = rp.get("sliding_attention") or {}, rp.get("full_attention") or {}
         self.theta_s = float(sl.get("rope_theta", 10000.0))
@@ -313,7 +316,9 @@ class Gemma4TextLM(TransformerLM):
         h = super()._embed(ids, st)
         if self.pli:
             L, P = self.num_layers, self.pli
-            tok = ops.embedding(ids, self.pli_embed_w, 0, self.pli_vocab).view(-1, L, P).float() * P ** 0.5
+            # picture / sound placeholders (virtual ids beyond the vocabulary) count as the padding token here
+            pli_ids = torch.where(ids >= self.pli_vocab, torch.full_like(ids, self.pad_id), ids)
+            tok = ops.embedding(pli_ids, self.pli_embed_w, 0, self.pli_vocab).view(-1, L, P).float() * P ** 0.5
             proj = (ops.gemm(h, self.pli_proj_w).float() * self.hidden ** -0.5).view(-1, L, P)
             proj = _rms(proj, self.pli_norm_w, self.eps).float()
             st.extra["per_layer_inputs"] = ((proj + tok.to(h.dtype).float()) * 2.0 ** -0.5).to(h.dtype)
@@ -394,8 +399,11 @@ class Gemma4TextLM(TransformerLM):
         window = 0 if glob else self.window
         r2t = self.req_manager.req_to_token_indexs
         q2 = q.reshape(T, hq * D).contiguous()
+        seq_pos = st.seq_pos
+        if not glob and st.is_prefill and st.extra.get("seq_pos_pictures") is not None:
+            seq_pos = st.extra["seq_pos_pictures"]
         if D <= self.big_head:
-            o = ops.attention_generic(q2, kv_layer, r2t, st.b_req_idx, st.seq_pos,
+            o = ops.attention_generic(q2, kv_layer, r2t, st.b_req_idx, seq_pos,
                                       st.batch_of_token if st.is_prefill else None, hq, hkv, D, 1.0, window=window)
         else:
             o = self._attention_torch(q, kv_layer, r2t, st, hq, hkv, D, window)
@@ -423,4 +431,91 @@ class Gemma4TextLM(TransformerLM):
             s = torch.einsum("thd,shd->hts", q[off:off + n].float(), k).masked_fill(~mask.unsqueeze(0), float("-inf"))
             out[off:off + n] = torch.einsum("hts,shd->thd", torch.softmax(s, dim=-1), v).to(q.dtype)
             off += n
+        return out
+
+
+@register_model("gemma4", condition=lambda cfg: bool(cfg.get("vision_config")), is_multimodal=True)
+class Gemma4LM(Gemma4TextLM):
+    """Gemma-4 with pictures: the soft tokens of the vision tower (`models/vit/gemma4_visual.py`) replace the
+    placeholder rows (not scaled like word embeddings); with `use_bidirectional_attention: vision` the tokens of one
+    picture see each other in both directions in the sliding-window layers (their causal limit becomes the
+    picture's last position there; global layers stay causal).  The audio tower is not built."""
+
+    def _prepare_prefill_state(self, st):
+        super()._prepare_prefill_state(st)
+        mm = st.extra.get("multimodal_params")
+        if not mm or not self.bidirectional_pictures:
+            return
+        ids = st.extra["input_ids_cpu"]
+        q_len = st.extra["q_len_cpu"].tolist()
+        pos = st.seq_pos.clone()
+        changed, off = False, 0
+        for b, n_tok in enumerate(q_len):
+            params = mm[b] if b < len(mm) and mm[b] else {}
+            seg = ids[off:off + n_tok]
+            for it in params.get("images", []):
+                t0, n = it.get("token_id"), it.get("token_num")
+                if t0 is None:
+                    continue
+                hit = ((seg >= t0) & (seg < t0 + n)).nonzero(as_tuple=True)[0]
+                if hit.numel() > 1:
+                    hit = (hit + off).to(pos.device)
+                    pos[hit] = pos[hit].max()
+                    changed = True
+            off += n_tok
+        if changed:
+            st.extra["seq_pos_pictures"] = pos      # used by the sliding-window layers only; global layers stay causal
+
+
+class Gemma4Tokenizer:
+    """Every image placeholder of the prompt (`<|image|>` text or its id) becomes begin-of-image id + the picture's
+    virtual ids + end-of-image id; the number of ids follows the tower's resize rule."""
+
+    def __init__(self, tokenizer, model_cfg: dict):
+        self.tokenizer = tokenizer
+        self.image_token = model_cfg.get("image_token", "<|image|>")
+        self.image_token_id = model_cfg.get("image_token_id", 258_880)
+        self.boi_id = model_cfg.get("boi_token_id", 255_999)
+        self.eoi_id = model_cfg.get("eoi_token_id", 258_882)
+        vc = model_cfg.get("vision_config") or {}
+        self.patch = int(vc.get("patch_size", 16))
+        self.k = int(vc.get("pooling_kernel_size", 3))
+        self.max_soft_tokens = int(model_cfg.get("max_soft_tokens", 280))
+
+    def __getattr__(self, name):
+        return getattr(self.tokenizer, name)
+
+    def init_imageitem_extral_params(self, img, multi_params=None, sampling_params=None):
+        pass
+
+    def get_image_token_length(self, img) -> int:
+        from .vit.gemma4_visual import soft_token_num
+
+        return soft_token_num(img.image_w, img.image_h, self.patch, self.max_soft_tokens, self.k)
+
+    def encode(self, prompt, multimodal_params=None, add_special_tokens: bool = False, **kw):
+        images = list(multimodal_params.images) if multimodal_params is not None else []
+
+        def run(im):
+            return [self.boi_id] + list(range(im.token_id, im.token_id + im.token_num)) + [self.eoi_id]
+
+        out, k = [], 0
+        if isinstance(prompt, (list, tuple)):
+            for t in prompt:
+                if t == self.image_token_id and k < len(images):
+                    out += run(images[k])
+                    k += 1
+                else:
+                    out.append(t)
+        else:
+            chunks = prompt.split(self.image_token)
+            out = list(self.tokenizer.encode(chunks[0], add_special_tokens=add_special_tokens))
+            for c in chunks[1:]:
+                if k >= len(images):
+                    raise ValueError("more image placeholders than pictures")
+                out += run(images[k])
+                k += 1
+                out += list(self.tokenizer.encode(c, add_special_tokens=False))
+        if k != len(images):
+            raise ValueError(f"the prompt has {k} image placeholders for {len(images)} images")
         return out

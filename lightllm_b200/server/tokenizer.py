@@ -73,6 +73,10 @@ def get_tokenizer(model_dir: str, tokenizer_mode: str = "fast", trust_remote_cod
         from ..models.qwen3_omni import Qwen3OmniTokenizer
 
         return Qwen3OmniTokenizer(tok, cfg)
+    if mt == "gemma4":
+        from ..models.gemma4 import Gemma4Tokenizer
+
+        return Gemma4Tokenizer(tok, cfg)
     if mt == "gemma3":
         from ..models.generic import Gemma3Tokenizer
 

@@ -76,6 +76,10 @@ def build_vision_tower(args, device, dtype=torch.bfloat16):
         from ...models.vit.clip_visual import ClipLlavaTower
 
         return ClipLlavaTower(cfg, SafetensorsSource(args.model_dir), device, dtype)
+    if mt == "gemma4":
+        from ...models.vit.gemma4_visual import Gemma4VisionTower
+
+        return Gemma4VisionTower(cfg, SafetensorsSource(args.model_dir), device, dtype)
     if mt == "gemma3":
         from ...models.vit.siglip_visual import SiglipGemma3Tower
 

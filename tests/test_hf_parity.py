@@ -1051,3 +1051,87 @@ def test_gemma4_moe_block_and_torch_attention(tmp_path):
               enable_moe_block=True, num_experts=4, top_k_experts=2, moe_intermediate_size=32,
               max_position_embeddings=256, tie_word_embeddings=False, pad_token_id=0)
     _gemma4_check(tmp_path, kw, force_torch_attention=True, n_tokens=40)
+
+
+def test_gemma4_vision_tower_and_picture_tokens(tmp_path):
+    """Gemma-4 with a picture: patch embedding with per-axis position tables, encoder blocks with two-axis rotary
+    embedding, pooling by grid position, projection; soft tokens replace placeholder rows, per-layer inputs treat
+    the placeholders as padding, picture tokens attend in both directions."""
+    import json
+
+    from safetensors.torch import save_file
+    from transformers import Gemma4Config, Gemma4ForConditionalGeneration
+
+    from lightllm_b200.common.infer_state import ModelInput
+    from lightllm_b200.models.base import load_config
+    from lightllm_b200.models.registry import get_model, is_multimodal
+    from lightllm_b200.models.vit.gemma4_visual import Gemma4VisionTower, soft_token_num
+    from lightllm_b200.models.weights import SafetensorsSource
+    from lightllm_b200.parallel import dist as pdist
+
+    torch.manual_seed(0)
+    text = dict(vocab_size=300, hidden_size=64, intermediate_size=128, num_hidden_layers=3, num_attention_heads=4,
+                num_key_value_heads=2, head_dim=16, global_head_dim=32, sliding_window=16,
+                layer_types=["sliding_attention", "sliding_attention", "full_attention"], hidden_size_per_layer_input=8,
+                vocab_size_per_layer_input=300, max_position_embeddings=256, pad_token_id=0,
+                use_bidirectional_attention="vision", tie_word_embeddings=True)
+    vision = dict(hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
+                  num_key_value_heads=4, head_dim=8, patch_size=16, pooling_kernel_size=3, position_embedding_size=64,
+                  use_clipped_linears=True, standardize=True)
+    cfg = Gemma4Config(text_config=text, vision_config=vision, audio_config=None, image_token_id=290, boi_token_id=291,
+                       eoi_token_id=292, video_token_id=293, audio_token_id=294)
+    hf = Gemma4ForConditionalGeneration(cfg).eval().float()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if "norm" in n or "position_embedding_table" in n:
+                p.add_(torch.randn_like(p) * 0.1)
+        for n, b in hf.named_buffers():
+            if n.endswith("input_min") or n.endswith("output_min"):
+                b.fill_(-1.5)
+            elif n.endswith("input_max") or n.endswith("output_max"):
+                b.fill_(1.5)
+            elif n.endswith("std_bias"):
+                b.copy_(torch.randn_like(b) * 0.1)
+            elif n.endswith("std_scale"):
+                b.copy_(1 + torch.randn_like(b) * 0.1)
+    d = tmp_path / "ckpt"
+    d.mkdir()
+    sd = {k: v.contiguous() for k, v in hf.state_dict().items() if k != "lm_head.weight"}
+    save_file(sd, str(d / "model.safetensors"))
+    (d / "config.json").write_text(json.dumps(cfg.to_dict()))
+
+    conf = load_config(str(d))
+    assert is_multimodal(conf) and soft_token_num(96, 96, 16, 4, 3) == 4
+    tower = Gemma4VisionTower(conf, SafetensorsSource(str(d)), torch.device("cpu"), torch.float32)
+    img = torch.rand(3, 96, 96)
+    patches, pos = tower.patchify(img)
+    assert patches.shape == (36, 768) and pos[7].tolist() == [1, 1]
+    n_img = 4
+    pre, post = [5, 17, 291], [292, 9, 44, 120, 7, 250]
+    hf_ids = torch.tensor([pre + [290] * n_img + post])
+    with torch.no_grad():
+        feats = hf.model.get_image_features(patches.unsqueeze(0), pos.unsqueeze(0), return_dict=True).pooler_output
+        ref = hf(input_ids=hf_ids, pixel_values=patches.unsqueeze(0), image_position_ids=pos.unsqueeze(0),
+                 mm_token_type_ids=(hf_ids == 290).long()).logits[0].float()
+    emb = tower.forward(patches, pos)
+    assert emb.shape == (n_img, 64) and (emb - feats.reshape(n_img, 64)).abs().max().item() < 1e-4
+
+    class Arena:
+        def read_rows(self, rows):
+            return emb[rows - 40]
+
+    m = get_model(conf, model_dir=str(d), pstate=pdist.ParallelState(device=torch.device("cpu")), data_type="float32",
+                  max_total_token_num=256, max_req_num=2, max_seq_length=128, disable_cudagraph=True)
+    assert type(m).__name__ == "Gemma4LM" and m.bidirectional_pictures
+    m.embed_arena = Arena()
+    tok0 = 100_000_000
+    ids = torch.tensor(pre + list(range(tok0, tok0 + n_img)) + post)
+    item = {"token_id": tok0, "token_num": n_img, "start_index_in_embed_cache": 40}
+    req, n = m.req_manager.alloc(), len(ids)
+    mi = ModelInput(batch_size=1, total_token_num=n, max_kv_len=n, is_prefill=True,
+                    b_req_idx=torch.tensor([req], dtype=torch.int32), b_seq_len=torch.tensor([n], dtype=torch.int32),
+                    mem_indexes=m.mem_manager.alloc(n).clone(), input_ids=ids,
+                    b_ready_cache_len=torch.zeros(1, dtype=torch.int32), max_q_len=n, return_all_logits=True,
+                    multimodal_params=[{"images": [item], "audios": []}])
+    got = m.forward(mi).logits.float()
+    assert (got - ref).abs().max().item() < 2e-3 * max(ref.abs().max().item(), 1.0)
