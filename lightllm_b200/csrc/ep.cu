@@ -125,7 +125,7 @@ __global__ void __launch_bounds__(256) ep_push_kernel(EpView v, const bf16* __re
     if (blockIdx.x == 0) *recv_total_out = s_total;
   }
   __syncthreads();
-  // rows of my own receive buffer that nobody writes this round carry no expert
+  // rows of my own receive buffer that nobody writes in this exchange carry no expert
   for (int64_t i = (int64_t)s_total * k + blockIdx.x * blockDim.x + threadIdx.x; i < (int64_t)max_recv * k;
        i += (int64_t)gridDim.x * blockDim.x)
     v.ids_recv[v.rank][i] = -1;
@@ -138,7 +138,7 @@ __global__ void __launch_bounds__(256) ep_push_kernel(EpView v, const bf16* __re
         continue;
       }
       const int row = s_base[r] + slot_in_block[(int64_t)t * EP_MAX_WORLD + r];
-      if (row >= max_recv) {  // receive buffer too small for this round: recorded, the token's share is lost
+      if (row >= max_recv) {  // receive buffer too small for this exchange: recorded, the token's share is lost
         if (threadIdx.x == 0) {
           where[(int64_t)t * EP_MAX_WORLD + r] = -1;
           atomicCAS(status, 0, 390);
