@@ -436,6 +436,319 @@ gqa_decode_int8_kernel(const bf16* __restrict__ q, int64_t q_stride, const int8_
   }
 }
 
+// ---------------------------------------------------------------------------------------
+// decode, head size 128, mma fragments built from registers
+// ---------------------------------------------------------------------------------------
+// The 8-bit rows are staged as they are (row pitch 144 bytes, which also staggers the rows over the banks) and the
+// mma operands are assembled straight from 16-byte shared-memory loads: no widened tile, no ldmatrix.
+//  * Q.K^T: the contraction runs over the head dimension, whose order does not matter as long as Q and K agree.
+//    Lane (g, tig) owns bytes [32 tig, 32 tig + 32) of a K row: k-step ks takes its bytes 4 ks .. 4 ks + 3 (two for
+//    each half of the B fragment).  The Q fragments are loaded once with the same mapping.
+//  * P.V: the output column order is free as long as the store undoes it.  Column g of n-tile nt stands for
+//    d = 16 g + nt: lane (g, tig) reads bytes [16 g, 16 g + 16) of token rows 2 tig, 2 tig + 1, 2 tig + 8, 2 tig + 9
+//    and pairs byte nt of two rows into one half2.
+constexpr int kRowPitch = 144;
+constexpr int kRegStages = 4;
+constexpr int kRegStageBytes = 2 * 16 * kRowPitch;            // K tile + V tile
+constexpr int kRegWarpBytes = kRegStages * kRegStageBytes;    // 18432
+constexpr int kRegSmemBytes = 4 * kRegWarpBytes;
+
+template <bool FP8>
+__device__ __forceinline__ void cvt_k_word(uint32_t w, uint32_t& b0, uint32_t& b1) {
+  if (FP8) {
+    __half2_raw a = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w & 0xffffu), __NV_E4M3);
+    __half2_raw b = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w >> 16), __NV_E4M3);
+    b0 = (uint32_t)a.x | ((uint32_t)a.y << 16);
+    b1 = (uint32_t)b.x | ((uint32_t)b.y << 16);
+  } else {
+    const __half2 bias = __halves2half2(__ushort_as_half((unsigned short)0x6480), __ushort_as_half((unsigned short)0x6480));
+    const uint32_t x = w ^ 0x80808080u;
+    uint32_t p0 = __byte_perm(x, 0x64646464u, 0x4140);
+    uint32_t p1 = __byte_perm(x, 0x64646464u, 0x4342);
+    __half2 h0 = __hsub2(*reinterpret_cast<__half2*>(&p0), bias);
+    __half2 h1 = __hsub2(*reinterpret_cast<__half2*>(&p1), bias);
+    b0 = *reinterpret_cast<uint32_t*>(&h0);
+    b1 = *reinterpret_cast<uint32_t*>(&h1);
+  }
+}
+
+// byte `i` (0..3) of word a and of word b as one half2 (a first)
+template <bool FP8>
+__device__ __forceinline__ uint32_t cvt_v_pair(uint32_t a, uint32_t b, int i) {
+  const uint32_t p = __byte_perm(a, b, (uint32_t)(i | ((4 + i) << 4)));   // low 16 bits: {a.byte i, b.byte i}
+  if (FP8) {
+    __half2_raw h = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(p & 0xffffu), __NV_E4M3);
+    return (uint32_t)h.x | ((uint32_t)h.y << 16);
+  } else {
+    const __half2 bias = __halves2half2(__ushort_as_half((unsigned short)0x6480), __ushort_as_half((unsigned short)0x6480));
+    uint32_t q = __byte_perm(p ^ 0x00008080u, 0x64646464u, 0x4140);
+    __half2 h = __hsub2(*reinterpret_cast<__half2*>(&q), bias);
+    return *reinterpret_cast<uint32_t*>(&h);
+  }
+}
+
+template <bool FP8>
+__global__ void __launch_bounds__(128)
+gqa_decode_q8_regs_kernel(const bf16* __restrict__ q, int64_t q_stride, const int8_t* __restrict__ kv_layer,
+                          const int* __restrict__ req_to_token, int64_t r2t_stride, const int* __restrict__ b_req_idx,
+                          const int* __restrict__ b_seq_len, bf16* __restrict__ out, int64_t out_stride,
+                          float* __restrict__ part_o, float* __restrict__ part_lse, int Hq, int Hkv, int num_splits,
+                          float scale_log2_in, const float* __restrict__ head_scales) {
+  pdl_wait();
+  constexpr int D = 128;
+  constexpr int ROW = FP8 ? D : D + kPad;          // bytes of a row in the pool
+  constexpr int CHUNKS = ROW / 16;                  // 8 or 9 (the ninth carries the int8 row's scale)
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint8_t* warp_smem = smem + (threadIdx.x >> 5) * kRegWarpBytes;
+
+  const int split = blockIdx.x;
+  const int G = Hq / Hkv;
+  const int gc = (G + 15) >> 4;
+  const int kvh = blockIdx.y / gc;
+  const int chunk_id = blockIdx.y % gc;
+  const int head0 = kvh * G + chunk_id * 16;
+  const int nrows = min(16, G - chunk_id * 16);
+  const int b = blockIdx.z;
+  const int req = b_req_idx[b];
+  const int L = b_seq_len[b];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, tig = lane & 3;
+  const float scale_log2 = FP8 ? scale_log2_in * head_scales[kvh] : scale_log2_in;
+  const float out_scale = FP8 ? head_scales[Hkv + kvh] : 1.f;
+
+  const int tiles_total = (L + 15) >> 4;
+  const int tiles_per_split = (tiles_total + num_splits - 1) / num_splits;
+  const int s0 = split * tiles_per_split * 16;
+  const int e0 = min(L, s0 + tiles_per_split * 16);
+
+  if (s0 >= e0) {
+    if (num_splits > 1) {
+      for (int r = threadIdx.x; r < nrows; r += blockDim.x)
+        part_lse[((int64_t)b * Hq + head0 + r) * num_splits + split] = -INFINITY;
+    } else {
+      for (int i = threadIdx.x; i < nrows * D; i += blockDim.x)
+        out[(int64_t)b * out_stride + (int64_t)(head0 + i / D) * D + (i % D)] = __float2bfloat16(0.f);
+    }
+    return;
+  }
+
+  // ---- Q fragments: rows g and g + 8, elements [32 tig, 32 tig + 32) of each, four per k-step ----
+  uint32_t qa[8][4];
+  {
+    uint4 r0[4], r1[4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      r0[c] = make_uint4(0, 0, 0, 0);
+      r1[c] = make_uint4(0, 0, 0, 0);
+      if (g < nrows)
+        r0[c] = bf16x8_to_f16x8(*reinterpret_cast<const uint4*>(q + (int64_t)b * q_stride + (int64_t)(head0 + g) * D +
+                                                                 tig * 32 + c * 8));
+      if (g + 8 < nrows)
+        r1[c] = bf16x8_to_f16x8(*reinterpret_cast<const uint4*>(q + (int64_t)b * q_stride +
+                                                                 (int64_t)(head0 + g + 8) * D + tig * 32 + c * 8));
+    }
+    // k-step ks uses elements 4 ks .. 4 ks + 3: half2 (4ks, 4ks+1) and half2 (4ks+2, 4ks+3)
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      const uint4& a = r0[ks >> 1];
+      const uint4& c = r1[ks >> 1];
+      qa[ks][0] = (ks & 1) ? a.z : a.x;
+      qa[ks][2] = (ks & 1) ? a.w : a.y;
+      qa[ks][1] = (ks & 1) ? c.z : c.x;
+      qa[ks][3] = (ks & 1) ? c.w : c.y;
+    }
+  }
+
+  const int ntiles = (e0 - s0 + 15) >> 4;
+  const int my_count = ntiles > warp ? (ntiles - warp + 3) / 4 : 0;
+  const int64_t r2t_base = (int64_t)req * r2t_stride;
+  const uint32_t wbase = smem_u32(warp_smem);
+
+  auto load_slots = [&](int i) {
+    int slot = -1;
+    if (i < my_count) {
+      const int p0 = s0 + (warp + 4 * i) * 16;
+      if (lane < 16 && p0 + lane < e0) slot = req_to_token[r2t_base + p0 + lane];
+    }
+    return slot;
+  };
+  int slot_ahead = load_slots(0);
+
+  auto issue = [&](int i) {
+    const int slot = slot_ahead;
+    slot_ahead = load_slots(i + 1);
+    if (i < my_count) {
+      const uint32_t sb = wbase + (i % kRegStages) * kRegStageBytes;
+      // 16 rows x CHUNKS chunks per tile; lanes walk the (row, chunk) pairs
+#pragma unroll
+      for (int it = 0; it < (16 * CHUNKS + 31) / 32; ++it) {   // every lane takes part in the shuffle
+        const int c = lane + 32 * it;
+        const bool active = c < 16 * CHUNKS;
+        const int tok = active ? c / CHUNKS : 0, ch = active ? c % CHUNKS : 0;
+        const int sl = __shfl_sync(0xffffffffu, slot, tok);
+        const bool ok = sl >= 0;
+        const int8_t* src = kv_layer + ((int64_t)(ok ? sl : 0) * (2 * Hkv) + kvh) * ROW + ch * 16;
+        if (active) {
+          cp_async16(sb + tok * kRowPitch + ch * 16, src, ok);
+          cp_async16(sb + 16 * kRowPitch + tok * kRowPitch + ch * 16, src + (int64_t)Hkv * ROW, ok);
+        }
+      }
+    }
+    cp_async_commit();
+  };
+
+  float o[16][4];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY};
+  float l_run[2] = {0.f, 0.f};
+
+#pragma unroll
+  for (int i = 0; i < kRegStages - 1; ++i) issue(i);
+
+  for (int i = 0; i < my_count; ++i) {
+    issue(i + kRegStages - 1);
+    cp_async_wait<kRegStages - 1>();
+    __syncwarp();
+    const uint8_t* kt = warp_smem + (i % kRegStages) * kRegStageBytes;
+    const uint8_t* vt = kt + 16 * kRowPitch;
+    const int p0 = s0 + (warp + 4 * i) * 16;
+
+    float s[2][4];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+      const uint8_t* row = kt + (8 * j + g) * kRowPitch + tig * 32;
+      const uint4 w0 = *reinterpret_cast<const uint4*>(row);
+      const uint4 w1 = *reinterpret_cast<const uint4*>(row + 16);
+      const uint32_t w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        uint32_t b0, b1;
+        cvt_k_word<FP8>(w[ks], b0, b1);
+        mma_f16_16816(s[j], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b0, b1);
+      }
+    }
+    float vs[2][2];
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+#pragma unroll
+      for (int c2 = 0; c2 < 2; ++c2) {
+        const int col = j * 8 + tig * 2 + c2;
+        const float ks_ = FP8 ? 1.f : *reinterpret_cast<const float*>(kt + col * kRowPitch + D);
+        vs[j][c2] = FP8 ? 1.f : *reinterpret_cast<const float*>(vt + col * kRowPitch + D);
+        const bool in = p0 + col < e0;
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          const int e = 2 * r + c2;
+          float v = in ? s[j][e] * ks_ * scale_log2 : -INFINITY;
+          s[j][e] = v;
+          mx[r] = fmaxf(mx[r], v);
+        }
+        if (!in) vs[j][c2] = 0.f;
+      }
+    }
+    float alpha[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+      float m_new = fmaxf(m_run[r], mx[r]);
+      float m_use = m_new == -INFINITY ? 0.f : m_new;
+      alpha[r] = exp2f(m_run[r] - m_use);
+      m_run[r] = m_new;
+      float rs = 0.f;
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        s[j][2 * r] = exp2f(s[j][2 * r] - m_use);
+        s[j][2 * r + 1] = exp2f(s[j][2 * r + 1] - m_use);
+        rs += s[j][2 * r] + s[j][2 * r + 1];
+      }
+      l_run[r] = l_run[r] * alpha[r] + rs;
+    }
+#pragma unroll
+    for (int nt = 0; nt < 16; ++nt) {
+      o[nt][0] *= alpha[0];
+      o[nt][1] *= alpha[0];
+      o[nt][2] *= alpha[1];
+      o[nt][3] *= alpha[1];
+    }
+    const uint32_t a0 = pack_f16x2(s[0][0] * vs[0][0], s[0][1] * vs[0][1]);
+    const uint32_t a1 = pack_f16x2(s[0][2] * vs[0][0], s[0][3] * vs[0][1]);
+    const uint32_t a2 = pack_f16x2(s[1][0] * vs[1][0], s[1][1] * vs[1][1]);
+    const uint32_t a3 = pack_f16x2(s[1][2] * vs[1][0], s[1][3] * vs[1][1]);
+    {
+      const uint8_t* base = vt + g * 16;
+      const uint4 va = *reinterpret_cast<const uint4*>(base + (2 * tig) * kRowPitch);
+      const uint4 vb = *reinterpret_cast<const uint4*>(base + (2 * tig + 1) * kRowPitch);
+      const uint4 vc = *reinterpret_cast<const uint4*>(base + (2 * tig + 8) * kRowPitch);
+      const uint4 vd = *reinterpret_cast<const uint4*>(base + (2 * tig + 9) * kRowPitch);
+      const uint32_t wa[4] = {va.x, va.y, va.z, va.w}, wb[4] = {vb.x, vb.y, vb.z, vb.w};
+      const uint32_t wc[4] = {vc.x, vc.y, vc.z, vc.w}, wd[4] = {vd.x, vd.y, vd.z, vd.w};
+#pragma unroll
+      for (int nt = 0; nt < 16; ++nt) {
+        const uint32_t b0 = cvt_v_pair<FP8>(wa[nt >> 2], wb[nt >> 2], nt & 3);
+        const uint32_t b1 = cvt_v_pair<FP8>(wc[nt >> 2], wd[nt >> 2], nt & 3);
+        mma_f16_16816(o[nt], a0, a1, a2, a3, b0, b1);
+      }
+    }
+    __syncwarp();
+  }
+  cp_async_wait<0>();
+  __syncwarp();
+
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+    l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+  }
+  static_assert(kRegWarpBytes >= 16 * 128 * 4 + 128, "warp memory too small for the merge buffer");
+  float* wo = reinterpret_cast<float*>(warp_smem);
+  float* wml = reinterpret_cast<float*>(warp_smem + 16 * D * 4);
+#pragma unroll
+  for (int nt = 0; nt < 16; ++nt) {   // column c of n-tile nt is d = 16 c + nt
+    const int d0 = (2 * tig) * 16 + nt, d1 = (2 * tig + 1) * 16 + nt;
+    wo[g * D + d0] = o[nt][0];
+    wo[g * D + d1] = o[nt][1];
+    wo[(g + 8) * D + d0] = o[nt][2];
+    wo[(g + 8) * D + d1] = o[nt][3];
+  }
+  if (tig == 0) {
+    wml[g] = m_run[0];
+    wml[g + 8] = m_run[1];
+    wml[16 + g] = l_run[0];
+    wml[16 + g + 8] = l_run[1];
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < nrows * D; idx += blockDim.x) {
+    int r = idx / D, d = idx % D;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, reinterpret_cast<const float*>(smem + w * kRegWarpBytes + 16 * D * 4)[r]);
+    float num = 0.f, den = 0.f;
+    if (M != -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float* po = reinterpret_cast<const float*>(smem + w * kRegWarpBytes);
+        const float* pml = reinterpret_cast<const float*>(smem + w * kRegWarpBytes + 16 * D * 4);
+        float sc2 = exp2f(pml[r] - M);
+        num += sc2 * po[r * D + d];
+        den += sc2 * pml[16 + r];
+      }
+    }
+    float val = den > 0.f ? num / den * out_scale : 0.f;
+    int head = head0 + r;
+    if (num_splits == 1) {
+      out[(int64_t)b * out_stride + (int64_t)head * D + d] = __float2bfloat16(val);
+    } else {
+      int64_t pi = ((int64_t)b * Hq + head) * num_splits + split;
+      part_o[pi * D + d] = val;
+      if (d == 0) part_lse[pi] = den > 0.f ? (M + log2f(den)) * kLn2 : -INFINITY;
+    }
+  }
+}
+
 template <int D>
 __global__ void __launch_bounds__(D)
 decode_merge_int8_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse, bf16* __restrict__ out,
@@ -474,6 +787,16 @@ LLB_EXPORT int llb_kv_quant_store_int8(const void* src, int64_t src_stride, void
 }
 
 namespace {
+// LLB_KV8_REGS=1 selects the register-fragment kernel for head size 128; the default widens the tile in shared memory
+bool kv8_regs_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("LLB_KV8_REGS");
+    on = (e != nullptr && e[0] == '1') ? 1 : 0;
+  }
+  return on == 1;
+}
+
 template <bool FP8>
 int launch_decode8(const void* q, int64_t q_stride, const void* kv_layer, const int* req_to_token, int64_t r2t_stride,
                    const int* b_req_idx, const int* b_seq_len, void* out, int64_t out_stride, float* part_o,
@@ -504,6 +827,25 @@ int launch_decode8(const void* q, int64_t q_stride, const void* kv_layer, const 
                  (const float*)part_lse, (bf16*)out, out_stride, Hq, num_splits);                                   \
       LLB_LAUNCH_CHECK();                                                                                           \
     }                                                                                                               \
+  }
+  if (D == 128 && kv8_regs_enabled()) {
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(gqa_decode_q8_regs_kernel<FP8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           kRegSmemBytes);
+      if (e != cudaSuccess) return (int)e;
+      configured = true;
+    }
+    launch_pdl(gqa_decode_q8_regs_kernel<FP8>, grid, dim3(128), kRegSmemBytes, st, (const bf16*)q, q_stride,
+               (const int8_t*)kv_layer, req_to_token, r2t_stride, b_req_idx, b_seq_len, (bf16*)out, out_stride,
+               part_o, part_lse, Hq, Hkv, num_splits, sl2, head_scales);
+    LLB_LAUNCH_CHECK();
+    if (num_splits > 1) {
+      launch_pdl(decode_merge_int8_kernel<128>, dim3(B * Hq), dim3(128), 0, st, (const float*)part_o,
+                 (const float*)part_lse, (bf16*)out, out_stride, Hq, num_splits);
+      LLB_LAUNCH_CHECK();
+    }
+    return LLB_OK;
   }
   if (D == 128)
     LAUNCH_DECODE8(128)
