@@ -615,19 +615,33 @@ gqa_decode_q8_regs_kernel(const bf16* __restrict__ q, int64_t q_stride, const in
     const int p0 = s0 + (warp + 4 * i) * 16;
 
     float s[2][4];
+    {
+      // four independent accumulation chains (two token groups x even / odd k-steps) instead of two of length eight
+      float acc[2][2][4];
+      uint32_t w[2][8];
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
-      const uint8_t* row = kt + (8 * j + g) * kRowPitch + tig * 32;
-      const uint4 w0 = *reinterpret_cast<const uint4*>(row);
-      const uint4 w1 = *reinterpret_cast<const uint4*>(row + 16);
-      const uint32_t w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+      for (int j = 0; j < 2; ++j) {
+        const uint8_t* row = kt + (8 * j + g) * kRowPitch + tig * 32;
+        const uint4 w0 = *reinterpret_cast<const uint4*>(row);
+        const uint4 w1 = *reinterpret_cast<const uint4*>(row + 16);
+        w[j][0] = w0.x, w[j][1] = w0.y, w[j][2] = w0.z, w[j][3] = w0.w;
+        w[j][4] = w1.x, w[j][5] = w1.y, w[j][6] = w1.z, w[j][7] = w1.w;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) acc[j][h][0] = acc[j][h][1] = acc[j][h][2] = acc[j][h][3] = 0.f;
+      }
 #pragma unroll
       for (int ks = 0; ks < 8; ++ks) {
-        uint32_t b0, b1;
-        cvt_k_word<FP8>(w[ks], b0, b1);
-        mma_f16_16816(s[j], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b0, b1);
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          uint32_t b0, b1;
+          cvt_k_word<FP8>(w[j][ks], b0, b1);
+          mma_f16_16816(acc[j][ks & 1], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b0, b1);
+        }
       }
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[j][e] = acc[j][0][e] + acc[j][1][e];
     }
     float vs[2][2];
     float mx[2] = {-INFINITY, -INFINITY};
@@ -787,12 +801,13 @@ LLB_EXPORT int llb_kv_quant_store_int8(const void* src, int64_t src_stride, void
 }
 
 namespace {
-// LLB_KV8_REGS=1 selects the register-fragment kernel for head size 128; the default widens the tile in shared memory
+// Head size 128 runs the register-fragment kernel; LLB_KV8_REGS=0 selects the kernel that widens the tile in shared
+// memory (the one head size 64 uses) for comparison.
 bool kv8_regs_enabled() {
   static int on = -1;
   if (on < 0) {
     const char* e = getenv("LLB_KV8_REGS");
-    on = (e != nullptr && e[0] == '1') ? 1 : 0;
+    on = (e == nullptr || e[0] != '0') ? 1 : 0;
   }
   return on == 1;
 }
