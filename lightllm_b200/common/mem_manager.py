@@ -242,7 +242,59 @@ class Fp8PerTensorKVMemoryManager(Fp8KVMemoryManager):
     per_tensor = True
 
 
-KV_MANAGERS = {"none": MemoryManager, "int8kv": Int8KVMemoryManager, "fp8kv_sph": Fp8KVMemoryManager,
+class CalibrationKVMemoryManager(MemoryManager):
+    """The plain pool that also records, per layer and head, the largest |K| and |V| value written: run
+    representative prompts, then `export(path)` writes the scale file the fp8 pools read (scale = amax / 448, per
+    head, K heads first).  Selected with kv_type "calibrate" (offline API); every rank of a tensor-parallel run
+    exports the heads it holds, `merge_exports` joins them."""
+
+    def __init__(self, size, dtype, head_num, head_dim, layer_num, device, always_copy: bool = False, **_):
+        super().__init__(size, dtype, head_num, head_dim, layer_num, device)
+        self.amax = torch.zeros((layer_num, 2 * head_num), dtype=torch.float32, device=device)
+
+    def layer(self, i: int):
+        from ..ops.kv_quant import CalibratingKVLayer
+
+        return CalibratingKVLayer(self.kv_buffer[i], self.head_dim, self.amax[i])
+
+    def export(self, path: str, architectures=None, per_tensor: bool = False, num_layers: Optional[int] = None):
+        import json
+
+        lim = float(torch.finfo(torch.float8_e4m3fn).max)
+        L = num_layers or self.layer_num
+        amax = self.amax[:L].float().cpu().clamp_min(1e-6)
+        if per_tensor:
+            H = self.head_num
+            amax = torch.stack([amax[:, :H].amax(1), amax[:, H:].amax(1)], dim=1)
+        scales = amax / lim
+        cfg = {"qmin": -lim, "qmax": lim, "num_layers": L, "num_head": self.head_num,
+               "quant_type": "per_tensor" if per_tensor else "per_head", "architectures": architectures,
+               "scales": scales.flatten().tolist(), "scales_shape": list(scales.shape)}
+        with open(path, "w") as f:
+            json.dump(cfg, f)
+        return cfg
+
+    @staticmethod
+    def merge_exports(paths, out_path: str):
+        """Joins per-rank per-head files (rank order) into one file for the whole model."""
+        import json
+
+        parts = [json.load(open(p)) for p in paths]
+        L = parts[0]["num_layers"]
+        ks, vs = [], []
+        for c in parts:
+            sc = torch.tensor(c["scales"]).view(*c["scales_shape"])
+            h = sc.shape[1] // 2
+            ks.append(sc[:, :h])
+            vs.append(sc[:, h:])
+        sc = torch.cat(ks + vs, dim=1)
+        cfg = dict(parts[0], num_head=sc.shape[1] // 2, scales=sc.flatten().tolist(), scales_shape=[L, sc.shape[1]])
+        with open(out_path, "w") as f:
+            json.dump(cfg, f)
+        return cfg
+
+
+KV_MANAGERS = {"none": MemoryManager, "calibrate": CalibrationKVMemoryManager, "int8kv": Int8KVMemoryManager, "fp8kv_sph": Fp8KVMemoryManager,
                "fp8kv_spt": Fp8PerTensorKVMemoryManager}
 
 

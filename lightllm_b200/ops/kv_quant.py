@@ -64,6 +64,34 @@ class Fp8KVLayer(QuantKVLayer):
         self.data[slot.long()] = q.view(torch.uint8)
 
 
+class CalibratingKVLayer(QuantKVLayer):
+    """A bf16 layer that records the largest |value| per head of everything stored into it (used to make the scale
+    file of the fp8 pools): `data` [slots + 1, 2 * Hkv, D] in the compute dtype, `amax` fp32 [2 * Hkv]."""
+
+    __slots__ = ("data", "head_dim", "amax")
+
+    def __init__(self, data: torch.Tensor, head_dim: int, amax: torch.Tensor):
+        self.data, self.head_dim, self.amax = data, head_dim, amax
+
+    @property
+    def device(self):
+        return self.data.device
+
+    @property
+    def is_cuda(self):
+        return self.data.is_cuda
+
+    def dequant_rows(self, slots, dtype):
+        return self.data.index_select(0, slots.to(self.data.device, torch.long)).to(dtype)
+
+    def dequant_all(self, dtype):
+        return self.data.to(dtype)
+
+    def store_(self, src, slot):
+        torch.maximum(self.amax, src.float().abs().amax(dim=(0, 2)), out=self.amax)
+        self.data[slot.long()] = src.to(self.data.dtype)
+
+
 class Int8KVLayer(QuantKVLayer):
     """One layer of the quantised pool: `data` int8 [slots + 1, 2 * Hkv, D + 16]."""
 
@@ -107,7 +135,7 @@ def quant_rows_reference(x: torch.Tensor):
 
 def quant_store_(layer, src: torch.Tensor, slot: torch.Tensor) -> None:
     """layer[slot[t]] = quantised src[t];  src [T, 2 * Hkv, D] (bf16 on the GPU)."""
-    if isinstance(layer, Fp8KVLayer):
+    if isinstance(layer, (Fp8KVLayer, CalibratingKVLayer)):
         return layer.store_(src, slot)
     T, rows, D = src.shape
     assert D == layer.head_dim and rows == layer.data.shape[1]
@@ -143,6 +171,9 @@ def gqa_decode(q, layer, req_to_token, b_req_idx, b_seq_len, Hq, Hkv, D, max_seq
     from . import _count, _scratch, c_int, check, f32, gqa_decode as plain, gqa_decode_num_splits, i64, kernels, ptr, \
         stream
 
+    if isinstance(layer, CalibratingKVLayer):
+        return plain(q, layer.data, req_to_token, b_req_idx, b_seq_len, Hq, Hkv, D, max_seq_len, sm_scale, out,
+                     num_splits, scratch)
     if not q.is_cuda or D not in (64, 128):
         if not q.is_cuda:
             return plain(q, layer.dequant_all(q.dtype), req_to_token, b_req_idx, b_seq_len, Hq, Hkv, D, max_seq_len,
@@ -197,6 +228,9 @@ def gqa_prefill(q, layer, req_to_token, b_req_idx, cu_q, b_ready_len, Hq, Hkv, D
                 sm_scale=None, out=None):
     from . import gqa_prefill as plain
 
+    if isinstance(layer, CalibratingKVLayer):
+        return plain(q, layer.data, req_to_token, b_req_idx, cu_q, b_ready_len, Hq, Hkv, D, max_q_len, sm_scale, out)
+
     lens = b_ready_len.to(layer.device) + (cu_q[1:] - cu_q[:-1]).to(layer.device)
     kv, r2t, idx = gather_dequant(layer, req_to_token, b_req_idx, lens.to(torch.int32), q.dtype)
     return plain(q, kv, r2t, idx, cu_q, b_ready_len, Hq, Hkv, D, max_q_len, sm_scale, out)
@@ -205,6 +239,8 @@ def gqa_prefill(q, layer, req_to_token, b_req_idx, cu_q, b_ready_len, Hq, Hkv, D
 def attention_generic(q, layer, req_to_token, b_req_idx, pos, batch_of, Hq, Hkv, D, sm_scale, *rest, **kw):
     from . import attention_generic as plain
 
+    if isinstance(layer, CalibratingKVLayer):
+        return plain(q, layer.data, req_to_token, b_req_idx, pos, batch_of, Hq, Hkv, D, sm_scale, *rest, **kw)
     dev = layer.device
     B = b_req_idx.shape[0]
     p = pos.to(dev, torch.long)

@@ -188,3 +188,37 @@ def test_model_with_fp8_pool_generates(tmp_path):
     same = sum(a == b for x, y in zip(want, got) for a, b in zip(x["token_ids"], y["token_ids"]))
     assert same >= 12                                                   # e4m3 rows: most greedy tokens survive
     assert llm.generate(prompts, sp) == got or True
+
+
+def test_calibration_run_writes_a_scale_file_the_fp8_pool_reads(tmp_path):
+    from lightllm_b200.common.mem_manager import CalibrationKVMemoryManager, Fp8KVMemoryManager
+    from lightllm_b200.engine.llm import LLM
+
+    rng = np.random.default_rng(0)
+    prompts = [rng.integers(3, 300, n).tolist() for n in (30, 55)]
+    sp = {"max_new_tokens": 6, "ignore_eos": True}
+    want = LLM(config=CFG, **KW).generate(prompts, sp)
+    llm = LLM(config=CFG, kv_type="calibrate", **KW)
+    mm = llm.model.mem_manager
+    assert isinstance(mm, CalibrationKVMemoryManager)
+    assert [o["token_ids"] for o in llm.generate(prompts, sp)] == [o["token_ids"] for o in want]   # recording changes nothing
+    assert (mm.amax > 0).all()
+    path = str(tmp_path / "cal.json")
+    cfg = mm.export(path, architectures=["LlamaForCausalLM"])
+    assert cfg["scales_shape"] == [2, 4] and cfg["quant_type"] == "per_head"
+    fp8 = LLM(config=CFG, kv_type="fp8kv_sph", kv_quant_calibration_config_path=path, **KW)
+    assert isinstance(fp8.model.mem_manager, Fp8KVMemoryManager)
+    assert torch.allclose(fp8.model.mem_manager.scales.cpu(), mm.amax.cpu() / 448.0)
+    got = fp8.generate(prompts, sp)
+    same = sum(a == b for x, y in zip(want, got) for a, b in zip(x["token_ids"], y["token_ids"]))
+    assert same >= 6          # the toy model's logits are nearly flat (all about -5.3): near-ties flip under e4m3 rows
+    # two tensor-parallel ranks, one KV head each, joined into the file of the whole model
+    a, b = str(tmp_path / "r0.json"), str(tmp_path / "r1.json")
+    m0 = CalibrationKVMemoryManager(8, torch.float32, 1, 16, 2, torch.device("cpu"))
+    m1 = CalibrationKVMemoryManager(8, torch.float32, 1, 16, 2, torch.device("cpu"))
+    m0.amax.copy_(torch.tensor([[1.0, 2.0], [3.0, 4.0]]))
+    m1.amax.copy_(torch.tensor([[5.0, 6.0], [7.0, 8.0]]))
+    m0.export(a), m1.export(b)
+    merged = CalibrationKVMemoryManager.merge_exports([a, b], str(tmp_path / "all.json"))
+    sc = torch.tensor(merged["scales"]).view(2, 4) * 448.0
+    assert torch.allclose(sc, torch.tensor([[1.0, 5.0, 2.0, 6.0], [3.0, 7.0, 4.0, 8.0]])) and merged["num_head"] == 2
