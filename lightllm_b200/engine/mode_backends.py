@@ -47,7 +47,7 @@ class TokenHealingBackend(ModelBackend):
         self._vocab_strs = None
         self.prefill_mask_func = self._mask
         self.decode_mask_func = self._mask
-        self.extra_post_req_handle_func = self._post
+        self.extra_post_req_handle_func = self._after_token
 
     def _vocab(self):
         if self._vocab_strs is None:
@@ -75,7 +75,7 @@ class TokenHealingBackend(ModelBackend):
                 m[torch.tensor(ok, device=logits.device)] = 0.0
                 logits[i] += m
 
-    def _post(self, r: InferReq, tok: int, lp: float):
+    def _after_token(self, r: InferReq, tok: int, lp: float):
         st = self._state(r)
         if st["remaining"]:
             s = self._vocab()[tok]
@@ -85,16 +85,17 @@ class TokenHealingBackend(ModelBackend):
 class XgrammarBackend(ModelBackend):
     """EBNF / JSON-schema constrained decoding through xgrammar token bitmasks."""
 
-    def __init__(self, *a, tokenizer=None, **kw):
+    def __init__(self, *a, tokenizer=None, tokenizer_info=None, **kw):
         super().__init__(*a, **kw)
         import xgrammar as xgr
 
         self.xgr = xgr
-        info = xgr.TokenizerInfo.from_huggingface(tokenizer, vocab_size=self.model.vocab)
+        info = tokenizer_info if tokenizer_info is not None else \
+            xgr.TokenizerInfo.from_huggingface(tokenizer, vocab_size=self.model.vocab)
         self.compiler = xgr.GrammarCompiler(info, max_threads=8)
         self.prefill_mask_func = self._mask
         self.decode_mask_func = self._mask
-        self.extra_post_req_handle_func = self._post
+        self.extra_post_req_handle_func = self._after_token
 
     def _matcher(self, r: InferReq):
         m = r.extra.get("xgr", False)
@@ -124,7 +125,7 @@ class XgrammarBackend(ModelBackend):
         self.xgr.apply_token_bitmask_inplace(sub, bitmask.to(logits.device))
         logits[idx] = sub
 
-    def _post(self, r: InferReq, tok: int, lp: float):
+    def _after_token(self, r: InferReq, tok: int, lp: float):
         m = self._matcher(r)
         if m is not None:
             if not m.accept_token(tok) or m.is_terminated():
