@@ -107,6 +107,8 @@ class XgrammarBackend(ModelBackend):
                 cg = self.compiler.compile_grammar(sp.guided_grammar)
             elif sp.guided_json:
                 cg = self.compiler.compile_json_schema(sp.guided_json)
+            elif sp.regular_constraint:   # regular expressions run on the same matcher (no outlines needed)
+                cg = self.compiler.compile_regex(sp.regular_constraint)
             else:
                 cg = None
             m = r.extra["xgr"] = self.xgr.GrammarMatcher(cg) if cg is not None else None
@@ -295,7 +297,12 @@ def select_backend_class(args):
     if mode == "xgrammar":
         return XgrammarBackend
     if mode == "outlines":
-        return OutlinesConstraintBackend
+        try:  # regular_constraint requests: the outlines FSM when the package is there, else the grammar matcher
+            import outlines  # noqa: F401
+
+            return OutlinesConstraintBackend
+        except Exception:
+            return XgrammarBackend
     if getattr(args, "first_token_constraint_mode", False):
         return FirstTokenConstraintBackend
     if getattr(args, "diverse_mode", False):

@@ -156,3 +156,12 @@ def test_diverse_backend_shares_the_prompt_between_samples():
     # the prompt was computed once: the siblings found all but its last token in the prefix tree
     assert llm.backend.stats["prefill_tokens"] <= 60 + 2 * 2
     assert [r.prompt_cache_len for r in group[1:]] == [59, 59]
+
+
+def test_regular_expression_constraint_on_the_grammar_matcher():
+    llm = _llm()
+    outs = llm.generate([[5, 6, 7], [8, 9, 10, 11]], {"max_new_tokens": 30, "regular_constraint": r"[A-C]{2}-[0-9]{3}"})
+    import re
+
+    for o in outs:
+        assert re.fullmatch(r"[A-C]{2}-[0-9]{3}", _text(o["token_ids"])) and o["finish_reason"] == "stop"
