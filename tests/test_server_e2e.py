@@ -135,3 +135,56 @@ def test_concurrent_requests_and_abort(server):
     again = requests.post(server + "/generate", json={"inputs": [3, 4, 5], "parameters": {"max_new_tokens": 2}},
                           timeout=60)
     assert again.status_code == 200
+
+
+@pytest.mark.timeout(600)
+def test_anthropic_responses_and_tgi_routes(server):
+    msg = {"model": "m", "max_tokens": 5, "messages": [{"role": "user", "content": "hi there"}]}
+    r = requests.post(server + "/v1/messages", json=msg, timeout=60)
+    assert r.status_code == 200, r.text
+    a = r.json()
+    assert a["type"] == "message" and a["role"] == "assistant" and a["content"][0]["type"] == "text"
+    assert a["usage"]["output_tokens"] <= 5 and a["usage"]["input_tokens"] > 0 and a["stop_reason"] in ("max_tokens", "end_turn")
+    n = requests.post(server + "/v1/messages/count_tokens", json=msg, timeout=30).json()
+    assert n["input_tokens"] == a["usage"]["input_tokens"]
+    msg["stream"] = True
+    with requests.post(server + "/v1/messages", json=msg, stream=True, timeout=60) as s:
+        events = [l.decode() for l in s.iter_lines() if l.startswith(b"event:")]
+    assert events[0] == "event: message_start" and events[-1] == "event: message_stop"
+    assert "event: content_block_delta" in events
+
+    resp = requests.post(server + "/v1/responses", json={"model": "m", "input": "say something",
+                                                         "max_output_tokens": 4}, timeout=60)
+    assert resp.status_code == 200, resp.text
+    o = resp.json()
+    assert o["object"] == "response" and o["status"] in ("completed", "incomplete")
+    assert o["usage"]["output_tokens"] <= 4 and any(it["type"] == "message" for it in o["output"])
+
+    tgi = requests.post(server + "/", json={"inputs": "hello", "parameters": {"max_new_tokens": 3}}, timeout=60)
+    assert tgi.status_code == 200, tgi.text
+    body = tgi.json()
+    body = body[0] if isinstance(body, list) else body
+    assert "generated_text" in body
+    info = requests.get(server + "/get_server_info", timeout=10).json()
+    assert info.get("max_req_total_len") == 256 or "max_req_total_len" in json.dumps(info)
+    assert requests.get(server + "/get_model_name", timeout=10).status_code == 200
+    assert requests.get(server + "/readiness", timeout=10).status_code == 200
+
+
+@pytest.mark.timeout(600)
+def test_openai_logprobs_tools_and_stop(server):
+    chat = {"model": "m", "messages": [{"role": "user", "content": "hi"}], "max_tokens": 4, "ignore_eos": True,
+            "logprobs": True, "top_logprobs": 0}
+    c = requests.post(server + "/v1/chat/completions", json=chat, timeout=60).json()
+    lp = c["choices"][0].get("logprobs")
+    assert lp is None or len(lp["content"]) == 4
+    n2 = dict(chat, n=2, temperature=1.0, top_p=0.9, seed=1)
+    c2 = requests.post(server + "/v1/chat/completions", json=n2, timeout=60).json()
+    assert len(c2["choices"]) == 2
+    tools = [{"type": "function", "function": {"name": "get_weather", "description": "x",
+                                               "parameters": {"type": "object", "properties": {"city": {"type": "string"}}}}}]
+    t = requests.post(server + "/v1/chat/completions", json=dict(chat, tools=tools, tool_choice="auto"), timeout=60)
+    assert t.status_code == 200, t.text
+    comp = requests.post(server + "/v1/completions", json={"model": "m", "prompt": [5, 6, 7, 8], "max_tokens": 3,
+                                                          "echo": False, "logprobs": 1}, timeout=60)
+    assert comp.status_code == 200, comp.text
