@@ -165,3 +165,39 @@ def test_regular_expression_constraint_on_the_grammar_matcher():
 
     for o in outs:
         assert re.fullmatch(r"[A-C]{2}-[0-9]{3}", _text(o["token_ids"])) and o["finish_reason"] == "stop"
+
+
+def test_prompt_logprobs_match_a_direct_forward_pass():
+    from lightllm_b200.common.infer_state import ModelInput
+
+    llm = LLM(config=CFG, **KW)
+    llm.args.return_all_prompt_logprobs = True
+    llm.backend.args.return_all_prompt_logprobs = True
+    prompt = np.random.default_rng(5).integers(3, 300, 70).tolist()
+    req = llm._new_req(prompt, {"max_new_tokens": 2, "ignore_eos": True, "prompt_logprobs": 0,
+                                "disable_prompt_cache": True})
+    llm.queue.extend([req])
+    from lightllm_b200.server.router.req_queue import Batch
+
+    running = Batch(0, [])
+    for _ in range(20):
+        nb = llm.queue.generate_new_batch(running)
+        if nb is not None:
+            llm.backend.add_reqs(nb.reqs)
+            running.merge(nb)
+        if not llm.backend.has_work():
+            break
+        llm.backend.step()
+        running.filter_out_finished_req()
+    got = torch.tensor(req.shm_logprobs.arr[1:70])
+    # the same numbers from one plain forward pass over the prompt
+    m = LLM(config=CFG, **KW).model
+    r = m.req_manager.alloc()
+    ids = torch.tensor(prompt)
+    mi = ModelInput(batch_size=1, total_token_num=70, max_kv_len=70, is_prefill=True,
+                    b_req_idx=torch.tensor([r], dtype=torch.int32), b_seq_len=torch.tensor([70], dtype=torch.int32),
+                    mem_indexes=m.mem_manager.alloc(70).clone(), input_ids=ids,
+                    b_ready_cache_len=torch.zeros(1, dtype=torch.int32), max_q_len=70, return_all_logits=True)
+    logp = torch.log_softmax(m.forward(mi).logits.float(), dim=-1)
+    want = logp[torch.arange(69), ids[1:]]
+    assert torch.allclose(got, want, atol=1e-4)
