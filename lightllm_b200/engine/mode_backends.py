@@ -137,16 +137,77 @@ class XgrammarBackend(ModelBackend):
 
 
 class OutlinesConstraintBackend(ModelBackend):
-    """Regex-constrained decoding with an outlines FSM (requires the `outlines` package)."""
+    """Regex-constrained decoding with an outlines finite-state index (`outlines_core`: Vocabulary, Index, Guide):
+    every request with `regular_constraint` walks its own guide; the tokens the current state allows are the only
+    ones left in the logits, and the request stops when the guide is finished.  The index of a pattern is built
+    once and shared.  Reference: mode_backend/continues_batch/outlines_constraint/impl.py."""
 
-    def __init__(self, *a, tokenizer=None, **kw):
+    def __init__(self, *a, tokenizer=None, vocabulary=None, **kw):
         super().__init__(*a, **kw)
         try:
-            from outlines.fsm.guide import RegexGuide  # noqa: F401
+            import outlines_core as oc
         except Exception as e:  # pragma: no cover
-            raise RuntimeError("--output_constraint_mode outlines needs the `outlines` package; "
+            raise RuntimeError("--output_constraint_mode outlines needs the `outlines_core` package; "
                                "use xgrammar instead") from e
-        self.tokenizer = tokenizer
+        self.oc = oc
+        self.eos = int(min(self.eos_ids)) if self.eos_ids else 0
+        self.vocabulary = vocabulary if vocabulary is not None else self._vocabulary_of(tokenizer)
+        self._indexes = {}
+        self.prefill_mask_func = self._mask
+        self.decode_mask_func = self._mask
+        self.extra_post_req_handle_func = self._after_token
+
+    def _vocabulary_of(self, tokenizer):
+        V = self.model.vocab
+        toks = tokenizer.convert_ids_to_tokens(list(range(min(V, len(tokenizer)))))
+        table = {}
+        for i, t in enumerate(toks):
+            if i in self.eos_ids or not isinstance(t, str):
+                continue
+            try:
+                text = tokenizer.convert_tokens_to_string([t])
+            except Exception:
+                text = t
+            if text:
+                table.setdefault(text, []).append(i)
+        return self.oc.Vocabulary(self.eos, table)
+
+    def _guide(self, r: InferReq):
+        g = r.extra.get("guide", False)
+        if g is False:
+            pat = r.sampling.regular_constraint
+            if pat:
+                idx = self._indexes.get(pat)
+                if idx is None:
+                    idx = self._indexes[pat] = self.oc.Index(pat, self.vocabulary)
+                g = self.oc.Guide(idx)
+            else:
+                g = None
+            r.extra["guide"] = g
+        return g
+
+    def _mask(self, reqs, logits):
+        for i, r in enumerate(reqs):
+            g = self._guide(r)
+            if g is None:
+                continue
+            allowed = torch.tensor(sorted(g.get_tokens()), dtype=torch.long, device=logits.device)
+            m = torch.full((logits.shape[1],), float("-inf"), device=logits.device)
+            m[allowed] = 0.0
+            logits[i] += m
+
+    def _after_token(self, r: InferReq, tok: int, lp: float):
+        g = self._guide(r)
+        if g is None:
+            return
+        from ..server.core.objs.req import FinishStatus
+
+        if tok == self.eos or g.is_finished():
+            r.finish_status.set_status(FinishStatus.FINISHED_STOP)
+            return
+        g.advance(tok)
+        if g.is_finished():
+            r.finish_status.set_status(FinishStatus.FINISHED_STOP)
 
 
 class RewardModelBackend(ModelBackend):
@@ -297,8 +358,8 @@ def select_backend_class(args):
     if mode == "xgrammar":
         return XgrammarBackend
     if mode == "outlines":
-        try:  # regular_constraint requests: the outlines FSM when the package is there, else the grammar matcher
-            import outlines  # noqa: F401
+        try:  # regular_constraint requests: the outlines index when the package is there, else the grammar matcher
+            import outlines_core  # noqa: F401
 
             return OutlinesConstraintBackend
         except Exception:

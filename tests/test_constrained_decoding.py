@@ -201,3 +201,25 @@ def test_prompt_logprobs_match_a_direct_forward_pass():
     logp = torch.log_softmax(m.forward(mi).logits.float(), dim=-1)
     want = logp[torch.arange(69), ids[1:]]
     assert torch.allclose(got, want, atol=1e-4)
+
+
+def test_outlines_index_regex_constraint():
+    oc = pytest.importorskip("outlines_core")
+    from lightllm_b200.engine.mode_backends import OutlinesConstraintBackend
+
+    table = {}
+    for i, t in enumerate(VOCAB):
+        if i != 2:
+            table.setdefault(t, []).append(i)
+    llm = LLM(config=CFG, **KW)
+    llm.backend = OutlinesConstraintBackend(llm.model, llm.args, vocabulary=oc.Vocabulary(2, table), is_master_in_dp=True)
+    import re
+
+    pat = r"(yes|no), [a-c]{3}\\."
+    outs = llm.generate([[5, 6, 7], [9, 10, 11, 12], [20]], [{"max_new_tokens": 30, "regular_constraint": pat},
+                                                            {"max_new_tokens": 30, "regular_constraint": pat},
+                                                            {"max_new_tokens": 5, "ignore_eos": True}])
+    for o in outs[:2]:
+        assert re.fullmatch(pat, _text(o["token_ids"])) and o["finish_reason"] == "stop"
+    assert len(outs[2]["token_ids"]) == 5
+    assert len(llm.backend._indexes) == 1                       # the index of a pattern is built once
