@@ -149,13 +149,16 @@ class Qwen3NextLM(Qwen3MoeLM):
         rows = self.max_req_num + 1
         n = len(self.lin_layers)
         self.conv_state = torch.zeros((n, rows, self.conv_dim, self.conv_k - 1), dtype=self.dtype, device=self.device)
-        self.ssm_state = torch.zeros((n, rows, self.nv, self.dk, self.dv), dtype=torch.float32, device=self.device)
+        # `--linear_att_ssm_data_type bfloat16` halves the recurrent state (updates still run in fp32)
+        ssm_dtype = torch.bfloat16 if str(self.extra.get("linear_att_ssm_data_type", "float32")) in ("bfloat16", "bf16") \
+            else torch.float32
+        self.ssm_state = torch.zeros((n, rows, self.nv, self.dk, self.dv), dtype=ssm_dtype, device=self.device)
         self._verify_snaps = {}
         self.state_snapshot_slots = int(self.extra.get("state_snapshot_slots") or 0)
         if self.state_snapshot_slots > 0:
             k = self.state_snapshot_slots
             self.conv_snap = torch.zeros((k, n, self.conv_dim, self.conv_k - 1), dtype=self.dtype, device=self.device)
-            self.ssm_snap = torch.zeros((k, n, self.nv, self.dk, self.dv), dtype=torch.float32, device=self.device)
+            self.ssm_snap = torch.zeros((k, n, self.nv, self.dk, self.dv), dtype=ssm_dtype, device=self.device)
         super()._init_mem(max_total_token_num, mem_fraction)
 
     needs_state_rollback = True   # a verification pass must be followed by `commit_verify`
@@ -175,7 +178,7 @@ class Qwen3NextLM(Qwen3MoeLM):
         for slot, (req, conv_snaps, ssm_snaps) in self._verify_snaps.items():
             b = torch.arange(req.shape[0], device=self.device)
             self.conv_state[slot].index_copy_(0, req, conv_snaps[b, n_keep - 1])
-            self.ssm_state[slot].index_copy_(0, req, ssm_snaps[b, n_keep - 1])
+            self.ssm_state[slot].index_copy_(0, req, ssm_snaps[b, n_keep - 1].to(self.ssm_state.dtype))
         self._verify_snaps.clear()
 
     # ------------------------------------------------------------------ layers
@@ -238,7 +241,7 @@ class Qwen3NextLM(Qwen3MoeLM):
             conv_state.index_copy_(0, req, new_conv.to(conv_state.dtype))
             qq, kk, vv = heads(y)
             core, new_s = la.gated_delta_step(qq, kk, vv, g, beta, ssm_state[req])
-            ssm_state.index_copy_(0, req, new_s)
+            ssm_state.index_copy_(0, req, new_s.to(ssm_state.dtype))
         elif st.extra.get("verify_pass"):
             # speculative verification: every request brings the same number of tokens; they go through the
             # recurrence one position at a time and the state after every position is kept, so that
@@ -246,7 +249,7 @@ class Qwen3NextLM(Qwen3MoeLM):
             req = st.b_req_idx.long()
             B = req.shape[0]
             qn = T // B
-            cs, ss = conv_state[req], ssm_state[req]
+            cs, ss = conv_state[req], ssm_state[req].float()
             conv_snaps, ssm_snaps, cores = [], [], []
             for t in range(qn):
                 y, cs = la.causal_conv_step(mixed[t::qn], cs, lw.conv_w)
@@ -258,7 +261,7 @@ class Qwen3NextLM(Qwen3MoeLM):
                 cores.append(o)
             self._verify_snaps[slot] = (req, torch.stack(conv_snaps, dim=1), torch.stack(ssm_snaps, dim=1))
             conv_state.index_copy_(0, req, cs)
-            ssm_state.index_copy_(0, req, ss)
+            ssm_state.index_copy_(0, req, ss.to(ssm_state.dtype))
             core = torch.stack(cores, dim=1).reshape(T, self.nv, self.dv)
         else:
             q_len, ready, reqs = st.extra["q_len_cpu"].tolist(), st.extra["ready_cpu"].tolist(), \

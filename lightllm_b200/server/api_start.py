@@ -147,7 +147,8 @@ def normal_or_p_d_start(args: StartArgs, config_override: dict = None):
     set_env_start_args(args)
     from ..utils.shm_cleanup import check_shm_size
 
-    check_shm_size(args)          # a warning when /dev/shm is smaller than the configuration wants
+    if not getattr(args, "disable_shm_warning", False):
+        check_shm_size(args)      # a warning when /dev/shm is smaller than the configuration wants
     start_core_processes(args, config_override)
     if args.health_monitor:
         from .health_monitor.manager import start_health_check_process

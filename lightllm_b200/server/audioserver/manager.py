@@ -107,7 +107,7 @@ def start_audio_process(args_dict: dict, pipe_writer=None):
         push.connect(zmq_addr(args, args.router_port))
         cache = EmbedCacheClient(args, hidden=tower.out_hidden, open_arena=True)
         mgr = AudioManager(args, tower, cache, lambda m: push.send_pyobj(m, protocol=pickle.HIGHEST_PROTOCOL),
-                           pull.recv_pyobj)
+                           pull.recv_pyobj, infer_batch_size=int(getattr(args, "audio_infer_batch_size", 0) or 8))
     except Exception:
         if pipe_writer is not None:
             pipe_writer.send(("init failed", traceback.format_exc()))

@@ -99,6 +99,9 @@ class HttpServerManager:
                 init(it, mm, sampling_params)
             n = self.tokenizer.get_image_token_length(it) if it.kind == "image" else \
                 self.tokenizer.get_audio_token_length(it)
+            cap = int(getattr(self.args, "max_image_token_count", 0) or 0)
+            if it.kind == "image" and cap > 0 and n > cap:
+                raise ValueError(f"an image needs {n} tokens, --max_image_token_count allows {cap}")
             it.token_num = n
             it.md5 = it.content_md5(salt=str(getattr(it, "grid_thwd", "")) + str(sorted(it.extra_params.items())))
             md5s.append(it.md5)

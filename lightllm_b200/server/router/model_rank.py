@@ -84,6 +84,7 @@ def _build_model_and_backend(args: StartArgs, ps):
                       quant_cfg=getattr(args, "quant_cfg", None), expert_dtype=getattr(args, "expert_dtype", None),
                       extra_kv_layers=_mtp_modules(args), kv_type=_kv_type(args),
                       state_snapshot_slots=_state_slots(args),
+                      linear_att_ssm_data_type=getattr(args, "linear_att_ssm_data_type", "float32"),
                       kv_quant_calibration_config_path=getattr(args, "kv_quant_calibration_config_path", None),
                       tpsp_mix_mode=bool(getattr(args, "enable_tpsp_mix_mode", False)))
     eos = args.eos_ids or args.eos_id or cfg.get("eos_token_id") or []

@@ -87,3 +87,15 @@ def test_concurrent_requests_with_a_shared_system_prompt():
     got = [o["token_ids"] for o in llm.generate(prompts, sp)]
     assert got == want
     assert llm.backend.state_cache.stats["hits"] >= 3
+
+
+def test_recurrent_state_kept_in_bf16():
+    rng = np.random.default_rng(4)
+    prompts = [rng.integers(3, 300, n).tolist() for n in (40, 70)]
+    sp = {"max_new_tokens": 8, "ignore_eos": True}
+    want = [o["token_ids"] for o in LLM(config=CFG, **KW).generate(prompts, sp)]
+    llm = LLM(config=CFG, linear_att_ssm_data_type="bfloat16", state_snapshot_slots=2, linear_att_hash_page_size=32, **KW)
+    assert llm.model.ssm_state.dtype == torch.bfloat16 and llm.model.ssm_snap.dtype == torch.bfloat16
+    got = [o["token_ids"] for o in llm.generate(prompts, sp)]
+    same = sum(a == b for x, y in zip(want, got) for a, b in zip(x, y))
+    assert same >= 12          # bf16 state: nearly the same greedy tokens on this toy model
