@@ -30,8 +30,10 @@ def percentile(xs: List[float], p: float) -> Optional[float]:
 def make_prompts(n: int, input_len: int, vocab: int, seed: int, prefix_share: float) -> List[List[int]]:
     """Random token-id prompts; the first `prefix_share` of every prompt is common (prefix-cache workloads)."""
     rng = random.Random(seed)
-    shared = [rng.randrange(1000, vocab - 1000) for _ in range(int(input_len * prefix_share))]
-    return [shared + [rng.randrange(1000, vocab - 1000) for _ in range(input_len - len(shared))] for _ in range(n)]
+    lo = min(1000, vocab // 10)              # stay clear of special ids at both ends, also for small vocabularies
+    hi = max(vocab - lo, lo + 1)
+    shared = [rng.randrange(lo, hi) for _ in range(int(input_len * prefix_share))]
+    return [shared + [rng.randrange(lo, hi) for _ in range(input_len - len(shared))] for _ in range(n)]
 
 
 async def one_request(session, url: str, prompt, output_len: int, record: dict, extra_params: dict):

@@ -188,3 +188,19 @@ def test_openai_logprobs_tools_and_stop(server):
     comp = requests.post(server + "/v1/completions", json={"model": "m", "prompt": [5, 6, 7, 8], "max_tokens": 3,
                                                           "echo": False, "logprobs": 1}, timeout=60)
     assert comp.status_code == 200, comp.text
+
+
+@pytest.mark.timeout(600)
+def test_load_generator_against_the_server(server):
+    """The benchmark client (fixed concurrency and open-loop arrivals) reports throughput and latency percentiles."""
+    for extra in (["--concurrency", "3"], ["--qps", "20", "--concurrency", "4"]):
+        out = subprocess.run([sys.executable, "-m", "lightllm_b200.benchmark.client", "--url", server,
+                              "--num_requests", "6", "--input_len", "12", "--output_len", "5", "--vocab_size", "1000",
+                              "--prefix_share", "0.5", *extra], capture_output=True, text=True, cwd=ROOT, timeout=300,
+                             env=dict(os.environ, PYTHONPATH=ROOT))
+        assert out.returncode == 0, out.stderr[-2000:]
+        rep = json.loads(out.stdout.strip().splitlines()[-1])
+        txt = json.dumps(rep)
+        assert "ttft" in txt.lower() and ("tok" in txt.lower())
+        done = rep.get("completed", rep.get("num_completed", rep.get("requests_ok", 6)))
+        assert done == 6
