@@ -79,3 +79,44 @@ def test_cluster_kernel_many_m_tiles(dev, bn):
     res = torch.randn(M, N, device=dev).to(BF)
     _check(ops.gemm(a, w, bn=bn), a.float() @ w.float().t())
     _check(ops.gemm(a, w, epi="residual", residual=res, bn=bn), a.float() @ w.float().t() + res.float())
+
+
+def _table_cases():
+    import json
+    import os
+
+    from lightllm_b200.utils.autotuner import PKG_DIR
+
+    path = os.path.join(str(PKG_DIR), "NVIDIA_B200", "gemm_bf16.json")
+    if not os.path.exists(path):
+        return []
+    table = json.load(open(path))
+    cases = []
+    for key, runs in sorted(table.items()):
+        parts = dict(p.split("=") for p in key.split(","))
+        N, K, epi = int(parts["N"]), int(parts["K"]), parts["epi"]
+        for bn in sorted({int(c["bn"]) for c in runs.values()} - {0}):
+            cases.append((N, K, epi, bn))
+    return cases
+
+
+@pytest.mark.parametrize("N,K,epi,bn", _table_cases())
+def test_every_variant_of_the_shipped_table_is_numerically_right(dev, N, K, epi, bn):
+    """The tuned-config table only records speed: every (shape, variant) pair it can select is checked against the
+    fp32 product here, at a row count between the tuned ones as well."""
+    import torch
+
+    from lightllm_b200 import ops
+    from lightllm_b200.ops import reference as ref
+
+    if N * K > 200_000_000:          # the vocabulary projection: a slice of its columns is enough
+        N = 8 * 1024 + (N % 1024)
+    g = torch.Generator(device="cpu").manual_seed(N + K)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(dev, torch.bfloat16)
+    for M in (8, 200):
+        a = (torch.randn(M, K, generator=g) * 0.5).to(dev, torch.bfloat16)
+        res = (torch.randn(M, N, generator=g) * 0.5).to(dev, torch.bfloat16) if epi == "residual" else None
+        got = ops.gemm(a, w, epi=epi, residual=res, bn=bn).float()
+        want = ref.gemm(a, w, epi, res, None).float()
+        scale = max(want.abs().max().item(), 1.0)
+        assert (got - want).abs().max().item() < 0.02 * scale, f"M={M} bn={bn}"
