@@ -214,3 +214,32 @@ def add_cli_args(parser: argparse.ArgumentParser) -> argparse.ArgumentParser:
 def make_argument_parser() -> argparse.ArgumentParser:
     return add_cli_args(argparse.ArgumentParser(prog="lightllm_b200.server.api_server",
                                                 formatter_class=argparse.RawTextHelpFormatter))
+
+
+# Accepted so that the reference's start scripts keep working; nothing in this package reads them.
+COMPAT_ONLY_FLAGS = (
+    "llm_prefill_att_backend", "llm_decode_att_backend", "vit_att_backend", "sampling_backend", "enable_torch_fallback",
+    "enable_triton_fallback", "disable_flashinfer_allreduce", "penalty_counter_mode", "load_way",
+    "llm_kv_quant_group_size", "enable_prefill_cudagraph", "prefill_cudagraph_max_handle_token",
+    "enable_dp_prefill_balance", "enable_dp_prompt_cache_fetch", "ep_redundancy_expert_config_path",
+    "auto_update_redundancy_expert", "enable_fused_shared_experts", "enable_return_routed_experts", "pd_trans_mode",
+    "use_config_server_to_init_nccl", "multinode_httpmanager_port", "multinode_router_gloo_port",
+    "config_server_visual_redis_port", "visual_use_proxy_mode", "visual_rpyc_port", "afs_image_embed_dir",
+    "afs_embed_capacity", "vit_quant_type", "vit_quant_cfg", "visual_tp", "audio_tp", "audio_dp", "audio_gpu_ids",
+    "visual_send_batch_size", "disable_image_resize", "enable_multimodal_url_cache", "linear_att_page_block_num",
+    "disable_linear_att_small_page_cpu_cache", "hypercorn_config", "enable_mps", "enable_monitor_auth",
+    "enable_torch_memory_saver", "enable_weight_cpu_backup")
+
+
+def compat_only_flags_in_use(args) -> list:
+    """Names of compatibility-only flags whose value differs from the default (for a start-up notice)."""
+    defaults = {}
+    for spec in FLAGS:
+        name, kind, default = spec[0].lstrip("-"), spec[1], spec[2]
+        defaults[name] = False if kind == "flag" else default
+    used = []
+    for name in COMPAT_ONLY_FLAGS:
+        if name in defaults and getattr(args, name, defaults[name]) != defaults[name]:
+            used.append(name)
+    return used
+

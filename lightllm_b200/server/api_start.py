@@ -22,6 +22,12 @@ from .core.objs.start_args import StartArgs, set_env_start_args
 
 def normalize_args(args: StartArgs, config_override: dict = None) -> StartArgs:
     a = args
+    from .api_cli import compat_only_flags_in_use
+
+    ignored = compat_only_flags_in_use(a)
+    if ignored:
+        print("[lightllm_b200] accepted for compatibility, without effect here: " +
+              ", ".join("--" + n for n in ignored), flush=True)
     assert a.tp >= 1 and a.dp >= 1 and a.tp % a.dp == 0, "--dp must divide --tp"
     assert a.tp % a.nnodes == 0, "--tp must be a multiple of --nnodes"
     if a.run_mode in ("normal", "prefill", "decode", "visual_only"):

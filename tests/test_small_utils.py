@@ -139,3 +139,14 @@ def test_token_capacity_estimate(tmp_path):
     assert kv_bytes_per_token(hybrid, 1) == 12 * 2 * 2 * 256 * 2
     r = max_total_tokens(str(tmp_path), tp=1, mem_fraction=0.5, gpu_gib=1.0)
     assert r["max_total_token_num"] == int((0.5 * 2 ** 30 - total) // (128 * 1024))
+
+
+def test_compatibility_only_flags_are_reported():
+    from lightllm_b200.server.api_cli import COMPAT_ONLY_FLAGS, FLAGS, compat_only_flags_in_use, make_argument_parser
+
+    known = {f[0].lstrip("-") for f in FLAGS}
+    assert set(COMPAT_ONLY_FLAGS) <= known
+    p = make_argument_parser()
+    assert compat_only_flags_in_use(p.parse_args(["--model_dir", "/x"])) == []
+    used = compat_only_flags_in_use(p.parse_args(["--model_dir", "/x", "--enable_mps", "--pd_trans_mode", "nixl"]))
+    assert sorted(used) == ["enable_mps", "pd_trans_mode"]
