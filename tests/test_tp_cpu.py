@@ -93,3 +93,54 @@ def test_moe_tp2_and_ep2_match_tp1(tmp_path):
     base = torch.load(tmp_path / "moe_tp1_ep0.pt")
     assert torch.load(tmp_path / "moe_tp2_ep0.pt") == base   # experts sliced along the intermediate dim
     assert torch.load(tmp_path / "moe_tp2_ep1.pt") == base   # whole experts per rank
+
+
+NEW_FAMILIES = {
+    "gemma4_text": dict(model_type="gemma4_text", hidden_size=128, intermediate_size=256, num_hidden_layers=4,
+                        num_attention_heads=4, num_key_value_heads=2, head_dim=32, global_head_dim=64,
+                        sliding_window=16, layer_types=["sliding_attention", "full_attention", "sliding_attention",
+                                                        "full_attention"],
+                        num_kv_shared_layers=2, use_double_wide_mlp=True, hidden_size_per_layer_input=16,
+                        vocab_size_per_layer_input=512, enable_moe_block=True, num_experts=4, top_k_experts=2,
+                        moe_intermediate_size=64, vocab_size=512, eos_token_id=2, tie_word_embeddings=True),
+    "qwen3_5_text": dict(model_type="qwen3_5_text", hidden_size=128, intermediate_size=256, num_hidden_layers=4,
+                         num_attention_heads=4, num_key_value_heads=2, head_dim=32, vocab_size=512, rms_norm_eps=1e-6,
+                         linear_num_value_heads=4, linear_num_key_heads=2, linear_key_head_dim=16,
+                         linear_value_head_dim=16, linear_conv_kernel_dim=4, full_attention_interval=2,
+                         eos_token_id=2, tie_word_embeddings=False),
+    "deepseek_v32": dict(model_type="deepseek_v32", hidden_size=128, intermediate_size=256, moe_intermediate_size=64,
+                         num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=4, n_routed_experts=4,
+                         n_shared_experts=1, num_experts_per_tok=2, n_group=2, topk_group=1, first_k_dense_replace=1,
+                         q_lora_rank=32, kv_lora_rank=48, qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16,
+                         vocab_size=512, routed_scaling_factor=2.5, norm_topk_prob=True, rms_norm_eps=1e-6,
+                         index_n_heads=4, index_head_dim=16, index_topk=12, eos_token_id=2),
+}
+
+
+def _family_worker(rank, world, port, out_dir, family):
+    from lightllm_b200.engine.llm import LLM
+    from lightllm_b200.parallel import dist as pdist
+
+    torch.set_num_threads(2)
+    pdist.init_distributed(world, rank, host="127.0.0.1", port=port, backend="gloo", device=torch.device("cpu"))
+    llm = LLM(config=NEW_FAMILIES[family], data_type="float32", max_total_token_num=2048, running_max_req_size=4,
+              max_req_total_len=128, batch_max_tokens=128, random_seed=0)
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(3, 512, (n,), generator=g).tolist() for n in (20, 45, 33)]
+    outs = llm.generate(prompts, {"max_new_tokens": 12, "ignore_eos": True})
+    if rank == 0:
+        torch.save({"tokens": [o["token_ids"] for o in outs], "logprobs": [o["logprobs"] for o in outs]},
+                   os.path.join(out_dir, f"{family}_tp{world}.pt"))
+    pdist.destroy()
+
+
+@pytest.mark.timeout(900)
+@pytest.mark.parametrize("family", sorted(NEW_FAMILIES))
+def test_newer_families_tp2_matches_tp1(tmp_path, family):
+    for world in (1, 2):
+        mp.spawn(_family_worker, args=(world, _free_port(), str(tmp_path), family), nprocs=world, join=True)
+    a = torch.load(tmp_path / f"{family}_tp1.pt")
+    b = torch.load(tmp_path / f"{family}_tp2.pt")
+    la, lb = np.concatenate(a["logprobs"]), np.concatenate(b["logprobs"])
+    assert a["tokens"] == b["tokens"] or np.abs(la - lb).max() < 5e-3
+    assert np.abs(la[:3] - lb[:3]).max() < 1e-3          # the first tokens of the first request agree closely
