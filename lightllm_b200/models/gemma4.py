@@ -43,7 +43,8 @@ from .weights import tp_range
 
 class Gemma4MemoryManager(MemoryManager):
     """Two pools over one slot space: [sliding layers, slots, 2 * Hkv, D] and [global layers, slots, 2 * Hg, Dg].
-    Only layers that own a cache are counted."""
+    Only layers that own a cache are counted.  To the code that moves KV (staging pages of disaggregated serving,
+    host / disk tiers) the manager looks like one layer whose row holds a token's elements of both pools."""
 
     def __init__(self, size, dtype, device, n_sliding, hkv, d, n_global, hg, dg):
         self.geo = (n_sliding, hkv, d, n_global, hg, dg)
@@ -53,16 +54,37 @@ class Gemma4MemoryManager(MemoryManager):
         ns, hkv, d, ng, hg, dg = self.geo
         self.kv_sliding = torch.zeros((ns, self.size + 1, 2 * hkv, d), dtype=self.dtype, device=self.device)
         self.kv_global = torch.zeros((ng, self.size + 1, 2 * hg, dg), dtype=self.dtype, device=self.device)
-        self.kv_buffer = None
+        self.kv_buffer = self.kv_sliding          # for code that only asks where the cache lives
+        # what everything that moves KV around sees: ONE layer whose row is a token's elements of both pools
+        self.elems_s, self.elems_g = ns * 2 * hkv * d, ng * 2 * hg * dg
+        self.layer_num = 1
+
+    def kv_row_shape(self):
+        return (self.elems_s + self.elems_g,)
 
     @staticmethod
     def bytes_per_token(dtype, n_sliding, hkv, d, n_global, hg, dg) -> int:
         return (n_sliding * 2 * hkv * d + n_global * 2 * hg * dg) * torch.empty((), dtype=dtype).element_size()
 
     def gather_pages(self, slots, out=None):
-        raise NotImplementedError("KV staging pages for models with two cache geometries are not built")
+        """[1, n, elements of both pools] staging copy of the given slots."""
+        idx = slots.to(self.device, torch.long)
+        n = idx.shape[0]
+        if out is None:
+            out = torch.empty((1, n, self.elems_s + self.elems_g), dtype=self.dtype, device=self.device)
+        row = torch.cat([self.kv_sliding[:, idx].permute(1, 0, 2, 3).reshape(n, -1),
+                         self.kv_global[:, idx].permute(1, 0, 2, 3).reshape(n, -1)], dim=1)
+        out[0, :n].copy_(row)
+        return out
 
-    scatter_pages = gather_pages
+    def scatter_pages(self, slots, pages) -> None:
+        idx = slots.to(self.device, torch.long)
+        n = idx.shape[0]
+        row = pages[0, :n].to(self.device)
+        ns, rs, ds = self.kv_sliding.shape[0], self.kv_sliding.shape[2], self.kv_sliding.shape[3]
+        ng, rg, dg = self.kv_global.shape[0], self.kv_global.shape[2], self.kv_global.shape[3]
+        self.kv_sliding[:, idx] = row[:, : self.elems_s].reshape(n, ns, rs, ds).permute(1, 0, 2, 3)
+        self.kv_global[:, idx] = row[:, self.elems_s:].reshape(n, ng, rg, dg).permute(1, 0, 2, 3)
 
 
 def _rms(x, w: Optional[torch.Tensor], eps: float):
