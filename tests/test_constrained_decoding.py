@@ -223,3 +223,22 @@ def test_outlines_index_regex_constraint():
         assert re.fullmatch(pat, _text(o["token_ids"])) and o["finish_reason"] == "stop"
     assert len(outs[2]["token_ids"]) == 5
     assert len(llm.backend._indexes) == 1                       # the index of a pattern is built once
+
+
+def test_backend_selection_from_start_arguments():
+    from types import SimpleNamespace
+
+    from lightllm_b200.engine import mode_backends as mb
+    from lightllm_b200.engine.backend import ModelBackend
+
+    def pick(**kw):
+        return mb.select_backend_class(SimpleNamespace(**kw))
+
+    assert pick() is ModelBackend
+    assert pick(run_mode="prefill") is mb.PDPrefillBackend and pick(run_mode="decode") is mb.PDDecodeBackend
+    assert pick(use_reward_model=True) is mb.RewardModelBackend
+    assert pick(token_healing_mode=True) is mb.TokenHealingBackend
+    assert pick(output_constraint_mode="xgrammar") is mb.XgrammarBackend
+    assert pick(output_constraint_mode="outlines") in (mb.OutlinesConstraintBackend, mb.XgrammarBackend)
+    assert pick(first_token_constraint_mode=True) is mb.FirstTokenConstraintBackend
+    assert pick(diverse_mode=True) is mb.DiverseBackend
