@@ -159,7 +159,11 @@ class OutlinesConstraintBackend(ModelBackend):
 
     def _vocabulary_of(self, tokenizer):
         V = self.model.vocab
-        toks = tokenizer.convert_ids_to_tokens(list(range(min(V, len(tokenizer)))))
+        try:
+            n = min(V, len(tokenizer))
+        except TypeError:
+            n = V
+        toks = tokenizer.convert_ids_to_tokens(list(range(n)))
         table = {}
         for i, t in enumerate(toks):
             if i in self.eos_ids or not isinstance(t, str):
