@@ -15,14 +15,14 @@ from lightllm_b200.utils.watchdog import MovingAverage, TimeChecker, Watchdog, r
 
 def test_watchdog_fires_only_without_heartbeat():
     hits = []
-    w = Watchdog(0.15, on_timeout=lambda: hits.append(time.monotonic()), poll=0.05).start()
+    w = Watchdog(1.0, on_timeout=lambda: hits.append(time.monotonic()), poll=0.05).start()
     for _ in range(8):
         time.sleep(0.05)
         w.heartbeat()
     assert not hits
-    time.sleep(0.4)
+    time.sleep(1.6)
     w.stop()
-    assert 1 <= len(hits) <= 3
+    assert 1 <= len(hits) <= 2
 
 
 def test_retry_and_moving_average():
