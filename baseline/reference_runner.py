@@ -83,6 +83,12 @@ def _run(args, MODELS):
     from lightllm.server.api_cli import make_argument_parser
     from lightllm.utils.envs_utils import set_env_start_args
 
+    # Under torch.distributed.run the workers inherit TORCHELASTIC_USE_AGENT_STORE=True, which makes torch's
+    # tcp:// rendezvous (the reference's init_process_group in lightllm/utils/dist_utils.py:150-155) connect EVERY
+    # rank as a client of nccl_host:nccl_port and start no server there, so all ranks wait for a store nobody
+    # serves.  The reference is normally started by its own launcher, without an elastic agent: drop the variable
+    # so that rank 0 hosts the store on the port it is given.
+    os.environ.pop("TORCHELASTIC_USE_AGENT_STORE", None)
     port = int(os.environ.get("MASTER_PORT", "29500")) + 37
     ref_args = make_argument_parser().parse_args([
         "--model_dir", model_dir, "--tp", str(world), "--data_type", "bf16",
@@ -130,36 +136,83 @@ def _run(args, MODELS):
     rng = np.random.default_rng(1234)
 
     def i32(n, v):
-        return torch.full((n,), v, dtype=torch.int32)
+        return torch.full((n,), v, dtype=torch.int32).pin_memory()
 
-    def wave():
+    # Inputs of a wave that do not depend on the prompts, staged once in pinned host memory (the other arm does
+    # the same): request rows, lengths, start offsets.  The reference's ModelInput.to_cuda() copies them with
+    # .cuda(non_blocking=True) inside forward.
+    no_mm_prefill = {}
+    pre = []
+    for s0 in range(0, conc, per_pass):
+        e0 = min(conc, s0 + per_pass)
+        B = e0 - s0
+        b_seq = i32(B, in_len)
+        pre.append((s0, e0, B, b_seq, i32(B, 0), (torch.arange(B, dtype=torch.int32) * in_len).pin_memory(),
+                    req_idx[s0:e0].clone().pin_memory(), i32(B, 0)))
+        no_mm_prefill[B] = [{"images": [], "audios": []} for _ in range(B)]
+    no_mm_decode = [{"images": [], "audios": []} for _ in range(conc)]
+    dec_req = req_idx.clone().pin_memory()
+    dec_zero = i32(conc, 0)
+    dec_seq = [i32(conc, in_len + t) for t in range(out_len)]
+    ring = [torch.empty(conc, dtype=torch.int64).pin_memory() for _ in range(4)]
+    io = {"h2d": 0, "d2h": 0, "passes": 0}
+
+    def nbytes(*ts):
+        return sum(t.numel() * t.element_size() for t in ts)
+
+    def wave(prompts_np, e2e=False):
+        """One wave.  e2e=False: sampled ids stay on the device between steps (device-timed `value`, same
+        treatment as the other arm's loop).  e2e=True: additionally every step's sampled ids are copied to pinned
+        host memory and read there before the step after next is issued (what a serving loop needs for stop
+        checks and streaming), and the copies are counted."""
         mm.free_all()
-        prompts = torch.from_numpy(rng.integers(1000, cfg["vocab_size"] - 1000, size=(conc, in_len), dtype=np.int64))
+        slots = mm.alloc(conc * total_len).view(conc, total_len)
+        slots_t = slots.t().contiguous().pin_memory()          # [position, request]
+        prompts = torch.from_numpy(prompts_np).pin_memory()
         next_ids = torch.empty(conc, dtype=torch.int64, device=dev)
-        for s in range(0, conc, per_pass):
-            e = min(conc, s + per_pass)
-            B = e - s
-            b_seq = i32(B, in_len)
-            b_ready = i32(B, 0)
-            b_q = b_seq - b_ready
+        pending = []
+        for s0, e0, B, b_seq, b_ready, start_loc, reqs_p, mtp0 in pre:
+            mem = slots[s0:e0, :in_len].reshape(-1).contiguous().pin_memory()
+            ids = prompts[s0:e0].reshape(-1)
             mi = ModelInput(batch_size=B, total_token_num=B * in_len, max_q_seq_len=in_len, max_kv_seq_len=in_len,
-                            max_cache_len=0, prefix_total_token_num=0, input_ids=prompts[s:e].reshape(-1),
-                            b_req_idx=req_idx[s:e].clone(), b_mtp_index=i32(B, 0), b_seq_len=b_seq,
-                            mem_indexes_cpu=mm.alloc(B * in_len), is_prefill=True, b_ready_cache_len=b_ready,
-                            b_prefill_start_loc=b_q.cumsum(0, dtype=torch.int32) - b_q,
-                            b_prefill_has_output_cpu=[True] * B,
-                            multimodal_params=[{"images": [], "audios": []} for _ in range(B)])
+                            max_cache_len=0, prefix_total_token_num=0, input_ids=ids, b_req_idx=reqs_p,
+                            b_mtp_index=mtp0, b_seq_len=b_seq, mem_indexes_cpu=mem, is_prefill=True,
+                            b_ready_cache_len=b_ready, b_prefill_start_loc=start_loc,
+                            b_prefill_has_output_cpu=[True] * B, multimodal_params=no_mm_prefill[B])
+            if e2e:
+                io["h2d"] += nbytes(ids, reqs_p, mtp0, b_seq, mem, b_ready, start_loc)
+                io["passes"] += 1
             out = model.forward(mi)
-            next_ids[s:e] = torch.argmax(out.logits, dim=-1)
+            next_ids[s0:e0] = torch.argmax(out.logits, dim=-1)
         for t in range(1, out_len):
             L = in_len + t
+            mem = slots_t[L - 1]
             mi = ModelInput(batch_size=conc, total_token_num=conc * L, max_q_seq_len=1, max_kv_seq_len=L,
-                            input_ids=next_ids, b_req_idx=req_idx.clone(), b_mtp_index=i32(conc, 0),
-                            b_seq_len=i32(conc, L), b_position_delta=i32(conc, 0), mem_indexes_cpu=mm.alloc(conc),
-                            is_prefill=False, multimodal_params=[{"images": [], "audios": []} for _ in range(conc)])
+                            input_ids=next_ids, b_req_idx=dec_req, b_mtp_index=dec_zero, b_seq_len=dec_seq[t],
+                            b_position_delta=dec_zero, mem_indexes_cpu=mem, is_prefill=False,
+                            multimodal_params=no_mm_decode)
             out = model.forward(mi)
             next_ids = torch.argmax(out.logits, dim=-1)
+            if e2e:
+                io["h2d"] += nbytes(dec_req, dec_zero, dec_seq[t], dec_zero, mem)
+                io["d2h"] += conc * 8
+                io["passes"] += 1
+                host = ring[t % 4]
+                host.copy_(next_ids, non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record()
+                pending.append((ev, host))
+                if len(pending) > 1:       # the previous step's ids are read while this step runs
+                    pev, ph = pending.pop(0)
+                    pev.synchronize()
+                    int(ph[0])
+        for pev, ph in pending:
+            pev.synchronize()
+            int(ph[0])
         return next_ids
+
+    def new_prompts():
+        return rng.integers(1000, cfg["vocab_size"] - 1000, size=(conc, in_len), dtype=np.int64)
 
     def barrier():
         if world > 1:
@@ -167,45 +220,56 @@ def _run(args, MODELS):
         torch.cuda.synchronize()
 
     for _ in range(args.warmup):
-        wave()
+        wave(new_prompts())
     barrier()
-    from bench import ClockSampler
+    from bench import ClockSampler, bench_config
 
     clocks = ClockSampler(dev.index or 0)
     clocks.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t0 = time.time()
     e0.record()
     for _ in range(args.steps):
-        wave()
+        wave(new_prompts())
     e1.record()
     barrier()
-    wall = time.time() - t0
     ms = e0.elapsed_time(e1)
     clock_info = clocks.stop()
+    wall = 0.0
+    if not args.skip_e2e:
+        wave(new_prompts(), e2e=True)
+        io.update(h2d=0, d2h=0, passes=0)
+        barrier()
+        t0 = time.time()
+        for _ in range(args.steps):
+            wave(new_prompts(), e2e=True)
+        barrier()
+        wall = time.time() - t0
     v = torch.tensor([ms, wall], dtype=torch.float64, device=dev)
     if world > 1:
         torch.distributed.all_reduce(v, op=torch.distributed.ReduceOp.MAX)
     ms, wall = float(v[0]), float(v[1])
     out_tokens = args.steps * conc * out_len
     if rank == 0:
-        print(json.dumps({
+        line = {
             "metric": "output tok/s per box at fixed concurrency", "value": round(out_tokens / (ms / 1e3), 1),
             "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(ms / args.steps, 2), "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform-random token ids, random-init weights",
-            "impl": "reference",
-            "config": {"model": args.model, "global_batch": conc, "seq_len": total_len, "input_len": in_len,
-                       "output_len": out_len, "parallelism": f"tp{args.gpus}",
-                       "step": "one wave of `global_batch` requests, prefill + all decode steps + greedy sampling",
-                       "l2": "inputs larger than L2 (weights and KV pool are streamed every pass)",
-                       "prefill_att_backend": type(model.prefill_att_backend).__name__,
+            "impl": "reference", "config": bench_config(args),
+            "engine": {"prefill_att_backend": type(model.prefill_att_backend).__name__,
                        "decode_att_backend": type(model.decode_att_backend).__name__},
             "clocks": clock_info,
-            "e2e": {"value": round(out_tokens / wall, 1), "unit": "tokens/s",
-                    "note": "same engine-level loop on the host clock (the reference server needs rpyc/hypercorn, "
-                            "absent offline); inputs staged from host memory by the reference's own ModelInput.to_cuda"},
-        }), flush=True)
+        }
+        if wall > 0:
+            line["e2e"] = {"value": round(out_tokens / wall, 1), "unit": "tokens/s",
+                           "h2d_bytes_per_step": round(io["h2d"] / max(io["passes"], 1), 1),
+                           "d2h_bytes_per_step": round(io["d2h"] / max(io["passes"], 1), 1),
+                           "bytes_are_per": "forward pass (prefill chunk or decode step)",
+                           "note": "the reference's engine API driven like a serving loop on the host clock (its HTTP "
+                                   "server needs rpyc / hypercorn, absent offline): every pass copies its inputs from "
+                                   "pinned host memory (ModelInput.to_cuda) and every decode step's sampled ids go "
+                                   "back to pinned host memory and are read there one step later"}
+        print(json.dumps(line), flush=True)
 
 
 def main(args, MODELS):

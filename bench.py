@@ -115,6 +115,16 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
+def bench_config(args) -> dict:
+    """The `config` entry of the result line; both arms print exactly this."""
+    return {"model": args.model, "global_batch": args.conc, "seq_len": args.in_len + args.out_len,
+            "input_len": args.in_len, "output_len": args.out_len,
+            "parallelism": f"tp{args.gpus}" + ("+tpsp" if getattr(args, "tpsp", False) else ""),
+            "batch_max_tokens": args.batch_max_tokens,
+            "step": "one wave of `global_batch` requests: chunked prefill passes, all decode steps, greedy sampling",
+            "l2": "inputs larger than L2 (weights and KV pool are streamed every pass)"}
+
+
 def reference_arm(args):
     """The unmodified reference engine (installed under baseline/_ref) on the same workload."""
     try:
@@ -289,11 +299,8 @@ def main():
             "ms_per_step": round(dev_ms / args.steps, 2), "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform-random token ids, random-init weights",
             "impl": "ours",
-            "config": {"model": args.model, "global_batch": conc, "seq_len": total_len, "input_len": in_len,
-                       "output_len": out_len, "parallelism": f"tp{args.gpus}" + ("+tpsp" if args.tpsp else ""), "step": "one wave of `global_batch` requests, prefill + all decode steps + sampling",
-                       "l2": "inputs larger than L2 (weights and KV pool are streamed every pass)",
-                       "gemm_wait_status": status},
-            "clocks": clock_info, "gpu_launches": launches,
+            "config": bench_config(args),
+            "clocks": clock_info, "gpu_launches": launches, "device_wait_status": status,
         }
         if e2e:
             line["e2e"] = {"value": round(out_tokens / e2e_s, 1), "unit": "tokens/s",
