@@ -63,6 +63,9 @@ class SlotAllocator:
         return b[:n]
 
     def alloc(self, n: int) -> torch.Tensor:
+        """`n` free slot numbers as an int32 host tensor.  The tensor is a view of one of RING reusable (pinned)
+        buffers: it is valid until RING - 1 further alloc() calls have been made; keep a copy (`.clone()`) of
+        anything needed longer."""
         out = self._buf(n)
         rc = self._lib.llb_slots_alloc(self._h, self._ct.c_int64(n), self._ct.c_void_p(out.data_ptr()))
         if rc != 0:

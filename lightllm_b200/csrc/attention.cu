@@ -514,11 +514,11 @@ LLB_EXPORT int llb_gqa_decode(const void* q, int64_t q_stride, const void* kv_la
   const float sl2 = sm_scale * kLog2e;
 #define LAUNCH_DECODE(DD)                                                                                         \
   {                                                                                                               \
-    static bool configured = false;                                                                               \
-    if (!configured) {                                                                                            \
+    static DeviceOnce configured;                                                                                    \
+    if (!configured.done()) {                                                                                            \
       int rc = set_smem(gqa_decode_kernel<DD, kDecodeStages>, decode_smem_bytes<DD>());                           \
       if (rc) return rc;                                                                                          \
-      configured = true;                                                                                          \
+      configured.set();                                                                                            \
     }                                                                                                             \
     launch_pdl(gqa_decode_kernel<DD, kDecodeStages>, grid, dim3(128), decode_smem_bytes<DD>(), st, (const bf16*)q, \
                q_stride, (const bf16*)kv_layer, req_to_token, r2t_stride, b_req_idx, b_seq_len, (bf16*)out,       \
@@ -569,11 +569,11 @@ LLB_EXPORT int llb_gqa_prefill(const void* q, int64_t q_stride, const void* kv_l
   const float sl2 = sm_scale * kLog2e;
 #define LAUNCH_PREFILL(DD)                                                                                       \
   {                                                                                                              \
-    static bool configured = false;                                                                              \
-    if (!configured) {                                                                                           \
+    static DeviceOnce configured;                                                                                   \
+    if (!configured.done()) {                                                                                           \
       int rc = set_smem(gqa_prefill_kernel<DD>, prefill_smem_bytes<DD>());                                       \
       if (rc) return rc;                                                                                         \
-      configured = true;                                                                                         \
+      configured.set();                                                                                           \
     }                                                                                                            \
     gqa_prefill_kernel<DD><<<grid, 128, prefill_smem_bytes<DD>(), st>>>(                                         \
         (const bf16*)q, q_stride, (const bf16*)kv_layer, req_to_token, r2t_stride, b_req_idx, cu_q, b_ready_len, \

@@ -826,12 +826,12 @@ int launch_decode8(const void* q, int64_t q_stride, const void* kv_layer, const 
   const float sl2 = sm_scale * kLog2e;
 #define LAUNCH_DECODE8(DD)                                                                                          \
   {                                                                                                                 \
-    static bool configured = false;                                                                                 \
-    if (!configured) {                                                                                              \
+    static DeviceOnce configured;                                                                                      \
+    if (!configured.done()) {                                                                                              \
       cudaError_t e = cudaFuncSetAttribute(gqa_decode_int8_kernel<DD, FP8>,                                         \
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, Int8DecodeSmem<DD>::TOTAL); \
       if (e != cudaSuccess) return (int)e;                                                                          \
-      configured = true;                                                                                            \
+      configured.set();                                                                                              \
     }                                                                                                               \
     launch_pdl(gqa_decode_int8_kernel<DD, FP8>, grid, dim3(128), Int8DecodeSmem<DD>::TOTAL, st, (const bf16*)q,     \
                q_stride, (const int8_t*)kv_layer, req_to_token, r2t_stride, b_req_idx, b_seq_len, (bf16*)out,       \
@@ -844,12 +844,12 @@ int launch_decode8(const void* q, int64_t q_stride, const void* kv_layer, const 
     }                                                                                                               \
   }
   if (D == 128 && kv8_regs_enabled()) {
-    static bool configured = false;
-    if (!configured) {
+    static DeviceOnce configured;     
+    if (!configured.done()) {
       cudaError_t e = cudaFuncSetAttribute(gqa_decode_q8_regs_kernel<FP8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            kRegSmemBytes);
       if (e != cudaSuccess) return (int)e;
-      configured = true;
+      configured.set();  
     }
     launch_pdl(gqa_decode_q8_regs_kernel<FP8>, grid, dim3(128), kRegSmemBytes, st, (const bf16*)q, q_stride,
                (const int8_t*)kv_layer, req_to_token, r2t_stride, b_req_idx, b_seq_len, (bf16*)out, out_stride,

@@ -13,8 +13,11 @@
 // Same arguments and result as llb_gqa_decode without the two scratch pointers.
 //
 // Limits and rules
-//   * B * Hq * num_splits must not exceed LLB_NO_ALLOC_MAX_ROWS (8192) when num_splits > 1, and D must be
-//     <= 128; larger requests return LLB_ERR_TOO_LARGE (-3) and launch nothing.
+//   * The head size D must be 64 or 128 (any other value returns LLB_ERR_UNSUPPORTED, as the regular entry
+//     point does).
+//   * With num_splits > 1, B * Hq * num_splits must not exceed LLB_NO_ALLOC_MAX_ROWS (8192); a larger request
+//     returns LLB_ERR_TOO_LARGE (-3) and launches nothing.  With num_splits == 1 the kernel writes the output
+//     directly, the scratch is not touched and B * Hq may be any size.
 //   * The scratch is (8192 * 128 + 8192) floats = 4 MiB + 32 KiB.  It is part of the library image, so
 //     every GPU that loads the library keeps these bytes until the process exits.
 //   * The first call on a device looks up the device address of the array (cudaGetSymbolAddress, with

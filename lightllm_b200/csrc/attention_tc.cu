@@ -383,11 +383,11 @@ LLB_EXPORT int llb_gqa_prefill_tc(const void* q, int64_t q_stride, const void* k
   if (B <= 0 || max_q_len <= 0) return LLB_OK;
   if (Hkv <= 0 || Hq % Hkv != 0 || (q_stride % 8) || (out_stride % 8) || ((uintptr_t)q & 15) || ((uintptr_t)out & 15))
     return LLB_ERR_BAD_ARG;
-  static bool configured = false;
-  if (!configured) {
+  static DeviceOnce configured;     
+  if (!configured.done()) {
     cudaError_t e = cudaFuncSetAttribute(gqa_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    configured.set();  
   }
   dim3 grid((max_q_len + BM - 1) / BM, Hq, B);
   gqa_prefill_tc_kernel<<<grid, THREADS, SMEM_BYTES, st>>>((const bf16*)q, q_stride, (const bf16*)kv_layer, req_to_token,

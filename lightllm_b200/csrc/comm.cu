@@ -320,11 +320,13 @@ int launch(const CommParams& p, int ranks_in_grid, int ctas, cudaStream_t st) {
                    : per <= 4 ? (const void*)tp_reduce_norm_kernel<4>
                               : (const void*)tp_reduce_norm_kernel<8>;
   // CTAs of one launch wait on CTAs of the peers' launches (two-shot), so all of them must be resident
-  static int max_resident[4] = {0, 0, 0, 0};
+  static int max_resident_tab[DeviceOnce::kMaxDevices][4] = {};
   const int slot = per <= 1 ? 0 : per <= 2 ? 1 : per <= 4 ? 2 : 3;
+  int dev = DeviceOnce::current();
+  if (dev < 0) dev = 0;
+  int* max_resident = max_resident_tab[dev];
   if (max_resident[slot] == 0) {
-    int occ = 0, dev = 0, sms = 0;
-    cudaGetDevice(&dev);
+    int occ = 0, sms = 0;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, fn, 256, 0) != cudaSuccess || occ < 1) occ = 1;
     max_resident[slot] = sms * occ;

@@ -71,6 +71,26 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
 typedef __nv_bfloat16 bf16;
 typedef __nv_bfloat162 bf162;
 
+// One-time per-device set-up (function attributes such as the dynamic shared-memory limit belong to the device
+// that was current when they were set): `static DeviceOnce once; if (!once.done()) { ...; once.set(); }`.
+struct DeviceOnce {
+  static constexpr int kMaxDevices = 64;
+  bool flags[kMaxDevices] = {};
+  static int current() {
+    int d = 0;
+    if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= kMaxDevices) return -1;
+    return d;
+  }
+  bool done() const {
+    int d = current();
+    return d >= 0 && flags[d];
+  }
+  void set() {
+    int d = current();
+    if (d >= 0) flags[d] = true;
+  }
+};
+
 __host__ __device__ __forceinline__ int cdiv(int a, int b) { return (a + b - 1) / b; }
 __host__ __device__ __forceinline__ int64_t cdiv64(int64_t a, int64_t b) { return (a + b - 1) / b; }
 

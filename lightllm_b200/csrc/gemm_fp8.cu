@@ -531,11 +531,11 @@ LLB_EXPORT int llb_gemm_fp8_block(const void* A, int64_t lda, const float* a_sca
   if (rc) return rc;
   rc = cached_tmap8(&tb, W, (uint64_t)w_rows_total, (uint64_t)K, (uint64_t)ldw);
   if (rc) return rc;
-  static bool configured = false;
-  if (!configured) {
+  static DeviceOnce configured;     
+  if (!configured.done()) {
     cudaError_t e = cudaFuncSetAttribute(gemm_fp8_block_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    configured.set();  
   }
   Fp8Params p;
   memset(&p, 0, sizeof(p));
@@ -587,11 +587,11 @@ LLB_EXPORT int llb_gemm_int8(const void* A, int64_t lda, const float* a_scale, c
   if (rc) return rc;
   rc = cached_tmap8(&tb, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw);
   if (rc) return rc;
-  static bool configured = false;
-  if (!configured) {
+  static DeviceOnce configured;     
+  if (!configured.done()) {
     cudaError_t e = cudaFuncSetAttribute(gemm_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    configured.set();  
   }
   Fp8Params p;
   memset(&p, 0, sizeof(p));

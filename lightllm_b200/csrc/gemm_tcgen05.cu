@@ -659,12 +659,12 @@ int cached_tmap(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols
 
 template <int BN, int EPI>
 int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, cudaStream_t st) {
-  static bool configured = false;
-  if (!configured) {
+  static DeviceOnce configured;     
+  if (!configured.done()) {
     cudaError_t e =
         cudaFuncSetAttribute(gemm_bf16_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<BN>());
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    configured.set();  
   }
   p.num_m_blocks = cdiv(p.M, BM);
   p.num_n_blocks = cdiv(p.N, BN);
@@ -862,12 +862,12 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 
 template <int EPI>
 int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams& p, cudaStream_t st) {
-  static bool configured = false;
-  if (!configured) {
+  static DeviceOnce configured;     
+  if (!configured.done()) {
     cudaError_t e = cudaFuncSetAttribute(gemm_bf16_pair_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          pair_smem_bytes());
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    configured.set();  
   }
   const int num_m = cdiv(p.M, 256), num_n = cdiv(p.N, PAIR_BN);
   p.num_m_blocks = num_m;
@@ -1186,12 +1186,12 @@ int launch_skinny(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams
   p.num_n_blocks = cdiv(p.N, TW * NB);
   int64_t panel_rows = kPanelBytes / ((int64_t)256 * p.K * 2);
   p.group_m = (int)(panel_rows < 2 ? 2 : (panel_rows > 32 ? 32 : panel_rows));
-  static bool configured = false;
-  if (!configured) {
+  static DeviceOnce configured;     
+  if (!configured.done()) {
     cudaError_t e = cudaFuncSetAttribute(gemm_bf16_skinny_kernel<NB, EPI, TW>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, sk_smem_bytes<NB, TW>());
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    configured.set();  
   }
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));

@@ -272,12 +272,12 @@ LLB_EXPORT int llb_mla_attention(const void* q_lat, const void* q_pe, int64_t qp
                                  const int* b_req_idx, const int* cu_q, const int* b_ready_len, const int* batch_of,
                                  void* out, int B, int T, int hq, int max_q_len, float sm_scale, cudaStream_t st) {
   if (T <= 0) return LLB_OK;
-  static bool configured = false;
-  if (!configured) {
+  static DeviceOnce configured;     
+  if (!configured.done()) {
     cudaError_t e =
         cudaFuncSetAttribute(mla_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, MLA_SMEM);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    configured.set();  
   }
   dim3 grid((hq + 15) / 16, T);
   mla_attention_kernel<<<grid, 256, MLA_SMEM, st>>>((const bf16*)q_lat, (const bf16*)q_pe, qpe_st, qpe_sh,

@@ -181,9 +181,12 @@ class ModelBackend:
             if req.finish_status.is_finished():
                 finished.append(req)
                 continue
-            if req.infer_aborted or req.stop_str_matched or req.shm_req.is_aborted:
-                if req.shm_req.is_aborted:
-                    req.infer_aborted = True
+            # `infer_aborted` is only ever set by abort(), which the rank process calls when an AbortedReqCmd
+            # arrives through the mailbox whose generation all tensor-parallel ranks agree on.  The shared
+            # request's own `is_aborted` flag is written by the HTTP worker at an arbitrary moment: ranks whose
+            # loops are a step apart would drop the request at different steps and run batches of different
+            # sizes (reference: base_backend.py:543-546 sets infer_aborted from the command as well).
+            if req.infer_aborted or req.stop_str_matched:
                 self._finish_without_token(req)
                 finished.append(req)
                 continue
@@ -257,6 +260,7 @@ class ModelBackend:
         for req in list(self.ctx.requests.values()):
             if req.finish_status.is_finished() and req not in finished:
                 finished.append(req)
+        finished = [r for r in finished if not r.retire_hold]   # e.g. prompt KV still being sent to a decode node
         for req in finished:
             self.ctx.remove_req(req)
         return {"kind": kind, "finished": finished, "tokens": n_tok}
@@ -475,7 +479,7 @@ class ModelBackend:
             r.update_finish_status(self.eos_ids, self.args.max_req_total_len)
             if self.extra_post_req_handle_func is not None:
                 self.extra_post_req_handle_func(r, tok, float(lps_np[i]))
-            if self.is_master_in_dp:
+            if self.is_master_in_dp and not r.retire_hold:
                 if r.cur_output_len == 1:
                     r.shm_req.first_token_time = now
                 r.publish()

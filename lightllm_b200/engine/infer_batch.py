@@ -69,6 +69,7 @@ class InferReq:
         self.stop_str_matched = False
         self.paused = False
         self.inflight = 0                      # decode steps launched whose token has not been read back yet
+        self.retire_hold = False               # finished but not to be published / removed yet (KV transfer running)
         self.filter_mark = False
         self.out_token_counter: Dict[int, int] = {}
         self.cumlogprob = 0.0

@@ -9,6 +9,7 @@ DiversehBackend) and model_rpc.py:72-99 (selection).
 from __future__ import annotations
 
 import os
+import time
 from typing import List
 
 import numpy as np
@@ -273,33 +274,85 @@ class DiverseBackend(ModelBackend):
 
 class PDPrefillBackend(ModelBackend):
     """Prefill node of a disaggregated deployment: when a request's first token is sampled, its prompt KV is
-    streamed to the paired decode rank (same tp rank) before the request is retired.
-    Reference: mode_backend/pd/prefill_node_impl/prefill_impl.py:50-92."""
+    streamed to the paired decode rank (same tp rank) by a worker thread while the inference loop goes on with
+    other requests.  The request stays in the table (slots referenced, first token not yet published) until the
+    transfer has ended on every tensor-parallel rank; a failed transfer ends it with FINISHED_ERROR.
+    Reference: mode_backend/pd/prefill_node_impl/prefill_impl.py:50-92 (its transfers run in a separate
+    kv-move process)."""
 
-    def __init__(self, *a, tp_rank: int = 0, page_tokens: int = 1024, **kw):
+    MAX_SETTLE = 64   # transfers whose outcome the ranks compare per step
+
+    def __init__(self, *a, tp_rank: int = 0, page_tokens: int = 1024, cpu_group=None, tp_size: int = 1, **kw):
         super().__init__(*a, **kw)
         from .pd import KVSender
 
         self.tp_rank = tp_rank
+        self.cpu_group, self.tp_size = cpu_group, tp_size
         self.sender = KVSender(self.model.mem_manager, page_tokens)
         self.extra_post_req_handle_func = self._ship
+        self._sending = []      # [(InferReq, token, logprob)] in submission order (the same on every rank)
+        self._outcome = {}      # req_id -> (ok, message) as seen by this rank's worker
 
     def _ship(self, r: InferReq, tok: int, lp: float):
         params = r.shm_req.sample_params.pd_kv_trans_params.to_dict()
         if not params or r.cur_output_len != 1:
             return
         n = r.cur_kv_len
-        try:
-            ids = r.shm_req.shm_prompt_ids.arr[:n].tolist()
-            self.sender.send_request((params["peer_ip"], params["peer_port"] + self.tp_rank), params["master_req_id"],
-                                     ids, torch.from_numpy(np.ascontiguousarray(r.slots[:n])), (tok, lp))
-        except Exception:
-            import traceback
+        ids = r.shm_req.shm_prompt_ids.arr[:n].tolist()
+        r.retire_hold = True
+        self._sending.append(r)
+        self.sender.submit((params["peer_ip"], params["peer_port"] + self.tp_rank), params["master_req_id"], ids,
+                           torch.from_numpy(np.ascontiguousarray(r.slots[:n])), (tok, lp), tag=r.req_id)
 
-            traceback.print_exc()
-            from ..server.core.objs.req import FinishStatus
+    def _settle_sends(self):
+        """Ends the requests whose transfer is over.  With tensor parallelism every rank sends its own KV shard;
+        a request is released on the step at which ALL ranks have an outcome for it (one small host all-reduce
+        per step while transfers are pending), so the ranks' pools and schedules stay identical."""
+        if not self._sending:
+            return
+        for tag, ok, msg in self.sender.poll_done():
+            self._outcome[tag] = (ok, msg)
+        head = self._sending[: self.MAX_SETTLE]
+        state = torch.zeros(self.MAX_SETTLE, dtype=torch.int32)     # 0 pending, 1 sent, 2 failed
+        for i, r in enumerate(head):
+            o = self._outcome.get(r.req_id)
+            if o is not None:
+                state[i] = 1 if o[0] else 2
+        if self.tp_size > 1 and self.cpu_group is not None:
+            import torch.distributed as dist
 
-            r.finish_status.set_status(FinishStatus.FINISHED_ERROR)
+            lo, hi = state.clone(), state.clone()
+            dist.all_reduce(lo, op=dist.ReduceOp.MIN, group=self.cpu_group)   # 0 while any rank is still sending
+            dist.all_reduce(hi, op=dist.ReduceOp.MAX, group=self.cpu_group)   # 2 if any rank failed
+            state = torch.where(lo == 0, lo, hi)
+        keep = []
+        for i, r in enumerate(head):
+            st = int(state[i])
+            if st == 0:
+                keep.append(r)
+                continue
+            o = self._outcome.pop(r.req_id, None)
+            if st == 2:
+                from ..server.core.objs.req import FinishStatus
+
+                print(f"[pd prefill] KV transfer of request {r.req_id} failed: {o[1] if o else 'on another rank'}",
+                      flush=True)
+                r.finish_status.set_status(FinishStatus.FINISHED_ERROR)
+            r.retire_hold = False
+            if self.is_master_in_dp:
+                r.shm_req.first_token_time = time.time()
+                r.publish()
+        self._sending = keep + self._sending[self.MAX_SETTLE:]
+
+    def has_work(self) -> bool:
+        return super().has_work() or bool(self._sending)
+
+    def step(self) -> dict:
+        self._settle_sends()
+        res = super().step()
+        if res["kind"] == "idle" and self._sending:
+            time.sleep(0.001)   # nothing to compute: wait for the worker without spinning
+        return res
 
 
 class PDDecodeBackend(ModelBackend):
@@ -308,7 +361,7 @@ class PDDecodeBackend(ModelBackend):
     `on_kv_done(group_req_id, ok)` is called on the master rank for each completed transfer.
     Reference: mode_backend/pd/decode_node_impl/decode_impl.py, up_status.py."""
 
-    def __init__(self, *a, tp_rank: int = 0, host: str = "0.0.0.0", kv_port: int = 0, page_tokens: int = 1024,
+    def __init__(self, *a, tp_rank: int = 0, host: str = "127.0.0.1", kv_port: int = 0, page_tokens: int = 1024,
                  page_num: int = 16, cpu_group=None, tp_size: int = 1, on_kv_done=None, **kw):
         super().__init__(*a, **kw)
         from .pd import KVReceiver

@@ -50,6 +50,8 @@ FLAGS = [
     ("--config_server_visual_redis_port", int, None, "redis port used by remote visual encoders"),
     ("--pd_kv_page_num", int, 16, "staging pages of the KV mover"),
     ("--pd_kv_page_size", int, 1024, "tokens per staging page"),
+    ("--pd_kv_auth_key", str, None, "shared secret of the KV-transfer control connections; give every prefill and "
+     "decode node of one deployment the same value (or set LLB_PD_KV_AUTHKEY)"),
     # ---- model ----
     ("--model_name", str, "default_model_name", "name reported by /v1/models"),
     ("--model_owner", str, None, "owner reported by /v1/models"),

@@ -80,6 +80,13 @@ def normalize_args(args: StartArgs, config_override: dict = None) -> StartArgs:
         assert a.mtp_step > 0 and a.mtp_draft_model_dir, "mtp needs --mtp_step and --mtp_draft_model_dir"
     if a.run_mode in ("prefill", "decode"):
         assert a.pd_master_ip and a.pd_master_port, "PD nodes need --pd_master_ip/--pd_master_port"
+        # inherited by the model-rank processes (engine/pd/kv_transport.py:auth_key)
+        os.environ["LLB_PD_MASTER_ADDR"] = f"{a.pd_master_ip}:{a.pd_master_port}"
+        if getattr(a, "pd_kv_auth_key", None):
+            os.environ["LLB_PD_KV_AUTHKEY"] = a.pd_kv_auth_key
+        elif not os.environ.get("LLB_PD_KV_AUTHKEY"):
+            print("[start] no --pd_kv_auth_key: the KV-transfer links are keyed by the pd_master address only",
+                  flush=True)
     # ---- names and ports ----
     if a.unique_server_name is None:
         a.unique_server_name = f"llb{os.getpid()}x{uuid.uuid4().hex[:6]}"

@@ -106,7 +106,7 @@ def _build_model_and_backend(args: StartArgs, ps):
     backend_cls = select_backend_class(args)
     kw = {}
     if args.run_mode == "prefill":
-        kw = dict(tp_rank=ps.tp_rank, page_tokens=args.pd_kv_page_size)
+        kw = dict(tp_rank=ps.tp_rank, page_tokens=args.pd_kv_page_size, cpu_group=ps.cpu_group, tp_size=ps.tp_size)
     elif args.run_mode == "decode":
         on_done = None
         if ps.tp_rank == 0 and args.pd_kv_status_port:

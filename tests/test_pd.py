@@ -157,6 +157,9 @@ def _pool(seed):
     return mm
 
 
+NTOK = 100   # 7 pages of 16 tokens: more pages than the slot allocator's ring of host buffers is deep
+
+
 def _recv_proc(q_port, q_out):
     from lightllm_b200.engine.pd import KVReceiver
     from lightllm_b200.engine.radix_cache import RadixCache
@@ -167,13 +170,34 @@ def _recv_proc(q_port, q_out):
     q_port.put(rx.port)
     import time
 
+    # a stranger without the deployment's key is turned away and the listener keeps serving
+    import os
+    from multiprocessing.connection import Client
+
+    try:
+        Client(("127.0.0.1", rx.port), authkey=b"not the key")
+        raise SystemExit("a wrong key was accepted")
+    except Exception as e:
+        assert "AuthenticationError" in type(e).__name__ or isinstance(e, (EOFError, OSError)), e
+
     done, t0 = [], time.time()
+    scratch = []
     while len(done) < 2 and time.time() - t0 < 60:
         done += rx.drain(cache)
+        # what a busy decode node does between two drains: a few decode-step allocations (they rotate the
+        # allocator's small ring of host buffers, which an uncopied slot list of an earlier page would alias)
+        for _ in range(5):
+            scratch.append(mm.alloc(1).clone())
+        if len(scratch) > 20:
+            for sl in scratch:
+                mm.free(sl)
+            scratch = []
         time.sleep(0.01)
+    for sl in scratch:
+        mm.free(sl)
     res = {}
     for gid, ok, first in done:
-        ids = np.arange(100 * gid, 100 * gid + 40, dtype=np.int64)
+        ids = np.arange(100 * gid, 100 * gid + NTOK, dtype=np.int64)
         node, n, slots = cache.match_prefix(ids, update_refs=False)
         res[gid] = (ok, first, n, mm.gather_pages(torch.from_numpy(np.asarray(slots))).numpy().copy())
     q_out.put(res)
@@ -193,17 +217,60 @@ def test_kv_transport_gloo():
         tx = KVSender(mm, page_tokens=16)
         sent = {}
         for gid in (1, 2):
-            slots = mm.alloc(40)
-            ids = list(range(100 * gid, 100 * gid + 40))
-            assert tx.send_request(("127.0.0.1", port), gid, ids, slots, first_token=(7, -0.5)) == 3
+            slots = mm.alloc(NTOK).clone()
+            ids = list(range(100 * gid, 100 * gid + NTOK))
+            if gid == 1:
+                assert tx.send_request(("127.0.0.1", port), gid, ids, slots, first_token=(7, -0.5)) == 7
+            else:   # the worker-thread path the prefill backend uses
+                tx.submit(("127.0.0.1", port), gid, ids, slots, first_token=(7, -0.5), tag="second")
+                import time
+
+                t0, got = time.time(), []
+                while not got and time.time() - t0 < 60:
+                    got = tx.poll_done()
+                    time.sleep(0.01)
+                assert got == [("second", True, None)]
             sent[gid] = mm.gather_pages(slots).clone()
         res = q_out.get(timeout=60)
         tx.close()
         for gid in (1, 2):
             ok, first, n, kv = res[gid]
-            assert ok and first == (7, -0.5) and n == 40
+            assert ok and first == (7, -0.5) and n == NTOK
             assert np.array_equal(kv, sent[gid].numpy())
     finally:
         p.join(timeout=30)
         if p.is_alive():
             p.kill()
+
+
+def test_kv_sender_peer_that_never_accepts():
+    """A decode node that is gone (a port nobody serves) or hangs (a socket that never answers the challenge) costs
+    the worker thread a bounded wait and ends the request with an error; the caller is never blocked."""
+    import socket
+    import time
+
+    from lightllm_b200.engine.pd import KVSender
+
+    mm = _pool(3)
+    tx = KVSender(mm, page_tokens=16, connect_timeout_s=1.0)
+    silent = socket.socket()
+    silent.bind(("127.0.0.1", 0))
+    silent.listen(1)           # accepts at the TCP level, never speaks
+    dead = socket.socket()
+    dead.bind(("127.0.0.1", 0))
+    dead_port = dead.getsockname()[1]
+    dead.close()               # nobody listens here any more
+    slots = mm.alloc(20).clone()
+    t0 = time.time()
+    tx.submit(("127.0.0.1", silent.getsockname()[1]), 1, list(range(20)), slots, tag="silent")
+    tx.submit(("127.0.0.1", dead_port), 2, list(range(20)), slots, tag="dead")
+    tx.submit(("127.0.0.1", dead_port), 3, list(range(20)), slots, tag="dead-again")
+    assert time.time() - t0 < 0.5      # submit never waits
+    got = []
+    while len(got) < 3 and time.time() - t0 < 30:
+        got += tx.poll_done()
+        time.sleep(0.02)
+    assert [g[0] for g in got] == ["silent", "dead", "dead-again"] and not any(g[1] for g in got)
+    assert "failed" in got[2][2] and time.time() - t0 < 10   # the second try on a broken peer fails at once
+    tx.close()
+    silent.close()

@@ -144,3 +144,47 @@ def test_newer_families_tp2_matches_tp1(tmp_path, family):
     la, lb = np.concatenate(a["logprobs"]), np.concatenate(b["logprobs"])
     assert a["tokens"] == b["tokens"] or np.abs(la - lb).max() < 5e-3
     assert np.abs(la[:3] - lb[:3]).max() < 1e-3          # the first tokens of the first request agree closely
+
+
+def _abort_worker(rank, world, port, out_dir):
+    """The HTTP worker raises `is_aborted` in the shared request at an arbitrary moment; tensor-parallel ranks
+    whose loops are a step apart see it at different steps.  Only the abort command (delivered to all ranks at
+    the same point of their schedules) may drop the request."""
+    from lightllm_b200.engine.llm import LLM
+    from lightllm_b200.parallel import dist as pdist
+
+    torch.set_num_threads(2)
+    pdist.init_distributed(world, rank, host="127.0.0.1", port=port, backend="gloo", device=torch.device("cpu"))
+    llm = LLM(config=TINY, data_type="float32", max_total_token_num=4096, running_max_req_size=8,
+              max_req_total_len=128, batch_max_tokens=256, random_seed=0)
+    be = llm.backend
+    reqs = [llm._new_req(p, {"max_new_tokens": 12, "ignore_eos": True}) for p in _prompts()[:3]]
+    be.add_reqs(reqs)
+    victim = reqs[1]
+    log = []
+    for step in range(40):
+        if not be.has_work():
+            break
+        if step == 3 + rank:               # rank 0 sees the flag one step earlier than rank 1
+            victim.is_aborted = True
+        if step == 6:                      # the command reaches both ranks at the same step
+            be.abort(victim.request_id)
+        res = be.step()
+        log.append((res["kind"], res["tokens"], sorted(r.req_id for r in res["finished"])))
+    torch.save({"log": log, "tokens": [r.get_output_ids() for r in reqs],
+                "reasons": [r.finish_status.get_finish_reason() for r in reqs]},
+               os.path.join(out_dir, f"abort_rank{rank}.pt"))
+    pdist.destroy()
+
+
+@pytest.mark.timeout(600)
+def test_abort_flag_seen_at_different_steps_keeps_ranks_in_step(tmp_path):
+    mp.spawn(_abort_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    a, b = torch.load(tmp_path / "abort_rank0.pt"), torch.load(tmp_path / "abort_rank1.pt")
+    assert a["log"] == b["log"]                      # identical schedules, step by step
+    assert a["tokens"] == b["tokens"]
+    assert a["reasons"][1] == "abort" and a["reasons"][0] == a["reasons"][2] == "length"
+    kinds = [k for k, _, _ in a["log"]]
+    first_without = next(i for i, (_, _, fin) in enumerate(a["log"]) if fin)
+    assert first_without == 6                        # dropped on the step of the command, not of the flag
+    assert len(a["tokens"][0]) == 12 and "decode" in kinds

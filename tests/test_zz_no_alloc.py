@@ -69,3 +69,17 @@ def test_no_alloc_rejects_oversized_request(dev):
     q, kv, r2t, b_req, b_len = _case(dev, lens, Hq, Hkv, D, 2)
     rc, _ = _call_no_alloc(q, kv, r2t, b_req, b_len, Hq, Hkv, D, 8)
     assert rc == -3
+
+
+def test_no_alloc_head_size_64_and_single_split(dev):
+    """Head size 64 goes through the same scratch; one split needs none, so even a batch with more rows than
+    the scratch holds is served."""
+    Hq, Hkv, D = 16, 4, 64
+    for lens, splits, seed in (([300, 41, 1200], 4, 3), ([50] * 600, 1, 4)):   # 600 * 16 = 9600 rows, one split
+        q, kv, r2t, b_req, b_len = _case(dev, lens, Hq, Hkv, D, seed)
+        want = ops.gqa_decode(q, kv, r2t, b_req, b_len, Hq, Hkv, D, max(lens), num_splits=splits)
+        rc, got = _call_no_alloc(q, kv, r2t, b_req, b_len, Hq, Hkv, D, splits)
+        assert rc == 0
+        torch.cuda.synchronize()
+        err = (got.float() - want.float()).abs().max().item()
+        assert err < 2e-2, f"max abs err {err}"
