@@ -207,14 +207,14 @@ def main():
                             input_ids=ids_all[s:e].reshape(-1), b_ready_cache_len=zero_p, b_q_len=len_p,
                             max_q_len=in_len)
             out = model.forward(mi)
-            tok, _ = ops.sample(out.logits)
+            tok, _ = ops.sample(out.logits_any)
             ops.scatter_next_token_(nxt, tok, dev_req[s:e])
         for t in range(1, out_len):
             L = in_len + t
             mi = ModelInput(batch_size=conc, total_token_num=conc * L, max_kv_len=L, is_prefill=False, b_req_idx=b_req,
                             b_seq_len=seq_all[t], mem_indexes=slots_t[L - 1])
             out = model.forward(mi)
-            tok, _ = ops.sample(out.logits)
+            tok, _ = ops.sample(out.logits_any)
             ops.scatter_next_token_(nxt, tok, dev_req)
         return tok
 

@@ -1,8 +1,8 @@
 """CUDA-event timing of the attention kernels on Llama-3-8B head geometry.
 
-    python -m lightllm_b200.utils.attn_bench [--B 16 --len 1024 --reps 5]            # causal prefill (tcgen05 kernel;
+    python -m lightllm_b200.benchmark.attn_bench [--B 16 --len 1024 --reps 5]            # causal prefill (tcgen05 kernel;
                                                                                       # LLB_ATTN_TC=0: mma.sync kernel)
-    python -m lightllm_b200.utils.attn_bench --decode --B 256 --len 1024 [--int8kv]  # split-KV decode, bf16 or int8 pool
+    python -m lightllm_b200.benchmark.attn_bench --decode --B 256 --len 1024 [--int8kv]  # split-KV decode, bf16 or int8 pool
 """
 from __future__ import annotations
 

@@ -2,7 +2,7 @@
 standalone add+RMSNorm kernel, over message sizes, grid sizes and both algorithms.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
-        --master-port 29621 -m lightllm_b200.utils.comm_bench
+        --master-port 29621 -m lightllm_b200.benchmark.comm_bench
 
 CUDA events on the launching stream, 3 warm-up and 30 timed calls back to back, max over ranks.  Both sides
 include their host launch cost (two launches for the NCCL side, one for the fused kernel).

@@ -1,7 +1,7 @@
 """CUDA-event timing of the tcgen05 GEMM against torch.matmul (cuBLAS) on the per-rank shapes of
 the Llama-3-8B / 70B layers.  L2 is flushed (256 MB memset) between timed iterations; median of 10.
 
-    python -m lightllm_b200.utils.gemm_bench [--quick]
+    python -m lightllm_b200.benchmark.gemm_bench [--quick]
 """
 from __future__ import annotations
 
@@ -101,6 +101,8 @@ def main():
     ap.add_argument("--only", default=None, help="M,N,K: run just this shape (3 plain launches of --bn, for profilers)")
     ap.add_argument("--bn", type=int, default=0, help="kernel selector passed to ops.gemm with --only")
     ap.add_argument("--fp8", action="store_true", help="block-scaled e4m3 GEMM on DeepSeek-V3 shapes vs the bf16 kernels")
+    ap.add_argument("--tp", type=int, default=0, help="with --decode: the per-rank Llama-3-8B layer shapes of a "
+                                                      "tensor-parallel split over this many ranks (M = 256)")
     a = ap.parse_args()
     dev = torch.device("cuda")
     if a.fp8:
@@ -123,6 +125,10 @@ def main():
         shapes = shapes[:9]
     if a.decode:
         shapes = [sh for sh in shapes if sh[0] <= 256] + [(32, 6144, 4096), (32, 28672, 4096), (8, 4096, 14336)]
+    if a.decode and a.tp > 1:
+        t = a.tp
+        shapes = [(256, 6144 // t, 4096), (256, 4096, 4096 // t), (256, 28672 // t, 4096), (256, 4096, 14336 // t),
+                  (256, 128256 // t, 4096)]
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     for M, N, K in shapes:
         reps = a.reps

@@ -1,6 +1,6 @@
 """CUDA-event timings of the non-GEMM hot kernels on serving shapes, with their roofline fractions.
 
-    python -m lightllm_b200.utils.kernel_bench [--peaks MEASURED_PEAKS.json]
+    python -m lightllm_b200.benchmark.kernel_bench [--peaks MEASURED_PEAKS.json]
 
 Each kernel: 3 warm-up launches, then the median of 10 samples of 4 back-to-back launches (operands larger than
 L2 or rotated, 256 MB L2 flush before every sample).  Bytes / FLOPs are the algorithmic ones of the op.

@@ -2,7 +2,7 @@
 one prefill pass and a few decode steps, launched eagerly (no CUDA graph) so that every kernel
 shows up as its own launch.
 
-    python -m lightllm_b200.utils.profile_step --layers 4 --batch 256 --ctx 1024 --decode-steps 3
+    python -m lightllm_b200.benchmark.profile_step --layers 4 --batch 256 --ctx 1024 --decode-steps 3
 """
 from __future__ import annotations
 
@@ -48,7 +48,7 @@ def main():
                         input_ids=torch.randint(0, a.vocab, (n * L,), generator=g),
                         b_ready_cache_len=torch.zeros(n, dtype=torch.int32), max_q_len=L)
         out = m.forward(mi)
-        tok, _ = ops.sample(out.logits)
+        tok, _ = ops.sample(out.logits_any)
         ops.scatter_next_token_(m.req_manager.req_to_next_token_ids, tok, reqs[s:e].to(dev))
     torch.cuda.synchronize()
     for t in range(a.decode_steps):
@@ -56,7 +56,7 @@ def main():
                         b_req_idx=reqs.clone(), b_seq_len=torch.full((B,), L + t + 1, dtype=torch.int32),
                         mem_indexes=slots[:, L + t].clone())
         out = m.forward(mi)
-        tok, _ = ops.sample(out.logits)
+        tok, _ = ops.sample(out.logits_any)
         ops.scatter_next_token_(m.req_manager.req_to_next_token_ids, tok, reqs.to(dev))
     torch.cuda.synchronize()
     print("profile_step done; gemm status", int(ops.gemm_status(dev).item()))

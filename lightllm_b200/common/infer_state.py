@@ -35,10 +35,66 @@ class ModelInput:
     verify_pass: bool = False            # speculative decoding: a pass whose later positions may be rolled back
 
 
-@dataclass
+class ShardedLogits:
+    """Vocabulary-parallel logits: this rank holds columns [v0, v0 + local.shape[1]) of the [rows, vocab] matrix.
+
+    With tensor parallelism the lm_head is split over the vocabulary.  Gathering the full fp32 matrix on every
+    rank costs rows x vocab x 4 bytes of all-gather per step (131 MB at batch 256 for a 128k vocabulary); a greedy
+    step only needs each shard's (max, arg-max, sum of exponentials) per row, a few KB.  `greedy()` does that;
+    `full()` is the gather for everything that needs the whole row (random sampling, penalties, token masks,
+    prompt logprobs).  Reference: lightllm/models/llama/layer_infer/post_layer_infer.py:88-117 always gathers.
+    """
+
+    def __init__(self, local: torch.Tensor, tp, v0: int, vocab: int):
+        self.local, self.tp, self.v0, self.vocab = local, tp, int(v0), int(vocab)
+        self._full = None
+
+    @property
+    def shape(self):
+        return (self.local.shape[0], self.vocab)
+
+    @property
+    def device(self):
+        return self.local.device
+
+    def __getitem__(self, rows):
+        assert not isinstance(rows, tuple), "only rows of vocabulary-parallel logits can be selected"
+        return ShardedLogits(self.local[rows], self.tp, self.v0, self.vocab)
+
+    def index_select(self, dim, index):
+        assert dim == 0
+        return ShardedLogits(self.local.index_select(0, index), self.tp, self.v0, self.vocab)
+
+    def full(self) -> torch.Tensor:
+        if self._full is None:
+            self._full = self.tp.gather_logits(self.local)
+        return self._full
+
+    def greedy(self):
+        """(ids int64 [rows], logprob fp32 [rows]) of the arg-max token, identical on every rank."""
+        import torch.distributed as dist
+
+        from .. import ops
+
+        part = ops.greedy_partials(self.local, self.v0)
+        B = part.shape[0]
+        parts = torch.empty((self.tp.size * B, *part.shape[1:]), dtype=part.dtype, device=part.device)
+        dist.all_gather_into_tensor(parts, part, group=self.tp.group)
+        return ops.greedy_merge(parts.view(self.tp.size, B, *part.shape[1:]))
+
+
 class ModelOutput:
-    logits: torch.Tensor                 # fp32 [B or T, vocab]
-    hidden: Optional[torch.Tensor] = None
+    """`logits_any`: fp32 [B or T, vocab] tensor, or ShardedLogits when the lm_head is vocabulary-parallel (hand
+    it to `ops.sample`); `logits`: always the dense matrix; `hidden`: final residual stream when asked for."""
+
+    def __init__(self, logits=None, hidden: Optional[torch.Tensor] = None):
+        self.logits_any, self.hidden = logits, hidden
+
+    @property
+    def logits(self) -> torch.Tensor:
+        """The dense [rows, vocab] matrix (gathered on first use when the model produced vocabulary shards)."""
+        x = self.logits_any
+        return x.full() if isinstance(x, ShardedLogits) else x
 
 
 @dataclass

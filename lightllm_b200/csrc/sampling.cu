@@ -239,9 +239,11 @@ LLB_EXPORT int llb_sample(const void* logits, int dtype, int64_t stride, int B, 
 // ---- all-greedy batches: arg-max + log-probability in two small passes over many CTAs ----
 // pass 1: CTA (b, s) scans slice s of row b (coalesced loads) and keeps (max, arg-max, sum exp(x - max));
 // pass 2: one warp per row merges the S partials.  part: [B, S, 3] floats (max, index bits, sum).
+// `idx_off` is added to the stored arg-max index: a tensor-parallel rank that holds columns [idx_off, idx_off + V)
+// of the full vocabulary writes global token ids, so the partials of all ranks can be merged as they are.
 template <typename T>
 __global__ void __launch_bounds__(256) greedy_partial_kernel(const T* __restrict__ logits, int64_t stride, int V,
-                                                             int per, float* __restrict__ part) {
+                                                             int per, float* __restrict__ part, int idx_off) {
   __shared__ float red[33];
   __shared__ ArgMax am[33];
   const int b = blockIdx.x, s = blockIdx.y, S = gridDim.y;
@@ -256,17 +258,19 @@ __global__ void __launch_bounds__(256) greedy_partial_kernel(const T* __restrict
   if (threadIdx.x == 0) {
     float* o = part + ((int64_t)b * S + s) * 3;
     o[0] = best.v;
-    o[1] = __int_as_float(best.i);
+    o[1] = __int_as_float(i1 > i0 ? best.i + idx_off : 0x7fffffff);
     o[2] = i1 > i0 ? z : 0.f;
   }
 }
 
-__global__ void greedy_final_kernel(const float* __restrict__ part, int S, int64_t* __restrict__ out_ids,
+// part: [R, B, S, 3]; R > 1 when the partials of R vocabulary shards (tensor-parallel ranks) were gathered.
+__global__ void greedy_final_kernel(const float* __restrict__ part, int S, int R, int64_t* __restrict__ out_ids,
                                     float* __restrict__ out_logprob) {
-  const int b = blockIdx.x, lane = threadIdx.x;
+  const int b = blockIdx.x, lane = threadIdx.x, B = gridDim.x;
+  const int n = S * R;
   ArgMax best{-INFINITY, 0x7fffffff};
-  for (int s = lane; s < S; s += 32) {
-    const float* o = part + ((int64_t)b * S + s) * 3;
+  for (int j = lane; j < n; j += 32) {
+    const float* o = part + (((int64_t)(j / S) * B + b) * S + (j % S)) * 3;
     best = better(best, ArgMax{o[0], __float_as_int(o[1])});
   }
 #pragma unroll
@@ -277,8 +281,8 @@ __global__ void greedy_final_kernel(const float* __restrict__ part, int S, int64
     best = better(best, t);
   }
   float z = 0.f;
-  for (int s = lane; s < S; s += 32) {
-    const float* o = part + ((int64_t)b * S + s) * 3;
+  for (int j = lane; j < n; j += 32) {
+    const float* o = part + (((int64_t)(j / S) * B + b) * S + (j % S)) * 3;
     if (o[2] > 0.f) z += o[2] * __expf(o[0] - best.v);
   }
   z = warp_sum(z);
@@ -296,13 +300,41 @@ LLB_EXPORT int llb_sample_greedy(const void* logits, int dtype, int64_t stride, 
   const int per = ((V + splits - 1) / splits + 3) & ~3;
   dim3 grid(B, splits);
   if (dtype == 0)
-    greedy_partial_kernel<float><<<grid, 256, 0, st>>>((const float*)logits, stride, V, per, scratch);
+    greedy_partial_kernel<float><<<grid, 256, 0, st>>>((const float*)logits, stride, V, per, scratch, 0);
   else if (dtype == 1)
-    greedy_partial_kernel<bf16><<<grid, 256, 0, st>>>((const bf16*)logits, stride, V, per, scratch);
+    greedy_partial_kernel<bf16><<<grid, 256, 0, st>>>((const bf16*)logits, stride, V, per, scratch, 0);
   else
     return LLB_ERR_UNSUPPORTED;
   LLB_LAUNCH_CHECK();
-  greedy_final_kernel<<<B, 32, 0, st>>>(scratch, splits, out_ids, out_logprob);
+  greedy_final_kernel<<<B, 32, 0, st>>>(scratch, splits, 1, out_ids, out_logprob);
+  LLB_LAUNCH_CHECK();
+  return LLB_OK;
+}
+
+// The two passes on their own, for vocabulary-parallel logits: every rank runs the first pass over its shard
+// (`idx_off` = first token id of the shard), the [B, splits, 3] partials of all ranks are exchanged (a few KB
+// instead of the logits), and the second pass merges `ranks` of them: part [ranks, B, splits, 3].
+LLB_EXPORT int llb_greedy_partial(const void* logits, int dtype, int64_t stride, int B, int V, int idx_off, float* part,
+                                  int splits, cudaStream_t st) {
+  if (B <= 0) return LLB_OK;
+  if (splits < 1 || splits > 1024 || part == nullptr) return LLB_ERR_BAD_ARG;
+  const int per = ((V + splits - 1) / splits + 3) & ~3;
+  dim3 grid(B, splits);
+  if (dtype == 0)
+    greedy_partial_kernel<float><<<grid, 256, 0, st>>>((const float*)logits, stride, V, per, part, idx_off);
+  else if (dtype == 1)
+    greedy_partial_kernel<bf16><<<grid, 256, 0, st>>>((const bf16*)logits, stride, V, per, part, idx_off);
+  else
+    return LLB_ERR_UNSUPPORTED;
+  LLB_LAUNCH_CHECK();
+  return LLB_OK;
+}
+
+LLB_EXPORT int llb_greedy_merge(const float* part, int B, int splits, int ranks, int64_t* out_ids, float* out_logprob,
+                                cudaStream_t st) {
+  if (B <= 0) return LLB_OK;
+  if (splits < 1 || ranks < 1 || part == nullptr) return LLB_ERR_BAD_ARG;
+  greedy_final_kernel<<<B, 32, 0, st>>>(part, splits, ranks, out_ids, out_logprob);
   LLB_LAUNCH_CHECK();
   return LLB_OK;
 }

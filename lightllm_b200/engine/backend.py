@@ -305,7 +305,7 @@ class ModelBackend:
         for r, c in items:
             r.cur_kv_len += int(c)
         self._snapshot_states(reqs)
-        logits = out.logits
+        logits = out.logits if want_all else self._logits_for_sampling(out, reqs, is_prefill=True)
         if want_all:
             self._handle_prompt_logprobs(reqs, chunks, ids, logits)
             last_rows = torch.from_numpy(np.cumsum(chunks) - 1).to(self.device)
@@ -401,7 +401,8 @@ class ModelBackend:
         self.stats["h2d_bytes"] += B * 12
         out = self.model.forward(mi)
         if defer:
-            ids, lps = self._sample(reqs, out.logits, np.ones(B, dtype=bool), is_prefill=False)
+            ids, lps = self._sample(reqs, self._logits_for_sampling(out, reqs, False), np.ones(B, dtype=bool),
+                                    is_prefill=False)
             if self.device.type == "cuda":
                 ids_h = self.pins.get("s_ids", B, torch.int64)
                 lps_h = self.pins.get("s_lps", B, torch.float32)
@@ -421,20 +422,44 @@ class ModelBackend:
             self._pending = (reqs, ids_h, lps_h, event)
         else:
             self._snapshot_states(reqs)
-            self._sample_and_post(reqs, out.logits, np.ones(B, dtype=bool), is_prefill=False)
+            self._sample_and_post(reqs, self._logits_for_sampling(out, reqs, False), np.ones(B, dtype=bool),
+                                  is_prefill=False)
         self.stats["decode_steps"] += 1
         self.stats["decode_tokens"] += B
         return B
 
     # ---- sampling + post ----
+    sharded_sampling = True   # subclasses that read whole logit rows in their own sampling code turn this off
+
+    def _needs_full_rows(self, reqs: List[InferReq], is_prefill: bool) -> bool:
+        if (self.prefill_mask_func if is_prefill else self.decode_mask_func) is not None:
+            return True
+        for r in reqs:
+            sp = r.sampling
+            if sp.top_k != 1 or sp.has_penalty or sp.invalid_token_ids or sp.exp_decay_factor > 1.0 or \
+                    (self.eos_ids and not sp.ignore_eos and r.cur_output_len + r.inflight + 1 < sp.min_new_tokens):
+                return True
+        return False
+
+    def _logits_for_sampling(self, out, reqs: List[InferReq], is_prefill: bool):
+        """The model's vocabulary shards when this step can be sampled from them (tensor parallelism, every row
+        greedy, nothing that edits logit rows), else the dense matrix."""
+        x = out.logits_any
+        if x is None or isinstance(x, torch.Tensor):
+            return x
+        if self.sharded_sampling and not self._needs_full_rows(reqs, is_prefill):
+            return x
+        return out.logits
+
     def _sample(self, reqs: List[InferReq], logits: torch.Tensor, has_out: np.ndarray, is_prefill: bool):
         """Masks / penalties, sampling and the device-side hand-over of the sampled ids to the next decode step."""
         dev = self.device
         sp = [r.sampling for r in reqs]
         mask_func = self.prefill_mask_func if is_prefill else self.decode_mask_func
-        if mask_func is not None:
-            mask_func(reqs, logits)
-        self._apply_penalties(reqs, logits)
+        if isinstance(logits, torch.Tensor):   # vocabulary shards only get here when nothing edits the rows
+            if mask_func is not None:
+                mask_func(reqs, logits)
+            self._apply_penalties(reqs, logits)
         all_greedy = all(s.top_k == 1 for s in sp)
         if all_greedy:
             ids, lps = ops.sample(logits)

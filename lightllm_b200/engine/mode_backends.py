@@ -218,6 +218,8 @@ class OutlinesConstraintBackend(ModelBackend):
 class RewardModelBackend(ModelBackend):
     """Reward models: one prefill, the score head output is stored in `reward_score`; no decoding."""
 
+    sharded_sampling = False   # reads a column of the dense matrix
+
     def _sample_and_post(self, reqs, logits, has_out, is_prefill):
         from ..server.core.objs.req import FinishStatus
 

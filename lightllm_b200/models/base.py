@@ -27,7 +27,7 @@ from typing import Dict, List, Optional
 import torch
 
 from .. import ops
-from ..common.infer_state import InferState, ModelInput, ModelOutput
+from ..common.infer_state import ShardedLogits, InferState, ModelInput, ModelOutput
 from ..common.mem_manager import MemoryManager, profile_max_tokens
 from ..common.req_manager import ReqManager
 from ..ops import reference as ref
@@ -596,9 +596,13 @@ class TransformerLM:
     def _lm_head(self, h, normed: bool = False):
         hn = h if normed else ops.rmsnorm(h, self.final_norm_w, self.eps, self.norm_w_offset)
         logits = ops.gemm(hn, self.lm_head_w, epi="f32")
-        logits = self.tp.gather_logits(logits)
         scale = getattr(self, "logit_scale", 1.0)
-        return logits * scale if scale != 1.0 else logits
+        if scale != 1.0:
+            logits = logits * scale
+        if self.tp.size == 1:
+            return logits
+        # vocabulary-parallel: the consumer decides whether it needs the gathered matrix (ModelOutput.logits)
+        return ShardedLogits(logits, self.tp, self.tp.rank * logits.shape[1], self.vocab)
 
     def _layers_forward(self, x, st: InferState):
         """x: embeddings [T, H]; returns the final residual stream (pre final-norm).  In the token-sharded mode

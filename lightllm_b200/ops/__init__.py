@@ -437,8 +437,43 @@ def apply_penalty_(logits, presence, frequency, repetition, cu, tok_ids, tok_cnt
     return logits
 
 
+def greedy_partials(logits, idx_off: int = 0):
+    """First pass of the all-greedy sampler over (a vocabulary shard of) the logits: [B, S, 3] fp32 rows of
+    (max, arg-max as global token id bits, sum exp(x - max)).  S depends on B and the shard width only."""
+    B, V = logits.shape
+    splits = max(1, min(64, 2368 // max(B, 1), V // 2048))
+    if not logits.is_cuda:
+        return ref.greedy_partials(logits, idx_off, splits)
+    dt = {torch.float32: 0, torch.bfloat16: 1}[logits.dtype]
+    part = torch.empty((B, splits, 3), dtype=torch.float32, device=logits.device)
+    check(kernels().llb_greedy_partial(ptr(logits), c_int(dt), i64(logits.stride(0)), c_int(B), c_int(V),
+                                       c_int(idx_off), ptr(part), c_int(splits), stream()), "greedy_partial")
+    _count()
+    return part
+
+
+def greedy_merge(parts):
+    """parts [R, B, S, 3] (the partials of R vocabulary shards) -> (ids int64 [B], logprob fp32 [B])."""
+    R, B, S, _ = parts.shape
+    if not parts.is_cuda:
+        return ref.greedy_merge(parts)
+    parts = parts.contiguous()
+    ids = torch.empty(B, dtype=torch.int64, device=parts.device)
+    lp = torch.empty(B, dtype=torch.float32, device=parts.device)
+    check(kernels().llb_greedy_merge(ptr(parts), c_int(B), c_int(S), c_int(R), ptr(ids), ptr(lp), stream()),
+          "greedy_merge")
+    _count()
+    return ids, lp
+
+
 def sample(logits, temperature=None, top_p=None, top_k=None, seeds=None, steps=None, want_logprob=True):
-    """Returns (ids int64 [B], logprob fp32 [B]).  Rows with top_k == 1 (or top_k None) are greedy."""
+    """Returns (ids int64 [B], logprob fp32 [B]).  Rows with top_k == 1 (or top_k None) are greedy.
+    `logits` may be vocabulary-parallel (`common.infer_state.ShardedLogits`): an all-greedy batch is then
+    sampled from the shards (a few KB exchanged per step), anything else from the gathered matrix."""
+    if hasattr(logits, "greedy"):
+        if temperature is None and top_k is None and top_p is None:
+            return logits.greedy()
+        logits = logits.full()
     if not logits.is_cuda:
         return ref.sample(logits, temperature, top_p, top_k, seeds, steps)
     B, V = logits.shape

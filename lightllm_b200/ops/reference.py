@@ -259,6 +259,38 @@ def sample(logits, temperature=None, top_p=None, top_k=None, seeds=None, steps=N
     return ids, lps
 
 
+def greedy_partials(logits, idx_off, splits):
+    """[B, S, 3]: (max, arg-max global id as float bits, sum exp(x - max)) of S column slices."""
+    B, V = logits.shape
+    per = ((V + splits - 1) // splits + 3) & ~3
+    out = torch.zeros((B, splits, 3), dtype=torch.float32, device=logits.device)
+    for s in range(splits):
+        i0, i1 = s * per, min(V, (s + 1) * per)
+        if i1 <= i0:
+            out[:, s, 0] = float("-inf")
+            out[:, s, 1] = torch.tensor([0x7FFFFFFF], dtype=torch.int32).view(torch.float32)
+            continue
+        x = logits[:, i0:i1].float()
+        m, i = x.max(dim=-1)
+        out[:, s, 0] = m
+        out[:, s, 1] = (i + i0 + idx_off).to(torch.int32).view(torch.float32)
+        out[:, s, 2] = torch.exp(x - m[:, None]).sum(-1)
+    return out
+
+
+def greedy_merge(parts):
+    R, B, S, _ = parts.shape
+    p = parts.permute(1, 0, 2, 3).reshape(B, R * S, 3)
+    m = p[..., 0]
+    idx = p[..., 1].contiguous().view(torch.int32).to(torch.int64)
+    best = m.max(dim=-1).values
+    # ties go to the smallest token id, as in one pass over the whole row
+    cand = torch.where(m == best[:, None], idx, torch.full_like(idx, 0x7FFFFFFF))
+    ids = cand.min(dim=-1).values
+    z = torch.where(p[..., 2] > 0, p[..., 2] * torch.exp(m - best[:, None]), torch.zeros_like(m)).sum(-1)
+    return ids, -torch.log(z)
+
+
 def filtered_support(x, top_p, top_k):
     """Boolean mask of the tokens that survive top-k then top-p on logits `x` (1-D)."""
     V = x.shape[0]

@@ -62,61 +62,76 @@ class FinishStatus(ctypes.Structure):
         return self._NAMES.get(self.status)
 
 
-class QueueItem(ctypes.Structure):
+class TokenText(ctypes.Structure):
+    """One decoded token as the detokenizer hands it to the HTTP worker: UTF-8 bytes (cut at
+    LIGHTLLM_TOKEN_MAX_BYTES), the token's index in the request's id array, and what the stream needs with it."""
+
     _pack_ = 4
     _fields_ = [("data", ctypes.c_ubyte * LIGHTLLM_TOKEN_MAX_BYTES), ("data_len", ctypes.c_int),
                 ("src_index", ctypes.c_int), ("special", ctypes.c_bool), ("count_output_tokens", ctypes.c_int)]
 
-    def set(self, text: str, src_index: int, special: bool, count_output_tokens: int):
-        data = text.encode("utf-8")
-        if len(data) > LIGHTLLM_TOKEN_MAX_BYTES:
-            data = data[:LIGHTLLM_TOKEN_MAX_BYTES]
-        ctypes.memmove(self.data, data, len(data))
-        self.data_len = len(data)
-        self.src_index = src_index
-        self.special = special
-        self.count_output_tokens = count_output_tokens
+    def store(self, text: str, src_index: int, special: bool, count_output_tokens: int):
+        raw = text.encode("utf-8")[:LIGHTLLM_TOKEN_MAX_BYTES]
+        ctypes.memmove(self.data, raw, len(raw))
+        self.data_len, self.src_index = len(raw), src_index
+        self.special, self.count_output_tokens = special, count_output_tokens
 
-    def get(self) -> Tuple[str, int, bool, int]:
-        text = bytes(self.data[: self.data_len]).decode("utf-8", errors="replace")
-        return text, self.src_index, self.special, self.count_output_tokens
+    def load(self) -> Tuple[str, int, bool, int]:
+        return (bytes(self.data[: self.data_len]).decode("utf-8", errors="replace"), self.src_index,
+                bool(self.special), self.count_output_tokens)
 
 
-class CircularQueue(ctypes.Structure):
-    """Single-producer (detokenizer) / single-consumer (HTTP worker) ring of decoded token texts."""
+class OutTokenRing(ctypes.Structure):
+    """Decoded-token ring inside the shared request: one producer (the detokenizer process), one consumer (the
+    HTTP worker).  `produced` and `consumed` are free-running counters (slot = counter mod size), each
+    written by exactly one side, so all LIGHTLLM_OUT_TOKEN_QUEUE_SIZE slots can be in use and "empty" and "full"
+    need no spare slot.  The producer fills the slot first and publishes by advancing `produced` afterwards.
+    Reference: lightllm/server/core/objs/out_token_circlequeue.py (head / tail indices, one slot kept free)."""
 
     _pack_ = 4
-    _fields_ = [("items", QueueItem * LIGHTLLM_OUT_TOKEN_QUEUE_SIZE), ("head", ctypes.c_int), ("tail", ctypes.c_int)]
+    _fields_ = [("items", TokenText * LIGHTLLM_OUT_TOKEN_QUEUE_SIZE), ("consumed", ctypes.c_uint32),
+                ("produced", ctypes.c_uint32)]
+    CAPACITY = LIGHTLLM_OUT_TOKEN_QUEUE_SIZE
+    WRAP = CAPACITY * ((1 << 31) // CAPACITY)   # counters wrap at a multiple of the size, whatever the size
+
+    def reset(self):
+        self.consumed = 0
+        self.produced = 0
+
+    def __len__(self) -> int:
+        return (self.produced - self.consumed) % self.WRAP
 
     def is_empty(self) -> bool:
-        return self.head == self.tail
+        return self.produced == self.consumed
 
     def is_full(self) -> bool:
-        return (self.tail + 1) % LIGHTLLM_OUT_TOKEN_QUEUE_SIZE == self.head
+        return len(self) >= self.CAPACITY
 
-    def __len__(self):
-        return (self.tail - self.head + LIGHTLLM_OUT_TOKEN_QUEUE_SIZE) % LIGHTLLM_OUT_TOKEN_QUEUE_SIZE
-
+    # ---- producer ----
     def push(self, text: str, src_index: int, special: bool, count_output_tokens: int):
         if self.is_full():
-            raise BufferError("out token queue is full")
-        self.items[self.tail].set(text, src_index, special, count_output_tokens)
-        self.tail = (self.tail + 1) % LIGHTLLM_OUT_TOKEN_QUEUE_SIZE  # publish after the item is written
+            raise BufferError("out token ring is full")
+        self.items[self.produced % self.CAPACITY].store(text, src_index, special, count_output_tokens)
+        self.produced = (self.produced + 1) % self.WRAP
 
-    def peek(self):
+    # ---- consumer ----
+    def peek(self) -> Tuple[str, int, bool, int]:
         if self.is_empty():
-            raise BufferError("out token queue is empty")
-        return self.items[self.head].get()
+            raise BufferError("out token ring is empty")
+        return self.items[self.consumed % self.CAPACITY].load()
 
     def pop_no_ret(self):
         if self.is_empty():
-            raise BufferError("out token queue is empty")
-        self.head = (self.head + 1) % LIGHTLLM_OUT_TOKEN_QUEUE_SIZE
+            raise BufferError("out token ring is empty")
+        self.consumed = (self.consumed + 1) % self.WRAP
 
-    def pop(self):
+    def pop(self) -> Tuple[str, int, bool, int]:
         item = self.peek()
         self.pop_no_ret()
         return item
+
+
+CircularQueue = OutTokenRing   # the reference's name for this structure
 
 
 class PrefixTokenIds(ctypes.Structure):
@@ -154,7 +169,7 @@ class Req(ctypes.Structure):
         ("finish_status", FinishStatus),
         ("is_aborted", ctypes.c_bool),
         ("finish_token_index", ctypes.c_int),
-        ("out_tokens_queue", CircularQueue),
+        ("out_tokens_queue", OutTokenRing),
         ("sample_params", SamplingParams),
         ("chunked_prefill_size", ctypes.c_int),
         ("router_max_wait_tokens", ctypes.c_int),
@@ -199,8 +214,7 @@ class Req(ctypes.Structure):
         self.stop_str_matched_token_index = -1
         self.dp_index = -1
         self.first_token_time = 0.0
-        self.out_tokens_queue.head = 0
-        self.out_tokens_queue.tail = 0
+        self.out_tokens_queue.reset()
         if isinstance(sample_param, SamplingParams):
             ctypes.memmove(ctypes.byref(self.sample_params), ctypes.byref(sample_param), ctypes.sizeof(SamplingParams))
         else:

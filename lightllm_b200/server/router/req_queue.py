@@ -13,7 +13,7 @@ impl_for_pd.py (PD variant), beam_impl.py (shared-prefix groups), dp_base_queue.
 from __future__ import annotations
 
 import random
-from typing import List, Optional
+from typing import List, Optional, Tuple
 
 import numpy as np
 
@@ -121,31 +121,66 @@ class BaseQueue:
         return gone
 
 
+class PeakEstimate:
+    """Past-Future estimate of the largest KV footprint a set of requests will reach.
+
+    Every request contributes (held, growth): tokens it holds once its prompt is in, and tokens it is still expected
+    to produce.  Requests finish in order of remaining growth; just before the request with the i-th largest
+    growth g_i finishes, the i requests that outlive the others have each grown by g_i, on top of what those i
+    hold now: peak = max_i (i * g_i + sum of `held` over the i largest growths).
+    Reference: lightllm/server/router/req_queue/chunked_prefill/impl.py:22-51."""
+
+    def __init__(self, pairs=()):
+        self.pairs: List[Tuple[int, int]] = list(pairs)
+
+    def copy(self) -> "PeakEstimate":
+        return PeakEstimate(self.pairs)
+
+    def add(self, held: int, growth: int):
+        self.pairs.append((int(held), int(growth)))
+
+    def __len__(self):
+        return len(self.pairs)
+
+    def peak(self) -> int:
+        if not self.pairs:
+            return 0
+        arr = np.array(sorted(self.pairs, key=lambda p: -p[1]), dtype=np.int64)
+        alive = np.arange(1, arr.shape[0] + 1, dtype=np.int64)
+        return int((arr[:, 1] * alive + np.cumsum(arr[:, 0])).max())
+
+    def held(self) -> int:
+        return int(sum(p[0] for p in self.pairs))
+
+
 class ChunkedPrefillQueue(BaseQueue):
-    def _init_cache_list(self, current_batch: Optional[Batch], is_busy: bool):
-        self.cache_len_list = []
-        if current_batch is not None:
-            for r in current_batch.get_req_list_for_dp(self.dp_index):
-                self.cache_len_list.append(self._tuple_of(r, is_busy))
+    PREFILL_PASSES_OF_SLACK = 2   # a new batch may queue up to this many forward passes of prompt tokens
 
     def _tuple_of(self, req: Req, is_busy: bool):
         return req.get_tuple_tokens(is_busy, self.statics.ema_req_out_len)
 
-    def _can_add_new_req(self, req: Req, is_busy: bool, new_batch_first_router_need_tokens: int):
-        self.cache_len_list.append(self._tuple_of(req, is_busy))
-        self.cache_len_list.sort(key=lambda x: -x[1])
-        a = np.array([e[0] for e in self.cache_len_list], dtype=np.int64)
-        b = np.array([e[1] for e in self.cache_len_list], dtype=np.int64)
-        cum_a = np.cumsum(a)
-        size = np.arange(1, len(a) + 1, dtype=np.int64)
-        need_max_token_num = int((b * size + cum_a).max())
-        ok_token = need_max_token_num < self.max_total_tokens
-        ok_req = len(self.cache_len_list) <= self.running_max_req_size
-        new_need = new_batch_first_router_need_tokens + req.get_first_router_need_tokens()
-        ok_prefill = new_need <= 2 * self.batch_max_tokens  # slack of two forward passes
-        if ok_token and ok_req and ok_prefill:
-            return True, new_need
-        return False, new_need
+    def _estimate_of(self, current_batch: Optional[Batch], is_busy: bool) -> PeakEstimate:
+        est = PeakEstimate()
+        if current_batch is not None:
+            for r in current_batch.get_req_list_for_dp(self.dp_index):
+                est.add(*self._tuple_of(r, is_busy))
+        return est
+
+    def _admit(self, est: PeakEstimate, req: Req, is_busy: bool, prefill_tokens: int):
+        """Adds `req` to the estimate; returns (fits, prompt tokens the next passes would then have to run)."""
+        est.add(*self._tuple_of(req, is_busy))
+        prefill_tokens += req.get_first_router_need_tokens()
+        fits = (est.peak() < self.max_total_tokens and len(est) <= self.running_max_req_size
+                and prefill_tokens <= self.PREFILL_PASSES_OF_SLACK * self.batch_max_tokens)
+        return fits, prefill_tokens
+
+    def _running_need(self, current_batch: Optional[Batch]) -> int:
+        """Tokens the next pass already owes to the running requests of this replica (one per decoding request,
+        the next chunk of a prompt still being prefilled); new prompts are budgeted on top of it
+        (reference: chunked_prefill/impl.py:67-69)."""
+        if current_batch is None:
+            return 0
+        return sum(r.get_decode_need_tokens() for r in current_batch.get_req_list_for_dp(self.dp_index))
 
     def generate_new_batch(self, current_batch: Optional[Batch], next_batch_id: int = 0) -> Optional[Batch]:
         if not self.waiting_req_list:
@@ -154,18 +189,16 @@ class ChunkedPrefillQueue(BaseQueue):
         if running >= self.running_max_req_size:
             return None
         is_busy = self.is_busy()
-        self._init_cache_list(current_batch, is_busy)
-        can_run, aborted = [], 0
-        first_tokens = 0
+        est = self._estimate_of(current_batch, is_busy)
+        prefill_tokens = self._running_need(current_batch)
+        can_run = []
         for req in self.waiting_req_list:
             if req.is_aborted:  # released by the router, never scheduled
-                aborted += 1
                 continue
-            ok, first_tokens = self._can_add_new_req(req, is_busy, first_tokens)
-            if ok:
-                can_run.append(req)
-            else:
+            ok, prefill_tokens = self._admit(est, req, is_busy, prefill_tokens)
+            if not ok:
                 break
+            can_run.append(req)
         if not can_run:
             return None
         taken = {id(r) for r in can_run}
@@ -174,15 +207,10 @@ class ChunkedPrefillQueue(BaseQueue):
 
     def calcu_batch_token_load(self, current_batch: Optional[Batch]):
         """(estimated peak ratio, current used ratio) for /token_load."""
-        is_busy = self.is_busy()
-        self._init_cache_list(current_batch, is_busy)
-        if not self.cache_len_list:
+        est = self._estimate_of(current_batch, self.is_busy())
+        if not len(est):
             return 0.0, 0.0
-        self.cache_len_list.sort(key=lambda x: -x[1])
-        a = np.array([e[0] for e in self.cache_len_list], dtype=np.int64)
-        b = np.array([e[1] for e in self.cache_len_list], dtype=np.int64)
-        peak = int((b * np.arange(1, len(a) + 1) + np.cumsum(a)).max())
-        return peak / self.max_total_tokens, int(a.sum()) / self.max_total_tokens
+        return est.peak() / self.max_total_tokens, est.held() / self.max_total_tokens
 
 
 class PDQueue(ChunkedPrefillQueue):
@@ -201,28 +229,29 @@ class ChunkedBeamContinuesBatchQueue(ChunkedPrefillQueue):
         if not self.waiting_req_list:
             return None
         is_busy = self.is_busy()
-        self._init_cache_list(current_batch, is_busy)
+        est = self._estimate_of(current_batch, is_busy)
         groups, order = {}, []
         for r in self.waiting_req_list:
             if r.group_req_id not in groups:
                 groups[r.group_req_id] = []
                 order.append(r.group_req_id)
             groups[r.group_req_id].append(r)
-        can_run, first_tokens = [], 0
+        can_run, prefill_tokens = [], self._running_need(current_batch)
         for gid in order:
-            saved = list(self.cache_len_list)
-            ok_all = True
-            ft = first_tokens
+            trial = est.copy()
+            ok_all, after = True, prefill_tokens
             for i, r in enumerate(groups[gid]):
-                ok, ft2 = self._can_add_new_req(r, is_busy, ft if i == 0 else ft - r.get_first_router_need_tokens())
-                ft = ft2 if i == 0 else ft
+                # the group's prompt is prefilled once: only its first member adds prompt tokens to the passes
+                ok, t = self._admit(trial, r, is_busy, prefill_tokens if i == 0 else
+                                    after - r.get_first_router_need_tokens())
+                if i == 0:
+                    after = t
                 if not ok:
                     ok_all = False
                     break
             if not ok_all:
-                self.cache_len_list = saved
                 break
-            first_tokens = ft
+            est, prefill_tokens = trial, after
             can_run.extend(groups[gid])
         if not can_run:
             return None

@@ -142,6 +142,30 @@ def test_sampler_greedy_many_ctas(dev, B, V):
     close(lp, want, 1e-3, 1e-3)
 
 
+@pytest.mark.parametrize("B,V,R", [(256, 128256, 8), (5, 32000, 2), (64, 151936, 4)])
+def test_sampler_greedy_from_vocabulary_shards(dev, B, V, R):
+    """The two greedy passes run per vocabulary shard (what R tensor-parallel ranks do) and merged give the
+    token and log-probability of one pass over the whole row; the CPU restatement agrees."""
+    torch.manual_seed(B + R)
+    logits = torch.randn(B, V, device=dev) * 4
+    logits[0, V - 1] = logits.max() + 2.0           # winner in the last shard
+    logits[1 % B, 5] = logits.max() + 3.0           # tie across two shards: the lower token id wins
+    logits[1 % B, V - 9] = logits[1 % B, 5]
+    Vl = V // R
+    parts = torch.stack([ops.greedy_partials(logits[:, r * Vl:(r + 1) * Vl], r * Vl) for r in range(R)])
+    ids, lp = ops.greedy_merge(parts)
+    want_ids = logits.argmax(-1)
+    want_ids[1 % B] = 5
+    assert ids.tolist() == want_ids.tolist()
+    want_lp = torch.log_softmax(logits.float(), -1).gather(1, want_ids[:, None])[:, 0]
+    close(lp, want_lp, 1e-3, 1e-3)
+    lc = logits.cpu()
+    parts_c = torch.stack([ops.greedy_partials(lc[:, r * Vl:(r + 1) * Vl], r * Vl) for r in range(R)])
+    ids_c, lp_c = ops.greedy_merge(parts_c)
+    assert ids_c.tolist() == want_ids.tolist()
+    close(lp_c, want_lp.cpu(), 1e-3, 1e-3)
+
+
 def test_sampler_topk_topp_support_and_distribution(dev):
     torch.manual_seed(7)
     V = 5000
