@@ -147,6 +147,12 @@ def main():
         if M <= 256:  # skinny kernel: 1000 + 10 * accumulators + K splits
             variants.update({"sk_n1s1": dict(bn=1011), "sk_n1s2": dict(bn=1012), "sk_n1s4": dict(bn=1014),
                              "sk_n2s1": dict(bn=1021), "sk_w128s1": dict(bn=1111), "sk_w128s2": dict(bn=1112)})
+        if M <= 256 and N <= 148 * 128:  # split-K without clusters: 2000 + splits (2000 = as many as fit)
+            variants.update({"spk_max": dict(bn=2000), "spk_s1": dict(bn=2001), "spk_s2": dict(bn=2002),
+                             "spk_s4": dict(bn=2004), "spk_s8": dict(bn=2008)})
+        if ((M + 255) // 256) * ((N + 255) // 256) * 2 <= 148:  # pair tiles split through the L2 workspace
+            variants.update({"psk_max": dict(bn=3000), "psk_s1": dict(bn=3001), "psk_s2": dict(bn=3002),
+                             "psk_s4": dict(bn=3004), "psk_s8": dict(bn=3008)})
         if a.stream_k:
             variants.update({"sk256": dict(bn=256, stream_k=1), "sk128": dict(bn=128, stream_k=1)})
         tiled = None
@@ -167,8 +173,16 @@ def main():
                 continue  # more tiles than arrival counters
             if kw.get("bn") == 512 and (M < 256 or N < 256):
                 continue
-            if kw.get("bn", 0) >= 1000 and ((K + 63) // 64) < 4 * (kw["bn"] % 10):
+            if 1000 <= kw.get("bn", 0) < 2000 and ((K + 63) // 64) < 4 * (kw["bn"] % 10):
                 continue
+            if 3000 < kw.get("bn", 0) < 3100:
+                sp, pr, kbs = kw["bn"] - 3000, ((M + 255) // 256) * ((N + 255) // 256), (K + 63) // 64
+                if pr * 2 * sp > 148 or -(-kbs // sp) * (sp - 1) >= kbs:
+                    continue
+            if 2000 < kw.get("bn", 0) < 2100:
+                sp, tl, kbs = kw["bn"] - 2000, (N + 127) // 128, (K + 63) // 64
+                if tl * sp > 148 or sp > (8 if M > 128 else 4) or -(-kbs // sp) * (sp - 1) >= kbs:
+                    continue
             t = timer(lambda i: ops.gemm(xs[i % copies], wsel[i % copies], out=out, **kw), flush, reps=reps)
             row[f"{name}_ms"] = round(t, 4)
             done.append(name)

@@ -1284,6 +1284,591 @@ void skinny_plan(int M, int N, int K, int epi, int* nb, int* splits, bool* use_p
 }
 
 
+// ---------------------------------------------------------------------------------------------
+// Split-K GEMM for M <= 256 without clusters: CTA (tile, split) multiplies all token rows (one or two 128-row
+// blocks, one tensor-memory accumulator each) with 128 weight rows over its share of K, so every weight byte is
+// staged once and the grid is tiles x splits CTAs whatever the shape (a narrow output with a long K fills the GPU
+// through the split).  The fp32 partial sums meet in an L2-resident workspace: a tile is cut into units of 128
+// rows x 32 columns (64 for the gated epilogues: one gate / up column group), unit u is finished by split
+// u % splits, every CTA stores the units it does not own ([column][row] order: a warp stores 32 consecutive
+// rows of a column per instruction), adds 1 to the tile's arrival counter and waits until all splits have arrived;
+// then it adds the other splits' values to its own accumulator columns of the units it owns and runs the epilogue
+// on them.  The work after the K loop is the same on every CTA.  All CTAs of a tile must be co-resident: the host
+// only uses this kernel with tiles x splits <= number of SMs (one CTA per SM by shared memory).  The wait is
+// bounded (status code 31).  Counters only grow; counter arrays are separate per split count so that a tile's
+// counter is always a multiple of `splits` when a launch starts.
+// ---------------------------------------------------------------------------------------------
+constexpr int SPK_BN = 128;
+constexpr int SPK_MAX_TILES = 2048;  // counters per split count
+template <int MBLK>
+constexpr int spk_stage_bytes() { return (MBLK * BM + SPK_BN) * BK * 2; }
+template <int MBLK>
+constexpr int spk_stages() { return MBLK == 2 ? 4 : 6; }
+template <int MBLK>
+constexpr int spk_smem_bytes() { return spk_stages<MBLK>() * spk_stage_bytes<MBLK>() + 1024 + 256 + EPI_STAGE_BYTES; }
+
+template <int MBLK, int EPI>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_splitk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                        const GemmParams p, const int splits) {
+  constexpr int STAGES = spk_stages<MBLK>();
+  constexpr int A_BYTES = BM * BK * 2;
+  constexpr int STAGE_BYTES = spk_stage_bytes<MBLK>();
+  constexpr uint32_t TMEM_COLS = MBLK * SPK_BN;
+  constexpr uint32_t IDESC = umma_idesc(BM, SPK_BN, 1);
+  constexpr bool GATED = EPI == EPI_GATED_SILU || EPI == EPI_GATED_GELU;
+  constexpr int UW = GATED ? 64 : 32;     // unit width in accumulator columns
+  constexpr int UPB = SPK_BN / UW;        // units per 128-row block
+  constexpr int U = MBLK * UPB;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
+  auto full_bar = [&](int s) { return bar_base + 8 * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8 * (STAGES + s); };
+  const uint32_t tfull_bar = bar_base + 8 * (2 * STAGES);
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+  __shared__ int spk_ok;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = blockIdx.x / splits, split = blockIdx.x - tile * splits;
+  const int n0 = tile * SPK_BN;
+  const int kb_total = (p.K + BK - 1) / BK;
+  const int kb_per = (kb_total + splits - 1) / splits;
+  const int kb0 = split * kb_per;
+  const int nk = max(min(kb_total, kb0 + kb_per) - kb0, 0);
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    mbar_init(tfull_bar, 1);
+    fence_barrier_init();
+  }
+  if (warp == 0) {
+    tmem_alloc(smem_u32(&tmem_base_slot), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {  // ---- TMA producer ----
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      // The weights do not depend on the kernel before this one: the first stages' weight tiles are requested while
+      // that kernel is still draining; the activations (its output) follow after the dependency wait.
+      const int pre = min(nk, STAGES);
+      for (int i = 0; i < pre; ++i) {
+        mbar_expect_tx(full_bar(i), STAGE_BYTES);
+        tma_load_2d(smem_base + i * STAGE_BYTES + MBLK * A_BYTES, &tmB, full_bar(i), (kb0 + i) * BK, n0);
+      }
+      pdl_wait();
+      for (int i = 0; i < pre; ++i) {
+#pragma unroll
+        for (int m = 0; m < MBLK; ++m)
+          tma_load_2d(smem_base + i * STAGE_BYTES + m * A_BYTES, &tmA, full_bar(i), (kb0 + i) * BK, m * BM);
+      }
+      int stage = pre == STAGES ? 0 : pre;
+      uint32_t phase = pre == STAGES ? 1 : 0;
+      for (int i = pre; i < nk; ++i) {
+        const int kb = kb0 + i;
+        mbar_wait(empty_bar(stage), phase ^ 1, &abort_flag, p.status, 31);
+        const uint32_t sa = smem_base + stage * STAGE_BYTES;
+        mbar_expect_tx(full_bar(stage), STAGE_BYTES);
+        tma_load_2d(sa + MBLK * A_BYTES, &tmB, full_bar(stage), kb * BK, n0);
+#pragma unroll
+        for (int m = 0; m < MBLK; ++m) tma_load_2d(sa + m * A_BYTES, &tmA, full_bar(stage), kb * BK, m * BM);
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    } else {
+      pdl_wait();
+    }
+  } else if (warp == 1) {
+    pdl_wait();
+    if (lane == 0) {  // ---- MMA issuer ----
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int i = 0; i < nk; ++i) {
+        mbar_wait(full_bar(stage), phase, &abort_flag, p.status, 32);
+        tc_fence_after();
+        const uint32_t sa = smem_base + stage * STAGE_BYTES;
+        const uint64_t db = umma_smem_desc_sw128(sa + MBLK * A_BYTES);
+#pragma unroll
+        for (int m = 0; m < MBLK; ++m) {
+          const uint64_t da = umma_smem_desc_sw128(sa + m * A_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma_bf16(tmem_base + m * SPK_BN, da + 2 * k, db + 2 * k, IDESC, (i | k) != 0);
+        }
+        umma_commit(empty_bar(stage));
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+      umma_commit(tfull_bar);
+    }
+  } else {
+    // ---- epilogue warps: thread = one row of every 128-row block ----
+    pdl_wait();
+    const int lane_grp = warp & 3;
+    const int erow = lane_grp * 32 + lane;
+    const int etid = threadIdx.x - 64;
+    mbar_wait(tfull_bar, 0, &abort_flag, p.status, 33);
+    tc_fence_after();
+    const uint32_t t_lane = tmem_base + ((uint32_t)(lane_grp * 32) << 16);
+    if (splits == 1) {
+      uint8_t* epi_stage = smem_raw + (bar_base + 256 - smem_u32(smem_raw)) + lane_grp * EPI_WARP_BYTES;
+#pragma unroll 1
+      for (int m = 0; m < MBLK; ++m) {
+        const int row = m * BM + erow;
+        epilogue_store<SPK_BN, EPI>(p, t_lane + m * SPK_BN, row, row < p.M, n0, false, [](uint32_t*, int) {}, epi_stage);
+        if (EPI == EPI_STORE) push_signal(p, m, max(0, min(SPK_BN, p.N - n0)));
+      }
+    } else {
+      float* ws_mine = p.sk_partials + (int64_t)blockIdx.x * (U * UW * BM);
+      uint32_t* counter = reinterpret_cast<uint32_t*>(p.sk_counters) + tile;
+      if (nk > 0) {
+#pragma unroll 1
+        for (int u = 0; u < U; ++u) {
+          if (u % splits == split) continue;
+          const int m = u / UPB, c = (u % UPB) * UW;
+          float* dst = ws_mine + (int64_t)u * (UW * BM) + erow;
+#pragma unroll 1
+          for (int cc = 0; cc < UW; cc += 32) {
+            uint32_t r[32];
+            tmem_ld_32x32(t_lane + m * SPK_BN + c + cc, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) __stcg(dst + (cc + j) * BM, __uint_as_float(r[j]));
+          }
+        }
+      }
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (etid == 0) {
+        const uint32_t prev = atomicAdd(counter, 1u);
+        const uint32_t target = (prev / (uint32_t)splits + 1u) * (uint32_t)splits;
+        int ok = 1;
+        uint64_t t0 = 0;
+        for (uint32_t spin = 0;; ++spin) {
+          uint32_t v;
+          asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
+          if ((int32_t)(v - target) >= 0) break;
+          if ((spin & 0xff) == 0xff) {
+            const uint64_t now = global_timer_ns();
+            if (t0 == 0) {
+              t0 = now;
+            } else if (now - t0 > 1000000000ull) {
+              if (p.status) atomicCAS(p.status, 0, 34);
+              ok = 0;
+              break;
+            }
+          }
+        }
+        spk_ok = ok;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      __threadfence();
+      int pushed[MBLK];
+#pragma unroll
+      for (int m = 0; m < MBLK; ++m) pushed[m] = 0;
+      if (spk_ok) {
+#pragma unroll 1
+        for (int u = split; u < U; u += splits) {
+          const int m = u / UPB, c = (u % UPB) * UW;
+          const int row = m * BM + erow;
+          const bool row_ok = row < p.M;
+          uint32_t r[GATED ? 64 : 32];
+#pragma unroll
+          for (int cc = 0; cc < UW; cc += 32) {
+            if (nk > 0) {
+              tmem_ld_32x32(t_lane + m * SPK_BN + c + cc, r + cc);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) r[cc + j] = 0u;
+            }
+          }
+          tmem_wait_ld();
+          for (int s2 = 0; s2 < splits; ++s2) {
+            if (s2 == split) continue;
+            // a split without k-blocks (K not a multiple of splits * 64) stored nothing
+            if (min(kb_total, s2 * kb_per + kb_per) - s2 * kb_per <= 0) continue;
+            const float* src = p.sk_partials + ((int64_t)(tile * splits + s2) * U + u) * (UW * BM) + erow;
+#pragma unroll
+            for (int j = 0; j < UW; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __ldcg(src + j * BM));
+          }
+          const int col0 = n0 + c;
+          if (GATED) {
+            // accumulator columns [32 gate | 32 up] -> 32 output columns starting at col0 / 2
+            if (row_ok && col0 < p.N) {
+              bf16* crow = (bf16*)p.C + (int64_t)row * p.ldc + col0 / 2;
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                float o[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                  const float gv = __uint_as_float(r[j + e]), uv = __uint_as_float(r[32 + j + e]);
+                  o[e] = (EPI == EPI_GATED_SILU ? silu_f(gv) : gelu_tanh_f(gv)) * uv;
+                }
+                *reinterpret_cast<bf16x8*>(crow + j) = pack8(o);
+              }
+            }
+          } else {
+            epi_direct32<EPI>(p, r, row, row_ok, col0);
+            pushed[m] += max(0, min(32, p.N - col0));
+          }
+        }
+      }
+      if (EPI == EPI_STORE && p.push_world > 0) {
+#pragma unroll
+        for (int m = 0; m < MBLK; ++m) push_signal(p, m, pushed[m]);
+      }
+    }
+    tc_fence_before();
+  }
+
+  __syncthreads();
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int MBLK, int EPI>
+int launch_splitk(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int splits, cudaStream_t st) {
+  static DeviceOnce configured;
+  if (!configured.done()) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_splitk_kernel<MBLK, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         spk_smem_bytes<MBLK>());
+    if (e != cudaSuccess) return (int)e;
+    configured.set();
+  }
+  const int tiles = cdiv(p.N, SPK_BN);
+  cudaError_t le = launch_pdl(gemm_bf16_splitk_kernel<MBLK, EPI>, dim3(tiles * splits), dim3(GEMM_THREADS),
+                              spk_smem_bytes<MBLK>(), st, ta, tb, p, splits);
+  return le == cudaSuccess ? LLB_OK : (int)le;
+}
+
+template <int MBLK>
+int dispatch_splitk(int epi, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int splits,
+                    cudaStream_t st) {
+  switch (epi) {
+    case EPI_STORE: return launch_splitk<MBLK, EPI_STORE>(ta, tb, p, splits, st);
+    case EPI_RESIDUAL: return launch_splitk<MBLK, EPI_RESIDUAL>(ta, tb, p, splits, st);
+    case EPI_GATED_SILU: return launch_splitk<MBLK, EPI_GATED_SILU>(ta, tb, p, splits, st);
+    case EPI_GATED_GELU: return launch_splitk<MBLK, EPI_GATED_GELU>(ta, tb, p, splits, st);
+    case EPI_F32: return launch_splitk<MBLK, EPI_F32>(ta, tb, p, splits, st);
+  }
+  return LLB_ERR_UNSUPPORTED;
+}
+
+// ---------------------------------------------------------------------------------------------
+// The same split through the L2 workspace, on CTA-pair tiles: a cluster of two CTAs computes a 256 x 256 tile
+// slice with cta_group::2 MMAs (CTA h stages token rows h*128.. and 128 of the 256 weight rows per k-block, i.e.
+// 16 KB of activations per 16 KB of weights, against 32 KB per 16 KB in the kernel above), and `splits` such
+// pairs share the K range of a tile.  What an SM can pull from L2 per microsecond is what bounds these launches,
+// so bytes staged per CTA is the figure of merit; the pair layout has the lowest.  CTA (tile, split, h) owns
+// 128 accumulator rows x 256 columns, cut into units of 32 (gated: 64) columns; the units are shared out among
+// the splits exactly as above, with one arrival counter per (tile, h).
+// ---------------------------------------------------------------------------------------------
+constexpr int PSK_TW = 256;
+constexpr int PSK_STAGES = 6;
+constexpr int PSK_STAGE_BYTES = BM * BK * 2 + (PSK_TW / 2) * BK * 2;  // 32 KB
+constexpr int psk_smem_bytes() { return PSK_STAGES * PSK_STAGE_BYTES + 1024 + 256 + EPI_STAGE_BYTES; }
+
+template <int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_pairsplit_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                           const GemmParams p, const int splits) {
+  constexpr int STAGES = PSK_STAGES;
+  constexpr int HALF = PSK_TW / 2;
+  constexpr int A_BYTES = BM * BK * 2;
+  constexpr int STAGE_BYTES = PSK_STAGE_BYTES;
+  constexpr uint32_t TMEM_COLS = PSK_TW;
+  constexpr uint32_t IDESC = umma_idesc(256, PSK_TW, 1);
+  constexpr bool GATED = EPI == EPI_GATED_SILU || EPI == EPI_GATED_GELU;
+  constexpr int UW = GATED ? 64 : 32;
+  constexpr int U = PSK_TW / UW;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
+  auto full_bar = [&](int s) { return bar_base + 8 * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8 * (STAGES + s); };
+  const uint32_t tfull_bar = bar_base + 8 * (2 * STAGES);
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int abort_flag;
+  __shared__ int spk_ok;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t half = cluster_ctarank();          // 0 = leader
+  const int pair = blockIdx.x >> 1;                  // (m block, tile, split)
+  const int per_m = p.num_n_blocks * splits;
+  const int mb = pair / per_m;
+  const int tile = (pair - mb * per_m) / splits, split = pair - mb * per_m - tile * splits;
+  const int m0 = mb * 256;
+  const int n0 = tile * PSK_TW;
+  const int kb_total = (p.K + BK - 1) / BK;
+  const int kb_per = (kb_total + splits - 1) / splits;
+  const int kb0 = split * kb_per;
+  const int nk = max(min(kb_total, kb0 + kb_per) - kb0, 0);
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    mbar_init(tfull_bar, 1);
+    fence_barrier_init();
+  }
+  if (warp == 0) {
+    tmem_alloc_pair(smem_u32(&tmem_base_slot), TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {  // ---- TMA producer (both CTAs; transaction bytes are counted on the leader's barrier) ----
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      const int wrow = n0 + (int)half * HALF;
+      const int pre = min(nk, STAGES);
+      for (int i = 0; i < pre; ++i) {  // weights first: they do not depend on the previous kernel
+        if (half == 0) mbar_expect_tx(full_bar(i), 2 * STAGE_BYTES);
+        tma_load_2d_pair(smem_base + i * STAGE_BYTES + A_BYTES, &tmB, map_to_cta(full_bar(i), 0), (kb0 + i) * BK, wrow);
+      }
+      pdl_wait();
+      for (int i = 0; i < pre; ++i)
+        tma_load_2d_pair(smem_base + i * STAGE_BYTES, &tmA, map_to_cta(full_bar(i), 0), (kb0 + i) * BK,
+                         m0 + (int)half * BM);
+      int stage = pre == STAGES ? 0 : pre;
+      uint32_t phase = pre == STAGES ? 1 : 0;
+      for (int i = pre; i < nk; ++i) {
+        const int kb = kb0 + i;
+        mbar_wait(empty_bar(stage), phase ^ 1, &abort_flag, p.status, 35);
+        const uint32_t sa = smem_base + stage * STAGE_BYTES;
+        const uint32_t lead_full = map_to_cta(full_bar(stage), 0);
+        if (half == 0) mbar_expect_tx(full_bar(stage), 2 * STAGE_BYTES);
+        tma_load_2d_pair(sa + A_BYTES, &tmB, lead_full, kb * BK, wrow);
+        tma_load_2d_pair(sa, &tmA, lead_full, kb * BK, m0 + (int)half * BM);
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+    } else {
+      pdl_wait();
+    }
+  } else if (warp == 1) {
+    pdl_wait();
+    if (lane == 0 && half == 0) {  // ---- MMA issuer of the pair ----
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int i = 0; i < nk; ++i) {
+        mbar_wait(full_bar(stage), phase, &abort_flag, p.status, 36);
+        tc_fence_after();
+        const uint32_t sa = smem_base + stage * STAGE_BYTES;
+        const uint64_t da = umma_smem_desc_sw128(sa);
+        const uint64_t db = umma_smem_desc_sw128(sa + A_BYTES);
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k) umma_bf16_pair(tmem_base, da + 2 * k, db + 2 * k, IDESC, (i | k) != 0);
+        umma_commit_pair(empty_bar(stage));
+        umma_commit_pair(map_to_cta(empty_bar(stage), 1));
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+      umma_commit_pair(tfull_bar);
+      umma_commit_pair(map_to_cta(tfull_bar, 1));
+    }
+  } else {
+    pdl_wait();
+    const int lane_grp = warp & 3;
+    const int erow = lane_grp * 32 + lane;
+    const int etid = threadIdx.x - 64;
+    if (nk > 0) mbar_wait(tfull_bar, 0, &abort_flag, p.status, 37);
+    tc_fence_after();
+    const int row = m0 + (int)half * BM + erow;
+    const bool row_ok = row < p.M;
+    const uint32_t t_lane = tmem_base + ((uint32_t)(lane_grp * 32) << 16);
+    const int row_block = mb * 2 + (int)half;
+    if (splits == 1) {
+      uint8_t* epi_stage = smem_raw + (bar_base + 256 - smem_u32(smem_raw)) + lane_grp * EPI_WARP_BYTES;
+      epilogue_store<PSK_TW, EPI>(p, t_lane, row, row_ok, n0, false, [](uint32_t*, int) {}, epi_stage);
+      if (EPI == EPI_STORE) push_signal(p, row_block, max(0, min(PSK_TW, p.N - n0)));
+    } else {
+      // workspace slot of CTA (m block, tile, half, split): U units of [UW columns][128 rows] floats
+      const int64_t slot0 = ((int64_t)(mb * p.num_n_blocks + tile) * 2 + half) * splits;
+      float* ws_mine = p.sk_partials + (slot0 + split) * (int64_t)(PSK_TW * BM);
+      uint32_t* counter = reinterpret_cast<uint32_t*>(p.sk_counters) + (mb * p.num_n_blocks + tile) * 2 + half;
+      if (nk > 0) {
+#pragma unroll 1
+        for (int u = 0; u < U; ++u) {
+          if (u % splits == split) continue;
+          float* dst = ws_mine + (int64_t)u * (UW * BM) + erow;
+#pragma unroll 1
+          for (int cc = 0; cc < UW; cc += 32) {
+            uint32_t r[32];
+            tmem_ld_32x32(t_lane + u * UW + cc, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) __stcg(dst + (cc + j) * BM, __uint_as_float(r[j]));
+          }
+        }
+      }
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (etid == 0) {
+        const uint32_t prev = atomicAdd(counter, 1u);
+        const uint32_t target = (prev / (uint32_t)splits + 1u) * (uint32_t)splits;
+        int ok = 1;
+        uint64_t t0 = 0;
+        for (uint32_t spin = 0;; ++spin) {
+          uint32_t v;
+          asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
+          if ((int32_t)(v - target) >= 0) break;
+          if ((spin & 0xff) == 0xff) {
+            const uint64_t now = global_timer_ns();
+            if (t0 == 0) {
+              t0 = now;
+            } else if (now - t0 > 1000000000ull) {
+              if (p.status) atomicCAS(p.status, 0, 38);
+              ok = 0;
+              break;
+            }
+          }
+        }
+        spk_ok = ok;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      __threadfence();
+      int pushed = 0;
+      if (spk_ok) {
+#pragma unroll 1
+        for (int u = split; u < U; u += splits) {
+          uint32_t r[GATED ? 64 : 32];
+#pragma unroll
+          for (int cc = 0; cc < UW; cc += 32) {
+            if (nk > 0) {
+              tmem_ld_32x32(t_lane + u * UW + cc, r + cc);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) r[cc + j] = 0u;
+            }
+          }
+          tmem_wait_ld();
+          for (int s2 = 0; s2 < splits; ++s2) {
+            if (s2 == split) continue;
+            if (min(kb_total, s2 * kb_per + kb_per) - s2 * kb_per <= 0) continue;
+            const float* src = p.sk_partials + (slot0 + s2) * (int64_t)(PSK_TW * BM) + (int64_t)u * (UW * BM) + erow;
+#pragma unroll
+            for (int j = 0; j < UW; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __ldcg(src + j * BM));
+          }
+          const int col0 = n0 + u * UW;
+          if (GATED) {
+            if (row_ok && col0 < p.N) {
+              bf16* crow = (bf16*)p.C + (int64_t)row * p.ldc + col0 / 2;
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                float o[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                  const float gv = __uint_as_float(r[j + e]), uv = __uint_as_float(r[32 + j + e]);
+                  o[e] = (EPI == EPI_GATED_SILU ? silu_f(gv) : gelu_tanh_f(gv)) * uv;
+                }
+                *reinterpret_cast<bf16x8*>(crow + j) = pack8(o);
+              }
+            }
+          } else {
+            epi_direct32<EPI>(p, r, row, row_ok, col0);
+            pushed += max(0, min(32, p.N - col0));
+          }
+        }
+      }
+      if (EPI == EPI_STORE && p.push_world > 0) push_signal(p, row_block, pushed);
+    }
+    tc_fence_before();
+  }
+
+  __syncthreads();
+  cluster_sync_all();  // the leader's MMAs read the peer's shared memory and commit into its barriers
+  if (warp == 0) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int EPI>
+int launch_pairsplit(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p_in, int splits, cudaStream_t st) {
+  GemmParams p = p_in;
+  p.num_m_blocks = cdiv(p.M, 256);
+  p.num_n_blocks = cdiv(p.N, PSK_TW);
+  static DeviceOnce configured;
+  if (!configured.done()) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_pairsplit_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         psk_smem_bytes());
+    if (e != cudaSuccess) return (int)e;
+    configured.set();
+  }
+  cudaError_t le = launch_pdl(gemm_bf16_pairsplit_kernel<EPI>, dim3(2 * p.num_m_blocks * p.num_n_blocks * splits),
+                              dim3(GEMM_THREADS), psk_smem_bytes(), st, ta, tb, p, splits);
+  return le == cudaSuccess ? LLB_OK : (int)le;
+}
+
+int dispatch_pairsplit(int epi, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int splits,
+                       cudaStream_t st) {
+  switch (epi) {
+    case EPI_STORE: return launch_pairsplit<EPI_STORE>(ta, tb, p, splits, st);
+    case EPI_RESIDUAL: return launch_pairsplit<EPI_RESIDUAL>(ta, tb, p, splits, st);
+    case EPI_GATED_SILU: return launch_pairsplit<EPI_GATED_SILU>(ta, tb, p, splits, st);
+    case EPI_GATED_GELU: return launch_pairsplit<EPI_GATED_GELU>(ta, tb, p, splits, st);
+    case EPI_F32: return launch_pairsplit<EPI_F32>(ta, tb, p, splits, st);
+  }
+  return LLB_ERR_UNSUPPORTED;
+}
+
+// Largest usable split count of the pair split-K kernel (0: the shape does not fit it): every split needs a
+// k-block, the units of a tile must divide among the splits, and all CTAs must be resident at once.
+int pairsplit_max_splits(int M, int N, int K, int epi) {
+  if ((N % 8) != 0) return 0;
+  const bool gated = epi == EPI_GATED_SILU || epi == EPI_GATED_GELU;
+  const int units = gated ? 4 : 8;
+  const int pairs = cdiv(M, 256) * cdiv(N, PSK_TW), kb = cdiv(K, BK);
+  if (pairs * 2 > sm_count() || pairs * 2 > SPK_MAX_TILES) return 0;
+  int s = 1;
+  while (s * 2 <= units && pairs * 2 * s * 2 <= sm_count() && (int64_t)cdiv(kb, s * 2) * (s * 2 - 1) < kb) s *= 2;
+  return s;
+}
+
+// Largest usable split count for the split-K kernel (0: the shape does not fit it).
+int splitk_max_splits(int M, int N, int K, int epi) {
+  if (M > 256 || (N % 8) != 0) return 0;
+  const bool gated = epi == EPI_GATED_SILU || epi == EPI_GATED_GELU;
+  const int mblk = M > 128 ? 2 : 1;
+  const int units = mblk * (gated ? 2 : 4);
+  const int tiles = cdiv(N, SPK_BN), kb = cdiv(K, BK);
+  if (tiles > sm_count() || tiles > SPK_MAX_TILES) return 0;
+  int s = 1;
+  while (s * 2 <= units && tiles * s * 2 <= sm_count() && (int64_t)cdiv(kb, s * 2) * (s * 2 - 1) < kb) s *= 2;
+  return s;
+}
+
 // one-shot configuration of the next llb_gemm_bf16 call (set by llb_gemm_set_push, cleared by the call)
 struct PushCfg {
   bf16* push[8];
@@ -1346,7 +1931,7 @@ LLB_EXPORT int llb_gemm_bf16(const void* A, int64_t lda, const void* W, int64_t 
     int sk_bn = bn ? bn : (N >= 256 ? 256 : (N >= 128 ? 128 : 64));
     int64_t tiles = (int64_t)cdiv(M, BM) * cdiv(N, sk_bn);
     bool fits = sk_partials != nullptr && sk_counters != nullptr &&
-                sk_partials_floats >= (int64_t)sm_count() * 2 * BM * sk_bn && sk_counters_len >= tiles;
+                sk_partials_floats >= (int64_t)sm_count() * 2 * BM * sk_bn && sk_counters_len >= tiles && tiles <= 8192;
     bool want = stream_k == 1 || (tiles < 3ll * sm_count() && tiles % sm_count() != 0 && kblocks >= 4);
     if (fits && want) {
       stream_k = 1;
@@ -1355,6 +1940,79 @@ LLB_EXPORT int llb_gemm_bf16(const void* A, int64_t lda, const void* W, int64_t 
       if (stream_k == 1 && !fits) return LLB_ERR_BAD_ARG;
       stream_k = 0;
     }
+  }
+  // split-K kernel without clusters: explicit (bn = 2000 + splits, 2000 = as many splits as fit)
+  if (bn >= 2000 && bn < 2100) {
+    int splits = bn - 2000;
+    const int smax = splitk_max_splits(M, N, K, epi);
+    if (smax == 0 || ldw < 0 || stream_k != 0) return LLB_ERR_UNSUPPORTED;
+    if (splits == 0) splits = smax;
+    if (splits > smax || (splits & (splits - 1)) != 0) return LLB_ERR_UNSUPPORTED;
+    const int mblk = M > 128 ? 2 : 1;
+    const int tiles = cdiv(N, SPK_BN);
+    int log2s = 0;
+    while ((1 << log2s) < splits) ++log2s;
+    if (splits > 1 && (sk_partials == nullptr || sk_counters == nullptr ||
+                       sk_partials_floats < (int64_t)tiles * splits * mblk * BM * SPK_BN ||
+                       sk_counters_len < 8192 + 4 * SPK_MAX_TILES))
+      return LLB_ERR_BAD_ARG;
+    CUtensorMap ta, tb;
+    int rc = cached_tmap(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM);
+    if (rc) return rc;
+    rc = cached_tmap(&tb, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, SPK_BN);
+    if (rc) return rc;
+    GemmParams p;
+    memset(&p, 0, sizeof(p));
+    apply_push(p);
+    if (p.push_world > 0 && (epi != EPI_STORE || (N % 32))) return LLB_ERR_UNSUPPORTED;
+    p.C = C;
+    p.residual = (const bf16*)residual;
+    p.bias = (const bf16*)bias;
+    p.status = status;
+    p.M = M;
+    p.N = N;
+    p.K = K;
+    p.ldc = ldc;
+    p.batch_count = 1;
+    p.sk_partials = sk_partials;
+    p.sk_counters = sk_counters ? sk_counters + 8192 + log2s * SPK_MAX_TILES : nullptr;
+    return mblk == 2 ? dispatch_splitk<2>(epi, ta, tb, p, splits, st) : dispatch_splitk<1>(epi, ta, tb, p, splits, st);
+  }
+  // the same split on CTA-pair tiles: explicit (bn = 3000 + splits, 3000 = as many splits as fit)
+  if (bn >= 3000 && bn < 3100) {
+    int splits = bn - 3000;
+    const int smax = pairsplit_max_splits(M, N, K, epi);
+    if (smax == 0 || ldw < 0 || stream_k != 0) return LLB_ERR_UNSUPPORTED;
+    if (splits == 0) splits = smax;
+    if (splits > smax || (splits & (splits - 1)) != 0) return LLB_ERR_UNSUPPORTED;
+    const int pairs = cdiv(M, 256) * cdiv(N, PSK_TW);
+    int log2s = 0;
+    while ((1 << log2s) < splits) ++log2s;
+    if (splits > 1 && (sk_partials == nullptr || sk_counters == nullptr ||
+                       sk_partials_floats < (int64_t)pairs * 2 * splits * BM * PSK_TW ||
+                       sk_counters_len < 8192 + 4 * SPK_MAX_TILES))
+      return LLB_ERR_BAD_ARG;
+    CUtensorMap ta, tb;
+    int rc = cached_tmap(&ta, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM);
+    if (rc) return rc;
+    rc = cached_tmap(&tb, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, PSK_TW / 2);
+    if (rc) return rc;
+    GemmParams p;
+    memset(&p, 0, sizeof(p));
+    apply_push(p);
+    if (p.push_world > 0 && (epi != EPI_STORE || (N % 32))) return LLB_ERR_UNSUPPORTED;
+    p.C = C;
+    p.residual = (const bf16*)residual;
+    p.bias = (const bf16*)bias;
+    p.status = status;
+    p.M = M;
+    p.N = N;
+    p.K = K;
+    p.ldc = ldc;
+    p.batch_count = 1;
+    p.sk_partials = sk_partials;
+    p.sk_counters = sk_counters ? sk_counters + 8192 + log2s * SPK_MAX_TILES : nullptr;
+    return dispatch_pairsplit(epi, ta, tb, p, splits, st);
   }
   // skinny (decode) kernel: explicit (bn = 1000 + 10 * nb + splits) or chosen for M <= 256
   int sk_nb = 0, sk_splits = 0, sk_tw = 256;

@@ -174,8 +174,9 @@ def _stream_k_scratch(device):
     cur = _sk_scratch.get(key)
     if cur is None:
         sms = torch.cuda.get_device_properties(device).multi_processor_count
+        # counters: [0, 8192) stream-K tiles (self-resetting); [8192, 16384) arrival counters of the split-K kernel
         cur = (torch.empty(sms * 2 * 128 * 256, dtype=torch.float32, device=device),
-               torch.zeros(8192, dtype=torch.int32, device=device))
+               torch.zeros(16384, dtype=torch.int32, device=device))
         _sk_scratch[key] = cur
     return cur
 
@@ -262,7 +263,7 @@ def gemm(a, w, epi: str = "store", residual=None, bias=None, out=None, bn: int =
         out = torch.empty((M, n_out), dtype=torch.float32 if epi == "f32" else a.dtype, device=a.device)
     if epi == "residual":
         assert residual.shape == out.shape and residual.stride(0) == out.stride(0)
-    skp, skc = (None, None) if stream_k == 0 else _stream_k_scratch(a.device)
+    skp, skc = (None, None) if (stream_k == 0 and not 2000 <= bn < 3100) else _stream_k_scratch(a.device)
     check(kernels().llb_gemm_bf16(ptr(a), i64(a.stride(0)), ptr(w), i64(ldw), ptr(out), i64(out.stride(0)),
                                   ptr(residual), ptr(bias), c_int(M), c_int(N), c_int(K), c_int(EPI_CODES[epi]),
                                   c_int(bn), c_int(stream_k), ptr(skp), i64(skp.numel() if skp is not None else 0),

@@ -161,8 +161,10 @@ def tune(candidates: Sequence[dict], bench: Callable[[dict], float], group=None)
 # ------------------------------------------------------------------ bf16 GEMM
 GEMM_KERNEL = "gemm_bf16"
 # `bn` selectors understood by ops.gemm: 0 automatic plan, 64 / 128 / 256 one-CTA tiles, 512 CTA-pair tiles,
-# 1000 + 10 * accumulators + splits cluster kernel (+ 100: 128-column tiles)
-GEMM_CANDIDATES = [{"bn": b} for b in (0, 64, 128, 256, 512, 1011, 1012, 1014, 1021, 1111, 1112)]
+# 1000 + 10 * accumulators + splits cluster kernel (+ 100: 128-column tiles), 2000 + splits one-CTA tiles and
+# 3000 + splits CTA-pair tiles with K split through the L2 workspace (x000: as many splits as fit)
+GEMM_CANDIDATES = [{"bn": b} for b in (0, 64, 128, 256, 512, 1011, 1012, 1014, 1021, 1111, 1112,
+                                       2000, 2002, 2004, 3000, 3001, 3002, 3004)]
 
 
 def gemm_static_key(N: int, K: int, epi: str) -> str:
@@ -182,7 +184,7 @@ def tune_gemm(M: int, N: int, K: int, epi: str = "store", group=None, reps: int 
 
     from .. import ops
     from ..ops import reference as ref
-    from .gemm_bench import timeit_graph
+    from ..benchmark.gemm_bench import timeit_graph
 
     dev = torch.device("cuda")
     copies = max(1, min(reps, int((1 << 30) // max((M * K + N * K) * 2, 1))))
@@ -238,6 +240,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", default="llama3-8b", help="a name known to bench.py or a directory with config.json")
     ap.add_argument("--tp", type=int, default=1)
+    ap.add_argument("--ms", default="1,8,16,32,64,128,192,256", help="row counts (decode batch sizes) to tune")
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--out", default=None, help="directory for the JSON table (default: the user cache)")
     a = ap.parse_args()
@@ -253,7 +256,7 @@ def main():
                    "llama3-70b": dict(hidden_size=8192, num_attention_heads=64, num_key_value_heads=8,
                                       intermediate_size=28672, vocab_size=128256)}
         cfg = presets[a.model]
-    tune_model(cfg, a.tp, force=a.force)
+    tune_model(cfg, a.tp, Ms=[int(x) for x in a.ms.split(",")], force=a.force)
 
 
 if __name__ == "__main__":
