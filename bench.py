@@ -191,7 +191,12 @@ def main():
         prefill_meta.append((s, e, pin(req_ids[s:e].clone()), pin(torch.full((B,), in_len, dtype=torch.int32)),
                              pin(torch.zeros(B, dtype=torch.int32))))
 
-    def static_wave(prompts_np):
+    phase_events = []   # (wave start, prefill done, wave done) CUDA events of the timed waves
+
+    def static_wave(prompts_np, mark=False):
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(3)] if (mark and cuda) else None
+        if evs:
+            evs[0].record()
         mm = model.mem_manager
         mm.free_all()
         slots = mm.alloc(conc * total_len).clone().view(conc, total_len)
@@ -209,6 +214,8 @@ def main():
             out = model.forward(mi)
             tok, _ = ops.sample(out.logits_any)
             ops.scatter_next_token_(nxt, tok, dev_req[s:e])
+        if evs:
+            evs[1].record()
         for t in range(1, out_len):
             L = in_len + t
             mi = ModelInput(batch_size=conc, total_token_num=conc * L, max_kv_len=L, is_prefill=False, b_req_idx=b_req,
@@ -216,6 +223,9 @@ def main():
             out = model.forward(mi)
             tok, _ = ops.sample(out.logits_any)
             ops.scatter_next_token_(nxt, tok, dev_req)
+        if evs:
+            evs[2].record()
+            phase_events.append(evs)
         return tok
 
     dev_req = req_ids.to(dev)
@@ -247,10 +257,17 @@ def main():
         (_HostEvent(), _HostEvent())
     ev0.record()
     for _ in range(args.steps):
-        static_wave(new_prompts())
+        static_wave(new_prompts(), mark=True)
     ev1.record()
     barrier()
     dev_ms = ev0.elapsed_time(ev1)
+    phases = None
+    if phase_events:
+        pre = sum(a.elapsed_time(b) for a, b, _ in phase_events) / len(phase_events)
+        dec = sum(b.elapsed_time(c) for _, b, c in phase_events) / len(phase_events)
+        phases = {"prefill_ms_per_step": round(pre, 1), "decode_ms_per_step": round(dec, 1),
+                  "ms_per_decode_pass": round(dec / max(out_len - 1, 1), 3),
+                  "note": "rank 0, device time inside the timed waves"}
     stage(f"timed waves done: {dev_ms / args.steps:.1f} ms/wave")
     launches = ops.launch_count() - n0
     clock_info = clocks.stop()
@@ -300,7 +317,7 @@ def main():
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform-random token ids, random-init weights",
             "impl": "ours",
             "config": bench_config(args),
-            "clocks": clock_info, "gpu_launches": launches, "device_wait_status": status,
+            "clocks": clock_info, "gpu_launches": launches, "device_wait_status": status, "phases": phases,
         }
         if e2e:
             line["e2e"] = {"value": round(out_tokens / e2e_s, 1), "unit": "tokens/s",

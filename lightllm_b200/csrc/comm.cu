@@ -345,6 +345,160 @@ int launch(const CommParams& p, int ranks_in_grid, int ctas, cudaStream_t st) {
 
 }  // namespace
 
+// ---------------------------------------------------------------------------------------------
+// Copy-engine path for prompt-sized reductions.  The bytes of a reduce-scatter / all-gather are moved by
+// cudaMemcpyAsync over NVLink (DMA engines, no SM), so that the transfer can run under the GEMMs of another
+// micro-batch; the kernels here are only the glue: a flag exchange ("my buffer of call e is complete" / "I have
+// seen everybody's") and the local sum of the gathered slices fused with the residual add and the RMSNorm.
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+struct CeFlagPtrs {
+  uint32_t* peer[MAX_WORLD];  // flag array [world] of every rank, as seen from this rank
+};
+
+// Writes `value` into slot `rank` of every rank's flag array (release: everything this stream did before is
+// visible to a peer that sees the flag), then waits until every slot of the local array has reached `value`.
+// The wait is bounded by `timeout_ns` (prompt passes of different ranks can be far apart when a process is still
+// warming up, so the limit is a parameter and longer than the decode kernels' one second); on expiry the code is
+// recorded in `status` and the kernel returns.
+// `mode`: bit 0 = signal, bit 1 = wait (both in a real run; one at a time where several ranks are emulated on one
+// stream, whose kernels run one after the other).
+__global__ void ce_signal_wait_kernel(CeFlagPtrs f, const uint32_t* local, int rank, int world, uint32_t value,
+                                      int* status, int code, uint64_t timeout_ns, int mode) {
+  const int t = threadIdx.x;
+  if (t >= world) return;
+  if (mode & 1) {
+    __threadfence_system();
+    st_release_sys(f.peer[t] + rank, value);
+  }
+  if (!(mode & 2)) return;
+  uint64_t t0 = 0;
+  for (uint32_t spin = 0;; ++spin) {
+    if ((int32_t)(ld_acquire_sys(local + t) - value) >= 0) return;
+    if ((spin & 0x3f) == 0x3f) {
+      if (status && *(volatile int*)status != 0) return;
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > timeout_ns) {
+        if (status) atomicCAS(status, 0, code + t);
+        return;
+      }
+      __nanosleep(128);
+    }
+  }
+}
+
+struct CeReduceParams {
+  const bf16* src[MAX_WORLD];  // [rows, H] partial sums: this rank's own rows and the slices pulled from the peers
+  bf16* residual;              // [rows, H] updated in place
+  bf16* out;                   // [rows, H] normalised rows
+  const bf16* norm_w;
+  int nsrc, rows, H;
+  float eps, w_offset;
+};
+
+template <int MAX_VEC>
+__global__ void __launch_bounds__(256) ce_reduce_norm_kernel(const CeReduceParams p) {
+  __shared__ float red[33];
+  const int nvec = p.H >> 3;
+  for (int row = blockIdx.x; row < p.rows; row += gridDim.x) {
+    float vals[MAX_VEC][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAX_VEC; ++i) {
+      const int v = threadIdx.x + i * 256;
+      if (v < nvec) {
+        const int64_t off = (int64_t)row * p.H + v * 8;
+        uint4 raw[MAX_WORLD];
+#pragma unroll
+        for (int q = 0; q < MAX_WORLD; ++q)
+          if (q < p.nsrc) raw[q] = ld_cg_16(p.src[q] + off);
+        float r[8];
+        unpack8(*reinterpret_cast<const bf16x8*>(p.residual + off), r);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) vals[i][k] = 0.f;
+#pragma unroll
+        for (int q = 0; q < MAX_WORLD; ++q)
+          if (q < p.nsrc) add8(vals[i], raw[q]);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) vals[i][k] += r[k];
+        const bf16x8 sres = pack8(vals[i]);
+        *reinterpret_cast<bf16x8*>(p.residual + off) = sres;
+        unpack8(sres, vals[i]);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) ss += vals[i][k] * vals[i][k];
+      }
+    }
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)p.H + p.eps);
+#pragma unroll
+    for (int i = 0; i < MAX_VEC; ++i) {
+      const int v = threadIdx.x + i * 256;
+      if (v < nvec) {
+        float wf[8], o[8];
+        unpack8(reinterpret_cast<const bf16x8*>(p.norm_w)[v], wf);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) o[k] = vals[i][k] * inv * (wf[k] + p.w_offset);
+        *reinterpret_cast<bf16x8*>(p.out + (int64_t)row * p.H + v * 8) = pack8(o);
+      }
+    }
+    __syncthreads();
+  }
+}
+
+}  // namespace
+
+LLB_EXPORT int llb_ce_signal_wait(void** peer_flags, const void* local_flags, int rank, int world, uint32_t value,
+                                  int* status, int code, int64_t timeout_ms, int mode, cudaStream_t st) {
+  if (world < 1 || world > MAX_WORLD) return LLB_ERR_BAD_ARG;
+  CeFlagPtrs f;
+  for (int q = 0; q < MAX_WORLD; ++q) f.peer[q] = q < world ? (uint32_t*)peer_flags[q] : nullptr;
+  ce_signal_wait_kernel<<<1, 32, 0, st>>>(f, (const uint32_t*)local_flags, rank, world, value, status, code,
+                                          (uint64_t)(timeout_ms > 0 ? timeout_ms : 1000) * 1000000ull, mode);
+  LLB_LAUNCH_CHECK();
+  return LLB_OK;
+}
+
+// residual[rows, H] += sum of the `nsrc` partial slices; out = rmsnorm(residual) * (norm_w + w_offset)
+LLB_EXPORT int llb_ce_reduce_norm(const void** srcs, int nsrc, void* residual, void* out, const void* norm_w, int rows,
+                                  int H, float eps, float w_offset, cudaStream_t st) {
+  if (rows <= 0) return LLB_OK;
+  if (nsrc < 1 || nsrc > MAX_WORLD || H % 8 != 0 || H > 8 * 256 * 8) return LLB_ERR_UNSUPPORTED;
+  CeReduceParams p;
+  memset(&p, 0, sizeof(p));
+  for (int q = 0; q < nsrc; ++q) p.src[q] = (const bf16*)srcs[q];
+  p.residual = (bf16*)residual;
+  p.out = (bf16*)out;
+  p.norm_w = (const bf16*)norm_w;
+  p.nsrc = nsrc;
+  p.rows = rows;
+  p.H = H;
+  p.eps = eps;
+  p.w_offset = w_offset;
+  const int per = cdiv(H / 8, 256);
+  const int grid = rows < 1184 ? rows : 1184;
+  if (per <= 1)
+    ce_reduce_norm_kernel<1><<<grid, 256, 0, st>>>(p);
+  else if (per <= 2)
+    ce_reduce_norm_kernel<2><<<grid, 256, 0, st>>>(p);
+  else if (per <= 4)
+    ce_reduce_norm_kernel<4><<<grid, 256, 0, st>>>(p);
+  else
+    ce_reduce_norm_kernel<8><<<grid, 256, 0, st>>>(p);
+  LLB_LAUNCH_CHECK();
+  return LLB_OK;
+}
+
+// One stream-ordered copy between any two device ranges this process can address (local memory, or a peer's
+// block opened through IPC: the driver routes it over NVLink on a copy engine).
+LLB_EXPORT int llb_memcpy_async(void* dst, const void* src, int64_t bytes, cudaStream_t st) {
+  if (bytes <= 0) return LLB_OK;
+  cudaError_t e = cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyDefault, st);
+  return e == cudaSuccess ? LLB_OK : (int)e;
+}
+
 // ---- symmetric memory helpers (plain cudaMalloc + legacy IPC handles; one process per GPU) ----
 LLB_EXPORT int llb_symm_alloc(void** out, int64_t bytes) {
   cudaError_t e = cudaMalloc(out, (size_t)bytes);

@@ -46,6 +46,7 @@ class LLM:
                         disk_cache_bytes=int(model_kw.pop("disk_cache_bytes", 0)),
                         linear_att_hash_page_size=int(model_kw.pop("linear_att_hash_page_size", 512)))
         tp_fused = model_kw.pop("tp_fused", None)
+        no_pipeline = bool(model_kw.pop("disable_prefill_pipeline", False))
         if tp_fused is None and self.ps.tp_size > 1 and self.ps.device.type == "cuda" \
                 and not model_kw.pop("disable_fused_tp", False):
             from ..parallel.fused import FusedTP
@@ -58,6 +59,10 @@ class LLM:
                                batch_max_tokens=batch_max_tokens, disable_cudagraph=disable_cudagraph,
                                graph_max_batch_size=graph_max_batch_size or running_max_req_size,
                                graph_max_len_in_batch=max_req_total_len + 8, **model_kw)
+        if tp_fused is not None and not no_pipeline:
+            from ..parallel import ce as _ce
+
+            _ce.attach(self.model, self.ps, batch_max_tokens, log=None)
         self.args = BackendArgs(batch_max_tokens=batch_max_tokens,
                                 chunked_prefill_size=chunked_prefill_size or max(batch_max_tokens // 2, 1),
                                 eos_ids=tuple(eos_ids), max_req_total_len=max_req_total_len,
@@ -103,6 +108,10 @@ class LLM:
             torch.cuda.synchronize(self.model.device)
         self.model.flush_graphs()
         fused = getattr(self.model.tp, "fused", None)
+        ce = getattr(self.model.tp, "ce", None)
+        if ce is not None:
+            self.model.tp.ce = None
+            ce.close()
         if fused is not None:
             fused.check()
             self.model.tp.fused = None

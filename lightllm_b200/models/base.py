@@ -403,7 +403,8 @@ class TransformerLM:
         return self._decode(mi)
 
     # ---- prefill ----
-    def _prefill(self, mi: ModelInput) -> ModelOutput:
+    def _build_prefill_state(self, mi: ModelInput):
+        """Stages a prompt pass' index tensors and runs the step prologue: (state, input ids on the device)."""
         dev = self.device
         B = mi.batch_size
         b_req_idx = mi.b_req_idx.to(dev, non_blocking=True)
@@ -430,17 +431,132 @@ class TransformerLM:
         st.extra["verify_pass"] = bool(getattr(mi, "verify_pass", False))
         st.extra["want_hidden"] = bool(mi.return_hidden)
         self._prepare_prefill_state(st)
+        return st, input_ids
+
+    def _last_rows(self, h, st: InferState, all_rows: bool):
+        if all_rows:
+            return h
+        B = st.batch_size
+        last_idx = (st.cu_q[1:] - 1).to(torch.int32)
+        last = torch.empty((B, self.hidden), dtype=h.dtype, device=self.device)
+        ops.copy_rows(last, h, None, last_idx, B)
+        return last
+
+    def _prefill(self, mi: ModelInput) -> ModelOutput:
+        halves = self._split_for_pipeline(mi)
+        if halves is not None:
+            return self._prefill_pipelined(mi, halves)
+        st, input_ids = self._build_prefill_state(mi)
         h = self._embed(input_ids, st)
         h = self._layers_forward(h, st)
         hidden = h if mi.return_hidden else None
-        if mi.return_all_logits:
-            last = h
-        else:
-            last_idx = (cu_q[1:] - 1).to(torch.int32)
-            last = torch.empty((B, self.hidden), dtype=h.dtype, device=dev)
-            ops.copy_rows(last, h, None, last_idx, B)
+        last = self._last_rows(h, st, mi.return_all_logits)
         logits = self._lm_head(last, normed=True) if st.extra.get("normed") else self._lm_head(last)
         return ModelOutput(logits=logits, hidden=hidden)
+
+    # ---- prompt passes as two micro-batches whose reductions run under each other's GEMMs ----
+    PIPELINE_MIN_TOKENS = 2048   # below this the pass is latency-bound and the fused kernels are faster
+
+    def _split_for_pipeline(self, mi: ModelInput):
+        """Two ModelInputs (a split of the requests with balanced token counts) when this pass qualifies for the
+        pipelined schedule: tensor parallelism on GPUs with a copy-engine reducer attached, a plain decoder stack
+        (no family hook between the layers, no multimodal rows, no hidden states wanted back), at least two
+        requests and enough tokens for the transfers to matter."""
+        ce = getattr(self.tp, "ce", None)
+        if ce is None or self.tp.size == 1 or mi.batch_size < 2 or mi.multimodal_params or mi.return_hidden \
+                or mi.draft_input_hidden is not None or getattr(mi, "verify_pass", False) or ce.hidden != self.hidden:
+            return None
+        cls = type(self)
+        base = TransformerLM
+        if any(getattr(cls, f) is not getattr(base, f) for f in
+               ("_layers_forward", "_after_layer", "_prepare_prefill_state", "_embed", "_attention_block",
+                "_row_parallel", "_reduce_partial")):
+            return None
+        q_len = (mi.b_q_len if mi.b_q_len is not None else (mi.b_seq_len - mi.b_ready_cache_len)).to(torch.int64)
+        T = int(q_len.sum())
+        if T < self.PIPELINE_MIN_TOKENS or T != mi.input_ids.shape[0]:
+            return None
+        cum = torch.cumsum(q_len, 0)
+        b0 = int(torch.searchsorted(cum, torch.tensor(T // 2), right=False)) + 1
+        b0 = max(1, min(mi.batch_size - 1, b0))
+        t0 = int(cum[b0 - 1])
+        if max(t0, T - t0) > ce.max_tokens:
+            return None
+        out = []
+        for lo, hi, tlo, thi in ((0, b0, 0, t0), (b0, mi.batch_size, t0, T)):
+            seq, rdy = mi.b_seq_len[lo:hi], mi.b_ready_cache_len[lo:hi]
+            ql = mi.b_q_len[lo:hi] if mi.b_q_len is not None else None
+            qn = (ql if ql is not None else (seq - rdy))
+            out.append(ModelInput(batch_size=hi - lo, total_token_num=int(seq.sum()), max_kv_len=int(seq.max()),
+                                  is_prefill=True, b_req_idx=mi.b_req_idx[lo:hi], b_seq_len=seq,
+                                  mem_indexes=mi.mem_indexes[tlo:thi], input_ids=mi.input_ids[tlo:thi],
+                                  b_ready_cache_len=rdy, b_q_len=ql, max_q_len=int(qn.max()),
+                                  return_all_logits=mi.return_all_logits))
+        return out
+
+    def _prefill_pipelined(self, mi: ModelInput, halves) -> ModelOutput:
+        """The layer stack over two micro-batches A and B.  Compute (attention, GEMMs) runs on the current stream
+        in the order A, B, A, B ...; every row-parallel GEMM is followed by a copy-engine reduction
+        (`parallel.ce.CopyEngineTP`: reduce-scatter, residual + RMSNorm on the owned rows, all-gather) queued on a
+        side stream, so the reduction of one micro-batch moves its bytes while the other micro-batch computes.
+        The residual stream is token-sharded inside the pass (each rank keeps its rows up to date) and the last
+        reduction applies the final norm.  Reference: the two-micro-batch overlap of
+        lightllm/common/basemodel/basemodel.py:757-945 (there for the expert-parallel path)."""
+        ce = self.tp.ce
+        dev = self.device
+        comp = torch.cuda.current_stream(dev)
+        if getattr(self, "_ce_stream", None) is None:
+            self._ce_stream = torch.cuda.Stream(device=dev)
+        comm = self._ce_stream
+        comm.wait_stream(comp)
+        sts, res, h = [], [], []
+        for m in halves:
+            st, ids = self._build_prefill_state(m)
+            x = self._embed(ids, st)
+            sts.append(st)
+            res.append(x)
+            h.append(ops.rmsnorm(x, self.layers[0].in_norm, self.eps, self.norm_w_offset))
+        ready = [None, None]          # event after which h[m] may be read on the compute stream
+        n = self.num_layers
+
+        def reduce_on_side_stream(m, partial, norm_w):
+            ev = torch.cuda.Event()
+            ev.record(comp)
+            with torch.cuda.stream(comm):
+                comm.wait_event(ev)
+                out = ce.reduce(partial, res[m], norm_w, self.eps, self.norm_w_offset)
+                done = torch.cuda.Event()
+                done.record(comm)
+            h[m], ready[m] = out, done
+
+        for i, lw in enumerate(self.layers):
+            for m in (0, 1):
+                if ready[m] is not None:
+                    comp.wait_event(ready[m])
+                a = self._attention_block(i, lw, h[m], sts[m])
+                partial = ops.gemm(a, lw.o_w, epi="store", bias=lw.o_b, out=ce.partial_out(a.shape[0]))
+                reduce_on_side_stream(m, partial, lw.post_norm)
+            nxt = self.layers[i + 1].in_norm if i + 1 < n else self.final_norm_w
+            for m in (0, 1):
+                comp.wait_event(ready[m])
+                f = self._ffn_block(i, lw, h[m], sts[m])
+                T = h[m].shape[0]
+                if f[0] == "rowpar":
+                    partial = ops.gemm(f[1], f[2], epi="store", out=ce.partial_out(T))
+                else:
+                    partial = ce.partial_out(T)
+                    partial.copy_(f[1])
+                reduce_on_side_stream(m, partial, nxt)
+        logits = []
+        for m in (0, 1):
+            comp.wait_event(ready[m])
+            last = self._last_rows(h[m], sts[m], mi.return_all_logits)
+            logits.append(self._lm_head(last, normed=True))
+        if isinstance(logits[0], ShardedLogits):
+            out = ShardedLogits(torch.cat([logits[0].local, logits[1].local], 0), self.tp, logits[0].v0, self.vocab)
+        else:
+            out = torch.cat(logits, 0)
+        return ModelOutput(logits=out)
 
     # ---- decode ----
     def graph_batch_sizes(self) -> List[int]:

@@ -30,6 +30,7 @@ class TPContext:
         self.group = st.tp_group
         self.device = st.device
         self.fused = fused  # parallel.fused.FusedTP or None
+        self.ce = None      # parallel.ce.CopyEngineTP (pipelined prompt passes), attached after the model is built
 
     # ---- primitives ----
     def all_reduce_(self, x):

@@ -87,6 +87,10 @@ def _build_model_and_backend(args: StartArgs, ps):
                       linear_att_ssm_data_type=getattr(args, "linear_att_ssm_data_type", "float32"),
                       kv_quant_calibration_config_path=getattr(args, "kv_quant_calibration_config_path", None),
                       tpsp_mix_mode=bool(getattr(args, "enable_tpsp_mix_mode", False)))
+    if fused is not None:   # prompt passes as two micro-batches with copy-engine reductions
+        from ...parallel import ce as _ce
+
+        _ce.attach(model, ps, args.batch_max_tokens)
     eos = args.eos_ids or args.eos_id or cfg.get("eos_token_id") or []
     eos = tuple(eos) if isinstance(eos, (list, tuple)) else (eos,)
     bargs = BackendArgs(batch_max_tokens=args.batch_max_tokens, chunked_prefill_size=args.chunked_prefill_size,

@@ -64,8 +64,17 @@ def test_tp_reduce_norm_emulated(dev, world, T, H, one_shot):
 
 
 @pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("T,N,K,bn", [(200, 1024, 2048, b) for b in (2002, 2004, 2008, 3002, 3004, 3008)] +
+                         [(256, 4096, 2048, b) for b in (2002, 2004, 3002, 3004)])
+def test_split_k_gemm_push_then_pushed_reduce_emulated(dev, world, T, N, K, bn):
+    """The split-K kernels' push epilogue (finished units stored into every rank's slot, columns counted per
+    128-row block) feeds the pushed reduction like the tile kernels' does."""
+    test_gemm_push_then_pushed_reduce_emulated(dev, world, T, N, K, bn)
+
+
+@pytest.mark.parametrize("world", [2, 4])
 @pytest.mark.parametrize("T,N,K", [(200, 1024, 512), (256, 4096, 2048), (37, 2048, 4096), (700, 1024, 1024)])
-def test_gemm_push_then_pushed_reduce_emulated(dev, world, T, N, K):
+def test_gemm_push_then_pushed_reduce_emulated(dev, world, T, N, K, bn=0):
     """GEMM epilogue in push mode (tiles stored into every rank's gather slot + column counters) followed by the
     reduce kernel in pushed mode; the ranks are slices of one GPU, run over three rounds without resetting."""
     from lightllm_b200 import ops
@@ -88,7 +97,7 @@ def test_gemm_push_then_pushed_reduce_emulated(dev, world, T, N, K):
                                              _ptr_array([cnt[q].data_ptr() for q in range(world)]), ctypes.c_int(r),
                                              ctypes.c_int(world), ctypes.c_int(max_mb))
             assert rc == 0
-            ops.gemm(acts[r], ws[r], out=gather[r][r])
+            ops.gemm(acts[r], ws[r], out=gather[r][r], bn=bn)
         out = [torch.empty(T, N, dtype=BF, device=dev) for _ in range(world)]
         rc = kernels().llb_tp_reduce_norm(
             _ptr_array([gather[r][q].data_ptr() for r in range(world) for q in range(world)]), dummy_tab, dummy_tab,
@@ -158,3 +167,45 @@ def test_tpsp_reduce_emulated(dev, world, T, H):
                 assert (residual[r][own].float() - want_res[own]).abs().max().item() < 6e-2
             assert (sums[r][par, :T].float() - want_out).abs().max().item() < 6e-2
             assert int(local[r][0].item()) == call + 1
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("T,H", [(4096, 4096), (1000, 2048), (5, 4096), (2047, 8192)])
+def test_copy_engine_reduce_emulated(dev, world, T, H):
+    """The copy-engine reduction (flag exchange, slice pulls with cudaMemcpyAsync, local sum + residual + RMSNorm,
+    pull of the normalised rows) with all ranks living on one GPU: the three phases of a call are run rank by
+    rank, which is the order real ranks reach them in."""
+    from lightllm_b200.parallel.ce import CopyEngineTP
+
+    torch.manual_seed(5)
+    maxT = 4096
+    total = CopyEngineTP.layout(maxT, H)[1]
+    regions = [torch.zeros(total, dtype=torch.uint8, device=dev) for _ in range(world)]
+    ptrs = [r.data_ptr() for r in regions]
+    ranks = [CopyEngineTP(r, world, maxT, H, dev, ptrs, ptrs[r]) for r in range(world)]
+    w = (torch.randn(H, device=dev) * 0.1 + 1).to(BF)
+    res0 = torch.randn(T, H, device=dev).to(BF)
+    residual = [res0.clone() for _ in range(world)]
+    want_res = res0.float().clone()
+    for call in range(4):
+        parts = [(torch.randn(T, H, device=dev) * 0.5).to(BF) for _ in range(world)]
+        for r in range(world):
+            ranks[r].partial_out(T).copy_(parts[r])
+        for mode in (1, 2):          # everybody announces, then everybody waits
+            for r in range(world):
+                ranks[r].phase_ready(mode)
+        for r in range(world):
+            ranks[r].phase_scatter_reduce(T, residual[r], w, 1e-5)
+        for mode in (1, 2):
+            for r in range(world):
+                ranks[r].phase_normed(mode)
+        outs = [ranks[r].phase_gather(T) for r in range(world)]
+        torch.cuda.synchronize()
+        assert all(rk.status() == 0 for rk in ranks), "a bounded wait ran out"
+        want_res = (want_res + sum(p.float() for p in parts)).to(BF).float()
+        want_out = ref.rmsnorm(want_res.to(BF), w, 1e-5).float()
+        for r in range(world):
+            lo, hi = ranks[r].rows_of(r, T)
+            if hi > lo:
+                assert (residual[r][lo:hi].float() - want_res[lo:hi]).abs().max().item() < 6e-2
+            assert (outs[r].float() - want_out).abs().max().item() < 6e-2

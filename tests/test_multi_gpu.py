@@ -42,25 +42,48 @@ def _worker(rank, world, port, out_dir, fused, tpsp=False):
     logits = m.forward(mi).logits.float().cpu()
     m.mem_manager.free(slots)
     m.req_manager.free(req)
+    # one prompt pass over three requests: with the fused path on, it runs as two micro-batches whose reductions
+    # go over the copy engines (the token threshold is lowered so that this small pass qualifies)
+    m.PIPELINE_MIN_TOKENS = 64
+    lens = [150, 200, 90]
+    ids3 = torch.randint(3, 32000, (sum(lens),), generator=g)
+    reqs = [m.req_manager.alloc() for _ in lens]
+    slots = m.mem_manager.alloc(sum(lens))
+    mi = ModelInput(batch_size=3, total_token_num=sum(lens), max_kv_len=max(lens), is_prefill=True,
+                    b_req_idx=torch.tensor(reqs, dtype=torch.int32), b_seq_len=torch.tensor(lens, dtype=torch.int32),
+                    mem_indexes=slots.clone(), input_ids=ids3, b_ready_cache_len=torch.zeros(3, dtype=torch.int32),
+                    max_q_len=max(lens))
+    ce_before = m.tp.ce.calls if m.tp.ce is not None else 0
+    logits_multi = m.forward(mi).logits.float().cpu()
+    ce_calls = (m.tp.ce.calls - ce_before) if m.tp.ce is not None else 0
+    ce_status = m.tp.ce.status() if m.tp.ce is not None else 0
+    m.mem_manager.free(slots)
+    for r in reqs:
+        m.req_manager.free(r)
     prompts = [torch.randint(3, 32000, (n,), generator=g).tolist() for n in (17, 64, 129, 300)]
     outs = llm.generate(prompts, {"max_new_tokens": 24, "ignore_eos": True})
     status = m.tp.fused.status() if (fused and m.tp.fused is not None) else 0
     probe = bool(m.tp.fused.self_test()) if (fused and m.tp.fused is not None) else True   # the start-up probe
     if rank == 0:
-        torch.save({"logits": logits, "tokens": [o["token_ids"] for o in outs], "status": status, "probe": probe},
+        torch.save({"logits": logits, "tokens": [o["token_ids"] for o in outs], "status": status, "probe": probe,
+                    "logits_multi": logits_multi, "ce_calls": ce_calls, "ce_status": ce_status},
                    os.path.join(out_dir, f"tp{world}_f{int(fused)}{'_sp' if tpsp else ''}.pt"))
     llm.close()
     pdist.destroy(hard_exit_on_hang=True)
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("W", [2, 4, 8])
 @pytest.mark.timeout(900)
-def test_tp2_fused_matches_nccl_and_tp1(tmp_path):
-    for world, fused in ((1, False), (2, False), (2, True)):
+def test_tp_fused_matches_nccl_and_tp1(tmp_path, W):
+    """W = 2 exercises the one-shot (pushed by the GEMM epilogue) reduction, W = 4 and 8 the two-shot one, the
+    vocabulary-sharded greedy sampling and KV heads replicated across ranks (2 KV heads)."""
+    if torch.cuda.device_count() < W:
+        pytest.skip(f"needs {W} GPUs")
+    for world, fused in ((1, False), (W, False), (W, True)):
         mp.spawn(_worker, args=(world, _free_port(), str(tmp_path), fused), nprocs=world, join=True)
     one = torch.load(tmp_path / "tp1_f0.pt")
-    nccl = torch.load(tmp_path / "tp2_f0.pt")
-    fus = torch.load(tmp_path / "tp2_f1.pt")
+    nccl = torch.load(tmp_path / f"tp{W}_f0.pt")
+    fus = torch.load(tmp_path / f"tp{W}_f1.pt")
     assert fus["status"] == 0, "a bounded wait in the fused all-reduce ran out"
     assert fus["probe"], "the start-up probe of the fused reduction disagreed with NCCL"
     scale = one["logits"].abs().max().item()
@@ -68,9 +91,14 @@ def test_tp2_fused_matches_nccl_and_tp1(tmp_path):
     assert (fus["logits"] - one["logits"]).abs().max().item() < 0.05 * scale + 0.05
     assert (fus["logits"] - nccl["logits"]).abs().max().item() < 0.05 * scale + 0.05
     assert all(len(t) == 24 for t in fus["tokens"])
+    # the pipelined prompt pass: 2 micro-batches x 2 reductions x 4 layers through the copy-engine reducer
+    assert nccl["ce_calls"] == 0 and fus["ce_calls"] == 16 and fus["ce_status"] == 0
+    assert one["logits_multi"].shape == fus["logits_multi"].shape == (3, 32000)
+    assert (nccl["logits_multi"] - one["logits_multi"]).abs().max().item() < 0.05 * scale + 0.05
+    assert (fus["logits_multi"] - one["logits_multi"]).abs().max().item() < 0.05 * scale + 0.05
     # token-sharded residual stream (reduce-scatter + norm on the shard + all-gather, one kernel)
-    mp.spawn(_worker, args=(2, _free_port(), str(tmp_path), True, True), nprocs=2, join=True)
-    sp = torch.load(tmp_path / "tp2_f1_sp.pt")
+    mp.spawn(_worker, args=(W, _free_port(), str(tmp_path), True, True), nprocs=W, join=True)
+    sp = torch.load(tmp_path / f"tp{W}_f1_sp.pt")
     assert sp["status"] == 0
     assert (sp["logits"] - one["logits"]).abs().max().item() < 0.05 * scale + 0.05
     assert all(len(t) == 24 for t in sp["tokens"])
@@ -91,7 +119,7 @@ def _ep_worker(rank, world, port, out_dir):
     llm = LLM(config=MOE, max_total_token_num=8192, running_max_req_size=8, max_req_total_len=512,
               batch_max_tokens=1024, enable_ep_moe=world > 1, disable_cudagraph=True)
     g = torch.Generator().manual_seed(0)
-    prompts = [torch.randint(3, 8192, (n,), generator=g).tolist() for n in (17, 300, 64, 129, 400, 33)]
+    prompts = [torch.randint(3, 8192, (n,), generator=g).tolist() for n in (17, 300, 64, 129, 400, 33, 210, 90)]
     # logits of one prefill pass (every rank runs its own copy of the prompt, so the exchange carries real traffic)
     from lightllm_b200.common.infer_state import ModelInput
 
@@ -106,7 +134,7 @@ def _ep_worker(rank, world, port, out_dir):
     logits = m.forward(mi).logits.float().cpu()
     m.mem_manager.free(slots)
     m.req_manager.free(req)
-    mine = prompts if world == 1 else (prompts[:4] if rank == 0 else prompts[4:])
+    mine = prompts if world == 1 else prompts[rank::world]
     outs = llm.generate(mine, {"max_new_tokens": 16, "ignore_eos": True})
     epg = getattr(llm.model, "_ep_group", None)
     status = epg.status() if epg is not None else 0
@@ -118,24 +146,30 @@ def _ep_worker(rank, world, port, out_dir):
     pdist.destroy(hard_exit_on_hang=True)
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("W", [2, 4, 8])
 @pytest.mark.timeout(600)
-def test_dp2_ep2_peer_memory_dispatch_matches_single_gpu(tmp_path):
+def test_dp_ep_peer_memory_dispatch_matches_single_gpu(tmp_path, W):
     """Data-parallel attention + expert-parallel MoE: tokens go to the experts' GPU and back through the
     peer-memory dispatch / combine kernels; greedy outputs must equal the single-GPU run (bf16: a diverging
     token is tolerated late in a sequence)."""
+    if torch.cuda.device_count() < W:
+        pytest.skip(f"needs {W} GPUs")
     mp.spawn(_ep_worker, args=(1, _free_port(), str(tmp_path)), nprocs=1, join=True)
-    mp.spawn(_ep_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    mp.spawn(_ep_worker, args=(W, _free_port(), str(tmp_path)), nprocs=W, join=True)
     one = torch.load(tmp_path / "ep1_r0.pt")
-    r0, r1 = torch.load(tmp_path / "ep2_r0.pt"), torch.load(tmp_path / "ep2_r1.pt")
-    assert r0["status"] == 0 and r1["status"] == 0, "a bounded wait of the expert-parallel exchange ran out"
+    rs = [torch.load(tmp_path / f"ep{W}_r{r}.pt") for r in range(W)]
+    assert all(r["status"] == 0 for r in rs), "a bounded wait of the expert-parallel exchange ran out"
     scale = one["logits"].abs().max().item()
-    for r in (r0, r1):   # the same network: only the summation order of the experts' partial results differs
+    for r in rs:   # the same network: only the summation order of the experts' partial results differs
         d = (r["logits"] - one["logits"]).abs()
         # rounding can flip a token's expert choice (this toy network's bf16 restatement is 0.08 x scale away from
         # fp32 at its worst element, 0.003 x scale on average): bound the mean tightly and the maximum loosely
         assert d.mean().item() < 0.01 * scale and d.max().item() < 0.15 * scale, (d.mean().item(), d.max().item())
     # greedy decoding of a random-weight model flips on bf16 rounding, so only ask for broad agreement
-    got = r0["tokens"] + r1["tokens"]
-    same_prefix = [next((i for i, (a, b) in enumerate(zip(x, y)) if a != b), len(x)) for x, y in zip(got, one["tokens"])]
-    assert sum(n == 16 for n in same_prefix) >= 3, same_prefix
+    got = {}
+    for r, res in enumerate(rs):
+        for j, toks in enumerate(res["tokens"]):
+            got[r + j * W] = toks                    # rank r ran prompts r, r + W, ...
+    same_prefix = [next((i for i, (a, b) in enumerate(zip(got[k], one["tokens"][k])) if a != b), len(got[k]))
+                   for k in sorted(got)]
+    assert len(got) == 8 and sum(n == 16 for n in same_prefix) >= 4, same_prefix
