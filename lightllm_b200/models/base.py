@@ -398,6 +398,10 @@ class TransformerLM:
     # ------------------------------------------------------------------ forward
     @torch.no_grad()
     def forward(self, mi: ModelInput) -> ModelOutput:
+        if mi.max_kv_len > self.max_seq_length:
+            # the request table's rows and the rotary tables end there: a longer sequence would read past them
+            raise ValueError(f"sequence of {mi.max_kv_len} tokens exceeds the model's max_seq_length "
+                             f"{self.max_seq_length} (max_req_total_len + 8)")
         if mi.is_prefill:
             return self._prefill(mi)
         return self._decode(mi)

@@ -28,7 +28,7 @@ def _worker(rank, world, port, out_dir, fused, tpsp=False):
     from lightllm_b200.parallel import dist as pdist
 
     pdist.init_distributed(world, rank, host="127.0.0.1", port=port, device=torch.device("cuda", rank))
-    llm = LLM(config=CFG, max_total_token_num=8192, running_max_req_size=8, max_req_total_len=512,
+    llm = LLM(config=CFG, max_total_token_num=8192, running_max_req_size=8, max_req_total_len=1024,
               batch_max_tokens=2048, disable_fused_tp=not fused, tpsp_mix_mode=tpsp)
     g = torch.Generator().manual_seed(0)
     ids = torch.randint(3, 32000, (700,), generator=g)
