@@ -41,6 +41,34 @@ MODELS = {
     "llama3-70b": dict(model_type="llama", hidden_size=8192, num_hidden_layers=80, num_attention_heads=64,
                        num_key_value_heads=8, head_dim=128, intermediate_size=28672, vocab_size=128256,
                        rms_norm_eps=1e-5, rope_theta=5e5, eos_token_id=128001, torch_dtype="bfloat16"),
+    # Qwen3-30B-A3B shapes (128 routed experts, top-8 softmax routing with normalised weights)
+    "qwen3-30b-a3b": dict(model_type="qwen3_moe", hidden_size=2048, num_hidden_layers=48, num_attention_heads=32,
+                          num_key_value_heads=4, head_dim=128, intermediate_size=6144, moe_intermediate_size=768,
+                          num_experts=128, num_experts_per_tok=8, norm_topk_prob=True, decoder_sparse_step=1,
+                          mlp_only_layers=[], vocab_size=151936, rms_norm_eps=1e-6, rope_theta=1e6, eos_token_id=151645,
+                          torch_dtype="bfloat16"),
+    # DeepSeek-V3 shapes, e4m3 weights with 128 x 128 block scales
+    "deepseek-v3": dict(model_type="deepseek_v3", hidden_size=7168, num_hidden_layers=61, num_attention_heads=128,
+                        num_key_value_heads=128, q_lora_rank=1536, kv_lora_rank=512, qk_nope_head_dim=128,
+                        qk_rope_head_dim=64, v_head_dim=128, intermediate_size=18432, moe_intermediate_size=2048,
+                        n_routed_experts=256, n_shared_experts=1, num_experts_per_tok=8, n_group=8, topk_group=4,
+                        first_k_dense_replace=3, moe_layer_freq=1, routed_scaling_factor=2.5, norm_topk_prob=True,
+                        scoring_func="sigmoid", topk_method="noaux_tc", vocab_size=129280, rms_norm_eps=1e-6,
+                        rope_theta=10000.0, eos_token_id=1, torch_dtype="bfloat16",
+                        quantization_config={"quant_method": "fp8", "fmt": "e4m3", "activation_scheme": "dynamic",
+                                             "weight_block_size": [128, 128]}),
+    "tiny-moe": dict(model_type="qwen3_moe", hidden_size=256, num_hidden_layers=2, num_attention_heads=4,
+                     num_key_value_heads=2, head_dim=64, intermediate_size=512, moe_intermediate_size=128,
+                     num_experts=8, num_experts_per_tok=2, norm_topk_prob=True, decoder_sparse_step=1, mlp_only_layers=[],
+                     vocab_size=1024, rms_norm_eps=1e-6, rope_theta=1e4, eos_token_id=2, torch_dtype="bfloat16"),
+    "tiny-ds": dict(model_type="deepseek_v3", hidden_size=256, intermediate_size=512, moe_intermediate_size=128,
+                    num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=4, n_routed_experts=8,
+                    n_shared_experts=1, num_experts_per_tok=2, n_group=2, topk_group=1, first_k_dense_replace=1,
+                    q_lora_rank=128, kv_lora_rank=128, qk_nope_head_dim=64, qk_rope_head_dim=32, v_head_dim=64,
+                    vocab_size=1024, routed_scaling_factor=2.5, norm_topk_prob=True, scoring_func="sigmoid",
+                    topk_method="noaux_tc", rms_norm_eps=1e-6, eos_token_id=2, torch_dtype="bfloat16",
+                    quantization_config={"quant_method": "fp8", "fmt": "e4m3", "activation_scheme": "dynamic",
+                                         "weight_block_size": [128, 128]}),
     "tiny": dict(model_type="llama", hidden_size=1024, num_hidden_layers=2, num_attention_heads=8,
                  num_key_value_heads=2, head_dim=128, intermediate_size=2816, vocab_size=32000, rms_norm_eps=1e-5,
                  rope_theta=5e5, eos_token_id=2, torch_dtype="bfloat16"),
@@ -60,7 +88,26 @@ def parse():
     ap.add_argument("--batch-max-tokens", type=int, default=16384)
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--tpsp", action="store_true", help="token-sharded residual stream between layers (N > 1)")
-    return ap.parse_args()
+    ap.add_argument("--config", type=int, default=2, choices=[2, 3, 4, 5],
+                    help="2 (default): Llama-3-8B, tensor parallel, fixed concurrency; 3: Llama-3-70B tensor parallel, "
+                         "Poisson arrivals; 4: Qwen3-30B-A3B shapes, expert parallel; 5: DeepSeek-V3 shapes fp8, "
+                         "data-parallel attention + expert parallel")
+    ap.add_argument("--requests", type=int, default=None, help="config 3: number of requests (1000)")
+    ap.add_argument("--rate", type=float, default=8.0, help="config 3: Poisson arrival rate, requests per second")
+    ap.add_argument("--in-range", default="128,4096", help="config 3: uniform prompt length range")
+    ap.add_argument("--out-range", default="64,1024", help="config 3: uniform output length range")
+    ap.add_argument("--warmup-out-len", type=int, default=None,
+                    help="configs 3-5: output length of the warm-up runs (default 16: graph capture and first-use "
+                         "set-up only; the timed runs use the configuration's lengths)")
+    a = ap.parse_args()
+    explicit = {x.split("=")[0] for x in sys.argv[1:] if x.startswith("--")}
+    preset = {3: dict(model="llama3-70b", conc=256, batch_max_tokens=16384),
+              4: dict(model="qwen3-30b-a3b", conc=512, in_len=2048, out_len=512, batch_max_tokens=8192),
+              5: dict(model="deepseek-v3", conc=1024, in_len=1024, out_len=1024, batch_max_tokens=8192)}.get(a.config, {})
+    for k, v in preset.items():
+        if "--" + k.replace("_", "-") not in explicit:
+            setattr(a, k, v)
+    return a
 
 
 class ClockSampler:
@@ -135,6 +182,170 @@ def reference_arm(args):
     reference_runner.main(args, MODELS)
 
 
+def serving_config(args, world):
+    """Configurations 3 - 5, all through the public offline API `LLM.generate` (admission queue, radix cache,
+    per-pass H2D of indices / prompt ids from pinned memory, per-pass D2H of the sampled ids, stop checks).
+
+    3: Llama-3-70B shapes, tensor parallel over the N GPUs; `--requests` (1000) random-token requests, prompt length
+       uniform in `--in-range`, output length uniform in `--out-range`, Poisson arrivals at `--rate` per second,
+       seed 0.  One step = the whole arrival trace.  value = output tokens / time from the first arrival to the
+       last token.
+    4 / 5: Qwen3-30B-A3B / DeepSeek-V3 (fp8 block-scaled) shapes, data-parallel attention (one replica per GPU)
+       with expert-parallel MoE; fixed input / output length; one step = one wave of `--conc` concurrent requests
+       (conc / N per GPU).
+    The device-timed value brackets the timed runs with CUDA events on the launching stream; the e2e value is the
+    host clock around the same calls."""
+    import torch
+
+    from lightllm_b200 import ops
+    from lightllm_b200.engine.llm import LLM
+    from lightllm_b200.parallel import dist as pdist
+
+    moe = args.config in (4, 5)
+    ps = pdist.init_from_env(dp=world if moe else 1)
+    dev, rank = ps.device, ps.global_rank
+    cuda = dev.type == "cuda"
+    cfg = dict(MODELS[args.model])
+    t_start = time.time()
+
+    def stage(msg):
+        if rank == 0:
+            print(f"[bench +{time.time() - t_start:6.1f}s] {msg}", file=sys.stderr, flush=True)
+
+    rng = np.random.default_rng(0)
+    vocab = cfg["vocab_size"]
+    lo_id, hi_id = (1000, vocab - 1000) if vocab > 4000 else (3, vocab - 1)
+    if args.config == 3:
+        n_req = args.requests or 1000
+        i0, i1 = (int(x) for x in args.in_range.split(","))
+        o0, o1 = (int(x) for x in args.out_range.split(","))
+        in_lens = rng.integers(i0, i1 + 1, size=n_req)
+        out_lens = rng.integers(o0, o1 + 1, size=n_req)
+        arrivals = np.cumsum(rng.exponential(1.0 / args.rate, size=n_req))
+        arrivals -= arrivals[0]
+        prompts = [rng.integers(lo_id, hi_id, size=int(n)).tolist() for n in in_lens]
+        max_total = int(i1 + o1) + 8
+        conc = args.conc
+        pool = min(int(conc * (i1 + o1) * 0.6) + args.batch_max_tokens, conc * max_total)
+        llm = LLM(config=cfg, max_total_token_num=pool, running_max_req_size=conc, max_req_total_len=max_total,
+                  batch_max_tokens=args.batch_max_tokens, chunked_prefill_size=args.batch_max_tokens // 2,
+                  graph_max_batch_size=conc)
+        per_rank_conc = conc
+    else:
+        per_rank_conc = max(1, args.conc // world)
+        total_len = args.in_len + args.out_len
+        pool = per_rank_conc * (total_len + 8) + args.batch_max_tokens
+        llm = LLM(config=cfg, max_total_token_num=pool, running_max_req_size=per_rank_conc,
+                  max_req_total_len=total_len + 8, batch_max_tokens=args.batch_max_tokens,
+                  chunked_prefill_size=args.batch_max_tokens // 2, graph_max_batch_size=per_rank_conc,
+                  enable_ep_moe=world > 1)
+    stage("model built")
+    llm.warmup([per_rank_conc])
+    stage("decode graph captured")
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        if cuda:
+            torch.cuda.synchronize(dev)
+
+    wrng = np.random.default_rng(1000 + rank)
+    wlen = args.warmup_out_len or 16
+
+    def one_run(warm: bool):
+        """(output tokens of this rank, outs)"""
+        if args.config == 3:
+            if warm:   # a short burst of the same traffic
+                k = min(32, len(prompts))
+                sp = [{"max_new_tokens": wlen, "ignore_eos": True} for _ in range(k)]
+                outs = llm.generate(prompts[:k], sp, arrival_times=list(arrivals[:k] * 0.1))
+            else:
+                sp = [{"max_new_tokens": int(o), "ignore_eos": True} for o in out_lens]
+                outs = llm.generate(prompts, sp, return_stats=True, arrival_times=list(arrivals))[0]
+            return sum(len(o["token_ids"]) for o in outs), outs
+        ps_ = wrng.integers(lo_id, hi_id, size=(per_rank_conc, args.in_len)).tolist()
+        sp = {"max_new_tokens": wlen if warm else args.out_len, "ignore_eos": True}
+        outs = llm.generate(ps_, sp, return_stats=not warm)
+        outs = outs[0] if not warm else outs
+        return sum(len(o["token_ids"]) for o in outs), outs
+
+    for i in range(args.warmup):
+        one_run(True)
+        if i == 0:
+            stage("first warm-up run done")
+    barrier()
+    stage("warm-up done")
+    clocks = ClockSampler(dev.index or 0)
+    clocks.start()
+    n0 = ops.launch_count()
+    st0 = dict(llm.backend.stats)
+    if cuda:
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+    t0 = time.time()
+    tokens, ttfts, itls = 0, [], []
+    for _ in range(args.steps):
+        n_tok, outs = one_run(False)
+        tokens += n_tok
+        for o in outs:
+            if o["ttft_s"] is not None:
+                ttfts.append(o["ttft_s"])
+            tt = o.get("token_times") or []
+            if len(tt) > 1:
+                itls.append((tt[-1] - tt[0]) / (len(tt) - 1))
+    if cuda:
+        ev1.record()
+    barrier()
+    wall = time.time() - t0
+    dev_ms = ev0.elapsed_time(ev1) if cuda else wall * 1e3
+    launches = ops.launch_count() - n0
+    clock_info = clocks.stop()
+    st1 = llm.backend.stats
+    fwd = (st1["prefill_steps"] - st0["prefill_steps"]) + (st1["decode_steps"] - st0["decode_steps"])
+    h2d = (st1["h2d_bytes"] - st0["h2d_bytes"]) / max(fwd, 1)
+    d2h = (st1["d2h_bytes"] - st0["d2h_bytes"]) / max(fwd, 1)
+    status = int(ops.gemm_status(dev).item()) if cuda else 0
+    v = torch.tensor([dev_ms, wall], dtype=torch.float64, device=dev)
+    tk = torch.tensor([tokens if (moe or rank == 0) else 0], dtype=torch.float64, device=dev)
+    lat = torch.tensor([statistics.median(ttfts) if ttfts else 0.0, statistics.median(itls) if itls else 0.0],
+                       dtype=torch.float64, device=dev)
+    if world > 1:
+        torch.distributed.all_reduce(v, op=torch.distributed.ReduceOp.MAX)
+        torch.distributed.all_reduce(tk)                                       # replicas serve different requests
+        torch.distributed.all_reduce(lat, op=torch.distributed.ReduceOp.MAX)   # the slowest replica's medians
+    dev_ms, wall, total_tokens = float(v[0]), float(v[1]), float(tk[0])
+    if rank == 0:
+        conf = bench_config(args)
+        if args.config == 3:
+            conf.update({"parallelism": f"tp{world}", "requests": len(prompts), "arrivals": f"Poisson {args.rate}/s, seed 0",
+                         "input_len": f"uniform {args.in_range}", "output_len": f"uniform {args.out_range}",
+                         "seq_len": max_total - 8, "global_batch": conc,
+                         "step": "the whole arrival trace, first arrival to last token"})
+        else:
+            conf.update({"parallelism": f"dp{world}+ep{world}" if world > 1 else "single GPU",
+                         "step": "one wave of `global_batch` concurrent requests (global_batch / N per GPU)",
+                         "weights": "e4m3 with 128x128 block scales" if args.config == 5 else "bf16"})
+        conf["warmup_runs"] = (f"{args.warmup} short runs (output length {wlen}) of the same traffic: graph capture "
+                               "and first-use set-up; the timed runs use the full lengths")
+        line = {"metric": "output tok/s per box at fixed concurrency" if moe else
+                "output tok/s per box under Poisson arrivals", "value": round(total_tokens / (dev_ms / 1e3), 1),
+                "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+                "ms_per_step": round(dev_ms / args.steps, 2), "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": None, "dtype": "fp8 e4m3 weights / bf16 activations" if args.config == 5 else "bf16",
+                "data": "synthetic uniform-random token ids, random-init weights", "impl": "ours", "config": conf,
+                "clocks": clock_info, "gpu_launches": launches, "device_wait_status": status,
+                "e2e": {"value": round(total_tokens / wall, 1), "unit": "tokens/s", "h2d_bytes_per_step": round(h2d, 1),
+                        "d2h_bytes_per_step": round(d2h, 1),
+                        "bytes_are_per": "forward pass (prefill chunk or decode step)",
+                        "p50_ttft_ms": round(float(lat[0]) * 1e3, 2), "p50_itl_ms": round(float(lat[1]) * 1e3, 3)}}
+        print(json.dumps(line), flush=True)
+    llm.close()
+    epg = getattr(llm.model, "_ep_group", None)
+    if epg is not None:
+        epg.close()
+    pdist.destroy(hard_exit_on_hang=True)
+
+
 def main():
     args = parse()
     if args.impl == "reference":
@@ -149,6 +360,8 @@ def main():
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run"
+    if args.config != 2:
+        return serving_config(args, world)
     ps = pdist.init_from_env()
     dev = ps.device
     rank = ps.global_rank

@@ -117,11 +117,31 @@ class LLM:
             self.model.tp.fused = None
             fused.close()
 
+    def _arrived(self, arrival_times, t_start: float, n_in: int) -> int:
+        """How many requests have arrived by now.  With several ranks the first rank's clock decides and the
+        others are told (one small host broadcast per scheduling round), so that all ranks admit the same
+        requests on the same step."""
+        n = n_in
+        if self.ps.global_rank == 0 or self.ps.world_size == 1:
+            now = time.time() - t_start
+            while n < len(arrival_times) and arrival_times[n] <= now:
+                n += 1
+        if self.ps.world_size > 1 and self.ps.cpu_group is not None:
+            import torch.distributed as dist
+
+            t = torch.tensor([n], dtype=torch.int64)
+            dist.broadcast(t, src=0, group=self.ps.cpu_group)
+            n = int(t.item())
+        return n
+
     @torch.no_grad()
     def generate(self, prompt_token_ids: List[List[int]], sampling_params: Union[dict, List[dict], None] = None,
-                 return_stats: bool = False):
+                 return_stats: bool = False, arrival_times: Optional[List[float]] = None):
         """Runs every prompt to completion with continuous batching; returns one dict per prompt:
-        {"token_ids", "logprobs", "finish_reason", "prompt_tokens", "ttft_s", "latency_s"}."""
+        {"token_ids", "logprobs", "finish_reason", "prompt_tokens", "ttft_s", "latency_s"}.
+        `arrival_times` (seconds from the call, non-decreasing): request i only enters the admission queue once its
+        time has come (an open-loop load, e.g. Poisson arrivals); "ttft_s" and "latency_s" then count from the
+        request's own arrival."""
         n = len(prompt_token_ids)
         if not isinstance(sampling_params, list):
             sampling_params = [sampling_params or {}] * n
@@ -134,7 +154,12 @@ class LLM:
             sp["max_new_tokens"] = min(sp.get("max_new_tokens", 16), limit - len(ids))
             reqs.append(self._new_req(list(ids), sp))
         t_submit = time.time()
-        self.queue.extend(reqs)
+        timed = arrival_times is not None
+        if timed:
+            assert len(arrival_times) == n and self.ps.dp_size == 1, "timed arrivals: one time per prompt, no --dp"
+            n_in = 0
+        else:
+            self.queue.extend(reqs)
         running = Batch(0, [])
         done = 0
         finish_time: Dict[int, float] = {}
@@ -143,6 +168,14 @@ class LLM:
             self.backend.on_token = lambda ir, tok, lp: token_times[ir.req_id].append(time.time())
         step_log = []
         while done < n:
+            if timed and n_in < n:
+                upto = self._arrived(arrival_times, t_submit, n_in)
+                if upto > n_in:
+                    self.queue.extend(reqs[n_in:upto])
+                    n_in = upto
+                if not self.backend.has_work() and self.queue.get_wait_req_num() == 0:
+                    time.sleep(0.0005)   # nothing running, nothing waiting: the next request has not arrived yet
+                    continue
             used = 1.0 - self.backend.ctx.get_can_alloc_token_num() / max(self.model.max_total_token_num, 1)
             self.queue.cur_token_usage_ratio = used
             new_batch = self.queue.generate_new_batch(running)
@@ -163,13 +196,14 @@ class LLM:
             running.filter_out_finished_req()
         self.backend.on_token = None
         outs = []
-        for r in reqs:
+        for i, r in enumerate(reqs):
             out_ids = r.get_output_ids()
             lps = r.shm_logprobs.arr[r.input_len: r.input_len + r.shm_cur_output_len].tolist()
+            t_arrive = t_submit + (arrival_times[i] if timed else 0.0)
             o = {"token_ids": out_ids, "logprobs": lps, "finish_reason": r.finish_status.get_finish_reason(),
                  "prompt_tokens": r.input_len, "prompt_cache_len": r.prompt_cache_len,
-                 "ttft_s": (r.first_token_time - t_submit) if r.first_token_time > 0 else None,
-                 "latency_s": finish_time.get(r.request_id, time.time()) - t_submit}
+                 "ttft_s": (r.first_token_time - t_arrive) if r.first_token_time > 0 else None,
+                 "latency_s": finish_time.get(r.request_id, time.time()) - t_arrive}
             if return_stats:
                 o["token_times"] = token_times[r.request_id]
             outs.append(o)
