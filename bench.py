@@ -96,6 +96,9 @@ def parse():
     ap.add_argument("--rate", type=float, default=8.0, help="config 3: Poisson arrival rate, requests per second")
     ap.add_argument("--in-range", default="128,4096", help="config 3: uniform prompt length range")
     ap.add_argument("--out-range", default="64,1024", help="config 3: uniform output length range")
+    ap.add_argument("--layers", type=int, default=None,
+                    help="development aid: build only this many layers (the result line says so and is not a "
+                         "measurement of the named configuration)")
     ap.add_argument("--warmup-out-len", type=int, default=None,
                     help="configs 3-5: output length of the warm-up runs (default 16: graph capture and first-use "
                          "set-up only; the timed runs use the configuration's lengths)")
@@ -206,6 +209,8 @@ def serving_config(args, world):
     dev, rank = ps.device, ps.global_rank
     cuda = dev.type == "cuda"
     cfg = dict(MODELS[args.model])
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
     t_start = time.time()
 
     def stage(msg):
@@ -263,7 +268,8 @@ def serving_config(args, world):
                 sp = [{"max_new_tokens": int(o), "ignore_eos": True} for o in out_lens]
                 outs = llm.generate(prompts, sp, return_stats=True, arrival_times=list(arrivals))[0]
             return sum(len(o["token_ids"]) for o in outs), outs
-        ps_ = wrng.integers(lo_id, hi_id, size=(per_rank_conc, args.in_len)).tolist()
+        n_here = max(1, per_rank_conc // 8) if warm else per_rank_conc
+        ps_ = wrng.integers(lo_id, hi_id, size=(n_here, args.in_len)).tolist()
         sp = {"max_new_tokens": wlen if warm else args.out_len, "ignore_eos": True}
         outs = llm.generate(ps_, sp, return_stats=not warm)
         outs = outs[0] if not warm else outs
@@ -325,8 +331,11 @@ def serving_config(args, world):
             conf.update({"parallelism": f"dp{world}+ep{world}" if world > 1 else "single GPU",
                          "step": "one wave of `global_batch` concurrent requests (global_batch / N per GPU)",
                          "weights": "e4m3 with 128x128 block scales" if args.config == 5 else "bf16"})
-        conf["warmup_runs"] = (f"{args.warmup} short runs (output length {wlen}) of the same traffic: graph capture "
-                               "and first-use set-up; the timed runs use the full lengths")
+        if args.layers:
+            conf["layers_override"] = f"{args.layers} layers only: NOT the named configuration"
+        conf["warmup_runs"] = (f"{args.warmup} short runs (output length {wlen}, an eighth of the requests) of the "
+                               "same traffic: graph capture and first-use set-up; the timed runs use the full "
+                               "lengths and request counts")
         line = {"metric": "output tok/s per box at fixed concurrency" if moe else
                 "output tok/s per box under Poisson arrivals", "value": round(total_tokens / (dev_ms / 1e3), 1),
                 "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,

@@ -58,6 +58,8 @@ class DPBackend(ModelBackend):
         n_tok, kind = 0, "idle"
         if any_prefill:
             kind = "prefill"
+            # every rank saw the same votes: the largest prompt chunk of this step bounds the expert exchange
+            self.model.ep_prefill_tokens_bound = max(int(votes[:, 0].max()), 1)
             if local_kind == "prefill":
                 n_tok = self._run_prefill(prefill)
             else:

@@ -402,8 +402,13 @@ class TransformerLM:
             # the request table's rows and the rotary tables end there: a longer sequence would read past them
             raise ValueError(f"sequence of {mi.max_kv_len} tokens exceeds the model's max_seq_length "
                              f"{self.max_seq_length} (max_req_total_len + 8)")
+        # expert-parallel exchanges size their launches by the largest token count any rank can bring to this pass:
+        # a decode step is bounded by the largest graph batch (the same on all ranks), a prompt pass by what the
+        # data-parallel backend learnt from the other replicas (`ep_prefill_tokens_bound`) or the chunk limit
         if mi.is_prefill:
+            self._ep_tokens_bound = int(getattr(self, "ep_prefill_tokens_bound", 0) or self.batch_max_tokens)
             return self._prefill(mi)
+        self._ep_tokens_bound = max(self.graph_max_batch_size, self.max_req_num)
         return self._decode(mi)
 
     # ---- prefill ----

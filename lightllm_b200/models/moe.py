@@ -139,7 +139,7 @@ def moe_ffn(model, lw, h, mc: MoEConfig):
     epg = ep_group_of(model, mc)
     if epg is not None:
         epg.moe(h, ids, w, lambda hr, ir, wr, o: moe_ops.fused_experts(hr, lw.w13, lw.w2, ir, wr, mc.act, lw.e0, out=o),
-                out=out, accumulate=accumulate)
+                out=out, accumulate=accumulate, tokens_bound=int(getattr(model, "_ep_tokens_bound", 0) or 0))
         return out
     moe_ops.fused_experts(h, lw.w13, lw.w2, ids, w, mc.act, lw.e0, out=out, accumulate=accumulate)
     return out

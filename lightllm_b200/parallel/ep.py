@@ -81,9 +81,14 @@ class EPGroup:
             dist.barrier(group=ps.cpu_group)  # every rank's buffers are initialised before the first round
 
     # ------------------------------------------------------------------
-    def moe(self, h, ids, w, expert_fn, out=None, accumulate: bool = False):
+    def moe(self, h, ids, w, expert_fn, out=None, accumulate: bool = False, tokens_bound: int = 0):
         """out[t] (+)= sum over the token's experts, wherever they live.  `expert_fn(h_rows, ids_rows, w_rows,
-        out_rows)` must add nothing for expert ids that are not local."""
+        out_rows)` must add nothing for expert ids that are not local.
+
+        `tokens_bound`: an upper bound on the number of tokens ANY rank brings to this exchange, the same value
+        on every rank (0: the group's `max_tokens`).  The experts then run over world x tokens_bound receive rows
+        instead of the worst case the buffers were sized for, which is what keeps a decode step (a few hundred
+        tokens in all) from paying for a prompt-sized launch."""
         T = h.shape[0]
         if out is None:
             out = torch.empty_like(h)
@@ -95,17 +100,21 @@ class EPGroup:
         if not self.cuda:
             return self._moe_gather_reduce(h, ids, w, expert_fn, out, accumulate)
         assert T <= self.max_tokens and h.is_contiguous() and ids.dtype == torch.int32 and w.dtype == torch.float32
+        rows = self.max_recv
+        if tokens_bound > 0:
+            assert T <= tokens_bound, "tokens_bound must cover every rank's token count"
+            rows = min(self.max_recv, self.world * tokens_bound)
         base = self.local.data_ptr()
         lib = kernels()
         check(lib.llb_ep_dispatch(self.t_h, self.t_ids, self.t_w, self.t_out, self.t_counts, self.t_flags,
                                   ctypes.c_int(self.rank), ctypes.c_int(self.world), ptr(h), ptr(ids), ptr(w),
                                   ctypes.c_int(T), ctypes.c_int(self.hidden), ctypes.c_int(self.k),
-                                  ctypes.c_int(self.e_local), ctypes.c_int(self.max_recv), ptr(self.dest_mask),
+                                  ctypes.c_int(self.e_local), ctypes.c_int(rows), ptr(self.dest_mask),
                                   ptr(self.slot), ptr(self.where), ctypes.c_void_p(base), ctypes.c_void_p(base + 16),
                                   ctypes.c_void_p(base + 8), ctypes.c_void_p(base + 12),
                                   ctypes.c_int(min(self.ctas, max(T, 1))), stream()), "ep_dispatch")
         _count(3)
-        expert_fn(self.h_recv, self.ids_recv, self.w_recv, self.out_recv)
+        expert_fn(self.h_recv[:rows], self.ids_recv[:rows], self.w_recv[:rows], self.out_recv[:rows])
         check(lib.llb_ep_combine(self.t_h, self.t_ids, self.t_w, self.t_out, self.t_counts, self.t_flags,
                                  ctypes.c_int(self.rank), ctypes.c_int(self.world), ptr(out), ctypes.c_int(T),
                                  ctypes.c_int(self.hidden), ptr(self.where), ctypes.c_int(1 if accumulate else 0),
