@@ -331,6 +331,13 @@ def serving_config(args, world):
             conf.update({"parallelism": f"dp{world}+ep{world}" if world > 1 else "single GPU",
                          "step": "one wave of `global_batch` concurrent requests (global_batch / N per GPU)",
                          "weights": "e4m3 with 128x128 block scales" if args.config == 5 else "bf16"})
+        if "decode_gpu_ms" in st1:
+            conf["decode_pass_device_ms"] = round((st1["decode_gpu_ms"] - st0.get("decode_gpu_ms", 0.0)) /
+                                                  max(st1["decode_steps"] - st0["decode_steps"], 1), 3)
+        steps_n = max(st1["decode_steps"] - st0["decode_steps"], 1)
+        for key, name in (("agree_s", "host_vote_ms_per_decode_pass"), ("wait_gpu_s", "host_wait_for_gpu_ms_per_decode_pass")):
+            if key in st1:
+                conf[name] = round((st1[key] - st0.get(key, 0.0)) * 1e3 / steps_n, 3)
         if args.layers:
             conf["layers_override"] = f"{args.layers} layers only: NOT the named configuration"
         conf["warmup_runs"] = (f"{args.warmup} short runs (output length {wlen}, an eighth of the requests) of the "

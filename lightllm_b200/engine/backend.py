@@ -140,6 +140,7 @@ class ModelBackend:
         self.stats = {"prefill_steps": 0, "decode_steps": 0, "prefill_tokens": 0, "decode_tokens": 0,
                       "h2d_bytes": 0, "d2h_bytes": 0, "paused": 0}
         self._steps = 0
+        self._step_timing = os.environ.get("LLB_STEP_TIMING", "0") == "1"
         self._pending = None  # a launched decode step whose tokens have not been read back yet
 
     # ------------------------------------------------------------------ requests
@@ -355,7 +356,7 @@ class ModelBackend:
         """A decode step may be launched ahead of the previous step's bookkeeping when nothing on the host shapes its
         logits (penalties, token masks, constrained decoding) and this is the plain backend."""
         on_gpu = self.device.type == "cuda" or os.environ.get("LLB_FORCE_DECODE_OVERLAP") == "1"  # CPU: tests only
-        if not (self.args.enable_decode_overlap and on_gpu and type(self) is ModelBackend):
+        if not (self.args.enable_decode_overlap and on_gpu and type(self).__name__ in ("ModelBackend", "DPBackend")):
             return False
         if self.state_cache is not None:   # snapshots are taken between steps
             return False
@@ -375,7 +376,9 @@ class ModelBackend:
             return
         reqs, ids_h, lps_h, event = pend
         if event is not None:
+            t0 = time.perf_counter()
             event.synchronize()
+            self.stats["wait_gpu_s"] = self.stats.get("wait_gpu_s", 0.0) + (time.perf_counter() - t0)
         live = []
         for i, r in enumerate(reqs):
             r.inflight = 0
@@ -399,6 +402,10 @@ class ModelBackend:
                         b_req_idx=pin.from_numpy("d_req", idx, torch.int32),
                         b_seq_len=pin.from_numpy("d_seq", seq, torch.int32), mem_indexes=slots)
         self.stats["h2d_bytes"] += B * 12
+        timing = self._step_timing and not defer and self.device.type == "cuda"
+        if timing:   # LLB_STEP_TIMING=1: device time of the synchronous decode passes (forward + sampling)
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record()
         out = self.model.forward(mi)
         if defer:
             ids, lps = self._sample(reqs, self._logits_for_sampling(out, reqs, False), np.ones(B, dtype=bool),
@@ -422,8 +429,14 @@ class ModelBackend:
             self._pending = (reqs, ids_h, lps_h, event)
         else:
             self._snapshot_states(reqs)
-            self._sample_and_post(reqs, self._logits_for_sampling(out, reqs, False), np.ones(B, dtype=bool),
-                                  is_prefill=False)
+            if timing:
+                ids, lps = self._sample(reqs, self._logits_for_sampling(out, reqs, False), np.ones(B, dtype=bool), False)
+                ev1.record()
+                self._post_sampled(reqs, ids, lps, np.ones(B, dtype=bool))
+                self.stats["decode_gpu_ms"] = self.stats.get("decode_gpu_ms", 0.0) + ev0.elapsed_time(ev1)
+            else:
+                self._sample_and_post(reqs, self._logits_for_sampling(out, reqs, False), np.ones(B, dtype=bool),
+                                      is_prefill=False)
         self.stats["decode_steps"] += 1
         self.stats["decode_tokens"] += B
         return B
@@ -477,9 +490,12 @@ class ModelBackend:
         return ids, lps
 
     def _sample_and_post(self, reqs: List[InferReq], logits: torch.Tensor, has_out: np.ndarray, is_prefill: bool):
+        ids, lps = self._sample(reqs, logits, has_out, is_prefill)
+        self._post_sampled(reqs, ids, lps, has_out)
+
+    def _post_sampled(self, reqs: List[InferReq], ids, lps, has_out: np.ndarray):
         dev = self.device
         B = len(reqs)
-        ids, lps = self._sample(reqs, logits, has_out, is_prefill)
         if dev.type == "cuda":
             ids_h = self.pins.get("s_ids", B, torch.int64)
             lps_h = self.pins.get("s_lps", B, torch.float32)

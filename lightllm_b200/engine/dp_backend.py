@@ -33,7 +33,9 @@ class DPBackend(ModelBackend):
         if self.ps.world_size == 1 or self.ps.cpu_group is None:
             return mine.view(1, 3)
         allv = torch.empty(self.ps.world_size * 3, dtype=torch.int64)
+        t0 = time.perf_counter()
         dist.all_gather_into_tensor(allv, mine, group=self.ps.cpu_group)
+        self.stats["agree_s"] = self.stats.get("agree_s", 0.0) + (time.perf_counter() - t0)
         return allv.view(self.ps.world_size, 3)
 
     def _hold_input(self, is_prefill: bool) -> ModelInput:
@@ -49,9 +51,21 @@ class DPBackend(ModelBackend):
 
     @torch.no_grad()
     def step(self) -> dict:
+        """One lock-step pass.  A plain decode step is launched before the previous step's tokens have been read back
+        (as in the single-replica backend): the host-side bookkeeping of step k and the vote for step k + 1 run while
+        the GPU executes, so a replica's GPU does not sit idle between passes and, through the layer-wise token
+        exchanges, hold up every other replica."""
         self._steps += 1
         prefill, decode, finished = self._get_classed_reqs()
         local_kind = self.control.select(len(prefill), len(decode))
+        defer = local_kind == "decode" and self._can_defer(decode)
+        if self._pending is not None and not defer:
+            # settle the step in flight first, so that the vote says what this replica will really run
+            self._flush_pending()
+            prefill, decode, fin2 = self._get_classed_reqs()
+            finished += [r for r in fin2 if r not in finished]
+            local_kind = self.control.select(len(prefill), len(decode))
+            defer = local_kind == "decode" and self._can_defer(decode)
         votes = self._agree(sum(c for _, c in prefill) if local_kind == "prefill" else 0,
                             len(decode) if local_kind == "decode" else 0)
         any_prefill, any_decode = bool((votes[:, 0] > 0).any()), bool((votes[:, 1] > 0).any())
@@ -68,17 +82,23 @@ class DPBackend(ModelBackend):
         elif any_decode:
             kind = "decode"
             if local_kind == "decode":
-                n_tok = self._run_decode(decode)
+                n_tok = self._run_decode(decode, defer=defer)
             else:
                 self.model.forward(self._hold_input(False))
                 self.stats["hold_decode"] += 1
         else:
-            time.sleep(self.idle_sleep_s)
+            if self._pending is not None:
+                self._flush_pending()
+            else:
+                time.sleep(self.idle_sleep_s)
         for req in list(self.ctx.requests.values()):
             if req.finish_status.is_finished() and req not in finished:
                 finished.append(req)
+        finished = [r for r in finished if not r.retire_hold]
         for req in finished:
             self.ctx.remove_req(req)
+        # requests whose last token is still in flight are in the table, so the (shared) votes cover them:
+        # every rank leaves drain() on the same step
         return {"kind": kind, "finished": finished, "tokens": n_tok, "world_busy": bool((votes[:, 2] > 0).any())}
 
     def drain(self):

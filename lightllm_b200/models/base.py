@@ -629,6 +629,9 @@ class TransformerLM:
 
     def _capture_decode_graph(self, bucket: int) -> dict:
         dev = self.device
+        # the launch shapes of the expert-parallel exchange are frozen into the graph: use the decode bound, also
+        # when graphs are captured ahead of the first forward call (warmup_graphs)
+        self._ep_tokens_bound = max(self.graph_max_batch_size, self.max_req_num)
         g = {
             "b_req_idx": torch.full((bucket,), self.req_manager.HOLD_REQUEST_ID, dtype=torch.int32, device=dev),
             "b_seq_len": torch.ones(bucket, dtype=torch.int32, device=dev),
