@@ -58,29 +58,33 @@ def _digest(paths) -> str:
     return h.hexdigest()
 
 
-def _compile_cu(src: Path, headers, force: bool) -> Path:
-    obj = OBJ / (src.stem + ".o")
-    stamp = OBJ / (src.stem + ".sha")
-    dig = _digest([src, *headers]) + " ".join(NVCC_FLAGS)
+def _compile_cu(src: Path, headers, force: bool, debug_bounds: bool = False) -> Path:
+    tag = ".dbg" if debug_bounds else ""
+    flags = NVCC_FLAGS + (["-DLLB_DEBUG_BOUNDS"] if debug_bounds else [])
+    obj = OBJ / (src.stem + tag + ".o")
+    stamp = OBJ / (src.stem + tag + ".sha")
+    dig = _digest([src, *headers]) + " ".join(flags)
     if not force and obj.exists() and stamp.exists() and stamp.read_text() == dig:
         return obj
-    cmd = [_nvcc(), *NVCC_FLAGS, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+    cmd = [_nvcc(), *flags, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
     r = subprocess.run(cmd, capture_output=True, text=True)
-    (OBJ / (src.stem + ".ptxas.log")).write_text(r.stderr)
+    (OBJ / (src.stem + tag + ".ptxas.log")).write_text(r.stderr)
     if r.returncode != 0:
         raise RuntimeError(f"nvcc failed for {src.name}:\n{r.stderr[-6000:]}")
     stamp.write_text(dig)
     return obj
 
 
-def build_kernels(force: bool = False, verbose: bool = True) -> Path:
+def build_kernels(force: bool = False, verbose: bool = True, debug_bounds: bool = False) -> Path:
+    """`debug_bounds`: the variant with index checks (-DLLB_DEBUG_BOUNDS, see csrc/common.cuh), linked into
+    libllb_kernels_dbg.so; it is loaded instead of the regular library when LLB_DEBUG_BOUNDS=1 at run time."""
     OBJ.mkdir(parents=True, exist_ok=True)
     srcs = sorted(CSRC.glob("*.cu"))
     headers = sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h"))
-    out = LIB / "libllb_kernels.so"
+    out = LIB / ("libllb_kernels_dbg.so" if debug_bounds else "libllb_kernels.so")
     with cf.ThreadPoolExecutor(max_workers=min(8, len(srcs) or 1)) as ex:
-        objs = list(ex.map(lambda s: _compile_cu(s, headers, force), srcs))
-    link_stamp = OBJ / "link.sha"
+        objs = list(ex.map(lambda s: _compile_cu(s, headers, force, debug_bounds), srcs))
+    link_stamp = OBJ / ("link.dbg.sha" if debug_bounds else "link.sha")
     dig = _digest(objs)
     if force or not out.exists() or not link_stamp.exists() or link_stamp.read_text() != dig:
         cmd = [_nvcc(), "-shared", "-o", str(out), *map(str, objs), "-Xcompiler", "-fPIC"]
@@ -125,7 +129,10 @@ def ptxas_report() -> str:
 
 
 def build_all(force: bool = False, verbose: bool = True):
-    return build_kernels(force, verbose), build_runtime(force, verbose)
+    out = build_kernels(force, verbose), build_runtime(force, verbose)
+    if os.environ.get("LLB_DEBUG_BOUNDS", "0") == "1":
+        build_kernels(force, verbose, debug_bounds=True)
+    return out
 
 
 if __name__ == "__main__":

@@ -20,6 +20,8 @@
 #include "common.cuh"
 
 using namespace llb;
+LLB_DEBUG_BOUNDS_STORAGE(attention)
+
 
 namespace {
 
@@ -60,7 +62,7 @@ gqa_decode_kernel(const bf16* __restrict__ q, int64_t q_stride, const bf16* __re
   const int head0 = kvh * G + chunk_id * 16;
   const int nrows = min(16, G - chunk_id * 16);
   const int b = blockIdx.z;
-  const int req = b_req_idx[b];
+  const int req = LLB_CHECK_REQ(b_req_idx[b]);
   const int L = b_seq_len[b];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, tig = lane & 3;
@@ -109,7 +111,7 @@ gqa_decode_kernel(const bf16* __restrict__ q, int64_t q_stride, const bf16* __re
     int slot = -1;
     if (i < my_count) {
       const int p0 = s0 + (warp + 4 * i) * 16;
-      if (lane < 16 && p0 + lane < e0) slot = req_to_token[r2t_base + p0 + lane];
+      if (lane < 16 && p0 + lane < e0) slot = LLB_CHECK_SLOT(req_to_token[r2t_base + p0 + lane]);
     }
     return slot;
   };
@@ -316,7 +318,7 @@ gqa_prefill_kernel(const bf16* __restrict__ q, int64_t q_stride, const bf16* __r
   const int q0 = tile * BM;
   if (q0 >= q_len) return;
   const int ready = b_ready_len[b];
-  const int req = b_req_idx[b];
+  const int req = LLB_CHECK_REQ(b_req_idx[b]);
   const int rows_valid = min(BM, q_len - q0);
   const int kv_end = ready + q0 + rows_valid;  // exclusive upper bound any row of this tile may see
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -337,7 +339,7 @@ gqa_prefill_kernel(const bf16* __restrict__ q, int64_t q_stride, const bf16* __r
       int tok = c / CH, ch = c % CH;
       int pos = kt + tok;
       bool ok = pos < kv_end;
-      int sl = ok ? req_to_token[r2t_base + pos] : 0;
+      int sl = ok ? LLB_CHECK_SLOT(req_to_token[r2t_base + pos]) : 0;
       const bf16* src = kv_layer + ((int64_t)sl * (2 * Hkv) + kvh) * D + ch * 8;
       cp_async16(sb + swz<D>(tok, ch), src, ok);
       cp_async16(sb + TILE_BYTES + swz<D>(tok, ch), src + (int64_t)Hkv * D, ok);

@@ -21,6 +21,8 @@
 
 using namespace llb;
 using namespace llb::sm100;
+LLB_DEBUG_BOUNDS_STORAGE(attention_tc)
+
 
 namespace {
 
@@ -94,7 +96,7 @@ gqa_prefill_tc_kernel(const bf16* __restrict__ q, int64_t q_stride, const bf16* 
   const int q0 = tile * BM;
   if (q0 >= q_len) return;  // whole CTA: nothing allocated yet
   const int ready = b_ready_len[b];
-  const int req = b_req_idx[b];
+  const int req = LLB_CHECK_REQ(b_req_idx[b]);
   const int rows_valid = min(BM, q_len - q0);
   const int kv_end = ready + q0 + rows_valid;  // exclusive bound on the keys any row of this tile may see
   const int n_tiles = (kv_end + BN - 1) / BN;
@@ -153,7 +155,7 @@ gqa_prefill_tc_kernel(const bf16* __restrict__ q, int64_t q_stride, const bf16* 
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         const int pos = kt + u * 32 + lane;
-        slots[u] = pos < kv_end ? req_to_token[r2t_base + pos] : -1;
+        slots[u] = pos < kv_end ? LLB_CHECK_SLOT(req_to_token[r2t_base + pos]) : -1;
       }
       const int ch = lane & 15;
       mbar_wait(k_empty(stage), par, &abort_flag, status, 41);

@@ -91,6 +91,49 @@ struct DeviceOnce {
   }
 };
 
+// ---------------------------------------------------------------------------------------
+// Debug build with index checks (compile with -DLLB_DEBUG_BOUNDS: `LLB_DEBUG_BOUNDS=1 python -m lightllm_b200.build`
+// produces libllb_kernels_dbg.so next to the regular library; LLB_DEBUG_BOUNDS=1 at run time loads it).
+// The kernels that turn an index read from memory into an address (KV pool slots, request-table rows and
+// columns, expert ids) compare it with the declared size first; an index outside records a code in a status
+// word and the access goes to entry 0 instead, so a wrong index is reported without touching memory beyond the
+// table.  The declared sizes live in a __constant__ struct per translation unit (no relocatable device code is
+// linked), set through the unit's exported setter; 0 = unknown = unchecked.
+//   901 pool slot   902 request row   903 request-table column   904 expert id
+// ---------------------------------------------------------------------------------------
+struct DebugBounds {
+  int pool_slots;   // valid slots are [0, pool_slots)  (the HOLD slot included)
+  int req_rows;     // valid request rows are [0, req_rows)  (the HOLD row included)
+  int r2t_cols;     // valid positions inside a request row
+  int num_experts;  // valid expert ids (negative ids mean "no expert" and pass)
+  int* status;
+};
+#ifdef LLB_DEBUG_BOUNDS
+#define LLB_DEBUG_BOUNDS_STORAGE(unit)                                                                      \
+  __constant__ llb::DebugBounds g_dbg_bounds = {0, 0, 0, 0, nullptr};                                      \
+  LLB_EXPORT int llb_debug_set_bounds_##unit(int pool_slots, int req_rows, int r2t_cols, int num_experts,  \
+                                             int* status) {                                                \
+    llb::DebugBounds b = {pool_slots, req_rows, r2t_cols, num_experts, status};                            \
+    cudaError_t e = cudaMemcpyToSymbol(g_dbg_bounds, &b, sizeof(b));                                       \
+    return e == cudaSuccess ? 0 : (int)e;                                                                  \
+  }
+#define LLB_DBG_CHECK(idx, field, code) llb::dbg_check((idx), g_dbg_bounds.field, g_dbg_bounds.status, (code))
+__device__ __forceinline__ int dbg_check(int idx, int limit, int* status, int code) {
+  if (limit > 0 && (idx < 0 || idx >= limit)) {
+    if (status) atomicCAS(status, 0, code);
+    return 0;
+  }
+  return idx;
+}
+#else
+#define LLB_DEBUG_BOUNDS_STORAGE(unit)
+#define LLB_DBG_CHECK(idx, field, code) (idx)
+#endif
+#define LLB_CHECK_SLOT(x) LLB_DBG_CHECK((x), pool_slots, 901)
+#define LLB_CHECK_REQ(x) LLB_DBG_CHECK((x), req_rows, 902)
+#define LLB_CHECK_POS(x) LLB_DBG_CHECK((x), r2t_cols, 903)
+#define LLB_CHECK_EXPERT(x) LLB_DBG_CHECK((x), num_experts, 904)
+
 __host__ __device__ __forceinline__ int cdiv(int a, int b) { return (a + b - 1) / b; }
 __host__ __device__ __forceinline__ int64_t cdiv64(int64_t a, int64_t b) { return (a + b - 1) / b; }
 

@@ -18,6 +18,8 @@
 #include "common.cuh"
 
 using namespace llb;
+LLB_DEBUG_BOUNDS_STORAGE(mla)
+
 
 namespace {
 
@@ -52,7 +54,7 @@ mla_attention_kernel(const bf16* __restrict__ q_lat, const bf16* __restrict__ q_
   const int head0 = blockIdx.x * 16;
   const int nrows = min(16, hq - head0);
   const int b = batch_of ? batch_of[t] : t;
-  const int req = b_req_idx[b];
+  const int req = LLB_CHECK_REQ(b_req_idx[b]);
   const int kv_len = b_ready_len[b] + (t - cu_q[b]) + 1;  // causal: positions 0 .. own position
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, tig = lane & 3;
@@ -79,7 +81,7 @@ mla_attention_kernel(const bf16* __restrict__ q_lat, const bf16* __restrict__ q_
       int tok = c / CH, ch = c % CH;
       int pos = p0 + tok;
       bool ok = pos < kv_len;
-      int sl = ok ? req_to_token[r2t_base + pos] : 0;
+      int sl = ok ? LLB_CHECK_SLOT(req_to_token[r2t_base + pos]) : 0;
       cp_async16(sb + swz576(tok, ch), kv_layer + (int64_t)sl * DQK + ch * 8, ok);
     }
     cp_async_commit();

@@ -15,6 +15,8 @@
 #include "common.cuh"
 
 using namespace llb;
+LLB_DEBUG_BOUNDS_STORAGE(moe)
+
 
 namespace {
 
@@ -197,7 +199,7 @@ moe_align_kernel(const int* __restrict__ ids, int n_pairs, int e0, int E_local, 
   for (int i = threadIdx.x; i < E_local; i += blockDim.x) cnt[i] = 0;
   __syncthreads();
   for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
-    int e = ids[p] - e0;
+    int e = (ids[p] < 0 ? ids[p] : LLB_CHECK_EXPERT(ids[p])) - e0;
     if (e >= 0 && e < E_local) atomicAdd(&cnt[e], 1);
   }
   __syncthreads();

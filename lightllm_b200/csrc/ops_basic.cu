@@ -7,6 +7,8 @@
 #include "common.cuh"
 
 using namespace llb;
+LLB_DEBUG_BOUNDS_STORAGE(ops_basic)
+
 
 // ---------------------------------------------------------------------------------------
 // RMSNorm:  y = x * rsqrt(mean(x^2) + eps) * (w + w_offset)
@@ -161,7 +163,7 @@ __global__ void __launch_bounds__(256) rope_kv_scatter_kernel(bf16* __restrict__
   const int half = rot_dim >> 1;
   const int half_lanes = half >> 3;
   const int p = pos[t];
-  const int s = slot[t];
+  const int s = LLB_CHECK_SLOT(slot[t]);
   bf16* row = qkv + (int64_t)t * qkv_stride;
   const float* cr = cos_t + (int64_t)p * half;
   const float* sr = sin_t + (int64_t)p * half;
@@ -284,11 +286,11 @@ __global__ void decode_prologue_kernel(int64_t* __restrict__ ids, int* __restric
                                        int next_token_stride) {
   int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= B) return;
-  int req = b_req_idx[b];
+  int req = LLB_CHECK_REQ(b_req_idx[b]);
   int L = b_seq_len[b];
   if (ids != nullptr) ids[b] = next_token[(int64_t)req * next_token_stride];
   pos[b] = L - 1;
-  req_to_token[(int64_t)req * r2t_stride + (L - 1)] = new_slot[b];
+  req_to_token[(int64_t)req * r2t_stride + LLB_CHECK_POS(L - 1)] = LLB_CHECK_SLOT(new_slot[b]);
 }
 
 LLB_EXPORT int llb_decode_prologue(int64_t* ids, int* pos, int* req_to_token, const int64_t* next_token,
@@ -306,14 +308,14 @@ __global__ void prefill_prologue_kernel(int* __restrict__ pos, int* __restrict__
                                         const int* __restrict__ b_ready_len, const int* __restrict__ cu_q,
                                         const int* __restrict__ new_slot, int64_t r2t_stride) {
   int b = blockIdx.x;
-  int req = b_req_idx[b];
+  int req = LLB_CHECK_REQ(b_req_idx[b]);
   int ready = b_ready_len[b];
   int s = cu_q[b], e = cu_q[b + 1];
   for (int j = s + threadIdx.x; j < e; j += blockDim.x) {
     int p = ready + (j - s);
     pos[j] = p;
     batch_of[j] = b;
-    req_to_token[(int64_t)req * r2t_stride + p] = new_slot[j];
+    req_to_token[(int64_t)req * r2t_stride + LLB_CHECK_POS(p)] = LLB_CHECK_SLOT(new_slot[j]);
   }
 }
 
@@ -334,7 +336,7 @@ __global__ void scatter_next_token_kernel(int64_t* __restrict__ next_token, cons
   int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= B) return;
   if (has_out != nullptr && !has_out[b]) return;
-  next_token[(int64_t)b_req_idx[b] * next_token_stride] = sampled[b];
+  next_token[(int64_t)LLB_CHECK_REQ(b_req_idx[b]) * next_token_stride] = sampled[b];
 }
 LLB_EXPORT int llb_scatter_next_token(int64_t* next_token, const int64_t* sampled, const int* b_req_idx,
                                       const uint8_t* has_out, int B, int next_token_stride, cudaStream_t st) {

@@ -243,6 +243,8 @@ class ModelBackend:
         fused = getattr(self.model.tp, "fused", None)
         if fused is not None and (self._steps & 127) == 1:
             fused.check()
+        if (self._steps & 127) == 1 and getattr(self.model, "debug_status", None) is not None:
+            self.model.check_debug_bounds()
         prefill, decode, finished = self._get_classed_reqs()
         kind = self.control.select(len(prefill), len(decode))
         n_tok = 0

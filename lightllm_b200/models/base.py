@@ -157,6 +157,16 @@ class TransformerLM:
         self._graphs: Dict[int, dict] = {}
         self._graph_pool = None
         self.weight_version = "default"
+        self.debug_status = None
+        if self.device.type == "cuda":
+            from ..ops._native import debug_bounds_enabled, set_debug_bounds
+
+            if debug_bounds_enabled():   # LLB_DEBUG_BOUNDS=1: the kernels check slot / request / expert indices
+                self.debug_status = torch.zeros(1, dtype=torch.int32, device=self.device)
+                set_debug_bounds(pool_slots=self.mem_manager.size + 1, req_rows=self.max_req_num + 1,
+                                 r2t_cols=self.max_seq_length,
+                                 num_experts=int(config.get("num_experts") or config.get("n_routed_experts") or
+                                                 config.get("num_local_experts") or 0), status=self.debug_status)
 
     def _open_checkpoint(self, model_dir):
         """The checkpoint as a WeightSource; AWQ checkpoints are presented de-quantised (no int4 GEMM here)."""
@@ -860,6 +870,14 @@ class TransformerLM:
         return self._dense_ffn(lw, h)
 
     # ------------------------------------------------------------------ misc
+    def check_debug_bounds(self):
+        """Raises if the checked build (LLB_DEBUG_BOUNDS=1) saw an index outside its table."""
+        if self.debug_status is not None:
+            code = int(self.debug_status.item())
+            if code:
+                what = {901: "KV pool slot", 902: "request row", 903: "request-table column", 904: "expert id"}
+                raise RuntimeError(f"index check failed on the device: {what.get(code, code)} out of range")
+
     def flush_graphs(self):
         self._graphs.clear()
 

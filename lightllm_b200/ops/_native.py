@@ -47,11 +47,38 @@ def _load(name: str):
     return ctypes.CDLL(str(path))
 
 
+def debug_bounds_enabled() -> bool:
+    return os.environ.get("LLB_DEBUG_BOUNDS", "0") == "1"
+
+
 def kernels():
     global _kernels
     if _kernels is None:
-        _kernels = _load("libllb_kernels.so")
+        if debug_bounds_enabled():   # the build with index checks (csrc/common.cuh)
+            if not (_LIB_DIR / "libllb_kernels_dbg.so").exists():
+                from .. import build as _b
+
+                _b.build_kernels(verbose=False, debug_bounds=True)
+            _kernels = _load("libllb_kernels_dbg.so")
+        else:
+            _kernels = _load("libllb_kernels.so")
     return _kernels
+
+
+_DEBUG_UNITS = ("ops_basic", "attention", "attention_tc", "mla", "moe")
+
+
+def set_debug_bounds(pool_slots: int = 0, req_rows: int = 0, r2t_cols: int = 0, num_experts: int = 0, status=None):
+    """Declares the table sizes the checked build compares indices with (0 = unchecked) and the int32 device word
+    that receives the code of the first violation.  A no-op in the regular build."""
+    if not debug_bounds_enabled():
+        return False
+    lib = kernels()
+    for unit in _DEBUG_UNITS:
+        fn = getattr(lib, f"llb_debug_set_bounds_{unit}")
+        check(fn(ctypes.c_int(pool_slots), ctypes.c_int(req_rows), ctypes.c_int(r2t_cols), ctypes.c_int(num_experts),
+                 ptr(status)), f"debug_set_bounds_{unit}")
+    return True
 
 
 def runtime():
