@@ -81,9 +81,6 @@ class FusedTP:
         """True if `partial` is the buffer handed out by `partial_out` for the coming call."""
         return partial.is_cuda and partial.data_ptr() == self.region.local_ptr + self.off_partial[self.parity]
 
-    def can_all_reduce(self, x) -> bool:
-        return False  # plain all-reduces (embedding, final residual) stay on NCCL
-
     def _tables(self, par):
         t = self._tabs.get(par)
         if t is None:
@@ -206,9 +203,6 @@ class FusedTP:
         buffer alternation in step, so that every pass starts on the same buffer (CUDA-graph replays reuse the
         captured addresses and two consecutive calls must never share a buffer)."""
         self.parity ^= 1
-
-    def all_reduce_(self, x):
-        raise NotImplementedError
 
     def check(self):
         """Raise if a bounded wait of the kernel ran out (a peer did not show up within a second)."""

@@ -36,8 +36,8 @@ class TPContext:
     def all_reduce_(self, x):
         if self.size == 1:
             return x
-        if self.fused is not None and self.fused.can_all_reduce(x):
-            return self.fused.all_reduce_(x)
+        # plain all-reduces (vocabulary-parallel embedding, the last layer's partial sums) are rare per pass:
+        # they stay on the library collective; the fused kernels cover reduce + residual + norm
         dist.all_reduce(x, group=self.group)
         return x
 

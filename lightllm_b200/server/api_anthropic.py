@@ -10,6 +10,7 @@ import uuid
 from types import SimpleNamespace
 
 from fastapi import Request
+from .api_stream_obj import stream_response
 from fastapi.responses import JSONResponse, StreamingResponse
 
 from .build_prompt import build_prompt
@@ -113,4 +114,4 @@ async def anthropic_messages_impl(raw: Request, g):
                                    "usage": {"output_tokens": n_out}})
         yield ev("message_stop", {"type": "message_stop"})
 
-    return StreamingResponse(stream(), media_type="text/event-stream")
+    return await stream_response(stream(), g)

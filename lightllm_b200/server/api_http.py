@@ -68,6 +68,16 @@ app = FastAPI()
 g_objs.app = app
 
 
+@app.middleware("http")
+async def echo_request_id(request: Request, call_next):
+    """A caller's X-Request-Id comes back on the response, so that proxies and clients can pair the two."""
+    response = await call_next(request)
+    xid = request.headers.get("X-Request-Id")
+    if xid:
+        response.headers["X-Request-Id"] = xid
+    return response
+
+
 def create_error_response(status_code: int, message: str) -> JSONResponse:
     if g_objs.metric_client is not None:
         g_objs.metric_client.counter_inc("lightllm_request_failure")

@@ -10,6 +10,7 @@ import json
 from collections import defaultdict
 
 from fastapi import Request
+from .api_stream_obj import stream_response
 from fastapi.responses import JSONResponse, Response, StreamingResponse
 
 from .core.objs.sampling_params import SamplingParams
@@ -93,4 +94,4 @@ async def lightllm_generate_stream(request: Request, g) -> Response:
                    "details": None}
             yield ("data:" + json.dumps(ret, ensure_ascii=False) + "\n\n").encode("utf-8")
 
-    return StreamingResponse(stream(), media_type="text/event-stream")
+    return await stream_response(stream(), g)

@@ -12,6 +12,7 @@ import uuid
 from typing import AsyncGenerator, Dict, List
 
 from fastapi import Request
+from .api_stream_obj import stream_response
 from fastapi.responses import JSONResponse, Response, StreamingResponse
 
 from .api_models import (ChatCompletionRequest, ChatCompletionResponse, ChatCompletionResponseChoice,
@@ -162,7 +163,7 @@ async def chat_completions_impl(request: ChatCompletionRequest, raw_request: Req
             yield ("data: " + json.dumps(chunk.model_dump(exclude_none=True), ensure_ascii=False) + "\n\n").encode()
         yield b"data: [DONE]\n\n"
 
-    return StreamingResponse(stream(), media_type="text/event-stream")
+    return await stream_response(stream(), g)
 
 
 async def completions_impl(request: CompletionRequest, raw_request: Request, g) -> Response:
@@ -209,7 +210,7 @@ async def completions_impl(request: CompletionRequest, raw_request: Request, g) 
                 yield ("data: " + json.dumps(chunk.model_dump(exclude_none=True), ensure_ascii=False) + "\n\n").encode()
             yield b"data: [DONE]\n\n"
 
-        return StreamingResponse(stream(), media_type="text/event-stream")
+        return await stream_response(stream(), g)
 
     choices = []
     total_prompt, total_out, cached = 0, 0, 0

@@ -10,6 +10,7 @@ import uuid
 from types import SimpleNamespace
 
 from fastapi import Request
+from .api_stream_obj import stream_response
 from fastapi.responses import JSONResponse, StreamingResponse
 
 from .build_prompt import build_prompt
@@ -73,4 +74,4 @@ async def responses_impl(raw: Request, g):
         done = {"type": "response.completed", "response": envelope("completed", "".join(text), n_in, n_out)}
         yield f"event: response.completed\ndata: {json.dumps(done, ensure_ascii=False)}\n\n".encode()
 
-    return StreamingResponse(stream(), media_type="text/event-stream")
+    return await stream_response(stream(), g)

@@ -5,6 +5,7 @@ from __future__ import annotations
 import json
 
 from fastapi import Request
+from .api_stream_obj import stream_response
 from fastapi.responses import JSONResponse, Response, StreamingResponse
 
 from .core.objs.sampling_params import SamplingParams
@@ -64,4 +65,4 @@ async def tgi_generate_stream_impl(request: Request, g) -> Response:
                    if fs.is_finished() else None}
             yield ("data:" + json.dumps(ret, ensure_ascii=False) + "\n\n").encode()
 
-    return StreamingResponse(stream(), media_type="text/event-stream")
+    return await stream_response(stream(), g)

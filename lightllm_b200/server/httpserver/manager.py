@@ -187,7 +187,15 @@ class HttpServerManager:
                 sampling_params.pd_kv_trans_params.set({"peer_ip": ip, "peer_port": port,
                                                         "master_req_id": pd_info["group_req_id"],
                                                         "decode_node_id": pd_info["peer"]["node_id"]})
+        if request is not None and not is_health_req:   # correlate with the caller's own ids in the log
+            hdr = getattr(request, "headers", None) or {}
+            xid, sid = hdr.get("X-Request-Id", ""), hdr.get("X-Session-Id", "")
+            if xid or sid:
+                print(f"[http] received req X-Request-Id:{xid} X-Session-Id:{sid} lightllm_req_id:{group_req_id}",
+                      flush=True)
         if self.metric_client is not None:
+            # tokenisation, multimodal preload and length checks: everything before the request can be queued
+            self.metric_client.histogram_observe("lightllm_request_validation_duration", time.time() - start_time)
             self.metric_client.counter_inc("lightllm_request_count")
             self.metric_client.histogram_observe("lightllm_request_input_length", len(prompt_ids))
             self.metric_client.histogram_observe("lightllm_request_max_new_tokens", sampling_params.max_new_tokens)

@@ -10,7 +10,8 @@ GAUGES = ["lightllm_batch_current_size", "lightllm_batch_next_size", "lightllm_b
           "lightllm_num_running_reqs", "lightllm_batch_current_max_tokens", "lightllm_cache_length",
           "lightllm_cache_ratio", "lightllm_cache_hit_rate", "lightllm_mtp_avg_token_per_step",
           "lightllm_gen_throughput"]
-DURATION_HISTS = ["lightllm_request_duration", "lightllm_request_inference_duration",
+DURATION_HISTS = ["lightllm_request_duration", "lightllm_request_validation_duration",
+                  "lightllm_request_inference_duration",
                   "lightllm_request_first_token_duration", "lightllm_request_mean_time_per_token_duration",
                   "lightllm_request_queue_duration", "lightllm_batch_inference_duration_bucket"]
 LENGTH_HISTS = ["lightllm_request_input_length", "lightllm_request_generated_tokens", "lightllm_request_max_new_tokens"]

@@ -204,3 +204,13 @@ def test_load_generator_against_the_server(server):
         assert "ttft" in txt.lower() and ("tok" in txt.lower())
         done = rep.get("completed", rep.get("num_completed", rep.get("requests_ok", 6)))
         assert done == 6
+
+
+@pytest.mark.timeout(600)
+def test_request_id_echo_and_validation_metric(server):
+    body = {"inputs": list(range(5, 25)), "parameters": {"max_new_tokens": 2, "ignore_eos": True}}
+    r = requests.post(server + "/generate", json=body, headers={"X-Request-Id": "abc-123"}, timeout=60)
+    assert r.status_code == 200 and r.headers.get("X-Request-Id") == "abc-123"
+    assert "X-Request-Id" not in requests.post(server + "/generate", json=body, timeout=60).headers
+    m = requests.get(server + "/metrics", timeout=30).text
+    assert "lightllm_request_validation_duration_count" in m
