@@ -2,8 +2,12 @@
 
 Every supported syntax is described by a begin marker, an end marker and a body decoder that
 turns the text between them into (name, json-arguments) pairs.  The streaming parser withholds
-text from the first (possibly partial) begin marker on and emits each call once its body is
-complete: one delta with the function name and the full argument string.
+text from the first (possibly partial) begin marker on.  For the JSON-bodied syntaxes (a single
+`{"name": ..., "arguments": {...}}` object per call) a call is streamed the way OpenAI clients expect:
+one delta with the function name and empty arguments as soon as the name is complete, then the
+argument text piece by piece as it is generated (deltas without a name, same tool index).  Bodies
+of any other shape (lists of calls, arguments given as a string, the tag-based syntaxes) are
+emitted once complete: one delta with the name and the full argument string.
 
 Reference: lightllm/server/function_call_parser.py (qwen25, llama3, mistral, deepseekv3/v31/v32,
 glm47, kimi_k2, qwen3_coder).
@@ -113,6 +117,73 @@ def _qwen3_coder_calls(body: str):
     return out
 
 
+_JSON_HEAD = re.compile(r'\s*\{\s*"name"\s*:\s*"((?:[^"\\]|\\.)*)"\s*,\s*"(?:arguments|parameters)"\s*:\s*')
+
+
+class _JsonArgStream:
+    """Incremental view of one `{"name": "f", "arguments": {...}}` body: `feed(body)` is called with everything
+    received so far and returns (name or None on later calls, new piece of the argument text).  `usable` turns
+    False as soon as the body cannot be streamed this way (the caller then waits for the whole body)."""
+
+    def __init__(self):
+        self.usable = True
+        self.name_sent = False
+        self.val_start = -1
+        self.emitted = 0          # characters of the argument value handed out
+        self.complete = False     # the argument value has been closed
+        # scanner state inside the value
+        self._pos, self._depth, self._in_str, self._esc = 0, 0, False, False
+
+    def feed(self, body: str):
+        if not self.usable or self.complete:
+            return None, ""
+        if self.val_start < 0:
+            m = _JSON_HEAD.match(body)
+            if m is None:
+                head = body.lstrip()
+                # still a prefix of what the pattern wants?  (a '{', then "name", its string, a comma, the key)
+                probe = '{"name":'
+                compact = re.sub(r"\s+", "", head[:64])
+                if compact and not (probe.startswith(compact[:len(probe)]) or compact.startswith(probe)):
+                    self.usable = False
+                return None, ""
+            if m.end() >= len(body):
+                return None, ""
+            if body[m.end()] not in "{[":
+                self.usable = False      # arguments given as a string or a scalar: decode at the end
+                return None, ""
+            self.val_start = self._pos = m.end()
+            self._name = json.loads('"' + m.group(1) + '"')
+        # advance the scanner to find the end of the value (if it is there yet)
+        i = self._pos
+        while i < len(body) and not self.complete:
+            ch = body[i]
+            if self._in_str:
+                if self._esc:
+                    self._esc = False
+                elif ch == "\\":
+                    self._esc = True
+                elif ch == '"':
+                    self._in_str = False
+            elif ch == '"':
+                self._in_str = True
+            elif ch in "{[":
+                self._depth += 1
+            elif ch in "}]":
+                self._depth -= 1
+                if self._depth == 0:
+                    self.complete = True
+            i += 1
+        self._pos = i
+        piece = body[self.val_start + self.emitted:i]
+        self.emitted += len(piece)
+        name = None
+        if not self.name_sent:
+            self.name_sent = True
+            name = self._name
+        return name, piece
+
+
 @dataclass
 class CallFormat:
     begin: str
@@ -149,6 +220,7 @@ class FunctionCallParser:
         self._buf = ""
         self._index = 0
         self._in_call = False
+        self._json_stream: Optional[_JsonArgStream] = None   # per call, JSON-bodied syntaxes only
 
     def has_tool_call(self, text: str) -> bool:
         return self.fmt.begin in text
@@ -183,6 +255,25 @@ class FunctionCallParser:
             pos = j + len(f.end)
         return "".join(normal).strip("\n"), calls
 
+    def _stream_json_body(self, body: str, calls: List[ToolCallItem]) -> bool:
+        """Feeds the body received so far to the incremental JSON view; returns True while that view is in charge
+        of this call (False: the body has to be decoded as a whole)."""
+        js = self._json_stream
+        if js is None or not js.usable:
+            return False
+        name, piece = js.feed(body)
+        if not js.usable:
+            return False
+        if name is not None:
+            if self.tool_names and name not in self.tool_names:
+                js.usable = False          # not one of the declared tools: dropped like in the whole-body path
+                js.dropped = True
+                return True
+            calls.append(ToolCallItem(self._index, name, ""))
+        if piece and not getattr(js, "dropped", False):
+            calls.append(ToolCallItem(self._index, None, piece))
+        return True
+
     def parse_stream_chunk(self, chunk: str) -> Tuple[str, List[ToolCallItem]]:
         f = self.fmt
         self._buf += chunk
@@ -194,6 +285,7 @@ class FunctionCallParser:
                     normal += self._buf[:i]
                     self._buf = self._buf[i + len(f.begin):]
                     self._in_call = True
+                    self._json_stream = _JsonArgStream() if f.decode is _json_calls else None
                     continue
                 keep = 0
                 for n in range(min(len(f.begin) - 1, len(self._buf)), 0, -1):
@@ -203,17 +295,41 @@ class FunctionCallParser:
                 normal += self._buf[:len(self._buf) - keep]
                 self._buf = self._buf[len(self._buf) - keep:]
                 break
+            js = self._json_stream
             if f.end is None:
-                # body runs to the end of generation: try to decode what we have when it parses as JSON
-                items = self._items(self._buf)
+                # body runs to the end of generation
+                if getattr(self, "_swallow", False):  # the call was streamed to its end: drop what follows it
+                    self._buf = ""
+                    break
+                if self._stream_json_body(self._buf, calls) or getattr(js, "dropped", False):
+                    if js.complete and js.name_sent and not getattr(js, "dropped", False):
+                        self._index += 1
+                        self._swallow = True
+                    break
+                if js is not None and js.name_sent:
+                    break                             # already handed out incrementally
+                items = self._items(self._buf)        # decode what we have once it parses as JSON
                 if items:
                     calls += items
                     self._buf = ""
                 break
             j = self._buf.find(f.end)
             if j < 0:
+                # keep a possible partial end marker out of the incremental view
+                hold = 0
+                for n in range(min(len(f.end) - 1, len(self._buf)), 0, -1):
+                    if f.end.startswith(self._buf[-n:]):
+                        hold = n
+                        break
+                self._stream_json_body(self._buf[:len(self._buf) - hold], calls)
                 break
-            calls += self._items(self._buf[:j])
+            streamed = self._stream_json_body(self._buf[:j], calls)
+            if streamed or (js is not None and js.name_sent):
+                if js.name_sent and not getattr(js, "dropped", False):
+                    self._index += 1
+            else:
+                calls += self._items(self._buf[:j])
             self._buf = self._buf[j + len(f.end):]
             self._in_call = False
+            self._json_stream = None
         return normal, calls

@@ -28,7 +28,51 @@ def test_qwen_tool_calls_whole_and_streamed(step):
     assert json.loads(calls[0].parameters) == {"city": "Paris"} and [c.tool_index for c in calls] == [0, 1]
     s_normal, s_calls = _stream(FunctionCallParser(TOOLS, "qwen25"), text, step)
     assert s_normal.strip() == "I will check."
-    assert [(c.name, json.loads(c.parameters)) for c in s_calls] == [(c.name, json.loads(c.parameters)) for c in calls]
+    assert _assemble(s_calls) == [(c.name, json.loads(c.parameters)) for c in calls]
+
+
+def _assemble(deltas):
+    """What an OpenAI client builds from the deltas: the first delta of a tool index names the function, the
+    argument pieces are concatenated."""
+    by = {}
+    for d in deltas:
+        slot = by.setdefault(d.tool_index, {"name": None, "args": ""})
+        if d.name is not None:
+            assert slot["name"] is None, "the function name is sent once per call"
+            slot["name"] = d.name
+        else:
+            assert slot["name"] is not None, "argument pieces only follow the delta that names the function"
+        slot["args"] += d.parameters
+    return [(by[i]["name"], json.loads(by[i]["args"])) for i in sorted(by)]
+
+
+@pytest.mark.parametrize("step", [1, 2, 5, 11])
+def test_json_arguments_stream_piece_by_piece(step):
+    text = ('<tool_call>{"name": "get_weather", "arguments": {"city": "Pa\\"ris}", "days": [1, {"k": "]"}], '
+            '"note": "x"}}</tool_call> done <tool_call>{"name":"add","arguments":{"a":1,"b":2}}</tool_call>')
+    normal, deltas = _stream(FunctionCallParser(TOOLS, "qwen25"), text, step)
+    assert normal.strip() == "done"
+    assert _assemble(deltas) == [("get_weather", {"city": 'Pa"ris}', "days": [1, {"k": "]"}], "note": "x"}),
+                                 ("add", {"a": 1, "b": 2})]
+    first = [d for d in deltas if d.tool_index == 0]
+    assert first[0].name == "get_weather" and first[0].parameters == ""      # name first, empty arguments
+    if step <= 5:
+        assert len(first) > 4                                                # the arguments came in several pieces
+    # the closing brace of the call object and the end marker never leak into the arguments
+    assert "".join(d.parameters for d in first).endswith('"note": "x"}')
+
+
+@pytest.mark.parametrize("step", [1, 3, 1000])
+def test_bodies_that_cannot_be_streamed_are_emitted_whole(step):
+    cases = [("mistral", '[TOOL_CALLS][{"name":"add","arguments":{"a":1}},{"name":"get_weather","arguments":{"city":"x"}}]',
+              [("add", {"a": 1}), ("get_weather", {"city": "x"})]),
+             ("qwen25", '<tool_call>{"name":"add","arguments":"{\\"a\\": 1}"}</tool_call>', [("add", {"a": 1})]),
+             ("qwen25", '<tool_call>{"arguments":{"a": 1},"name":"add"}</tool_call>', [("add", {"a": 1})]),
+             ("llama3", '<|python_tag|>{"name": "add", "parameters": {"a": 5, "b": 7}} trailing', [("add", {"a": 5, "b": 7})]),
+             ("qwen25", '<tool_call>{"name":"rm_rf","arguments":{"a":1}}</tool_call>tail', [])]
+    for fmt, text, want in cases:
+        normal, deltas = _stream(FunctionCallParser(TOOLS, fmt), text, step)
+        assert _assemble(deltas) == want, (fmt, text)
 
 
 def test_other_call_syntaxes_and_unknown_tools():
