@@ -275,6 +275,17 @@ async def startup_event():
         add_pd_routes(app, g_objs)
     loop = asyncio.get_event_loop()
     loop.create_task(g_objs.httpserver_manager.handle_loop())
+    from .httpserver import multinode_relay
+
+    if multinode_relay.enabled(args):
+        if args.node_rank == 0:
+            relay = multinode_relay.RelayMaster(args.multinode_httpmanager_port, args.nnodes - 1)
+            await relay.wait_peers()
+            g_objs.httpserver_manager.relay_master = relay
+        else:
+            relay = multinode_relay.RelayFollower(args.nccl_host, args.multinode_httpmanager_port, args.node_rank)
+            await relay.hello()
+            g_objs.relay_task = loop.create_task(relay.follow(g_objs.httpserver_manager))
     if args.run_mode in ("prefill", "decode"):
         from .httpserver.pd_loop import start_pd_loops
 

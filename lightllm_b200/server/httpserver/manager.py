@@ -78,6 +78,7 @@ class HttpServerManager:
         self.run_reqs_count_mark = SharedInt(f"{self.name}_run_reqs_count_mark")
         self.metric_client = metric_client
         self.paused = False  # RL: admission gate
+        self.relay_master = None  # httpserver/multinode_relay.py on node 0 of a multi-node tensor-parallel deployment
         self.master_id_to_local: Dict[int, int] = {}  # PD nodes: pd_master request id -> local group id
         self.eos_ids = set(args.eos_ids or [])
         self.all_special_ids = set(getattr(self.tokenizer, "all_special_ids", []) or [])
@@ -157,12 +158,15 @@ class HttpServerManager:
 
     # ------------------------------------------------------------------ generate
     async def generate(self, prompt: Union[str, List[int]], sampling_params: SamplingParams, multimodal_params=None,
-                       request=None, is_health_req: bool = False, pd_info: Optional[dict] = None):
-        """`pd_info` (P/D nodes only) = {"group_req_id": the pd_master's id, "peer": the paired node}."""
+                       request=None, is_health_req: bool = False, pd_info: Optional[dict] = None,
+                       group_req_id: Optional[int] = None):
+        """`pd_info` (P/D nodes only) = {"group_req_id": the pd_master's id, "peer": the paired node}.
+        `group_req_id`: set on the follower nodes of a multi-node tensor-parallel deployment, where node 0 chose it."""
         if self.paused and not is_health_req:
             raise ServerBusyError("generation is paused")
         start_time = time.time()
-        group_req_id = self.id_gen.generate_id()
+        if group_req_id is None:
+            group_req_id = self.id_gen.generate_id()
         sampling_params.group_request_id = group_req_id
         mm, mm_record_ids = None, []
         if multimodal_params and self.enable_multimodal and \
@@ -232,6 +236,8 @@ class HttpServerManager:
         self.req_id_to_out_inf[group_req_id] = status
         self.run_reqs_count_mark.add(1)
         first_stage = self.send_to_visual if mm is not None else self.send_to_router
+        if self.relay_master is not None:     # multi-node tensor parallelism: the other nodes queue the same request
+            await self.relay_master.relay(group_req_id, prompt_ids, sampling_params, multimodal_params)
         await first_stage.send_pyobj(GroupReqIndexes(group_req_id, multimodal_params, indexes, start_time),
                                      protocol=pickle.HIGHEST_PROTOCOL)
         try:

@@ -63,6 +63,9 @@ class RouterManager:
         self.max_total_token_num = 0
         self._last_load_refresh = 0.0
         self.metrics = None
+        self.mn_sync = None     # server/router/multinode_sync.py when --nnodes > 1 and --dp 1
+        self._mn_dropped = set()  # group ids of waiting requests that node 0 dropped (client gone)
+        self._exit_flushed = False
 
     # ------------------------------------------------------------------ start-up
     def wait_to_model_ready(self):
@@ -88,6 +91,30 @@ class RouterManager:
         self.args.max_total_token_num = self.max_total_token_num
         self.shm_max_total_token_num.set_value(self.max_total_token_num)
         self.req_queue = build_req_queue(self.args, self.max_total_token_num, self.dp_size_in_node, self.statics)
+        if self.args.nnodes > 1 and self.args.dp == 1:
+            self._init_multinode_sync()
+
+    def _init_multinode_sync(self):
+        """A gloo group of the routers (one per node) on `--multinode_router_gloo_port` of node 0's address; the
+        pool size every router plans with is the smallest one any node measured."""
+        import datetime
+
+        import torch
+        import torch.distributed as dist
+
+        from .multinode_sync import MultiNodeRouterSync
+
+        a = self.args
+        dist.init_process_group("gloo", init_method=f"tcp://{a.nccl_host}:{a.multinode_router_gloo_port}",
+                                rank=a.node_rank, world_size=a.nnodes, timeout=datetime.timedelta(minutes=30))
+        t = torch.tensor([self.max_total_token_num], dtype=torch.int64)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        if int(t) != self.max_total_token_num:
+            self.max_total_token_num = int(t)
+            self.args.max_total_token_num = self.max_total_token_num
+            self.shm_max_total_token_num.set_value(self.max_total_token_num)
+            self.req_queue = build_req_queue(a, self.max_total_token_num, self.dp_size_in_node, self.statics)
+        self.mn_sync = MultiNodeRouterSync(None, a.node_rank, a.nnodes)
 
     # ------------------------------------------------------------------ loop pieces
     def _recv_new_reqs(self, limit: int = 256):
@@ -111,6 +138,9 @@ class RouterManager:
         for idx in g.shm_req_indexes:
             r = self.shm_req_manager.get_req_obj_by_index(idx)
             r._mm_params = g.multimodal_params
+            if r.group_req_id in self._mn_dropped:      # node 0 dropped it before it got here
+                self._mn_dropped.discard(r.group_req_id)
+                r.is_aborted = True
             reqs.append(r)
         self.req_queue.extend(reqs)
         self.send_to_detok.send_pyobj(g, protocol=pickle.HIGHEST_PROTOCOL)
@@ -135,15 +165,8 @@ class RouterManager:
         self.batch_id += 1
         return self.req_queue.generate_new_batch(self.running_batch, self.batch_id)
 
-    def _flush_mailbox(self, new_batch: Optional[Batch]):
-        """Writes everything pending (new batch, aborts, stop hits, control commands) as one message."""
-        if not self.mailbox.is_empty():
-            return False
-        cmds = list(self.pending_cmds)
-        self.pending_cmds = []
-        if new_batch is not None:
-            cmds.append(NewReqsCmd([(r.request_id, r.index_in_shm_mem, getattr(r, "_mm_params", None),
-                                     r.sample_params.suggested_dp_index) for r in new_batch.reqs]))
+    def _abort_and_stop_cmds(self):
+        cmds = []
         if self.running_batch is not None:
             for r in self.running_batch.reqs:
                 if r.is_aborted and not getattr(r, "_abort_sent", False):
@@ -152,6 +175,65 @@ class RouterManager:
                 if r.stop_str_matched and not getattr(r, "_stop_sent", False):
                     r._stop_sent = True
                     cmds.append(StopStrMatchedReqCmd(r.request_id))
+        return cmds
+
+    def _new_reqs_cmd(self, batch: Batch):
+        return NewReqsCmd([(r.request_id, r.index_in_shm_mem, getattr(r, "_mm_params", None),
+                            r.sample_params.suggested_dp_index) for r in batch.reqs])
+
+    def _round_multinode(self):
+        """One scheduling round of a multi-node tensor-parallel deployment (see router/multinode_sync.py): node 0
+        decides, every node admits the same groups in the same order and writes the same message to its ranks."""
+        q, sync = self.req_queue, self.mn_sync
+        waiting = list(dict.fromkeys(r.group_req_id for r in q.waiting_req_list if not r.is_aborted))
+        all_free, allowed = sync.gather(waiting, self.mailbox.is_empty())
+        plan = None
+        if sync.is_master:
+            chosen, cmds = [], []
+            if all_free:
+                cmds, self.pending_cmds = list(self.pending_cmds), []
+                paused = self.running_batch is not None and any(r.is_paused for r in self.running_batch.reqs)
+                if not paused:
+                    ratio = self._usage_ratio()
+                    if hasattr(q, "set_usage"):
+                        q.set_usage([ratio] * self.dp_size_in_node)
+                    b = q.generate_new_batch(self.running_batch, self.batch_id + 1, allowed_groups=allowed)
+                    if b is not None:
+                        q.waiting_req_list = b.reqs + q.waiting_req_list      # take() below removes them again
+                        chosen = list(dict.fromkeys(r.group_req_id for r in b.reqs))
+                cmds += self._abort_and_stop_cmds()
+            plan = (chosen, cmds, sorted(self._mn_dropped))
+            self._mn_dropped.clear()
+        chosen, cmds, dropped = sync.broadcast(plan)
+        if not sync.is_master and dropped:
+            self._mn_dropped.update(dropped)
+            for r in q.waiting_req_list:
+                if r.group_req_id in self._mn_dropped:
+                    r.is_aborted = True
+        self.batch_id += 1
+        new_batch = q.take(chosen, self.batch_id)
+        if new_batch is not None:
+            cmds = cmds + [self._new_reqs_cmd(new_batch)]
+        if cmds:
+            self.mailbox.write_obj(cmds)
+            self.mailbox.set_ready()
+            if any(isinstance(c, ExitCmd) for c in cmds):
+                self._exit_flushed = True
+        if new_batch is not None:
+            if self.running_batch is None:
+                self.running_batch = new_batch
+            else:
+                self.running_batch.merge(new_batch)
+
+    def _flush_mailbox(self, new_batch: Optional[Batch]):
+        """Writes everything pending (new batch, aborts, stop hits, control commands) as one message."""
+        if not self.mailbox.is_empty():
+            return False
+        cmds = list(self.pending_cmds)
+        self.pending_cmds = []
+        if new_batch is not None:
+            cmds.append(self._new_reqs_cmd(new_batch))
+        cmds += self._abort_and_stop_cmds()
         if not cmds:
             return True
         self.mailbox.write_obj(cmds)
@@ -174,9 +256,13 @@ class RouterManager:
 
     def _step(self):
         self._recv_new_reqs()
+        if self.mn_sync is not None and self.mn_sync.is_master:
+            self._mn_dropped.update(r.group_req_id for r in self.req_queue.waiting_req_list if r.is_aborted)
         self._release_waiting_aborted()
         new_batch = None
-        if self.mailbox.is_empty():
+        if self.mn_sync is not None:
+            self._round_multinode()
+        elif self.mailbox.is_empty():
             new_batch = self._schedule()
             if self._flush_mailbox(new_batch) and new_batch is not None:
                 if self.running_batch is None:
@@ -207,7 +293,9 @@ class RouterManager:
         while not exiting:
             t0 = time.time()
             self._step()
-            if any(isinstance(c, ExitCmd) for c in self.pending_cmds):
+            if self.mn_sync is not None:
+                exiting = self._exit_flushed
+            elif any(isinstance(c, ExitCmd) for c in self.pending_cmds):
                 while not self._flush_mailbox(None):
                     time.sleep(0.001)
                 exiting = True

@@ -182,7 +182,22 @@ class ChunkedPrefillQueue(BaseQueue):
             return 0
         return sum(r.get_decode_need_tokens() for r in current_batch.get_req_list_for_dp(self.dp_index))
 
-    def generate_new_batch(self, current_batch: Optional[Batch], next_batch_id: int = 0) -> Optional[Batch]:
+    def take(self, group_req_ids: List[int], next_batch_id: int = 0) -> Optional[Batch]:
+        """Admits exactly the requests of these groups, in the given order, without consulting the estimate
+        (multi-node tensor parallelism: the master node's router has decided for everybody)."""
+        if not group_req_ids:
+            return None
+        order = {g: i for i, g in enumerate(group_req_ids)}
+        chosen = sorted((r for r in self.waiting_req_list if r.group_req_id in order),
+                        key=lambda r: (order[r.group_req_id], r.request_id))
+        taken = {id(r) for r in chosen}
+        self.waiting_req_list = [r for r in self.waiting_req_list if id(r) not in taken]
+        return Batch(next_batch_id, chosen, self.dp_size_in_node) if chosen else None
+
+    def generate_new_batch(self, current_batch: Optional[Batch], next_batch_id: int = 0,
+                           allowed_groups=None) -> Optional[Batch]:
+        """`allowed_groups`: only requests of these group ids may be admitted (the scan stops at the first waiting
+        request outside it, keeping the order first come, first served)."""
         if not self.waiting_req_list:
             return None
         running = len(current_batch.get_req_list_for_dp(self.dp_index)) if current_batch is not None else 0
@@ -195,6 +210,8 @@ class ChunkedPrefillQueue(BaseQueue):
         for req in self.waiting_req_list:
             if req.is_aborted:  # released by the router, never scheduled
                 continue
+            if allowed_groups is not None and req.group_req_id not in allowed_groups:
+                break
             ok, prefill_tokens = self._admit(est, req, is_busy, prefill_tokens)
             if not ok:
                 break
