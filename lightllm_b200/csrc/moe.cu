@@ -314,6 +314,32 @@ LLB_EXPORT int llb_grouped_topk(const void* logits, int dtype, int64_t stride, c
   return LLB_OK;
 }
 
+// Redundant experts under expert parallelism: counts how often every expert is chosen (the statistic the placement
+// of redundant experts is taken from) and rewrites the router's expert ids into the "physical" id space
+// rank x (experts per rank + redundant per rank) through this rank's table, in which an expert this rank holds a
+// copy of points at the copy.
+__global__ void moe_count_remap_kernel(const int* __restrict__ ids, int n_pairs, const int* __restrict__ table, int E,
+                                       int* __restrict__ counter, int* __restrict__ out) {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_pairs; i += gridDim.x * blockDim.x) {
+    int e = ids[i];
+    if (e < 0 || e >= E) {
+      out[i] = -1;
+      continue;
+    }
+    if (counter != nullptr) atomicAdd(counter + e, 1);
+    out[i] = table[e];
+  }
+}
+
+LLB_EXPORT int llb_moe_count_remap(const int* ids, int n_pairs, const int* table, int E, int* counter, int* out,
+                                   cudaStream_t st) {
+  if (n_pairs <= 0) return LLB_OK;
+  int blocks = cdiv(n_pairs, 256);
+  moe_count_remap_kernel<<<blocks < 296 ? blocks : 296, 256, 0, st>>>(ids, n_pairs, table, E, counter, out);
+  LLB_LAUNCH_CHECK();
+  return LLB_OK;
+}
+
 LLB_EXPORT int llb_moe_align(const int* ids, int n_pairs, int e0, int E_local, int m_pad, int* sorted_pair,
                              int* pair_row, int* mblock_expert, int* expert_off, int* total_rows, cudaStream_t st) {
   if (E_local > 2048 || m_pad % 128 != 0) return LLB_ERR_UNSUPPORTED;

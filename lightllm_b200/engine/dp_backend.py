@@ -24,6 +24,12 @@ class DPBackend(ModelBackend):
         self.ps = self.model.ps
         self.idle_sleep_s = idle_sleep_s
         self.stats.update({"hold_prefill": 0, "hold_decode": 0})
+        self.redundancy = None    # re-places this rank's redundant expert copies from live hit counters
+        if self.model.extra.get("auto_update_redundancy_expert") and \
+                any(getattr(lw, "ep_table", None) is not None for lw in self.model.layers):
+            from .redundancy import RedundancyExpertManager
+
+            self.redundancy = RedundancyExpertManager(self.model)
 
     def has_work(self) -> bool:
         return True  # the agreement inside step() decides; every rank must keep calling step()
@@ -56,6 +62,8 @@ class DPBackend(ModelBackend):
         the GPU executes, so a replica's GPU does not sit idle between passes and, through the layer-wise token
         exchanges, hold up every other replica."""
         self._steps += 1
+        if self.redundancy is not None and self.redundancy.step():
+            self.stats["redundancy_updates"] = self.stats.get("redundancy_updates", 0) + 1
         prefill, decode, finished = self._get_classed_reqs()
         local_kind = self.control.select(len(prefill), len(decode))
         defer = local_kind == "decode" and self._can_defer(decode)

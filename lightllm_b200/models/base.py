@@ -146,6 +146,9 @@ class TransformerLM:
                              device=str(self.device) if self.device.type == "cuda" else "cpu",
                              fp8_names=self.fp8_weight_names())
         self.weight_source = weight_source
+        from ..engine.redundancy import RedundancyConfig
+
+        self.redundancy_cfg = RedundancyConfig.load(extra.get("ep_redundancy_expert_config_path"))
         self._load_weights(weight_source)
         self._init_rope()
         if share_with is not None:
@@ -166,7 +169,8 @@ class TransformerLM:
                 set_debug_bounds(pool_slots=self.mem_manager.size + 1, req_rows=self.max_req_num + 1,
                                  r2t_cols=self.max_seq_length,
                                  num_experts=int(config.get("num_experts") or config.get("n_routed_experts") or
-                                                 config.get("num_local_experts") or 0), status=self.debug_status)
+                                                 config.get("num_local_experts") or 0) +
+                                 self.ps.world_size * self.redundancy_cfg.num, status=self.debug_status)
 
     def _open_checkpoint(self, model_dir):
         """The checkpoint as a WeightSource; AWQ checkpoints are presented de-quantised (no int4 GEMM here)."""

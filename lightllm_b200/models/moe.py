@@ -19,6 +19,8 @@ lightllm/common/basemodel/triton_kernel/fused_moe/*, models/qwen3_moe, models/de
 """
 from __future__ import annotations
 
+import re
+
 import torch
 
 from .. import ops
@@ -77,36 +79,55 @@ def load_experts(model, lw, src, prefix: str, mc: MoEConfig, ep: bool, gate_name
     else:
         e0, e1 = 0, mc.num_experts
         i0, i1 = tp_range(mc.inter, r, tp)
+    # redundant experts (data-parallel attention + expert parallelism only): R more slots behind the rank's own experts
+    red_ids, layer_no = [], -1
+    red_cfg = getattr(model, "redundancy_cfg", None)
+    if ep and tp > 1 and model.ps.dp_size > 1 and red_cfg is not None and red_cfg.num > 0:
+        m = re.search(r"layers\.(\d+)\.", prefix)
+        layer_no = int(m.group(1)) if m else -1
+        red_ids = red_cfg.ids(layer_no)
+    expert_ids = list(range(e0, e1)) + red_ids
     raw = getattr(src, "base", src)  # the fp8 payload lives under a de-quantising view
-    if getattr(model, "fp8_compute", False) and i0 % 128 == 0 and (i1 - i0) % 128 == 0 and mc.act == "silu":
-        # keep the experts in e4m3 with their block scales: grouped fp8 GEMMs, half the weight bytes
-        from ..models import quant
-        from ..ops import fp8
+    use_fp8 = getattr(model, "fp8_compute", False) and i0 % 128 == 0 and (i1 - i0) % 128 == 0 and mc.act == "silu"
 
-        w13, w2 = [], []
-        for e in range(e0, e1):
-            q = prefix + f"{experts_name}.{e}."
+    def read_expert(e: int):
+        """(w13, w2) of one expert as they are stacked: host tensors (bf16) or one-expert Fp8Weight objects."""
+        q = prefix + f"{experts_name}.{e}."
+        if use_fp8:
+            from ..models import quant
+            from ..ops import fp8
+
             g = quant.load_fp8_weight(raw, q + "gate_proj.weight", 0, i0, i1)
             u = quant.load_fp8_weight(raw, q + "up_proj.weight", 0, i0, i1)
-            w13.append(fp8.interleave_gate_up_fp8(g, u))
-            w2.append(quant.load_fp8_weight(raw, q + "down_proj.weight", 1, i0, i1))
-        lw.w13 = fp8.Fp8Experts(fp8.stack_experts(w13), e1 - e0).to(model.device)
-        lw.w2 = fp8.Fp8Experts(fp8.stack_experts(w2), e1 - e0).to(model.device)
-        w13 = w2 = None
-    else:
-        w13, w2 = [], []
-    for e in range(e0, e1) if w13 is not None else ():
-        q = prefix + f"{experts_name}.{e}."
+            return fp8.interleave_gate_up_fp8(g, u), quant.load_fp8_weight(raw, q + "down_proj.weight", 1, i0, i1)
         g = src.get(q + "gate_proj.weight", 0, i0, i1)
         u = src.get(q + "up_proj.weight", 0, i0, i1)
-        w13.append(ref.interleave_gate_up(g, u))
-        w2.append(src.get(q + "down_proj.weight", 1, i0, i1))
-    if w13 is not None:
-        lw.w13 = dev(torch.stack(w13))
-        lw.w2 = dev(torch.stack(w2))
+        return ref.interleave_gate_up(g, u), src.get(q + "down_proj.weight", 1, i0, i1)
+
+    mats = [read_expert(e) for e in expert_ids]
+    if use_fp8:
+        # keep the experts in e4m3 with their block scales: grouped fp8 GEMMs, half the weight bytes
+        from ..ops import fp8
+
+        lw.w13 = fp8.Fp8Experts(fp8.stack_experts([m[0] for m in mats]), len(mats)).to(model.device)
+        lw.w2 = fp8.Fp8Experts(fp8.stack_experts([m[1] for m in mats]), len(mats)).to(model.device)
+    else:
+        lw.w13 = dev(torch.stack([m[0] for m in mats]))
+        lw.w2 = dev(torch.stack([m[1] for m in mats]))
+    del mats
     lw.e0 = e0 if (ep and tp > 1) else 0
     lw.ep_world = tp if ep else 1
     lw.is_moe = True
+    lw.ep_table = None
+    if red_ids:
+        from ..engine.redundancy import physical_table
+
+        R = len(red_ids)
+        lw.e0 = r * (e1 - e0 + R)                     # first PHYSICAL id of this rank
+        lw.ep_table = physical_table(mc.num_experts, tp, r, red_ids).to(model.device)
+        lw.ep_counter = torch.zeros(mc.num_experts, dtype=torch.int32, device=model.device)
+        lw.ep_red_num, lw.ep_red_ids, lw.ep_layer = R, list(red_ids), layer_no
+        lw.ep_read_expert = read_expert               # the manager re-reads experts from the checkpoint later
     if mc.n_shared:
         model._load_dense_ffn(lw, src, prefix + mc.shared_name + ".", mc.shared_inter)
         if mc.shared_gate:
@@ -136,6 +157,8 @@ def moe_ffn(model, lw, h, mc: MoEConfig):
         if mc.shared_gate:  # every rank scales its partial sum by the same (replicated) gate
             out.mul_(torch.sigmoid(torch.nn.functional.linear(h.float(), lw.shared_gate_w.float())).to(out.dtype))
         accumulate = True
+    if getattr(lw, "ep_table", None) is not None:      # redundant experts: physical ids + hit counters
+        ids = moe_ops.count_remap(ids, lw.ep_table, lw.ep_counter)
     epg = ep_group_of(model, mc)
     if epg is not None:
         epg.moe(h, ids, w, lambda hr, ir, wr, o: moe_ops.fused_experts(hr, lw.w13, lw.w2, ir, wr, mc.act, lw.e0, out=o),
@@ -153,5 +176,7 @@ def ep_group_of(model, mc: MoEConfig):
     if g is None:
         from ..parallel.ep import EPGroup
 
-        g = model._ep_group = EPGroup(model.ps, model.hidden, mc.top_k, mc.num_experts, model.batch_max_tokens)
+        red = getattr(model, "redundancy_cfg", None)
+        n_phys = mc.num_experts + model.ps.world_size * (red.num if red is not None else 0)
+        g = model._ep_group = EPGroup(model.ps, model.hidden, mc.top_k, n_phys, model.batch_max_tokens)
     return g

@@ -138,6 +138,26 @@ def moe_align(ids, E_local: int, e0: int = 0) -> MoeLayout:
     return lay
 
 
+def count_remap(ids, table, counter=None):
+    """ids [T, k] int32 (router's expert ids) -> table[ids] (ids outside the table become -1); counter[e] += number of
+    times e was chosen.  One launch; CPU: torch ops."""
+    if not ids.is_cuda:
+        flat = ids.reshape(-1).long()
+        ok = (flat >= 0) & (flat < table.numel())
+        if counter is not None:
+            counter += torch.bincount(flat[ok], minlength=counter.numel()).to(counter.dtype)
+        out = torch.full_like(flat, -1, dtype=torch.int32)
+        out[ok] = table[flat[ok]]
+        return out.view_as(ids)
+    assert ids.dtype == torch.int32 and table.dtype == torch.int32 and ids.is_contiguous()
+    out = torch.empty_like(ids)
+    check(kernels().llb_moe_count_remap(ptr(ids), c_int(ids.numel()), ptr(table), c_int(table.numel()),
+                                        ptr(counter) if counter is not None else None, ptr(out), stream()),
+          "moe_count_remap")
+    _count()
+    return out
+
+
 def gemm_grouped(a_sorted, w_stacked, mblock_expert, n_per_expert: int, epi: str = "store", out=None, bn: int = 0):
     """a_sorted [M_pad, K] bf16, w_stacked [E, N, K] bf16 -> [M_pad, N] (or [M_pad, N/2] gated)."""
     from . import EPI_CODES

@@ -86,7 +86,9 @@ def _build_model_and_backend(args: StartArgs, ps):
                       state_snapshot_slots=_state_slots(args),
                       linear_att_ssm_data_type=getattr(args, "linear_att_ssm_data_type", "float32"),
                       kv_quant_calibration_config_path=getattr(args, "kv_quant_calibration_config_path", None),
-                      tpsp_mix_mode=bool(getattr(args, "enable_tpsp_mix_mode", False)))
+                      tpsp_mix_mode=bool(getattr(args, "enable_tpsp_mix_mode", False)),
+                      ep_redundancy_expert_config_path=getattr(args, "ep_redundancy_expert_config_path", None),
+                      auto_update_redundancy_expert=bool(getattr(args, "auto_update_redundancy_expert", False)))
     if fused is not None:   # prompt passes as two micro-batches with copy-engine reductions
         from ...parallel import ce as _ce
 

@@ -55,3 +55,19 @@ def test_fused_experts(dev, T, E, k, H, I, e0, El):
     acc = base.clone()
     moe.fused_experts(x, w13, w2, ids, w, "silu", e0, out=acc, accumulate=True)
     assert (acc.float() - (base.float() + want.float())).abs().max().item() < 6e-2
+
+
+@pytest.mark.parametrize("T,k,E", [(1, 8, 128), (300, 8, 256), (5000, 4, 64)])
+def test_count_remap_matches_cpu(dev, T, k, E):
+    """Physical-id rewrite + hit counters of the redundant-expert path: the kernel against the torch restatement."""
+    from lightllm_b200.engine.redundancy import physical_table
+
+    g = torch.Generator().manual_seed(T)
+    ids = torch.randint(-1, E, (T, k), generator=g, dtype=torch.int32)
+    table = physical_table(E, 8, 3, [0, 1, E - 1, E // 2])
+    cnt_ref = torch.zeros(E, dtype=torch.int32)
+    want = moe.count_remap(ids, table, cnt_ref)
+    cnt = torch.zeros(E, dtype=torch.int32, device=dev)
+    got = moe.count_remap(ids.to(dev), table.to(dev), cnt)
+    assert torch.equal(got.cpu(), want) and torch.equal(cnt.cpu(), cnt_ref)
+    assert torch.equal(moe.count_remap(ids.to(dev), table.to(dev), None).cpu(), want)
