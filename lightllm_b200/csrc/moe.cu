@@ -331,6 +331,32 @@ __global__ void moe_count_remap_kernel(const int* __restrict__ ids, int n_pairs,
   }
 }
 
+// Routed-expert capture: buf[slot[t], layer, :] = ids[t, :] as 8- or 16-bit integers (buf is [slots, layers, k]).
+template <typename OUT>
+__global__ void route_capture_kernel(const int* __restrict__ ids, const int* __restrict__ slot, int n_pairs, int k,
+                                     OUT* __restrict__ buf, int n_slots, int n_layers, int layer) {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_pairs; i += gridDim.x * blockDim.x) {
+    int t = i / k, j = i - t * k;
+    int s = slot[t];
+    if (s < 0 || s >= n_slots) continue;
+    buf[((int64_t)s * n_layers + layer) * k + j] = (OUT)ids[i];
+  }
+}
+
+LLB_EXPORT int llb_route_capture(const int* ids, const int* slot, int T, int k, void* buf, int n_slots, int n_layers,
+                                 int layer, int elem_bytes, cudaStream_t st) {
+  if (T <= 0) return LLB_OK;
+  if (elem_bytes != 1 && elem_bytes != 2) return LLB_ERR_UNSUPPORTED;
+  int n = T * k, blocks = cdiv(n, 256);
+  if (blocks > 296) blocks = 296;
+  if (elem_bytes == 1)
+    route_capture_kernel<uint8_t><<<blocks, 256, 0, st>>>(ids, slot, n, k, (uint8_t*)buf, n_slots, n_layers, layer);
+  else
+    route_capture_kernel<int16_t><<<blocks, 256, 0, st>>>(ids, slot, n, k, (int16_t*)buf, n_slots, n_layers, layer);
+  LLB_LAUNCH_CHECK();
+  return LLB_OK;
+}
+
 LLB_EXPORT int llb_moe_count_remap(const int* ids, int n_pairs, const int* table, int E, int* counter, int* out,
                                    cudaStream_t st) {
   if (n_pairs <= 0) return LLB_OK;

@@ -509,6 +509,21 @@ class ModelBackend:
         self.stats["d2h_bytes"] += B * 12
         self._post(reqs, ids_h.numpy(), lps_h.numpy(), has_out)
 
+    def _dump_routed_experts(self, r: InferReq):
+        """Copies the routed expert ids of the request's tokens (all but the last produced one, which never went
+        through the model) into the request's shared array.  Reference:
+        lightllm/server/router/model_infer/infer_req_ext.py:177-192."""
+        sr = r.shm_req
+        out = getattr(sr, "shm_routed", None)
+        if out is None:
+            return
+        n = min(r.cur_kv_len, sr.input_len + r.cur_output_len - 1, out.arr.shape[0])
+        if n <= 0:
+            return
+        slots = self.model.req_manager.req_to_token_indexs[r.req_idx, :n]
+        out.arr[:n] = self.model.route_capture.extract(slots)
+        sr.routed_len = n
+
     def _post(self, reqs: List[InferReq], ids_np, lps_np, has_out):
         """Host-side bookkeeping of sampled tokens: append, finish checks, publishing to the shared request."""
         now = time.time()
@@ -525,6 +540,8 @@ class ModelBackend:
             if self.is_master_in_dp and not r.retire_hold:
                 if r.cur_output_len == 1:
                     r.shm_req.first_token_time = now
+                if r.finish_status.is_finished() and self.model.route_capture is not None:
+                    self._dump_routed_experts(r)      # before the finish state becomes visible
                 r.publish()
             if self.on_token is not None:
                 self.on_token(r, tok, float(lps_np[i]))

@@ -88,6 +88,9 @@ class LLM:
         self._next_id += 8
         r.init(rid, ids, params, None, chunked_prefill_size=self.args.chunked_prefill_size,
                router_max_wait_tokens=self.args.router_max_wait_tokens, max_total_len=self.args.max_req_total_len)
+        rc = self.model.route_capture
+        if rc is not None:
+            r.create_routed_shm_array(rc.num_layers, rc.top_k, rc.np_dtype)
         return r
 
     def warmup(self, batch_sizes: Optional[List[int]] = None):
@@ -206,6 +209,8 @@ class LLM:
                  "latency_s": finish_time.get(r.request_id, time.time()) - t_arrive}
             if return_stats:
                 o["token_times"] = token_times[r.request_id]
+            if getattr(r, "shm_routed", None) is not None:
+                o["routed_experts"] = r.shm_routed.arr[:r.routed_len].copy()
             outs.append(o)
             r.release_shm_arrays()
         if hasattr(self.backend, "drain"):

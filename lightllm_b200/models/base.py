@@ -157,6 +157,11 @@ class TransformerLM:
         else:
             self._init_mem(max_total_token_num, mem_fraction)
             self.req_manager = ReqManager(max_req_num, max_seq_length, self.mem_manager, self.device)
+        self.route_capture = None
+        if extra.get("enable_return_routed_experts") and share_with is None:
+            from ..common.route_capture import RouteCapture
+
+            self.route_capture = RouteCapture(config, self.mem_manager.size + 1, self.device)
         self._graphs: Dict[int, dict] = {}
         self._graph_pool = None
         self.weight_version = "default"

@@ -136,7 +136,7 @@ def load_experts(model, lw, src, prefix: str, mc: MoEConfig, ep: bool, gate_name
         lw.gate_up_w = lw.down_w = None
 
 
-def moe_ffn(model, lw, h, mc: MoEConfig):
+def moe_ffn(model, lw, h, mc: MoEConfig, layer: int = -1, st=None):
     """Returns the per-rank partial sum [T, H] of routed (+ shared) experts, written where the TP reduction
     wants it."""
     T = h.shape[0]
@@ -157,6 +157,9 @@ def moe_ffn(model, lw, h, mc: MoEConfig):
         if mc.shared_gate:  # every rank scales its partial sum by the same (replicated) gate
             out.mul_(torch.sigmoid(torch.nn.functional.linear(h.float(), lw.shared_gate_w.float())).to(out.dtype))
         accumulate = True
+    rc = getattr(model, "route_capture", None)
+    if rc is not None and st is not None:              # --enable_return_routed_experts
+        rc.capture(layer, ids, st.mem_index)
     if getattr(lw, "ep_table", None) is not None:      # redundant experts: physical ids + hit counters
         ids = moe_ops.count_remap(ids, lw.ep_table, lw.ep_counter)
     epg = ep_group_of(model, mc)

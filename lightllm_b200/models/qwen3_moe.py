@@ -36,7 +36,7 @@ class Qwen3MoeLM(TransformerLM):
 
     def _ffn_block(self, i, lw, h, st):
         if lw.is_moe:
-            return "partial", moe.moe_ffn(self, lw, h, self.moe)
+            return "partial", moe.moe_ffn(self, lw, h, self.moe, layer=i, st=st)
         return self._dense_ffn(lw, h)
 
 

@@ -43,7 +43,8 @@ async def lightllm_generate(request: Request, g) -> Response:
     prompt = body.pop("inputs")
     params = dict(body.pop("parameters", {}))
     return_details = params.pop("return_details", False)
-    params.pop("return_routed_experts", None)
+    return_routed = params.pop("return_routed_experts", bool(getattr(g.args, "enable_return_routed_experts", False)))
+    routed = {}
     sp = _make_params(g, params)
     mm = body.get("multimodal_params")
     texts = defaultdict(list)
@@ -57,6 +58,8 @@ async def lightllm_generate(request: Request, g) -> Response:
         texts[sub_id].append(text)
         logprobs[sub_id].append(meta.get("logprob"))
         prompt_tokens = meta.get("prompt_tokens", prompt_tokens)
+        if "routed_experts" in meta:     # travels with the last token only; kept out of the per-token details
+            routed[sub_id] = meta.pop("routed_experts")
         if return_details:
             m = dict(meta)
             m["text"] = text
@@ -71,6 +74,8 @@ async def lightllm_generate(request: Request, g) -> Response:
            "logprobs": logprobs[ids[0]] if len(ids) == 1 else [logprobs[i] for i in ids]}
     if return_details:
         ret["tokens"] = tokens[ids[0]] if len(ids) == 1 else [tokens[i] for i in ids]
+    if return_routed and routed:
+        ret["routed_experts"] = routed.get(ids[0]) if len(ids) == 1 else [routed.get(i) for i in ids]
     return Response(content=json.dumps(ret, ensure_ascii=False).encode("utf-8"), media_type="application/json")
 
 

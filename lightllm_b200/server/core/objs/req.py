@@ -183,6 +183,7 @@ class Req(ctypes.Structure):
         ("stop_str_matched_token_index", ctypes.c_int),
         ("dp_index", ctypes.c_int),
         ("first_token_time", ctypes.c_double),
+        ("routed_len", ctypes.c_int),          # tokens whose routed experts the rank wrote to the "routed" array
     ]
 
     # ---- life cycle ----
@@ -214,6 +215,7 @@ class Req(ctypes.Structure):
         self.stop_str_matched_token_index = -1
         self.dp_index = -1
         self.first_token_time = 0.0
+        self.routed_len = 0
         self.out_tokens_queue.reset()
         if isinstance(sample_param, SamplingParams):
             ctypes.memmove(ctypes.byref(self.sample_params), ctypes.byref(sample_param), ctypes.sizeof(SamplingParams))
@@ -252,6 +254,17 @@ class Req(ctypes.Structure):
     def create_logprobs_shm_array(self):
         self.shm_logprobs = ShmArray(self._name("logprobs"), (self.alloc_shm_numpy_len,), np.float32).create_shm()
 
+    def create_routed_shm_array(self, num_moe_layers: int, top_k: int, dtype):
+        """Per-token routed expert ids [tokens, MoE layers, top_k], written by the model rank when the request
+        finishes (`--enable_return_routed_experts`)."""
+        self.shm_routed = ShmArray(self._name("routed"), (self.alloc_shm_numpy_len, num_moe_layers, top_k),
+                                   dtype).create_shm()
+
+    def link_routed_shm_array(self, shm_prefix: str, num_moe_layers: int, top_k: int, dtype):
+        self._shm_prefix = shm_prefix
+        self.shm_routed = ShmArray(self._name("routed"), (self.alloc_shm_numpy_len, num_moe_layers, top_k),
+                                   dtype).link_shm()
+
     def link_prompt_ids_shm_array(self, shm_prefix: str):
         self._shm_prefix = shm_prefix
         self.shm_prompt_ids = ShmArray(self._name("prompts"), (self.alloc_shm_numpy_len,), np.int64).link_shm()
@@ -261,7 +274,7 @@ class Req(ctypes.Structure):
         self.shm_logprobs = ShmArray(self._name("logprobs"), (self.alloc_shm_numpy_len,), np.float32).link_shm()
 
     def release_shm_arrays(self, unlink: bool = False):
-        for a in ("shm_prompt_ids", "shm_logprobs"):
+        for a in ("shm_prompt_ids", "shm_logprobs", "shm_routed"):
             arr = getattr(self, a, None)
             if arr is not None:
                 arr.close_shm(unlink=unlink or None)

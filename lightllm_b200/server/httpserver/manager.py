@@ -78,6 +78,15 @@ class HttpServerManager:
         self.run_reqs_count_mark = SharedInt(f"{self.name}_run_reqs_count_mark")
         self.metric_client = metric_client
         self.paused = False  # RL: admission gate
+        self.routed_shape = None  # (MoE layers, top_k, dtype) with --enable_return_routed_experts
+        if getattr(args, "enable_return_routed_experts", False):
+            from ...common import route_capture as rc
+            from ...models.base import load_config
+
+            cfg = getattr(args, "_config_override", None) or load_config(args.model_dir)
+            if not rc.moe_layer_map(cfg):
+                raise ValueError("--enable_return_routed_experts needs a mixture-of-experts model")
+            self.routed_shape = (len(rc.moe_layer_map(cfg)), rc.top_k_of(cfg), rc.np_dtype_of(cfg))
         self.relay_master = None  # httpserver/multinode_relay.py on node 0 of a multi-node tensor-parallel deployment
         self.master_id_to_local: Dict[int, int] = {}  # PD nodes: pd_master request id -> local group id
         self.eos_ids = set(args.eos_ids or [])
@@ -222,6 +231,8 @@ class HttpServerManager:
                        router_max_wait_tokens=self.args.router_max_wait_tokens, mtp_step=self.args.mtp_step,
                        shm_prefix=self.name, max_total_len=self.max_req_total_len)
                 r.group_req_id = group_req_id
+                if self.routed_shape is not None:
+                    r.create_routed_shm_array(*self.routed_shape)
                 if self.args.enable_prompt_logprobs is False:
                     r.sample_params.prompt_logprobs = -1
                 req_objs.append(r)
@@ -351,6 +362,10 @@ class HttpServerManager:
                                 continue
                             if fs.is_finished():
                                 st.finished.add(r.request_id)
+                                if getattr(r, "shm_routed", None) is not None and r.routed_len > 0:
+                                    from ...common.route_capture import encode
+
+                                    metadata["routed_experts"] = encode(r.shm_routed.arr[:r.routed_len].copy())
                             pulled.append((r.request_id, text, metadata, fs))
                     if pulled:
                         async with st.lock:

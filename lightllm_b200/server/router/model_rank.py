@@ -88,7 +88,8 @@ def _build_model_and_backend(args: StartArgs, ps):
                       kv_quant_calibration_config_path=getattr(args, "kv_quant_calibration_config_path", None),
                       tpsp_mix_mode=bool(getattr(args, "enable_tpsp_mix_mode", False)),
                       ep_redundancy_expert_config_path=getattr(args, "ep_redundancy_expert_config_path", None),
-                      auto_update_redundancy_expert=bool(getattr(args, "auto_update_redundancy_expert", False)))
+                      auto_update_redundancy_expert=bool(getattr(args, "auto_update_redundancy_expert", False)),
+                      enable_return_routed_experts=bool(getattr(args, "enable_return_routed_experts", False)))
     if fused is not None:   # prompt passes as two micro-batches with copy-engine reductions
         from ...parallel import ce as _ce
 
@@ -184,6 +185,9 @@ class ModelRankLoop:
                 r = self.shm_req_manager.get_req_obj_by_index(shm_index)
                 r.link_prompt_ids_shm_array(self.args.unique_server_name)
                 r.link_logprobs_shm_array(self.args.unique_server_name)
+                rc = self.model.route_capture
+                if rc is not None:
+                    r.link_routed_shm_array(self.args.unique_server_name, rc.num_layers, rc.top_k, rc.np_dtype)
                 r._mm_params = mm_params
                 mine.append(r)
             if mine:

@@ -71,3 +71,22 @@ def test_count_remap_matches_cpu(dev, T, k, E):
     got = moe.count_remap(ids.to(dev), table.to(dev), cnt)
     assert torch.equal(got.cpu(), want) and torch.equal(cnt.cpu(), cnt_ref)
     assert torch.equal(moe.count_remap(ids.to(dev), table.to(dev), None).cpu(), want)
+
+
+@pytest.mark.parametrize("E,T,k", [(128, 300, 8), (384, 77, 6)])
+def test_route_capture_scatter_matches_cpu(dev, E, T, k):
+    """Routed-expert capture: the scatter kernel (8- and 16-bit ids) against the torch indexing restatement."""
+    from lightllm_b200.common.route_capture import RouteCapture
+
+    cfg = dict(num_hidden_layers=4, num_experts=E, num_experts_per_tok=k, decoder_sparse_step=1, mlp_only_layers=[1])
+    g = torch.Generator().manual_seed(E)
+    ids = torch.randint(0, E, (T, k), generator=g, dtype=torch.int32)
+    slots = torch.randperm(1000, generator=g)[:T].to(torch.int32)
+    a, b = RouteCapture(cfg, 1000, "cpu"), RouteCapture(cfg, 1000, dev)
+    for layer in (0, 2, 3, 1):           # layer 1 is dense: ignored
+        a.capture(layer, ids + 0, slots)
+        b.capture(layer, ids.to(dev), slots.to(dev))
+        ids = (ids + 1) % E
+    assert torch.equal(b.buf.cpu(), a.buf)
+    pick = slots[:10]
+    assert (b.extract(pick) == a.extract(pick)).all()
