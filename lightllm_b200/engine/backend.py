@@ -153,6 +153,18 @@ class ModelBackend:
             out.append(req)
         return out
 
+    def fetch_prefixes(self, new_reqs) -> int:
+        """Data-parallel serving: pulls the part of each new prompt that another replica has cached and this one has
+        not (`engine/dp_prefix_fetch.py`).  `new_reqs` = (owner replica, prompt ids) of every new request, the same
+        list on every rank; collective."""
+        if getattr(self, "_prefix_fetch", None) is None:
+            from .dp_prefix_fetch import DPPrefixFetch
+
+            self._prefix_fetch = DPPrefixFetch(self)
+        n = self._prefix_fetch.run(new_reqs)
+        self.stats["dp_fetched_tokens"] = self.stats.get("dp_fetched_tokens", 0) + n
+        return n
+
     def abort(self, req_id: int):
         req = self.ctx.requests.get(req_id)
         if req is not None:

@@ -166,6 +166,8 @@ class ModelRankLoop:
         self.running = True
         self.profiler = None
         self.dp_index = ps.dp_rank
+        self.prefix_fetch = bool(getattr(args, "enable_dp_prompt_cache_fetch", False)) and ps.dp_size > 1 and \
+            args.nnodes == 1 and backend.radix_cache is not None
 
     def _agree_generation(self) -> int:
         g = self.mailbox.generation()
@@ -179,6 +181,8 @@ class ModelRankLoop:
         b = self.backend
         if isinstance(cmd, NewReqsCmd):
             mine = []
+            if self.prefix_fetch:     # copy prefixes another replica has cached before the requests are admitted
+                b.fetch_prefixes([(dp_index, self._peek_prompt(shm_index)) for _, shm_index, _, dp_index in cmd.reqs])
             for req_id, shm_index, mm_params, dp_index in cmd.reqs:
                 if self.ps.dp_size > 1 and dp_index != self.dp_index:
                     continue
@@ -207,6 +211,18 @@ class ModelRankLoop:
             handle_rl_cmd(self, cmd)
         elif isinstance(cmd, ExitCmd):
             self.running = False
+
+    def _peek_prompt(self, shm_index: int):
+        """Prompt token ids of a request that may belong to another replica (read through a short-lived link)."""
+        r = self.shm_req_manager.get_req_obj_by_index(shm_index)
+        try:
+            r.link_prompt_ids_shm_array(self.args.unique_server_name)
+            ids = r.shm_prompt_ids.arr[: r.input_len].copy()
+            r.shm_prompt_ids.close_shm(unlink=None)
+            r.shm_prompt_ids = None
+            return ids
+        finally:
+            self.shm_req_manager.put_back_req_obj(r)
 
     def _profiler_cmd(self, what: str):
         from ...utils.profiler import ProcessProfiler
