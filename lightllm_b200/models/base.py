@@ -471,16 +471,41 @@ class TransformerLM:
         return last
 
     def _prefill(self, mi: ModelInput) -> ModelOutput:
-        halves = self._split_for_pipeline(mi)
+        balance_on = self._dp_balance_on()      # a static property: every replica takes the same path
+        halves = None if balance_on else self._split_for_pipeline(mi)
         if halves is not None:
             return self._prefill_pipelined(mi, halves)
         st, input_ids = self._build_prefill_state(mi)
         h = self._embed(input_ids, st)
+        bal = self._prepare_dp_balance(st) if balance_on else None
+        if bal is not None:       # token-wise work on an even split of all replicas' tokens
+            h = bal.to_balanced(h)
         h = self._layers_forward(h, st)
+        if bal is not None:
+            h = bal.to_origin(h)
         hidden = h if mi.return_hidden else None
         last = self._last_rows(h, st, mi.return_all_logits)
         logits = self._lm_head(last, normed=True) if st.extra.get("normed") else self._lm_head(last)
         return ModelOutput(logits=logits, hidden=hidden)
+
+    def _dp_balance_on(self) -> bool:
+        """`--enable_dp_prefill_balance` applies to this model: data parallel, a plain decoder stack (families that
+        edit the stream between layers keep their own token layout) and no draft modules riding on the passes."""
+        if not self.extra.get("enable_dp_prefill_balance") or self.ps.dp_size <= 1 or self.extra_kv_layers or \
+                self.share_with is not None:
+            return False
+        cls, base = type(self), TransformerLM
+        return cls._after_layer is base._after_layer and cls._layers_forward is base._layers_forward
+
+    def _prepare_dp_balance(self, st: InferState):
+        """The token exchange of this prompt pass (common/dp_balance.py), or None when the replicas are balanced
+        already.  Collective: every replica runs a prompt pass on the same step (the data-parallel backend's
+        lock-step)."""
+        from ..common.dp_balance import DPBalance
+
+        bal = DPBalance.prepare(self.ps, st.num_tokens)
+        st.extra["balance"] = bal
+        return bal
 
     # ---- prompt passes as two micro-batches whose reductions run under each other's GEMMs ----
     PIPELINE_MIN_TOKENS = 2048   # below this the pass is latency-bound and the fused kernels are faster
@@ -759,8 +784,12 @@ class TransformerLM:
         h = ops.rmsnorm(residual, self.layers[0].in_norm, self.eps, self.norm_w_offset)
         n = self.num_layers
         self._tpsp_now = self._tpsp_active(x.shape[0], st)
+        bal = st.extra.get("balance")   # data-parallel token balance: attention on the owners, the rest balanced
         for i, lw in enumerate(self.layers):
-            a = self._attention_block(i, lw, h, st)                      # [T, hq*D] (pre o_proj)
+            if bal is None:
+                a = self._attention_block(i, lw, h, st)                  # [T, hq*D] (pre o_proj)
+            else:
+                a = bal.to_balanced(self._attention_block(i, lw, bal.to_origin(h), st))
             h = self._row_parallel(a, lw.o_w, lw.o_b, residual, lw.post_norm)
             nxt = self.layers[i + 1].in_norm if i + 1 < n else (self.final_norm_w if self._tpsp_now else None)
             f = self._ffn_block(i, lw, h, st)

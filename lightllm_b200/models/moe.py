@@ -158,7 +158,7 @@ def moe_ffn(model, lw, h, mc: MoEConfig, layer: int = -1, st=None):
             out.mul_(torch.sigmoid(torch.nn.functional.linear(h.float(), lw.shared_gate_w.float())).to(out.dtype))
         accumulate = True
     rc = getattr(model, "route_capture", None)
-    if rc is not None and st is not None:              # --enable_return_routed_experts
+    if rc is not None and st is not None and st.extra.get("balance") is None:   # --enable_return_routed_experts
         rc.capture(layer, ids, st.mem_index)
     if getattr(lw, "ep_table", None) is not None:      # redundant experts: physical ids + hit counters
         ids = moe_ops.count_remap(ids, lw.ep_table, lw.ep_counter)

@@ -89,7 +89,8 @@ def _build_model_and_backend(args: StartArgs, ps):
                       tpsp_mix_mode=bool(getattr(args, "enable_tpsp_mix_mode", False)),
                       ep_redundancy_expert_config_path=getattr(args, "ep_redundancy_expert_config_path", None),
                       auto_update_redundancy_expert=bool(getattr(args, "auto_update_redundancy_expert", False)),
-                      enable_return_routed_experts=bool(getattr(args, "enable_return_routed_experts", False)))
+                      enable_return_routed_experts=bool(getattr(args, "enable_return_routed_experts", False)),
+                      enable_dp_prefill_balance=bool(getattr(args, "enable_dp_prefill_balance", False)))
     if fused is not None:   # prompt passes as two micro-batches with copy-engine reductions
         from ...parallel import ce as _ce
 
