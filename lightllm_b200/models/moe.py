@@ -6,7 +6,8 @@ interleaved in 32-row blocks, so the grouped GEMM's epilogue applies the gated a
 
   * tensor parallel (default): every rank holds all experts, each sliced along the intermediate
     dimension (I_local = I / tp)
-  * expert parallel (`enable_ep_moe`): every rank holds E / tp whole experts.  With tensor-parallel
+  * expert parallel (`enable_ep_moe`): every rank holds E / tp whole experts (E / world under `--dp`; a replica
+    may itself be tensor parallel, its ranks then share the replica's tokens out between them for the exchange).  With tensor-parallel
     attention the hidden states are replicated, so a rank simply evaluates its own experts for all
     tokens (pairs routed elsewhere are dropped by the alignment kernel) -- no all-to-all needed.
 
@@ -67,7 +68,6 @@ def load_experts(model, lw, src, prefix: str, mc: MoEConfig, ep: bool, gate_name
     """Fills lw.router_w (fp32 logits GEMM runs in bf16 weights), lw.w13, lw.w2, lw.e0, lw.e_local (+ shared expert)."""
     tp, r = model.tp.size, model.tp.rank
     if ep and model.ps.dp_size > 1:  # data-parallel attention: the experts are spread over every rank of the world
-        assert model.ps.tp_size == 1, "expert parallelism under --dp needs --dp equal to the world size"
         tp, r = model.ps.world_size, model.ps.global_rank
     dev = model._dev
     lw.router_w = dev(src.get(prefix + f"{gate_name}.weight"))
@@ -164,8 +164,20 @@ def moe_ffn(model, lw, h, mc: MoEConfig, layer: int = -1, st=None):
         ids = moe_ops.count_remap(ids, lw.ep_table, lw.ep_counter)
     epg = ep_group_of(model, mc)
     if epg is not None:
-        epg.moe(h, ids, w, lambda hr, ir, wr, o: moe_ops.fused_experts(hr, lw.w13, lw.w2, ir, wr, mc.act, lw.e0, out=o),
-                out=out, accumulate=accumulate, tokens_bound=int(getattr(model, "_ep_tokens_bound", 0) or 0))
+        fn = lambda hr, ir, wr, o: moe_ops.fused_experts(hr, lw.w13, lw.w2, ir, wr, mc.act, lw.e0, out=o)  # noqa: E731
+        bound = int(getattr(model, "_ep_tokens_bound", 0) or 0)
+        tp, t = model.ps.tp_size, model.ps.tp_rank
+        if tp == 1:
+            epg.moe(h, ids, w, fn, out=out, accumulate=accumulate, tokens_bound=bound)
+            return out
+        # tensor parallelism inside the replica: its ranks hold the same tokens, so each sends only its share of
+        # them through the exchange and leaves the other rows of the partial sum to the other ranks; the replica's
+        # reduction that follows adds the shares up
+        per = -(-T // tp)
+        lo, hi = min(t * per, T), min((t + 1) * per, T)
+        if not accumulate:
+            out.zero_()
+        epg.moe(h[lo:hi], ids[lo:hi], w[lo:hi], fn, out=out[lo:hi], accumulate=True, tokens_bound=bound)
         return out
     moe_ops.fused_experts(h, lw.w13, lw.w2, ids, w, mc.act, lw.e0, out=out, accumulate=accumulate)
     return out

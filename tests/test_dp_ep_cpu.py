@@ -59,3 +59,33 @@ def test_dp2_ep2_matches_single(tmp_path, name):
     assert r0["tokens"] == one["tokens"][:4]
     assert r1["tokens"] == one["tokens"][4:]
     assert r1["stats"]["hold_prefill"] + r1["stats"]["hold_decode"] > 0   # the short rank kept stepping for the other
+
+
+def _worker_tp_in_replica(rank, world, dp, port, out_dir):
+    from lightllm_b200.engine.llm import LLM
+    from lightllm_b200.parallel import dist as pdist
+
+    torch.set_num_threads(1)
+    ps = pdist.init_distributed(world, rank, dp=dp, host="127.0.0.1", port=port, backend="gloo",
+                                device=torch.device("cpu"))
+    llm = LLM(config=CFG, data_type="float32", max_total_token_num=4096, running_max_req_size=8, max_req_total_len=128,
+              batch_max_tokens=64, random_seed=0, enable_ep_moe=True)
+    prompts = _prompts()
+    mine = prompts[:4] if ps.dp_rank == 0 else prompts[4:]
+    outs = llm.generate(mine, {"max_new_tokens": 12, "ignore_eos": True})
+    lw = llm.model.layers[0]
+    torch.save({"tokens": [o["token_ids"] for o in outs], "experts": tuple(lw.w13.shape), "e0": lw.e0},
+               os.path.join(out_dir, f"tpdp_r{rank}.pt"))
+    pdist.destroy()
+
+
+@pytest.mark.timeout(900)
+def test_dp2_with_tp2_replicas_and_ep4_matches_single(tmp_path):
+    """4 ranks: 2 replicas of 2 tensor-parallel ranks each, the 8 experts spread over all 4 ranks."""
+    mp.spawn(_worker, args=(1, 1, _free_port(), str(tmp_path), CFG), nprocs=1, join=True)
+    mp.spawn(_worker_tp_in_replica, args=(4, 2, _free_port(), str(tmp_path)), nprocs=4, join=True)
+    one = torch.load(tmp_path / "w1_r0.pt")
+    rs = [torch.load(tmp_path / f"tpdp_r{r}.pt") for r in range(4)]
+    assert rs[0]["tokens"] == one["tokens"][:4]       # a replica's first rank publishes its tokens
+    assert rs[2]["tokens"] == one["tokens"][4:]
+    assert [r["experts"][0] for r in rs] == [2, 2, 2, 2] and [r["e0"] for r in rs] == [0, 2, 4, 6]
