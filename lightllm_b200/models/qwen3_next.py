@@ -235,7 +235,12 @@ class Qwen3NextLM(Qwen3MoeLM):
             kk = m[:, kd:2 * kd].view(-1, self.nk, self.dk).repeat_interleave(self.vrep, dim=1)
             return qq, kk, m[:, 2 * kd:].view(-1, self.nv, self.dv)
 
-        if not st.is_prefill:  # one token per request, all requests at once
+        if not st.is_prefill and h.is_cuda and la.step_kernel_supported(self.dk, self.dv, self.conv_k):
+            # one token per request: convolution step + state update / read-out, two kernels
+            core = la.conv_and_delta_step(mixed.contiguous(), conv_state, lw.conv_w, ssm_state,
+                                          st.b_req_idx.to(torch.int32), g.float(), beta, self.nk, self.nv, self.dk,
+                                          self.dv)
+        elif not st.is_prefill:  # one token per request, all requests at once (torch restatement)
             req = st.b_req_idx.long()
             y, new_conv = la.causal_conv_step(mixed, conv_state[req], lw.conv_w)
             conv_state.index_copy_(0, req, new_conv.to(conv_state.dtype))

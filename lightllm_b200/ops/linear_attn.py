@@ -104,6 +104,43 @@ def gated_delta_chunked(q, k, v, g, beta, S0=None, chunk: int = 64):
     return out.transpose(0, 1), S
 
 
+def conv_and_delta_step(mixed, conv_state, conv_w_f32, ssm_state, req, g, beta, nk: int, nv: int, dk: int, dv: int):
+    """The decode step of one Gated DeltaNet layer for a batch, two kernels (csrc/linear_attn.cu): convolution step
+    over the q / k / v channels, then per (request, value head) the normalisation of q and k, the state update and the
+    read-out, with the state row strips held in registers (one read and one write of the state).  Updates
+    `conv_state [slots, C, K-1]` and `ssm_state [slots, nv, dk, dv]` (fp32 or bf16) in place at rows `req`.
+
+    mixed [B, C] fp32, conv_w_f32 [C, K] fp32, req [B] int32, g / beta [B, nv] fp32 -> core [B, nv, dv] fp32."""
+    import ctypes
+
+    from . import _count
+    from ._native import check, kernels, ptr, stream
+
+    B, C = mixed.shape
+    K = conv_w_f32.shape[1]
+    assert mixed.dtype == torch.float32 and mixed.is_contiguous() and C == 2 * nk * dk + nv * dv
+    assert conv_state.is_contiguous() and ssm_state.is_contiguous() and req.dtype == torch.int32
+    assert conv_state.dtype in (torch.float32, torch.bfloat16) and ssm_state.dtype in (torch.float32, torch.bfloat16)
+    g, beta = g.contiguous(), beta.contiguous()
+    y = torch.empty_like(mixed)
+    ci = ctypes.c_int
+    check(kernels().llb_gdn_conv_step(ptr(mixed), ptr(conv_state), ci(int(conv_state.dtype == torch.bfloat16)),
+                                      ptr(conv_w_f32), ptr(req), ptr(y), ci(B), ci(C), ci(K), stream()),
+          "gdn_conv_step")
+    core = torch.empty((B, nv, dv), dtype=torch.float32, device=mixed.device)
+    check(kernels().llb_gdn_recurrent_step(ptr(y), ptr(g), ptr(beta), ptr(ssm_state),
+                                           ci(int(ssm_state.dtype == torch.bfloat16)), ptr(req), ptr(core), ci(B),
+                                           ci(nk), ci(nv), ci(dk), ci(dv), stream()), "gdn_recurrent_step")
+    _count(2)
+    return core
+
+
+def step_kernel_supported(dk: int, dv: int, K: int) -> bool:
+    """Shapes the decode-step kernels take: the value head fits a CTA in whole warps (dv a multiple of 32, at most
+    256) and a thread's strip of a state column fits its registers (dk <= 64 x (256 // dv))."""
+    return dv % 32 == 0 and 32 <= dv <= 256 and 1 <= K <= 16 and 1 <= dk <= 64 * (256 // dv)
+
+
 def rmsnorm_gated(x: torch.Tensor, z: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
     """norm(x) * w * silu(z) over the last dimension (the norm sees x alone; z only gates)."""
     xf = x.float()
