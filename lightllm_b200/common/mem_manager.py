@@ -241,6 +241,40 @@ class Fp8KVMemoryManager(MemoryManager):
         return Fp8KVLayer(self.kv_buffer[i], self.head_dim, self.scales[i])
 
 
+class Int4KVMemoryManager(MemoryManager):
+    """GQA/MHA pool with 4-bit rows and one fp16 scale per group of `group_size` values (`ops/kv_quant.py`:
+    Int4KVLayer): a quarter of the bf16 pool's payload plus the scales.  There is no attention kernel over the packed
+    rows: every pass attends over a widened copy of the rows its requests refer to, so this pool trades decode speed
+    for capacity and decode steps run outside CUDA graphs.
+    Reference: lightllm/common/kv_cache_mem_manager/ppl_int4kv_mem_manager.py (`--llm_kv_type int4kv`)."""
+
+    no_cuda_graph = True
+
+    def __init__(self, size: int, dtype: torch.dtype, head_num: int, head_dim: int, layer_num: int,
+                 device: torch.device, always_copy: bool = False, group_size: int = 8):
+        self.compute_dtype = dtype
+        self.group_size = int(group_size or 8)
+        if head_dim % self.group_size or self.group_size % 2:
+            raise ValueError(f"int4 KV cache: group size {self.group_size} must be even and divide the head size")
+        super().__init__(size, torch.uint8, head_num, head_dim, layer_num, device)
+
+    def kv_row_shape(self):
+        from ..ops.kv_quant import Int4KVLayer
+
+        return (2 * self.head_num, Int4KVLayer.row_bytes(self.head_dim, self.group_size))
+
+    @staticmethod
+    def bytes_per_token(dtype, head_num, head_dim, layer_num, group_size: int = 8) -> int:
+        from ..ops.kv_quant import Int4KVLayer
+
+        return layer_num * 2 * head_num * Int4KVLayer.row_bytes(head_dim, group_size)
+
+    def layer(self, i: int):
+        from ..ops.kv_quant import Int4KVLayer
+
+        return Int4KVLayer(self.kv_buffer[i], self.head_dim, self.group_size)
+
+
 class Fp8PerTensorKVMemoryManager(Fp8KVMemoryManager):
     per_tensor = True
 
@@ -298,15 +332,14 @@ class CalibrationKVMemoryManager(MemoryManager):
 
 
 KV_MANAGERS = {"none": MemoryManager, "calibrate": CalibrationKVMemoryManager, "int8kv": Int8KVMemoryManager, "fp8kv_sph": Fp8KVMemoryManager,
-               "fp8kv_spt": Fp8PerTensorKVMemoryManager}
+               "fp8kv_spt": Fp8PerTensorKVMemoryManager, "int4kv": Int4KVMemoryManager}
 
 
 def select_mem_manager_class(kv_type: Optional[str]):
     """Pool class for `--llm_kv_type` (reference: kv_cache_mem_manager/mem_utils.py select_mem_manager_class)."""
     k = (kv_type or "none").lower()
     if k not in KV_MANAGERS:
-        raise ValueError(f"--llm_kv_type {kv_type!r} is not available (have: {sorted(KV_MANAGERS)}); the int4 and "
-                         "calibrated fp8 pools of the reference are not built")
+        raise ValueError(f"--llm_kv_type {kv_type!r} is not available (have: {sorted(KV_MANAGERS)})")
     return KV_MANAGERS[k]
 
 

@@ -157,6 +157,8 @@ class TransformerLM:
         else:
             self._init_mem(max_total_token_num, mem_fraction)
             self.req_manager = ReqManager(max_req_num, max_seq_length, self.mem_manager, self.device)
+        if getattr(self.mem_manager, "no_cuda_graph", False):    # a pool whose attention route syncs with the host
+            self.disable_cudagraph = True
         self.route_capture = None
         if extra.get("enable_return_routed_experts") and share_with is None:
             from ..common.route_capture import RouteCapture
@@ -384,14 +386,23 @@ class TransformerLM:
         return select_mem_manager_class(self.extra.get("kv_type"))
 
     def kv_bytes_per_token(self) -> int:
+        kw = {"group_size": self._kv_group_size()} if self._is_int4_kv() else {}
         return self._kv_manager_class().bytes_per_token(self.dtype, self.hkv, self.head_dim,
-                                                        self.num_layers + self.extra_kv_layers)
+                                                        self.num_layers + self.extra_kv_layers, **kw)
+
+    def _is_int4_kv(self) -> bool:
+        return str(self.extra.get("kv_type") or "").lower() == "int4kv"
+
+    def _kv_group_size(self) -> int:
+        return int(self.extra.get("kv_quant_group_size") or 8)
 
     def _kv_manager_kwargs(self) -> dict:
         kw = {}
         if str(self.extra.get("kv_type") or "").startswith("fp8kv"):
             kw["calibration"] = self.extra.get("kv_quant_calibration_config_path")
             kw["head_range"] = getattr(self, "_kv_range", None)
+        if self._is_int4_kv():
+            kw["group_size"] = self._kv_group_size()
         return kw
 
     def _make_mem_manager(self, size):

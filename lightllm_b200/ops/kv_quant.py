@@ -124,6 +124,59 @@ class Int8KVLayer(QuantKVLayer):
         return (self.data[..., : self.head_dim].float() * self.scales(self.data)).to(dtype)
 
 
+class Int4KVLayer(QuantKVLayer):
+    """One layer of the 4-bit pool: `data` uint8 [slots + 1, 2 * Hkv, D / 2 + 2 * D / group]: two values per byte
+    (low nibble first, stored as value + 8), then one fp16 scale per `group` consecutive values (x = q * scale,
+    scale = max|x| / 7 over the group).  Attention runs on a widened copy of the rows a batch refers to.
+    Reference: lightllm/common/kv_cache_mem_manager/ppl_int4kv_mem_manager.py (`--llm_kv_type int4kv`,
+    `--llm_kv_quant_group_size`)."""
+
+    __slots__ = ("data", "head_dim", "group")
+
+    def __init__(self, data: torch.Tensor, head_dim: int, group: int):
+        assert data.dtype == torch.uint8 and head_dim % group == 0 and group % 2 == 0
+        assert data.shape[-1] == self.row_bytes(head_dim, group)
+        self.data, self.head_dim, self.group = data, head_dim, group
+
+    @staticmethod
+    def row_bytes(head_dim: int, group: int) -> int:
+        return head_dim // 2 + 2 * (head_dim // group)
+
+    @property
+    def device(self):
+        return self.data.device
+
+    @property
+    def is_cuda(self):
+        return self.data.is_cuda
+
+    def _deq(self, rows: torch.Tensor, dtype) -> torch.Tensor:
+        D, g = self.head_dim, self.group
+        packed = rows[..., : D // 2]
+        lo = (packed & 0xF).to(torch.int16) - 8
+        hi = (packed >> 4).to(torch.int16) - 8
+        q = torch.stack([lo, hi], dim=-1).reshape(*rows.shape[:-1], D // g, g).float()
+        scale = rows[..., D // 2:].contiguous().view(torch.float16).float().unsqueeze(-1)
+        return (q * scale).reshape(*rows.shape[:-1], D).to(dtype)
+
+    def dequant_rows(self, slots: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+        return self._deq(self.data.index_select(0, slots.to(self.data.device, torch.long)), dtype)
+
+    def dequant_all(self, dtype: torch.dtype) -> torch.Tensor:
+        return self._deq(self.data, dtype)
+
+    def store_(self, src: torch.Tensor, slot: torch.Tensor) -> None:
+        D, g = self.head_dim, self.group
+        x = src.float().reshape(*src.shape[:-1], D // g, g)
+        amax = x.abs().amax(dim=-1, keepdim=True)
+        scale = torch.where(amax > 0, amax / 7.0, torch.ones_like(amax)).to(torch.float16)
+        q = torch.clamp(torch.round(x / scale.float()), -7, 7).to(torch.int16) + 8
+        q = q.reshape(*src.shape[:-1], D // 2, 2)
+        packed = (q[..., 0] | (q[..., 1] << 4)).to(torch.uint8)
+        row = torch.cat([packed, scale.squeeze(-1).contiguous().view(torch.uint8)], dim=-1)
+        self.data[slot.long()] = row
+
+
 def quant_rows_reference(x: torch.Tensor):
     """x [..., D] -> (int8 [..., D], fp32 scale [..., 1]); the definition the CUDA kernel is checked against."""
     xf = x.float()
@@ -135,7 +188,7 @@ def quant_rows_reference(x: torch.Tensor):
 
 def quant_store_(layer, src: torch.Tensor, slot: torch.Tensor) -> None:
     """layer[slot[t]] = quantised src[t];  src [T, 2 * Hkv, D] (bf16 on the GPU)."""
-    if isinstance(layer, (Fp8KVLayer, CalibratingKVLayer)):
+    if isinstance(layer, (Fp8KVLayer, CalibratingKVLayer, Int4KVLayer)):
         return layer.store_(src, slot)
     T, rows, D = src.shape
     assert D == layer.head_dim and rows == layer.data.shape[1]
@@ -174,7 +227,7 @@ def gqa_decode(q, layer, req_to_token, b_req_idx, b_seq_len, Hq, Hkv, D, max_seq
     if isinstance(layer, CalibratingKVLayer):
         return plain(q, layer.data, req_to_token, b_req_idx, b_seq_len, Hq, Hkv, D, max_seq_len, sm_scale, out,
                      num_splits, scratch)
-    if not q.is_cuda or D not in (64, 128):
+    if not q.is_cuda or D not in (64, 128) or isinstance(layer, Int4KVLayer):
         if not q.is_cuda:
             return plain(q, layer.dequant_all(q.dtype), req_to_token, b_req_idx, b_seq_len, Hq, Hkv, D, max_seq_len,
                          sm_scale)

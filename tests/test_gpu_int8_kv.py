@@ -160,3 +160,29 @@ def test_llama_with_fp8_pool(dev):
     b = LLM(config=cfg, kv_type="fp8kv_sph", **kw).generate(prompts, sp)
     same = sum(x == y for oa, ob in zip(a, b) for x, y in zip(oa["token_ids"], ob["token_ids"]))
     assert same >= 0.5 * 4 * 12, f"{same} of 48 greedy tokens agree"
+
+
+def test_llama_with_int4_pool_generates_on_the_device(dev):
+    """The 4-bit pool on the GPU: packed rows written and read by the pool's routes (store, widened copy for
+    attention, page copies of the prefix cache), decode outside CUDA graphs; greedy tokens mostly agree with the
+    bf16 pool (random weights: near-ties may flip)."""
+    from lightllm_b200.common.mem_manager import Int4KVMemoryManager
+    from lightllm_b200.engine.llm import LLM
+
+    cfg = dict(model_type="llama", hidden_size=512, intermediate_size=1024, num_hidden_layers=2,
+               num_attention_heads=8, num_key_value_heads=2, head_dim=128, vocab_size=1000, rms_norm_eps=1e-5,
+               eos_token_id=2)
+    kw = dict(max_total_token_num=8192, running_max_req_size=16, max_req_total_len=1024, batch_max_tokens=1024)
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(3, 1000, (n,), generator=g).tolist() for n in (200, 37, 300, 64)]
+    sp = {"max_new_tokens": 12, "ignore_eos": True}
+    a = LLM(config=cfg, **kw).generate(prompts, sp)
+    llm = LLM(config=cfg, kv_type="int4kv", **kw)
+    assert isinstance(llm.model.mem_manager, Int4KVMemoryManager) and llm.model.disable_cudagraph
+    assert llm.model.kv_bytes_per_token() == 2 * 2 * 2 * (64 + 32)
+    b = llm.generate(prompts, sp)
+    assert all(len(o["token_ids"]) == 12 for o in b)
+    same = sum(x == y for oa, ob in zip(a, b) for x, y in zip(oa["token_ids"], ob["token_ids"]))
+    assert same >= 0.4 * 4 * 12, f"{same} of 48 greedy tokens agree"
+    again = llm.generate(prompts, sp)
+    assert again[2]["prompt_cache_len"] > 0

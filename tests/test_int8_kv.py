@@ -27,7 +27,7 @@ def test_row_layout_and_quantisation_error():
     assert (mm.layer(0).data == 0).all() and (mm.layer(2).data == 0).all()
     assert select_mem_manager_class(None) is MemoryManager and select_mem_manager_class("int8kv") is Int8KVMemoryManager
     with pytest.raises(ValueError):
-        select_mem_manager_class("int4kv")
+        select_mem_manager_class("fp8kv_dsa")
 
 
 def test_pages_move_as_opaque_rows():
@@ -222,3 +222,64 @@ def test_calibration_run_writes_a_scale_file_the_fp8_pool_reads(tmp_path):
     merged = CalibrationKVMemoryManager.merge_exports([a, b], str(tmp_path / "all.json"))
     sc = torch.tensor(merged["scales"]).view(2, 4) * 448.0
     assert torch.allclose(sc, torch.tensor([[1.0, 5.0, 2.0, 6.0], [3.0, 7.0, 4.0, 8.0]])) and merged["num_head"] == 2
+
+
+def test_int4_pool_layout_error_and_engine():
+    """`--llm_kv_type int4kv`: two values per byte + one fp16 scale per group; error at most half a step per value;
+    pages move as opaque rows; a model on this pool stays close to the full-precision one and generates through the
+    engine with prefix-cache hits."""
+    from lightllm_b200.common.infer_state import ModelInput
+    from lightllm_b200.common.mem_manager import Int4KVMemoryManager
+    from lightllm_b200.engine.llm import LLM
+
+    torch.manual_seed(0)
+    mm = Int4KVMemoryManager(64, torch.float32, 2, 32, 3, torch.device("cpu"), group_size=8)
+    assert mm.kv_buffer.shape == (3, 65, 4, 16 + 8) and mm.kv_buffer.dtype == torch.uint8
+    assert Int4KVMemoryManager.bytes_per_token(torch.bfloat16, 2, 32, 3, group_size=8) == 3 * 4 * 24
+    assert select_mem_manager_class("int4kv") is Int4KVMemoryManager
+    layer = mm.layer(1)
+    src = torch.randn(5, 4, 32) * torch.tensor([0.1, 1.0, 10.0, 0.0]).view(1, 4, 1)
+    slots = torch.tensor([7, 3, 60, 0, 9], dtype=torch.int32)
+    kv_quant.quant_store_(layer, src, slots)
+    back = layer.dequant_rows(slots, torch.float32)
+    amax = src.view(5, 4, 4, 8).abs().amax(-1, keepdim=True)
+    err = (back - src).view(5, 4, 4, 8).abs()
+    assert (err <= amax / 14 * 1.01 + 1e-6).all()                     # half a step of max / 7 (fp16 scale)
+    assert (back[:, 3] == 0).all() and (mm.layer(0).data == 0).all()
+    pages = mm.gather_pages(torch.tensor([3, 60], dtype=torch.int32))
+    mm.scatter_pages(torch.tensor([20, 21], dtype=torch.int32), pages)
+    assert torch.equal(mm.layer(1).dequant_rows(torch.tensor([20, 21]), torch.float32),
+                       mm.layer(1).dequant_rows(torch.tensor([3, 60]), torch.float32))
+    with pytest.raises(ValueError):
+        Int4KVMemoryManager(8, torch.float32, 2, 32, 1, torch.device("cpu"), group_size=5)
+
+    a = LLM(config=CFG, **KW).model
+    b = LLM(config=CFG, kv_type="int4kv", kv_quant_group_size=8, **KW).model
+    assert isinstance(b.mem_manager, Int4KVMemoryManager) and b.kv_bytes_per_token() == 2 * 2 * 2 * (8 + 4)
+    ids = torch.randint(3, 300, (50,), generator=torch.Generator().manual_seed(3))
+
+    def run(m):
+        req = m.req_manager.alloc()
+        mi = ModelInput(batch_size=1, total_token_num=50, max_kv_len=50, is_prefill=True,
+                        b_req_idx=torch.tensor([req], dtype=torch.int32), b_seq_len=torch.tensor([50], dtype=torch.int32),
+                        mem_indexes=m.mem_manager.alloc(50).clone(), input_ids=ids,
+                        b_ready_cache_len=torch.zeros(1, dtype=torch.int32), max_q_len=50, return_all_logits=True)
+        out = [m.forward(mi).logits.float()]
+        m.req_manager.req_to_next_token_ids[req] = 17
+        mi = ModelInput(batch_size=1, total_token_num=51, max_kv_len=51, is_prefill=False,
+                        b_req_idx=torch.tensor([req], dtype=torch.int32), b_seq_len=torch.tensor([51], dtype=torch.int32),
+                        mem_indexes=m.mem_manager.alloc(1).clone())
+        out.append(m.forward(mi).logits.float())
+        return torch.cat(out)
+
+    la, lb = run(a), run(b)
+    scale = la.abs().max().item()
+    assert (la - lb).abs().max().item() < 0.25 * scale               # 4-bit rows: about 7 % per element
+    assert (la.argmax(-1) == lb.argmax(-1)).float().mean() > 0.6
+    rng = np.random.default_rng(0)
+    prompts = [rng.integers(3, 300, n).tolist() for n in (9, 40, 70)]
+    sp = {"max_new_tokens": 8, "ignore_eos": True}
+    llm = LLM(config=CFG, kv_type="int4kv", **KW)
+    out = llm.generate(prompts, sp)
+    again = llm.generate(prompts, sp)
+    assert all(len(o["token_ids"]) == 8 for o in out) and again[2]["prompt_cache_len"] > 0
