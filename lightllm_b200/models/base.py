@@ -177,7 +177,9 @@ class TransformerLM:
                                  r2t_cols=self.max_seq_length,
                                  num_experts=int(config.get("num_experts") or config.get("n_routed_experts") or
                                                  config.get("num_local_experts") or 0) +
-                                 self.ps.world_size * self.redundancy_cfg.num, status=self.debug_status)
+                                 self.ps.world_size * self.redundancy_cfg.num +
+                                 (int(config.get("n_shared_experts") or 0)
+                                  if extra.get("enable_fused_shared_experts") else 0), status=self.debug_status)
 
     def _open_checkpoint(self, model_dir):
         """The checkpoint as a WeightSource; AWQ checkpoints are presented de-quantised (no int4 GEMM here)."""

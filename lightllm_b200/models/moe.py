@@ -105,6 +105,21 @@ def load_experts(model, lw, src, prefix: str, mc: MoEConfig, ep: bool, gate_name
         return ref.interleave_gate_up(g, u), src.get(q + "down_proj.weight", 1, i0, i1)
 
     mats = [read_expert(e) for e in expert_ids]
+    # `--enable_fused_shared_experts` (tensor-parallel experts): the shared expert joins the grouped GEMMs as
+    # n_shared more experts that every token selects with weight 1, instead of two GEMMs of its own
+    lw.fused_shared = 0
+    ns = mc.n_shared
+    if ns and model.extra.get("enable_fused_shared_experts") and not ep and not use_fp8 and not mc.shared_gate \
+            and mc.shared_inter == ns * mc.inter:
+        q = prefix + mc.shared_name + "."
+        il = i1 - i0
+        s0 = tp_range(mc.shared_inter, r, tp)[0]
+        for j in range(ns):
+            a, b = s0 + j * il, s0 + (j + 1) * il
+            mats.append((ref.interleave_gate_up(src.get(q + "gate_proj.weight", 0, a, b),
+                                                src.get(q + "up_proj.weight", 0, a, b)),
+                         src.get(q + "down_proj.weight", 1, a, b)))
+        lw.fused_shared = ns
     if use_fp8:
         # keep the experts in e4m3 with their block scales: grouped fp8 GEMMs, half the weight bytes
         from ..ops import fp8
@@ -128,7 +143,7 @@ def load_experts(model, lw, src, prefix: str, mc: MoEConfig, ep: bool, gate_name
         lw.ep_counter = torch.zeros(mc.num_experts, dtype=torch.int32, device=model.device)
         lw.ep_red_num, lw.ep_red_ids, lw.ep_layer = R, list(red_ids), layer_no
         lw.ep_read_expert = read_expert               # the manager re-reads experts from the checkpoint later
-    if mc.n_shared:
+    if mc.n_shared and not lw.fused_shared:
         model._load_dense_ffn(lw, src, prefix + mc.shared_name + ".", mc.shared_inter)
         if mc.shared_gate:
             lw.shared_gate_w = dev(src.get(prefix + mc.shared_name + "_gate.weight"))
@@ -146,9 +161,16 @@ def moe_ffn(model, lw, h, mc: MoEConfig, layer: int = -1, st=None):
     else:
         ids, w = moe_ops.grouped_topk(logits, lw.router_bias, mc.top_k, mc.n_group, mc.topk_group,
                                       mc.scoring == "sigmoid", mc.renorm, mc.routed_scale)
+    rc = getattr(model, "route_capture", None)
+    if rc is not None and st is not None and st.extra.get("balance") is None:   # --enable_return_routed_experts
+        rc.capture(layer, ids, st.mem_index)
     out = model._partial_out(T)
     accumulate = False
-    if mc.n_shared:
+    if lw.fused_shared:       # the shared expert's slices are experts E .. E + n - 1, chosen by every token
+        extra = torch.arange(mc.num_experts, mc.num_experts + lw.fused_shared, dtype=ids.dtype, device=ids.device)
+        ids = torch.cat([ids, extra.expand(T, -1)], dim=1)
+        w = torch.cat([w, torch.ones((T, lw.fused_shared), dtype=w.dtype, device=w.device)], dim=1)
+    elif mc.n_shared:
         if lw.shared_fused:
             act = ops.gemm(h, lw.shared_gate_up_w, epi="gated_" + mc.act)
         else:
@@ -157,9 +179,6 @@ def moe_ffn(model, lw, h, mc: MoEConfig, layer: int = -1, st=None):
         if mc.shared_gate:  # every rank scales its partial sum by the same (replicated) gate
             out.mul_(torch.sigmoid(torch.nn.functional.linear(h.float(), lw.shared_gate_w.float())).to(out.dtype))
         accumulate = True
-    rc = getattr(model, "route_capture", None)
-    if rc is not None and st is not None and st.extra.get("balance") is None:   # --enable_return_routed_experts
-        rc.capture(layer, ids, st.mem_index)
     if getattr(lw, "ep_table", None) is not None:      # redundant experts: physical ids + hit counters
         ids = moe_ops.count_remap(ids, lw.ep_table, lw.ep_counter)
     epg = ep_group_of(model, mc)

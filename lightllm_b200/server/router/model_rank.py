@@ -91,7 +91,8 @@ def _build_model_and_backend(args: StartArgs, ps):
                       auto_update_redundancy_expert=bool(getattr(args, "auto_update_redundancy_expert", False)),
                       enable_return_routed_experts=bool(getattr(args, "enable_return_routed_experts", False)),
                       enable_dp_prefill_balance=bool(getattr(args, "enable_dp_prefill_balance", False)),
-                      kv_quant_group_size=getattr(args, "llm_kv_quant_group_size", 8))
+                      kv_quant_group_size=getattr(args, "llm_kv_quant_group_size", 8),
+                      enable_fused_shared_experts=bool(getattr(args, "enable_fused_shared_experts", False)))
     if fused is not None:   # prompt passes as two micro-batches with copy-engine reductions
         from ...parallel import ce as _ce
 
