@@ -21,13 +21,90 @@ import numpy as np
 MIN_AUDIO_LEN = 480  # samples at 16 kHz: shorter clips are zero padded
 
 
-async def fetch_resource(url: str, request=None, timeout: int = 5, proxy: Optional[str] = None) -> bytes:
+class UrlCache:
+    """Downloaded bytes by URL, least recently used first out (`--enable_multimodal_url_cache`): the same picture
+    asked for again (a conversation that carries its earlier turns) is not downloaded again.
+    Reference: lightllm/utils/multimodal_utils.py (the URL cache around fetch_resource)."""
+
+    def __init__(self, max_items: int = 256, max_bytes: int = 256 << 20):
+        from collections import OrderedDict
+
+        self.max_items, self.max_bytes = max_items, max_bytes
+        self.items: "OrderedDict[str, bytes]" = OrderedDict()
+        self.bytes = 0
+        self.hits = self.misses = 0
+
+    def get(self, url: str) -> Optional[bytes]:
+        data = self.items.get(url)
+        if data is None:
+            self.misses += 1
+            return None
+        self.items.move_to_end(url)
+        self.hits += 1
+        return data
+
+    def put(self, url: str, data: bytes) -> None:
+        if len(data) > self.max_bytes:
+            return
+        old = self.items.pop(url, None)
+        if old is not None:
+            self.bytes -= len(old)
+        self.items[url] = data
+        self.bytes += len(data)
+        while len(self.items) > self.max_items or self.bytes > self.max_bytes:
+            _, gone = self.items.popitem(last=False)
+            self.bytes -= len(gone)
+
+
+_url_cache = UrlCache(int(os.getenv("LLB_MULTIMODAL_URL_CACHE_ITEMS", "256")),
+                      int(os.getenv("LLB_MULTIMODAL_URL_CACHE_MB", "256")) << 20)
+
+
+def _start_args():
+    from .core.objs.start_args import get_env_start_args
+
+    return get_env_start_args()
+
+
+async def _download(url: str, timeout: int, proxy: Optional[str]) -> bytes:
     import aiohttp
 
     async with aiohttp.ClientSession(timeout=aiohttp.ClientTimeout(total=timeout)) as sess:
         async with sess.get(url, proxy=proxy) as resp:
             resp.raise_for_status()
             return await resp.read()
+
+
+async def fetch_resource(url: str, request=None, timeout: int = 5, proxy: Optional[str] = None) -> bytes:
+    use_cache = bool(getattr(_start_args(), "enable_multimodal_url_cache", False))
+    if use_cache:
+        data = _url_cache.get(url)
+        if data is not None:
+            return data
+    data = await _download(url, timeout, proxy)
+    if use_cache:
+        _url_cache.put(url, data)
+    return data
+
+
+def resized_dimensions(w: int, h: int, max_pixels: int):
+    """(w, h) scaled down, keeping the aspect ratio, so that w * h <= max_pixels (unchanged when it already is)."""
+    if max_pixels is None or max_pixels <= 0 or w * h <= max_pixels:
+        return w, h
+    f = (max_pixels / float(w * h)) ** 0.5
+    nw, nh = max(1, int(w * f)), max(1, int(h * f))
+    return nw, nh
+
+
+def _resize_image_bytes(raw: bytes, w: int, h: int) -> bytes:
+    from PIL import Image
+
+    with Image.open(BytesIO(raw)) as im:
+        fmt = im.format if im.format in ("PNG", "JPEG", "WEBP") else "PNG"
+        out = im.convert("RGB").resize((w, h), Image.BICUBIC)
+    buf = BytesIO()
+    out.save(buf, format=fmt)
+    return buf.getvalue()
 
 
 class _Item:
@@ -88,11 +165,15 @@ class ImageItem(_Item):
     async def preload(self, request=None):
         if self._preload_data is not None:
             return
+        args = _start_args()
+        max_pixels = int(getattr(args, "max_image_pixels", 0) or 0)
+        if bool(getattr(args, "disable_image_resize", False)):
+            max_pixels = 0
         try:
             if self._type == "image_size":  # synthetic image for benchmarks: data = (w, h)
                 from PIL import Image
 
-                w, h = self._data
+                w, h = resized_dimensions(int(self._data[0]), int(self._data[1]), max_pixels)
                 buf = BytesIO()
                 Image.new("RGB", (int(w), int(h)), (127, 127, 127)).save(buf, format="PNG")
                 raw = buf.getvalue()
@@ -102,6 +183,10 @@ class ImageItem(_Item):
 
             with Image.open(BytesIO(raw)) as im:
                 self.image_w, self.image_h = im.size
+            w, h = resized_dimensions(self.image_w, self.image_h, max_pixels)
+            if (w, h) != (self.image_w, self.image_h):      # `--max_image_pixels` unless `--disable_image_resize`
+                raw = await asyncio.get_running_loop().run_in_executor(None, _resize_image_bytes, raw, w, h)
+                self.image_w, self.image_h = w, h
             self._preload_data = raw
         except Exception as e:
             raise ValueError(f"Failed to read image type={self._type}, data[:100]={str(self._data)[:100]}: {e}")
