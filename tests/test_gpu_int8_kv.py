@@ -164,8 +164,10 @@ def test_llama_with_fp8_pool(dev):
 
 def test_llama_with_int4_pool_generates_on_the_device(dev):
     """The 4-bit pool on the GPU: packed rows written and read by the pool's routes (store, widened copy for
-    attention, page copies of the prefix cache), decode outside CUDA graphs; greedy tokens mostly agree with the
-    bf16 pool (random weights: near-ties may flip)."""
+    attention, page copies of the prefix cache), decode outside CUDA graphs.  Teacher-forced logits stay within the
+    4-bit error of the bf16 pool's (greedy continuations of a random-weight model diverge after the first flip, so
+    they are only checked for length)."""
+    from lightllm_b200.common.infer_state import ModelInput
     from lightllm_b200.common.mem_manager import Int4KVMemoryManager
     from lightllm_b200.engine.llm import LLM
 
@@ -174,15 +176,39 @@ def test_llama_with_int4_pool_generates_on_the_device(dev):
                eos_token_id=2)
     kw = dict(max_total_token_num=8192, running_max_req_size=16, max_req_total_len=1024, batch_max_tokens=1024)
     g = torch.Generator().manual_seed(0)
-    prompts = [torch.randint(3, 1000, (n,), generator=g).tolist() for n in (200, 37, 300, 64)]
-    sp = {"max_new_tokens": 12, "ignore_eos": True}
-    a = LLM(config=cfg, **kw).generate(prompts, sp)
+    ids = torch.randint(3, 1000, (150,), generator=g)
+
+    def run(m):
+        req = m.req_manager.alloc()
+        outs = []
+        for s, e in ((0, 100), (100, 150)):          # the second chunk attends to packed rows of the first
+            n = e - s
+            mi = ModelInput(batch_size=1, total_token_num=e, max_kv_len=e, is_prefill=True,
+                            b_req_idx=torch.tensor([req], dtype=torch.int32),
+                            b_seq_len=torch.tensor([e], dtype=torch.int32), mem_indexes=m.mem_manager.alloc(n).clone(),
+                            input_ids=ids[s:e], b_ready_cache_len=torch.tensor([s], dtype=torch.int32), max_q_len=n,
+                            return_all_logits=True)
+            outs.append(m.forward(mi).logits.float().cpu())
+        m.req_manager.req_to_next_token_ids[req] = 17
+        mi = ModelInput(batch_size=1, total_token_num=151, max_kv_len=151, is_prefill=False,
+                        b_req_idx=torch.tensor([req], dtype=torch.int32),
+                        b_seq_len=torch.tensor([151], dtype=torch.int32), mem_indexes=m.mem_manager.alloc(1).clone())
+        outs.append(m.forward(mi).logits.float().cpu())
+        return torch.cat(outs)
+
+    la = run(LLM(config=cfg, **kw).model)
     llm = LLM(config=cfg, kv_type="int4kv", **kw)
     assert isinstance(llm.model.mem_manager, Int4KVMemoryManager) and llm.model.disable_cudagraph
     assert llm.model.kv_bytes_per_token() == 2 * 2 * 2 * (64 + 32)
+    lb = run(llm.model)
+    scale = la.abs().max().item()
+    # every pass attends over the widened copy of the packed rows, its own new tokens included: 4-bit noise
+    # (about 7 % per K / V element) on all rows, far from the error a layout mistake would give (the scale itself)
+    assert (la - lb).abs().max().item() < 0.3 * scale
+    assert (la - lb).abs().mean().item() < 0.05 * scale
+    prompts = [torch.randint(3, 1000, (n,), generator=g).tolist() for n in (200, 37, 300, 64)]
+    sp = {"max_new_tokens": 12, "ignore_eos": True}
     b = llm.generate(prompts, sp)
     assert all(len(o["token_ids"]) == 12 for o in b)
-    same = sum(x == y for oa, ob in zip(a, b) for x, y in zip(oa["token_ids"], ob["token_ids"]))
-    assert same >= 0.4 * 4 * 12, f"{same} of 48 greedy tokens agree"
     again = llm.generate(prompts, sp)
     assert again[2]["prompt_cache_len"] > 0
