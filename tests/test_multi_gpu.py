@@ -173,3 +173,70 @@ def test_dp_ep_peer_memory_dispatch_matches_single_gpu(tmp_path, W):
     same_prefix = [next((i for i, (a, b) in enumerate(zip(got[k], one["tokens"][k])) if a != b), len(got[k]))
                    for k in sorted(got)]
     assert len(got) == 8 and sum(n == 16 for n in same_prefix) >= 4, same_prefix
+
+
+def _dp_options_worker(rank, world, port, out_dir, red_path):
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import numpy as np
+
+    from lightllm_b200.engine.llm import LLM
+    from lightllm_b200.parallel import dist as pdist
+
+    pdist.init_distributed(world, rank, dp=world, host="127.0.0.1", port=port, device=torch.device("cuda", rank))
+    llm = LLM(config=MOE, max_total_token_num=8192, running_max_req_size=8, max_req_total_len=512,
+              batch_max_tokens=1024, enable_ep_moe=world > 1, disable_cudagraph=True,
+              ep_redundancy_expert_config_path=red_path if world > 1 else None,
+              enable_dp_prefill_balance=world > 1)
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(3, 8192, (n,), generator=g).tolist() for n in (300, 400, 210, 33)]
+    tail = torch.randint(3, 8192, (40,), generator=g).tolist()
+    # unbalanced prompt load: replica 0 gets 910 tokens, the last replica 33
+    mine = prompts if world == 1 else (prompts[:3] if rank == 0 else prompts[3:])
+    outs = llm.generate(mine, {"max_new_tokens": 12, "ignore_eos": True})
+    lw = [l for l in llm.model.layers if getattr(l, "ep_table", None) is not None]
+    hits = int(lw[0].ep_counter.sum().item()) if lw else 0
+    # cross-replica prefix fetch: prompt 1 (400 tokens) was served by replica 0; replica 1 is asked for prompt 1 + tail
+    got, cache_len, second = 0, 0, None
+    if world > 1:
+        new = [(1, np.array(prompts[1] + tail))]
+        got = llm.backend.fetch_prefixes(new)
+    if world == 1 or rank == 1:
+        second = llm.generate([prompts[1] + tail], {"max_new_tokens": 8, "ignore_eos": True})[0]
+        cache_len = second["prompt_cache_len"]
+    else:       # the other replica serves something too, so that both step through the same passes
+        llm.generate([prompts[3] + tail], {"max_new_tokens": 8, "ignore_eos": True})
+    epg = getattr(llm.model, "_ep_group", None)
+    torch.save({"tokens": [o["token_ids"] for o in outs], "status": epg.status() if epg is not None else 0,
+                "hits": hits, "got": got, "cache_len": cache_len,
+                "second": second["token_ids"] if second is not None else None},
+               os.path.join(out_dir, f"opt{world}_r{rank}.pt"))
+    llm.close()
+    if epg is not None:
+        epg.close()
+    pdist.destroy(hard_exit_on_hang=True)
+
+
+@pytest.mark.timeout(600)
+def test_dp_ep_redundant_experts_balance_and_prefix_fetch_on_two_gpus(tmp_path):
+    """Two replicas on two GPUs with redundant experts (physical expert ids through the peer-memory exchange),
+    balanced prompt passes (NCCL all-to-all around attention) and a prefix copied from the other replica (NCCL
+    send / recv): outputs stay those of a single GPU up to bf16 flips."""
+    import json
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    red = tmp_path / "red.json"
+    red.write_text(json.dumps({"redundancy_expert_num": 2, "default": [3, 12]}))
+    mp.spawn(_dp_options_worker, args=(1, _free_port(), str(tmp_path), None), nprocs=1, join=True)
+    mp.spawn(_dp_options_worker, args=(2, _free_port(), str(tmp_path), str(red)), nprocs=2, join=True)
+    one = torch.load(tmp_path / "opt1_r0.pt")
+    r0, r1 = torch.load(tmp_path / "opt2_r0.pt"), torch.load(tmp_path / "opt2_r1.pt")
+    assert r0["status"] == 0 and r1["status"] == 0
+    assert r0["hits"] > 0 and r1["hits"] > 0                      # the rewrite kernel counted the routed experts
+    got = r0["tokens"] + r1["tokens"]
+    same_prefix = [next((i for i, (a, b) in enumerate(zip(x, y)) if a != b), len(x)) for x, y in zip(got, one["tokens"])]
+    assert len(got) == 4 and sum(n == 12 for n in same_prefix) >= 2, same_prefix
+    assert r1["got"] >= 380 and r1["cache_len"] >= 380            # 399 tokens of the 400-token prompt at most
+    # the copied rows hold the right KV: the continuation agrees with the single GPU's (bf16: a late flip is tolerated)
+    agree = sum(a == b for a, b in zip(r1["second"], one["second"]))
+    assert r1["second"][0] == one["second"][0] or agree >= 4, (r1["second"], one["second"])
