@@ -115,6 +115,106 @@ __global__ void __launch_bounds__(256) gdn_recurrent_step_kernel(
   }
 }
 
+// The serving shape (head sizes known at compile time): a warp owns DK / 8 state rows, a lane four neighbouring
+// columns of them, so a thread's strip is DK / 8 vector loads that do not depend on anything and are all in
+// flight before the first product; the same registers are written back after the update.
+__device__ __forceinline__ void ld4(const float* p, float (&v)[4]) {
+  float4 t = *reinterpret_cast<const float4*>(p);
+  v[0] = t.x, v[1] = t.y, v[2] = t.z, v[3] = t.w;
+}
+__device__ __forceinline__ void ld4(const bf16* p, float (&v)[4]) {
+  uint2 t = *reinterpret_cast<const uint2*>(p);
+  __nv_bfloat162 a = *reinterpret_cast<__nv_bfloat162*>(&t.x), b = *reinterpret_cast<__nv_bfloat162*>(&t.y);
+  v[0] = __low2float(a), v[1] = __high2float(a), v[2] = __low2float(b), v[3] = __high2float(b);
+}
+__device__ __forceinline__ void st4(float* p, const float (&v)[4]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void st4(bf16* p, const float (&v)[4]) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+  uint2 t;
+  t.x = *reinterpret_cast<unsigned*>(&a);
+  t.y = *reinterpret_cast<unsigned*>(&b);
+  *reinterpret_cast<uint2*>(p) = t;
+}
+
+template <typename ST, int DK, int DV>
+__global__ void __launch_bounds__(256, 2) gdn_recurrent_step_vec_kernel(
+    const float* __restrict__ y, const float* __restrict__ g, const float* __restrict__ beta, ST* __restrict__ state,
+    const int* __restrict__ req, float* __restrict__ out, int nk, int nv, int C) {
+  constexpr int NW = 8, RPW = DK / NW;
+  static_assert(DV == 128 && DK % NW == 0, "a lane owns four columns of a 128-wide value head");
+  __shared__ float qs[DK], ks[DK];
+  __shared__ __align__(16) float red[NW][DV];
+  __shared__ float red33[33];
+  const int b = blockIdx.x / nv, h = blockIdx.x - b * nv;
+  const int hk = h / (nv / nk), kd = nk * DK;
+  const float* yb = y + (int64_t)b * C;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, col0 = lane * 4;
+  // the state strip first: nothing below depends on it until the products
+  ST* S = state + (((int64_t)req[b] * nv + h) * DK + warp * RPW) * DV + col0;
+  float s[RPW][4];
+#pragma unroll
+  for (int t = 0; t < RPW; ++t) ld4(S + t * DV, s[t]);
+  float sq = 0.f, sk = 0.f;
+  for (int i = tid; i < DK; i += 256) {
+    float qv = yb[hk * DK + i], kv = yb[kd + hk * DK + i];
+    qs[i] = qv;
+    ks[i] = kv;
+    sq += qv * qv;
+    sk += kv * kv;
+  }
+  sq = block_sum(sq, red33);
+  sk = block_sum(sk, red33);
+  const float qscale = rsqrtf(sq + 1e-6f) * rsqrtf((float)DK), kscale = rsqrtf(sk + 1e-6f);
+  float v[4];
+#pragma unroll
+  for (int c = 0; c < 4; ++c) v[c] = yb[2 * kd + h * DV + col0 + c];
+  const float decay = __expf(g[(int64_t)b * nv + h]), bt = beta[(int64_t)b * nv + h];
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int t = 0; t < RPW; ++t) {
+    const float kr = ks[warp * RPW + t] * kscale;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      s[t][c] *= decay;
+      acc[c] += s[t][c] * kr;
+    }
+  }
+  st4(&red[warp][col0], acc);
+  __syncthreads();
+  float d[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int w = 0; w < NW; ++w) {
+    float t4[4];
+    ld4(&red[w][col0], t4);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) d[c] += t4[c];
+  }
+#pragma unroll
+  for (int c = 0; c < 4; ++c) d[c] = bt * (v[c] - d[c]);
+  __syncthreads();
+  float o[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int t = 0; t < RPW; ++t) {
+    const float kr = ks[warp * RPW + t] * kscale, qr = qs[warp * RPW + t] * qscale;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      s[t][c] += kr * d[c];
+      o[c] += s[t][c] * qr;
+    }
+    st4(S + t * DV, s[t]);
+  }
+  st4(&red[warp][col0], o);
+  __syncthreads();
+  if (tid < DV) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < NW; ++w) t += red[w][tid];
+    out[((int64_t)b * nv + h) * DV + tid] = t;
+  }
+}
+
 }  // namespace
 
 // x, y [B, C] fp32; state [slots, C, K-1] (fp32: state_bf16 = 0, bf16: 1); w [C, K] fp32; req [B] slot of every row
@@ -139,6 +239,17 @@ LLB_EXPORT int llb_gdn_recurrent_step(const float* y, const float* g, const floa
                                       cudaStream_t st) {
   if (B <= 0) return LLB_OK;
   if (nk < 1 || nv % nk != 0 || dv < 32 || dv > 256 || dv % 32 != 0 || dk < 1) return LLB_ERR_UNSUPPORTED;
+  if (dk == 128 && dv == 128) {                // the serving shape: vector loads, two CTAs per SM
+    int C = 2 * nk * dk + nv * dv;
+    if (state_bf16)
+      gdn_recurrent_step_vec_kernel<bf16, 128, 128><<<B * nv, 256, 0, st>>>(y, g, beta, (bf16*)state, req, out, nk, nv,
+                                                                            C);
+    else
+      gdn_recurrent_step_vec_kernel<float, 128, 128><<<B * nv, 256, 0, st>>>(y, g, beta, (float*)state, req, out, nk,
+                                                                             nv, C);
+    LLB_LAUNCH_CHECK();
+    return LLB_OK;
+  }
   int groups = 256 / dv;                       // threads = dv * groups <= 256
   if (groups > dk) groups = dk;
   int rpt = (dk + groups - 1) / groups;
