@@ -142,6 +142,52 @@ class ModelBackend:
         self._steps = 0
         self._step_timing = os.environ.get("LLB_STEP_TIMING", "0") == "1"
         self._pending = None  # a launched decode step whose tokens have not been read back yet
+        if self.radix_cache is not None and model.config.get("prompt_cache_kv_buffer"):
+            self.preload_prompt_cache_kv(model.config, getattr(model, "model_dir", None))
+
+    # ------------------------------------------------------------------ saved prompt prefix
+    def save_prompt_cache_kv(self, token_ids, path: str) -> int:
+        """Writes the KV rows of a cached prompt prefix (as they sit in the pool: every layer's rows of this rank's KV
+        heads) to `path`; returns the number of tokens saved.  A deployment lists the file per rank under
+        `prompt_cache_kv_buffer` and the tokens under `prompt_cache_token_ids` in config.json; at start-up the rows
+        are loaded into the pool and pinned in the prefix tree (a system prompt computed once, e.g. in full precision
+        for a quantised deployment).  Reference: lightllm/server/router/model_infer/infer_batch.py:253-265."""
+        ids = np.asarray(token_ids, dtype=np.int64)
+        node, n, slots = self.radix_cache.match_prefix(ids, update_refs=True)
+        if node is None:
+            return 0
+        try:
+            pages = self.model.mem_manager.gather_pages(torch.from_numpy(np.ascontiguousarray(slots[:n])).to(torch.int32))
+            torch.save({"token_ids": torch.from_numpy(ids[:n].copy()), "kv": pages.cpu()}, path)
+        finally:
+            self.radix_cache.dec_node_ref_counter(node)
+        return n
+
+    def preload_prompt_cache_kv(self, cfg: dict, model_dir: Optional[str]) -> int:
+        """Loads the saved prefix of this rank and pins it (reference:
+        lightllm/server/router/model_infer/mode_backend/base_backend.py:961-977)."""
+        rank = self.model.ps.global_rank
+        files = cfg["prompt_cache_kv_buffer"]
+        name = files.get(f"rank_{rank}") if isinstance(files, dict) else files
+        if not name:
+            return 0
+        path = name if os.path.isabs(name) or not model_dir else os.path.join(model_dir, name)
+        blob = torch.load(path, weights_only=True, map_location="cpu")
+        kv = blob["kv"] if isinstance(blob, dict) else blob
+        ids = np.asarray(cfg.get("prompt_cache_token_ids") if cfg.get("prompt_cache_token_ids") is not None
+                         else blob["token_ids"], dtype=np.int64)
+        mm = self.model.mem_manager
+        n = min(len(ids), kv.shape[1])
+        want = (mm.layer_num, *mm.kv_row_shape())
+        if (kv.shape[0], *kv.shape[2:]) != want or kv.dtype != mm.dtype:
+            raise ValueError(f"prompt cache file {path}: rows {tuple(kv.shape)} {kv.dtype} do not fit this pool "
+                             f"{want} {mm.dtype}")
+        slots = mm.alloc(n).clone()
+        mm.scatter_pages(slots, kv[:, :n].to(mm.device))
+        self.radix_cache.insert(ids[:n], slots.cpu().numpy().astype(np.int32))
+        self.radix_cache.match_prefix(ids[:n], update_refs=True)       # pinned for the life of the process
+        self.stats["prompt_cache_preloaded_tokens"] = n
+        return n
 
     # ------------------------------------------------------------------ requests
     def add_reqs(self, shm_reqs: List[Req]) -> List[InferReq]:

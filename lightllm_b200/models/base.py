@@ -112,6 +112,7 @@ class TransformerLM:
                  share_with: Optional["TransformerLM"] = None, extra_kv_layers: int = 0, **extra):
         config = normalize_config(config)
         self.config = config
+        self.model_dir = model_dir
         self.ps = pstate or pdist.state()
         self.device = self.ps.device
         self.tp = TPContext(self.ps, fused=tp_fused)
