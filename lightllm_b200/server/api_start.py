@@ -75,7 +75,7 @@ def normalize_args(args: StartArgs, config_override: dict = None) -> StartArgs:
         assert a.output_constraint_mode == "none", "token healing and output constraints are exclusive"
     assert not (a.first_token_constraint_mode and a.output_constraint_mode != "none")
     if a.enable_ep_moe:
-        assert a.dp == a.tp or a.dp == 1, "--enable_ep_moe expects --dp 1 or --dp equal to --tp"
+        assert a.tp % a.dp == 0, "--enable_ep_moe: --dp must divide --tp (replicas of tp / dp tensor-parallel ranks)"
     if a.mtp_mode is not None:
         assert a.mtp_step > 0 and a.mtp_draft_model_dir, "mtp needs --mtp_step and --mtp_draft_model_dir"
     if a.run_mode in ("prefill", "decode"):
