@@ -103,3 +103,23 @@ def test_dp2_ep2_with_redundant_experts_matches_single(tmp_path):
         assert all(e not in own for ids in res["red"] for e in ids)      # never a copy of an own expert
     written = json.loads((tmp_path / "redundancy_expert_config.json").read_text())
     assert written["redundancy_expert_num"] == 2 and len(written["0"]) == 2 and len(written["1"]) == 2
+
+
+def test_write_expert_slot_bf16_and_fp8():
+    """Replacing one expert inside the stacked tensors the grouped GEMMs read (what a live re-placement commits)."""
+    from lightllm_b200.engine.redundancy import write_expert_slot
+    from lightllm_b200.ops import fp8
+
+    torch.manual_seed(0)
+    stacked = torch.randn(4, 64, 128)
+    new = torch.randn(64, 128)
+    keep = stacked.clone()
+    write_expert_slot(stacked, 2, new)
+    assert torch.equal(stacked[2], new) and torch.equal(stacked[[0, 1, 3]], keep[[0, 1, 3]])
+    ws = [fp8.Fp8Weight.from_float(torch.randn(128, 256), 32) for _ in range(3)]
+    ex = fp8.Fp8Experts(fp8.stack_experts(ws), 3)
+    before = ex.dequant().clone()
+    repl = fp8.Fp8Weight.from_float(torch.randn(128, 256) * 3, 32)
+    write_expert_slot(ex, 1, repl)
+    after = ex.dequant()
+    assert torch.equal(after[1], repl.dequant()) and torch.equal(after[[0, 2]], before[[0, 2]])
