@@ -54,9 +54,15 @@ def state() -> ParallelState:
 
 def init_distributed(world_size: int = 1, rank: int = 0, dp: int = 1, nnodes: int = 1, node_rank: int = 0,
                      host: str = "127.0.0.1", port: int = 28765, backend: Optional[str] = None,
-                     device: Optional[torch.device] = None, timeout_s: float = 1800.0) -> ParallelState:
+                     device: Optional[torch.device] = None, timeout_s: float = 1800.0,
+                     config_server: Optional[tuple] = None) -> ParallelState:
     """Create the world group and the derived groups; a 1-element all-reduce warms the backend up
-    (reference: lightllm/utils/dist_utils.py:130-161)."""
+    (reference: lightllm/utils/dist_utils.py:130-161).
+
+    `config_server` = (host, http port): `--use_config_server_to_init_nccl`.  The rendezvous store then lives in
+    the config server (rank 0 asks it to start one on `port`, the other ranks wait until it is up) and every rank,
+    rank 0 included, joins as a client, so a model world can be restarted without rank 0's port lingering
+    (reference: lightllm/utils/dist_utils.py:293-318)."""
     global _STATE
     assert world_size % dp == 0, "--dp must divide --tp"
     per_node = world_size // nnodes
@@ -71,6 +77,8 @@ def init_distributed(world_size: int = 1, rank: int = 0, dp: int = 1, nnodes: in
     if device.type == "cuda":
         torch.cuda.set_device(device)
     if world_size > 1:
+        if not dist.is_initialized() and config_server is not None:
+            _external_store(config_server, port, rank, world_size)
         if not dist.is_initialized():
             dist.init_process_group(backend, init_method=f"tcp://{host}:{port}", world_size=world_size, rank=rank,
                                     timeout=datetime.timedelta(seconds=timeout_s))
@@ -110,6 +118,30 @@ def init_from_env(dp: int = 1) -> ParallelState:
     host = os.environ.get("MASTER_ADDR", "127.0.0.1")
     port = int(os.environ.get("MASTER_PORT", "28765"))
     return init_distributed(world, rank, dp=dp, host=host, port=port)
+
+
+def _external_store(config_server, store_port: int, rank: int, world_size: int, wait_s: float = 180.0):
+    """Asks the config server for a rendezvous store on `store_port` and makes this process join it as a client."""
+    import json
+    import time
+    import urllib.error
+    import urllib.request
+
+    host, http_port = config_server
+    url = f"http://{host}:{http_port}/start_tcp_store_server?tcp_store_port={store_port}&rank_id={rank}" \
+          f"&world_size={world_size}"
+    t0 = time.time()
+    while True:
+        try:
+            with urllib.request.urlopen(url, timeout=30) as r:
+                if r.status == 200 and json.loads(r.read()).get("status") == "ok":
+                    break
+        except (urllib.error.URLError, OSError):
+            pass                      # rank 0 has not asked yet (503) or the server is still coming up
+        if time.time() - t0 > wait_s:
+            raise TimeoutError(f"the config server at {host}:{http_port} did not provide a store on port {store_port}")
+        time.sleep(0.2)
+    os.environ["TORCHELASTIC_USE_AGENT_STORE"] = "True"     # torch: every rank is a client of the tcp:// store
 
 
 def destroy(hard_exit_on_hang: bool = False, wait_s: float = 20.0):

@@ -224,7 +224,6 @@ COMPAT_ONLY_FLAGS = (
     "enable_triton_fallback", "disable_flashinfer_allreduce", "penalty_counter_mode", "load_way",
     "enable_prefill_cudagraph", "prefill_cudagraph_max_handle_token",
     "pd_trans_mode",
-    "use_config_server_to_init_nccl",
     "config_server_visual_redis_port", "visual_use_proxy_mode", "visual_rpyc_port", "afs_image_embed_dir",
     "afs_embed_capacity", "vit_quant_type", "vit_quant_cfg", "visual_tp", "audio_tp", "audio_dp", "audio_gpu_ids",
     "visual_send_batch_size", "linear_att_page_block_num",

@@ -284,7 +284,9 @@ def model_rank_main(args_dict: dict, rank: int, pipe, config_override: Optional[
         local_rank = rank % node_world
         device = torch.device("cuda", local_rank) if use_cuda else torch.device("cpu")
         ps = pdist.init_distributed(args.tp, rank, dp=args.dp, nnodes=args.nnodes, node_rank=args.node_rank,
-                                    host=args.nccl_host, port=args.nccl_port, device=device)
+                                    host=args.nccl_host, port=args.nccl_port, device=device,
+                                    config_server=(args.config_server_host, args.config_server_port)
+                                    if getattr(args, "use_config_server_to_init_nccl", False) else None)
         if config_override is not None:
             args._config_override = config_override
         model, backend = _build_model_and_backend(args, ps)
