@@ -21,6 +21,19 @@ def _addr(args, suffix):
     return zmq_addr(args, f"{args.metric_port}_{suffix}")
 
 
+def gateway_auth_handler(url, method, timeout, headers, data):
+    """`--enable_monitor_auth`: pushes to the gateway carry HTTP basic auth taken from the environment
+    (reference: lightllm/server/metrics/metrics.py:38-43)."""
+    import os
+
+    from prometheus_client.exposition import basic_auth_handler
+
+    user, password = os.getenv("USERNAME"), os.getenv("PASSWORD")
+    if user is None or password is None:
+        raise ValueError("--enable_monitor_auth needs the USERNAME and PASSWORD environment variables")
+    return basic_auth_handler(url, method, timeout, headers, data, user, password)
+
+
 class MetricServer:
     def __init__(self, args: StartArgs):
         self.args = args
@@ -40,11 +53,14 @@ class MetricServer:
         from prometheus_client import push_to_gateway
 
         grouping = dict(kv.split("=", 1) for kv in (self.args.grouping_key or []) if "=" in kv)
+        kw = {}
+        if getattr(self.args, "enable_monitor_auth", False):     # basic auth from the USERNAME / PASSWORD variables
+            kw["handler"] = gateway_auth_handler
         while True:
             time.sleep(self.args.push_interval)
             try:
                 push_to_gateway(self.args.metric_gateway, job=self.args.job_name, registry=self.monitor.registry,
-                                grouping_key=grouping)
+                                grouping_key=grouping, **kw)
             except Exception:
                 pass
 
