@@ -107,39 +107,49 @@ class DeepseekV32LM(DeepseekV2LM):
         return self._sparse_attend(qi, w, idx_layer, q_lat, q_pe, kv_layer, st)
 
     def _sparse_attend(self, qi, w, idx_layer, q_lat, q_pe, kv_layer, st):
-        """Per request: index scores of its query tokens over its whole context, top-k selection under the causal
-        mask, softmax attention over the selected latent rows."""
-        kvl, dev = self.kv_lora, q_lat.device
+        """Index scores of every query token over its request's context, top-k selection under the causal mask, then
+        ONE launch of the absorbed-MLA attention kernel in its decode form over per-token slot lists: token t is
+        handed to the kernel as a "request" whose table row holds the slots selected for it.  Decode batches are
+        scored in one batched product; prompt passes per request (their score matrices differ in shape)."""
+        dev = q_lat.device
         r2t = self.req_manager.req_to_token_indexs
+        T, K = q_lat.shape[0], self.idx_topk
         B = st.b_req_idx.shape[0]
-        req_cpu = st.b_req_idx.tolist()
-        len_cpu = st.b_seq_len.tolist()
-        if st.is_prefill:
-            q_len = st.extra["q_len_cpu"].tolist()
+        sel = torch.zeros((T, K), dtype=torch.int32, device=dev)
+        sel_len = torch.empty(T, dtype=torch.int32, device=dev)
+
+        def pick(score, k):
+            # stable order: equal scores (e.g. all heads cut off by the relu) keep the earlier token, whatever the
+            # shape of the call; masked entries (-inf) sort behind every real one
+            return score.sort(dim=-1, descending=True, stable=True).indices[:, :k]
+
+        if not st.is_prefill:
+            S = int(st.max_kv_len)
+            lens = st.b_seq_len.long()
+            rows = r2t.index_select(0, st.b_req_idx.long())[:, :S]                       # [B, S] slots
+            kk = idx_layer[rows.long()].float()                                          # [B, S, Dn]
+            score = (torch.relu(torch.einsum("bhd,bsd->bhs", qi, kk)) * w.unsqueeze(-1)).sum(1)   # [B, S]
+            score = score.masked_fill(torch.arange(S, device=dev)[None, :] >= lens[:, None], float("-inf"))
+            k = min(K, S)
+            sel[:, :k] = rows.gather(1, pick(score, k))
+            sel_len.copy_(lens.clamp(max=K))
         else:
-            q_len = [1] * B
-        out = torch.empty((q_lat.shape[0], q_lat.shape[1], kvl), dtype=q_lat.dtype, device=dev)
-        off = 0
-        for b in range(B):
-            n, S = int(q_len[b]), int(len_cpu[b])
-            sl = slice(off, off + n)
-            slots = r2t[req_cpu[b], :S].long()
-            qpos = torch.arange(S - n, S, device=dev)                                   # positions of the query tokens
-            causal = torch.arange(S, device=dev)[None, :] <= qpos[:, None]              # [n, S]
-            kk = idx_layer[slots].float()                                               # [S, Dn]
-            score = (torch.relu(torch.einsum("thd,sd->ths", qi[sl], kk)) * w[sl].unsqueeze(-1)).sum(1)   # [n, S]
-            score = score.masked_fill(~causal, float("-inf"))
-            if S > self.idx_topk:
-                # stable order: equal scores (e.g. all heads cut off by the relu) keep the earlier token, whatever
-                # the shape of the call
-                top = score.sort(dim=-1, descending=True, stable=True).indices[:, : self.idx_topk]
-                keep = torch.zeros_like(causal).scatter_(1, top, True) & causal
-            else:
-                keep = causal
-            kv = kv_layer[slots, 0].float()                                             # [S, kvl + rope]
-            att = torch.einsum("thc,sc->ths", q_lat[sl].float(), kv[:, :kvl]) + \
-                torch.einsum("thr,sr->ths", q_pe[sl].float(), kv[:, kvl:])
-            att = (att * self.sm_scale).masked_fill(~keep.unsqueeze(1), float("-inf"))
-            out[sl] = torch.einsum("ths,sc->thc", torch.softmax(att, dim=-1), kv[:, :kvl]).to(out.dtype)
-            off += n
-        return out
+            req_cpu, len_cpu = st.b_req_idx.tolist(), st.b_seq_len.tolist()
+            q_len = st.extra["q_len_cpu"].tolist()
+            off = 0
+            for b in range(B):
+                n, S = int(q_len[b]), int(len_cpu[b])
+                sl = slice(off, off + n)
+                slots = r2t[req_cpu[b], :S]
+                qpos = torch.arange(S - n, S, device=dev)                                # positions of the query tokens
+                causal = torch.arange(S, device=dev)[None, :] <= qpos[:, None]           # [n, S]
+                kk = idx_layer[slots.long()].float()                                     # [S, Dn]
+                score = (torch.relu(torch.einsum("thd,sd->ths", qi[sl], kk)) * w[sl].unsqueeze(-1)).sum(1)   # [n, S]
+                score = score.masked_fill(~causal, float("-inf"))
+                k = min(K, S)
+                sel[sl, :k] = slots[pick(score, k)]
+                sel_len[sl] = (qpos + 1).clamp(max=K).to(torch.int32)
+                off += n
+        tok = torch.arange(T + 1, dtype=torch.int32, device=dev)
+        return mla_ops.mla_attention(q_lat.contiguous(), q_pe, kv_layer, sel, tok[:T], sel_len, tok, sel_len - 1,
+                                     self.kv_lora, self.sm_scale, False, 1, K)

@@ -111,3 +111,51 @@ def test_deepseek_tiny_model_gpu_matches_cpu(dev):
     scale = outs["cpu"].abs().max().item()
     err = (outs["cpu"] - outs["gpu"]).abs().max().item()
     assert err < 0.08 * scale + 0.05, (err, scale)
+
+
+def test_deepseek_v32_sparse_attention_gpu_matches_cpu(dev):
+    """DeepSeek-V3.2: contexts beyond `index_topk` select their keys with the indexer and attend through the MLA
+    kernel over per-token slot lists (prompt pass and a decode step); the fp32 CPU restatement takes the same route
+    on torch ops.  A near-tie in the selection can flip one key under bf16 rounding: the mean error is bounded
+    tightly, the worst element loosely."""
+    from lightllm_b200.common.infer_state import ModelInput
+    from lightllm_b200.models.registry import get_model
+    from lightllm_b200.parallel import dist as pdist
+
+    cfg = dict(model_type="deepseek_v32", hidden_size=512, num_hidden_layers=3, num_attention_heads=16, q_lora_rank=256,
+               kv_lora_rank=512, qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128, intermediate_size=1024,
+               moe_intermediate_size=256, n_routed_experts=16, n_shared_experts=1, num_experts_per_tok=4, n_group=4,
+               topk_group=2, first_k_dense_replace=1, routed_scaling_factor=2.5, scoring_func="sigmoid",
+               topk_method="noaux_tc", norm_topk_prob=True, vocab_size=2048, rms_norm_eps=1e-6, rope_theta=1e4,
+               eos_token_id=2, index_n_heads=4, index_head_dim=64, index_topk=64, max_position_embeddings=512)
+    ids = torch.randint(3, 2048, (150,), generator=torch.Generator().manual_seed(0))
+    outs = {}
+    source = None
+    for name, device in (("cpu", torch.device("cpu")), ("gpu", dev)):
+        ps = pdist.ParallelState(device=device)
+        m = get_model(cfg, pstate=ps, data_type="bfloat16" if name == "gpu" else "float32", max_total_token_num=1024,
+                      max_req_num=4, max_seq_length=256, disable_cudagraph=True, random_seed=0, weight_source=source)
+        source = m.weight_source
+        calls = []
+        orig = m._sparse_attend
+        m._sparse_attend = lambda *a, _o=orig, _c=calls: (_c.append(1), _o(*a))[1]
+        req = m.req_manager.alloc()
+        slots = m.mem_manager.alloc(len(ids))
+        mi = ModelInput(batch_size=1, total_token_num=len(ids), max_kv_len=len(ids), is_prefill=True,
+                        b_req_idx=torch.tensor([req], dtype=torch.int32),
+                        b_seq_len=torch.tensor([len(ids)], dtype=torch.int32), mem_indexes=slots.clone(),
+                        input_ids=ids, b_ready_cache_len=torch.zeros(1, dtype=torch.int32), max_q_len=len(ids),
+                        return_all_logits=True)
+        pre = m.forward(mi).logits.float().cpu()
+        m.req_manager.req_to_next_token_ids[req] = 17
+        mi = ModelInput(batch_size=1, total_token_num=151, max_kv_len=151, is_prefill=False,
+                        b_req_idx=torch.tensor([req], dtype=torch.int32),
+                        b_seq_len=torch.tensor([151], dtype=torch.int32), mem_indexes=m.mem_manager.alloc(1).clone())
+        dec = m.forward(mi).logits.float().cpu()
+        outs[name] = torch.cat([pre, dec])
+        assert len(calls) == 2 * 3                       # the selection route ran in every layer of both passes
+    scale = outs["cpu"].abs().max().item()
+    d = (outs["cpu"] - outs["gpu"]).abs()
+    assert d.mean().item() < 0.02 * scale, (d.mean().item(), scale)
+    assert d.max().item() < 0.5 * scale, (d.max().item(), scale)
+    assert d[:64].max().item() < 0.08 * scale + 0.05     # the first index_topk positions select everything
