@@ -9,8 +9,9 @@ and the absorbed MLA attention of t runs over the `index_topk` best-scoring toke
 live in a per-layer cache next to the latent KV cache (same slots).
 
 While a batch's contexts are no longer than `index_topk` every token is selected and the dense MLA kernel runs.
-Beyond that the selection and the attention over the selected tokens run on torch ops with a dense mask over the
-request's context (correct, not fast), outside CUDA graphs.  The reference quantises the indexer's q and k to fp8
+Beyond that the scores and the selection run on torch ops (stable sort) and the attention over the selected tokens is
+one launch of the MLA kernel in its decode form over per-token slot lists (`_sparse_attend`), outside CUDA graphs.
+The reference quantises the indexer's q and k to fp8
 after a Hadamard rotation (which leaves q . k unchanged); here they stay in the compute dtype.
 
 Reference: lightllm/models/deepseek3_2/{model.py,layer_infer/transformer_layer_infer.py (NsaInfer),
