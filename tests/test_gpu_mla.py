@@ -127,7 +127,7 @@ def test_deepseek_v32_sparse_attention_gpu_matches_cpu(dev):
                moe_intermediate_size=256, n_routed_experts=16, n_shared_experts=1, num_experts_per_tok=4, n_group=4,
                topk_group=2, first_k_dense_replace=1, routed_scaling_factor=2.5, scoring_func="sigmoid",
                topk_method="noaux_tc", norm_topk_prob=True, vocab_size=2048, rms_norm_eps=1e-6, rope_theta=1e4,
-               eos_token_id=2, index_n_heads=4, index_head_dim=64, index_topk=64, max_position_embeddings=512)
+               eos_token_id=2, index_n_heads=16, index_head_dim=64, index_topk=64, max_position_embeddings=512)
     ids = torch.randint(3, 2048, (150,), generator=torch.Generator().manual_seed(0))
     outs = {}
     source = None
