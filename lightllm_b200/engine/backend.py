@@ -391,7 +391,8 @@ class ModelBackend:
             arr = r.shm_req.shm_prompt_ids.arr
             nxt[off:off + c] = arr[start + 1:start + c + 1]
             off += c
-        lp = ops.token_logprob(logits, torch.from_numpy(nxt).to(self.device)).cpu().numpy()
+        nxt_dev = torch.from_numpy(nxt).to(self.device)
+        lp = ops.token_logprob(logits, nxt_dev).cpu().numpy()
         off = 0
         for r, c in zip(reqs, chunks):
             c = int(c)
@@ -399,7 +400,27 @@ class ModelBackend:
             n = min(c, r.shm_req.input_len - 1 - start)
             if n > 0 and self.is_master_in_dp:
                 r.shm_req.shm_logprobs.arr[start + 1:start + 1 + n] = lp[off:off + n]
+                meta = getattr(r.shm_req, "shm_prompt_meta", None)
+                if meta is not None and r.sampling.prompt_logprobs >= 0:
+                    self._prompt_rank_and_topk(meta.arr, start, n, logits[off:off + n], nxt_dev[off:off + n])
             off += c
+
+    @staticmethod
+    def _prompt_rank_and_topk(out: np.ndarray, start: int, n: int, logits, next_ids, block: int = 1024):
+        """Rank of every prompt token among the vocabulary at its position and the k most likely tokens there
+        (out[pos] = [rank, k ids, k logprobs]); in blocks of rows, the log-softmax of a block is materialised."""
+        k = (out.shape[1] - 1) // 2
+        for a in range(0, n, block):
+            b = min(a + block, n)
+            lsm = torch.log_softmax(logits[a:b].float(), dim=-1)
+            own = lsm.gather(1, next_ids[a:b].view(-1, 1))
+            rank = (lsm > own).sum(-1) + 1
+            rows = slice(start + 1 + a, start + 1 + b)
+            out[rows, 0] = rank.float().cpu().numpy()
+            if k:
+                vals, idx = lsm.topk(k, dim=-1)
+                out[rows, 1:1 + k] = idx.float().cpu().numpy()
+                out[rows, 1 + k:] = vals.cpu().numpy()
 
     # ---- decode ----
     def _snapshot_states(self, reqs: List[InferReq]):

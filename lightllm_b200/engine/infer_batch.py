@@ -186,7 +186,8 @@ class InferenceContext:
     def _match_radix_cache(self, req: InferReq):
         """Reuse cached KV of the longest known prefix of prompt[:-1] (the last prompt token must run
         through the model to produce the first output)."""
-        if self.radix_cache is None or req.shm_req.sample_params.disable_prompt_cache:
+        if self.radix_cache is None or req.shm_req.sample_params.disable_prompt_cache or \
+                req.shm_req.sample_params.prompt_logprobs >= 0:     # every prompt position must run through the model
             return
         ids = req.shm_req.shm_prompt_ids.arr[: max(req.total_len() - 1, 0)]
         node, n, slots = self.radix_cache.match_prefix(ids, update_refs=True)

@@ -43,6 +43,7 @@ async def lightllm_generate(request: Request, g) -> Response:
     prompt = body.pop("inputs")
     params = dict(body.pop("parameters", {}))
     return_details = params.pop("return_details", False)
+    prompt_lp = None
     return_routed = params.pop("return_routed_experts", bool(getattr(g.args, "enable_return_routed_experts", False)))
     routed = {}
     sp = _make_params(g, params)
@@ -60,6 +61,8 @@ async def lightllm_generate(request: Request, g) -> Response:
         prompt_tokens = meta.get("prompt_tokens", prompt_tokens)
         if "routed_experts" in meta:     # travels with the last token only; kept out of the per-token details
             routed[sub_id] = meta.pop("routed_experts")
+        if "prompt_logprobs" in meta:
+            prompt_lp = (meta.pop("prompt_token_ids", None), meta.pop("prompt_logprobs"))
         if return_details:
             m = dict(meta)
             m["text"] = text
@@ -74,6 +77,8 @@ async def lightllm_generate(request: Request, g) -> Response:
            "logprobs": logprobs[ids[0]] if len(ids) == 1 else [logprobs[i] for i in ids]}
     if return_details:
         ret["tokens"] = tokens[ids[0]] if len(ids) == 1 else [tokens[i] for i in ids]
+    if prompt_lp is not None:
+        ret["prompt_token_ids"], ret["prompt_logprobs"] = prompt_lp
     if return_routed and routed:
         ret["routed_experts"] = routed.get(ids[0]) if len(ids) == 1 else [routed.get(i) for i in ids]
     return Response(content=json.dumps(ret, ensure_ascii=False).encode("utf-8"), media_type="application/json")

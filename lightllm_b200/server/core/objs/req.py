@@ -254,6 +254,24 @@ class Req(ctypes.Structure):
     def create_logprobs_shm_array(self):
         self.shm_logprobs = ShmArray(self._name("logprobs"), (self.alloc_shm_numpy_len,), np.float32).create_shm()
 
+    PROMPT_TOPK_MAX = 20
+
+    def prompt_meta_cols(self) -> int:
+        """Columns of the per-position prompt record: rank of the prompt token, then k ids and k logprobs of the
+        k most likely tokens at that position (`prompt_logprobs` = k, capped)."""
+        k = min(max(int(self.sample_params.prompt_logprobs), 0), self.PROMPT_TOPK_MAX)
+        return 1 + 2 * k
+
+    def create_prompt_meta_shm_array(self):
+        self.shm_prompt_meta = ShmArray(self._name("pmeta"), (self.input_len + 1, self.prompt_meta_cols()),
+                                        np.float32).create_shm()
+        self.shm_prompt_meta.arr[:, 0] = -1.0
+
+    def link_prompt_meta_shm_array(self, shm_prefix: str):
+        self._shm_prefix = shm_prefix
+        self.shm_prompt_meta = ShmArray(self._name("pmeta"), (self.input_len + 1, self.prompt_meta_cols()),
+                                        np.float32).link_shm()
+
     def create_routed_shm_array(self, num_moe_layers: int, top_k: int, dtype):
         """Per-token routed expert ids [tokens, MoE layers, top_k], written by the model rank when the request
         finishes (`--enable_return_routed_experts`)."""
@@ -274,7 +292,7 @@ class Req(ctypes.Structure):
         self.shm_logprobs = ShmArray(self._name("logprobs"), (self.alloc_shm_numpy_len,), np.float32).link_shm()
 
     def release_shm_arrays(self, unlink: bool = False):
-        for a in ("shm_prompt_ids", "shm_logprobs", "shm_routed"):
+        for a in ("shm_prompt_ids", "shm_logprobs", "shm_routed", "shm_prompt_meta"):
             arr = getattr(self, a, None)
             if arr is not None:
                 arr.close_shm(unlink=unlink or None)

@@ -235,6 +235,8 @@ class HttpServerManager:
                     r.create_routed_shm_array(*self.routed_shape)
                 if self.args.enable_prompt_logprobs is False:
                     r.sample_params.prompt_logprobs = -1
+                elif r.sample_params.prompt_logprobs >= 0:
+                    r.create_prompt_meta_shm_array()
                 req_objs.append(r)
         except Exception:
             for r in req_objs:
@@ -310,6 +312,33 @@ class HttpServerManager:
                                   f"prompt_cache_len {metadata.get('prompt_cache_len', 0)}", flush=True)
                         return
 
+    def _prompt_logprobs_of(self, r) -> list:
+        """One entry per prompt position: None for the first, then {token id: {"logprob", "rank", "decoded_token"}}
+        with the prompt's own token (`prompt_logprobs` = 0) or the k most likely tokens and the prompt's own one
+        (`prompt_logprobs` = k).  Reference: lightllm/server/core/objs/token_metadata.py:100-157."""
+        tok = self.tokenizer
+
+        def info(tid, lp, rank):
+            try:
+                text = tok.decode([tid], skip_special_tokens=False)
+            except Exception:
+                text = None
+            return {"logprob": float(lp), "rank": rank, "decoded_token": text}
+
+        meta = getattr(r, "shm_prompt_meta", None)
+        k = (meta.arr.shape[1] - 1) // 2 if meta is not None else 0
+        out = [None]
+        for pos in range(1, r.input_len):
+            tid = int(r.shm_prompt_ids.arr[pos])
+            rank = int(meta.arr[pos, 0]) if meta is not None and meta.arr[pos, 0] > 0 else None
+            entry = {}
+            if k and rank is not None:
+                for j in range(k):
+                    entry[int(meta.arr[pos, 1 + j])] = info(int(meta.arr[pos, 1 + j]), meta.arr[pos, 1 + k + j], j + 1)
+            entry[tid] = info(tid, r.shm_logprobs.arr[pos], rank)
+            out.append(entry)
+        return out
+
     async def abort(self, group_req_id: int) -> bool:
         st = self.req_id_to_out_inf.get(group_req_id)
         if st is None:
@@ -362,6 +391,9 @@ class HttpServerManager:
                                 continue
                             if fs.is_finished():
                                 st.finished.add(r.request_id)
+                                if r.sample_params.prompt_logprobs >= 0:
+                                    metadata["prompt_token_ids"] = r.shm_prompt_ids.arr[: r.input_len].tolist()
+                                    metadata["prompt_logprobs"] = self._prompt_logprobs_of(r)
                                 if getattr(r, "shm_routed", None) is not None and r.routed_len > 0:
                                     from ...common.route_capture import encode
 

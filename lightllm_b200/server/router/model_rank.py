@@ -192,6 +192,8 @@ class ModelRankLoop:
                 r = self.shm_req_manager.get_req_obj_by_index(shm_index)
                 r.link_prompt_ids_shm_array(self.args.unique_server_name)
                 r.link_logprobs_shm_array(self.args.unique_server_name)
+                if r.sample_params.prompt_logprobs >= 0 and self.args.enable_prompt_logprobs:
+                    r.link_prompt_meta_shm_array(self.args.unique_server_name)
                 rc = self.model.route_capture
                 if rc is not None:
                     r.link_routed_shm_array(self.args.unique_server_name, rc.num_layers, rc.top_k, rc.np_dtype)
