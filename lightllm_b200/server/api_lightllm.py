@@ -43,7 +43,7 @@ async def lightllm_generate(request: Request, g) -> Response:
     prompt = body.pop("inputs")
     params = dict(body.pop("parameters", {}))
     return_details = params.pop("return_details", False)
-    prompt_lp = None
+    prompt_lp = input_usage = None
     return_routed = params.pop("return_routed_experts", bool(getattr(g.args, "enable_return_routed_experts", False)))
     routed = {}
     sp = _make_params(g, params)
@@ -61,6 +61,8 @@ async def lightllm_generate(request: Request, g) -> Response:
         prompt_tokens = meta.get("prompt_tokens", prompt_tokens)
         if "routed_experts" in meta:     # travels with the last token only; kept out of the per-token details
             routed[sub_id] = meta.pop("routed_experts")
+        if "input_usage" in meta:
+            input_usage = meta.pop("input_usage")
         if "prompt_logprobs" in meta:
             prompt_lp = (meta.pop("prompt_token_ids", None), meta.pop("prompt_logprobs"))
         if return_details:
@@ -79,6 +81,8 @@ async def lightllm_generate(request: Request, g) -> Response:
         ret["tokens"] = tokens[ids[0]] if len(ids) == 1 else [tokens[i] for i in ids]
     if prompt_lp is not None:
         ret["prompt_token_ids"], ret["prompt_logprobs"] = prompt_lp
+    if input_usage is not None:
+        ret["input_usage"] = input_usage
     if return_routed and routed:
         ret["routed_experts"] = routed.get(ids[0]) if len(ids) == 1 else [routed.get(i) for i in ids]
     return Response(content=json.dumps(ret, ensure_ascii=False).encode("utf-8"), media_type="application/json")

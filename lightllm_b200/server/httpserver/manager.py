@@ -259,6 +259,11 @@ class HttpServerManager:
                                                           status, request):
                 if first and pd_info is not None and self.args.run_mode == "prefill":
                     item[2]["prompt_ids"] = prompt_ids  # the pd_master hands them to the decode node
+                if first:     # only the first token's record says what the prompt was made of
+                    img = sum(int(i.token_num or 0) for i in mm.images) if mm is not None else 0
+                    aud = sum(int(a.token_num or 0) for a in mm.audios) if mm is not None else 0
+                    item[2]["input_usage"] = {"input_text_tokens": len(prompt_ids) - img - aud,
+                                              "input_audio_tokens": aud, "input_image_tokens": img}
                 first = False
                 yield item
         finally:

@@ -68,6 +68,7 @@ def test_generate_and_prefix_cache(server):
     body = {"inputs": list(range(5, 45)), "parameters": {"max_new_tokens": 8, "ignore_eos": True, "return_details": True}}
     r1 = requests.post(server + "/generate", json=body, timeout=60).json()
     assert r1["count_output_tokens"] == 8 and r1["finish_reason"] == "length" and r1["prompt_tokens"] == 40
+    assert r1["input_usage"] == {"input_text_tokens": 40, "input_audio_tokens": 0, "input_image_tokens": 0}
     assert len(r1["tokens"]) == 8 and all("logprob" in t for t in r1["tokens"])
     r2 = requests.post(server + "/generate", json=body, timeout=60).json()
     assert r2["generated_text"] == r1["generated_text"]        # greedy is deterministic
