@@ -445,7 +445,7 @@ class ModelBackend:
             return False
         for r in reqs:
             sp = r.sampling
-            if sp.has_penalty or sp.invalid_token_ids or sp.exp_decay_factor > 1.0 or \
+            if sp.has_penalty or sp.invalid_token_ids or sp.allowed_token_ids or sp.exp_decay_factor > 1.0 or \
                     (self.eos_ids and not sp.ignore_eos and r.cur_output_len + r.inflight + 1 < sp.min_new_tokens):
                 return False
         return True
@@ -530,7 +530,8 @@ class ModelBackend:
             return True
         for r in reqs:
             sp = r.sampling
-            if sp.top_k != 1 or sp.has_penalty or sp.invalid_token_ids or sp.exp_decay_factor > 1.0 or \
+            if sp.top_k != 1 or sp.has_penalty or sp.invalid_token_ids or sp.allowed_token_ids or \
+                    sp.exp_decay_factor > 1.0 or \
                     (self.eos_ids and not sp.ignore_eos and r.cur_output_len + r.inflight + 1 < sp.min_new_tokens):
                 return True
         return False
@@ -634,6 +635,13 @@ class ModelBackend:
                          and r.cur_output_len + 1 < r.sampling.min_new_tokens)
                         for r in reqs)
         need_decay = any(r.sampling.exp_decay_factor > 1.0 for r in reqs)
+        for i, r in enumerate(reqs):      # `allowed_token_ids`: everything else becomes impossible (rare: torch ops)
+            if r.sampling.allowed_token_ids:
+                ok = torch.tensor([t for t in r.sampling.allowed_token_ids if 0 <= t < logits.shape[1]],
+                                  dtype=torch.long, device=logits.device)
+                keep = logits[i, ok].clone()
+                logits[i].fill_(float("-inf"))
+                logits[i, ok] = keep
         if not (need_pen or need_mask or need_decay):
             return
         dev = self.device
