@@ -620,7 +620,7 @@ class ModelBackend:
             if self.is_master_in_dp and not r.retire_hold:
                 if r.cur_output_len == 1:
                     r.shm_req.first_token_time = now
-                if r.finish_status.is_finished() and self.model.route_capture is not None:
+                if r.finish_status.is_finished() and getattr(self.model, "route_capture", None) is not None:
                     self._dump_routed_experts(r)      # before the finish state becomes visible
                 r.publish()
             if self.on_token is not None:

@@ -88,7 +88,7 @@ class LLM:
         self._next_id += 8
         r.init(rid, ids, params, None, chunked_prefill_size=self.args.chunked_prefill_size,
                router_max_wait_tokens=self.args.router_max_wait_tokens, max_total_len=self.args.max_req_total_len)
-        rc = self.model.route_capture
+        rc = getattr(self.model, "route_capture", None)
         if rc is not None:
             r.create_routed_shm_array(rc.num_layers, rc.top_k, rc.np_dtype)
         return r

@@ -226,7 +226,7 @@ COMPAT_ONLY_FLAGS = (
     "pd_trans_mode",
     "config_server_visual_redis_port", "visual_use_proxy_mode", "visual_rpyc_port", "afs_image_embed_dir",
     "afs_embed_capacity", "vit_quant_type", "vit_quant_cfg", "visual_tp", "audio_tp", "audio_dp", "audio_gpu_ids",
-    "visual_send_batch_size", "linear_att_page_block_num",
+    "linear_att_page_block_num",
     "disable_linear_att_small_page_cpu_cache", "hypercorn_config", "enable_mps",
     "enable_torch_memory_saver", "enable_weight_cpu_backup")
 

@@ -194,7 +194,7 @@ class ModelRankLoop:
                 r.link_logprobs_shm_array(self.args.unique_server_name)
                 if r.sample_params.prompt_logprobs >= 0 and self.args.enable_prompt_logprobs:
                     r.link_prompt_meta_shm_array(self.args.unique_server_name)
-                rc = self.model.route_capture
+                rc = getattr(self.model, "route_capture", None)
                 if rc is not None:
                     r.link_routed_shm_array(self.args.unique_server_name, rc.num_layers, rc.top_k, rc.np_dtype)
                 r._mm_params = mm_params

@@ -97,12 +97,15 @@ def build_vision_tower(args, device, dtype=torch.bfloat16):
 
 
 class VisualManager:
-    def __init__(self, args: StartArgs, tower=None, cache=None, send_next=None, recv=None, infer_batch_size: int = 8):
+    def __init__(self, args: StartArgs, tower=None, cache=None, send_next=None, recv=None, infer_batch_size: int = 8,
+                 try_recv=None, send_batch_size: int = 1):
         self.args = args
         self.tower = tower
         self.cache = cache
         self.send_next = send_next
         self.recv = recv
+        self.try_recv = try_recv                  # non-blocking receive (None when nothing waits)
+        self.send_batch_size = max(1, int(send_batch_size or 1))   # `--visual_send_batch_size`
         self.infer_batch_size = infer_batch_size
         self.waiting: List[GroupReqIndexes] = []
 
@@ -133,17 +136,31 @@ class VisualManager:
             self.embed(pending)
         self.send_next(group)
 
+    def handle_many(self, msgs: list):
+        """Requests that arrived together share encoder passes: their missing pictures are embedded in batches of
+        `infer_batch_size` (one record once, however many requests carry it), then everything travels on in arrival
+        order (control commands keep their place)."""
+        try:
+            pending = []
+            for m in msgs:
+                if isinstance(m, GroupReqIndexes):
+                    pending += self._pending_images(m)
+            if pending:
+                self.embed(pending)
+        except Exception:
+            traceback.print_exc()       # the router fails a request whose embeddings never become ready
+        for m in msgs:
+            self.send_next(m)
+
     def loop(self):
         while True:
-            msg = self.recv()
-            try:
-                if isinstance(msg, GroupReqIndexes):
-                    self.handle(msg)
-                else:
-                    self.send_next(msg)  # control commands travel on to the router
-            except Exception:
-                traceback.print_exc()
-                self.send_next(msg)  # the router fails the request when its embeddings never become ready
+            msgs = [self.recv()]
+            while self.try_recv is not None and len(msgs) < self.send_batch_size:
+                m = self.try_recv()
+                if m is None:
+                    break
+                msgs.append(m)
+            self.handle_many(msgs)
 
 
 def start_visual_process(args_dict: dict, pipe_writer=None):
@@ -163,8 +180,15 @@ def start_visual_process(args_dict: dict, pipe_writer=None):
         nxt = args.audio_port if getattr(args, "enable_multimodal_audio", False) else args.router_port
         push.connect(zmq_addr(args, nxt))
         cache = EmbedCacheClient(args, hidden=tower.out_hidden, open_arena=True)
+        def try_recv():
+            try:
+                return pull.recv_pyobj(zmq.NOBLOCK)
+            except zmq.ZMQError:
+                return None
+
         mgr = VisualManager(args, tower, cache, lambda m: push.send_pyobj(m, protocol=pickle.HIGHEST_PROTOCOL),
-                            pull.recv_pyobj, infer_batch_size=args.visual_infer_batch_size or 8)
+                            pull.recv_pyobj, infer_batch_size=args.visual_infer_batch_size or 8, try_recv=try_recv,
+                            send_batch_size=getattr(args, "visual_send_batch_size", 1) or 1)
     except Exception:
         if pipe_writer is not None:
             pipe_writer.send(("init failed", traceback.format_exc()))

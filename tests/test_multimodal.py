@@ -121,6 +121,28 @@ def test_visual_manager_embeds_and_forwards():
         assert torch.equal(got, want)
         vm.handle(g)  # already embedded: forwarded without another tower pass (no payload left to read)
         assert len(sent) == 2
+        # requests that arrived together share encoder passes and travel on in arrival order, control messages too
+        raw2 = _png(56, 56, seed=5)
+        n2 = image_token_num(56, 56)[0]
+        rec2 = client.alloc(["m2"], [n2])[0]
+        client.set_items_data([rec2["id"]], [raw2])
+        t2, gh2, gw2 = image_token_num(56, 56)[1]
+        item2 = {"uuid": rec2["id"], "token_id": rec2["token_id"], "token_num": n2,
+                 "start_index_in_embed_cache": rec2["start_index_in_embed_cache"], "grid_thwd": (t2, gh2, gw2, 2)}
+        calls = []
+        real = tower.encode_images
+        tower.encode_images = lambda payloads, items=None: (calls.append(len(payloads)), real(payloads, items=items))[1]
+        ga = GroupReqIndexes(16, {"images": [item2], "audios": []}, [1], 0.0)
+        gb = GroupReqIndexes(24, {"images": [item2, item], "audios": []}, [2], 0.0)   # the same picture again
+        queue = [ga, "control", gb]
+        vm2 = VisualManager(args, tower, client, sent.append, lambda: queue.pop(0),
+                            try_recv=lambda: queue.pop(0) if queue else None, send_batch_size=8)
+        msgs = [vm2.recv()]
+        while (m := vm2.try_recv()) is not None:
+            msgs.append(m)
+        vm2.handle_many(msgs)
+        assert sent[2:] == [ga, "control", gb] and calls == [1]          # one pass, one new picture
+        assert client.get_items_embed([rec2["id"]]) == [True]
         client.arena.close()
         client.sock.close(0)
     finally:
