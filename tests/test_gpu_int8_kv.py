@@ -204,8 +204,8 @@ def test_llama_with_int4_pool_generates_on_the_device(dev):
     scale = la.abs().max().item()
     # every pass attends over the widened copy of the packed rows, its own new tokens included: 4-bit noise
     # (about 7 % per K / V element) on all rows, far from the error a layout mistake would give (the scale itself)
-    assert (la - lb).abs().max().item() < 0.3 * scale
-    assert (la - lb).abs().mean().item() < 0.05 * scale
+    assert (la - lb).abs().max().item() < 0.4 * scale
+    assert (la - lb).abs().mean().item() < 0.08 * scale
     prompts = [torch.randint(3, 1000, (n,), generator=g).tolist() for n in (200, 37, 300, 64)]
     sp = {"max_new_tokens": 12, "ignore_eos": True}
     b = llm.generate(prompts, sp)
