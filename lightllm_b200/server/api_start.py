@@ -167,6 +167,7 @@ def normal_or_p_d_start(args: StartArgs, config_override: dict = None):
         from .health_monitor.manager import start_health_check_process
 
         process_manager.start_submodule_processes([start_health_check_process], [(args.to_dict(),)])
+    _watch_children()
     try:
         run_http_server(args)
     finally:
@@ -179,10 +180,34 @@ def pd_master_start(args: StartArgs):
     from .metrics.manager import start_metric_manager
 
     process_manager.start_submodule_processes([start_metric_manager], [(args.to_dict(),)])
+    _watch_children()
     try:
         run_http_server(args)
     finally:
         process_manager.terminate_all()
+
+
+def _watch_children(interval_s: float = 1.0, grace_s: float = 15.0):
+    """The HTTP server occupies the launcher's main thread, so a daemon thread watches the other processes: when
+    one of them dies the server is no use any more (there is no in-process recovery of a lost rank), so the launcher
+    stops the HTTP server, tears the remaining processes down and exits non-zero; whatever supervises the deployment
+    restarts it.  Reference: lightllm/utils/start_utils.py:113-160."""
+    import signal
+    import threading
+
+    def watch():
+        while True:
+            time.sleep(interval_s)
+            dead = process_manager.any_dead()
+            if dead is None:
+                continue
+            print(f"[launcher] a server process died ({dead}): shutting everything down", flush=True)
+            process_manager.terminate_all()
+            os.kill(os.getpid(), signal.SIGTERM)      # lets the HTTP server close its sockets and workers
+            time.sleep(grace_s)
+            os._exit(1)
+
+    threading.Thread(target=watch, daemon=True, name="child-watch").start()
 
 
 def config_server_start(args: StartArgs):
