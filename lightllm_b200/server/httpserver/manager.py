@@ -365,9 +365,10 @@ class HttpServerManager:
         asyncio.create_task(self.recycle_resource_loop())
         while True:
             try:
-                await asyncio.wait_for(self.recv_from_detok.recv_pyobj(), timeout=0.05)
-            except asyncio.TimeoutError:
-                pass
+                # the detokenizer's messages are wake-ups only; polling first (instead of cancelling a pending
+                # receive after a timeout) never drops one in the middle of its delivery
+                if await self.recv_from_detok.poll(50):
+                    await self.recv_from_detok.recv_pyobj()
             except Exception:
                 await asyncio.sleep(0.01)
             try:
