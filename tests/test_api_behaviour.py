@@ -169,3 +169,22 @@ def test_validation_errors_are_400(server):
     assert _gen(server, [5, 6, 100000]).status_code == 400            # token id outside the vocabulary
     assert _gen(server, list(range(3, 3 + 400)) , max_new_tokens=8).status_code == 400     # longer than the limit
     assert requests.get(server + "/health", timeout=30).status_code == 200
+
+
+@pytest.mark.timeout(300)
+def test_length_repair_and_stop_sequences(server):
+    # prompt + max_new_tokens beyond the request limit: max_new_tokens is reduced silently, the request ends "length"
+    ids = list(range(10, 110))
+    r = _gen(server, ids, max_new_tokens=65535, ignore_eos=True).json()
+    assert r["finish_reason"] == "length" and r["prompt_tokens"] == 100 and 100 <= r["count_output_tokens"] <= 156
+    # stop sequences given as token ids end the request with "stop" and are matched inside the rank
+    base = [t["id"] for t in _gen(server, ids[:30], max_new_tokens=12, ignore_eos=True,
+                                  return_details=True).json()["tokens"]]
+    r = _gen(server, ids[:30], max_new_tokens=12, ignore_eos=True, return_details=True,
+             stop_sequences=[base[3:5]]).json()
+    got = [t["id"] for t in r["tokens"]]
+    assert r["finish_reason"] == "stop" and got == base[:5]
+    # min_new_tokens keeps a request going past a stop token sequence that comes too early
+    r = _gen(server, ids[:30], max_new_tokens=12, min_new_tokens=8, ignore_eos=True, return_details=True,
+             stop_sequences=[base[3:5]]).json()
+    assert r["count_output_tokens"] >= 8
