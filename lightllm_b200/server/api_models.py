@@ -78,6 +78,8 @@ class ChatCompletionRequest(BaseModel):
     role_settings: Optional[Dict[str, str]] = None
     character_settings: Optional[List[Dict[str, str]]] = None
     min_new_tokens: Optional[int] = 1
+    guided_regex: Optional[str] = None        # constrained decoding (needs --output_constraint_mode)
+    guided_grammar: Optional[str] = None
 
 
 class CompletionRequest(BaseModel):

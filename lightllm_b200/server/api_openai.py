@@ -43,6 +43,10 @@ def _sampling_dict(req, max_new: int, stop, n: int) -> dict:
             d["guided_json"] = rf.json_schema.schema_
         elif rf.type == "json_object":
             d["guided_grammar"] = "json"
+    if getattr(req, "guided_regex", None):
+        d["regular_constraint"] = req.guided_regex
+    elif getattr(req, "guided_grammar", None) and "guided_grammar" not in d and "guided_json" not in d:
+        d["guided_grammar"] = req.guided_grammar
     return d
 
 
