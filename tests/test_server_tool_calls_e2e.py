@@ -33,7 +33,8 @@ def server(tmp_path_factory):
     proc = subprocess.Popen([sys.executable, "-m", "lightllm_b200.server.api_server", "--model_dir", str(d), "--port",
                              str(port), "--data_type", "fp32", "--max_total_token_num", "4096",
                              "--running_max_req_size", "8", "--max_req_total_len", "512", "--tp", "1",
-                             "--output_constraint_mode", "xgrammar", "--tool_call_parser", "qwen25"],
+                             "--output_constraint_mode", "xgrammar", "--tool_call_parser", "qwen25",
+                             "--reasoning_parser", "qwen3"],
                             env=env, stdout=log, stderr=subprocess.STDOUT, cwd=ROOT, start_new_session=True)
     url = f"http://127.0.0.1:{port}"
     t0, up = time.time(), False
@@ -122,3 +123,32 @@ def test_anthropic_and_responses_tool_use(server):
         events = [l.decode() for l in r.iter_lines() if l.startswith(b"event:")]
     assert events[0] == "event: response.created" and events[-1] in ("event: response.completed",
                                                                        "event: response.incomplete")
+
+
+@pytest.mark.timeout(600)
+def test_reasoning_is_separated_and_streamed(server):
+    """`--reasoning_parser qwen3`: text between <think> and </think> comes back as reasoning_content (chat), as a
+    thinking block (Messages) and as a reasoning item (Responses); streamed chunks carry it in reasoning deltas."""
+    from lightllm_b200.server import api_anthropic as an
+    from lightllm_b200.server import api_responses as rs
+
+    regex = r"<think>\nthe user greets me\n</think>\n\nHello there!"
+    body = {"model": "m", "messages": [{"role": "user", "content": "hi"}], "max_tokens": 200, "guided_regex": regex}
+    resp = requests.post(server + "/v1/chat/completions", json=body, timeout=120).json()
+    msg = resp["choices"][0]["message"]
+    assert msg["reasoning_content"].strip() == "the user greets me" and msg["content"].strip() == "Hello there!"
+    assert resp["choices"][0]["finish_reason"] == "stop"
+    m = an.chat_response_to_message(resp, "m")
+    assert [b["type"] for b in m["content"]] == ["thinking", "text"] and m["stop_reason"] == "end_turn"
+    out = rs.chat_response_to_response(resp, {"model": "m", "input": "hi"})
+    assert [o["type"] for o in out["output"]] == ["reasoning", "message"]
+    body.update(stream=True, stream_reasoning=True)
+    reasoning, content = "", ""
+    with requests.post(server + "/v1/chat/completions", json=body, stream=True, timeout=120) as r:
+        for line in r.iter_lines():
+            if not line.startswith(b"data: ") or line == b"data: [DONE]":
+                continue
+            for choice in json.loads(line[6:])["choices"]:
+                reasoning += choice["delta"].get("reasoning_content") or ""
+                content += choice["delta"].get("content") or ""
+    assert reasoning.strip() == "the user greets me" and content.strip() == "Hello there!"
