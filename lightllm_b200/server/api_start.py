@@ -123,27 +123,33 @@ def start_core_processes(args: StartArgs, config_override: dict = None):
 
     d = args.to_dict()
     d = {k: v for k, v in d.items() if not k.startswith("_")}
-    process_manager.start_submodule_processes([start_metric_manager], [(d,)])
-    process_manager.start_submodule_processes([start_detokenization_process], [(d,)])
-    if args.enable_multimodal:  # the arena must exist before the ranks and the visual server open it
-        from ..models.base import load_config
+    # processes that do not depend on each other start (and import their libraries) side by side; the embedding
+    # arena must exist before the ranks and the visual server open it, so with multimodal input there are two stages
+    funcs, fargs = [start_metric_manager, start_detokenization_process], [(d,), (d,)]
+    if args.enable_multimodal:
+        from ..models.base import embed_row_width, load_config
         from .embed_cache.manager import start_cache_manager
 
-        from ..models.base import embed_row_width
-
         hidden = embed_row_width(config_override or load_config(args.model_dir))
-        process_manager.start_submodule_processes([start_cache_manager], [(d, hidden)])
-    process_manager.start_submodule_processes([start_router_process], [(d, config_override)])
+        funcs.append(start_cache_manager)
+        fargs.append((d, hidden))
+        process_manager.start_submodule_processes(funcs, fargs)
+        funcs, fargs = [], []
+    funcs.append(start_router_process)
+    fargs.append((d, config_override))
     if args.enable_multimodal:
         from .visualserver.manager import start_visual_process
 
         dv = dict(d)
         dv["_config_override"] = config_override
-        process_manager.start_submodule_processes([start_visual_process], [(dv,)])
+        funcs.append(start_visual_process)
+        fargs.append((dv,))
         if getattr(args, "enable_multimodal_audio", False):
             from .audioserver.manager import start_audio_process
 
-            process_manager.start_submodule_processes([start_audio_process], [(dv,)])
+            funcs.append(start_audio_process)
+            fargs.append((dv,))
+    process_manager.start_submodule_processes(funcs, fargs)
 
 
 def run_http_server(args: StartArgs):
