@@ -38,7 +38,8 @@ def server(tmp_path_factory):
     log = open(d / "server.log", "w")
     proc = subprocess.Popen([sys.executable, "-m", "lightllm_b200.server.api_server", "--model_dir", str(d), "--port",
                              str(port), "--data_type", "fp32", "--max_total_token_num", "4096",
-                             "--running_max_req_size", "16", "--max_req_total_len", "256", "--tp", "1", "--enable_rl"],
+                             "--running_max_req_size", "16", "--max_req_total_len", "256", "--tp", "1", "--enable_rl",
+                             "--enable_prompt_logprobs"],
                             env=env, stdout=log, stderr=subprocess.STDOUT, cwd=ROOT, start_new_session=True)
     url = f"http://127.0.0.1:{port}"
     t0, up = time.time(), False
@@ -188,3 +189,35 @@ def test_length_repair_and_stop_sequences(server):
     r = _gen(server, ids[:30], max_new_tokens=12, min_new_tokens=8, ignore_eos=True, return_details=True,
              stop_sequences=[base[3:5]]).json()
     assert r["count_output_tokens"] >= 8
+
+
+@pytest.mark.timeout(600)
+def test_prompt_logprobs(server):
+    """`--enable_prompt_logprobs`: `prompt_logprobs` = 0 returns every prompt token's logprob and rank, k > 0 also the
+    k most likely tokens per position (reference: lightllm/server/core/objs/token_metadata.py:100-157)."""
+    import math
+
+    ids = list(range(7, 37))
+    body = {"inputs": ids, "parameters": {"max_new_tokens": 3, "ignore_eos": True, "prompt_logprobs": 0}}
+    r0 = requests.post(server + "/generate", json=body, timeout=120).json()
+    assert r0["prompt_token_ids"] == ids and len(r0["prompt_logprobs"]) == 30 and r0["prompt_logprobs"][0] is None
+    own = []
+    for pos in range(1, 30):
+        entry = r0["prompt_logprobs"][pos]
+        assert list(entry) == [str(ids[pos])]
+        e = entry[str(ids[pos])]
+        assert e["logprob"] < 0 and 1 <= e["rank"] <= 512
+        own.append((e["logprob"], e["rank"]))
+    body["parameters"]["prompt_logprobs"] = 3
+    r3 = requests.post(server + "/generate", json=body, timeout=120).json()        # no prefix-cache shortcut
+    for pos in range(1, 30):
+        entry = r3["prompt_logprobs"][pos]
+        e = entry[str(ids[pos])]
+        assert abs(e["logprob"] - own[pos - 1][0]) < 1e-4 and e["rank"] == own[pos - 1][1]
+        top = sorted((v for v in entry.values() if v["rank"] <= 3), key=lambda v: v["rank"])
+        assert [v["rank"] for v in top][:3] == [1, 2, 3] and len(entry) in (3, 4)
+        assert top[0]["logprob"] >= top[1]["logprob"] >= top[2]["logprob"] >= e["logprob"] - 1e-6 or e["rank"] <= 3
+        assert math.exp(top[0]["logprob"]) <= 1.0
+    plain = requests.post(server + "/generate", json={"inputs": ids, "parameters": {"max_new_tokens": 3}},
+                          timeout=120).json()
+    assert "prompt_logprobs" not in plain
