@@ -85,14 +85,15 @@ class DPBackend(ModelBackend):
             if local_kind == "prefill":
                 n_tok = self._run_prefill(prefill)
             else:
-                self.model.forward(self._hold_input(True))
+                self._hold_pass(True)
                 self.stats["hold_prefill"] += 1
         elif any_decode:
             kind = "decode"
+            self._before_decode_round(int(votes[:, 1].max()))
             if local_kind == "decode":
                 n_tok = self._run_decode(decode, defer=defer)
             else:
-                self.model.forward(self._hold_input(False))
+                self._hold_pass(False)
                 self.stats["hold_decode"] += 1
         else:
             if self._pending is not None:
@@ -108,6 +109,14 @@ class DPBackend(ModelBackend):
         # requests whose last token is still in flight are in the table, so the (shared) votes cover them:
         # every rank leaves drain() on the same step
         return {"kind": kind, "finished": finished, "tokens": n_tok, "world_busy": bool((votes[:, 2] > 0).any())}
+
+    def _hold_pass(self, is_prefill: bool):
+        """What an idle replica runs while the others work: the same sequence of model passes (every MoE layer of
+        every pass is a collective), over the hold request."""
+        self.model.forward(self._hold_input(is_prefill))
+
+    def _before_decode_round(self, max_decode_reqs: int):
+        """Hook: every replica knows the largest decode batch of the round."""
 
     def drain(self):
         """Keep stepping (holding) until no rank has a live request: a rank that finished early must stay in the

@@ -23,6 +23,7 @@ import torch
 from .. import ops
 from ..common.infer_state import ModelInput
 from .backend import ModelBackend
+from .dp_backend import DPBackend
 from .infer_batch import InferReq
 
 
@@ -72,6 +73,9 @@ class MTPBackend(ModelBackend):
         for i, r in enumerate(reqs):
             r.extra["drafts"] = props[i].tolist()
 
+    def _propose_nothing(self):
+        """Hook for lock-step data parallelism: a step that has nothing to propose for (plain backend: no pass)."""
+
     # ------------------------------------------------------------------ prefill
     def _run_prefill(self, items) -> int:
         reqs = [r for r, _ in items]
@@ -107,7 +111,7 @@ class MTPBackend(ModelBackend):
         return int(has_out.sum())
 
     # ------------------------------------------------------------------ decode = verify + propose
-    def _run_decode(self, reqs: List[InferReq]) -> int:
+    def _run_decode(self, reqs: List[InferReq], defer: bool = False) -> int:
         k, B = self.k, len(reqs)
         q = k + 1
         base = np.array([r.cur_kv_len for r in reqs], dtype=np.int32)
@@ -177,6 +181,8 @@ class MTPBackend(ModelBackend):
             self.model.commit_verify(emitted)
         # next proposals from the accepted positions (requests that just finished need none)
         live = [i for i, r in enumerate(reqs) if not r.finish_status.is_finished()]
+        if not live:
+            self._propose_nothing()
         if live:
             rows = np.concatenate([np.arange(i * q, i * q + emitted[i]) for i in live])
             rows_t = torch.from_numpy(rows).to(self.device)
@@ -188,3 +194,33 @@ class MTPBackend(ModelBackend):
         self.stats["mtp_steps"] += 1
         self.stats["decode_tokens"] += int(emitted.sum())
         return int(emitted.sum())
+
+
+class DPMTPBackend(DPBackend, MTPBackend):
+    """Speculative decoding under lock-step data parallelism (`--dp` > 1 with `--mtp_mode`): every replica runs the
+    same sequence of model passes in a round (target pass, then `mtp_step` draft passes), whatever it has to do
+    itself, because every MoE layer of every pass is an exchange among all replicas: an idle replica, or one whose
+    requests all just finished, runs the passes over the hold request.  A decode round's target pass is the
+    prompt-shaped verification pass, so the bound of the expert exchange is (largest decode batch) x (mtp_step + 1).
+    Reference: lightllm/server/router/model_infer/mode_backend/dp_backend/impl.py (prefill_mtp / decode_mtp and
+    their padded variants)."""
+
+    def _hold_pass(self, is_prefill: bool):
+        mi = self._hold_input(True)           # verification passes are prompt-shaped too
+        mi.return_hidden = True
+        out = self.model.forward(mi)
+        self._hold_drafts(out.hidden)
+
+    def _hold_drafts(self, hidden):
+        h = hidden[-1:].contiguous() if hidden is not None else None
+        for j in range(self.k):
+            mod = self.drafts[min(j, len(self.drafts) - 1)]
+            mi = self._hold_input(True)
+            mi.draft_input_hidden, mi.return_hidden = h, True
+            h = mod.forward(mi).hidden
+
+    def _propose_nothing(self):
+        self._hold_drafts(torch.zeros((1, self.model.hidden), dtype=self.model.dtype, device=self.device))
+
+    def _before_decode_round(self, max_decode_reqs: int):
+        self.model.ep_prefill_tokens_bound = max(1, max_decode_reqs * (self.k + 1))

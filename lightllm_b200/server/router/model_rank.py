@@ -140,6 +140,8 @@ def _build_model_and_backend(args: StartArgs, ps):
         if isinstance(draft_dir, (list, tuple)):
             draft_dir = draft_dir[0] if draft_dir else None
         drafts = build_mtp_modules(model, _mtp_modules(args), model_dir=draft_dir or args.model_dir)
+        if ps.dp_size > 1:       # lock-step data parallelism: every replica runs the same passes per round
+            from ...engine.mtp_backend import DPMTPBackend as MTPBackend  # noqa: F811
         backend = MTPBackend(model, bargs, draft_models=drafts, mtp_step=args.mtp_step, is_master_in_dp=(ps.tp_rank == 0))
     else:
         backend = backend_cls(model, bargs, is_master_in_dp=(ps.tp_rank == 0), **kw)
