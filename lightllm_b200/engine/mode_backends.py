@@ -274,6 +274,13 @@ class DiverseBackend(ModelBackend):
         return res
 
 
+def decode_replica_of(master_req_id: int, decode_dp: int) -> int:
+    """The replica of a data-parallel decode node that serves a request: both sides compute it from the master's
+    request id (ids advance in steps of 8), the prefill side to address the KV, the decode side to place the
+    follow-up request."""
+    return (int(master_req_id) // 8) % max(1, int(decode_dp))
+
+
 class PDPrefillBackend(ModelBackend):
     """Prefill node of a disaggregated deployment: when a request's first token is sampled, its prompt KV is
     streamed to the paired decode rank (same tp rank) by a worker thread while the inference loop goes on with
@@ -303,7 +310,12 @@ class PDPrefillBackend(ModelBackend):
         ids = r.shm_req.shm_prompt_ids.arr[:n].tolist()
         r.retire_hold = True
         self._sending.append(r)
-        self.sender.submit((params["peer_ip"], params["peer_port"] + self.tp_rank), params["master_req_id"], ids,
+        # rank (replica j, tensor-parallel rank t) of the decode node listens on its port base + j * (ranks per
+        # replica) + t; P and D replicas have the same number of ranks
+        d_dp, d_tp = int(params.get("decode_dp", 1) or 1), int(params.get("decode_tp", 1) or 1)
+        per = max(1, d_tp // d_dp)
+        port = params["peer_port"] + decode_replica_of(params["master_req_id"], d_dp) * per + self.tp_rank
+        self.sender.submit((params["peer_ip"], port), params["master_req_id"], ids,
                            torch.from_numpy(np.ascontiguousarray(r.slots[:n])), (tok, lp), tag=r.req_id)
 
     def _settle_sends(self):
@@ -400,10 +412,34 @@ class PDDecodeBackend(ModelBackend):
                 self.on_kv_done(gid, ok)
 
 
+def _pd_dp_classes():
+    from .dp_backend import DPBackend
+
+    class PDDPPrefillBackend(DPBackend, PDPrefillBackend):
+        """Prefill node with data-parallel replicas (`--run_mode prefill --dp` > 1): the lock-step rounds of the
+        data-parallel backend, KV shipped to the decode replica that will serve the request.  One rank per replica
+        (the agreement among a replica's tensor-parallel ranks on settled transfers has no host group here).
+        Reference: mode_backend/pd/prefill_node_impl/prefill_impl_for_dp.py."""
+
+        def step(self) -> dict:
+            self._settle_sends()
+            return DPBackend.step(self)
+
+    class PDDPDecodeBackend(DPBackend, PDDecodeBackend):
+        """Decode node with data-parallel replicas: every rank lands the KV pages addressed to it between the
+        lock-step rounds.  Reference: mode_backend/pd/decode_node_impl/decode_impl_for_dp.py."""
+
+    return PDDPPrefillBackend, PDDPDecodeBackend
+
+
 def select_backend_class(args):
     if int(getattr(args, "dp", 1) or 1) > 1:
         from .dp_backend import DPBackend
 
+        mode = getattr(args, "run_mode", "normal")
+        if mode in ("prefill", "decode"):
+            assert int(args.tp) == int(args.dp), "P/D nodes with --dp > 1 run one rank per replica (--dp equal to --tp)"
+            return _pd_dp_classes()[0 if mode == "prefill" else 1]
         return DPBackend
     if getattr(args, "run_mode", "normal") == "prefill":
         return PDPrefillBackend

@@ -162,7 +162,7 @@ class PDKVTransParams(ctypes.Structure):
     _pack_ = 4
     _fields_ = [("prefill_node_id", NodeUUId), ("decode_node_id", NodeUUId), ("peer_ip", ctypes.c_ubyte * 64),
                 ("peer_ip_len", ctypes.c_int), ("peer_port", ctypes.c_int), ("master_req_id", ctypes.c_int64),
-                ("valid", ctypes.c_bool)]
+                ("valid", ctypes.c_bool), ("decode_dp", ctypes.c_int), ("decode_tp", ctypes.c_int)]
 
     def set(self, d: Optional[dict]):
         self.valid = bool(d)
@@ -175,13 +175,16 @@ class PDKVTransParams(ctypes.Structure):
         self.peer_ip_len = len(ip)
         self.peer_port = int(d.get("peer_port", 0))
         self.master_req_id = int(d.get("master_req_id", 0))
+        self.decode_dp = int(d.get("decode_dp", 1) or 1)      # replicas and ranks of the decode node: the KV of a
+        self.decode_tp = int(d.get("decode_tp", 1) or 1)      # request goes to the replica that will serve it
 
     def to_dict(self):
         if not self.valid:
             return None
         return {"prefill_node_id": self.prefill_node_id.get(), "decode_node_id": self.decode_node_id.get(),
                 "peer_ip": bytes(self.peer_ip[: self.peer_ip_len]).decode(), "peer_port": self.peer_port,
-                "master_req_id": self.master_req_id}
+                "master_req_id": self.master_req_id, "decode_dp": max(1, self.decode_dp),
+                "decode_tp": max(1, self.decode_tp)}
 
 
 class SamplingParams(ctypes.Structure):

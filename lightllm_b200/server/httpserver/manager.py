@@ -199,7 +199,9 @@ class HttpServerManager:
                 ip, port = pd_info["peer"]["kv_endpoint"]
                 sampling_params.pd_kv_trans_params.set({"peer_ip": ip, "peer_port": port,
                                                         "master_req_id": pd_info["group_req_id"],
-                                                        "decode_node_id": pd_info["peer"]["node_id"]})
+                                                        "decode_node_id": pd_info["peer"]["node_id"],
+                                                        "decode_dp": pd_info["peer"].get("dp", 1),
+                                                        "decode_tp": pd_info["peer"].get("tp", 1)})
         if request is not None and not is_health_req:   # correlate with the caller's own ids in the log
             hdr = getattr(request, "headers", None) or {}
             xid, sid = hdr.get("X-Request-Id", ""), hdr.get("X-Session-Id", "")

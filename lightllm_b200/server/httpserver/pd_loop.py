@@ -40,6 +40,11 @@ async def serve_request(g, req: PDRequest, send):
         sp = SamplingParams().init(tokenizer=mgr.tokenizer, **sp_kw)
         sp.pd_master_node_id.set(int(req.peer["node_id"]) if req.peer else 0)
         mode = g.args.run_mode
+        if mode == "decode" and int(getattr(g.args, "dp", 1) or 1) > 1:
+            # the prefill node sent the KV to this replica (engine/mode_backends.py: decode_replica_of)
+            from ...engine.mode_backends import decode_replica_of
+
+            sp.suggested_dp_index = decode_replica_of(req.group_req_id, int(g.args.dp))
         if mode == "prefill":
             sp.max_new_tokens = 1  # P emits exactly the first token; the sequence continues on D
         pd_info = {"group_req_id": req.group_req_id, "peer": req.peer, "first_token": req.first_token}

@@ -116,7 +116,8 @@ def _build_model_and_backend(args: StartArgs, ps):
     backend_cls = select_backend_class(args)
     kw = {}
     if args.run_mode == "prefill":
-        kw = dict(tp_rank=ps.tp_rank, page_tokens=args.pd_kv_page_size, cpu_group=ps.cpu_group, tp_size=ps.tp_size)
+        kw = dict(tp_rank=ps.tp_rank, page_tokens=args.pd_kv_page_size,
+                  cpu_group=ps.cpu_group if ps.dp_size == 1 else None, tp_size=ps.tp_size)
     elif args.run_mode == "decode":
         on_done = None
         if ps.tp_rank == 0 and args.pd_kv_status_port:
@@ -125,9 +126,11 @@ def _build_model_and_backend(args: StartArgs, ps):
             sock = zmq.Context.instance().socket(zmq.PUSH)
             sock.connect(f"tcp://127.0.0.1:{args.pd_kv_status_port}")
             on_done = lambda gid, ok: sock.send_pyobj((gid, ok))  # noqa: E731
-        kw = dict(tp_rank=ps.tp_rank, host=args.host if args.host not in ("localhost",) else "127.0.0.1",
+        # a rank receives KV pages on pd_kv_port + its global rank (replica j, tensor-parallel rank t: j * tp + t)
+        kw = dict(tp_rank=ps.global_rank if ps.dp_size > 1 else ps.tp_rank,
+                  host=args.host if args.host not in ("localhost",) else "127.0.0.1",
                   kv_port=args.pd_kv_port, page_tokens=args.pd_kv_page_size, page_num=args.pd_kv_page_num,
-                  cpu_group=ps.cpu_group, tp_size=ps.tp_size, on_kv_done=on_done)
+                  cpu_group=ps.cpu_group if ps.dp_size == 1 else None, tp_size=ps.tp_size, on_kv_done=on_done)
     elif backend_cls.__name__ in ("TokenHealingBackend", "XgrammarBackend", "OutlinesConstraintBackend"):
         from ..tokenizer import get_tokenizer
 
