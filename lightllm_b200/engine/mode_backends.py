@@ -302,13 +302,20 @@ class PDPrefillBackend(ModelBackend):
         self._sending = []      # [(InferReq, token, logprob)] in submission order (the same on every rank)
         self._outcome = {}      # req_id -> (ok, message) as seen by this rank's worker
 
-    def _ship(self, r: InferReq, tok: int, lp: float):
+    def _wants_ship(self, r: InferReq):
         params = r.shm_req.sample_params.pd_kv_trans_params.to_dict()
-        if not params or r.cur_output_len != 1:
+        return params if (params and r.cur_output_len == 1) else None
+
+    def _ship(self, r: InferReq, tok: int, lp: float):
+        params = self._wants_ship(r)
+        if params is None:
             return
+        r.retire_hold = True
+        self._submit(r, params, tok, lp)
+
+    def _submit(self, r: InferReq, params: dict, tok: int, lp: float):
         n = r.cur_kv_len
         ids = r.shm_req.shm_prompt_ids.arr[:n].tolist()
-        r.retire_hold = True
         self._sending.append(r)
         # rank (replica j, tensor-parallel rank t) of the decode node listens on its port base + j * (ranks per
         # replica) + t; P and D replicas have the same number of ranks
@@ -430,6 +437,39 @@ def _pd_dp_classes():
         lock-step rounds.  Reference: mode_backend/pd/decode_node_impl/decode_impl_for_dp.py."""
 
     return PDDPPrefillBackend, PDDPDecodeBackend
+
+
+def pd_mtp_classes():
+    """P/D node backends with speculative decoding (`--mtp_mode` on a prefill / decode node).  The KV pool carries
+    the draft modules' layers, so the prefill node runs the draft pass over the prompt before it ships the pages
+    (the hook only marks the request at sampling time, the transfer is submitted after the draft pass), and the
+    decode node verifies and proposes as the plain speculative backend does.
+    Reference: mode_backend/chunked_prefill/impl.py:244-446 run by the pd backends."""
+    from .mtp_backend import MTPBackend
+
+    class PDPrefillMTPBackend(PDPrefillBackend, MTPBackend):
+        def __init__(self, *a, **kw):
+            super().__init__(*a, **kw)
+            self._ship_after_drafts = []
+            self.extra_post_req_handle_func = self._mark_for_shipping
+
+        def _mark_for_shipping(self, r: InferReq, tok: int, lp: float):
+            params = self._wants_ship(r)
+            if params is not None:
+                r.retire_hold = True
+                self._ship_after_drafts.append((r, params, tok, lp))
+
+        def _run_prefill(self, items) -> int:
+            n = MTPBackend._run_prefill(self, items)
+            marked, self._ship_after_drafts = self._ship_after_drafts, []
+            for r, params, tok, lp in marked:
+                self._submit(r, params, tok, lp)
+            return n
+
+    class PDDecodeMTPBackend(PDDecodeBackend, MTPBackend):
+        pass
+
+    return PDPrefillMTPBackend, PDDecodeMTPBackend
 
 
 def select_backend_class(args):

@@ -143,9 +143,18 @@ def _build_model_and_backend(args: StartArgs, ps):
         if isinstance(draft_dir, (list, tuple)):
             draft_dir = draft_dir[0] if draft_dir else None
         drafts = build_mtp_modules(model, _mtp_modules(args), model_dir=draft_dir or args.model_dir)
+        mkw = {}
         if ps.dp_size > 1:       # lock-step data parallelism: every replica runs the same passes per round
+            assert args.run_mode not in ("prefill", "decode"), \
+                "speculative decoding on P/D nodes with --dp > 1 is not supported"
             from ...engine.mtp_backend import DPMTPBackend as MTPBackend  # noqa: F811
-        backend = MTPBackend(model, bargs, draft_models=drafts, mtp_step=args.mtp_step, is_master_in_dp=(ps.tp_rank == 0))
+        elif args.run_mode in ("prefill", "decode"):
+            from ...engine.mode_backends import pd_mtp_classes
+
+            MTPBackend = pd_mtp_classes()[0 if args.run_mode == "prefill" else 1]  # noqa: F811
+            mkw = kw
+        backend = MTPBackend(model, bargs, draft_models=drafts, mtp_step=args.mtp_step,
+                             is_master_in_dp=(ps.tp_rank == 0), **mkw)
     else:
         backend = backend_cls(model, bargs, is_master_in_dp=(ps.tp_rank == 0), **kw)
     if getattr(args, "enable_multimodal", False):
