@@ -198,18 +198,22 @@ FLAGS = [
 ]
 
 
+ALIASES = {"--performance_mode": ["--p_mode"]}     # short spellings the reference accepts
+
+
 def add_cli_args(parser: argparse.ArgumentParser) -> argparse.ArgumentParser:
     for spec in FLAGS:
         name, kind, default, help_ = spec[:4]
         extra = dict(spec[4]) if len(spec) > 4 else {}
+        names = [name] + ALIASES.get(name, [])
         if kind == "flag":
-            parser.add_argument(name, action="store_true", default=default, help=help_)
+            parser.add_argument(*names, action="store_true", default=default, help=help_)
         elif kind == "append":
-            parser.add_argument(name, action="append", default=default, help=help_)
+            parser.add_argument(*names, action="append", default=default, help=help_)
         elif isinstance(kind, tuple):
-            parser.add_argument(name, type=kind[1], nargs="+", default=default, help=help_, **extra)
+            parser.add_argument(*names, type=kind[1], nargs="+", default=default, help=help_, **extra)
         else:
-            parser.add_argument(name, type=kind, default=default, help=help_, **extra)
+            parser.add_argument(*names, type=kind, default=default, help=help_, **extra)
     return parser
 
 
