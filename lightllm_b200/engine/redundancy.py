@@ -88,9 +88,11 @@ class RedundancyExpertManager:
                  out_path: str = "./redundancy_expert_config.json"):
         self.model = model
         self.layers = [lw for lw in model.layers if getattr(lw, "ep_table", None) is not None]
-        env = os.environ.get
-        self.interval = float(env("LLB_REDUNDANCY_EXPERT_UPDATE_INTERVAL", 30 * 60)) if interval_s is None else interval_s
-        self.max_updates = int(env("LLB_REDUNDANCY_EXPERT_UPDATE_MAX_LOAD_COUNT", 1)) if max_updates is None \
+        def env(name, default):      # the reference's spelling of the variable is honoured too
+            return os.environ.get("LLB_" + name, os.environ.get("LIGHTLLM_" + name, default))
+
+        self.interval = float(env("REDUNDANCY_EXPERT_UPDATE_INTERVAL", 30 * 60)) if interval_s is None else interval_s
+        self.max_updates = int(env("REDUNDANCY_EXPERT_UPDATE_MAX_LOAD_COUNT", 1)) if max_updates is None \
             else max_updates
         self.updates = 0
         self.state = self.CHECK

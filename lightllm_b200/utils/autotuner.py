@@ -29,7 +29,7 @@ PKG_DIR = Path(__file__).resolve().parent.parent / "kernel_configs"
 
 def autotune_level() -> int:
     try:
-        return int(os.environ.get("LLB_AUTOTUNE_LEVEL", "0"))
+        return int(os.environ.get("LLB_AUTOTUNE_LEVEL", os.environ.get("LIGHTLLM_TRITON_AUTOTUNE_LEVEL", "0")))
     except ValueError:
         return 0
 
