@@ -170,6 +170,39 @@ async def chat_completions_impl(request: ChatCompletionRequest, raw_request: Req
     return await stream_response(stream(), g)
 
 
+def _completion_logprobs(tokenizer, out_tokens, out_lps, prompt_ids, prompt_lp, drop_output: bool):
+    """`logprobs` of a completion choice: with echo the prompt's tokens first (logprob None for the first one), each
+    with its own logprob and, when the engine computed them, the most likely tokens at that position."""
+    tokens, token_lps, tops, offsets = [], [], [], []
+    off = 0
+
+    def push(text, lp, top):
+        nonlocal off
+        tokens.append(text)
+        token_lps.append(lp)
+        tops.append(top)
+        offsets.append(off)
+        off += len(text)
+
+    if prompt_ids is not None:
+        for pos, tid in enumerate(prompt_ids):
+            try:
+                text = tokenizer.decode([tid], skip_special_tokens=False)
+            except Exception:
+                text = f"<{tid}>"
+            entry = prompt_lp[pos] if (prompt_lp is not None and pos < len(prompt_lp)) else None
+            if not entry:
+                push(text, None, None)
+                continue
+            own = entry.get(tid) or entry.get(str(tid)) or {}
+            top = {(v.get("decoded_token") or str(k)): v["logprob"] for k, v in entry.items()}
+            push(text, own.get("logprob"), top)
+    if not drop_output:
+        for text, lp in zip(out_tokens, out_lps):
+            push(text, lp, {text: lp} if lp is not None else None)
+    return CompletionLogprobs(tokens=tokens, token_logprobs=token_lps, top_logprobs=tops, text_offset=offsets)
+
+
 async def completions_impl(request: CompletionRequest, raw_request: Request, g) -> Response:
     if request.logit_bias is not None:
         return create_error_response(400, "The logit_bias parameter is not currently supported")
@@ -184,10 +217,17 @@ async def completions_impl(request: CompletionRequest, raw_request: Request, g) 
     req_id = f"cmpl-{uuid.uuid4().hex}"
     mgr = g.httpserver_manager
 
+    # echo + logprobs: the prompt's own token logprobs come back too (what evaluation harnesses score continuations
+    # with); needs --enable_prompt_logprobs, otherwise the prompt tokens are echoed without logprobs
+    want_prompt_lp = bool(request.echo and request.logprobs is not None and
+                          getattr(g.args, "enable_prompt_logprobs", False) and not request.stream)
+
     def make_sp():
         sp = SamplingParams()
         d = _sampling_dict(request, max(max_new, 1), request.stop, n)
         d["add_special_tokens"] = True
+        if want_prompt_lp:
+            d["prompt_logprobs"] = max(0, min(int(request.logprobs), 20))
         sp.init(tokenizer=mgr.tokenizer, **d)
         sp.verify(g.args.vocab_size)
         return sp
@@ -223,7 +263,10 @@ async def completions_impl(request: CompletionRequest, raw_request: Request, g) 
         lps: Dict[int, list] = {}
         finish: Dict[int, str] = {}
         ptoks = 0
+        prompt_lp = prompt_ids = None
         async for sub_id, text, meta, fs in mgr.generate(prompt, make_sp(), None, raw_request):
+            if "prompt_logprobs" in meta:
+                prompt_lp, prompt_ids = meta.pop("prompt_logprobs"), meta.pop("prompt_token_ids", None)
             texts.setdefault(sub_id, []).append(text)
             lps.setdefault(sub_id, []).append(meta.get("logprob"))
             ptoks = meta.get("prompt_tokens", ptoks)
@@ -238,8 +281,14 @@ async def completions_impl(request: CompletionRequest, raw_request: Request, g) 
                 body = prompt + body
             lp = None
             if request.logprobs is not None:
-                lp = CompletionLogprobs(tokens=texts[sid], token_logprobs=lps[sid], top_logprobs=[None] * len(texts[sid]),
-                                        text_offset=[])
+                lp = _completion_logprobs(mgr.tokenizer, texts[sid], lps[sid], prompt_ids if request.echo else None,
+                                          prompt_lp, request.max_tokens == 0)
+                if request.echo and prompt_ids is not None and not isinstance(prompt, str):
+                    body = "".join(lp.tokens[: len(prompt_ids)]) + body
+            if request.max_tokens == 0:       # scoring only: nothing of the one token the engine produced is shown
+                total_out -= len(texts[sid])
+                body = prompt if (request.echo and isinstance(prompt, str)) else \
+                    ("".join(lp.tokens) if (lp is not None and request.echo) else "")
             choices.append(CompletionChoice(text=body, index=len(choices), logprobs=lp, finish_reason=finish.get(sid)))
     resp = CompletionResponse(id=req_id, created=created, model=request.model, choices=choices,
                               usage=_usage(total_prompt, total_out, cached))

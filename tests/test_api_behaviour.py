@@ -221,3 +221,24 @@ def test_prompt_logprobs(server):
     plain = requests.post(server + "/generate", json={"inputs": ids, "parameters": {"max_new_tokens": 3}},
                           timeout=120).json()
     assert "prompt_logprobs" not in plain
+
+
+@pytest.mark.timeout(300)
+def test_completions_echo_with_logprobs_scores_the_prompt(server):
+    """/v1/completions with echo + logprobs (+ max_tokens 0): the way evaluation harnesses score a continuation."""
+    ids = list(range(7, 37))
+    want = _gen(server, ids, max_new_tokens=1, prompt_logprobs=0).json()["prompt_logprobs"]
+    body = {"model": "m", "prompt": ids, "echo": True, "logprobs": 2, "max_tokens": 0}
+    c = requests.post(server + "/v1/completions", json=body, timeout=120).json()
+    lp = c["choices"][0]["logprobs"]
+    assert len(lp["tokens"]) == 30 and lp["token_logprobs"][0] is None and lp["top_logprobs"][0] is None
+    for pos in range(1, 30):
+        assert abs(lp["token_logprobs"][pos] - want[pos][str(ids[pos])]["logprob"]) < 1e-4
+        assert 2 <= len(lp["top_logprobs"][pos]) <= 3
+    assert lp["text_offset"] == [sum(len(t) for t in lp["tokens"][:i]) for i in range(30)]
+    assert c["usage"]["completion_tokens"] == 0 and c["choices"][0]["text"] == "".join(lp["tokens"])
+    # with output: the generated tokens follow the prompt's
+    body.update(max_tokens=3, ignore_eos=True)
+    c = requests.post(server + "/v1/completions", json=body, timeout=120).json()
+    lp = c["choices"][0]["logprobs"]
+    assert len(lp["tokens"]) == 33 and all(x is not None for x in lp["token_logprobs"][1:])
