@@ -6,6 +6,7 @@ lightllm/utils/shm_utils.py.
 """
 from __future__ import annotations
 
+import os
 from multiprocessing import shared_memory
 from typing import Optional
 
@@ -14,22 +15,48 @@ import numpy as np
 from ....utils.shm_cleanup import get_cleanup, register_posix_shm_for_cleanup
 
 
-def create_or_link_shm(name: str, size: int, force_create: bool = False):
-    """Returns (SharedMemory, created)."""
+def create_or_link_shm(name: str, size: int, force_create: bool = False, settle_s: float = 2.0):
+    """Returns (SharedMemory, created).  Several processes of a server start side by side and may reach the same
+    segment at the same moment: the one that loses the creation race waits until the winner has given the segment
+    its size (a freshly created segment is empty for an instant) instead of judging it too small.  A segment that
+    stays too small (left over from an earlier server with other limits) is replaced."""
+    import time
+
     try:
         shm = shared_memory.SharedMemory(name=name, create=True, size=size)
         return shm, True
     except FileExistsError:
-        shm = shared_memory.SharedMemory(name=name, create=False)
-        if shm.size < size or force_create:
+        t0 = time.time()
+        while True:
+            try:
+                shm = shared_memory.SharedMemory(name=name, create=False)
+            except FileNotFoundError:
+                return create_or_link_shm(name, size, force_create, settle_s)    # it went away meanwhile: start over
+            except ValueError:
+                shm = None                        # still empty: cannot be mapped yet
+            if shm is not None and shm.size >= size and not force_create:
+                return shm, False
+            if force_create or time.time() - t0 > settle_s:
+                break
+            if shm is not None:
+                shm.close()
+            time.sleep(0.01)
+        if shm is not None:
             shm.close()
             try:
                 shm.unlink()
             except FileNotFoundError:
                 pass
-            shm = shared_memory.SharedMemory(name=name, create=True, size=size)
-            return shm, True
-        return shm, False
+        else:
+            try:
+                shared_memory.SharedMemory(name=name, create=False).unlink()
+            except (FileNotFoundError, ValueError):
+                try:
+                    os.unlink("/dev/shm/" + name.lstrip("/"))
+                except OSError:
+                    pass
+        shm = shared_memory.SharedMemory(name=name, create=True, size=size)
+        return shm, True
 
 
 def _untrack(shm):

@@ -250,3 +250,42 @@ def test_mailbox_every_reader_sees_every_message_once():
         box.write_obj(b"x" * (2 << 20))       # larger than the buffer: refused, not truncated
     box.shm.close()
     box.shm.unlink()
+
+
+def _racer(i, name, n_rounds, barrier, out):
+    from lightllm_b200.server.core.objs.shm_array import create_or_link_shm
+
+    bad = 0
+    for r in range(n_rounds):
+        barrier.wait()
+        shm, created = create_or_link_shm(f"{name}_{r}", 4096)
+        shm.buf[i] = i + 1
+        barrier.wait()
+        if bytes(shm.buf[:4]) != bytes([1, 2, 3, 4]):      # everybody landed in the same segment
+            bad += 1
+        barrier.wait()
+        shm.close()
+        if created:
+            try:
+                shm.unlink()
+            except FileNotFoundError:
+                pass
+    out.put((i, bad))
+
+
+def test_processes_that_start_together_share_one_segment():
+    """Processes of a server start side by side: whoever loses the creation race must wait for the winner to size
+    the segment, not replace it (a freshly created POSIX segment is empty for an instant)."""
+    import multiprocessing as mp
+    import os
+
+    ctx = mp.get_context("spawn")
+    barrier, out = ctx.Barrier(4), ctx.Queue()
+    name = f"llb_race_{os.getpid()}"
+    ps = [ctx.Process(target=_racer, args=(i, name, 40, barrier, out)) for i in range(4)]
+    for p in ps:
+        p.start()
+    res = sorted(out.get(timeout=120) for _ in ps)
+    for p in ps:
+        p.join(timeout=30)
+    assert res == [(0, 0), (1, 0), (2, 0), (3, 0)]
