@@ -407,6 +407,18 @@ class HttpServerManager:
 
                                     metadata["routed_experts"] = encode(r.shm_routed.arr[:r.routed_len].copy())
                             pulled.append((r.request_id, text, metadata, fs))
+                        # an aborted request is dropped by the detokenizer at once, so its last token may never
+                        # arrive: once the detokenizer has let go of it and nothing is queued, the stream is ended
+                        # here (a client may still be listening, e.g. after /abort_request)
+                        if r.is_aborted and r.can_released_mark and q.is_empty() and r.request_id not in st.finished:
+                            st.finished.add(r.request_id)
+                            pulled.append((r.request_id, "", {"id": -1, "logprob": 0.0, "cumlogprob": float(r.cumlogprob),
+                                                              "special": True, "count_output_tokens": r.shm_cur_output_len,
+                                                              "prompt_cache_len": r.prompt_cache_len,
+                                                              "cpu_prompt_cache_len": r.cpu_prompt_cache_len,
+                                                              "disk_prompt_cache_len": r.disk_prompt_cache_len,
+                                                              "mtp_accepted_token_num": r.mtp_accepted_token_num},
+                                           FinishStatus(FinishStatus.FINISHED_ABORTED)))
                     if pulled:
                         async with st.lock:
                             st.out_token_info_list.extend(pulled)
@@ -420,7 +432,8 @@ class HttpServerManager:
         while True:
             await asyncio.sleep(0.02)
             for gid, st in list(self.req_id_to_out_inf.items()):
-                if st.can_release():
+                # only after every sub-request's final item has been handed to its stream
+                if st.can_release() and all(r.request_id in st.finished for r in st.req_objs):
                     del self.req_id_to_out_inf[gid]
                     for r in st.req_objs:
                         r.release_shm_arrays(unlink=True)

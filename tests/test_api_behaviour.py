@@ -90,14 +90,19 @@ def test_abort_chaos_leaves_nothing_behind(server):
         except Exception as e:                     # an aborted stream may end abruptly; the server must survive
             results.append((i, got, repr(e)))
 
-    threads = [threading.Thread(target=client, args=(i,)) for i in range(12)]
-    for t in threads:
-        t.start()
-    time.sleep(1.0)
-    assert requests.post(server + "/abort_request", json={"abort_all": True}, timeout=30).json()["success"]
-    for t in threads:
-        t.join(timeout=180)
-    assert len(results) == 12
+    for delay in (1.0, 0.05, 0.3):          # late, while the requests are still being admitted, in mid-generation
+        results.clear()
+        threads = [threading.Thread(target=client, args=(i,)) for i in range(12)]
+        t0 = time.time()
+        for t in threads:
+            t.start()
+        time.sleep(delay)
+        assert requests.post(server + "/abort_request", json={"abort_all": True}, timeout=30).json()["success"]
+        for t in threads:
+            t.join(timeout=180)
+        # a client that keeps listening gets the end of its stream promptly, whatever stage the abort caught
+        assert len(results) == 12 and time.time() - t0 < 60, results
+        assert not [r for r in results if isinstance(r[2], str)], results
     # everything drains: no running request, the whole pool free again (prefix-cache entries count as free)
     deadline = time.time() + 60
     while time.time() < deadline:
