@@ -299,6 +299,9 @@ def model_rank_main(args_dict: dict, rank: int, pipe, config_override: Optional[
         node_world = args.tp // args.nnodes
         local_rank = rank % node_world
         device = torch.device("cuda", local_rank) if use_cuda else torch.device("cpu")
+        if not use_cuda and node_world > 1:
+            # CPU ranks of one host share its cores: without a limit every rank's math library spins on all of them
+            torch.set_num_threads(max(1, (os.cpu_count() or 2) // node_world))
         ps = pdist.init_distributed(args.tp, rank, dp=args.dp, nnodes=args.nnodes, node_rank=args.node_rank,
                                     host=args.nccl_host, port=args.nccl_port, device=device,
                                     config_server=(args.config_server_host, args.config_server_port)
