@@ -52,6 +52,14 @@ def _mtp_modules(args) -> int:
     return 1 if str(args.mtp_mode).startswith("eagle") else max(1, int(args.mtp_step))
 
 
+def _publishes(args, ps) -> bool:
+    """The rank of a replica that writes tokens and finish states into its node's shared request objects: the
+    replica's first rank, and, when a tensor-parallel replica spans nodes, its first rank on every node (each node has
+    its own request objects, HTTP server and detokenizer)."""
+    per_node = max(1, args.tp // args.nnodes)
+    return ps.tp_rank % min(ps.tp_size, per_node) == 0
+
+
 def _build_model_and_backend(args: StartArgs, ps):
     from ...engine.backend import BackendArgs, ModelBackend
     from ...models.base import load_config
@@ -154,9 +162,9 @@ def _build_model_and_backend(args: StartArgs, ps):
             MTPBackend = pd_mtp_classes()[0 if args.run_mode == "prefill" else 1]  # noqa: F811
             mkw = kw
         backend = MTPBackend(model, bargs, draft_models=drafts, mtp_step=args.mtp_step,
-                             is_master_in_dp=(ps.tp_rank == 0), **mkw)
+                             is_master_in_dp=_publishes(args, ps), **mkw)
     else:
-        backend = backend_cls(model, bargs, is_master_in_dp=(ps.tp_rank == 0), **kw)
+        backend = backend_cls(model, bargs, is_master_in_dp=_publishes(args, ps), **kw)
     if getattr(args, "enable_multimodal", False):
         from ..embed_cache.cache import EmbedArena
         from ..embed_cache.manager import arena_name, arena_rows
@@ -299,9 +307,10 @@ def model_rank_main(args_dict: dict, rank: int, pipe, config_override: Optional[
         node_world = args.tp // args.nnodes
         local_rank = rank % node_world
         device = torch.device("cuda", local_rank) if use_cuda else torch.device("cpu")
-        if not use_cuda and node_world > 1:
-            # CPU ranks of one host share its cores: without a limit every rank's math library spins on all of them
-            torch.set_num_threads(max(1, (os.cpu_count() or 2) // node_world))
+        if not use_cuda and args.tp > 1:
+            # CPU ranks (tests: also the "nodes") of one host share its cores: without a limit every rank's math
+            # library spins on all of them
+            torch.set_num_threads(max(1, (os.cpu_count() or 2) // args.tp))
         ps = pdist.init_distributed(args.tp, rank, dp=args.dp, nnodes=args.nnodes, node_rank=args.node_rank,
                                     host=args.nccl_host, port=args.nccl_port, device=device,
                                     config_server=(args.config_server_host, args.config_server_port)

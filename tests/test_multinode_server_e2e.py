@@ -107,6 +107,12 @@ def test_two_nodes_on_one_host(tmp_path):
                         break
         time.sleep(2)
         assert _ask(url) == want                          # still in lock-step (prefix-cache hits on both nodes)
+        # more requests than request slots (8): finished requests are recycled on BOTH nodes (every node's first
+        # rank publishes tokens and finish states into its own node's request objects)
+        for i in range(12):
+            r = requests.post(url + "/generate", json={"inputs": list(range(5 + i, 30 + i)), "parameters":
+                                                       {"max_new_tokens": 3, "ignore_eos": True}}, timeout=60)
+            assert r.status_code == 200 and r.json()["count_output_tokens"] == 3, (i, r.text[:200])
         assert all(p.poll() is None for p in nodes)
     finally:
         for p in nodes:
