@@ -1,5 +1,6 @@
 """A busy pd_master answers a streaming request with HTTP 429 instead of a 200 whose body breaks: the event
-generator is primed before the response starts (server/api_stream_obj.py).  Other run modes start at once."""
+generator is primed before the response starts (server/api_stream_obj.py).  Other run modes wait for the first chunk
+for a short while only (an early refusal still becomes a status code, a slow first token does not hold the headers)."""
 import asyncio
 from types import SimpleNamespace
 
@@ -45,14 +46,44 @@ def test_pd_master_stream_is_complete_and_unduplicated():
     assert r.headers["content-type"].startswith("text/event-stream")
 
 
-def test_other_modes_start_the_response_at_once():
-    # the generator has not run when the response object is built: its refusal can no longer change the status
-    c = _app("normal", fail_at=0)
-    try:
-        r = c.get("/s")
-        assert r.status_code == 200
-    except Exception:
-        pass          # depending on the transport the broken body surfaces as a client-side error: still not a 429
+def test_other_modes_turn_an_early_refusal_into_a_status_code_too():
+    # admission is refused within about two seconds (no free request slot): the first chunk is awaited that long
+    r = _app("normal", fail_at=0).get("/s")
+    assert r.status_code == 429
+    r = _app("normal", fail_at=-1).get("/s")
+    assert r.status_code == 200 and r.text == "data:0\\n\\ndata:1\\n\\ndata:2\\n\\n"
+
+
+def test_other_modes_do_not_wait_long_for_a_slow_first_chunk(monkeypatch):
+    import time
+
+    from lightllm_b200.server import api_stream_obj as so
+
+    monkeypatch.setattr(so, "EARLY_S", 0.1)
+    built = {}
+
+    async def slow():
+        await asyncio.sleep(0.6)             # a long prompt: the first token takes longer than the waiting window
+        yield b"a"
+        yield b"b"
+
+    async def run():
+        t0 = time.time()
+        resp = await so.stream_response(slow(), SimpleNamespace(args=SimpleNamespace(run_mode="normal")))
+        built["after"] = time.time() - t0
+        return b"".join([c async for c in resp.body_iterator])
+
+    assert asyncio.run(run()) == b"ab" and built["after"] < 0.4       # the response object existed before the chunk
+    # the empty stream and the forced immediate start
+    async def nothing():
+        return
+        yield b""
+
+    async def run2():
+        resp = await so.stream_response(nothing(), SimpleNamespace(args=SimpleNamespace(run_mode="normal")))
+        return b"".join([c async for c in resp.body_iterator])
+
+    assert asyncio.run(run2()) == b""
 
 
 def test_empty_stream():
