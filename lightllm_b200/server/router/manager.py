@@ -11,6 +11,7 @@ Reference: lightllm/server/router/manager.py:45-512.
 from __future__ import annotations
 
 import multiprocessing as mp
+import os
 import pickle
 import socket
 import time
@@ -38,6 +39,8 @@ def zmq_addr(args, port) -> str:
 
 
 class RouterManager:
+    MULTINODE_WAIT_S = float(os.environ.get("LLB_MULTINODE_WAIT_S", 30.0))
+
     def __init__(self, args: StartArgs, config_override: Optional[dict] = None):
         self.args = args
         self.name = args.unique_server_name
@@ -189,6 +192,14 @@ class RouterManager:
         all_free, allowed = sync.gather(waiting, self.mailbox.is_empty())
         plan = None
         if sync.is_master:
+            # a request that some node never received (its relay failed there, e.g. no free request slot) would
+            # block everything behind it in arrival order for ever: after a while the master gives it up
+            now = time.time()
+            for r in q.waiting_req_list:
+                if not r.is_aborted and r.group_req_id not in allowed and now - r.recv_time > self.MULTINODE_WAIT_S:
+                    print(f"[router] request {r.group_req_id} did not arrive on every node within "
+                          f"{self.MULTINODE_WAIT_S:.0f} s: dropped", flush=True)
+                    r.is_aborted = True
             chosen, cmds = [], []
             if all_free:
                 cmds, self.pending_cmds = list(self.pending_cmds), []

@@ -108,7 +108,27 @@ def _node(rank, port, q):
     if rank == 0:
         r.pending_cmds.append(ExitCmd())
     r._round_multinode()
-    q.put((rank, _describe(r.mailbox.msgs), r._exit_flushed, dropped_on_follower))
+    # a request that never reaches node 1 (its relay failed there): node 0 gives it up after the waiting limit, the
+    # requests behind it are no longer blocked
+    r2 = _router(rank)
+    r2.MULTINODE_WAIT_S = 0.2
+    lost, behind = _req(800), _req(808)
+    if rank == 0:
+        r2.req_queue.extend([lost, behind])
+    else:
+        r2.req_queue.extend([behind])
+    r2._round_multinode()
+    first = _describe(r2.mailbox.msgs)
+    import time as _t
+
+    _t.sleep(0.3)
+    r2._round_multinode()           # node 0 marks the lost request as aborted ...
+    if rank == 0:
+        r2._mn_dropped.update(x.group_req_id for x in r2.req_queue.waiting_req_list if x.is_aborted)
+        r2.req_queue.pop_aborted()
+    r2._round_multinode()           # ... and the one behind it is admitted everywhere
+    q.put((rank, _describe(r.mailbox.msgs), r._exit_flushed, dropped_on_follower, first, _describe(r2.mailbox.msgs),
+           lost.is_aborted))
     dist.barrier()
     dist.destroy_process_group()
 
@@ -130,6 +150,8 @@ def test_two_routers_write_identical_message_sequences():
                   [("ExitCmd", None), ("NewReqsCmd", [24])]]
     assert got[0][1] and got[1][1]                                           # both loops leave after the exit
     assert got[1][2]                                                         # the follower dropped request 2 too
+    assert got[0][3] == [] and got[1][3] == []                               # blocked while the lost request waits
+    assert got[0][4] == got[1][4] == [[("NewReqsCmd", [808])]] and got[0][5]  # given up on node 0, the next one runs
 
 
 class _FakeManager:
