@@ -97,8 +97,25 @@ def _get_text_tokenizer(model_dir: str, tokenizer_mode: str = "fast", trust_remo
 
     use_fast = tokenizer_mode != "slow"
     try:
-        return AutoTokenizer.from_pretrained(model_dir, use_fast=use_fast, trust_remote_code=trust_remote_code)
+        tok = AutoTokenizer.from_pretrained(model_dir, use_fast=use_fast, trust_remote_code=trust_remote_code)
     except Exception:
         if tokenizer_mode == "auto" or use_fast:
-            return AutoTokenizer.from_pretrained(model_dir, use_fast=not use_fast, trust_remote_code=trust_remote_code)
-        raise
+            tok = AutoTokenizer.from_pretrained(model_dir, use_fast=not use_fast, trust_remote_code=trust_remote_code)
+        else:
+            raise
+    if _model_type(model_dir) == "deepseek_v32":
+        # no Jinja template ships with this model: its prompt format is rendered in Python
+        from ..models.deepseek_v32_chat import DeepSeekV32Tokenizer
+
+        tok = DeepSeekV32Tokenizer(tok)
+    return tok
+
+
+def _model_type(model_dir: str) -> str:
+    try:
+        import json
+
+        with open(os.path.join(model_dir, "config.json")) as f:
+            return str(json.load(f).get("model_type", ""))
+    except (OSError, ValueError):
+        return ""
