@@ -12,7 +12,7 @@ from typing import List, Optional, Tuple
 import numpy as np
 import torch
 
-from .llama import Qwen2LM, Qwen3LM
+from .llama import LlamaLM, Qwen2LM, Qwen3LM
 from .registry import register_model
 from .remap import RemapSource
 
@@ -146,7 +146,9 @@ class Qwen2VLTokenizer:
         vc = model_cfg.get("vision_config") or {}
         self.patch = int(vc.get("patch_size", 14))
         self.merge = int(vc.get("spatial_merge_size", 2))
-        self.image_pad_id = model_cfg.get("image_token_id", 151655)
+        tc = model_cfg.get("text_config") or {}
+        self.image_pad_id = model_cfg.get("image_token_id", tc.get("image_token_id",
+                                                                   model_cfg.get("image_token_index", 151655)))
         self.min_pixels = int(model_cfg.get("min_pixels", 56 * 56))
         self.max_pixels = int(model_cfg.get("max_pixels", 14 * 14 * 4 * 1280))
 
@@ -324,8 +326,17 @@ register_model("qwen3_5", condition=_has_vision, is_multimodal=True)(Qwen3_5VLLM
 register_model("qwen3_5_moe", condition=_has_vision, is_multimodal=True)(Qwen3_5MoeVLLM)
 
 
-def _text_type_is(kind: str):
-    return lambda cfg: (cfg.get("text_config") or {}).get("model_type") == kind
+def is_tarsier2(cfg: dict) -> bool:
+    """A `llava` wrapper config around the Qwen2-VL vision tower (Tarsier2), whatever its decoder."""
+    if cfg.get("model_type") != "llava":
+        return False
+    vc = cfg.get("vision_config") or {}
+    return (cfg.get("text_config") or {}).get("model_type") == "qwen2_vl" or vc.get("model_type") == "qwen2_vl" or \
+        ("spatial_merge_size" in vc and "embed_dim" in vc)
+
+
+def _text_type_is(kind: str, tarsier: bool = False):
+    return lambda cfg: (cfg.get("text_config") or {}).get("model_type") == kind and (not tarsier or is_tarsier2(cfg))
 
 
 @register_model("llava", condition=_text_type_is("qwen2_vl"), is_multimodal=True)
@@ -346,3 +357,30 @@ class Tarsier2Qwen2VLLM(Qwen2VLLM):
             elif n.startswith("language_model.lm_head."):
                 t["lm_head." + n[len("language_model.lm_head."):]] = n
         return RemapSource(src, t) if t else src
+
+
+def _language_model_tensors(src):
+    from .llava import LlavaLM
+
+    return LlavaLM._wrap_source(None, src)
+
+
+@register_model("llava", condition=_text_type_is("qwen2", tarsier=True), is_multimodal=True)
+class Tarsier2Qwen2LM(Qwen2LM):
+    """Tarsier2 over a plain Qwen2 decoder (sequential positions): the Qwen2-VL tower's embeddings stand in for the
+    picture's run of token ids.  Reference: lightllm/models/tarsier2/model.py (Tarsier2Qwen2TpPartModel)."""
+
+    model_type = "llava"
+
+    def _wrap_source(self, src):
+        return _language_model_tensors(src)
+
+
+@register_model("llava", condition=_text_type_is("llama", tarsier=True), is_multimodal=True)
+class Tarsier2LlamaLM(LlamaLM):
+    """Tarsier2 over a Llama decoder.  Reference: lightllm/models/tarsier2/model.py (Tarsier2LlamaTpPartModel)."""
+
+    model_type = "llava"
+
+    def _wrap_source(self, src):
+        return _language_model_tensors(src)

@@ -52,8 +52,9 @@ def get_tokenizer(model_dir: str, tokenizer_mode: str = "fast", trust_remote_cod
 
     cfg = config_override or load_config(model_dir)
     mt = cfg.get("model_type")
-    if mt in ("qwen2_vl", "qwen2_5_vl") or (mt == "llava" and
-                                            (cfg.get("text_config") or {}).get("model_type") == "qwen2_vl"):
+    from ..models.qwen2_vl import is_tarsier2
+
+    if mt in ("qwen2_vl", "qwen2_5_vl") or is_tarsier2(cfg):
         from ..models.qwen2_vl import Qwen2VLTokenizer
 
         return Qwen2VLTokenizer(tok, cfg)

@@ -28,7 +28,9 @@ def build_vision_tower(args, device, dtype=torch.bfloat16):
 
     cfg = getattr(args, "_config_override", None) or load_config(args.model_dir)
     mt = cfg.get("model_type")
-    tarsier2 = mt == "llava" and (cfg.get("text_config") or {}).get("model_type") == "qwen2_vl"
+    from ...models.qwen2_vl import is_tarsier2
+
+    tarsier2 = is_tarsier2(cfg)
     if mt in ("qwen2_vl", "qwen2_5_vl") or tarsier2:
         from ...models.base import TransformerLM
         from ...models.vit.qwen2_vl_visual import Qwen2VLVisionTower

@@ -1135,3 +1135,84 @@ def test_gemma4_vision_tower_and_picture_tokens(tmp_path):
                     multimodal_params=[{"images": [item], "audios": []}])
     got = m.forward(mi).logits.float()
     assert (got - ref).abs().max().item() < 2e-3 * max(ref.abs().max().item(), 1.0)
+
+
+@pytest.mark.parametrize("kind", ["qwen2", "llama"])
+def test_tarsier2_over_plain_decoders(tmp_path, kind):
+    """Tarsier2 wrappers whose decoder is a plain Qwen2 / Llama model (sequential positions): the Qwen2-VL tower's
+    embeddings replace the picture's run of ids; against the Hugging Face decoder fed with the same embeddings."""
+    import json
+
+    from safetensors.torch import save_file
+    from transformers import LlamaConfig, LlamaForCausalLM, Qwen2Config, Qwen2ForCausalLM
+    from transformers.models.qwen2_vl.configuration_qwen2_vl import Qwen2VLVisionConfig
+    from transformers.models.qwen2_vl.modeling_qwen2_vl import Qwen2VisionTransformerPretrainedModel
+
+    from lightllm_b200.common.infer_state import ModelInput
+    from lightllm_b200.models.base import load_config
+    from lightllm_b200.models.registry import get_model, is_multimodal
+    from lightllm_b200.models.vit.qwen2_vl_visual import Qwen2VLVisionTower, patchify
+    from lightllm_b200.models.weights import SafetensorsSource
+    from lightllm_b200.parallel import dist as pdist
+    from lightllm_b200.server.tokenizer import get_tokenizer
+
+    torch.manual_seed(0)
+    text = dict(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                vocab_size=300, max_position_embeddings=512, tie_word_embeddings=False)
+    vision = dict(depth=2, embed_dim=32, hidden_size=64, num_heads=4, mlp_ratio=2, patch_size=14, spatial_merge_size=2,
+                  temporal_patch_size=2, in_chans=3)
+    lm = (Qwen2ForCausalLM(Qwen2Config(**text)) if kind == "qwen2" else LlamaForCausalLM(LlamaConfig(**text))).eval().float()
+    vit = Qwen2VisionTransformerPretrainedModel(Qwen2VLVisionConfig(**vision)).eval().float()
+    d = tmp_path / "ckpt"
+    d.mkdir()
+    tensors = {"language_model." + k: v.contiguous() for k, v in lm.state_dict().items()}
+    tensors.update({"vision_tower." + k: v.contiguous() for k, v in vit.state_dict().items()})
+    save_file(tensors, str(d / "model.safetensors"))
+    wrapper = {"model_type": "llava", "architectures": ["TarsierForConditionalGeneration"],
+               "text_config": dict(lm.config.to_dict(), model_type=kind, image_token_id=290, vision_start_token_id=292,
+                                   vision_end_token_id=293),
+               "vision_config": dict(vision, model_type="qwen2_vl"), "image_token_index": 290}
+    (d / "config.json").write_text(json.dumps(wrapper))
+
+    pixels = torch.randn(1, 3, 56, 84)
+    patches, (t, gh, gw) = patchify(pixels)
+    n_img = t * gh * gw // 4
+    pre, post = [5, 17, 292], [293, 9, 44, 120, 7]
+    with torch.no_grad():
+        feats = vit(patches, grid_thw=torch.tensor([[t, gh, gw]]))
+        feats = getattr(feats, "pooler_output", feats)
+        feats = feats[0] if isinstance(feats, (tuple, list)) else feats
+        emb_in = lm.get_input_embeddings()(torch.tensor([pre + [0] * n_img + post]))
+        emb_in[0, len(pre): len(pre) + n_img] = feats
+        ref = lm(inputs_embeds=emb_in).logits[0].float()
+
+    conf = load_config(str(d))
+    assert is_multimodal(conf)
+    tower = Qwen2VLVisionTower(conf["vision_config"], SafetensorsSource(str(d)), torch.device("cpu"), torch.float32,
+                               prefix="vision_tower.")
+    emb = tower.forward(patches, [(t, gh, gw)])
+    assert (emb - feats).abs().max().item() < 1e-4
+
+    class Arena:
+        def read_rows(self, rows):
+            return emb[rows - 40]
+
+    m = get_model(conf, model_dir=str(d), pstate=pdist.ParallelState(device=torch.device("cpu")), data_type="float32",
+                  max_total_token_num=256, max_req_num=2, max_seq_length=128, disable_cudagraph=True)
+    assert type(m).__name__ == ("Tarsier2Qwen2LM" if kind == "qwen2" else "Tarsier2LlamaLM")
+    m.embed_arena = Arena()
+    tok0 = 100_000_000
+    ids = torch.tensor(pre + list(range(tok0, tok0 + n_img)) + post)
+    item = {"token_id": tok0, "token_num": n_img, "start_index_in_embed_cache": 40, "grid_thwd": (t, gh, gw, 2)}
+    req, n = m.req_manager.alloc(), len(ids)
+    mi = ModelInput(batch_size=1, total_token_num=n, max_kv_len=n, is_prefill=True,
+                    b_req_idx=torch.tensor([req], dtype=torch.int32), b_seq_len=torch.tensor([n], dtype=torch.int32),
+                    mem_indexes=m.mem_manager.alloc(n).clone(), input_ids=ids,
+                    b_ready_cache_len=torch.zeros(1, dtype=torch.int32), max_q_len=n, return_all_logits=True,
+                    multimodal_params=[{"images": [item], "audios": []}])
+    got = m.forward(mi).logits.float()
+    assert (got - ref).abs().max().item() < 2e-3 * max(ref.abs().max().item(), 1.0)
+
+    # the serving tokenizer of such a checkpoint is the Qwen2-VL one, keyed by the wrapper's picture token
+    tk = get_tokenizer(str(d), multimodal=True, vocab_size=300)
+    assert type(tk).__name__ == "Qwen2VLTokenizer" and tk.image_pad_id == 290
