@@ -168,14 +168,16 @@ FLAGS = [
     ("--visual_gpu_ids", ("list", int), None, "GPUs of the visual encoder"),
     ("--visual_tp", int, 1, "tensor parallel size of the visual encoder"),
     ("--visual_dp", int, 1, "replicas of the visual encoder"),
-    ("--visual_rpyc_port", int, None, "control port of a remote visual encoder"),
-    ("--visual_use_proxy_mode", "flag", False, "use visual encoders registered at the config server"),
+    ("--visual_rpyc_port", int, None, "--run_mode visual_only: the port this vision encoder is asked on"),
+    ("--visual_use_proxy_mode", "flag", False, "keep no vision tower: pictures go to the encoders (--run_mode "
+     "visual_only) registered at the config server"),
     ("--audio_gpu_ids", ("list", int), None, "GPUs of the audio encoder"),
     ("--audio_tp", int, 1, "tensor parallel size of the audio encoder"),
     ("--audio_dp", int, 1, "replicas of the audio encoder"),
     ("--audio_infer_batch_size", int, None, "clips per encoder pass"),
-    ("--afs_image_embed_dir", str, None, "shared directory with precomputed image embeddings"),
-    ("--afs_embed_capacity", int, 250000, "entries of the shared embedding directory"),
+    ("--afs_image_embed_dir", str, None, "directory all servers see: image embeddings by content hash, shared "
+     "between vision encoders and the servers that use them"),
+    ("--afs_embed_capacity", int, 250000, "files kept in --afs_image_embed_dir (least recently used go first)"),
     # ---- operations ----
     ("--health_monitor", "flag", False, "watch /health and restart the server after repeated failures"),
     ("--metric_gateway", str, None, "Prometheus push gateway address"),
@@ -228,8 +230,7 @@ COMPAT_ONLY_FLAGS = (
     "enable_triton_fallback", "disable_flashinfer_allreduce", "penalty_counter_mode", "load_way",
     "enable_prefill_cudagraph", "prefill_cudagraph_max_handle_token",
     "pd_trans_mode",
-    "config_server_visual_redis_port", "visual_use_proxy_mode", "visual_rpyc_port", "afs_image_embed_dir",
-    "afs_embed_capacity", "vit_quant_type", "vit_quant_cfg", "visual_tp", "audio_tp", "audio_dp", "audio_gpu_ids",
+    "config_server_visual_redis_port", "vit_quant_type", "vit_quant_cfg", "visual_tp", "audio_tp", "audio_dp", "audio_gpu_ids",
     "linear_att_page_block_num",
     "disable_linear_att_small_page_cpu_cache", "hypercorn_config", "enable_mps",
     "enable_torch_memory_saver", "enable_weight_cpu_backup")

@@ -138,7 +138,10 @@ def start_core_processes(args: StartArgs, config_override: dict = None):
     funcs.append(start_router_process)
     fargs.append((d, config_override))
     if args.enable_multimodal:
-        from .visualserver.manager import start_visual_process
+        if getattr(args, "visual_use_proxy_mode", False):
+            from .visualserver.remote import start_proxy_visual_process as start_visual_process
+        else:
+            from .visualserver.manager import start_visual_process
 
         dv = dict(d)
         dv["_config_override"] = config_override
@@ -226,10 +229,16 @@ def config_server_start(args: StartArgs):
                 log_level="warning")
 
 
-def visual_only_start(args: StartArgs):
-    from .visualserver.manager import start_visual_process
+def visual_only_start(args: StartArgs, config_override: dict = None):
+    """A vision encoder on its own: it registers at the config server and embeds pictures for the servers that run
+    with `--visual_use_proxy_mode` (reference: api_start.py visual_only_start)."""
+    from .visualserver.remote import start_visual_only_process
 
-    args = normalize_args(args)
+    args = normalize_args(args, config_override)
+    if getattr(args, "afs_image_embed_dir", None):
+        os.makedirs(args.afs_image_embed_dir, mode=0o777, exist_ok=True)
     set_env_start_args(args)
-    process_manager.start_submodule_processes([start_visual_process], [(args.to_dict(),)])
+    d = {k: v for k, v in args.to_dict().items() if not k.startswith("_")}
+    d["_config_override"] = config_override
+    process_manager.start_submodule_processes([start_visual_only_process], [(d,)])
     process_manager.supervise()

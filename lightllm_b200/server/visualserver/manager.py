@@ -141,18 +141,38 @@ class VisualManager:
     def handle_many(self, msgs: list):
         """Requests that arrived together share encoder passes: their missing pictures are embedded in batches of
         `infer_batch_size` (one record once, however many requests carry it), then everything travels on in arrival
-        order (control commands keep their place)."""
-        try:
-            pending = []
-            for m in msgs:
-                if isinstance(m, GroupReqIndexes):
-                    pending += self._pending_images(m)
-            if pending:
-                self.embed(pending)
-        except Exception:
-            traceback.print_exc()       # the router fails a request whose embeddings never become ready
+        order (control commands keep their place).  When the pass fails, the requests whose pictures are still
+        missing are marked aborted before they travel on: the router ends them instead of running them over
+        unwritten arena rows."""
+        failed = set()
+        pending = []
         for m in msgs:
+            if isinstance(m, GroupReqIndexes):
+                pending += self._pending_images(m)
+        if pending:
+            try:
+                self.embed(pending)
+            except Exception:
+                traceback.print_exc()
+                for m in msgs:
+                    try:
+                        if isinstance(m, GroupReqIndexes) and self._pending_images(m):
+                            failed.add(id(m))
+                    except Exception:
+                        failed.add(id(m))
+        for m in msgs:
+            if id(m) in failed:
+                self._abort(m)
             self.send_next(m)
+
+    def _abort(self, group: GroupReqIndexes):
+        mgr = getattr(self, "shm_req_manager", None)
+        if mgr is None:
+            return
+        for idx in group.shm_req_indexes:
+            req = mgr.get_req_obj_by_index(idx)
+            req.is_aborted = True
+            mgr.put_back_req_obj(req)
 
     def loop(self):
         while True:
@@ -163,6 +183,19 @@ class VisualManager:
                     break
                 msgs.append(m)
             self.handle_many(msgs)
+
+
+def open_req_table(args):
+    """The shared request table, to mark requests aborted; None where there is none (a tower used on its own)."""
+    try:
+        from ..core.objs.shm_req_manager import ShmReqManager
+        from ..core.objs.start_args import set_env_start_args
+
+        set_env_start_args(args)
+        return ShmReqManager(args.unique_server_name, args.running_max_req_size)
+    except Exception:
+        traceback.print_exc()
+        return None
 
 
 def start_visual_process(args_dict: dict, pipe_writer=None):
@@ -191,6 +224,7 @@ def start_visual_process(args_dict: dict, pipe_writer=None):
         mgr = VisualManager(args, tower, cache, lambda m: push.send_pyobj(m, protocol=pickle.HIGHEST_PROTOCOL),
                             pull.recv_pyobj, infer_batch_size=args.visual_infer_batch_size or 8, try_recv=try_recv,
                             send_batch_size=getattr(args, "visual_send_batch_size", 1) or 1)
+        mgr.shm_req_manager = open_req_table(args)
     except Exception:
         if pipe_writer is not None:
             pipe_writer.send(("init failed", traceback.format_exc()))

@@ -76,34 +76,22 @@ def server(tmp_path_factory):
         os.killpg(proc.pid, signal.SIGKILL)
 
 
-@pytest.mark.timeout(900)
-def test_image_request_matches_offline(server):
+def offline_tokens(raw, pre, post, n_new=5):
+    """The first `n_new` greedy tokens of prompt `pre + picture + post` computed in this process: the same tower
+    and language model as the servers of these tests (random weights are a function of the tensor names)."""
     from lightllm_b200.common.infer_state import ModelInput
     from lightllm_b200.models.registry import get_model
-    from lightllm_b200.models.vit.qwen2_vl_visual import Qwen2VLVisionTower, image_token_num, preprocess_image
+    from lightllm_b200.models.vit.qwen2_vl_visual import Qwen2VLVisionTower, preprocess_image
     from lightllm_b200.models.weights import RandomSource
     from lightllm_b200.parallel import dist as pdist
 
-    url, d = server
-    raw = _png(84, 56)
-    n_img, (t, gh, gw) = image_token_num(84, 56)
-    pre, post = [5, 17, 33], [9, 44, 120, 7]
-    body = {"inputs": pre + [290] + post,
-            "parameters": {"max_new_tokens": 5, "ignore_eos": True, "return_details": True},
-            "multimodal_params": {"images": [{"type": "base64", "data": base64.b64encode(raw).decode()}]}}
-    r = requests.post(url + "/generate", json=body, timeout=180)
-    log = open(d / "server.log").read()[-3000:]
-    assert r.status_code == 200, r.text + log
-    out = r.json()
-    assert out["prompt_tokens"] == len(pre) + n_img + len(post), str(out) + log
-    got = [tk["id"] for tk in out["tokens"]]
-
-    # offline: the same tower and language model (weights are a function of the tensor names), the same image
     vcfg = dict(CFG["vision_config"])
     tower = Qwen2VLVisionTower(vcfg, RandomSource(Qwen2VLVisionTower.weight_shapes(vcfg), dtype=torch.float32),
                                torch.device("cpu"), torch.float32)
     patches, grid = preprocess_image(raw)
+    t, gh, gw = grid
     emb = tower.forward(patches, [grid]).bfloat16().float()      # the arena stores bf16
+    n_img = emb.shape[0]
 
     class Arena:
         def read_rows(self, rows):
@@ -124,12 +112,33 @@ def test_image_request_matches_offline(server):
                     b_ready_cache_len=torch.zeros(1, dtype=torch.int32), max_q_len=n,
                     multimodal_params=[{"images": [item], "audios": []}])
     want = [int(m.forward(mi).logits[0].argmax())]
-    for k in range(4):
+    for k in range(n_new - 1):
         m.req_manager.req_to_next_token_ids[req] = want[-1]
         mi = ModelInput(batch_size=1, total_token_num=n + k + 1, max_kv_len=n + k + 1, is_prefill=False,
                         b_req_idx=torch.tensor([req], dtype=torch.int32),
                         b_seq_len=torch.tensor([n + k + 1], dtype=torch.int32), mem_indexes=m.mem_manager.alloc(1).clone())
         want.append(int(m.forward(mi).logits[0].argmax()))
+    return want
+
+
+@pytest.mark.timeout(900)
+def test_image_request_matches_offline(server):
+    from lightllm_b200.models.vit.qwen2_vl_visual import image_token_num
+
+    url, d = server
+    raw = _png(84, 56)
+    n_img, (t, gh, gw) = image_token_num(84, 56)
+    pre, post = [5, 17, 33], [9, 44, 120, 7]
+    body = {"inputs": pre + [290] + post,
+            "parameters": {"max_new_tokens": 5, "ignore_eos": True, "return_details": True},
+            "multimodal_params": {"images": [{"type": "base64", "data": base64.b64encode(raw).decode()}]}}
+    r = requests.post(url + "/generate", json=body, timeout=180)
+    log = open(d / "server.log").read()[-3000:]
+    assert r.status_code == 200, r.text + log
+    out = r.json()
+    assert out["prompt_tokens"] == len(pre) + n_img + len(post), str(out) + log
+    got = [tk["id"] for tk in out["tokens"]]
+    want = offline_tokens(raw, pre, post)
     assert got == want, log
     # the same image again: served from the embed cache (same virtual ids -> prefix cache hit on the prompt)
     r2 = requests.post(url + "/generate", json=body, timeout=180).json()
