@@ -78,7 +78,19 @@ class HostKVCache:
         esz = torch.empty((), dtype=mem_manager.dtype).element_size()
         self.page_bytes = int(np.prod(self.page_shape)) * esz
         self.n_pages = max(1, int(bytes_budget) // self.page_bytes)
-        self.pool = torch.empty((self.n_pages, *self.page_shape), dtype=mem_manager.dtype, pin_memory=self.cuda)
+        from ..utils import host_memory as hm
+
+        self.host_buffer = None
+        if hm.huge_pages_wanted() or hm.numa_policy_wanted():
+            # huge pages / NUMA placement asked for: own mapping, registered with CUDA, instead of torch's pinned pool
+            self.host_buffer = hm.HostBuffer.create(
+                self.n_pages * self.page_bytes, huge_pages=hm.huge_pages_wanted(), numa=hm.numa_policy_wanted(),
+                device_index=self.device.index if self.cuda else None, register=self.cuda)
+            self.pool = self.host_buffer.tensor(mem_manager.dtype, (self.n_pages, *self.page_shape))
+            for note in self.host_buffer.notes:
+                print(f"[host kv cache {name}] {note}", flush=True)
+        else:
+            self.pool = torch.empty((self.n_pages, *self.page_shape), dtype=mem_manager.dtype, pin_memory=self.cuda)
         self.index: "OrderedDict[bytes, int]" = OrderedDict()
         self.free = list(range(self.n_pages - 1, -1, -1))
         self.disk = None
