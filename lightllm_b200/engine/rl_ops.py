@@ -16,23 +16,48 @@ def flush_cache(loop):
     return True
 
 
+def _weight_slots(m):
+    """(owner, attribute, tensor) of every plain weight tensor of the model: layer tables first, then the
+    embedding, the final norm and the head (which may be the embedding itself)."""
+    for lw in m.layers:
+        for k, t in list(lw.tensors().items()):
+            if isinstance(t, torch.Tensor):
+                yield lw, k, t
+    for k in ("embed_w", "final_norm_w", "lm_head_w"):
+        t = getattr(m, k, None)
+        if isinstance(t, torch.Tensor):
+            yield m, k, t
+
+
 def release_memory_occupation(loop, tags=("kv_cache",)):
-    """Frees the KV pool (and optionally weights to a host backup) so a co-located trainer can use the GPU."""
+    """Frees the KV pool and / or the weights so that a co-located trainer can use the GPU.  Weights: with
+    `--enable_weight_cpu_backup` they are copied to (pinned) host memory first and come back on resume; without,
+    only their shapes are kept and resume hands out zeroed tensors that the trainer's next weight push fills.
+    Reference: lightllm/common/basemodel/basemodel.py:100-116 (memory-saver regions, `enable_cpu_backup`)."""
     m = loop.model
     if loop.backend.has_work():
         raise RuntimeError("cannot release memory while requests are running")
     flush_cache(loop)
     m.flush_graphs()
-    if "kv_cache" in tags:
+    if "kv_cache" in tags and m.mem_manager.kv_buffer is not None:
         m._released_kv_shape = tuple(m.mem_manager.kv_buffer.shape)
         m.mem_manager.kv_buffer = None
-    if "weights" in tags:
-        m._weight_backup = {}
-        for i, lw in enumerate(m.layers):
-            for k, t in list(lw.tensors().items()):
-                if isinstance(t, torch.Tensor):
-                    m._weight_backup[(i, k)] = t.cpu()
-                    setattr(lw, k, None)
+    if "weights" in tags and getattr(m, "_weight_backup", None) is None:
+        keep = bool(getattr(getattr(loop, "args", None), "enable_weight_cpu_backup", True))
+        saved, slots = {}, []          # one entry per storage: tied tensors stay tied after resume
+        for owner, k, t in _weight_slots(m):
+            key = (t.data_ptr(), tuple(t.shape), t.dtype)
+            if key not in saved:
+                if keep:
+                    host = torch.empty(t.shape, dtype=t.dtype, pin_memory=t.is_cuda)
+                    host.copy_(t)
+                    saved[key] = host
+                else:
+                    saved[key] = (tuple(t.shape), t.dtype)
+            slots.append((owner, k, key))
+        for owner, k, _ in slots:
+            setattr(owner, k, None)
+        m._weight_backup = (keep, saved, slots)
     if m.device.type == "cuda":
         torch.cuda.empty_cache()
 
@@ -42,8 +67,15 @@ def resume_memory_occupation(loop, tags=("kv_cache",)):
     if "kv_cache" in tags and m.mem_manager.kv_buffer is None:
         m.mem_manager.kv_buffer = torch.zeros(m._released_kv_shape, dtype=m.mem_manager.dtype, device=m.device)
     if "weights" in tags and getattr(m, "_weight_backup", None):
-        for (i, k), t in m._weight_backup.items():
-            setattr(m.layers[i], k, t.to(m.device))
+        keep, saved, slots = m._weight_backup
+        live = {}
+        for owner, k, key in slots:
+            if key not in live:
+                v = saved[key]
+                live[key] = v.to(m.device, non_blocking=True) if keep else torch.zeros(v[0], dtype=v[1], device=m.device)
+            setattr(owner, k, live[key])
+        if m.device.type == "cuda":
+            torch.cuda.synchronize()
         m._weight_backup = None
 
 

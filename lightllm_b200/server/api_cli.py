@@ -196,7 +196,8 @@ FLAGS = [
     # ---- RL ----
     ("--enable_rl", "flag", False, "weight-update / pause / flush control plane for RL trainers"),
     ("--enable_torch_memory_saver", "flag", False, "release and resume GPU memory on request"),
-    ("--enable_weight_cpu_backup", "flag", False, "keep a host copy of the weights while released"),
+    ("--enable_weight_cpu_backup", "flag", False, "release_memory_occupation of the weights keeps a pinned host "
+     "copy that resume restores (without it, resume hands out zeroed weights for the next push)"),
 ]
 
 
@@ -233,7 +234,7 @@ COMPAT_ONLY_FLAGS = (
     "config_server_visual_redis_port", "vit_quant_type", "vit_quant_cfg", "visual_tp", "audio_tp", "audio_dp", "audio_gpu_ids",
     "linear_att_page_block_num",
     "disable_linear_att_small_page_cpu_cache", "hypercorn_config", "enable_mps",
-    "enable_torch_memory_saver", "enable_weight_cpu_backup")
+    "enable_torch_memory_saver")
 
 
 def compat_only_flags_in_use(args) -> list:

@@ -86,3 +86,33 @@ def test_update_weights_from_shared_memory():
         shm.close()
         shm.unlink()
     pdist.destroy()
+
+
+def test_release_and_resume_weights_with_and_without_host_backup():
+    llm, loop = _engine()
+    prompt = [list(range(5, 30))]
+    sp = {"max_new_tokens": 6, "ignore_eos": True}
+    before = llm.generate(prompt, sp)[0]["token_ids"]
+    m = llm.model
+    tied = m.lm_head_w is m.embed_w
+    n_layer_tensors = sum(1 for lw in m.layers for t in lw.tensors().values() if isinstance(t, torch.Tensor))
+    head_before = m.lm_head_w.clone()
+
+    loop.args = SimpleNamespace(enable_weight_cpu_backup=True)
+    rl_ops.release_memory_occupation(loop, tags=("kv_cache", "weights"))
+    assert m.mem_manager.kv_buffer is None and m.embed_w is None and m.lm_head_w is None and m.final_norm_w is None
+    assert all(not isinstance(t, torch.Tensor) for lw in m.layers for t in lw.tensors().values())
+    keep, saved, slots = m._weight_backup
+    assert keep and len(slots) == n_layer_tensors + 3 and all(isinstance(v, torch.Tensor) for v in saved.values())
+    rl_ops.release_memory_occupation(loop, tags=("weights",))        # a second release keeps the first backup
+    assert m._weight_backup[2] is slots
+    rl_ops.resume_memory_occupation(loop, tags=("kv_cache", "weights"))
+    assert m._weight_backup is None and (m.lm_head_w is m.embed_w) == tied
+    assert llm.generate(prompt, sp)[0]["token_ids"] == before
+
+    loop.args = SimpleNamespace(enable_weight_cpu_backup=False)
+    rl_ops.release_memory_occupation(loop, tags=("weights",))
+    assert all(isinstance(v, tuple) for v in m._weight_backup[1].values())          # shapes only
+    rl_ops.resume_memory_occupation(loop, tags=("weights",))
+    assert m.lm_head_w.shape == head_before.shape and float(m.lm_head_w.abs().sum()) == 0.0   # to be filled by a push
+    assert (m.lm_head_w is m.embed_w) == tied
