@@ -231,7 +231,7 @@ COMPAT_ONLY_FLAGS = (
     "enable_triton_fallback", "disable_flashinfer_allreduce", "penalty_counter_mode", "load_way",
     "enable_prefill_cudagraph", "prefill_cudagraph_max_handle_token",
     "pd_trans_mode",
-    "config_server_visual_redis_port", "vit_quant_type", "vit_quant_cfg", "visual_tp", "audio_tp", "audio_dp", "audio_gpu_ids",
+    "config_server_visual_redis_port", "vit_quant_type", "vit_quant_cfg", "visual_tp", "audio_tp",
     "linear_att_page_block_num",
     "disable_linear_att_small_page_cpu_cache", "hypercorn_config", "enable_mps",
     "enable_torch_memory_saver")

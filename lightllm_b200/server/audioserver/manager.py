@@ -43,8 +43,12 @@ def build_audio_tower(args, device, dtype=torch.bfloat16):
 
 
 class AudioManager:
-    def __init__(self, args: StartArgs, tower=None, cache=None, send_next=None, recv=None, infer_batch_size: int = 8):
+    def __init__(self, args: StartArgs, tower=None, cache=None, send_next=None, recv=None, infer_batch_size: int = 8,
+                 towers=None):
+        self.towers = list(towers) if towers else ([tower] if tower is not None else [])      # `--audio_dp` replicas
+        tower = self.towers[0] if self.towers else None
         self.args, self.tower, self.cache = args, tower, cache
+        self.shm_req_manager = None
         self.send_next, self.recv = send_next, recv
         self.infer_batch_size = infer_batch_size
 
@@ -58,10 +62,16 @@ class AudioManager:
 
     def embed(self, audios: List[dict]):
         items = list({a["uuid"]: a for a in audios}.values())
-        for s in range(0, len(items), self.infer_batch_size):
-            chunk = items[s:s + self.infer_batch_size]
+        for s in range(0, len(items), self.infer_batch_size * max(1, len(self.towers))):
+            chunk = items[s:s + self.infer_batch_size * max(1, len(self.towers))]
             clips = [np.frombuffer(self.cache.get_payload(a["uuid"]), dtype=np.float32) for a in chunk]
-            embs = self.tower.encode_audios(clips, items=chunk)
+            if len(self.towers) > 1 and len(chunk) > 1:
+                from ..visualserver.manager import encode_on_replicas
+
+                embs = encode_on_replicas(self.towers, len(chunk), self.infer_batch_size, lambda tower, idx: tower.encode_audios(
+                    [clips[i] for i in idx], items=[chunk[i] for i in idx]))
+            else:
+                embs = self.tower.encode_audios(clips, items=chunk)
             for it, e in zip(chunk, embs):
                 assert e.shape[0] == it["token_num"], f"clip gives {e.shape[0]} tokens, the prompt reserved {it['token_num']}"
                 arr = getattr(self.cache.arena, "arr", None)
@@ -87,7 +97,14 @@ class AudioManager:
                     self.send_next(msg)
             except Exception:
                 traceback.print_exc()
-                self.send_next(msg)  # the router fails the request when its embeddings never become ready
+                # clips that could not be embedded: their requests end as aborted instead of running over
+                # unwritten arena rows
+                if isinstance(msg, GroupReqIndexes) and self.shm_req_manager is not None:
+                    for idx in msg.shm_req_indexes:
+                        req = self.shm_req_manager.get_req_obj_by_index(idx)
+                        req.is_aborted = True
+                        self.shm_req_manager.put_back_req_obj(req)
+                self.send_next(msg)
 
 
 def start_audio_process(args_dict: dict, pipe_writer=None):
@@ -97,9 +114,12 @@ def start_audio_process(args_dict: dict, pipe_writer=None):
     set_proc_title(f"lightllm::{args.unique_server_name}::audio_server")
     start_parent_check_thread()
     try:
-        dev_index = (args.visual_gpu_ids or [0])[0] if torch.cuda.is_available() else None
-        device = torch.device("cuda", dev_index) if dev_index is not None else torch.device("cpu")
-        tower = build_audio_tower(args, device, torch.bfloat16 if device.type == "cuda" else torch.float32)
+        from ..visualserver.manager import open_req_table, replica_devices
+
+        gpu_ids = getattr(args, "audio_gpu_ids", None) or args.visual_gpu_ids
+        towers = [build_audio_tower(args, dev, torch.bfloat16 if dev.type == "cuda" else torch.float32)
+                  for dev in replica_devices(gpu_ids, getattr(args, "audio_dp", 1))]
+        tower = towers[0]
         ctx = zmq.Context(2)
         pull = ctx.socket(zmq.PULL)
         pull.bind(zmq_addr(args, args.audio_port))
@@ -107,7 +127,9 @@ def start_audio_process(args_dict: dict, pipe_writer=None):
         push.connect(zmq_addr(args, args.router_port))
         cache = EmbedCacheClient(args, hidden=tower.out_hidden, open_arena=True)
         mgr = AudioManager(args, tower, cache, lambda m: push.send_pyobj(m, protocol=pickle.HIGHEST_PROTOCOL),
-                           pull.recv_pyobj, infer_batch_size=int(getattr(args, "audio_infer_batch_size", 0) or 8))
+                           pull.recv_pyobj, infer_batch_size=int(getattr(args, "audio_infer_batch_size", 0) or 8),
+                           towers=towers)
+        mgr.shm_req_manager = open_req_table(args)
     except Exception:
         if pipe_writer is not None:
             pipe_writer.send(("init failed", traceback.format_exc()))

@@ -98,10 +98,45 @@ def build_vision_tower(args, device, dtype=torch.bfloat16):
     raise ValueError(f"no vision tower for model_type {mt!r}")
 
 
+def encode_on_replicas(towers, n_items: int, batch_size: int, encode):
+    """Data-parallel encoder pass: the item indices 0..n_items-1 are dealt round-robin to the towers, every tower
+    works through its share in batches of `batch_size` on a thread of its own (bound to the tower's GPU), and
+    `encode(tower, indices) -> list of tensors` does one batch.  Returns the results by item index."""
+    from concurrent.futures import ThreadPoolExecutor
+
+    out = [None] * n_items
+
+    def work(r):
+        tower = towers[r]
+        dev = getattr(tower, "device", None)
+        if dev is not None and getattr(dev, "type", "cpu") == "cuda":
+            torch.cuda.set_device(dev)
+        mine = list(range(r, n_items, len(towers)))
+        for s in range(0, len(mine), batch_size):
+            idx = mine[s:s + batch_size]
+            for i, e in zip(idx, encode(tower, idx)):
+                out[i] = e
+
+    with ThreadPoolExecutor(max_workers=len(towers)) as ex:
+        list(ex.map(work, range(len(towers))))
+    return out
+
+
+def replica_devices(gpu_ids, dp: int):
+    """One device per encoder replica: `gpu_ids[r]` (cycled when fewer are given), the CPU without CUDA."""
+    dp = max(1, int(dp or 1))
+    if not torch.cuda.is_available():
+        return [torch.device("cpu")] * dp
+    ids = list(gpu_ids or range(dp))
+    return [torch.device("cuda", ids[r % len(ids)]) for r in range(dp)]
+
+
 class VisualManager:
     def __init__(self, args: StartArgs, tower=None, cache=None, send_next=None, recv=None, infer_batch_size: int = 8,
-                 try_recv=None, send_batch_size: int = 1):
+                 try_recv=None, send_batch_size: int = 1, towers=None):
         self.args = args
+        self.towers = list(towers) if towers else ([tower] if tower is not None else [])   # `--visual_dp` replicas
+        tower = self.towers[0] if self.towers else None
         self.tower = tower
         self.cache = cache
         self.send_next = send_next
@@ -123,6 +158,17 @@ class VisualManager:
         """Runs the tower over `images` (deduplicated by cache record) and publishes the embeddings."""
         uniq = {i["uuid"]: i for i in images}
         items = list(uniq.values())
+        if len(self.towers) > 1 and len(items) > 1:
+            # the cache client is one socket: payloads are read and results written on this thread, only the
+            # tower passes run side by side
+            payloads = [self.cache.get_payload(i["uuid"]) for i in items]
+            embs = encode_on_replicas(self.towers, len(items), self.infer_batch_size, lambda tower, idx: tower.encode_images(
+                [payloads[i] for i in idx], items=[items[i] for i in idx]))
+            for it, e in zip(items, embs):
+                assert e.shape[0] == it["token_num"], f"image gives {e.shape[0]} tokens, the prompt reserved {it['token_num']}"
+                self.cache.arena.write(it["start_index_in_embed_cache"], e)
+            self.cache.set_items_embed([i["uuid"] for i in items])
+            return
         for s in range(0, len(items), self.infer_batch_size):
             chunk = items[s:s + self.infer_batch_size]
             payloads = [self.cache.get_payload(i["uuid"]) for i in chunk]
@@ -205,9 +251,9 @@ def start_visual_process(args_dict: dict, pipe_writer=None):
     set_proc_title(f"lightllm::{args.unique_server_name}::visual_server")
     start_parent_check_thread()
     try:
-        dev_index = (args.visual_gpu_ids or [0])[0] if torch.cuda.is_available() else None
-        device = torch.device("cuda", dev_index) if dev_index is not None else torch.device("cpu")
-        tower = build_vision_tower(args, device, torch.bfloat16 if device.type == "cuda" else torch.float32)
+        towers = [build_vision_tower(args, dev, torch.bfloat16 if dev.type == "cuda" else torch.float32)
+                  for dev in replica_devices(args.visual_gpu_ids, getattr(args, "visual_dp", 1))]
+        tower = towers[0]
         ctx = zmq.Context(2)
         pull = ctx.socket(zmq.PULL)
         pull.bind(zmq_addr(args, args.visual_port))
@@ -223,7 +269,7 @@ def start_visual_process(args_dict: dict, pipe_writer=None):
 
         mgr = VisualManager(args, tower, cache, lambda m: push.send_pyobj(m, protocol=pickle.HIGHEST_PROTOCOL),
                             pull.recv_pyobj, infer_batch_size=args.visual_infer_batch_size or 8, try_recv=try_recv,
-                            send_batch_size=getattr(args, "visual_send_batch_size", 1) or 1)
+                            send_batch_size=getattr(args, "visual_send_batch_size", 1) or 1, towers=towers)
         mgr.shm_req_manager = open_req_table(args)
     except Exception:
         if pipe_writer is not None:

@@ -224,3 +224,76 @@ def test_qwen_vl_v1_tower_and_tokenizer():
     mp = SimpleNamespace(images=[SimpleNamespace(token_id=5000, token_num=16), SimpleNamespace(token_id=6000, token_num=16)])
     ids = tk.encode("look <img>a.jpg</img> and <img>b.jpg</img> ok", mp)
     assert ids == [5, 1, 5, 900] + list(range(5000, 5016)) + [901, 7, 5, 1, 5, 900] + list(range(6000, 6016)) + [901, 7, 5]
+
+
+def test_encoder_replicas_share_a_batch_of_pictures():
+    """`--visual_dp` / `--audio_dp`: the pictures of one pass are dealt to the replicas, which run on threads of
+    their own; payload reads and arena writes stay on the manager's thread; results do not depend on the dealing."""
+    import threading as th
+
+    from lightllm_b200.server.audioserver.manager import AudioManager
+    from lightllm_b200.server.core.objs.io_objs import GroupReqIndexes
+    from lightllm_b200.server.visualserver.manager import VisualManager, encode_on_replicas, replica_devices
+
+    main = th.get_ident()
+
+    class Tower:
+        def __init__(self):
+            self.batches, self.threads = [], set()
+
+        def encode_images(self, payloads, items=None):
+            self.batches.append(len(payloads))
+            self.threads.add(th.get_ident())
+            return [torch.full((it["token_num"], 4), float(p[0])) for p, it in zip(payloads, items)]
+
+        def encode_audios(self, clips, items=None):
+            self.threads.add(th.get_ident())
+            return [torch.full((it["token_num"], 4), float(c[0])) for c, it in zip(clips, items)]
+
+    class Cache:
+        def __init__(self, payloads):
+            self.payloads, self.ready, self.rows, self.callers = payloads, set(), {}, set()
+            self.arena = SimpleNamespace(write=lambda start, e: (self.callers.add(th.get_ident()),
+                                                                 self.rows.__setitem__(start, e.clone())))
+
+        def get_items_embed(self, ids):
+            return [i in self.ready for i in ids]
+
+        def set_items_embed(self, ids):
+            self.callers.add(th.get_ident())
+            self.ready.update(ids)
+
+        def get_payload(self, uid):
+            self.callers.add(th.get_ident())
+            return self.payloads[uid]
+
+    items = [{"uuid": u, "token_num": 1 + u % 3, "start_index_in_embed_cache": 10 * u} for u in range(7)]
+    towers = [Tower(), Tower(), Tower()]
+    cache = Cache({u: bytes([u + 1]) * 4 for u in range(7)})
+    sent = []
+    vm = VisualManager(SimpleNamespace(), None, cache, sent.append, None, infer_batch_size=2, towers=towers)
+    g = GroupReqIndexes(8, {"images": items + [items[0]], "audios": []}, [0], 0.0)
+    vm.handle_many([g])
+    assert sent == [g] and cache.ready == set(range(7)) and cache.callers == {main}
+    assert [sorted(t.batches, reverse=True) for t in towers] == [[2, 1], [2], [2]]     # 3 + 2 + 2 pictures
+    assert all(t.threads and main not in t.threads for t in towers)
+    for it in items:
+        assert torch.equal(cache.rows[it["start_index_in_embed_cache"]], torch.full((it["token_num"], 4), it["uuid"] + 1.0))
+    # one picture: no threads, the first replica does it
+    cache.payloads[9] = bytes([42]) * 4
+    vm.handle_many([GroupReqIndexes(16, {"images": [{"uuid": 9, "token_num": 2, "start_index_in_embed_cache": 99}],
+                                        "audios": []}, [1], 0.0)])
+    assert main in towers[0].threads and float(cache.rows[99][0, 0]) == 42.0
+
+    clips = {u: np.full(8, u + 0.5, dtype=np.float32).tobytes() for u in range(5)}
+    acache = Cache(clips)
+    atowers = [Tower(), Tower()]
+    am = AudioManager(SimpleNamespace(), None, acache, sent.append, None, infer_batch_size=2, towers=atowers)
+    am.handle(GroupReqIndexes(24, {"images": [], "audios": [{"uuid": u, "token_num": 2, "start_index_in_embed_cache": u}
+                                                           for u in range(5)]}, [2], 0.0))
+    assert acache.ready == set(range(5)) and acache.callers == {main} and all(t.threads for t in atowers)
+    assert float(acache.rows[3][0, 0]) == 3.5
+
+    assert replica_devices(None, 3) == [torch.device("cpu")] * 3 or torch.cuda.is_available()
+    out = encode_on_replicas([Tower(), Tower()], 5, 2, lambda t, idx: [torch.tensor(float(i)) for i in idx])
+    assert [float(x) for x in out] == [0.0, 1.0, 2.0, 3.0, 4.0]
