@@ -52,6 +52,7 @@ class BackendArgs:
     # of step k (token append, finish checks, publishing) runs while the GPU executes step k + 1
     enable_decode_overlap: bool = True
     linear_att_hash_page_size: int = 512   # hybrid models: token granularity of the recurrent-state snapshots
+    state_host_cache_bytes: int = 0        # hybrid models: pinned host room for snapshots pushed out of the GPU table
 
 
 class PinnedRing:
@@ -121,7 +122,8 @@ class ModelBackend:
         if self.radix_cache is not None and not getattr(model, "supports_prefix_cache", True):
             from .state_cache import StateSnapshotCache
 
-            self.state_cache = StateSnapshotCache(model, self.args.linear_att_hash_page_size)
+            self.state_cache = StateSnapshotCache(model, self.args.linear_att_hash_page_size,
+                                                  host_bytes=self.args.state_host_cache_bytes)
             self.ctx.state_cache = self.state_cache
         if self.args.cpu_cache_bytes > 0 and self.radix_cache is not None and self.state_cache is None:
             from .host_kv_cache import HostKVCache

@@ -44,7 +44,8 @@ class LLM:
                         cpu_cache_page_tokens=int(model_kw.pop("cpu_cache_page_tokens", 256)),
                         disk_cache_dir=model_kw.pop("disk_cache_dir", None),
                         disk_cache_bytes=int(model_kw.pop("disk_cache_bytes", 0)),
-                        linear_att_hash_page_size=int(model_kw.pop("linear_att_hash_page_size", 512)))
+                        linear_att_hash_page_size=int(model_kw.pop("linear_att_hash_page_size", 512)),
+                        state_host_cache_bytes=int(model_kw.pop("state_host_cache_bytes", 0)))
         tp_fused = model_kw.pop("tp_fused", None)
         no_pipeline = bool(model_kw.pop("disable_prefill_pipeline", False))
         if tp_fused is None and self.ps.tp_size > 1 and self.ps.device.type == "cuda" \

@@ -171,6 +171,27 @@ class Qwen3NextLM(Qwen3MoeLM):
         self.conv_state[:, req_idx] = self.conv_snap[slot]
         self.ssm_state[:, req_idx] = self.ssm_snap[slot]
 
+    # host tier of the snapshot table (engine/state_cache.py)
+    def alloc_host_snapshots(self, nbytes: int) -> int:
+        """Pinned host room for as many snapshots as fit into `nbytes`; returns their number."""
+        one = self.conv_snap[0].numel() * self.conv_snap.element_size() + \
+            self.ssm_snap[0].numel() * self.ssm_snap.element_size()
+        k = int(nbytes) // max(one, 1)
+        if k <= 0:
+            return 0
+        pin = self.device.type == "cuda"
+        self.conv_host = torch.empty((k, *self.conv_snap.shape[1:]), dtype=self.conv_snap.dtype, pin_memory=pin)
+        self.ssm_host = torch.empty((k, *self.ssm_snap.shape[1:]), dtype=self.ssm_snap.dtype, pin_memory=pin)
+        return k
+
+    def export_state_snapshot(self, slot: int, host_slot: int):
+        self.conv_host[host_slot].copy_(self.conv_snap[slot])      # synchronous: the GPU slot is reused right after
+        self.ssm_host[host_slot].copy_(self.ssm_snap[slot])
+
+    def import_state_snapshot(self, host_slot: int, slot: int):
+        self.conv_snap[slot].copy_(self.conv_host[host_slot], non_blocking=True)
+        self.ssm_snap[slot].copy_(self.ssm_host[host_slot], non_blocking=True)
+
     def commit_verify(self, n_keep):
         """After a verification pass (`verify_pass=True`) over the batch: request b keeps its first n_keep[b] >= 1
         positions; the recurrent state of every linear layer is set to the state after that position."""

@@ -232,8 +232,7 @@ COMPAT_ONLY_FLAGS = (
     "enable_prefill_cudagraph", "prefill_cudagraph_max_handle_token",
     "pd_trans_mode",
     "config_server_visual_redis_port", "vit_quant_type", "vit_quant_cfg", "visual_tp", "audio_tp",
-    "linear_att_page_block_num",
-    "disable_linear_att_small_page_cpu_cache", "hypercorn_config", "enable_mps",
+    "linear_att_page_block_num", "hypercorn_config", "enable_mps",
     "enable_torch_memory_saver")
 
 

@@ -118,7 +118,10 @@ def _build_model_and_backend(args: StartArgs, ps):
                         cpu_cache_page_tokens=args.cpu_cache_token_page_size,
                         disk_cache_dir=args.disk_cache_dir if args.enable_disk_cache else None,
                         disk_cache_bytes=int(args.disk_cache_storage_size * (1 << 30)) if args.enable_disk_cache else 0,
-                        linear_att_hash_page_size=int(getattr(args, "linear_att_hash_page_size", 512) or 512))
+                        linear_att_hash_page_size=int(getattr(args, "linear_att_hash_page_size", 512) or 512),
+                        state_host_cache_bytes=int(args.cpu_cache_storage_size * (1 << 30)) if (
+                            args.enable_cpu_cache and not getattr(args, "disable_linear_att_small_page_cpu_cache", False))
+                        else 0)
     from ...engine.mode_backends import select_backend_class
 
     backend_cls = select_backend_class(args)

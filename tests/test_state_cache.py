@@ -99,3 +99,68 @@ def test_recurrent_state_kept_in_bf16():
     got = [o["token_ids"] for o in llm.generate(prompts, sp)]
     same = sum(a == b for x, y in zip(want, got) for a, b in zip(x, y))
     assert same >= 12          # bf16 state: nearly the same greedy tokens on this toy model
+
+
+def test_host_tier_keeps_snapshots_that_fall_out_of_the_gpu_table():
+    ids = np.arange(200)
+
+    class M:
+        state_snapshot_slots = 1
+
+        def __init__(self):
+            self.gpu, self.host, self.req_state = {}, {}, {}
+
+        def save_state_snapshot(self, slot, req):
+            self.gpu[slot] = self.req_state[req]
+
+        def load_state_snapshot(self, slot, req):
+            self.req_state[req] = self.gpu[slot]
+
+        def alloc_host_snapshots(self, nbytes):
+            return nbytes // 100
+
+        def export_state_snapshot(self, slot, h):
+            self.host[h] = self.gpu[slot]
+
+        def import_state_snapshot(self, h, slot):
+            self.gpu[slot] = self.host[h]
+
+    m = M()
+    c = StateSnapshotCache(m, 16, host_bytes=250)       # one GPU slot, two host slots
+    assert c.host_slots == 2
+    m.req_state = {0: "s32", 1: "s64", 2: "s96", 3: "s128"}
+    assert c.save(0, ids[:32]) and c.save(1, ids[:64])               # 32 moves to the host
+    assert c.stats["to_host"] == 1 and [v[1] for v in c.host_index.values()] == [32]
+    assert c.lookup(ids, 63) == (32, 0)                              # found on the host, back in the GPU slot;
+    assert c.stats["from_host"] == 1 and m.gpu[0] == "s32"           # 64 took its place on the host
+    assert [v[1] for v in c.host_index.values()] == [64]
+    c.restore(0, 7, 32)
+    assert m.req_state[7] == "s32"
+    assert c.save(2, ids[:96]) and c.save(3, ids[:128])              # host: 64, 32, then 96 pushes 64 out for good
+    assert sorted(v[1] for v in c.host_index.values()) == [32, 96]
+    assert c.lookup(ids, 80) == (32, 0) and m.gpu[0] == "s32"        # 64 is gone, 32 is the longest left below 80
+    assert c.lookup(ids, 200)[0] == 128                              # (now on the host) comes back
+    m.req_state[4] = "s128b"
+    assert not c.save(4, ids[:128])                                  # already on the GPU: only refreshed
+    c.clear()
+    assert c.lookup(ids, 200) == (0, None) and len(c.host_free) == 2
+
+
+def test_second_turn_starts_from_a_snapshot_kept_on_the_host():
+    rng = np.random.default_rng(3)
+    sp = {"max_new_tokens": 8, "ignore_eos": True}
+    a = rng.integers(3, 300, 100).tolist()
+    b = rng.integers(3, 300, 100).tolist()
+    plain = LLM(config=CFG, **KW)
+    a2 = a + plain.generate([a], sp)[0]["token_ids"] + rng.integers(3, 300, 20).tolist()
+    want = plain.generate([a2], sp)[0]["token_ids"]
+
+    llm = LLM(config=CFG, state_snapshot_slots=1, linear_att_hash_page_size=32, state_host_cache_bytes=8 << 20, **KW)
+    sc = llm.backend.state_cache
+    assert sc.host_slots > 1
+    llm.generate([a], sp)
+    llm.generate([b], sp)             # the only GPU slot now holds a snapshot of b
+    assert sc.stats["to_host"] >= 1
+    got = llm.generate([a2], sp)[0]
+    assert got["token_ids"] == want and sc.stats["from_host"] == 1 and sc.stats["hits"] == 1
+    assert got["prompt_cache_len"] == 96       # the prompt's last boundary (decoding 8 tokens crossed no other one)
