@@ -400,8 +400,9 @@ class PDDecodeBackend(ModelBackend):
         mine = torch.full((self.MAX_KEYS,), -1, dtype=torch.int64)
         k = keys[: self.MAX_KEYS]
         mine[: len(k)] = torch.tensor(k, dtype=torch.int64)
-        allk = torch.empty((self.tp_size, self.MAX_KEYS), dtype=torch.int64)
-        dist.all_gather_into_tensor(allk, mine, group=self.cpu_group)
+        flat = torch.empty(self.tp_size * self.MAX_KEYS, dtype=torch.int64)   # gloo wants the output one-dimensional
+        dist.all_gather_into_tensor(flat, mine, group=self.cpu_group)
+        allk = flat.view(self.tp_size, self.MAX_KEYS)
         common = set(allk[0].tolist())
         for i in range(1, self.tp_size):
             common &= set(allk[i].tolist())
