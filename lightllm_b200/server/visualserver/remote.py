@@ -4,7 +4,8 @@ pictures to one of the registered encoders.
 
 An encoder listens on a ZeroMQ ROUTER socket (`--visual_rpyc_port`).  A request is one pickled
 `(request id, [(item, payload bytes), ...])`; the answer carries the embeddings inline, one tensor per item, so
-the two sides need no shared file system.  With `--afs_image_embed_dir` (a directory that all servers see) the
+the two sides need no shared file system.  Every message carries an HMAC-SHA256 signature (`LLB_VIT_AUTHKEY`, else
+a key derived from the config server's address) that is checked before the body is unpickled.  With `--afs_image_embed_dir` (a directory that all servers see) the
 encoders also keep every embedding there under the picture's content hash, at most `--afs_embed_capacity` files
 (least recently used first out), and both sides look there before they compute or ask: a picture embedded once
 is not sent again, whichever server meets it next.
@@ -19,6 +20,8 @@ lightllm/server/embed_cache/afs_utils.py (its ready marks live in redis; here th
 from __future__ import annotations
 
 import base64
+import hashlib
+import hmac
 import itertools
 import os
 import pickle
@@ -37,6 +40,29 @@ import zmq
 from ...utils.process_utils import set_proc_title, start_parent_check_thread
 from ..core.objs.start_args import StartArgs
 from .manager import VisualManager, build_vision_tower, open_req_table
+
+
+def auth_key(args=None) -> bytes:
+    """Key of the message signatures between servers and encoders.  `LLB_VIT_AUTHKEY` (the same on every machine
+    of a deployment) or, without it, a key derived from the config server's address: that keeps other deployments
+    out, but not someone who knows the address."""
+    k = os.environ.get("LLB_VIT_AUTHKEY")
+    if k:
+        return hashlib.sha256(k.encode()).digest()
+    where = f"{getattr(args, 'config_server_host', None)}:{getattr(args, 'config_server_port', None)}"
+    return hashlib.sha256(("llb-vit:" + where).encode()).digest()
+
+
+def seal(key: bytes, obj) -> list:
+    """Message frames: signature, pickled body.  The body is only unpickled after the signature has been checked."""
+    body = pickle.dumps(obj, protocol=pickle.HIGHEST_PROTOCOL)
+    return [hmac.new(key, body, hashlib.sha256).digest(), body]
+
+
+def unseal(key: bytes, frames):
+    if len(frames) != 2 or not hmac.compare_digest(frames[0], hmac.new(key, frames[1], hashlib.sha256).digest()):
+        raise PermissionError("message signature does not match (different LLB_VIT_AUTHKEY / config server?)")
+    return pickle.loads(frames[1])
 
 
 def remote_timeout_s() -> float:
@@ -134,8 +160,10 @@ def shared_dir_of(args) -> Optional[SharedEmbedDir]:
 class VisualOnlyServer:
     """Serves embedding requests with a local tower."""
 
-    def __init__(self, tower, sock, shared: Optional[SharedEmbedDir] = None, infer_batch_size: int = 8):
+    def __init__(self, tower, sock, shared: Optional[SharedEmbedDir] = None, infer_batch_size: int = 8,
+                 key: Optional[bytes] = None):
         self.tower, self.sock, self.shared = tower, sock, shared
+        self.key = key or auth_key()
         self.infer_batch_size = max(1, int(infer_batch_size or 1))
         self.served = 0          # tower passes' pictures (not counting shared-directory hits)
 
@@ -172,15 +200,18 @@ class VisualOnlyServer:
     def serve_one(self, timeout_ms: Optional[int] = None) -> bool:
         if timeout_ms is not None and not self.sock.poll(timeout_ms):
             return False
-        ident, raw = self.sock.recv_multipart()
+        ident, *frames = self.sock.recv_multipart()
         rid = None
         try:
-            rid, pairs = pickle.loads(raw)
+            rid, pairs = unseal(self.key, frames)
             reply = (rid, "ok", self.encode(pairs))
+        except PermissionError as e:
+            print(f"[visual_only] dropped a request: {e}", flush=True)
+            return True               # no answer to a stranger
         except Exception as e:  # noqa: BLE001
             traceback.print_exc()
             reply = (rid, "error", f"{type(e).__name__}: {e}")
-        self.sock.send_multipart([ident, pickle.dumps(reply, protocol=pickle.HIGHEST_PROTOCOL)])
+        self.sock.send_multipart([ident] + seal(self.key, reply))
         return True
 
     def loop(self, stop: Optional[threading.Event] = None):
@@ -226,7 +257,7 @@ def start_visual_only_process(args_dict: dict, pipe_writer=None):
         tower = build_vision_tower(args, device, torch.bfloat16 if device.type == "cuda" else torch.float32)
         sock = zmq.Context(2).socket(zmq.ROUTER)
         sock.bind(f"tcp://{args.host if args.host not in (None, '') else '0.0.0.0'}:{args.visual_rpyc_port}")
-        server = VisualOnlyServer(tower, sock, shared_dir_of(args), args.visual_infer_batch_size or 8)
+        server = VisualOnlyServer(tower, sock, shared_dir_of(args), args.visual_infer_batch_size or 8, key=auth_key(args))
         node = VitNode(getattr(args, "visual_node_id", None) or uuid.uuid4().int & ((1 << 62) - 1),
                        args.host if args.host not in (None, "", "0.0.0.0") else "127.0.0.1", int(args.visual_rpyc_port))
         threading.Thread(target=keep_registered, args=(node, args.config_server_host, int(args.config_server_port)),
@@ -302,12 +333,14 @@ class ProxyVisualManager(VisualManager):
 
     def __init__(self, args, cache=None, send_next=None, recv=None, infer_batch_size: int = 8, try_recv=None,
                  send_batch_size: int = 1, encoders: Optional[RemoteEncoders] = None,
-                 shared: Optional[SharedEmbedDir] = None, timeout_s: Optional[float] = None):
+                 shared: Optional[SharedEmbedDir] = None, timeout_s: Optional[float] = None,
+                 key: Optional[bytes] = None):
         super().__init__(args, None, cache, send_next, recv, infer_batch_size, try_recv, send_batch_size)
         self.encoders = encoders or RemoteEncoders(getattr(args, "config_server_host", None),
                                                    getattr(args, "config_server_port", None))
         self.shared = shared if shared is not None else shared_dir_of(args)
         self.timeout_s = remote_timeout_s() if timeout_s is None else timeout_s
+        self.key = key or auth_key(args)
         self._rid = itertools.count(1)
 
     def _publish(self, item: dict, emb: torch.Tensor):
@@ -318,7 +351,7 @@ class ProxyVisualManager(VisualManager):
     def _ask(self, nid: int, pairs) -> List[torch.Tensor]:
         sock = self.encoders.socks[nid]
         rid = next(self._rid)
-        sock.send(pickle.dumps((rid, pairs), protocol=pickle.HIGHEST_PROTOCOL))
+        sock.send_multipart(seal(self.key, (rid, pairs)))
         deadline = time.time() + self.timeout_s
         while True:
             left = deadline - time.time()
@@ -326,7 +359,10 @@ class ProxyVisualManager(VisualManager):
                 if left <= 0:
                     raise TimeoutError(f"encoder {self.encoders.nodes[nid].host_ip_port}: no answer in {self.timeout_s:.0f} s")
                 continue
-            got, status, body = pickle.loads(sock.recv())
+            try:
+                got, status, body = unseal(self.key, sock.recv_multipart())
+            except PermissionError:
+                continue
             if got != rid:
                 continue              # a late answer to a request that was given up
             if status != "ok":

@@ -120,6 +120,16 @@ def test_proxy_asks_encoders_and_reuses_the_shared_directory(tmp_path):
             vm.handle_many([GroupReqIndexes(32, {"images": [_item(4, "m4", 2, 20)], "audios": []}, [3], 0.0)])
             assert 4 in cache.ready
             enc.refresh(force=True)
+        # a sender with another key gets no answer and the tower is not run for it
+        before = len(tower.calls)
+        stranger = remote.ProxyVisualManager(args, _Cache({8: b"uvwxU"}), sent.append, None, encoders=enc, shared=None,
+                                             timeout_s=0.5, key=b"k" * 32)
+        try:
+            stranger._ask(1, [(_item(8, "m8", 1, 40), b"uvwxU")])
+            raise AssertionError("a request signed with another key was answered")
+        except TimeoutError:
+            pass
+        assert len(tower.calls) == before
         # an encoder that leaves the list is dropped
         listed[:] = [remote.VitNode(1, "127.0.0.1", port)]
         enc.refresh(force=True)
