@@ -279,11 +279,13 @@ async def startup_event():
 
     if multinode_relay.enabled(args):
         if args.node_rank == 0:
-            relay = multinode_relay.RelayMaster(args.multinode_httpmanager_port, args.nnodes - 1)
+            relay = multinode_relay.RelayMaster(args.multinode_httpmanager_port, args.nnodes - 1,
+                                                key=multinode_relay.relay_key(args))
             await relay.wait_peers()
             g_objs.httpserver_manager.relay_master = relay
         else:
-            relay = multinode_relay.RelayFollower(args.nccl_host, args.multinode_httpmanager_port, args.node_rank)
+            relay = multinode_relay.RelayFollower(args.nccl_host, args.multinode_httpmanager_port, args.node_rank,
+                                                  key=multinode_relay.relay_key(args))
             await relay.hello()
             g_objs.relay_task = loop.create_task(relay.follow(g_objs.httpserver_manager))
     if args.run_mode in ("prefill", "decode"):

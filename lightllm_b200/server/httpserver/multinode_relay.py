@@ -7,18 +7,25 @@ The other nodes produce the same tokens and simply drop them.
 
 Wire: node 0 binds a ZeroMQ ROUTER socket on `--multinode_httpmanager_port`; every other node connects a DEALER
 to `--nccl_host` and says hello with its node rank; node 0 serves requests once all have said hello, so nothing is
-relayed into the void.  Reference: lightllm/server/httpserver/manager.py:91-104, 201-260 (multinode_req_manager,
+relayed into the void.  Messages are signed (`LLB_RELAY_AUTHKEY`, else a key derived from `--nccl_host` and the
+port) and checked before they are unpickled.  Reference: lightllm/server/httpserver/manager.py:91-104, 201-260 (multinode_req_manager,
 loop_for_request, transfer of (prompt, sampling_params, multimodal_params) to the slave nodes).
 """
 from __future__ import annotations
 
 import asyncio
-import pickle
 import time
 from typing import Dict
 
 import zmq
 import zmq.asyncio
+
+from ...utils.signed_msg import derive_key, seal, unseal
+
+
+def relay_key(args) -> bytes:
+    return derive_key("LLB_RELAY_AUTHKEY", f"{getattr(args, 'nccl_host', None)}:"
+                                           f"{getattr(args, 'multinode_httpmanager_port', None)}")
 
 
 def enabled(args) -> bool:
@@ -26,7 +33,8 @@ def enabled(args) -> bool:
 
 
 class RelayMaster:
-    def __init__(self, port: int, n_peers: int, host: str = "0.0.0.0"):
+    def __init__(self, port: int, n_peers: int, host: str = "0.0.0.0", key: bytes = b""):
+        self.key = key or derive_key("LLB_RELAY_AUTHKEY", str(port))
         self.sock = zmq.asyncio.Context.instance().socket(zmq.ROUTER)
         self.sock.bind(f"tcp://{host}:{port}")
         self.n_peers = n_peers
@@ -40,24 +48,28 @@ class RelayMaster:
                 if left <= 0:
                     raise TimeoutError(f"{self.n_peers - len(self.peers)} node(s) never connected to the request relay")
                 continue
-            ident, payload = await self.sock.recv_multipart()
-            msg = pickle.loads(payload)
+            ident, *frames = await self.sock.recv_multipart()
+            try:
+                msg = unseal(self.key, frames)
+            except PermissionError as e:
+                print(f"[relay] dropped a message: {e}", flush=True)
+                continue
             if msg[0] == "hello":
                 self.peers[int(msg[1])] = ident
-                await self.sock.send_multipart([ident, pickle.dumps(("welcome",))])
+                await self.sock.send_multipart([ident] + seal(self.key, ("welcome",)))
 
     async def relay(self, group_req_id: int, prompt_ids, sampling_params, multimodal_params):
-        payload = pickle.dumps(("req", group_req_id, list(prompt_ids), bytes(sampling_params), multimodal_params),
-                               protocol=pickle.HIGHEST_PROTOCOL)
+        frames = seal(self.key, ("req", group_req_id, list(prompt_ids), bytes(sampling_params), multimodal_params))
         for ident in self.peers.values():
-            await self.sock.send_multipart([ident, payload])
+            await self.sock.send_multipart([ident] + frames)
 
     def close(self):
         self.sock.close(linger=0)
 
 
 class RelayFollower:
-    def __init__(self, master_host: str, port: int, node_rank: int):
+    def __init__(self, master_host: str, port: int, node_rank: int, key: bytes = b""):
+        self.key = key or derive_key("LLB_RELAY_AUTHKEY", str(port))
         self.sock = zmq.asyncio.Context.instance().socket(zmq.DEALER)
         self.sock.connect(f"tcp://{master_host}:{port}")
         self.node_rank = node_rank
@@ -66,9 +78,9 @@ class RelayFollower:
     async def hello(self, timeout_s: float = 600.0):
         t0 = time.time()
         while time.time() - t0 < timeout_s:       # node 0 may come up later than this node
-            await self.sock.send(pickle.dumps(("hello", self.node_rank)))
+            await self.sock.send_multipart(seal(self.key, ("hello", self.node_rank)))
             if await self.sock.poll(1000):
-                assert pickle.loads(await self.sock.recv())[0] == "welcome"
+                assert unseal(self.key, await self.sock.recv_multipart())[0] == "welcome"
                 return
         raise TimeoutError("node 0's request relay did not answer")
 
@@ -84,7 +96,11 @@ class RelayFollower:
                 print(f"[relay] node {self.node_rank}: request {gid} ended with {type(e).__name__}: {e}", flush=True)
 
         while True:
-            msg = pickle.loads(await self.sock.recv())
+            try:
+                msg = unseal(self.key, await self.sock.recv_multipart())
+            except PermissionError as e:
+                print(f"[relay] node {self.node_rank}: dropped a message: {e}", flush=True)
+                continue
             if msg[0] != "req":
                 continue
             _, gid, prompt_ids, sp_bytes, mm = msg

@@ -20,8 +20,6 @@ lightllm/server/embed_cache/afs_utils.py (its ready marks live in redis; here th
 from __future__ import annotations
 
 import base64
-import hashlib
-import hmac
 import itertools
 import os
 import pickle
@@ -38,31 +36,16 @@ import torch
 import zmq
 
 from ...utils.process_utils import set_proc_title, start_parent_check_thread
+from ...utils.signed_msg import derive_key, seal, unseal
 from ..core.objs.start_args import StartArgs
 from .manager import VisualManager, build_vision_tower, open_req_table
 
 
 def auth_key(args=None) -> bytes:
-    """Key of the message signatures between servers and encoders.  `LLB_VIT_AUTHKEY` (the same on every machine
-    of a deployment) or, without it, a key derived from the config server's address: that keeps other deployments
-    out, but not someone who knows the address."""
-    k = os.environ.get("LLB_VIT_AUTHKEY")
-    if k:
-        return hashlib.sha256(k.encode()).digest()
-    where = f"{getattr(args, 'config_server_host', None)}:{getattr(args, 'config_server_port', None)}"
-    return hashlib.sha256(("llb-vit:" + where).encode()).digest()
-
-
-def seal(key: bytes, obj) -> list:
-    """Message frames: signature, pickled body.  The body is only unpickled after the signature has been checked."""
-    body = pickle.dumps(obj, protocol=pickle.HIGHEST_PROTOCOL)
-    return [hmac.new(key, body, hashlib.sha256).digest(), body]
-
-
-def unseal(key: bytes, frames):
-    if len(frames) != 2 or not hmac.compare_digest(frames[0], hmac.new(key, frames[1], hashlib.sha256).digest()):
-        raise PermissionError("message signature does not match (different LLB_VIT_AUTHKEY / config server?)")
-    return pickle.loads(frames[1])
+    """Key of the message signatures between servers and encoders: `LLB_VIT_AUTHKEY` (the same on every machine of
+    a deployment) or, without it, a key derived from the config server's address."""
+    return derive_key("LLB_VIT_AUTHKEY", f"{getattr(args, 'config_server_host', None)}:"
+                                         f"{getattr(args, 'config_server_port', None)}")
 
 
 def remote_timeout_s() -> float:
