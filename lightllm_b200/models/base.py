@@ -379,7 +379,16 @@ class TransformerLM:
 
     def _init_rope(self):
         n = max(self.max_seq_length + 8, 16)
-        self.cos, self.sin = ref.build_rope_cache(n, self.rot_dim, self.rope_theta, self.rope_scaling,
+        theta = self.rope_theta
+        # LIGHTLLM_NTK_ALPHA > 1: NTK-aware context extension without fine-tuning, by raising the rotary base
+        # (reference: lightllm/models/llama/model.py:117-126)
+        try:
+            alpha = float(os.environ.get("LLB_NTK_ALPHA", os.environ.get("LIGHTLLM_NTK_ALPHA", "1")))
+        except ValueError:
+            alpha = 1.0
+        if alpha > 1.0 and self.rot_dim > 2 and not self.rope_scaling:
+            theta = theta * alpha ** (self.rot_dim / (self.rot_dim - 2))
+        self.cos, self.sin = ref.build_rope_cache(n, self.rot_dim, theta, self.rope_scaling,
                                                   device=self.device)
 
     # ------------------------------------------------------------------ memory

@@ -3,12 +3,17 @@
 from __future__ import annotations
 
 import json
+import os
 
 from fastapi import Request
 from .api_stream_obj import stream_response
 from fastapi.responses import JSONResponse, Response, StreamingResponse
 
 from .core.objs.sampling_params import SamplingParams
+
+
+# `RETURN_LIST=1`: the non-streaming answer is wrapped in a list, as the hosted inference API does
+RETURN_LIST = os.getenv("RETURN_LIST", "FALSE").upper() in ("ON", "TRUE", "1")
 
 
 def _params(d: dict) -> dict:
@@ -44,7 +49,7 @@ async def tgi_generate_impl(request: Request, g) -> Response:
         if len(texts) > 1:
             ret["details"]["best_of_sequences"] = [{"generated_text": "".join(texts[i]), "tokens": toks[i]}
                                                    for i in sorted(texts)[1:]]
-    return JSONResponse([ret])
+    return JSONResponse([ret] if RETURN_LIST else ret)
 
 
 async def tgi_generate_stream_impl(request: Request, g) -> Response:

@@ -23,7 +23,7 @@ from typing import List, Optional, Tuple
 
 import numpy as np
 
-from .sampling_params import SamplingParams
+from .sampling_params import MAX_PROMPT_LOGPROBS, SamplingParams
 from .shm_array import ShmArray
 
 LIGHTLLM_OUT_TOKEN_QUEUE_SIZE = int(os.getenv("LIGHTLLM_OUT_TOKEN_QUEUE_SIZE", 8))
@@ -254,7 +254,7 @@ class Req(ctypes.Structure):
     def create_logprobs_shm_array(self):
         self.shm_logprobs = ShmArray(self._name("logprobs"), (self.alloc_shm_numpy_len,), np.float32).create_shm()
 
-    PROMPT_TOPK_MAX = 20
+    PROMPT_TOPK_MAX = MAX_PROMPT_LOGPROBS
 
     def prompt_meta_cols(self) -> int:
         """Columns of the per-position prompt record: rank of the prompt token, then k ids and k logprobs of the

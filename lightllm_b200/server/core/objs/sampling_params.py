@@ -23,6 +23,10 @@ GRAMMAR_MAX_BYTES = int(os.getenv("LIGHTLLM_GRAMMAR_CONSTRAINT_MAX_LENGTH", 2048
 JSON_SCHEMA_MAX_BYTES = int(os.getenv("LIGHTLLM_JSON_SCHEMA_MAX_LENGTH", 2048))
 MAX_BEST_OF = 8
 INPUT_PENALTY_DEFAULT = os.getenv("INPUT_PENALTY", "False").upper() in ("ON", "TRUE", "1")
+# most alternatives per prompt position that `prompt_logprobs` may ask for (they are kept in shared memory per request)
+MAX_PROMPT_LOGPROBS = int(os.getenv("LIGHTLLM_MAX_PROMPT_LOGPROBS", 20))
+# default of `skip_special_tokens` for requests that do not say (the OpenAI routes set it themselves)
+SKIP_SPECIAL_TOKENS = os.getenv("SKIP_SPECIAL_TOKENS", "False").upper() in ("ON", "TRUE", "1")
 
 
 class ParamError(ValueError):
@@ -273,7 +277,7 @@ class SamplingParams(ctypes.Structure):
         self.suggested_dp_index = int(kw.get("suggested_dp_index", -1))
         self.pd_master_node_id.set(int(kw.get("pd_master_node_id", 0)))
         self.pd_kv_trans_params.set(kw.get("pd_kv_trans_params"))
-        self.skip_special_tokens = bool(kw.get("skip_special_tokens", True))
+        self.skip_special_tokens = bool(kw.get("skip_special_tokens", SKIP_SPECIAL_TOKENS))
         self.add_special_tokens = bool(kw.get("add_special_tokens", True))
         self.add_spaces_between_special_tokens = bool(kw.get("add_spaces_between_special_tokens", True))
         self.print_eos_token = bool(kw.get("print_eos_token", False))
@@ -282,6 +286,8 @@ class SamplingParams(ctypes.Structure):
         self.seed = -1 if seed is None else int(seed)
         pl = kw.get("prompt_logprobs", -1)
         self.prompt_logprobs = -1 if pl is None else int(pl)
+        if self.prompt_logprobs < -1 or self.prompt_logprobs > MAX_PROMPT_LOGPROBS:
+            raise ValueError(f"prompt_logprobs must be in [-1, {MAX_PROMPT_LOGPROBS}], got {self.prompt_logprobs}")
         if not self.do_sample:  # greedy
             self.temperature, self.top_p, self.top_k = 1.0, 1.0, 1
         elif self.temperature < 1e-5:

@@ -15,6 +15,7 @@ glm47, kimi_k2, qwen3_coder).
 from __future__ import annotations
 
 import json
+import os
 import re
 from dataclasses import dataclass
 from typing import Any, Callable, Dict, List, Optional, Tuple
@@ -211,6 +212,8 @@ class FunctionCallParser:
         if tool_call_parser not in _FORMATS:
             raise ValueError(f"unknown tool call parser {tool_call_parser!r}; known: {sorted(_FORMATS)}")
         self.fmt = _FORMATS[tool_call_parser]
+        # with LIGHTLLM_ENABLE_TOOL_NAME_CHECK=1 calls to functions that the request did not declare are dropped
+        self.check_names = os.getenv("LIGHTLLM_ENABLE_TOOL_NAME_CHECK", "False").upper() in ("ON", "TRUE", "1")
         self.tool_names = set()
         for t in tools or []:
             fn = getattr(t, "function", None) or (t.get("function") if isinstance(t, dict) else None)
@@ -228,7 +231,7 @@ class FunctionCallParser:
     def _items(self, body: str) -> List[ToolCallItem]:
         out = []
         for name, args in self.fmt.decode(body):
-            if self.tool_names and name not in self.tool_names:
+            if self.check_names and self.tool_names and name not in self.tool_names:
                 continue
             out.append(ToolCallItem(self._index, name, args))
             self._index += 1
@@ -265,7 +268,7 @@ class FunctionCallParser:
         if not js.usable:
             return False
         if name is not None:
-            if self.tool_names and name not in self.tool_names:
+            if self.check_names and self.tool_names and name not in self.tool_names:
                 js.usable = False          # not one of the declared tools: dropped like in the whole-body path
                 js.dropped = True
                 return True

@@ -20,7 +20,10 @@ from typing import Dict
 import zmq
 import zmq.asyncio
 
+from ...utils.log_utils import init_logger
 from ...utils.signed_msg import derive_key, seal, unseal
+
+logger = init_logger(__name__)
 
 
 def relay_key(args) -> bytes:
@@ -52,7 +55,7 @@ class RelayMaster:
             try:
                 msg = unseal(self.key, frames)
             except PermissionError as e:
-                print(f"[relay] dropped a message: {e}", flush=True)
+                logger.warning(f"dropped a message: {e}")
                 continue
             if msg[0] == "hello":
                 self.peers[int(msg[1])] = ident
@@ -93,13 +96,13 @@ class RelayFollower:
                 async for _ in manager.generate(prompt_ids, sp, mm, group_req_id=gid):
                     pass
             except Exception as e:        # a request that fails here fails on node 0 for the same reason
-                print(f"[relay] node {self.node_rank}: request {gid} ended with {type(e).__name__}: {e}", flush=True)
+                logger.warning(f"node {self.node_rank}: request {gid} ended with {type(e).__name__}: {e}")
 
         while True:
             try:
                 msg = unseal(self.key, await self.sock.recv_multipart())
             except PermissionError as e:
-                print(f"[relay] node {self.node_rank}: dropped a message: {e}", flush=True)
+                logger.warning(f"node {self.node_rank}: dropped a message: {e}")
                 continue
             if msg[0] != "req":
                 continue

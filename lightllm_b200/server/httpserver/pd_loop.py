@@ -6,11 +6,18 @@ open, registers, heartbeats every 30 s with the node's load, runs every PDReques
 from __future__ import annotations
 
 import asyncio
+import os
 import pickle
 import traceback
 
 from ..core.objs.sampling_params import SamplingParams
 from ..pd_io_struct import NodeRunStatus, PDHeartbeat, PDPromptIds, PDRegister, PDRequest, PDToken, UpKVStatus
+
+def ws_max_size():
+    """Largest websocket message in bytes; unlimited unless LIGHTLLM_WEBSOCKET_MAX_SIZE says otherwise."""
+    v = os.environ.get("LIGHTLLM_WEBSOCKET_MAX_SIZE")
+    return int(v) if v else None
+
 
 HEARTBEAT_S = 30.0
 RETRY_S = 10.0
@@ -69,7 +76,7 @@ async def pd_master_link(g, master_url: str, connect=None):
     if connect is None:
         import websockets
 
-        connect = lambda url: websockets.connect(url, max_size=None, ping_interval=20)  # noqa: E731
+        connect = lambda url: websockets.connect(url, max_size=ws_max_size(), ping_interval=20)  # noqa: E731
     args = g.args
     reg = PDRegister(node_id_of(args), f"{args.host}:{args.port}", args.run_mode, args.to_dict())
     while True:
@@ -115,7 +122,7 @@ async def kv_status_link(g, master_url: str, queue: "asyncio.Queue[UpKVStatus]",
     if connect is None:
         import websockets
 
-        connect = lambda url: websockets.connect(url, max_size=None)  # noqa: E731
+        connect = lambda url: websockets.connect(url, max_size=ws_max_size())  # noqa: E731
     while True:
         try:
             async with connect(f"{master_url}/kv_move_status") as ws:

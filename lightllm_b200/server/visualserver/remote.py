@@ -36,7 +36,10 @@ import torch
 import zmq
 
 from ...utils.process_utils import set_proc_title, start_parent_check_thread
+from ...utils.log_utils import init_logger
 from ...utils.signed_msg import derive_key, seal, unseal
+
+logger = init_logger(__name__)
 from ..core.objs.start_args import StartArgs
 from .manager import VisualManager, build_vision_tower, open_req_table
 
@@ -189,7 +192,7 @@ class VisualOnlyServer:
             rid, pairs = unseal(self.key, frames)
             reply = (rid, "ok", self.encode(pairs))
         except PermissionError as e:
-            print(f"[visual_only] dropped a request: {e}", flush=True)
+            logger.warning(f"dropped a request: {e}")
             return True               # no answer to a stranger
         except Exception as e:  # noqa: BLE001
             traceback.print_exc()
@@ -221,7 +224,7 @@ def keep_registered(node: VitNode, host: str, port: int, stop: Optional[threadin
                             last = time.time()
                         await asyncio.sleep(0.2)
             except Exception as e:  # noqa: BLE001
-                print(f"[visual_only] config server {host}:{port} not reachable ({type(e).__name__}); retrying", flush=True)
+                logger.warning(f"config server {host}:{port} not reachable ({type(e).__name__}); retrying")
                 await asyncio.sleep(2.0)
 
     asyncio.run(run())
@@ -282,7 +285,7 @@ class RemoteEncoders:
         try:
             listed = {n.node_id: n for n in self._fetch()}
         except Exception as e:  # noqa: BLE001
-            print(f"[visual proxy] cannot list the encoders ({type(e).__name__}: {e})", flush=True)
+            logger.warning(f"cannot list the encoders ({type(e).__name__}: {e})")
             return
         for nid in list(self.nodes):
             if nid not in listed or listed[nid].host_ip_port != self.nodes[nid].host_ip_port:
@@ -379,7 +382,7 @@ class ProxyVisualManager(VisualManager):
                     break
                 except Exception as e:  # noqa: BLE001
                     err = e
-                    print(f"[visual proxy] {e}", flush=True)
+                    logger.warning(f"{e}")
                     self.encoders.drop(nid)      # listed again at the next refresh if it is still registered
                     self.encoders._last = 0.0
             if embs is None:

@@ -1,5 +1,6 @@
 """Tool-call and reasoning parsers: whole texts and streams cut at arbitrary places give the same result."""
 import json
+import os
 
 import pytest
 
@@ -63,7 +64,8 @@ def test_json_arguments_stream_piece_by_piece(step):
 
 
 @pytest.mark.parametrize("step", [1, 3, 1000])
-def test_bodies_that_cannot_be_streamed_are_emitted_whole(step):
+def test_bodies_that_cannot_be_streamed_are_emitted_whole(step, monkeypatch):
+    monkeypatch.setenv("LIGHTLLM_ENABLE_TOOL_NAME_CHECK", "1")
     cases = [("mistral", '[TOOL_CALLS][{"name":"add","arguments":{"a":1}},{"name":"get_weather","arguments":{"city":"x"}}]',
               [("add", {"a": 1}), ("get_weather", {"city": "x"})]),
              ("qwen25", '<tool_call>{"name":"add","arguments":"{\\"a\\": 1}"}</tool_call>', [("add", {"a": 1})]),
@@ -87,8 +89,15 @@ def test_other_call_syntaxes_and_unknown_tools():
             "<｜tool▁call▁end｜><｜tool▁calls▁end｜>")
     _, calls = p.parse_non_stream("ok " + body)
     assert calls[0].name == "add" and json.loads(calls[0].parameters) == {"a": 1, "b": 1}
-    # a call to a function that was not offered is dropped
-    _, calls = FunctionCallParser(TOOLS, "qwen25").parse_non_stream('<tool_call>{"name": "rm_rf", "arguments": {}}</tool_call>')
+    # a call to a function that was not offered passes, unless the name check is switched on
+    undeclared = '<tool_call>{"name": "rm_rf", "arguments": {}}</tool_call>'
+    _, calls = FunctionCallParser(TOOLS, "qwen25").parse_non_stream(undeclared)
+    assert [c.name for c in calls] == ["rm_rf"]
+    os.environ["LIGHTLLM_ENABLE_TOOL_NAME_CHECK"] = "1"
+    try:
+        _, calls = FunctionCallParser(TOOLS, "qwen25").parse_non_stream(undeclared)
+    finally:
+        del os.environ["LIGHTLLM_ENABLE_TOOL_NAME_CHECK"]
     assert calls == []
     assert not FunctionCallParser(TOOLS, "qwen25").has_tool_call("plain text")
     with pytest.raises(ValueError):

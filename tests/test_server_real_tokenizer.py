@@ -103,8 +103,14 @@ def _gen(url, prompt, **params):
 def test_text_prompts_and_incremental_detokenisation(server):
     url, tok = server
     for prompt in ("hello world", "Grüße aus München – 你好世界 😀", "the quick brown fox"):
-        r = _gen(url, prompt, ignore_eos=True, return_details=True, do_sample=True, temperature=3.0, seed=11)
+        r = _gen(url, prompt, ignore_eos=True, return_details=True, do_sample=True, temperature=3.0, seed=11,
+                 skip_special_tokens=True)
         assert r["prompt_tokens"] == len(tok.encode(prompt))
+        # without the parameter special tokens are written out (SKIP_SPECIAL_TOKENS=1 in the server's environment
+        # turns the default around): the same ids, a text that is not shorter
+        shown = _gen(url, prompt, ignore_eos=True, return_details=True, do_sample=True, temperature=3.0, seed=11)
+        assert [t["id"] for t in shown["tokens"]] == [t["id"] for t in r["tokens"]]
+        assert len(shown["generated_text"][0]) >= len(r["generated_text"][0])
         ids = [t["id"] for t in r["tokens"]]
         pieces = "".join(t["text"] for t in r["tokens"])
         assert pieces == r["generated_text"][0]

@@ -150,3 +150,58 @@ def test_compatibility_only_flags_are_reported():
     assert compat_only_flags_in_use(p.parse_args(["--model_dir", "/x"])) == []
     used = compat_only_flags_in_use(p.parse_args(["--model_dir", "/x", "--enable_mps", "--pd_trans_mode", "nixl"]))
     assert sorted(used) == ["enable_mps", "pd_trans_mode"]
+
+
+def test_env_knobs_of_the_reference(monkeypatch):
+    """NTK alpha raises the rotary base; the websocket size limit and the TGI list wrapper follow their variables."""
+    import importlib
+
+    import torch
+
+    from lightllm_b200.engine.llm import LLM
+    from lightllm_b200.ops import reference as ref
+    from lightllm_b200.server.httpserver import pd_loop
+
+    cfg = dict(model_type="llama", hidden_size=64, num_hidden_layers=1, num_attention_heads=2, num_key_value_heads=2,
+               head_dim=32, intermediate_size=128, vocab_size=128, rms_norm_eps=1e-6, rope_theta=1e4, eos_token_id=2)
+    kw = dict(data_type="float32", max_total_token_num=256, running_max_req_size=2, max_req_total_len=64, batch_max_tokens=64)
+    plain = LLM(config=cfg, **kw).model
+    monkeypatch.setenv("LIGHTLLM_NTK_ALPHA", "4")
+    ntk = LLM(config=cfg, **kw).model
+    want_cos, _ = ref.build_rope_cache(plain.cos.shape[0], 32, 1e4 * 4 ** (32 / 30), None, device=torch.device("cpu"))
+    assert torch.allclose(ntk.cos, want_cos) and not torch.allclose(ntk.cos, plain.cos)
+    monkeypatch.delenv("LIGHTLLM_WEBSOCKET_MAX_SIZE", raising=False)
+    assert pd_loop.ws_max_size() is None
+    monkeypatch.setenv("LIGHTLLM_WEBSOCKET_MAX_SIZE", "1048576")
+    assert pd_loop.ws_max_size() == 1 << 20
+    from lightllm_b200.server import api_tgi
+
+    monkeypatch.setenv("RETURN_LIST", "1")
+    assert importlib.reload(api_tgi).RETURN_LIST is True
+    monkeypatch.delenv("RETURN_LIST")
+    assert importlib.reload(api_tgi).RETURN_LIST is False
+
+
+def test_loggers_follow_the_environment(monkeypatch, tmp_path, capsys):
+    import logging
+
+    from lightllm_b200.utils import log_utils
+
+    log_utils.reset_for_tests()
+    monkeypatch.setenv("LIGHTLLM_LOG_LEVEL", "warning")
+    monkeypatch.setenv("LIGHTLLM_LOG_DIR", str(tmp_path / "logs"))
+    lg = log_utils.init_logger("lightllm_b200.server.somewhere")
+    assert lg is log_utils.init_logger("lightllm_b200.server.somewhere") and lg.name == "lightllm_b200.server.somewhere"
+    lg.info("quiet")
+    lg.warning("loud %d", 7)
+    out = capsys.readouterr().out
+    assert "loud 7" in out and "quiet" not in out and "WARNING" in out and "server.somewhere" in out
+    files = list((tmp_path / "logs").iterdir())
+    assert len(files) == 1 and "loud 7" in files[0].read_text()
+    log_utils.reset_for_tests()
+    monkeypatch.setenv("LLB_LOG_LEVEL", "10")
+    monkeypatch.delenv("LIGHTLLM_LOG_DIR")
+    assert log_utils.log_level() == logging.DEBUG
+    monkeypatch.setenv("LLB_LOG_LEVEL", "nonsense")
+    assert log_utils.log_level() == logging.INFO
+    log_utils.reset_for_tests()
