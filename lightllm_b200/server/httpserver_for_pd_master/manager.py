@@ -13,6 +13,7 @@ Reference: lightllm/server/httpserver_for_pd_master/manager.py, register_loop.py
 from __future__ import annotations
 
 import asyncio
+import os
 import pickle
 import re
 import time
@@ -28,6 +29,20 @@ from .selector import create_selector
 HEARTBEAT_TIMEOUT_S = 90.0
 FIRST_TOKEN_TIMEOUT_S = 600.0
 KV_MOVE_TIMEOUT_S = 182.0
+
+
+def split_block_tokens() -> int:
+    try:
+        return max(1, int(os.environ.get("LLB_PD_SPLIT_MAX_NEW_TOKENS", os.environ.get("LIGHTLLM_PD_SPLIT_MAX_NEW_TOKENS", "2048"))))
+    except ValueError:
+        return 2048
+
+
+def split_max_new_tokens(max_new_tokens: int) -> List[int]:
+    """Budgets of the blocks a request is served in: full blocks, then the rest."""
+    b = split_block_tokens()
+    full, rest = divmod(max(int(max_new_tokens), 0), b)
+    return ([b] * full + ([rest] if rest else [])) or [int(max_new_tokens)]
 
 
 class _ReqState:
@@ -46,6 +61,8 @@ class HttpServerManagerForPDMaster:
         self.nodes: Dict[int, PDClient] = {}
         self.selector = create_selector(args.select_p_d_node_strategy)
         self.reqs: Dict[int, _ReqState] = {}
+        self.alias: Dict[int, int] = {}             # a client request's id -> the id of the block it is in
+        self.block_prompt_ids: Dict[int, List[int]] = {}
         self._next_id = MAX_BEST_OF
         self.paused = False
         self.tokenizer = None
@@ -128,23 +145,79 @@ class HttpServerManagerForPDMaster:
 
     async def generate(self, prompt, sampling_params: SamplingParams, multimodal_params=None, request=None,
                        is_health_req: bool = False):
+        """One client request.  A long `max_new_tokens` is served in blocks of `split_block_tokens()`: decode nodes
+        schedule conservatively (they reserve room for every token a request may still produce), so one request
+        that asks for a huge budget would hold a node's pool on its own; each block is a request of its own on the
+        same pair of nodes whose prompt is the original prompt plus everything generated so far (the prefill
+        node finds all but the last block's tokens in its prefix cache).  Most requests end inside their first
+        block.  Reference: httpserver_for_pd_master/manager.py:204-268, 662-668."""
         if self.paused and not is_health_req:
             raise ServerBusyError("generation is paused")
         if not self.topology_ready():
             raise ServerBusyError("no complete prefill/decode topology is registered")
         if sampling_params.n != 1:
             raise ValueError("pd_master mode serves n == best_of == 1")
-        gid = self._next_id
-        self._next_id += MAX_BEST_OF
+        origin = self._next_id
         p, d = self.selector.select_p_d_node(prompt, sampling_params, multimodal_params)
+        sp = sampling_params.to_dict()
+        total = int(sp["max_new_tokens"])
+        has_media = bool(multimodal_params) and any((multimodal_params or {}).get(k) for k in ("images", "audios")) \
+            if isinstance(multimodal_params, dict) else bool(multimodal_params)
+        blocks = [total] if has_media else split_max_new_tokens(total)   # a picture's ids cannot be sent back as text
+        start = time.time()
+        produced, history, first_meta, prompt_ids = 0, [], None, None
+        block_prompt = prompt
+        try:
+            for bi, budget in enumerate(blocks):
+                last = bi == len(blocks) - 1
+                gid = self._next_id
+                self._next_id += MAX_BEST_OF
+                self.alias[origin] = gid
+                sp_b = dict(sp)
+                sp_b["max_new_tokens"] = budget
+                sp_b["min_new_tokens"] = max(1, int(sp.get("min_new_tokens", 1)) - produced)
+                ended = False
+                block = self._run_block(gid, p, d, block_prompt, sp_b, multimodal_params, request, start)
+                async for _, text, meta, fs in block:
+                    if first_meta is None:
+                        first_meta = dict(meta)
+                        prompt_ids = self.block_prompt_ids.pop(gid, None)
+                    if "id" in meta:
+                        history.append(int(meta["id"]))
+                    if bi > 0:      # what the client sees describes the whole request, not the block
+                        meta = dict(meta)
+                        if "count_output_tokens" in meta:
+                            meta["count_output_tokens"] += produced
+                        for k in ("prompt_tokens", "prompt_cache_len"):
+                            if k in first_meta:
+                                meta[k] = first_meta[k]
+                    if fs.is_finished() and fs.get_finish_reason() == "length" and not last and "error" not in meta:
+                        fs = FinishStatus()              # the block's budget, not the request's
+                    elif fs.is_finished():
+                        ended = True
+                    try:
+                        yield origin, text, meta, fs
+                    except GeneratorExit:
+                        await block.aclose()         # the client went away: the block's bookkeeping ends with it
+                        raise
+                    if ended:
+                        await block.aclose()
+                        return
+                produced += budget
+                if prompt_ids is None or len(history) < produced:
+                    return                                # the stream broke off without an end mark
+                block_prompt = list(prompt_ids) + history
+        finally:
+            self.alias.pop(origin, None)
+
+    async def _run_block(self, gid, p, d, prompt, sp: dict, multimodal_params, request, start):
         chars = len(prompt)
         st = self.reqs[gid] = _ReqState(gid, p, d, chars)
         for n in (p, d):
             n.dispatched_req_num += 1
         p.dispatched_prompt_chars += chars
-        sp = sampling_params.to_dict()
+        sp = dict(sp)
         sp["group_request_id"] = gid
-        start = time.time()
         try:
             await self._send(p, PDRequest(gid, prompt, sp, multimodal_params, peer=d.to_wire()))
             first: PDToken = await asyncio.wait_for(st.tokens.get(), FIRST_TOKEN_TIMEOUT_S)
@@ -153,6 +226,8 @@ class HttpServerManagerForPDMaster:
             meta["first_token_cost_ms"] = (time.time() - start) * 1e3
             if "prompt_cache_len" in meta and meta.get("prompt_tokens"):
                 self.selector.record_prompt_cache_hit_rate(meta["prompt_cache_len"] / meta["prompt_tokens"])
+            if st.prompt_ids is not None:
+                self.block_prompt_ids[gid] = st.prompt_ids
             yield first.sub_req_id, first.text, meta, fs
             if fs.is_finished():
                 return
@@ -183,17 +258,20 @@ class HttpServerManagerForPDMaster:
                     return
         finally:
             self.reqs.pop(gid, None)
+            self.block_prompt_ids.pop(gid, None)
             for n in (p, d):
                 n.dispatched_req_num = max(0, n.dispatched_req_num - 1)
             p.dispatched_prompt_chars = max(0, p.dispatched_prompt_chars - chars)
 
     async def abort(self, group_req_id: int) -> bool:
-        st = self.reqs.get(group_req_id)
+        """`group_req_id` is the id the client's stream carries; the nodes know the running block's id."""
+        gid = self.alias.get(group_req_id, group_req_id)
+        st = self.reqs.get(gid)
         if st is None:
             return False
         for n in (st.p, st.d):
             try:
-                await self._send(n, ("ABORT", group_req_id))
+                await self._send(n, ("ABORT", gid))
             except Exception:
                 pass
         return True
