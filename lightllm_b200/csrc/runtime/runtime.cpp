@@ -278,6 +278,41 @@ LLB_EXPORT int64_t llb_radix_evict(void* h, int64_t need, int32_t* out, int64_t 
   return released;
 }
 
+// Compaction: a node that nobody references and that has exactly one child, also unreferenced, absorbs that
+// child (keys and slots appended, grandchildren adopted).  Chains like that are left behind when a sibling
+// branch is evicted or when a sequence was inserted piece by piece.  Node handles held by callers always have a
+// reference count above zero, so no handle is invalidated.  Returns the number of nodes merged away.
+LLB_EXPORT int64_t llb_radix_merge(void* h) {
+  auto* t = reinterpret_cast<RTree*>(h);
+  int64_t merged = 0;
+  std::vector<RNode*> st;
+  for (auto& kv : t->root->children) st.push_back(kv.second);
+  while (!st.empty()) {
+    RNode* n = st.back();
+    st.pop_back();
+    bool changed = false;
+    while (n->ref == 0 && n->children.size() == 1) {
+      RNode* c = n->children.begin()->second;
+      if (c->ref != 0) break;
+      n->key.insert(n->key.end(), c->key.begin(), c->key.end());
+      n->value.insert(n->value.end(), c->value.begin(), c->value.end());
+      n->time_id = std::max(n->time_id, c->time_id);
+      std::unordered_map<int64_t, RNode*> kids = std::move(c->children);
+      c->children.clear();
+      n->children = std::move(kids);
+      for (auto& kv : n->children) kv.second->parent = n;
+      c->parent = nullptr;
+      c->alive = false;
+      t->graveyard.push_back(c);
+      ++merged;
+      changed = true;
+    }
+    if (changed) t->maybe_evictable(n);
+    for (auto& kv : n->children) st.push_back(kv.second);
+  }
+  return merged;
+}
+
 LLB_EXPORT int64_t llb_radix_node_count(void* h) {
   auto* t = reinterpret_cast<RTree*>(h);
   int64_t c = 0;

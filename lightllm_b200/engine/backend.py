@@ -131,6 +131,10 @@ class ModelBackend:
             self.ctx.host_cache = HostKVCache(model.mem_manager, self.args.cpu_cache_bytes,
                                               self.args.cpu_cache_page_tokens, self.args.disk_cache_dir,
                                               self.args.disk_cache_bytes, name=f"rank{model.ps.global_rank}")
+        on = os.environ.get("LLB_RADIX_TREE_MERGE_ENABLE", os.environ.get("LIGHTLLM_RADIX_TREE_MERGE_ENABLE", ""))
+        self._merge_delta = int(os.environ.get("LLB_RADIX_TREE_MERGE_DELTA", os.environ.get(
+            "LIGHTLLM_RADIX_TREE_MERGE_DELTA", "6000"))) if on.strip().upper() in ("1", "ON", "TRUE") else 0
+        self._merge_ticks = 0
         self.pins = PinnedRing(pin=self.device.type == "cuda")
         self.control = ControlState(self.args)
         self.is_master_in_dp = is_master_in_dp   # only one rank per replica writes into shm
@@ -297,6 +301,17 @@ class ModelBackend:
 
     # ------------------------------------------------------------------ one step
     @torch.no_grad()
+    def _tick_tree_merge(self):
+        """`LIGHTLLM_RADIX_TREE_MERGE_ENABLE=1`: every `LIGHTLLM_RADIX_TREE_MERGE_DELTA` (default 6000) forward
+        passes the prefix tree merges its chains of unreferenced single-child nodes.  The tick counts forward
+        passes, which the ranks of a tensor-parallel group run in lock-step, so their trees stay identical.
+        Reference: mode_backend/base_backend.py:620-632."""
+        if self._merge_delta <= 0 or self.radix_cache is None:
+            return
+        self._merge_ticks += 1
+        if self._merge_ticks % self._merge_delta == 0:
+            self.tree_merges = getattr(self, "tree_merges", 0) + int(self.radix_cache.merge_unreferenced_nodes() or 0)
+
     def step(self) -> dict:
         """Runs at most one forward pass.  Returns {"kind", "finished": [InferReq], "tokens": n}."""
         self._steps += 1
@@ -320,6 +335,8 @@ class ModelBackend:
                 n_tok = self._run_prefill(prefill)
             elif kind == "decode":
                 n_tok = self._run_decode(decode)
+        if kind in ("prefill", "decode"):
+            self._tick_tree_merge()
         for req in list(self.ctx.requests.values()):
             if req.finish_status.is_finished() and req not in finished:
                 finished.append(req)

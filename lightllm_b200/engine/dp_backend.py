@@ -62,6 +62,7 @@ class DPBackend(ModelBackend):
         the GPU executes, so a replica's GPU does not sit idle between passes and, through the layer-wise token
         exchanges, hold up every other replica."""
         self._steps += 1
+        self._tick_tree_merge()      # every call is a lock-step over all ranks: the tick is the same everywhere
         if self.redundancy is not None and self.redundancy.step():
             self.stats["redundancy_updates"] = self.stats.get("redundancy_updates", 0) + 1
         prefill, decode, finished = self._get_classed_reqs()

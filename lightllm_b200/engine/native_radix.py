@@ -36,6 +36,8 @@ def _lib():
         lib.llb_radix_dec_ref.restype = ctypes.c_int32
         lib.llb_radix_evict.restype = ctypes.c_int64
         lib.llb_radix_evict.argtypes = [ctypes.c_void_p, ctypes.c_int64, _i32p, ctypes.c_int64]
+        lib.llb_radix_merge.restype = ctypes.c_int64
+        lib.llb_radix_merge.argtypes = [ctypes.c_void_p]
         lib.llb_radix_node_count.restype = ctypes.c_int64
         lib.llb_radix_node_count.argtypes = [ctypes.c_void_p]
         lib._radix_typed = True
@@ -139,5 +141,6 @@ class NativeRadixCache:
     def clear_tree_nodes(self):
         self.evict(self.get_tree_total_tokens_num(), lambda v: self.mem_manager.free(v) if self.mem_manager else None)
 
-    def merge_unreferenced_nodes(self):
-        pass  # the native tree keeps paths compact enough: nodes only split where prefixes diverge
+    def merge_unreferenced_nodes(self) -> int:
+        """Merges chains of unreferenced single-child nodes; returns how many nodes went away."""
+        return int(self._lib.llb_radix_merge(self._h))

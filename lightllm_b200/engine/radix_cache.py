@@ -223,15 +223,19 @@ class RadixCache:
             self.mem_manager.free(np.concatenate(chunks))
 
     def merge_unreferenced_nodes(self):
-        """Compaction: a node with a single unreferenced child and equal ref count is merged with it."""
+        """Compaction: an unreferenced node whose only child is unreferenced too absorbs that child.  Handles that
+        callers hold always have a reference count above zero, so none is invalidated.  Returns the number of
+        nodes merged away.  Reference: dynamic_prompt/radix_cache.py:347-403."""
+        merged = 0
         stack = [self.root]
         while stack:
             node = stack.pop()
             for child in list(node.children.values()):
-                while len(child.children) == 1:
+                while len(child.children) == 1 and child.ref_counter == 0:
                     (gc,) = child.children.values()
-                    if gc.ref_counter != child.ref_counter:
+                    if gc.ref_counter != 0:
                         break
+                    merged += 1
                     child.key = np.concatenate([child.key, gc.key])
                     child.value = np.concatenate([child.value, gc.value])
                     child.node_len = child.key.shape[0]
@@ -242,6 +246,7 @@ class RadixCache:
                     gc._alive = False
                     self._maybe_evictable(child)
                 stack.append(child)
+        return merged
 
     def all_nodes(self):
         out, stack = [], [self.root]

@@ -143,7 +143,7 @@ def test_python_and_native_trees_agree_on_random_sequences(seed):
     held = []          # [(node_a, node_b)]
     next_slot = 0
     for step in range(600):
-        op = rng.choice(["insert", "insert", "match", "match_ref", "release", "evict"])
+        op = rng.choice(["insert", "insert", "match", "match_ref", "release", "evict", "merge"])
         if op == "insert":
             n = int(rng.integers(1, 24))
             key = rng.integers(0, 4, size=n).astype(np.int64)
@@ -168,6 +168,9 @@ def test_python_and_native_trees_agree_on_random_sequences(seed):
             na, nb = held.pop(int(rng.integers(0, len(held))))
             a.dec_node_ref_counter(na)
             b.dec_node_ref_counter(nb)
+        elif op == "merge":
+            assert a.merge_unreferenced_nodes() == b.merge_unreferenced_nodes(), f"step {step}"
+            assert len(a.all_nodes()) == b.node_count(), f"step {step}"
         elif op == "evict":
             need = int(rng.integers(1, 40))
             fa, fb = [], []
@@ -187,3 +190,48 @@ def test_python_and_native_trees_agree_on_random_sequences(seed):
     assert a.evict(10**9, lambda s: fa.extend(np.asarray(s).tolist())) == total
     assert b.evict(10**9, lambda s: fb.extend(np.asarray(s).tolist())) == total
     assert sorted(fa) == sorted(fb) and len(set(fa)) == len(fa) == total          # every slot released exactly once
+
+
+def test_native_tree_compaction():
+    t = NativeRadixCache("n", 100, 0)
+    t.insert(k(1, 2, 3), v(0, 3))
+    t.insert(k(1, 2, 3, 4, 5), v(10, 5))
+    t.insert(k(1, 2, 3, 4, 5, 6), v(20, 6))
+    t.insert(k(1, 2, 3, 9), v(30, 4))                   # a second branch below [1, 2, 3]
+    assert t.node_count() == 5
+    assert t.merge_unreferenced_nodes() == 1 and t.node_count() == 4      # [4, 5] + [6]; the fork stays
+    node, n, slots = t.match_prefix(k(1, 2, 3, 4, 5, 6), update_refs=True)
+    assert n == 6 and slots.tolist() == [0, 1, 2, 13, 14, 25]
+    freed = []
+    assert t.evict(100, lambda s: freed.extend(np.asarray(s).tolist())) == 1 and freed == [33]   # the other branch goes
+    assert t.merge_unreferenced_nodes() == 0            # the remaining chain is referenced
+    t.dec_node_ref_counter(node)
+    assert t.merge_unreferenced_nodes() == 1 and t.node_count() == 2
+    _, n, slots = t.match_prefix(k(1, 2, 3, 4, 5, 6, 7))
+    assert n == 6 and slots.tolist() == [0, 1, 2, 13, 14, 25]
+    assert t.insert(k(1, 2, 3, 4, 8), v(40, 5)) == 4 and t.node_count() == 4      # a merged node splits again
+    assert t.evict(100, lambda s: freed.extend(np.asarray(s).tolist())) == 7 and t.get_tree_total_tokens_num() == 0
+
+
+def test_backend_merges_the_tree_on_a_pass_counter(monkeypatch):
+    from lightllm_b200.engine.llm import LLM
+
+    cfg = dict(model_type="llama", hidden_size=64, num_hidden_layers=1, num_attention_heads=2, num_key_value_heads=2,
+               head_dim=32, intermediate_size=128, vocab_size=128, rms_norm_eps=1e-6, rope_theta=1e4, eos_token_id=2)
+    kw = dict(data_type="float32", max_total_token_num=1024, running_max_req_size=4, max_req_total_len=128, batch_max_tokens=64)
+    sp = {"max_new_tokens": 6, "ignore_eos": True}
+    prompts = [list(range(3, 40)), list(range(3, 30)) + [90, 91, 92], list(range(3, 40)) + [70, 71]]
+    plain = LLM(config=cfg, **kw)
+    want = [plain.generate([p], sp)[0]["token_ids"] for p in prompts]
+    nodes_plain = plain.backend.radix_cache.node_count() if hasattr(plain.backend.radix_cache, "node_count") else None
+    monkeypatch.setenv("LIGHTLLM_RADIX_TREE_MERGE_ENABLE", "1")
+    monkeypatch.setenv("LIGHTLLM_RADIX_TREE_MERGE_DELTA", "3")
+    llm = LLM(config=cfg, **kw)
+    assert llm.backend._merge_delta == 3
+    got = [llm.generate([p], sp)[0]["token_ids"] for p in prompts]
+    assert got == want and llm.backend._merge_ticks >= 18
+    rc = llm.backend.radix_cache
+    assert rc.get_refed_tokens_num() == 0
+    assert llm.model.mem_manager.can_use_mem_size + rc.get_tree_total_tokens_num() == llm.model.mem_manager.size
+    if nodes_plain is not None:
+        assert rc.node_count() <= nodes_plain
