@@ -15,6 +15,7 @@ audio_process.py}.
 from __future__ import annotations
 
 import math
+import os
 from typing import List
 
 import numpy as np
@@ -29,7 +30,7 @@ from .vit.qwen3_vl_visual import Qwen3VLVisionTower
 SAMPLE_RATE = 16000
 HOP = 160
 MIN_AUDIO_LEN = 480
-MAX_AUDIO_SECONDS = 3600
+MAX_AUDIO_SECONDS = int(os.environ.get("LIGHTLLM_MAX_AUDIO_DURATION_SECONDS", "3600"))   # longer clips are cut
 
 
 def _after_conv(n: int) -> int:
