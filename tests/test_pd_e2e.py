@@ -102,3 +102,45 @@ def test_pd_generate_matches_offline(cluster):
               batch_max_tokens=256)
     want = llm.generate([prompt], {"max_new_tokens": 9, "ignore_eos": True})[0]["token_ids"]
     assert got == want, logs
+
+
+@pytest.mark.timeout(900)
+def test_clients_that_leave_mid_stream_leak_nothing(cluster):
+    """Streams through the master, some clients hang up after one, two or five tokens (before or after the KV has
+    moved to the decode node); afterwards more sequential requests than either node has request slots complete."""
+    import random
+    import threading
+
+    url = cluster["master"]
+    for it in range(3):
+        rng = random.Random(it)
+        results = []
+
+        def client():
+            ids = [rng.randrange(3, 500) for _ in range(rng.randrange(20, 80))]
+            leave = rng.choice([1, 2, 5, None])
+            got, t0 = 0, time.time()
+            try:
+                with requests.post(url + "/generate_stream", json={"inputs": ids, "parameters": {
+                        "max_new_tokens": 30, "ignore_eos": True}}, stream=True, timeout=120) as r:
+                    assert r.status_code == 200, r.text
+                    for line in r.iter_lines():
+                        if line.startswith(b"data:"):
+                            got += 1
+                            if leave is not None and got >= leave:
+                                break
+                results.append((got, leave, time.time() - t0))
+            except Exception as e:  # noqa: BLE001
+                results.append(("error", repr(e), time.time() - t0))
+
+        threads = [threading.Thread(target=client) for _ in range(6)]
+        for t in threads:
+            t.start()
+        for t in threads:
+            t.join(timeout=150)
+        assert len(results) == 6 and all(r[0] != "error" for r in results), results
+        assert all(r[0] == (30 if r[1] is None else r[1]) for r in results), results
+    for k in range(10):           # 8 request slots per node: a leaked slot would show here
+        r = requests.post(url + "/generate", json={"inputs": list(range(5 + k, 40 + k)), "parameters": {
+            "max_new_tokens": 4, "ignore_eos": True}}, timeout=120)
+        assert r.status_code == 200 and r.json()["count_output_tokens"] == 4, r.text
