@@ -117,3 +117,51 @@ def test_two_nodes_on_one_host(tmp_path):
     finally:
         for p in nodes:
             _stop(p)
+
+
+@pytest.mark.timeout(900)
+def test_losing_a_node_takes_the_other_one_down(tmp_path):
+    """One tensor-parallel group over two nodes cannot go on without one of them: when node 1 is killed, node 0's
+    ranks fail in their next collective, its launcher ends the whole server (a supervisor restarts both) and the
+    open streams end instead of hanging."""
+    import threading
+
+    (tmp_path / "config.json").write_text(json.dumps(CFG))
+    http0, http1, nccl, relay, gloo = (_free_port() for _ in range(5))
+    common = ["--tp", "2", "--nnodes", "2", "--nccl_host", "127.0.0.1", "--nccl_port", str(nccl),
+              "--multinode_httpmanager_port", str(relay), "--multinode_router_gloo_port", str(gloo)]
+    nodes = [_launch(tmp_path, "node0", http0, common + ["--node_rank", "0"]),
+             _launch(tmp_path, "node1", http1, common + ["--node_rank", "1"])]
+    url = f"http://127.0.0.1:{http0}"
+    try:
+        _wait(url, nodes, tmp_path)
+        ended, streaming = [], threading.Event()
+
+        def client():
+            got = 0
+            try:
+                with requests.post(url + "/generate_stream", json={"inputs": list(range(5, 60)), "parameters": {
+                        "max_new_tokens": 240, "ignore_eos": True}}, stream=True, timeout=300) as r:
+                    for line in r.iter_lines():
+                        if line.startswith(b"data:"):
+                            got += 1
+                            if got == 3:
+                                streaming.set()
+                ended.append(("closed", got))
+            except Exception as e:  # noqa: BLE001
+                ended.append((type(e).__name__, got))
+
+        t = threading.Thread(target=client)
+        t.start()
+        assert streaming.wait(120)
+        os.killpg(nodes[1].pid, signal.SIGKILL)
+        t0 = time.time()
+        while time.time() - t0 < 180 and nodes[0].poll() is None:
+            time.sleep(1)
+        assert nodes[0].poll() is not None, "node 0 kept running without its peer"
+        t.join(timeout=60)
+        assert ended and ended[0][1] < 240, ended
+        assert "shutting everything down" in (tmp_path / "node0.log").read_text()
+    finally:
+        for p in nodes:
+            _stop(p)
