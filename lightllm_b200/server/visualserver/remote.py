@@ -317,6 +317,8 @@ class RemoteEncoders:
 class ProxyVisualManager(VisualManager):
     """`VisualManager` whose tower pass happens on a registered encoder."""
 
+    LOOK_EVERY_S = 5.0      # while waiting for an answer: how often to ask whether the encoder is still registered
+
     def __init__(self, args, cache=None, send_next=None, recv=None, infer_batch_size: int = 8, try_recv=None,
                  send_batch_size: int = 1, encoders: Optional[RemoteEncoders] = None,
                  shared: Optional[SharedEmbedDir] = None, timeout_s: Optional[float] = None,
@@ -338,12 +340,19 @@ class ProxyVisualManager(VisualManager):
         sock = self.encoders.socks[nid]
         rid = next(self._rid)
         sock.send_multipart(seal(self.key, (rid, pairs)))
+        where = self.encoders.nodes[nid].host_ip_port
         deadline = time.time() + self.timeout_s
+        next_look = time.time() + self.LOOK_EVERY_S
         while True:
             left = deadline - time.time()
             if left <= 0 or not sock.poll(int(min(left, 1.0) * 1000) + 1):
                 if left <= 0:
-                    raise TimeoutError(f"encoder {self.encoders.nodes[nid].host_ip_port}: no answer in {self.timeout_s:.0f} s")
+                    raise TimeoutError(f"encoder {where}: no answer in {self.timeout_s:.0f} s")
+                if time.time() >= next_look:      # an encoder that died has left the config server's list by now
+                    next_look = time.time() + self.LOOK_EVERY_S
+                    self.encoders.refresh(force=True)
+                    if nid not in self.encoders.nodes:
+                        raise ConnectionError(f"encoder {where} is no longer registered")
                 continue
             try:
                 got, status, body = unseal(self.key, sock.recv_multipart())
@@ -383,7 +392,8 @@ class ProxyVisualManager(VisualManager):
                 except Exception as e:  # noqa: BLE001
                     err = e
                     logger.warning(f"{e}")
-                    self.encoders.drop(nid)      # listed again at the next refresh if it is still registered
+                    if nid in self.encoders.nodes:
+                        self.encoders.drop(nid)  # listed again at the next refresh if it is still registered
                     self.encoders._last = 0.0
             if embs is None:
                 raise RuntimeError(f"no vision encoder answered ({err or 'none is registered at the config server'})")

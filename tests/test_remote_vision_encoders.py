@@ -130,6 +130,18 @@ def test_proxy_asks_encoders_and_reuses_the_shared_directory(tmp_path):
         except TimeoutError:
             pass
         assert len(tower.calls) == before
+        # an encoder that dies while a request waits for it: it leaves the list, the wait ends long before the limit
+        listed.insert(0, remote.VitNode(2, "127.0.0.1", dead_port))
+        enc.refresh(force=True)
+        slow = remote.ProxyVisualManager(args, cache, sent.append, None, encoders=enc, shared=None, timeout_s=30.0)
+        slow.LOOK_EVERY_S = 0.2
+        listed[:] = [remote.VitNode(1, "127.0.0.1", port)]          # what the config server says from now on
+        t0 = time.time()
+        try:
+            slow._ask(2, [(_item(9, "m9", 1, 50), b"zzzzZ")])
+            raise AssertionError("a dead encoder answered")
+        except ConnectionError as e:
+            assert "no longer registered" in str(e) and time.time() - t0 < 5
         # an encoder that leaves the list is dropped
         listed[:] = [remote.VitNode(1, "127.0.0.1", port)]
         enc.refresh(force=True)
