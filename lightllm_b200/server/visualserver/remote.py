@@ -72,12 +72,13 @@ class SharedEmbedDir:
     when complete (written aside, then renamed), so its presence is the "ready" mark; reading one refreshes its
     time stamp and the oldest files go when there are more than `capacity`."""
 
-    SWEEP_EVERY = 64      # stores between two capacity checks
+    RESCAN_EVERY = 4096   # stores between two full counts (other writers share the directory)
 
     def __init__(self, root: str, capacity: int = 250000):
         self.root, self.capacity = root, max(1, int(capacity))
         os.makedirs(root, exist_ok=True)
-        self._stores = 0
+        self._count = len(self._files())      # files believed to be there; exact after every scan
+        self._since_scan = 0
 
     def _path(self, md5: str) -> str:
         return os.path.join(self.root, md5[:2], md5 + ".pt")
@@ -100,6 +101,7 @@ class SharedEmbedDir:
         if not md5:
             return
         p = self._path(md5)
+        fresh = not os.path.exists(p)
         os.makedirs(os.path.dirname(p), exist_ok=True)
         fd, tmp = tempfile.mkstemp(dir=os.path.dirname(p), suffix=".part")
         try:
@@ -112,13 +114,18 @@ class SharedEmbedDir:
             except OSError:
                 pass
             raise
-        self._stores += 1
-        if self._stores % self.SWEEP_EVERY == 0 or self.capacity < self.SWEEP_EVERY:
+        self._count += int(fresh)
+        self._since_scan += 1
+        if self._count > self.capacity or self._since_scan >= self.RESCAN_EVERY:
             self.sweep()
 
-    def sweep(self):
+    def _files(self):
         files = []
-        for sub in os.listdir(self.root):
+        try:
+            subs = os.listdir(self.root)
+        except OSError:
+            return files
+        for sub in subs:
             d = os.path.join(self.root, sub)
             if not os.path.isdir(d):
                 continue
@@ -128,13 +135,24 @@ class SharedEmbedDir:
                         files.append((os.path.getmtime(os.path.join(d, name)), os.path.join(d, name)))
                     except OSError:
                         pass
+        return files
+
+    def sweep(self):
+        """Counts the files and removes the least recently used ones above the capacity (a little more than
+        needed, so that a full directory is not scanned on every store)."""
+        files = self._files()
+        self._since_scan = 0
         extra = len(files) - self.capacity
         if extra > 0:
+            extra = min(len(files), extra + self.capacity // 50)
             for _, p in sorted(files)[:extra]:
                 try:
                     os.unlink(p)
                 except OSError:
                     pass
+            self._count = len(files) - extra
+        else:
+            self._count = len(files)
 
 
 def shared_dir_of(args) -> Optional[SharedEmbedDir]:
@@ -230,6 +248,21 @@ def keep_registered(node: VitNode, host: str, port: int, stop: Optional[threadin
     asyncio.run(run())
 
 
+def address_towards(host: str, port: int) -> str:
+    """This machine's address on the route to `host` (what the other servers can reach an encoder under when it
+    listens on all interfaces); 127.0.0.1 when no route is known."""
+    import socket
+
+    s = socket.socket(socket.AF_INET, socket.SOCK_DGRAM)
+    try:
+        s.connect((host, port))           # no packet is sent: the kernel only picks the source address
+        return s.getsockname()[0]
+    except OSError:
+        return "127.0.0.1"
+    finally:
+        s.close()
+
+
 def start_visual_only_process(args_dict: dict, pipe_writer=None):
     args = StartArgs.from_dict(args_dict)
     set_proc_title(f"lightllm::{args.unique_server_name}::visual_only_server")
@@ -245,7 +278,8 @@ def start_visual_only_process(args_dict: dict, pipe_writer=None):
         sock.bind(f"tcp://{args.host if args.host not in (None, '') else '0.0.0.0'}:{args.visual_rpyc_port}")
         server = VisualOnlyServer(tower, sock, shared_dir_of(args), args.visual_infer_batch_size or 8, key=auth_key(args))
         node = VitNode(getattr(args, "visual_node_id", None) or uuid.uuid4().int & ((1 << 62) - 1),
-                       args.host if args.host not in (None, "", "0.0.0.0") else "127.0.0.1", int(args.visual_rpyc_port))
+                       args.host if args.host not in (None, "", "0.0.0.0") else
+                       address_towards(args.config_server_host, int(args.config_server_port)), int(args.visual_rpyc_port))
         threading.Thread(target=keep_registered, args=(node, args.config_server_host, int(args.config_server_port)),
                          daemon=True).start()
     except Exception:
