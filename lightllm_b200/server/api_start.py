@@ -167,10 +167,11 @@ def normal_or_p_d_start(args: StartArgs, config_override: dict = None):
     set_proc_title(f"lightllm::{args.model_name}::api_server")
     args = normalize_args(args, config_override)
     set_env_start_args(args)
-    from ..utils.shm_cleanup import check_shm_size
+    from ..utils.shm_cleanup import check_shm_size, note_or_sweep_orphans
 
     if not getattr(args, "disable_shm_warning", False):
         check_shm_size(args)      # a warning when /dev/shm is smaller than the configuration wants
+        note_or_sweep_orphans()   # segments of servers that were killed outright: said, or removed when asked to
     start_core_processes(args, config_override)
     if args.health_monitor:
         from .health_monitor.manager import start_health_check_process

@@ -17,6 +17,7 @@ import ctypes
 import ctypes.util
 import logging
 import os
+import re
 import signal
 import threading
 from typing import Dict, Optional, Set, Tuple
@@ -152,3 +153,82 @@ def check_shm_size(args, path: str = "/dev/shm") -> Tuple[float, float, bool]:
     if not ok:
         log.warning("%s has %.1f GiB, the configuration wants about %.1f GiB (docker: --shm-size)", path, have, want)
     return have, want, ok
+
+
+# ------------------------------------------------------------------ segments of servers that were killed
+_SERVER_SEGMENT = re.compile(r"^(llb(\d+)x[0-9a-f]{6})_")
+
+
+def orphan_segments(path: str = "/dev/shm", pid_alive=None) -> dict:
+    """Segments named after a launcher (`llb<launcher pid>x<tag>_...`) whose launcher no longer runs and that
+    belong to this user: {server name: [file names]}.  A server that is killed outright (SIGKILL, out of memory)
+    cannot remove its segments; everything else removes them on the way out."""
+    if pid_alive is None:
+        def pid_alive(pid: int) -> bool:
+            try:
+                os.kill(pid, 0)
+                return True
+            except ProcessLookupError:
+                return False
+            except PermissionError:
+                return True
+    out: dict = {}
+    try:
+        names = os.listdir(path)
+    except OSError:
+        return out
+    for n in names:
+        m = _SERVER_SEGMENT.match(n)
+        if m is None or pid_alive(int(m.group(2))):
+            continue
+        try:
+            if os.stat(os.path.join(path, n)).st_uid != os.getuid():
+                continue
+        except OSError:
+            continue
+        out.setdefault(m.group(1), []).append(n)
+    return out
+
+
+def sweep_orphans(path: str = "/dev/shm", pid_alive=None) -> int:
+    """Removes what `orphan_segments` lists; returns the number of files removed.  The launcher calls it at start
+    when `LLB_SWEEP_ORPHAN_SHM=1`: the check goes by process ids, so it must stay off where several containers
+    with process-id namespaces of their own share one /dev/shm."""
+    n = 0
+    for files in orphan_segments(path, pid_alive).values():
+        for f in files:
+            try:
+                os.unlink(os.path.join(path, f))
+                n += 1
+            except OSError:
+                pass
+    return n
+
+
+def note_or_sweep_orphans(path: str = "/dev/shm") -> int:
+    """At server start: sweep when asked to, else say what lies around."""
+    if os.environ.get("LLB_SWEEP_ORPHAN_SHM", "").strip().lower() in ("1", "true", "on"):
+        n = sweep_orphans(path)
+        if n:
+            log.warning("removed %d shared-memory segments of servers that no longer run", n)
+        return n
+    found = orphan_segments(path)
+    if found:
+        log.warning("%d shared-memory segments of %d servers that no longer run lie in %s "
+                    "(LLB_SWEEP_ORPHAN_SHM=1, or python -m lightllm_b200.utils.shm_cleanup --sweep, removes them)",
+                    sum(len(v) for v in found.values()), len(found), path)
+    return 0
+
+
+if __name__ == "__main__":
+    import argparse
+
+    ap = argparse.ArgumentParser(description="segments of servers that were killed")
+    ap.add_argument("--path", default="/dev/shm")
+    ap.add_argument("--sweep", action="store_true", help="remove them (default: list)")
+    a = ap.parse_args()
+    if a.sweep:
+        print(f"removed {sweep_orphans(a.path)} segments")
+    else:
+        for server, files in sorted(orphan_segments(a.path).items()):
+            print(f"{server}: {len(files)} segments")

@@ -205,3 +205,25 @@ def test_loggers_follow_the_environment(monkeypatch, tmp_path, capsys):
     monkeypatch.setenv("LLB_LOG_LEVEL", "nonsense")
     assert log_utils.log_level() == logging.INFO
     log_utils.reset_for_tests()
+
+
+def test_orphan_shared_memory_segments(tmp_path, monkeypatch):
+    from lightllm_b200.utils import shm_cleanup as sc
+
+    names = ["llb111xabcdef_req_shm_total", "llb111xabcdef_token_load", "llb222x012345_req_shm_total",
+             "llb333xdeadbe_shm_prompts_0", "psm_1234", "llbXYZ_notours", "llb111xabcdef"]
+    for n in names:
+        (tmp_path / n).write_bytes(b"x")
+    alive = lambda pid: pid == 222  # noqa: E731
+    found = sc.orphan_segments(str(tmp_path), alive)
+    assert {k: sorted(v) for k, v in found.items()} == {
+        "llb111xabcdef": ["llb111xabcdef_req_shm_total", "llb111xabcdef_token_load"],
+        "llb333xdeadbe": ["llb333xdeadbe_shm_prompts_0"]}
+    assert sc.sweep_orphans(str(tmp_path), alive) == 3
+    assert sorted(p.name for p in tmp_path.iterdir()) == sorted(["llb222x012345_req_shm_total", "psm_1234",
+                                                                 "llbXYZ_notours", "llb111xabcdef"])
+    # this process is alive: its own segments are never listed
+    (tmp_path / f"llb{os.getpid()}xabc123_x").write_bytes(b"x")
+    assert f"llb{os.getpid()}xabc123" not in sc.orphan_segments(str(tmp_path))
+    monkeypatch.delenv("LLB_SWEEP_ORPHAN_SHM", raising=False)
+    assert sc.note_or_sweep_orphans(str(tmp_path)) == 0
