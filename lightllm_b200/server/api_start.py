@@ -15,7 +15,7 @@ import time
 import uuid
 
 from ..utils import config_utils
-from ..utils.net_utils import alloc_can_use_network_port
+from ..utils.net_utils import alloc_can_use_network_port, require_free_ports
 from ..utils.process_utils import process_manager, set_proc_title
 from .core.objs.start_args import StartArgs, set_env_start_args
 
@@ -165,6 +165,7 @@ def run_http_server(args: StartArgs):
 
 def normal_or_p_d_start(args: StartArgs, config_override: dict = None):
     set_proc_title(f"lightllm::{args.model_name}::api_server")
+    require_free_ports(args.host, [args.port], "HTTP server")
     args = normalize_args(args, config_override)
     set_env_start_args(args)
     from ..utils.shm_cleanup import check_shm_size, note_or_sweep_orphans
@@ -185,6 +186,7 @@ def normal_or_p_d_start(args: StartArgs, config_override: dict = None):
 
 
 def pd_master_start(args: StartArgs):
+    require_free_ports(args.host, [args.port], "pd_master")
     args = normalize_args(args, {"vocab_size": None})
     set_env_start_args(args)
     from .metrics.manager import start_metric_manager

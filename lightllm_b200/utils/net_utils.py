@@ -51,3 +51,24 @@ def get_hostname_ip() -> str:
         return socket.gethostbyname(socket.gethostname())
     except Exception:
         return "127.0.0.1"
+
+
+def port_is_free(host: str, port: int) -> bool:
+    """Whether a listening socket can be bound to (host, port) right now."""
+    s = socket.socket(socket.AF_INET, socket.SOCK_STREAM)
+    s.setsockopt(socket.SOL_SOCKET, socket.SO_REUSEADDR, 1)
+    try:
+        s.bind((host if host not in (None, "") else "0.0.0.0", int(port)))
+        return True
+    except OSError:
+        return False
+    finally:
+        s.close()
+
+
+def require_free_ports(host: str, ports, what: str = "server"):
+    """Stops with one clear line before any process is started (the HTTP server would only find out at the end of
+    start-up).  Reference: lightllm/server/api_start.py (validate_ports)."""
+    busy = [int(p) for p in ports if p is not None and not port_is_free(host, p)]
+    if busy:
+        raise SystemExit(f"[lightllm_b200] cannot start the {what}: port(s) {busy} on {host or '0.0.0.0'} are in use")

@@ -227,3 +227,30 @@ def test_orphan_shared_memory_segments(tmp_path, monkeypatch):
     assert f"llb{os.getpid()}xabc123" not in sc.orphan_segments(str(tmp_path))
     monkeypatch.delenv("LLB_SWEEP_ORPHAN_SHM", raising=False)
     assert sc.note_or_sweep_orphans(str(tmp_path)) == 0
+
+
+def test_a_busy_http_port_stops_the_launcher_before_anything_starts(tmp_path):
+    import socket
+    import subprocess
+
+    from lightllm_b200.utils.net_utils import port_is_free, require_free_ports
+
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    s.listen(1)
+    port = s.getsockname()[1]
+    try:
+        assert not port_is_free("127.0.0.1", port)
+        with pytest.raises(SystemExit) as e:
+            require_free_ports("127.0.0.1", [port, None], "HTTP server")
+        assert str(port) in str(e.value)
+        (tmp_path / "config.json").write_text("{}")
+        t0 = time.time()
+        r = subprocess.run([sys.executable, "-m", "lightllm_b200.server.api_server", "--model_dir", str(tmp_path),
+                            "--host", "127.0.0.1", "--port", str(port)], capture_output=True, text=True, timeout=120,
+                           env=dict(os.environ, LLB_FORCE_CPU="1", PYTHONPATH=os.path.dirname(os.path.dirname(__file__))))
+        assert r.returncode != 0 and "in use" in (r.stderr + r.stdout) and time.time() - t0 < 60
+    finally:
+        s.close()
+    assert port_is_free("127.0.0.1", port)
+    require_free_ports("127.0.0.1", [port])
