@@ -166,6 +166,8 @@ def run_http_server(args: StartArgs):
 def normal_or_p_d_start(args: StartArgs, config_override: dict = None):
     set_proc_title(f"lightllm::{args.model_name}::api_server")
     require_free_ports(args.host, [args.port], "HTTP server")
+    if config_override is None and args.model_dir and not os.path.isfile(os.path.join(args.model_dir, "config.json")):
+        raise SystemExit(f"[lightllm_b200] --model_dir {args.model_dir}: no config.json there")
     args = normalize_args(args, config_override)
     set_env_start_args(args)
     from ..utils.shm_cleanup import check_shm_size, note_or_sweep_orphans

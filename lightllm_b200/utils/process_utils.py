@@ -81,18 +81,26 @@ class SubmoduleManager:
             p.start()
             pipes.append(r)
             procs.append(p)
+        def give_up():
+            # the processes of this call are not registered yet: they go down with the registered ones, or the
+            # launcher would wait for them for ever when it exits
+            for q in procs:
+                if q.is_alive():
+                    kill_tree(q.pid)
+            self.terminate_all()
+
         for p, r, fn in zip(procs, pipes, start_funcs):
             t0 = time.time()
             while not r.poll(0.2):
                 if not p.is_alive():
-                    self.terminate_all()
+                    give_up()
                     raise RuntimeError(f"{fn.__name__} died during start-up (exit code {p.exitcode})")
                 if time.time() - t0 > timeout_s:
-                    self.terminate_all()
+                    give_up()
                     raise TimeoutError(f"{fn.__name__} start-up timed out")
             msg = r.recv()
             if msg != "init ok":
-                self.terminate_all()
+                give_up()
                 raise RuntimeError(f"{fn.__name__} failed to start: {msg}")
         self.processes.extend(procs)
         return procs

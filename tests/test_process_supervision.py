@@ -146,3 +146,29 @@ def test_debug_switch_forces_an_unhealthy_answer(monkeypatch):
     if inspect.isawaitable(res):
         res = asyncio.run(res)
     assert res is False
+
+
+@pytest.mark.timeout(600)
+def test_a_failed_start_leaves_no_processes_behind(tmp_path):
+    """A model that cannot be built (unknown architecture): the launcher reports it, ends with a non-zero code and
+    takes the processes that had already started with it (they used to keep it from exiting)."""
+    import psutil
+
+    (tmp_path / "config.json").write_text(json.dumps({"model_type": "no_such_architecture", "hidden_size": 64}))
+    env = dict(os.environ, LLB_FORCE_CPU="1", PYTHONPATH=ROOT)
+    proc = subprocess.Popen([sys.executable, "-m", "lightllm_b200.server.api_server", "--model_dir", str(tmp_path), "--port",
+                             str(_free_port()), "--data_type", "fp32"], env=env, stdout=subprocess.PIPE,
+                            stderr=subprocess.STDOUT, text=True, cwd=ROOT, start_new_session=True)
+    try:
+        out, _ = proc.communicate(timeout=300)
+    except subprocess.TimeoutExpired:
+        os.killpg(proc.pid, signal.SIGKILL)
+        pytest.fail("the launcher did not exit after a failed start")
+    assert proc.returncode not in (0, None) and "unsupported model_type 'no_such_architecture'" in out
+    time.sleep(1)
+    left = [p for p in psutil.process_iter(["cmdline", "name"]) if str(tmp_path) in " ".join(p.info["cmdline"] or [])]
+    assert not left, left
+    # a directory without a model: one line, at once
+    r = subprocess.run([sys.executable, "-m", "lightllm_b200.server.api_server", "--model_dir", str(tmp_path / "nothing"),
+                        "--port", str(_free_port())], env=env, capture_output=True, text=True, timeout=120, cwd=ROOT)
+    assert r.returncode != 0 and "no config.json there" in (r.stdout + r.stderr)
