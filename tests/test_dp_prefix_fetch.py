@@ -55,9 +55,9 @@ def _worker(rank, world, port, out_dir):
     tail = torch.randint(3, 512, (20,), generator=g).tolist()
     other = torch.randint(3, 512, (30,), generator=g).tolist()
     par = {"max_new_tokens": 6, "ignore_eos": True}
-    # round 1: replica 0 serves the shared prompt, replica 1 something else
+    # scheduling pass 1: replica 0 serves the shared prompt, replica 1 something else
     first = llm.generate([shared] if rank == 0 or world == 1 else [other], par)
-    # round 2: the router gives shared + tail to replica 1 (replica 0 gets an unrelated prompt); every rank sees the
+    # scheduling pass 2: the router gives shared + tail to replica 1 (replica 0 gets an unrelated prompt); every rank sees the
     # same list of new requests
     new = [(world - 1, np.array(shared + tail)), (0, np.array(other + tail))]
     got = llm.backend.fetch_prefixes(new) if world > 1 else 0

@@ -73,22 +73,22 @@ def _node(rank, port, q):
     dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=2)
     r = _router(rank)
     reqs = {i: _req(8 * i) for i in range(4)}
-    # round 1: node 0 has requests 0, 1, 2; node 1 only 1 and 0 (other order, 2 not yet relayed) -> 0, 1 admitted
+    # scheduling pass 1: node 0 has requests 0, 1, 2; node 1 only 1 and 0 (other order, 2 not yet relayed) -> 0, 1 admitted
     r.req_queue.extend([reqs[0], reqs[1], reqs[2]] if rank == 0 else [reqs[1], reqs[0]])
     r._round_multinode()
-    # round 2: request 2 has arrived everywhere, but node 1's mailbox is still full -> nothing is written anywhere
+    # scheduling pass 2: request 2 has arrived everywhere, but node 1's mailbox is still full -> nothing is written anywhere
     if rank == 1:
         r.req_queue.append(reqs[2])
         r.mailbox.busy = True
     r._round_multinode()
     r.mailbox.busy = False
-    # round 3: node 0 learns that request 0 was aborted and gets a cache flush command; the pool (2 requests' worth)
+    # scheduling pass 3: node 0 learns that request 0 was aborted and gets a cache flush command; the pool (2 requests' worth)
     # is full, so request 2 keeps waiting; node 1 must send the same abort + flush
     if rank == 0:
         reqs[0].is_aborted = True
         r.pending_cmds.append(FlushCacheCmd())
     r._round_multinode()
-    # round 4: both running requests have finished on node 1 already, on node 0 not yet (node-local timing);
+    # scheduling pass 4: both running requests have finished on node 1 already, on node 0 not yet (node-local timing);
     # request 3 arrives on node 0 only and request 2's client goes away on node 0 before admission
     if rank == 1:
         r.running_batch = None
@@ -104,7 +104,7 @@ def _node(rank, port, q):
         r.req_queue.append(reqs[3])
     else:
         r.running_batch = None
-    # round 5: request 3 everywhere -> admitted; exit command from node 0
+    # scheduling pass 5: request 3 everywhere -> admitted; exit command from node 0
     if rank == 0:
         r.pending_cmds.append(ExitCmd())
     r._round_multinode()
