@@ -288,6 +288,8 @@ async def startup_event():
                                                   key=multinode_relay.relay_key(args))
             await relay.hello()
             g_objs.relay_task = loop.create_task(relay.follow(g_objs.httpserver_manager))
+    if args.run_mode == "pd_master" and getattr(args, "config_server_host", None) and args.config_server_port:
+        g_objs.pd_master_register_task = loop.create_task(g_objs.httpserver_manager.keep_registered_at_config_server())
     if args.run_mode in ("prefill", "decode"):
         from .httpserver.pd_loop import start_pd_loops
 

@@ -79,13 +79,17 @@ def normalize_args(args: StartArgs, config_override: dict = None) -> StartArgs:
     if a.mtp_mode is not None:
         assert a.mtp_step > 0 and a.mtp_draft_model_dir, "mtp needs --mtp_step and --mtp_draft_model_dir"
     if a.run_mode in ("prefill", "decode"):
-        assert a.pd_master_ip and a.pd_master_port, "PD nodes need --pd_master_ip/--pd_master_port"
-        # inherited by the model-rank processes (engine/pd/kv_transport.py:auth_key)
-        os.environ["LLB_PD_MASTER_ADDR"] = f"{a.pd_master_ip}:{a.pd_master_port}"
+        via_config = bool(getattr(a, "config_server_host", None) and getattr(a, "config_server_port", None))
+        assert via_config or (a.pd_master_ip and a.pd_master_port), \
+            "PD nodes need --pd_master_ip / --pd_master_port, or --config_server_host / --config_server_port where the pd_masters register"
+        # inherited by the model-rank processes (engine/pd/kv_transport.py:auth_key): what all nodes of the
+        # deployment have in common
+        os.environ["LLB_PD_MASTER_ADDR"] = f"{a.config_server_host}:{a.config_server_port}" if via_config else \
+            f"{a.pd_master_ip}:{a.pd_master_port}"
         if getattr(a, "pd_kv_auth_key", None):
             os.environ["LLB_PD_KV_AUTHKEY"] = a.pd_kv_auth_key
         elif not os.environ.get("LLB_PD_KV_AUTHKEY"):
-            print("[start] no --pd_kv_auth_key: the KV-transfer links are keyed by the pd_master address only",
+            print("[start] no --pd_kv_auth_key: the KV-transfer links are keyed by the pd_master (or config server) address only",
                   flush=True)
     # ---- names and ports ----
     if a.unique_server_name is None:

@@ -135,8 +135,10 @@ async def kv_status_link(g, master_url: str, queue: "asyncio.Queue[UpKVStatus]",
             await asyncio.sleep(RETRY_S)
 
 
-async def kv_status_pump(g, queue):
-    """Decode nodes: rank 0 of the model pushes (group_req_id, ok) over zmq when a transfer is complete."""
+async def kv_status_pump(g, queues):
+    """Decode nodes: rank 0 of the model pushes (group_req_id, ok) over zmq when a transfer is complete.  `queues`
+    maps each master to its upload queue; a note goes to every master (one that does not know the request drops
+    it)."""
     import zmq
     import zmq.asyncio
 
@@ -144,16 +146,60 @@ async def kv_status_pump(g, queue):
     sock.bind(f"tcp://127.0.0.1:{g.args.pd_kv_status_port}")
     while True:
         gid, ok = await sock.recv_pyobj()
-        await queue.put(UpKVStatus(gid, ok=ok))
+        for q in list(queues.values()):
+            await q.put(UpKVStatus(gid, ok=ok))
+
+
+def _link_master(g, url: str, queues: dict) -> list:
+    tasks = [asyncio.create_task(pd_master_link(g, url))]
+    if g.args.run_mode == "decode":
+        queues[url] = asyncio.Queue()
+        tasks.append(asyncio.create_task(kv_status_link(g, url, queues[url])))
+    return tasks
+
+
+async def follow_config_server(g, queues: dict, links: dict, fetch=None, every_s: float = 10.0):
+    """Keeps one link per pd_master that the config server lists (`/registered_objects`); masters that leave the
+    list are let go.  Reference: httpserver/pd_loop.py (its loop over the registered pd_masters)."""
+    import base64
+
+    args = g.args
+
+    def http_fetch():
+        import requests
+
+        r = requests.get(f"http://{args.config_server_host}:{args.config_server_port}/registered_objects", timeout=10)
+        r.raise_for_status()
+        return pickle.loads(base64.b64decode(r.json()["data"]))
+
+    fetch = fetch or http_fetch
+    while True:
+        try:
+            listed = {f"ws://{m.host_ip_port}" for m in await asyncio.to_thread(fetch)}
+        except Exception as e:  # noqa: BLE001
+            print(f"[pd_loop] cannot list the pd_masters ({type(e).__name__}: {e})", flush=True)
+            listed = None
+        if listed is not None:
+            for url in listed - set(links):
+                links[url] = _link_master(g, url, queues)
+            for url in set(links) - listed:
+                for t in links.pop(url):
+                    t.cancel()
+                queues.pop(url, None)
+        await asyncio.sleep(every_s)
 
 
 def start_pd_loops(g):
     args = g.args
-    masters = [f"ws://{args.pd_master_ip}:{args.pd_master_port}"]
-    tasks = [asyncio.create_task(pd_master_link(g, m)) for m in masters]
-    if args.run_mode == "decode":
-        g.kv_status_queue = asyncio.Queue()
-        tasks += [asyncio.create_task(kv_status_link(g, m, g.kv_status_queue)) for m in masters]
-        if args.pd_kv_status_port:
-            tasks.append(asyncio.create_task(kv_status_pump(g, g.kv_status_queue)))
+    queues, links = {}, {}
+    g.kv_status_queues, g.pd_master_links = queues, links
+    tasks = []
+    if getattr(args, "config_server_host", None) and getattr(args, "config_server_port", None):
+        tasks.append(asyncio.create_task(follow_config_server(g, queues, links)))
+    else:
+        url = f"ws://{args.pd_master_ip}:{args.pd_master_port}"
+        links[url] = _link_master(g, url, queues)
+        tasks += links[url]
+    if args.run_mode == "decode" and args.pd_kv_status_port:
+        tasks.append(asyncio.create_task(kv_status_pump(g, queues)))
     return tasks

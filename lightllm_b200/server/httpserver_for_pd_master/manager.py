@@ -64,12 +64,57 @@ class HttpServerManagerForPDMaster:
         self.alias: Dict[int, int] = {}             # a client request's id -> the id of the block it is in
         self.block_prompt_ids: Dict[int, List[int]] = {}
         self._next_id = MAX_BEST_OF
+        self._id_end = 0                            # end of the id range drawn from the config server
         self.paused = False
         self.tokenizer = None
         m = re.fullmatch(r"(\d+)p(\d+)d", args.pd_master_mode or "elastic")
         self.fixed_topology = (int(m.group(1)), int(m.group(2))) if m else None
         if not m and (args.pd_master_mode or "elastic") != "elastic":
             raise ValueError("--pd_master_mode is 'elastic' or '<P>p<D>d'")
+
+    # ---------------------------------------------------------------- ids
+    async def _take_id(self) -> int:
+        """The next request id.  Several pd_masters behind one config server draw disjoint ranges from it
+        (`/allocate_global_unique_id_range`), so that ids stay unique on the nodes they share."""
+        host, port = getattr(self.args, "config_server_host", None), getattr(self.args, "config_server_port", None)
+        if host and port:
+            if self._next_id + MAX_BEST_OF > self._id_end:
+                import requests
+
+                def fetch():
+                    r = requests.get(f"http://{host}:{port}/allocate_global_unique_id_range", timeout=10)
+                    r.raise_for_status()
+                    return r.json()
+
+                got = await asyncio.to_thread(fetch)
+                first = -(-int(got["start_id"]) // MAX_BEST_OF) * MAX_BEST_OF
+                self._next_id, self._id_end = max(first, MAX_BEST_OF), int(got["end_id"])
+        gid = self._next_id
+        self._next_id += MAX_BEST_OF
+        return gid
+
+    async def keep_registered_at_config_server(self, beat_s: float = 10.0):
+        """Holds the websocket that lists this master at the config server (prefill / decode nodes find the masters
+        there); opens it again when it breaks.  Reference: httpserver_for_pd_master/register_loop.py."""
+        import websockets
+
+        from ..pd_io_struct import PDMasterInfo
+
+        a = self.args
+        info = PDMasterInfo(os.getpid(), f"{a.host}:{a.port}")
+        while True:
+            try:
+                async with websockets.connect(f"ws://{a.config_server_host}:{a.config_server_port}/pd_master_register",
+                                              max_size=None) as ws:
+                    await ws.send(pickle.dumps(info))
+                    while True:
+                        await ws.send("beat")
+                        await asyncio.sleep(beat_s)
+            except asyncio.CancelledError:
+                raise
+            except Exception as e:  # noqa: BLE001
+                print(f"[pd_master] config server not reachable ({type(e).__name__}: {e}); retrying", flush=True)
+                await asyncio.sleep(3.0)
 
     # ---------------------------------------------------------------- registry
     def _refresh(self):
@@ -157,7 +202,7 @@ class HttpServerManagerForPDMaster:
             raise ServerBusyError("no complete prefill/decode topology is registered")
         if sampling_params.n != 1:
             raise ValueError("pd_master mode serves n == best_of == 1")
-        origin = self._next_id
+        origin = await self._take_id()
         p, d = self.selector.select_p_d_node(prompt, sampling_params, multimodal_params)
         sp = sampling_params.to_dict()
         total = int(sp["max_new_tokens"])
@@ -170,8 +215,7 @@ class HttpServerManagerForPDMaster:
         try:
             for bi, budget in enumerate(blocks):
                 last = bi == len(blocks) - 1
-                gid = self._next_id
-                self._next_id += MAX_BEST_OF
+                gid = origin if bi == 0 else await self._take_id()
                 self.alias[origin] = gid
                 sp_b = dict(sp)
                 sp_b["max_new_tokens"] = budget

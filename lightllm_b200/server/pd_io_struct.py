@@ -65,6 +65,13 @@ class PDClient:
 
 
 @dataclass
+class PDMasterInfo:
+    """What a pd_master leaves at the config server: prefill / decode nodes connect to `host_ip_port`."""
+    node_id: int
+    host_ip_port: str
+
+
+@dataclass
 class PDRegister:
     node_id: int
     client_ip_port: str
