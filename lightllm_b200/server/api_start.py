@@ -163,8 +163,11 @@ def run_http_server(args: StartArgs):
     import uvicorn
 
     set_env_start_args(args)
+    from .httpserver.pd_loop import ws_max_size
+
+    # websocket frames from prefill / decode nodes (prompt ids of long prompts): 128 MB unless the variable says otherwise
     uvicorn.run("lightllm_b200.server.api_http:app", host=args.host, port=args.port, workers=args.httpserver_workers,
-                log_level="warning", loop="uvloop", timeout_keep_alive=5)
+                log_level="warning", loop="uvloop", timeout_keep_alive=5, ws_max_size=ws_max_size() or (128 << 20))
 
 
 def normal_or_p_d_start(args: StartArgs, config_override: dict = None):
