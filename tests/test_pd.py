@@ -274,3 +274,58 @@ def test_kv_sender_peer_that_never_accepts():
     assert "failed" in got[2][2] and time.time() - t0 < 10   # the second try on a broken peer fails at once
     tx.close()
     silent.close()
+
+
+def test_nodes_follow_the_config_servers_list_of_masters(monkeypatch):
+    """One link per listed pd_master; a master that leaves the list is let go, a decode node gets one status queue
+    per master and a transfer note goes to all of them."""
+    from lightllm_b200.server.httpserver import pd_loop
+    from lightllm_b200.server.pd_io_struct import PDMasterInfo
+
+    started, cancelled = [], []
+
+    async def fake_link(g, url, *a, **kw):
+        started.append(("link", url))
+        try:
+            await asyncio.sleep(3600)
+        except asyncio.CancelledError:
+            cancelled.append(("link", url))
+            raise
+
+    async def fake_status(g, url, queue, *a, **kw):
+        started.append(("status", url))
+        try:
+            await asyncio.sleep(3600)
+        except asyncio.CancelledError:
+            cancelled.append(("status", url))
+            raise
+
+    monkeypatch.setattr(pd_loop, "pd_master_link", fake_link)
+    monkeypatch.setattr(pd_loop, "kv_status_link", fake_status)
+    listed = [PDMasterInfo(1, "10.0.0.1:9000")]
+
+    async def go():
+        g = SimpleNamespace(args=SimpleNamespace(run_mode="decode", config_server_host="h", config_server_port=1))
+        queues, links = {}, {}
+        task = asyncio.create_task(pd_loop.follow_config_server(g, queues, links, fetch=lambda: list(listed), every_s=0.05))
+        await asyncio.sleep(0.2)
+        assert set(links) == {"ws://10.0.0.1:9000"} and set(queues) == set(links)
+        listed.append(PDMasterInfo(2, "10.0.0.2:9000"))
+        await asyncio.sleep(0.2)
+        assert set(links) == {"ws://10.0.0.1:9000", "ws://10.0.0.2:9000"}
+        for q in queues.values():               # what kv_status_pump does with one note
+            await q.put(UpKVStatus(8, ok=True))
+        assert all(q.qsize() == 1 for q in queues.values())
+        del listed[0]
+        await asyncio.sleep(0.2)
+        assert set(links) == {"ws://10.0.0.2:9000"} and set(queues) == set(links)
+        assert sorted(cancelled) == [("link", "ws://10.0.0.1:9000"), ("status", "ws://10.0.0.1:9000")]
+        listed.clear()
+        listed.append(None)                     # a broken answer: the links stay as they are
+        await asyncio.sleep(0.2)
+        assert set(links) == {"ws://10.0.0.2:9000"}
+        task.cancel()
+
+    asyncio.run(go())
+    assert sorted(started) == [("link", "ws://10.0.0.1:9000"), ("link", "ws://10.0.0.2:9000"),
+                               ("status", "ws://10.0.0.1:9000"), ("status", "ws://10.0.0.2:9000")]
