@@ -75,6 +75,10 @@ class DeTokenizationManager:
                 tok, src_index = d.get_next_token_id_and_index()
                 text = decode_token(self.tokenizer, d, tok, self.eos_ids)
                 special = tok in self.all_special_ids
+                if r.is_aborted and src_index == r.finish_token_index and r.finish_status.get_status() == 3:
+                    # the place-holder token with which an aborted request is ended (the router writes one for a
+                    # request that never ran): it carries no text
+                    text, special = "", True
                 count = len(d.output_ids)
                 if d.stop_strs and d.stop_sequences_str_match():
                     # the ranks are told through the router; generation ends at this token
